@@ -1,0 +1,496 @@
+// Image augmentation + packing kernel for sm_100a.
+//
+// One launch transforms a whole batch.  A record is handled by a thread-block cluster of
+// `bands` CTAs; CTA b owns a band of output rows.  Each CTA
+//   1. builds the horizontal / vertical bilinear tap tables of the crop->output resize
+//      (the 11-bit fixed-point form cv::resize(INTER_LINEAR) uses for 8-bit images),
+//   2. resizes its band straight from the source image in global memory, applies the
+//      brightness/saturation matrix and the HSV hue shift per pixel, and keeps the band
+//      as planar uint8 in shared memory, already flipped and in output channel order,
+//   3. if contrast is active, reduces per-channel sums (warp shuffles, then shared memory)
+//      and exchanges the partial sums with the other CTAs of the cluster through
+//      distributed shared memory, so the per-image mean never touches global memory,
+//   4. applies contrast and lighting, converts to the output type, standardises and
+//      streams the band out with 128-bit stores into the record's slot of the batch buffer.
+//
+// The arithmetic of every stage is the integer / float32 arithmetic OpenCV applies for the
+// calls aeon makes (src/etl_image.cpp:146-202, src/image.cpp:336-406, src/etl_image.cpp:246-341);
+// this file is compiled with -fmad=false and uses explicit fused operations only where
+// OpenCV's own code is fused.
+#include <cooperative_groups.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/aeon_b200.h"
+#include "device_common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace aeonb
+{
+    namespace
+    {
+        constexpr int AUG_THREADS  = 256;
+        constexpr int AUG_MAX_BAND = 8; // portable cluster size limit
+
+        struct aug_launch
+        {
+            const aeonb_image_desc* descs; // device copy
+            aeonb_image_layout      layout;
+            int                     rows_per_band;
+            int                     tile_pitch; // bytes per tile row (multiple of 16)
+            int                     vector_ok;  // slots are 16-byte aligned with unit x stride
+        };
+
+        struct row_tap
+        {
+            int   y0, y1; // source rows inside the crop box (already clamped)
+            short b0, b1;
+        };
+
+        __device__ __forceinline__ int clamp_u8(int v) { return min(max(v, 0), 255); }
+
+        __device__ __forceinline__ short sat_s16(int v) { return (short)min(max(v, -32768), 32767); }
+
+        // Source index and tap weights for destination index d (cv::resize, INTER_LINEAR, 8-bit).
+        __device__ __forceinline__ void linear_tap(int d, int src_len, int dst_len, bool clamp_weights, int& s, short& w0, short& w1)
+        {
+            const double scale = 1.0 / ((double)dst_len / (double)src_len);
+            float        f     = (float)(((double)d + 0.5) * scale - 0.5);
+            float        fl    = floorf(f);
+            s                  = (int)fl;
+            f                  = f - fl;
+            if (clamp_weights)
+            {
+                if (s < 0)
+                {
+                    f = 0.f;
+                    s = 0;
+                }
+                if (s >= src_len - 1)
+                {
+                    f = 0.f;
+                    s = src_len - 1;
+                }
+            }
+            w0 = sat_s16(__float2int_rn((1.f - f) * 2048.f));
+            w1 = sat_s16(__float2int_rn(f * 2048.f));
+        }
+
+        __device__ __forceinline__ int nearest_tap(int d, int src_len, int dst_len)
+        {
+            const double scale = 1.0 / ((double)dst_len / (double)src_len);
+            return min((int)floor((double)d * scale), src_len - 1);
+        }
+
+        struct bgr
+        {
+            int b, g, r;
+        };
+
+        // Pixel of the (virtual) canvas at crop-relative coordinates.
+        template <int PIX>
+        __device__ __forceinline__ bgr fetch(const aeonb_image_desc& d, int x, int y)
+        {
+            const int sx = d.crop_x + x - d.canvas_x;
+            const int sy = d.crop_y + y - d.canvas_y;
+            bgr       p{0, 0, 0};
+            if ((unsigned)sx < (unsigned)d.src_w && (unsigned)sy < (unsigned)d.src_h)
+            {
+                const uint8_t* s = d.src + (size_t)sy * d.src_pitch + (size_t)sx * PIX;
+                if (PIX == 4)
+                {
+                    const uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(s));
+                    p.b              = v & 0xFF;
+                    p.g              = (v >> 8) & 0xFF;
+                    p.r              = (v >> 16) & 0xFF;
+                }
+                else
+                {
+                    p.b = __ldg(s);
+                    p.g = __ldg(s + 1);
+                    p.r = __ldg(s + 2);
+                }
+            }
+            return p;
+        }
+
+        // 8-bit BGR->HSV (H in [0,180)) with 12-bit reciprocal tables, then the hue shift with C
+        // remainder semantics stored through a uint8_t, then float32 HSV->BGR.
+        __device__ __forceinline__ bgr hue_rotate(bgr p, int hue, bool truncate, const int* sdiv, const int* hdiv)
+        {
+            const int v    = max(max(p.b, p.g), p.r);
+            const int vmin = min(min(p.b, p.g), p.r);
+            const int diff = v - vmin;
+            const int s    = (diff * sdiv[v] + (1 << 11)) >> 12;
+            int       h;
+            if (v == p.r)
+                h = p.g - p.b;
+            else if (v == p.g)
+                h = p.b - p.r + 2 * diff;
+            else
+                h = p.r - p.g + 4 * diff;
+            h = (h * hdiv[diff] + (1 << 11)) >> 12;
+            if (h < 0)
+                h += 180;
+            h = ((h + hue) % 180) & 0xFF;
+
+            const float hf     = (float)h * (6.0f / 180.0f);
+            const float sf     = (float)s * (1.0f / 255.0f);
+            const float vf     = (float)v * (1.0f / 255.0f);
+            const float fl     = floorf(hf);
+            const float f      = hf - fl;
+            int         sector = (int)fl;
+            if (sector >= 6)
+                sector -= 6; // h <= 255 gives sector <= 8
+            const float t1 = vf * (1.0f - sf);
+            const float t2 = vf * __fmaf_rn(-sf, f, 1.0f);
+            const float t3 = vf * __fmaf_rn(-sf, 1.0f - f, 1.0f);
+            float       fb, fg, fr;
+            switch (sector)
+            {
+            case 0: fb = t1; fg = t3; fr = vf; break;
+            case 1: fb = t1; fg = vf; fr = t2; break;
+            case 2: fb = t3; fg = vf; fr = t1; break;
+            case 3: fb = vf; fg = t2; fr = t1; break;
+            case 4: fb = vf; fg = t1; fr = t3; break;
+            default: fb = t2; fg = t1; fr = vf; break;
+            }
+            bgr o;
+            if (truncate)
+            {
+                o.b = clamp_u8(__float2int_rz(fb * 255.0f));
+                o.g = clamp_u8(__float2int_rz(fg * 255.0f));
+                o.r = clamp_u8(__float2int_rz(fr * 255.0f));
+            }
+            else
+            {
+                o.b = clamp_u8(__float2int_rn(fb * 255.0f));
+                o.g = clamp_u8(__float2int_rn(fg * 255.0f));
+                o.r = clamp_u8(__float2int_rn(fr * 255.0f));
+            }
+            return o;
+        }
+
+        template <typename T>
+        __device__ __forceinline__ T convert_out(int v);
+        template <>
+        __device__ __forceinline__ uint8_t convert_out<uint8_t>(int v) { return (uint8_t)v; }
+        template <>
+        __device__ __forceinline__ int8_t convert_out<int8_t>(int v) { return (int8_t)min(v, 127); }
+        template <>
+        __device__ __forceinline__ int16_t convert_out<int16_t>(int v) { return (int16_t)v; }
+        template <>
+        __device__ __forceinline__ uint16_t convert_out<uint16_t>(int v) { return (uint16_t)v; }
+        template <>
+        __device__ __forceinline__ int32_t convert_out<int32_t>(int v) { return v; }
+        template <>
+        __device__ __forceinline__ float convert_out<float>(int v) { return (float)v; }
+        template <>
+        __device__ __forceinline__ double convert_out<double>(int v) { return (double)v; }
+
+        template <typename T>
+        struct out_vec
+        {
+            static constexpr int N = 16 / sizeof(T);
+            T                    v[N];
+        };
+
+        template <typename T, int PIX>
+        __global__ void __launch_bounds__(AUG_THREADS) aug_pack_kernel(const aug_launch L)
+        {
+            extern __shared__ __align__(16) unsigned char smem[];
+            __shared__ aeonb_image_desc d;
+            __shared__ unsigned int     part_sum[3];  // this CTA's per-channel sums (output channel order)
+            __shared__ float            contrast_add[3];
+            __shared__ int              hsv_sdiv[256];
+            __shared__ int              hsv_hdiv[256];
+
+            cg::cluster_group cluster = cg::this_cluster();
+            const int         band    = blockIdx.x;
+            const int         bands   = gridDim.x;
+            const int         tid     = threadIdx.x;
+            const aeonb_image_layout& lay = L.layout;
+
+            // ---- record descriptor -> shared memory
+            {
+                const int* g = reinterpret_cast<const int*>(L.descs + blockIdx.y);
+                int*       s = reinterpret_cast<int*>(&d);
+                for (int i = tid; i < (int)(sizeof(aeonb_image_desc) / sizeof(int)); i += AUG_THREADS)
+                    s[i] = g[i];
+                if (tid < 3)
+                    part_sum[tid] = 0;
+            }
+            __syncthreads();
+
+            const int  out_w    = d.src ? d.out_w : 0;
+            const int  out_h    = d.src ? d.out_h : 0;
+            const int  row0     = band * L.rows_per_band;
+            const int  row_end  = min(row0 + L.rows_per_band, lay.slot_h);
+            const int  img_end  = min(row_end, out_h); // rows that carry image data
+            const int  pitch    = L.tile_pitch;
+            const int  plane    = L.rows_per_band * pitch;
+            const bool use_hue  = d.hue != 0;
+            const bool use_ctr  = d.contrast != 1.0f;
+            const bool swap_rb  = lay.bgr_to_rgb != 0;
+
+            unsigned char* tile = smem;                                            // [3][rows_per_band][pitch]
+            int*           xofs = reinterpret_cast<int*>(smem + 3 * plane);        // [out_w]
+            short2*        xw   = reinterpret_cast<short2*>(xofs + lay.slot_w);    // [out_w]
+            row_tap*       ytab = reinterpret_cast<row_tap*>(xw + lay.slot_w);     // [rows_per_band]
+
+            // ---- tap tables
+            for (int x = tid; x < out_w; x += AUG_THREADS)
+            {
+                int   s;
+                short a0 = 2048, a1 = 0;
+                if (d.interp == AEONB_INTERP_LINEAR)
+                    linear_tap(x, d.crop_w, out_w, true, s, a0, a1);
+                else
+                    s = nearest_tap(x, d.crop_w, out_w);
+                xofs[x] = s;
+                xw[x]   = make_short2(a0, a1);
+            }
+            for (int r = tid; r < img_end - row0; r += AUG_THREADS)
+            {
+                row_tap t;
+                if (d.interp == AEONB_INTERP_LINEAR)
+                {
+                    int s;
+                    linear_tap(row0 + r, d.crop_h, out_h, false, s, t.b0, t.b1);
+                    t.y0 = min(max(s, 0), d.crop_h - 1);
+                    t.y1 = min(max(s + 1, 0), d.crop_h - 1);
+                }
+                else
+                {
+                    t.y0 = t.y1 = nearest_tap(row0 + r, d.crop_h, out_h);
+                    t.b0        = 2048;
+                    t.b1        = 0;
+                }
+                ytab[r] = t;
+            }
+            if (use_hue)
+            {
+                for (int i = tid; i < 256; i += AUG_THREADS)
+                {
+                    hsv_sdiv[i] = i ? __double2int_rn((double)(255 << 12) / (double)i) : 0;
+                    hsv_hdiv[i] = i ? __double2int_rn((double)(180 << 12) / (6.0 * (double)i)) : 0;
+                }
+            }
+            // zero the tile so the padding columns/rows of the slot read as zero
+            for (int i = tid; i < 3 * plane / 16; i += AUG_THREADS)
+                reinterpret_cast<int4*>(tile)[i] = make_int4(0, 0, 0, 0);
+            __syncthreads();
+
+            // ---- resize + per-pixel photometric into the tile
+            unsigned int sum0 = 0, sum1 = 0, sum2 = 0;
+            {
+                const int npix = max(img_end - row0, 0) * out_w;
+                int       r = 0, x = tid;
+                while (out_w > 0 && x >= out_w)
+                {
+                    x -= out_w;
+                    ++r;
+                }
+                for (int p = tid; p < npix; p += AUG_THREADS)
+                {
+                    const row_tap t  = ytab[r];
+                    const int     sx = xofs[x];
+                    const short2  a  = xw[x];
+                    bgr           px;
+                    if (d.interp == AEONB_INTERP_LINEAR)
+                    {
+                        const int sx1 = min(sx + 1, d.crop_w - 1);
+                        const bgr p00 = fetch<PIX>(d, sx, t.y0);
+                        const bgr p01 = fetch<PIX>(d, sx1, t.y0);
+                        const bgr p10 = fetch<PIX>(d, sx, t.y1);
+                        const bgr p11 = fetch<PIX>(d, sx1, t.y1);
+                        // horizontal pass keeps 11 fractional bits; vertical pass as in OpenCV's 8-bit path
+                        const int hb0 = p00.b * a.x + p01.b * a.y, hb1 = p10.b * a.x + p11.b * a.y;
+                        const int hg0 = p00.g * a.x + p01.g * a.y, hg1 = p10.g * a.x + p11.g * a.y;
+                        const int hr0 = p00.r * a.x + p01.r * a.y, hr1 = p10.r * a.x + p11.r * a.y;
+                        px.b = clamp_u8((((t.b0 * (hb0 >> 4)) >> 16) + ((t.b1 * (hb1 >> 4)) >> 16) + 2) >> 2);
+                        px.g = clamp_u8((((t.b0 * (hg0 >> 4)) >> 16) + ((t.b1 * (hg1 >> 4)) >> 16) + 2) >> 2);
+                        px.r = clamp_u8((((t.b0 * (hr0 >> 4)) >> 16) + ((t.b1 * (hr1 >> 4)) >> 16) + 2) >> 2);
+                    }
+                    else
+                    {
+                        px = fetch<PIX>(d, sx, t.y0);
+                    }
+                    if (d.color_enable)
+                    {
+                        const short* m = d.color_matrix;
+                        const int    b = (px.b * m[0] + px.g * m[1] + px.r * m[2] + 512) >> 10;
+                        const int    g = (px.b * m[3] + px.g * m[4] + px.r * m[5] + 512) >> 10;
+                        const int    rr = (px.b * m[6] + px.g * m[7] + px.r * m[8] + 512) >> 10;
+                        px.b = clamp_u8(b);
+                        px.g = clamp_u8(g);
+                        px.r = clamp_u8(rr);
+                    }
+                    if (use_hue)
+                        px = hue_rotate(px, d.hue, x < d.hsv_vector_cols, hsv_sdiv, hsv_hdiv);
+
+                    const int xo = d.flip ? out_w - 1 - x : x;
+                    const int c0 = swap_rb ? px.r : px.b;
+                    const int c2 = swap_rb ? px.b : px.r;
+                    unsigned char* o = tile + r * pitch + xo;
+                    o[0]             = (unsigned char)c0;
+                    o[plane]         = (unsigned char)px.g;
+                    o[2 * plane]     = (unsigned char)c2;
+                    sum0 += c0;
+                    sum1 += px.g;
+                    sum2 += c2;
+
+                    x += AUG_THREADS;
+                    while (x >= out_w)
+                    {
+                        x -= out_w;
+                        ++r;
+                    }
+                }
+            }
+
+            // ---- per-image channel means for contrast, exchanged across the cluster
+            if (use_ctr)
+            {
+                sum0 = warp_sum(sum0);
+                sum1 = warp_sum(sum1);
+                sum2 = warp_sum(sum2);
+                if ((tid & 31) == 0)
+                {
+                    atomicAdd(&part_sum[0], sum0);
+                    atomicAdd(&part_sum[1], sum1);
+                    atomicAdd(&part_sum[2], sum2);
+                }
+                cluster.sync(); // all partial sums of the record are in place (also a CTA barrier)
+                if (tid < 3)
+                {
+                    unsigned long long total = 0;
+                    for (int b = 0; b < bands; ++b)
+                        total += *cluster.map_shared_rank(&part_sum[tid], b);
+                    const double mean = (double)total / (double)((long long)out_w * out_h);
+                    contrast_add[tid] = (float)((1.0 - (double)d.contrast) * mean);
+                }
+                cluster.sync(); // remote reads done before any CTA of the cluster may exit
+            }
+            else
+            {
+                __syncthreads();
+            }
+
+            // ---- contrast, lighting, conversion, standardisation, store
+            {
+                constexpr int VEC     = out_vec<T>::N;
+                const int     rows    = row_end - row0;
+                const int     chunks  = (lay.slot_w + VEC - 1) / VEC;
+                const int     total   = 3 * rows * chunks;
+                T*            dst     = reinterpret_cast<T*>(d.dst);
+                const bool    std_on  = lay.standardize != 0;
+                const bool    light   = d.lighting_enable != 0;
+                for (int i = tid; i < total; i += AUG_THREADS)
+                {
+                    const int chunk = i % chunks;
+                    const int rc    = i / chunks;
+                    const int r     = rc % rows;
+                    const int c     = rc / rows;
+                    const int x0    = chunk * VEC;
+                    const int y     = row0 + r;
+                    const int cin   = swap_rb ? 2 - c : c; // channel index in BGR order
+                    const unsigned char* src = tile + c * plane + r * pitch + x0;
+                    out_vec<T>           o;
+#pragma unroll
+                    for (int k = 0; k < VEC; ++k)
+                    {
+                        int        v       = src[k];
+                        const bool in_img  = (x0 + k < out_w) && (y < out_h);
+                        if (in_img)
+                        {
+                            if (use_ctr)
+                                v = clamp_u8(__float2int_rn((float)v * d.contrast + contrast_add[c]));
+                            if (light)
+                            {
+                                v = clamp_u8(__float2int_rn((float)v * d.lighting_scale));
+                                v = clamp_u8(v + d.lighting_offset[cin]);
+                            }
+                        }
+                        T e = convert_out<T>(v);
+                        if (std_on && in_img)
+                            e = standardize_value(e, lay, c);
+                        o.v[k] = e;
+                    }
+                    T* g = dst + (int64_t)c * lay.stride_c + (int64_t)y * lay.stride_y + (int64_t)x0 * lay.stride_x;
+                    if (L.vector_ok && x0 + VEC <= lay.slot_w)
+                    {
+                        *reinterpret_cast<int4*>(g) = *reinterpret_cast<const int4*>(o.v);
+                    }
+                    else
+                    {
+                        for (int k = 0; k < VEC && x0 + k < lay.slot_w; ++k)
+                            g[(int64_t)k * lay.stride_x] = o.v[k];
+                    }
+                }
+            }
+        }
+
+        template <typename T>
+        cudaError_t launch_typed(const aug_launch& L, int n, int bands, size_t smem, int pix, cudaStream_t stream)
+        {
+            auto kern = pix == 4 ? aug_pack_kernel<T, 4> : aug_pack_kernel<T, 3>;
+            cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (err != cudaSuccess)
+                return err;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim            = dim3(bands, n, 1);
+            cfg.blockDim           = dim3(AUG_THREADS, 1, 1);
+            cfg.dynamicSmemBytes   = smem;
+            cfg.stream             = stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id               = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = bands;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs                = attr;
+            cfg.numAttrs             = 1;
+            return cudaLaunchKernelEx(&cfg, kern, L);
+        }
+    }
+
+    // Host entry used by the C ABI: `descs_dev` is the device copy of the descriptors.
+    // Returns a CUDA error; *why is set for configurations the kernel does not cover.
+    cudaError_t launch_aug_pack(const aeonb_image_desc* descs_dev, int n, const aeonb_image_layout& layout, int pixel_stride,
+                                bool slots_aligned, cudaStream_t stream, const char** why)
+    {
+        *why = nullptr;
+        int bands = 1;
+        while (bands < AUG_MAX_BAND && layout.slot_h / (bands * 2) >= 8)
+            bands *= 2;
+        aug_launch L;
+        L.descs         = descs_dev;
+        L.layout        = layout;
+        L.rows_per_band = (layout.slot_h + bands - 1) / bands;
+        L.tile_pitch    = (layout.slot_w + 15) / 16 * 16;
+        const size_t elem = layout.dtype == AEONB_F64 ? 8 : layout.dtype == AEONB_F32 || layout.dtype == AEONB_I32 ? 4
+                          : layout.dtype == AEONB_I16 || layout.dtype == AEONB_U16 ? 2 : 1;
+        L.vector_ok = slots_aligned && layout.stride_x == 1 && (layout.stride_y * elem) % 16 == 0 &&
+                      (layout.stride_c * elem) % 16 == 0;
+        const size_t smem = (size_t)3 * L.rows_per_band * L.tile_pitch + (size_t)layout.slot_w * (sizeof(int) + sizeof(short2)) +
+                            (size_t)L.rows_per_band * sizeof(row_tap) + 16;
+        if (smem > 200 * 1024)
+        {
+            *why = "output image too large for the on-chip band tile (rows/8 * width * 3 must stay under 200 KB)";
+            return cudaErrorInvalidValue;
+        }
+        switch (layout.dtype)
+        {
+        case AEONB_U8: return launch_typed<uint8_t>(L, n, bands, smem, pixel_stride, stream);
+        case AEONB_I8: return launch_typed<int8_t>(L, n, bands, smem, pixel_stride, stream);
+        case AEONB_I16: return launch_typed<int16_t>(L, n, bands, smem, pixel_stride, stream);
+        case AEONB_U16: return launch_typed<uint16_t>(L, n, bands, smem, pixel_stride, stream);
+        case AEONB_I32: return launch_typed<int32_t>(L, n, bands, smem, pixel_stride, stream);
+        case AEONB_F32: return launch_typed<float>(L, n, bands, smem, pixel_stride, stream);
+        case AEONB_F64: return launch_typed<double>(L, n, bands, smem, pixel_stride, stream);
+        }
+        *why = "unknown output dtype";
+        return cudaErrorInvalidValue;
+    }
+}

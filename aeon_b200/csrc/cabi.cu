@@ -1,0 +1,339 @@
+// C ABI: context management and the batch-kernel entry points.
+#include <algorithm>
+#include <cstring>
+#include <sstream>
+#include <vector>
+
+#include "context.hpp"
+
+namespace aeonb
+{
+    namespace
+    {
+        thread_local std::string g_last_error;
+    }
+
+    void set_last_error(const std::string& msg) { g_last_error = msg; }
+
+    int fail(int code, const std::string& msg)
+    {
+        g_last_error = msg;
+        return code;
+    }
+
+    std::string cuda_message(const char* what, cudaError_t e)
+    {
+        std::ostringstream ss;
+        ss << what << " failed: " << cudaGetErrorName(e) << " (" << cudaGetErrorString(e) << ")";
+        return ss.str();
+    }
+
+    void staging_slot::reserve(size_t bytes)
+    {
+        if (bytes <= capacity)
+            return;
+        release();
+        size_t cap = std::max<size_t>(bytes, 64 * 1024);
+        AEONB_CUDA(cudaMallocHost(&host, cap));
+        AEONB_CUDA(cudaMalloc(&dev, cap));
+        if (!copied)
+            AEONB_CUDA(cudaEventCreateWithFlags(&copied, cudaEventDisableTiming));
+        capacity = cap;
+    }
+
+    void staging_slot::release()
+    {
+        if (host)
+            cudaFreeHost(host);
+        if (dev)
+            cudaFree(dev);
+        host = dev = nullptr;
+        capacity   = 0;
+    }
+}
+
+using namespace aeonb;
+
+void* aeonb_ctx::upload(const void* host, size_t bytes)
+{
+    staging_slot& slot = ring[ring_next];
+    ring_next          = (ring_next + 1) % ring.size();
+    if (slot.busy)
+    {
+        AEONB_CUDA(cudaEventSynchronize(slot.copied));
+        slot.busy = false;
+    }
+    if (bytes > slot.capacity)
+    {
+        // A kernel enqueued earlier may still read the old device buffer.
+        AEONB_CUDA(cudaStreamSynchronize(stream));
+        slot.reserve(bytes);
+    }
+    std::memcpy(slot.host, host, bytes);
+    AEONB_CUDA(cudaMemcpyAsync(slot.dev, slot.host, bytes, cudaMemcpyHostToDevice, stream));
+    AEONB_CUDA(cudaEventRecord(slot.copied, stream));
+    slot.busy = true;
+    return slot.dev;
+}
+
+extern "C" {
+
+const char* aeonb_last_error(void)
+{
+    return g_last_error.c_str();
+}
+
+const char* aeonb_version(void)
+{
+    return "aeon_b200 0.1 (sm_100a)";
+}
+
+int aeonb_ctx_create(int device, void* stream, aeonb_ctx** out)
+{
+    return guarded([&]() {
+        if (!out)
+            throw std::invalid_argument("aeonb_ctx_create: out is NULL");
+        int count = 0;
+        AEONB_CUDA(cudaGetDeviceCount(&count));
+        if (device < 0 || device >= count)
+            throw std::invalid_argument("aeonb_ctx_create: no such CUDA device");
+        AEONB_CUDA(cudaSetDevice(device));
+        auto* ctx   = new aeonb_ctx();
+        ctx->device = device;
+        if (stream)
+            ctx->stream = static_cast<cudaStream_t>(stream);
+        else
+        {
+            AEONB_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+            ctx->own_stream = true;
+        }
+        ctx->ring.resize(8);
+        *out = ctx;
+        return AEONB_OK;
+    });
+}
+
+void aeonb_ctx_destroy(aeonb_ctx* ctx)
+{
+    if (!ctx)
+        return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (auto& s : ctx->ring)
+    {
+        s.release();
+        if (s.copied)
+            cudaEventDestroy(s.copied);
+    }
+    if (ctx->own_stream)
+        cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+void* aeonb_ctx_stream(aeonb_ctx* ctx)
+{
+    return ctx ? ctx->stream : nullptr;
+}
+
+int aeonb_ctx_synchronize(aeonb_ctx* ctx)
+{
+    return guarded([&]() {
+        if (!ctx)
+            throw std::invalid_argument("context is NULL");
+        AEONB_CUDA(cudaStreamSynchronize(ctx->stream));
+        return AEONB_OK;
+    });
+}
+
+static size_t dtype_size(int dtype)
+{
+    switch (dtype)
+    {
+    case AEONB_U8:
+    case AEONB_I8: return 1;
+    case AEONB_I16:
+    case AEONB_U16: return 2;
+    case AEONB_I32:
+    case AEONB_F32: return 4;
+    case AEONB_F64: return 8;
+    }
+    throw std::invalid_argument("unknown output dtype");
+}
+
+static void check_image_batch(const aeonb_image_desc* d, int n, const aeonb_image_layout& L, int& pixel_stride, bool& aligned)
+{
+    if (L.slot_w <= 0 || L.slot_h <= 0)
+        throw std::invalid_argument("invalid width or height of the output slot");
+    if (L.channels != 3)
+        throw error(AEONB_ERR_UNSUPPORTED, "the image kernel handles 3-channel images only");
+    if (L.standardize && !(L.dtype == AEONB_F32 || L.dtype == AEONB_F64))
+        throw std::invalid_argument(
+            "Standardization (mean, stddev) is supported only for float or double 'output_type'.");
+    dtype_size(L.dtype);
+    pixel_stride = 0;
+    aligned      = true;
+    for (int i = 0; i < n; ++i)
+    {
+        const aeonb_image_desc& r = d[i];
+        std::ostringstream      ss;
+        if (!r.dst)
+            ss << "record " << i << ": destination is NULL";
+        else if (r.src)
+        {
+            if (r.src_pixel_stride != 3 && r.src_pixel_stride != 4)
+                ss << "record " << i << ": source pixel stride must be 3 or 4";
+            else if (pixel_stride && r.src_pixel_stride != pixel_stride)
+                ss << "record " << i << ": all sources of a batch must share one pixel stride";
+            else if (r.src_w <= 0 || r.src_h <= 0 || r.src_pitch < r.src_w * r.src_pixel_stride)
+                ss << "record " << i << ": invalid source size or pitch";
+            else if (r.src_pixel_stride == 4 && (((uintptr_t)r.src | (uintptr_t)r.src_pitch) & 3))
+                ss << "record " << i << ": 4-byte pixels need a 4-byte aligned source and pitch";
+            else if (r.canvas_x < 0 || r.canvas_y < 0 || r.canvas_x + r.src_w > r.canvas_w || r.canvas_y + r.src_h > r.canvas_h)
+                ss << "record " << i << ": Invalid parameters to expand image";
+            else if (r.crop_w <= 0 || r.crop_h <= 0 || r.crop_x < 0 || r.crop_y < 0 || r.crop_x + r.crop_w > r.canvas_w ||
+                     r.crop_y + r.crop_h > r.canvas_h)
+                ss << "record " << i << ": crop box (" << r.crop_x << "," << r.crop_y << " " << r.crop_w << "x" << r.crop_h
+                   << ") is outside the " << r.canvas_w << "x" << r.canvas_h << " image";
+            else if (r.out_w <= 0 || r.out_h <= 0 || r.out_w > L.slot_w || r.out_h > L.slot_h)
+                ss << "record " << i << ": output size " << r.out_w << "x" << r.out_h << " does not fit the slot";
+            else if (r.interp != AEONB_INTERP_LINEAR && r.interp != AEONB_INTERP_NEAREST)
+                ss << "record " << i << ": interpolation method outside the accelerated set (NEAREST, LINEAR)";
+            if (r.src_pixel_stride == 3 || r.src_pixel_stride == 4)
+                pixel_stride = r.src_pixel_stride;
+        }
+        const std::string msg = ss.str();
+        if (!msg.empty())
+            throw std::invalid_argument(msg);
+        if ((uintptr_t)r.dst & 15)
+            aligned = false;
+    }
+    if (!pixel_stride)
+        pixel_stride = 3;
+}
+
+int aeonb_image_batch(aeonb_ctx* ctx, const aeonb_image_desc* descs, int n, const aeonb_image_layout* layout)
+{
+    return guarded([&]() {
+        if (!ctx || !layout || (n > 0 && !descs))
+            throw std::invalid_argument("aeonb_image_batch: NULL argument");
+        if (n <= 0)
+            return AEONB_OK;
+        int  pixel_stride;
+        bool aligned;
+        check_image_batch(descs, n, *layout, pixel_stride, aligned);
+        AEONB_CUDA(cudaSetDevice(ctx->device));
+        auto* dev = static_cast<const aeonb_image_desc*>(ctx->upload(descs, sizeof(aeonb_image_desc) * n));
+        const char* why = nullptr;
+        cudaError_t e   = launch_aug_pack(dev, n, *layout, pixel_stride, aligned, ctx->stream, &why);
+        if (why)
+            throw error(AEONB_ERR_UNSUPPORTED, why);
+        if (e != cudaSuccess)
+            throw error(AEONB_ERR_CUDA, cuda_message("image kernel launch", e));
+        ctx->launches++;
+        return AEONB_OK;
+    });
+}
+
+int64_t aeonb_image_batch_bytes(const aeonb_image_desc* descs, int n, const aeonb_image_layout* layout)
+{
+    if (!descs || !layout)
+        return 0;
+    int64_t total = 0;
+    size_t  esz   = 1;
+    try
+    {
+        esz = dtype_size(layout->dtype);
+    }
+    catch (...)
+    {
+        return 0;
+    }
+    for (int i = 0; i < n; ++i)
+    {
+        const aeonb_image_desc& r = descs[i];
+        if (r.src)
+        {
+            // part of the crop box that lies on the source image; canvas zeros are never read
+            int64_t x0 = std::max(r.crop_x, r.canvas_x), x1 = std::min(r.crop_x + r.crop_w, r.canvas_x + r.src_w);
+            int64_t y0 = std::max(r.crop_y, r.canvas_y), y1 = std::min(r.crop_y + r.crop_h, r.canvas_y + r.src_h);
+            if (x1 > x0 && y1 > y0)
+                total += (x1 - x0) * (y1 - y0) * 3;
+        }
+        total += (int64_t)layout->slot_w * layout->slot_h * layout->channels * esz;
+    }
+    return total;
+}
+
+int aeonb_jpeg_backend_batch(aeonb_ctx* ctx, const aeonb_jpeg_desc* descs, int n)
+{
+    return guarded([&]() {
+        if (!ctx || (n > 0 && !descs))
+            throw std::invalid_argument("aeonb_jpeg_backend_batch: NULL argument");
+        if (n <= 0)
+            return AEONB_OK;
+        std::vector<int2> work;
+        size_t            smem = 0;
+        for (int i = 0; i < n; ++i)
+        {
+            const aeonb_jpeg_desc& r = descs[i];
+            std::ostringstream     ss;
+            const bool sampling_ok = r.ncomp == 1 || (r.ncomp == 3 && r.hs[1] == 1 && r.vs[1] == 1 && r.hs[2] == 1 && r.vs[2] == 1 &&
+                                                      ((r.hs[0] == 1 && r.vs[0] == 1) || (r.hs[0] == 2 && r.vs[0] == 1) ||
+                                                       (r.hs[0] == 2 && r.vs[0] == 2)));
+            if (r.width <= 0 || r.height <= 0 || !r.dst)
+                ss << "record " << i << ": empty image or NULL destination";
+            else if (!sampling_ok || (r.ncomp == 1 && (r.hs[0] != 1 || r.vs[0] != 1)))
+                ss << "record " << i << ": unsupported component layout (supported: grey, 4:4:4, 4:2:2, 4:2:0)";
+            else if (r.dst_pixel_stride != 3 && r.dst_pixel_stride != 4)
+                ss << "record " << i << ": destination pixel stride must be 3 or 4";
+            else if (r.dst_pitch < r.width * r.dst_pixel_stride || (r.dst_pitch & (r.dst_pixel_stride == 4 ? 15 : 3)) ||
+                     ((uintptr_t)r.dst & (r.dst_pixel_stride == 4 ? 15 : 3)))
+                ss << "record " << i << ": destination must be " << (r.dst_pixel_stride == 4 ? 16 : 4)
+                   << "-byte aligned with a pitch that is a multiple of that";
+            else
+            {
+                for (int c = 0; c < r.ncomp; ++c)
+                {
+                    if (!r.coef[c] || !r.quant[c] || ((uintptr_t)r.coef[c] & 15) || ((uintptr_t)r.quant[c] & 1))
+                        ss << "record " << i << ": coefficient planes must be 16-byte aligned device pointers";
+                    else if (r.blocks_w[c] * 8 * r.hs[0] / r.hs[c] < r.width || r.blocks_h[c] * 8 * r.vs[0] / r.vs[c] < r.height ||
+                             r.blocks_w[c] != r.blocks_w[0] / r.hs[0] * r.hs[c] || r.blocks_h[c] != r.blocks_h[0] / r.vs[0] * r.vs[c])
+                        ss << "record " << i << ": coefficient plane size does not match the image";
+                }
+            }
+            const std::string msg = ss.str();
+            if (!msg.empty())
+                throw std::invalid_argument(msg);
+            smem = std::max(smem, jpeg_backend_smem(r));
+            const int mcu_rows = r.blocks_h[0] / r.vs[0];
+            for (int m = 0; m < mcu_rows; ++m)
+                if (m * r.vs[0] * 8 < r.height)
+                    work.push_back(make_int2(i, m));
+        }
+        if (smem > 200 * 1024)
+            throw error(AEONB_ERR_UNSUPPORTED, "image too wide for the on-chip MCU-row strip");
+        AEONB_CUDA(cudaSetDevice(ctx->device));
+        auto* ddev = static_cast<const aeonb_jpeg_desc*>(ctx->upload(descs, sizeof(aeonb_jpeg_desc) * n));
+        auto* wdev = static_cast<const int2*>(ctx->upload(work.data(), sizeof(int2) * work.size()));
+        cudaError_t e = launch_jpeg_backend(ddev, wdev, (int)work.size(), smem, ctx->stream);
+        if (e != cudaSuccess)
+            throw error(AEONB_ERR_CUDA, cuda_message("jpeg back-end kernel launch", e));
+        ctx->launches++;
+        return AEONB_OK;
+    });
+}
+
+int64_t aeonb_jpeg_backend_bytes(const aeonb_jpeg_desc* descs, int n)
+{
+    int64_t total = 0;
+    for (int i = 0; descs && i < n; ++i)
+    {
+        const aeonb_jpeg_desc& r = descs[i];
+        for (int c = 0; c < r.ncomp; ++c)
+            total += (int64_t)r.blocks_w[c] * r.blocks_h[c] * 64 * 2;
+        total += (int64_t)r.width * r.height * 3;
+    }
+    return total;
+}
+
+} // extern "C"

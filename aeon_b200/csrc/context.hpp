@@ -1,0 +1,94 @@
+// Per-GPU context behind the C ABI: stream, descriptor staging ring, scratch arena.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/aeon_b200.h"
+
+namespace aeonb
+{
+    // Status + message carried across the C boundary (aeon throws; the ABI returns codes).
+    struct error : std::runtime_error
+    {
+        int code;
+        error(int c, const std::string& what) : std::runtime_error(what), code(c) {}
+    };
+
+    void        set_last_error(const std::string& msg);
+    int         fail(int code, const std::string& msg);
+    std::string cuda_message(const char* what, cudaError_t e);
+
+#define AEONB_CUDA(call)                                                                                               \
+    do                                                                                                                 \
+    {                                                                                                                  \
+        cudaError_t e__ = (call);                                                                                      \
+        if (e__ != cudaSuccess)                                                                                        \
+            throw ::aeonb::error(AEONB_ERR_CUDA, ::aeonb::cuda_message(#call, e__));                                   \
+    } while (0)
+
+    // Runs `fn`, translating exceptions into a status code + thread-local message.
+    template <typename F>
+    int guarded(F&& fn)
+    {
+        try
+        {
+            return fn();
+        }
+        catch (const error& e)
+        {
+            return fail(e.code, e.what());
+        }
+        catch (const std::invalid_argument& e)
+        {
+            return fail(AEONB_ERR_INVALID, e.what());
+        }
+        catch (const std::exception& e)
+        {
+            return fail(AEONB_ERR_DECODE, e.what());
+        }
+    }
+
+    // A pinned host buffer paired with a device buffer of the same size; used to ship small
+    // descriptor arrays (and, in the provider, coefficient planes) with one async copy.
+    struct staging_slot
+    {
+        void*       host     = nullptr;
+        void*       dev      = nullptr;
+        size_t      capacity = 0;
+        cudaEvent_t copied   = nullptr; // recorded after the last H2D copy out of `host`
+        bool        busy     = false;
+        void        reserve(size_t bytes);
+        void        release();
+    };
+}
+
+struct aeonb_ctx
+{
+    int                                device     = 0;
+    cudaStream_t                       stream     = nullptr;
+    bool                               own_stream = false;
+    std::vector<aeonb::staging_slot>   ring;      // descriptor staging
+    size_t                             ring_next  = 0;
+    int64_t                            launches   = 0; // kernels launched through this context
+
+    // Copies `bytes` of host data to the device on the stream; the returned device pointer is
+    // valid for kernels enqueued after this call.
+    void* upload(const void* host, size_t bytes);
+};
+
+namespace aeonb
+{
+    // Kernel launchers (defined next to the kernels).
+    cudaError_t launch_aug_pack(const aeonb_image_desc* descs_dev, int n, const aeonb_image_layout& layout, int pixel_stride,
+                                bool slots_aligned, cudaStream_t stream, const char** why);
+    cudaError_t launch_jpeg_backend(const aeonb_jpeg_desc* descs_dev, const int2* work_dev, int n_work, size_t smem,
+                                    cudaStream_t stream);
+    size_t      jpeg_backend_smem(const aeonb_jpeg_desc& d);
+    cudaError_t launch_specgram(const aeonb_specgram_desc* descs_dev, int n, const aeonb_specgram_config& cfg,
+                                const float* window_dev, const float* fbank_dev, cudaStream_t stream, const char** why);
+}

@@ -1,0 +1,44 @@
+// Host half of JPEG decoding: marker parsing and baseline Huffman entropy decoding.
+//
+// aeon calls cv::imdecode per record (src/etl_image.cpp:83-99, src/cap_mjpeg_decoder.cpp:132-147).
+// The serial, bit-granular part of that work stays on the CPU here; it produces quantised
+// DCT coefficient blocks which the GPU back end turns into pixels.  Coefficients of a block
+// are written in column-major order (element (row r, column c) at index c*8+r) so that a GPU
+// thread that owns one block column reads its eight values with a single 128-bit load.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <string>
+
+#include "../../../include/aeon_b200.h"
+
+namespace aeonb
+{
+    struct jpeg_frame
+    {
+        aeonb_jpeg_info info{};
+        uint16_t        quant[3][64]{}; // column-major, per component
+        // scan description
+        const uint8_t* scan          = nullptr; // first entropy-coded byte
+        size_t         scan_size     = 0;
+        int            restart_interval = 0;
+        int            dc_table[3]{};
+        int            ac_table[3]{};
+        struct huff
+        {
+            bool     present = false;
+            uint8_t  bits[17]{};
+            uint8_t  vals[256]{};
+        } dc[4], ac[4];
+    };
+
+    // Parses the headers up to the start of scan.  Throws aeonb::error(AEONB_ERR_DECODE) with
+    // aeon's message ("Decoding image failed due to invalid data in the image file.") on
+    // anything that is not a baseline sequential 8-bit JPEG with 1 or 3 components.
+    void jpeg_parse(const void* data, size_t size, jpeg_frame& frame);
+
+    // Entropy-decodes the scan.  coef[c] must hold info.coef_count[c] int16 values; they are
+    // fully overwritten (absent coefficients are zero).
+    void jpeg_entropy_decode(const jpeg_frame& frame, int16_t* const coef[3]);
+}

@@ -1,0 +1,385 @@
+// JPEG back-end kernel for sm_100a: dequantisation, 8x8 integer inverse DCT, chroma
+// upsampling and YCbCr->BGR for a whole batch in one launch.
+//
+// The host has already undone the entropy coding; this kernel does everything else
+// cv::imdecode does for a baseline JPEG (aeon: src/etl_image.cpp:83-99,
+// src/cap_mjpeg_decoder.cpp:132-147), with the arithmetic of libjpeg's default decoder
+// settings: the 13-bit-constant Loeffler-Ligtenberg-Moschytz inverse DCT with two guard
+// bits between the column and row passes, triangle-filter ("fancy") chroma upsampling and
+// 16-bit fixed-point colour conversion.
+//
+// Work decomposition: one CTA per (record, MCU row).  Eight threads cooperate on a block:
+// in the column pass thread c loads column c of the block with one 128-bit load (the host
+// stores blocks column-major for exactly this), in the row pass thread r owns row r; the
+// 8x8 transpose in between goes through a conflict-free padded shared-memory scratch.
+// Samples land in shared-memory component planes; the CTA also transforms the chroma
+// blocks of the MCU rows above and below, because the triangle filter needs one chroma
+// row on either side.  A second phase upsamples, converts and writes 4 pixels per thread
+// (one 128-bit store per thread for 4-byte pixels, three 32-bit stores for 3-byte pixels).
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/aeon_b200.h"
+
+namespace aeonb
+{
+    namespace
+    {
+        constexpr int JPG_THREADS = 256;
+        constexpr int WS_BLOCK    = 72; // int32 words per block in the transpose scratch (8 rows * stride 9)
+
+        struct jpeg_launch
+        {
+            const aeonb_jpeg_desc* descs; // device
+            const int2*            work;  // device: (record, mcu row) per CTA
+        };
+
+        __device__ __forceinline__ int clamp255(int v) { return min(max(v, 0), 255); }
+
+        constexpr int CONST_BITS = 13;
+        constexpr int PASS1_BITS = 2;
+        constexpr int C_0_298631336 = 2446;
+        constexpr int C_0_390180644 = 3196;
+        constexpr int C_0_541196100 = 4433;
+        constexpr int C_0_765366865 = 6270;
+        constexpr int C_0_899976223 = 7373;
+        constexpr int C_1_175875602 = 9633;
+        constexpr int C_1_501321110 = 12299;
+        constexpr int C_1_847759065 = 15137;
+        constexpr int C_1_961570560 = 16069;
+        constexpr int C_2_053119869 = 16819;
+        constexpr int C_2_562915447 = 20995;
+        constexpr int C_3_072711026 = 25172;
+
+        // One 8-point inverse DCT (LLM factorisation); inputs x[0..7] are frequency samples,
+        // outputs are descaled by `shift` with round-half-up.
+        template <int SHIFT>
+        __device__ __forceinline__ void idct8(const int (&x)[8], int (&o)[8])
+        {
+            int z1 = (x[2] + x[6]) * C_0_541196100;
+            int t2 = z1 - x[6] * C_1_847759065;
+            int t3 = z1 + x[2] * C_0_765366865;
+            int t0 = (x[0] + x[4]) << CONST_BITS;
+            int t1 = (x[0] - x[4]) << CONST_BITS;
+            const int e0 = t0 + t3, e3 = t0 - t3, e1 = t1 + t2, e2 = t1 - t2;
+
+            int o0 = x[7], o1 = x[5], o2 = x[3], o3 = x[1];
+            z1       = o0 + o3;
+            int z2   = o1 + o2;
+            int z3   = o0 + o2;
+            int z4   = o1 + o3;
+            const int z5 = (z3 + z4) * C_1_175875602;
+            o0 *= C_0_298631336;
+            o1 *= C_2_053119869;
+            o2 *= C_3_072711026;
+            o3 *= C_1_501321110;
+            z1 = -z1 * C_0_899976223;
+            z2 = -z2 * C_2_562915447;
+            z3 = -z3 * C_1_961570560 + z5;
+            z4 = -z4 * C_0_390180644 + z5;
+            o0 += z1 + z3;
+            o1 += z2 + z4;
+            o2 += z2 + z3;
+            o3 += z1 + z4;
+            constexpr int RND = 1 << (SHIFT - 1);
+            o[0] = (e0 + o3 + RND) >> SHIFT;
+            o[7] = (e0 - o3 + RND) >> SHIFT;
+            o[1] = (e1 + o2 + RND) >> SHIFT;
+            o[6] = (e1 - o2 + RND) >> SHIFT;
+            o[2] = (e2 + o1 + RND) >> SHIFT;
+            o[5] = (e2 - o1 + RND) >> SHIFT;
+            o[3] = (e3 + o0 + RND) >> SHIFT;
+            o[4] = (e3 - o0 + RND) >> SHIFT;
+        }
+
+        // A list of block rows to transform: component, block row in the coefficient plane,
+        // destination row in the shared sample plane, and which sample rows are wanted.
+        struct block_row_job
+        {
+            int comp;
+            int block_row;
+            int dst_row;   // sample row in the shared plane where block row 0 would land
+            int only_row;  // -1: all eight rows; else only this row of the block is stored
+        };
+
+        __device__ __forceinline__ void store_bgr4(uint8_t* dst, int pix, const int (&b)[4], const int (&g)[4], const int (&r)[4], int n)
+        {
+            if (pix == 4 && n == 4)
+            {
+                uint4 v;
+                v.x = b[0] | (g[0] << 8) | (r[0] << 16);
+                v.y = b[1] | (g[1] << 8) | (r[1] << 16);
+                v.z = b[2] | (g[2] << 8) | (r[2] << 16);
+                v.w = b[3] | (g[3] << 8) | (r[3] << 16);
+                *reinterpret_cast<uint4*>(dst) = v;
+            }
+            else if (pix == 3 && n == 4)
+            {
+                uint32_t* d = reinterpret_cast<uint32_t*>(dst);
+                d[0]        = b[0] | (g[0] << 8) | (r[0] << 16) | (b[1] << 24);
+                d[1]        = g[1] | (r[1] << 8) | (b[2] << 16) | (g[2] << 24);
+                d[2]        = r[2] | (b[3] << 8) | (g[3] << 16) | (r[3] << 24);
+            }
+            else
+            {
+                for (int k = 0; k < n; ++k)
+                {
+                    dst[k * pix + 0] = (uint8_t)b[k];
+                    dst[k * pix + 1] = (uint8_t)g[k];
+                    dst[k * pix + 2] = (uint8_t)r[k];
+                    if (pix == 4)
+                        dst[k * pix + 3] = 0;
+                }
+            }
+        }
+
+        __global__ void __launch_bounds__(JPG_THREADS) jpeg_backend_kernel(const jpeg_launch L)
+        {
+            extern __shared__ __align__(16) unsigned char smem[];
+            __shared__ aeonb_jpeg_desc d;
+            __shared__ uint16_t        quant[3][64];
+            __shared__ block_row_job   jobs[8];
+            __shared__ int             njobs;
+
+            const int  tid  = threadIdx.x;
+            const int2 wk   = L.work[blockIdx.x];
+            const int  mrow = wk.y;
+            {
+                const int* g = reinterpret_cast<const int*>(L.descs + wk.x);
+                int*       s = reinterpret_cast<int*>(&d);
+                for (int i = tid; i < (int)(sizeof(aeonb_jpeg_desc) / sizeof(int)); i += JPG_THREADS)
+                    s[i] = g[i];
+            }
+            __syncthreads();
+            for (int i = tid; i < d.ncomp * 64; i += JPG_THREADS)
+                quant[i >> 6][i & 63] = __ldg(d.quant[i >> 6] + (i & 63));
+
+            const int ncomp = d.ncomp;
+            const int hs0 = d.hs[0], vs0 = d.vs[0];           // luma sampling == MCU size in blocks
+            const int fh = ncomp == 3 ? hs0 : 1;              // horizontal / vertical chroma upsampling factors
+            const int fv = ncomp == 3 ? vs0 : 1;
+            const int yw = d.blocks_w[0] * 8;                 // luma plane pitch (bytes)
+            const int cwp = ncomp == 3 ? d.blocks_w[1] * 8 : 0; // chroma plane pitch
+            const int yrows = vs0 * 8;
+            const int crows = 8 + (fv == 2 ? 2 : 0);          // chroma rows kept, incl. one halo row above/below for 2x vertical
+            uint8_t*  yplane  = smem;
+            uint8_t*  cbplane = yplane + yrows * yw;
+            uint8_t*  crplane = cbplane + crows * cwp;
+            int*      scratch = reinterpret_cast<int*>(smem + ((yrows * yw + 2 * crows * cwp + 15) & ~15));
+
+            if (tid == 0)
+            {
+                int n = 0;
+                for (int v = 0; v < vs0; ++v)
+                    jobs[n++] = block_row_job{0, mrow * vs0 + v, v * 8, -1};
+                if (ncomp == 3)
+                {
+                    const int halo = fv == 2 ? 1 : 0;
+                    for (int c = 1; c < 3; ++c)
+                    {
+                        jobs[n++] = block_row_job{c, mrow, halo, -1};
+                        if (halo && mrow > 0)
+                            jobs[n++] = block_row_job{c, mrow - 1, halo - 8, 7};
+                        if (halo && mrow + 1 < d.blocks_h[c])
+                            jobs[n++] = block_row_job{c, mrow + 1, halo + 8, 0};
+                    }
+                }
+                njobs = n;
+            }
+            __syncthreads();
+
+            // ---- phase 1: dequantise + inverse DCT into the shared sample planes
+            {
+                const int lane8 = tid & 7;                 // column in pass 1, row in pass 2
+                const int slot  = tid >> 3;                // block slot inside the CTA (32 per iteration)
+                int*      ws    = scratch + slot * WS_BLOCK;
+                for (int j = 0; j < njobs; ++j)
+                {
+                    const block_row_job job = jobs[j];
+                    const int           bw  = d.blocks_w[job.comp];
+                    const int16_t*      src = d.coef[job.comp] + (size_t)job.block_row * bw * 64;
+                    uint8_t*            plane = job.comp == 0 ? yplane : job.comp == 1 ? cbplane : crplane;
+                    const int           pitch = job.comp == 0 ? yw : cwp;
+                    const uint16_t*     q     = quant[job.comp] + lane8 * 8;
+                    for (int b0 = 0; b0 < bw; b0 += JPG_THREADS / 8)
+                    {
+                        const int  b      = b0 + slot;
+                        const bool active = b < bw;
+                        int        col[8];
+                        if (active)
+                        {
+                            const int4 raw = __ldg(reinterpret_cast<const int4*>(src + (size_t)b * 64 + lane8 * 8));
+                            int        x[8];
+                            x[0] = (short)(raw.x & 0xFFFF) * q[0];
+                            x[1] = (raw.x >> 16) * q[1];
+                            x[2] = (short)(raw.y & 0xFFFF) * q[2];
+                            x[3] = (raw.y >> 16) * q[3];
+                            x[4] = (short)(raw.z & 0xFFFF) * q[4];
+                            x[5] = (raw.z >> 16) * q[5];
+                            x[6] = (short)(raw.w & 0xFFFF) * q[6];
+                            x[7] = (raw.w >> 16) * q[7];
+                            idct8<CONST_BITS - PASS1_BITS>(x, col);
+#pragma unroll
+                            for (int r = 0; r < 8; ++r)
+                                ws[r * 9 + lane8] = col[r];
+                        }
+                        __syncwarp();
+                        if (active && (job.only_row < 0 || job.only_row == lane8))
+                        {
+                            int x[8], o[8];
+#pragma unroll
+                            for (int c = 0; c < 8; ++c)
+                                x[c] = ws[lane8 * 9 + c];
+                            idct8<CONST_BITS + PASS1_BITS + 3>(x, o);
+                            const uint32_t lo = clamp255(o[0] + 128) | (clamp255(o[1] + 128) << 8) | (clamp255(o[2] + 128) << 16) |
+                                                (clamp255(o[3] + 128) << 24);
+                            const uint32_t hi = clamp255(o[4] + 128) | (clamp255(o[5] + 128) << 8) | (clamp255(o[6] + 128) << 16) |
+                                                (clamp255(o[7] + 128) << 24);
+                            uint2* out = reinterpret_cast<uint2*>(plane + (job.dst_row + lane8) * pitch + b * 8);
+                            *out       = make_uint2(lo, hi);
+                        }
+                        __syncwarp();
+                    }
+                }
+            }
+            __syncthreads();
+
+            // ---- phase 2: upsample, convert, store; one thread = 4 pixels of one row
+            {
+                const int W = d.width, H = d.height;
+                const int pix   = d.dst_pixel_stride;
+                const int y0    = mrow * yrows;
+                const int rows  = min(yrows, H - y0);
+                const int quads = (W + 3) / 4;
+                const int chh   = ncomp == 3 ? (H * d.vs[1] + vs0 - 1) / vs0 : 0; // real chroma rows / cols
+                const int cw    = ncomp == 3 ? (W * d.hs[1] + hs0 - 1) / hs0 : 0;
+                const int crow_base = mrow * 8 - (fv == 2 ? 1 : 0); // chroma plane row of shared row 0
+                for (int i = tid; i < rows * quads; i += JPG_THREADS)
+                {
+                    const int ry = i / quads;
+                    const int x0 = (i - ry * quads) * 4;
+                    const int y  = y0 + ry;
+                    const int n  = min(4, W - x0);
+                    int       b[4], g[4], r[4];
+                    const uint32_t yy = *reinterpret_cast<const uint32_t*>(yplane + ry * yw + x0);
+                    if (ncomp == 1)
+                    {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            b[k] = g[k] = r[k] = (yy >> (8 * k)) & 0xFF;
+                    }
+                    else
+                    {
+                        int cb[4], cr[4];
+                        if (fh == 1)
+                        {
+                            const int cy = y - crow_base;
+                            const uint32_t u = *reinterpret_cast<const uint32_t*>(cbplane + cy * cwp + x0);
+                            const uint32_t v = *reinterpret_cast<const uint32_t*>(crplane + cy * cwp + x0);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                            {
+                                cb[k] = (u >> (8 * k)) & 0xFF;
+                                cr[k] = (v >> (8 * k)) & 0xFF;
+                            }
+                        }
+                        else
+                        {
+                            // chroma columns x0/2-1 .. x0/2+2 (clamped) of the near and far rows
+                            const int cx0 = x0 >> 1;
+                            int       col[4];
+                            col[0] = max(cx0 - 1, 0);
+                            col[1] = min(cx0, cw - 1);
+                            col[2] = min(cx0 + 1, cw - 1);
+                            col[3] = min(cx0 + 2, cw - 1);
+                            int near_row, far_row;
+                            if (fv == 2)
+                            {
+                                const int cy = y >> 1;
+                                near_row     = cy;
+                                far_row      = (y & 1) ? min(cy + 1, chh - 1) : max(cy - 1, 0);
+                            }
+                            else
+                            {
+                                near_row = far_row = y;
+                            }
+                            near_row -= crow_base;
+                            far_row -= crow_base;
+                            int sb[4], sr[4]; // column sums (vertical filter already applied)
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                            {
+                                const int nb = cbplane[near_row * cwp + col[k]], nr = crplane[near_row * cwp + col[k]];
+                                if (fv == 2)
+                                {
+                                    sb[k] = 3 * nb + cbplane[far_row * cwp + col[k]];
+                                    sr[k] = 3 * nr + crplane[far_row * cwp + col[k]];
+                                }
+                                else
+                                {
+                                    sb[k] = nb;
+                                    sr[k] = nr;
+                                }
+                            }
+                            if (fv == 2)
+                            {
+                                cb[0] = (3 * sb[1] + sb[0] + 8) >> 4;
+                                cb[1] = (3 * sb[1] + sb[2] + 7) >> 4;
+                                cb[2] = (3 * sb[2] + sb[1] + 8) >> 4;
+                                cb[3] = (3 * sb[2] + sb[3] + 7) >> 4;
+                                cr[0] = (3 * sr[1] + sr[0] + 8) >> 4;
+                                cr[1] = (3 * sr[1] + sr[2] + 7) >> 4;
+                                cr[2] = (3 * sr[2] + sr[1] + 8) >> 4;
+                                cr[3] = (3 * sr[2] + sr[3] + 7) >> 4;
+                            }
+                            else
+                            {
+                                cb[0] = (3 * sb[1] + sb[0] + 1) >> 2;
+                                cb[1] = (3 * sb[1] + sb[2] + 2) >> 2;
+                                cb[2] = (3 * sb[2] + sb[1] + 1) >> 2;
+                                cb[3] = (3 * sb[2] + sb[3] + 2) >> 2;
+                                cr[0] = (3 * sr[1] + sr[0] + 1) >> 2;
+                                cr[1] = (3 * sr[1] + sr[2] + 2) >> 2;
+                                cr[2] = (3 * sr[2] + sr[1] + 1) >> 2;
+                                cr[3] = (3 * sr[2] + sr[3] + 2) >> 2;
+                            }
+                        }
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                        {
+                            const int yv = (yy >> (8 * k)) & 0xFF;
+                            const int u = cb[k] - 128, v = cr[k] - 128;
+                            r[k] = clamp255(yv + ((91881 * v + 32768) >> 16));
+                            g[k] = clamp255(yv + ((-22554 * u - 46802 * v + 32768) >> 16));
+                            b[k] = clamp255(yv + ((116130 * u + 32768) >> 16));
+                        }
+                    }
+                    store_bgr4(d.dst + (size_t)y * d.dst_pitch + (size_t)x0 * pix, pix, b, g, r, n);
+                }
+            }
+        }
+    }
+
+    cudaError_t launch_jpeg_backend(const aeonb_jpeg_desc* descs_dev, const int2* work_dev, int n_work, size_t smem,
+                                    cudaStream_t stream)
+    {
+        if (n_work <= 0)
+            return cudaSuccess;
+        cudaError_t err = cudaFuncSetAttribute(jpeg_backend_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess)
+            return err;
+        jpeg_launch L{descs_dev, work_dev};
+        jpeg_backend_kernel<<<n_work, JPG_THREADS, smem, stream>>>(L);
+        return cudaGetLastError();
+    }
+
+    // Shared memory one CTA needs for a record.
+    size_t jpeg_backend_smem(const aeonb_jpeg_desc& d)
+    {
+        const int yrows = d.vs[0] * 8;
+        const int fv    = d.ncomp == 3 ? d.vs[0] : 1;
+        const int crows = 8 + (fv == 2 ? 2 : 0);
+        const size_t planes = (size_t)yrows * d.blocks_w[0] * 8 + (d.ncomp == 3 ? (size_t)2 * crows * d.blocks_w[1] * 8 : 0);
+        return ((planes + 15) & ~(size_t)15) + (size_t)(JPG_THREADS / 8) * WS_BLOCK * sizeof(int);
+    }
+}

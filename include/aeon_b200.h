@@ -1,0 +1,262 @@
+/*
+ * aeon_b200 -- C ABI of the B200 implementation of aeon's per-record ETL hot path.
+ *
+ * Every entry point takes plain pointers and sizes, returns 0 (AEONB_OK) or a
+ * negative status, and never throws.  aeonb_last_error() gives the message of the
+ * last failure on the calling thread.  Citations name the aeon source the entry
+ * point stands in for (paths relative to the aeon tree).
+ *
+ * Levels, from the GPU up:
+ *   1. batch kernels over device-resident data (aeonb_image_batch, aeonb_jpeg_backend_batch,
+ *      aeonb_specgram_batch): one launch per batch;
+ *   2. host helpers that stay on the CPU by design (JPEG entropy decode, AVI index parse,
+ *      augmentation parameter draws);
+ *   3. the provider: encoded records in host memory -> augmented batch, i.e. what
+ *      aeon's batch_decoder + provider_interface::provide do per decode chunk;
+ *   4. the loader: manifest -> batches, i.e. aeon's loader / DataLoader iterator.
+ */
+#ifndef AEON_B200_H
+#define AEON_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AEONB_OK 0
+#define AEONB_ERR_INVALID (-1)     /* bad argument or configuration (aeon: std::invalid_argument) */
+#define AEONB_ERR_CUDA (-2)        /* a CUDA runtime call failed */
+#define AEONB_ERR_UNSUPPORTED (-3) /* valid request outside what the kernels implement */
+#define AEONB_ERR_DECODE (-4)      /* corrupt or unsupported encoded record (aeon: std::runtime_error) */
+#define AEONB_ERR_IO (-5)          /* file or manifest problem */
+#define AEONB_END 1                /* loader iteration finished (aeon: iterator == end) */
+
+typedef struct aeonb_ctx      aeonb_ctx;      /* one GPU: device id, stream, descriptor staging, scratch arena */
+typedef struct aeonb_provider aeonb_provider; /* aeon provider_base + batch_decoder for one configuration */
+typedef struct aeonb_loader   aeonb_loader;   /* aeon loader_local */
+
+const char* aeonb_last_error(void);
+const char* aeonb_version(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Context
+ * ---------------------------------------------------------------------------------------------- */
+
+/* Creates the per-GPU context.  `stream` is a cudaStream_t to run on, or NULL to let the
+ * context create its own non-blocking stream. */
+int  aeonb_ctx_create(int device, void* stream, aeonb_ctx** out);
+void aeonb_ctx_destroy(aeonb_ctx* ctx);
+void* aeonb_ctx_stream(aeonb_ctx* ctx);
+int  aeonb_ctx_synchronize(aeonb_ctx* ctx);
+
+/* ------------------------------------------------------------------------------------------------
+ * 1a. Image augmentation + packing kernel
+ *     replaces image::transformer::transform_single_image (src/etl_image.cpp:146-202),
+ *     photometric::cbsjitter / lighting (src/image.cpp:336-406) and image::loader::load
+ *     (src/etl_image.cpp:246-341); with frame strides also video::loader::load
+ *     (src/etl_video.cpp:76-107).
+ * ---------------------------------------------------------------------------------------------- */
+
+enum aeonb_dtype
+{
+    AEONB_U8 = 0,
+    AEONB_I8 = 1,
+    AEONB_I16 = 2,
+    AEONB_U16 = 3,
+    AEONB_I32 = 4,
+    AEONB_F32 = 5,
+    AEONB_F64 = 6
+};
+
+enum aeonb_interp
+{
+    AEONB_INTERP_NEAREST = 0,
+    AEONB_INTERP_LINEAR = 1
+};
+
+/* One image (or video frame) to transform.  All coordinates are pixels.
+ * The source is an 8-bit interleaved image in device memory (B,G,R[,x] per pixel).
+ * The "canvas" models aeon's expand / padding: a zero image of canvas_w x canvas_h with
+ * the source pasted at (canvas_x, canvas_y); without expand the canvas equals the source.
+ * The crop box is given in canvas coordinates and is resized to out_w x out_h. */
+typedef struct aeonb_image_desc
+{
+    const uint8_t* src;  /* device pointer; NULL produces an all-zero image (video padding frame) */
+    int32_t src_pitch;   /* bytes between source rows */
+    int32_t src_pixel_stride; /* 3 (BGR) or 4 (BGRx) bytes per pixel */
+    int32_t src_w, src_h;
+    int32_t canvas_w, canvas_h, canvas_x, canvas_y;
+    int32_t crop_x, crop_y, crop_w, crop_h;
+    int32_t out_w, out_h; /* size after resize; <= slot size, the rest of the slot is zero-filled */
+    int32_t interp;       /* aeonb_interp */
+    int32_t flip;         /* horizontal flip, applied last */
+    /* photometric (src/image.cpp:358-406); every stage rounds to uint8 before the next */
+    int32_t color_enable; /* apply color_matrix (brightness / saturation) */
+    int16_t color_matrix[9]; /* round(m*1024), row-major, BGR order: the 10-bit form cv::transform uses */
+    int16_t reserved0;
+    int32_t hue;          /* added to H (units of 2 degrees); 0 disables the HSV round trip */
+    int32_t hsv_vector_cols; /* columns [0, hsv_vector_cols) of each row truncate in HSV->BGR, the rest round */
+    float   contrast;     /* 1.0f disables; otherwise x*c + (1-c)*channel mean of the image */
+    int32_t lighting_enable;
+    float   lighting_scale;     /* 1/(1+std) */
+    int32_t lighting_offset[3]; /* round(pixel_c/(1+std)), BGR order */
+    void*   dst;          /* device pointer to this record's slot (element (0,0,0)) */
+} aeonb_image_desc;
+
+/* Output slot geometry shared by the whole batch. */
+typedef struct aeonb_image_layout
+{
+    int32_t slot_w, slot_h; /* spatial size of the slot */
+    int32_t channels;       /* 3 (1 is reserved) */
+    int32_t dtype;          /* aeonb_dtype of the output elements */
+    int32_t bgr_to_rgb;     /* reverse the channel order on output */
+    int64_t stride_c, stride_y, stride_x; /* element strides of the slot; CHW: (H*W, W, 1); HWC: (1, W*C, C);
+                                             video CTHW frame: (T*H*W, W, 1) */
+    int32_t standardize;    /* apply x*(1/255) - mean[c], then *rstd[c] (src/image.cpp:129-174) */
+    float   mean[3];        /* indexed by OUTPUT channel */
+    float   rstd[3];        /* 1/std, or 1.0f where std == 0 */
+    double  mean64[3];      /* same for AEONB_F64 output */
+    double  rstd64[3];
+} aeonb_image_layout;
+
+/* Transforms n images with one kernel launch on the context's stream.  `descs` is host memory
+ * and may be reused as soon as the call returns.  Asynchronous with respect to the host. */
+int aeonb_image_batch(aeonb_ctx* ctx, const aeonb_image_desc* descs, int n, const aeonb_image_layout* layout);
+
+/* Bytes the kernel must read and write for this batch (unique source bytes inside the crop
+ * boxes + output bytes): the figure a bandwidth roofline is computed from. */
+int64_t aeonb_image_batch_bytes(const aeonb_image_desc* descs, int n, const aeonb_image_layout* layout);
+
+/* ------------------------------------------------------------------------------------------------
+ * 1b. JPEG back end kernel: dequantisation + 8x8 integer inverse DCT + chroma upsampling +
+ *     YCbCr->BGR, i.e. everything cv::imdecode (src/etl_image.cpp:90, src/cap_mjpeg_decoder.cpp:140)
+ *     does after entropy decoding.
+ * ---------------------------------------------------------------------------------------------- */
+
+typedef struct aeonb_jpeg_desc
+{
+    const int16_t*  coef[3];  /* device: per component, blocks in raster order, 64 int16 each, stored
+                                 COLUMN-major inside the block (element (row r, col c) at c*8+r) */
+    const uint16_t* quant[3]; /* device: 64 quantiser steps per component, same column-major order */
+    int32_t width, height;    /* image size in pixels */
+    int32_t ncomp;            /* 1 (grey) or 3 (YCbCr) */
+    int32_t hs[3], vs[3];     /* sampling factors; supported: grey, 4:4:4, 4:2:2 (2x1), 4:2:0 (2x2) */
+    int32_t blocks_w[3], blocks_h[3]; /* coefficient plane size in blocks (padded to whole MCUs) */
+    uint8_t* dst;             /* device: interleaved B,G,R[,x] output */
+    int32_t dst_pitch;
+    int32_t dst_pixel_stride; /* 3 or 4 */
+} aeonb_jpeg_desc;
+
+int aeonb_jpeg_backend_batch(aeonb_ctx* ctx, const aeonb_jpeg_desc* descs, int n);
+int64_t aeonb_jpeg_backend_bytes(const aeonb_jpeg_desc* descs, int n);
+
+/* ------------------------------------------------------------------------------------------------
+ * 1c. Spectrogram kernel: framing + window + DFT magnitude + mel filter bank + log
+ *     (specgram::wav_to_specgram / specgram_to_cepsgram, src/specgram.cpp:26-137).
+ * ---------------------------------------------------------------------------------------------- */
+
+typedef struct aeonb_specgram_desc
+{
+    const int16_t* samples; /* device */
+    int32_t n_samples;
+    float*  dst;            /* device: max_time_steps x n_out floats, rows past the clip are zero-filled */
+} aeonb_specgram_desc;
+
+typedef struct aeonb_specgram_config
+{
+    int32_t frame_length;   /* samples per frame == DFT length */
+    int32_t frame_stride;
+    int32_t max_time_steps;
+    int32_t num_filters;    /* mel filters; 0 = output the magnitude spectrogram (frame_length/2+1 bins) */
+    int32_t sample_rate;
+    int32_t window;         /* 0 none, 1 hann, 2 hamming, 3 blackman, 4 bartlett (src/specgram.cpp:156-189) */
+} aeonb_specgram_config;
+
+int aeonb_specgram_batch(aeonb_ctx* ctx, const aeonb_specgram_desc* descs, int n, const aeonb_specgram_config* cfg);
+int64_t aeonb_specgram_bytes(const aeonb_specgram_desc* descs, int n, const aeonb_specgram_config* cfg);
+
+/* ------------------------------------------------------------------------------------------------
+ * 2. Host helpers
+ * ---------------------------------------------------------------------------------------------- */
+
+/* Header-only parse of a baseline JPEG. */
+typedef struct aeonb_jpeg_info
+{
+    int32_t width, height, ncomp;
+    int32_t hs[3], vs[3];
+    int32_t blocks_w[3], blocks_h[3];
+    int64_t coef_count[3]; /* int16 elements per component plane */
+} aeonb_jpeg_info;
+
+int aeonb_jpeg_parse(const void* data, size_t size, aeonb_jpeg_info* info);
+
+/* Entropy-decodes a baseline JPEG into per-component coefficient planes (layout as in
+ * aeonb_jpeg_desc) and quantiser tables, all host memory supplied by the caller. */
+int aeonb_jpeg_entropy_decode(const void* data, size_t size, int16_t* coef[3], uint16_t* quant[3]);
+
+/* Draws augmentation parameters exactly as aeon's param_factory::make_params does
+ * (src/augment_image.cpp:107-230) for `n` records whose decoded sizes are in_w/in_h,
+ * using per-slot std::minstd_rand0 engines seeded as aeon's batch_decoder seeds them
+ * (src/batch_decoder.cpp:47-54).  Writes 24 doubles per record:
+ * crop x,y,w,h, out w,h, flip, angle, hue, contrast, brightness, saturation,
+ * lighting0..2, color_noise_std, padding off x,y, expand ratio, expand off x,y, expand w,h, reserved. */
+int aeonb_draw_params(const char* augmentation_json, uint32_t seed, int decode_size, int n, const int32_t* in_w,
+                      const int32_t* in_h, int out_w, int out_h, double* out);
+
+/* ------------------------------------------------------------------------------------------------
+ * 3. Provider: encoded records -> augmented batch
+ *    (provider_interface::provide, src/provider_interface.hpp:42-44, driven per decode chunk the
+ *    way batch_decoder::filler / process do, src/batch_decoder.cpp:62-99)
+ * ---------------------------------------------------------------------------------------------- */
+
+/* `config_json` carries aeon's own keys: "etl", "augmentation", "batch_size", "random_seed",
+ * "batch_major", plus optional "decode_size" (RNG slots, default batch_size) and
+ * "decode_threads" (host entropy-decode workers, default: hardware threads). */
+int  aeonb_provider_create(aeonb_ctx* ctx, const char* config_json, aeonb_provider** out);
+void aeonb_provider_destroy(aeonb_provider* p);
+
+int         aeonb_provider_input_count(const aeonb_provider* p);  /* elements per record */
+int         aeonb_provider_output_count(const aeonb_provider* p); /* named output buffers */
+const char* aeonb_provider_output_name(const aeonb_provider* p, int i);
+/* Shape of one record of output i: up to 8 dims; returns the rank.  *dtype receives an aeonb_dtype. */
+int     aeonb_provider_output_shape(const aeonb_provider* p, int i, int64_t* dims, int32_t* dtype);
+int64_t aeonb_provider_output_bytes(const aeonb_provider* p, int i); /* bytes per record */
+
+/* Processes n records (n <= batch_size).  elems[r*input_count + e] / sizes[...] address element e of
+ * record r in host memory.  outputs[i] receives n records of output i; it is device memory when
+ * outputs_on_device != 0, else host memory (copied back before the call returns).
+ * The call returns after the batch is complete. */
+int aeonb_provider_run(aeonb_provider* p, const void* const* elems, const size_t* sizes, int n, void* const* outputs,
+                       int outputs_on_device);
+
+/* Statistics of the last aeonb_provider_run: host->device and device->host bytes, kernel launches. */
+int aeonb_provider_stats(const aeonb_provider* p, int64_t* h2d_bytes, int64_t* d2h_bytes, int32_t* launches);
+
+/* ------------------------------------------------------------------------------------------------
+ * 4. Loader (loader_factory::get_loader + loader::iterator, src/loader.hpp:112-175;
+ *    python aeon.DataLoader, src/api.cpp:104-425)
+ * ---------------------------------------------------------------------------------------------- */
+
+int  aeonb_loader_create(const char* config_json, int device, aeonb_loader** out);
+void aeonb_loader_destroy(aeonb_loader* l);
+int  aeonb_loader_record_count(const aeonb_loader* l);
+int  aeonb_loader_batch_size(const aeonb_loader* l);
+int  aeonb_loader_batch_count(const aeonb_loader* l);
+int  aeonb_loader_output_count(const aeonb_loader* l);
+const char* aeonb_loader_output_name(const aeonb_loader* l, int i);
+int  aeonb_loader_output_shape(const aeonb_loader* l, int i, int64_t* dims, int32_t* dtype);
+const char* aeonb_loader_axis_names(const aeonb_loader* l, int i); /* comma separated */
+const char* aeonb_loader_config(const aeonb_loader* l);            /* JSON of the effective configuration */
+/* Advances to the next batch.  buffers[i] receives a pointer (host, or device when the loader
+ * was configured with "device_output": true) valid until the next call.  Returns AEONB_END when
+ * the iteration is complete. */
+int aeonb_loader_next(aeonb_loader* l, void** buffers);
+int aeonb_loader_reset(aeonb_loader* l);
+int aeonb_loader_position(const aeonb_loader* l);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AEON_B200_H */

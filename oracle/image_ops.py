@@ -1,0 +1,405 @@
+"""CPU oracle for aeon's per-record image ETL arithmetic (TEST INFRASTRUCTURE ONLY).
+
+This module is a checker.  Nothing in the shipped package imports it; only the
+test-suite, the smoke check and the CPU-baseline leg of the benchmark do.
+
+aeon delegates every pixel operation to OpenCV (un-vendored, version unpinned by
+the reference's CMake: ``find_package(OpenCV REQUIRED)``).  The functions below
+restate, in numpy integer / float32 arithmetic, what OpenCV 4.13 computes for the
+exact call sequence aeon makes.  Each one names the aeon call site it follows
+(paths are relative to the aeon source tree) and is pinned in the CPU test-suite
+against the OpenCV binary itself (python ``cv2`` 4.13.0, exhaustively where the
+domain is small) and against aeon's own golden vectors
+(``test/test_data/augment_output_linear_{train,eval}.bin``).
+
+Array conventions: images are ``uint8`` ``H x W x 3`` in BGR order, exactly as
+``cv::imdecode`` hands them to aeon.
+"""
+import numpy as np
+
+f32 = np.float32
+f64 = np.float64
+
+# ---------------------------------------------------------------------------------------------
+# small helpers
+# ---------------------------------------------------------------------------------------------
+
+
+def _rne(x):
+    """Round half to even (OpenCV ``cvRound`` / ``saturate_cast`` from floating point)."""
+    return np.rint(x)
+
+
+def _sat_u8(x):
+    return np.clip(x, 0, 255).astype(np.uint8)
+
+
+def _fnmadd32(a, b, c):
+    """Single-rounding float32 ``c - a*b`` (what an FMA instruction returns)."""
+    return (np.asarray(c, f64) - np.asarray(a, f64) * np.asarray(b, f64)).astype(f32)
+
+
+# ---------------------------------------------------------------------------------------------
+# geometry: cv::resize(INTER_LINEAR) on 8-bit data   (aeon: src/image.cpp:93-106 -> cv::resize)
+# ---------------------------------------------------------------------------------------------
+
+RESIZE_COEF_BITS = 11
+RESIZE_COEF_ONE = 1 << RESIZE_COEF_BITS
+
+
+def linear_taps(src_len, dst_len, clamp_weights):
+    """Source index and 11-bit fixed-point tap pair for every destination index.
+
+    ``clamp_weights`` is True for the horizontal axis, where OpenCV moves a tap that
+    falls outside the row onto the border pixel and gives it the whole weight; on
+    the vertical axis only the row index is clamped and the weights are kept.
+    """
+    scale = f64(src_len) / f64(dst_len)
+    d = np.arange(dst_len, dtype=f64)
+    f = ((d + 0.5) * scale - 0.5).astype(f32)
+    s = np.floor(f).astype(np.int32)
+    f = f - s.astype(f32)
+    if clamp_weights:
+        lo = s < 0
+        f = np.where(lo, f32(0), f)
+        s = np.where(lo, 0, s)
+        hi = s >= src_len - 1
+        f = np.where(hi, f32(0), f)
+        s = np.where(hi, src_len - 1, s)
+    w0 = np.clip(_rne((f32(1) - f) * f32(RESIZE_COEF_ONE)), -32768, 32767).astype(np.int32)
+    w1 = np.clip(_rne(f * f32(RESIZE_COEF_ONE)), -32768, 32767).astype(np.int32)
+    return s, w0, w1
+
+
+def resize_linear_u8(src, out_w, out_h):
+    """Bit-exact ``cv::resize(src, dst, Size(out_w,out_h), 0, 0, INTER_LINEAR)`` for uint8.
+
+    aeon skips the call when the size is unchanged (src/image.cpp:97-100); the
+    arithmetic below degenerates to a copy in that case, so no special case is needed.
+    """
+    h, w = src.shape[:2]
+    sx, a0, a1 = linear_taps(w, out_w, True)
+    sy, b0, b1 = linear_taps(h, out_h, False)
+    sx1 = np.minimum(sx + 1, w - 1)
+    y0 = np.clip(sy, 0, h - 1)
+    y1 = np.clip(sy + 1, 0, h - 1)
+    s = src.astype(np.int32)
+    # horizontal pass keeps 11 fractional bits
+    hor = s[:, sx, :] * a0[None, :, None] + s[:, sx1, :] * a1[None, :, None]
+    r0 = hor[y0] >> 4
+    r1 = hor[y1] >> 4
+    out = (((b0[:, None, None] * r0) >> 16) + ((b1[:, None, None] * r1) >> 16) + 2) >> 2
+    return _sat_u8(out)
+
+
+def resize_nearest_u8(src, out_w, out_h):
+    """``cv::resize(..., INTER_NEAREST)``: source index = min(floor(d * src/dst), src-1)."""
+    h, w = src.shape[:2]
+    ix = np.minimum(np.floor(np.arange(out_w) * (f64(w) / out_w)).astype(np.int64), w - 1)
+    iy = np.minimum(np.floor(np.arange(out_h) * (f64(h) / out_h)).astype(np.int64), h - 1)
+    return src[iy][:, ix]
+
+
+def expand(src, offset_xy, out_size_wh):
+    """aeon ``image::expand`` (src/image.cpp:276-303): zero canvas with the image pasted in."""
+    h, w = src.shape[:2]
+    ox, oy = offset_xy
+    ow, oh = out_size_wh
+    if w + ox > ow or h + oy > oh or ox * oy < 0 or w * h <= 0:
+        raise ValueError("Invalid parameters to expand image")
+    if (ow, oh) == (w, h):
+        return src
+    out = np.zeros((oh, ow) + src.shape[2:], src.dtype)
+    out[oy:oy + h, ox:ox + w] = src
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# photometric: aeon photometric::cbsjitter (src/image.cpp:358-406)
+# ---------------------------------------------------------------------------------------------
+
+GRAY_BGR = (0.0820, 0.6094, 0.3086)  # src/image.cpp:367
+
+
+def color_matrix(brightness, saturation):
+    """3x3 float32 matrix ``b*(s*I + (1-s)*1*g^T)`` of src/image.cpp:367-371 (BGR order)."""
+    b = f32(brightness)
+    s = f32(saturation)
+    g = np.array(GRAY_BGR, f32)
+    oms = f32(f32(1) - s)
+    gray = (f64(oms) * g.astype(f64)).astype(f32)          # (1-s)*ones*g^T, gemm accumulates in double
+    sb = f32(f64(s) * f64(b))
+    m = np.zeros((3, 3), f32)
+    for i in range(3):
+        for j in range(3):
+            m[i, j] = f32(f32(sb if i == j else 0) + f32(gray[j] * b))
+    return m
+
+
+TRANSFORM_BITS = 10
+
+
+def transform_u8(img, m):
+    """``cv::transform`` of an 8-bit 3-channel image by a 3x3 float matrix.
+
+    OpenCV evaluates this case in 10-bit fixed point: coefficients are
+    ``round_half_even(m*1024)`` saturated to int16, the dot product is rounded with
+    ``+512 >> 10`` and saturated to uint8 (src/image.cpp:372 -> cv::transform).
+    """
+    mi = np.clip(_rne(np.asarray(m, f32) * f32(1 << TRANSFORM_BITS)), -32768, 32767).astype(np.int32)
+    s = img.astype(np.int32)
+    out = np.empty(img.shape, np.int32)
+    for k in range(3):
+        out[..., k] = (s[..., 0] * mi[k, 0] + s[..., 1] * mi[k, 1] + s[..., 2] * mi[k, 2]
+                       + (1 << (TRANSFORM_BITS - 1))) >> TRANSFORM_BITS
+    return _sat_u8(out)
+
+
+HSV_SHIFT = 12
+
+
+def _hsv_tables():
+    sdiv = np.zeros(256, np.int32)
+    hdiv = np.zeros(256, np.int32)
+    i = np.arange(1, 256, dtype=f64)
+    sdiv[1:] = _rne((255 << HSV_SHIFT) / i).astype(np.int32)
+    hdiv[1:] = _rne((180 << HSV_SHIFT) / (6.0 * i)).astype(np.int32)
+    return sdiv, hdiv
+
+
+_SDIV, _HDIV180 = _hsv_tables()
+
+
+def bgr2hsv_u8(img):
+    """8-bit ``cv::cvtColor(BGR2HSV)`` with H in [0,180): reciprocal tables, 12-bit fixed point."""
+    b = img[..., 0].astype(np.int32)
+    g = img[..., 1].astype(np.int32)
+    r = img[..., 2].astype(np.int32)
+    v = np.maximum(np.maximum(b, g), r)
+    diff = v - np.minimum(np.minimum(b, g), r)
+    half = 1 << (HSV_SHIFT - 1)
+    s = (diff * _SDIV[v] + half) >> HSV_SHIFT
+    h = np.where(v == r, g - b, np.where(v == g, b - r + 2 * diff, r - g + 4 * diff))
+    h = (h * _HDIV180[diff] + half) >> HSV_SHIFT
+    h = np.where(h < 0, h + 180, h)
+    return np.stack([h, s, v], -1).astype(np.uint8)
+
+
+_SECTOR = np.array([[1, 3, 0], [1, 0, 2], [3, 0, 1], [0, 2, 1], [0, 1, 3], [2, 1, 0]])
+
+
+HSV_VECTOR_BLOCK = 32   # pixels per vector iteration of OpenCV's AVX2 HSV->BGR row kernel
+
+
+def hsv2bgr_u8(hsv, vector_block=HSV_VECTOR_BLOCK):
+    """8-bit ``cv::cvtColor(HSV2BGR)`` for H scaled by 180.
+
+    Float32 sector interpolation; the two interpolated corners use a fused
+    multiply-add.  OpenCV converts each row in vector blocks of ``vector_block``
+    pixels whose final ``*255`` is TRUNCATED, and finishes the row (the last
+    ``W mod vector_block`` pixels) in scalar code that ROUNDS half-to-even; both
+    behaviours are reproduced because aeon's output inherits them.  H values of
+    180..255 (which aeon's hue wrap produces for negative sums) land in sector
+    ``floor(h/30) mod 6``.  Checked over all 2^24 inputs in both modes.
+    """
+    h = hsv[..., 0].astype(f32) * f32(6.0 / 180.0)
+    s = hsv[..., 1].astype(f32) * f32(1.0 / 255.0)
+    v = hsv[..., 2].astype(f32) * f32(1.0 / 255.0)
+    sector = np.floor(h).astype(np.int32)
+    f = h - sector.astype(f32)
+    sector = sector % 6
+    one = np.ones_like(s)
+    tab = np.stack([v, v * (f32(1) - s), v * _fnmadd32(s, f, one), v * _fnmadd32(s, f32(1) - f, one)], 0)
+    idx = _SECTOR[sector]
+    out = np.stack([np.take_along_axis(tab, idx[..., k][None], 0)[0] for k in range(3)], -1)
+    out = out * f32(255)
+    width = hsv.shape[-2]
+    body = (width // vector_block) * vector_block if vector_block else 0
+    res = _rne(out)
+    if body:
+        res[..., :body, :] = np.trunc(out[..., :body, :])
+    return _sat_u8(res.astype(np.int32))
+
+
+def hue_shift_u8(img, hue):
+    """src/image.cpp:376-394: BGR->HSV, ``H = uint8((H + hue) % 180)`` with C remainder, HSV->BGR."""
+    hsv = bgr2hsv_u8(img)
+    t = hsv[..., 0].astype(np.int32) + int(hue)
+    rem = np.fmod(t, 180).astype(np.int32)            # C '%': sign follows the dividend
+    hsv[..., 0] = (rem & 0xFF).astype(np.uint8)       # stored back through a uint8_t*
+    return hsv2bgr_u8(hsv)
+
+
+def channel_sums(img):
+    return img.reshape(-1, img.shape[-1]).astype(np.int64).sum(0)
+
+
+def contrast_u8(img, contrast):
+    """src/image.cpp:396-405: ``float(x)*c + float((1-c)*mean_channel)`` -> round-half-even uint8."""
+    c = f32(contrast)
+    mean = channel_sums(img).astype(f64) / f64(img.shape[0] * img.shape[1])
+    add = ((1.0 - f64(c)) * mean).astype(f32)
+    return _sat_u8(_rne(img.astype(f32) * c + add))
+
+
+def cbsjitter(img, contrast, brightness, saturation, hue):
+    if f32(brightness) != 1.0 or f32(saturation) != 1.0:
+        img = transform_u8(img, color_matrix(brightness, saturation))
+    if int(hue) != 0:
+        img = hue_shift_u8(img, hue)
+    if f32(contrast) != 1.0:
+        img = contrast_u8(img, contrast)
+    return img
+
+
+# src/image.cpp:320-324
+CPCA = np.array([[0.39731118, 0.70119634, -0.59200296],
+                 [-0.81698062, -0.02354167, -0.57618440],
+                 [0.41795513, -0.71257945, -0.56351045]], f32)
+CSTD = np.array([19.72083305, 37.09388853, 121.78006099], f32)
+
+
+def lighting_pixel(alphas):
+    """The colour-noise pixel ``CPCA * (CSTD o alpha)`` of src/image.cpp:341 (float32, BGR order)."""
+    t = (CSTD * np.asarray(alphas, f32)).astype(f32)
+    return (CPCA.astype(f64) @ t.astype(f64)).astype(f32)
+
+
+def lighting_terms(alphas, color_noise_std):
+    """(scale, integer offsets) that ``(img + pixel) / (1 + std)`` applies to a uint8 image.
+
+    The cv::MatExpr is evaluated as ``convertTo(uint8, alpha)`` followed by a saturating
+    add of the scalar ``pixel*alpha``, which OpenCV rounds to integers for 8-bit data.
+    No reference test fixes this choice (parity unpinned; the alternatives differ by 1 LSB).
+    """
+    alpha = 1.0 / (1.0 + f64(f32(color_noise_std)))
+    pix = lighting_pixel(alphas).astype(f64) * alpha
+    return f32(alpha), _rne(pix).astype(np.int32)
+
+
+def lighting_u8(img, alphas, color_noise_std):
+    if alphas is None or len(alphas) == 0:
+        return img
+    scale, offs = lighting_terms(alphas, color_noise_std)
+    t = _sat_u8(_rne(img.astype(f32) * scale)).astype(np.int32)
+    return _sat_u8(t + offs[None, None, :])
+
+
+# ---------------------------------------------------------------------------------------------
+# transformer / loader (aeon src/etl_image.cpp:146-202 and :246-341)
+# ---------------------------------------------------------------------------------------------
+
+
+class ImageParams:
+    """Field-for-field stand-in for aeon's ``augment::image::params`` (src/augment_image.hpp:69-123)."""
+
+    def __init__(self, **kw):
+        self.expand_ratio = 1.0
+        self.expand_offset = (0, 0)
+        self.expand_size = (0, 0)
+        self.cropbox = (0, 0, 0, 0)           # x, y, w, h
+        self.output_size = (0, 0)             # w, h
+        self.angle = 0
+        self.flip = False
+        self.padding = 0
+        self.padding_crop_offset = (0, 0)
+        self.resize_short_size = 0
+        self.interpolation_method = "LINEAR"
+        self.lighting = []
+        self.color_noise_std = 0.0
+        self.contrast = 1.0
+        self.brightness = 1.0
+        self.saturation = 1.0
+        self.hue = 0
+        for k, v in kw.items():
+            if not hasattr(self, k):
+                raise AttributeError(k)
+            setattr(self, k, v)
+
+
+def resized_short_size(w, h, target):
+    """src/image.cpp:108-116 (float percent, round half away from zero)."""
+    pct = f32(target) / f32(min(h, w))
+    rw = int(np.floor(f64(f32(w) * pct) + 0.5))
+    rh = int(np.floor(f64(f32(h) * pct) + 0.5))
+    return rw, rh
+
+
+def _resize(img, size_wh, method):
+    if (img.shape[1], img.shape[0]) == tuple(size_wh):
+        return img
+    m = method.upper()
+    if m == "LINEAR":
+        return resize_linear_u8(img, size_wh[0], size_wh[1])
+    if m == "NEAREST":
+        return resize_nearest_u8(img, size_wh[0], size_wh[1])
+    raise NotImplementedError("interpolation method %s has no oracle" % method)
+
+
+def transform_single_image(img, p):
+    """aeon ``image::transformer::transform_single_image`` (src/etl_image.cpp:146-202)."""
+    if p.angle != 0:
+        raise NotImplementedError("rotation is outside the accelerated path")
+    if f32(p.expand_ratio) > 1.0:
+        img = expand(img, p.expand_offset, p.expand_size)
+    if p.resize_short_size != 0:
+        img = _resize(img, resized_short_size(img.shape[1], img.shape[0], p.resize_short_size),
+                      p.interpolation_method)
+    x, y, w, h = p.cropbox
+    if x < 0 or y < 0 or w <= 0 or h <= 0 or x + w > img.shape[1] or y + h > img.shape[0]:
+        raise ValueError("cropbox outside the image")
+    img = img[y:y + h, x:x + w]
+    if p.padding != 0 and tuple(p.padding_crop_offset) != (p.padding, p.padding):
+        pad = p.padding
+        canvas = np.zeros((h + 2 * pad, w + 2 * pad, img.shape[2]), img.dtype)
+        canvas[pad:pad + h, pad:pad + w] = img
+        ox, oy = p.padding_crop_offset
+        img = canvas[oy:oy + h, ox:ox + w]
+    img = _resize(img, p.output_size, p.interpolation_method)
+    img = cbsjitter(img, p.contrast, p.brightness, p.saturation, p.hue)
+    img = lighting_u8(img, p.lighting, p.color_noise_std)
+    if p.flip:
+        img = img[:, ::-1]
+    return np.ascontiguousarray(img)
+
+
+_DTYPES = {"uint8_t": np.uint8, "int8_t": np.int8, "int16_t": np.int16, "uint16_t": np.uint16,
+           "int32_t": np.int32, "uint32_t": np.int32, "float": np.float32, "double": np.float64,
+           "char": np.int8}
+
+
+def load_image(img, channel_major=True, bgr_to_rgb=False, output_type="uint8_t", mean=None, stddev=None):
+    """aeon ``image::loader::load`` for one image without ``fixed_aspect_ratio``
+    (src/etl_image.cpp:317-339): depth conversion, optional BGR->RGB, HWC->CHW split,
+    then ``x*(1/255) - mean_c`` and ``*(1/std_c)`` in the output precision
+    (src/image.cpp:129-174; a zero std leaves the channel unscaled).
+    """
+    dt = _DTYPES[output_type]
+    if np.issubdtype(dt, np.integer) and dt != np.uint8:
+        info = np.iinfo(dt)
+        x = np.clip(img.astype(np.int64), info.min, info.max).astype(dt)
+    else:
+        x = img.astype(dt)
+    if bgr_to_rgb:
+        x = x[..., ::-1]
+    if mean is not None and len(mean):
+        x = x.copy()
+        for c in range(x.shape[2]):
+            t = x[..., c] * dt(1.0 / 255.0)
+            t = t - dt(mean[c])
+            if stddev[c]:
+                t = t * dt(1.0 / stddev[c])
+            x[..., c] = t
+    if channel_major:
+        x = np.transpose(x, (2, 0, 1))
+    return np.ascontiguousarray(x)
+
+
+def load_video(frames, max_frame_count):
+    """aeon ``video::transformer`` trimming/padding + ``video::loader::load``
+    (src/etl_video.cpp:49-107): uint8 planes at ``c*T*H*W + t*H*W``, no channel swap."""
+    frames = list(frames[:max_frame_count])
+    h, w = frames[0].shape[:2]
+    while len(frames) < max_frame_count:
+        frames.append(np.zeros((h, w, 3), np.uint8))
+    return np.ascontiguousarray(np.stack(frames, 0).transpose(3, 0, 1, 2))
