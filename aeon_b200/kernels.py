@@ -1,0 +1,160 @@
+"""Thin python callers of the batch-kernel entry points (device tensors in, device tensors out).
+
+torch is used for device memory only; every computation happens inside libaeon_b200.so.
+"""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _lib as L
+
+_TORCH_DTYPE = {L.U8: torch.uint8, L.I8: torch.int8, L.I16: torch.int16, L.U16: torch.int16, L.I32: torch.int32,
+                L.F32: torch.float32, L.F64: torch.float64}
+DTYPE_BY_NAME = {"uint8_t": L.U8, "int8_t": L.I8, "char": L.I8, "int16_t": L.I16, "uint16_t": L.U16,
+                 "int32_t": L.I32, "uint32_t": L.I32, "float": L.F32, "double": L.F64}
+DTYPE_SIZE = {L.U8: 1, L.I8: 1, L.I16: 2, L.U16: 2, L.I32: 4, L.F32: 4, L.F64: 8}
+INTERP_BY_NAME = {"NEAREST": L.INTERP_NEAREST, "LINEAR": L.INTERP_LINEAR}
+
+
+class Context:
+    """One GPU context of the library (aeonb_ctx)."""
+
+    def __init__(self, device=0):
+        self.lib = L.load()
+        self.device = int(device)
+        # The library runs on a stream torch knows about, so tensors allocated under
+        # `with torch.cuda.stream(ctx.torch_stream)` are ordered with the kernels.
+        self.torch_stream = torch.cuda.Stream(device=self.device)
+        h = C.c_void_p()
+        L.check(self.lib.aeonb_ctx_create(self.device, C.c_void_p(self.torch_stream.cuda_stream), C.byref(h)))
+        self.handle = h
+
+    def synchronize(self):
+        L.check(self.lib.aeonb_ctx_synchronize(self.handle))
+
+    @property
+    def stream(self):
+        return self.lib.aeonb_ctx_stream(self.handle)
+
+    def close(self):
+        if self.handle:
+            self.lib.aeonb_ctx_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def make_layout(slot_w, slot_h, dtype=L.U8, channel_major=True, bgr_to_rgb=False, mean=None, stddev=None,
+                strides=None):
+    lay = L.ImageLayout()
+    lay.slot_w, lay.slot_h, lay.channels, lay.dtype = slot_w, slot_h, 3, dtype
+    lay.bgr_to_rgb = int(bool(bgr_to_rgb))
+    if strides is None:
+        strides = (slot_h * slot_w, slot_w, 1) if channel_major else (1, slot_w * 3, 3)
+    lay.stride_c, lay.stride_y, lay.stride_x = strides
+    if mean is not None and len(mean):
+        lay.standardize = 1
+        for c in range(3):
+            r = 1.0 / stddev[c] if stddev[c] else 1.0
+            lay.mean[c], lay.rstd[c] = mean[c], r
+            lay.mean64[c], lay.rstd64[c] = mean[c], r
+    return lay
+
+
+def fill_desc(desc, src, p, dst_ptr, lib=None):
+    """Fill an ImageDesc from a source tensor (H x W x 3|4 uint8 on the GPU, or None) and a parameter
+    object with aeon's ``augment::image::params`` fields (see oracle.image_ops.ImageParams)."""
+    lib = lib or L.load()
+    desc.dst = dst_ptr
+    if src is None:
+        desc.src = None
+        return
+    h, w, pix = src.shape
+    desc.src = src.data_ptr()
+    desc.src_pitch = src.stride(0)
+    desc.src_pixel_stride = pix
+    desc.src_w, desc.src_h = w, h
+    if float(np.float32(p.expand_ratio)) > 1.0:
+        desc.canvas_w, desc.canvas_h = p.expand_size
+        desc.canvas_x, desc.canvas_y = p.expand_offset
+    elif p.padding and tuple(p.padding_crop_offset) != (p.padding, p.padding):
+        desc.canvas_w, desc.canvas_h = w + 2 * p.padding, h + 2 * p.padding
+        desc.canvas_x = desc.canvas_y = p.padding
+    else:
+        desc.canvas_w, desc.canvas_h, desc.canvas_x, desc.canvas_y = w, h, 0, 0
+    x, y, cw, ch = p.cropbox
+    if p.padding and tuple(p.padding_crop_offset) != (p.padding, p.padding):
+        x, y = p.padding_crop_offset
+    desc.crop_x, desc.crop_y, desc.crop_w, desc.crop_h = x, y, cw, ch
+    desc.out_w, desc.out_h = p.output_size
+    desc.interp = INTERP_BY_NAME[p.interpolation_method.upper()]
+    desc.flip = int(bool(p.flip))
+    light = (C.c_float * 3)(*[float(v) for v in p.lighting]) if len(p.lighting) else None
+    L.check(lib.aeonb_image_desc_set_photometric(C.byref(desc), float(p.contrast), float(p.brightness),
+                                                 float(p.saturation), int(p.hue), light, float(p.color_noise_std)))
+
+
+def image_batch(ctx, sources, params, out, layout, record_stride=None):
+    """Run the image kernel: sources[i] -> out[i].  `out` is a device tensor whose first dim is the batch."""
+    n = len(sources)
+    descs = (L.ImageDesc * n)()
+    esz = out.element_size()
+    stride = record_stride if record_stride is not None else out.stride(0)
+    for i in range(n):
+        fill_desc(descs[i], sources[i], params[i], out.data_ptr() + i * stride * esz, ctx.lib)
+    L.check(ctx.lib.aeonb_image_batch(ctx.handle, descs, n, C.byref(layout)))
+    return descs
+
+
+def jpeg_parse(data):
+    info = L.JpegInfo()
+    buf = (C.c_char * len(data)).from_buffer_copy(data)
+    L.check(L.load().aeonb_jpeg_parse(buf, len(data), C.byref(info)))
+    return info
+
+
+def jpeg_entropy_decode(data):
+    """Host entropy decode -> (info, [coef planes as int16 numpy], [quant tables as uint16 numpy])."""
+    lib = L.load()
+    info = jpeg_parse(data)
+    coefs = [np.zeros(max(int(info.coef_count[c]), 1), np.int16) for c in range(3)]
+    quants = [np.zeros(64, np.uint16) for _ in range(3)]
+    cp = (C.c_void_p * 3)(*[c.ctypes.data for c in coefs])
+    qp = (C.c_void_p * 3)(*[q.ctypes.data for q in quants])
+    buf = (C.c_char * len(data)).from_buffer_copy(data)
+    L.check(lib.aeonb_jpeg_entropy_decode(buf, len(data), cp, qp))
+    return info, coefs[:info.ncomp], quants[:info.ncomp]
+
+
+def jpeg_decode_batch(ctx, encoded, pixel_stride=3):
+    """Decode JPEG byte strings: host entropy decode, device back end.  Returns H x W x pixel_stride tensors."""
+    dev = torch.device("cuda", ctx.device)
+    torch.cuda.synchronize(dev)
+    n = len(encoded)
+    descs = (L.JpegDesc * n)()
+    keep, outs = [], []
+    for i, data in enumerate(encoded):
+        info, coefs, quants = jpeg_entropy_decode(data)
+        d = descs[i]
+        d.width, d.height, d.ncomp = info.width, info.height, info.ncomp
+        for c in range(info.ncomp):
+            ct = torch.from_numpy(coefs[c]).to(dev)
+            qt = torch.from_numpy(quants[c].view(np.int16)).to(dev)
+            keep += [ct, qt]
+            d.coef[c], d.quant[c] = ct.data_ptr(), qt.data_ptr()
+            d.hs[c], d.vs[c] = info.hs[c], info.vs[c]
+            d.blocks_w[c], d.blocks_h[c] = info.blocks_w[c], info.blocks_h[c]
+        pitch = (info.width * pixel_stride + 15) // 16 * 16
+        buf = torch.zeros((info.height, pitch), dtype=torch.uint8, device=dev)
+        d.dst, d.dst_pitch, d.dst_pixel_stride = buf.data_ptr(), pitch, pixel_stride
+        outs.append(torch.as_strided(buf, (info.height, info.width, pixel_stride), (pitch, pixel_stride, 1)))
+        keep.append(buf)
+    torch.cuda.synchronize(dev)
+    L.check(ctx.lib.aeonb_jpeg_backend_batch(ctx.handle, descs, n))
+    ctx.synchronize()
+    return outs, descs

@@ -205,6 +205,13 @@ int aeonb_jpeg_entropy_decode(const void* data, size_t size, int16_t* coef[3], u
 int aeonb_draw_params(const char* augmentation_json, uint32_t seed, int decode_size, int n, const int32_t* in_w,
                       const int32_t* in_h, int out_w, int out_h, double* out);
 
+/* Fills the photometric fields of `desc` (colour matrix, hue, HSV vector columns, contrast,
+ * lighting scale/offsets) from aeon's parameter values, doing on the host what
+ * photometric::cbsjitter / lighting do before they touch pixels (src/image.cpp:336-346,362-371).
+ * `lighting` is NULL or 3 floats; desc->out_w must already be set. */
+int aeonb_image_desc_set_photometric(aeonb_image_desc* desc, float contrast, float brightness, float saturation, int hue,
+                                     const float* lighting, float color_noise_std);
+
 /* ------------------------------------------------------------------------------------------------
  * 3. Provider: encoded records -> augmented batch
  *    (provider_interface::provide, src/provider_interface.hpp:42-44, driven per decode chunk the
