@@ -89,6 +89,4 @@ namespace aeonb
     cudaError_t launch_jpeg_backend(const aeonb_jpeg_desc* descs_dev, const int2* work_dev, int n_work, size_t smem,
                                     cudaStream_t stream);
     size_t      jpeg_backend_smem(const aeonb_jpeg_desc& d);
-    cudaError_t launch_specgram(const aeonb_specgram_desc* descs_dev, int n, const aeonb_specgram_config& cfg,
-                                const float* window_dev, const float* fbank_dev, cudaStream_t stream, const char** why);
 }

@@ -1,0 +1,101 @@
+// The provider: encoded records in host memory -> one augmented batch on the GPU.
+//
+// It plays the part of aeon's provider_base (src/provider.cpp:24-119) together with the
+// per-slot random engines of batch_decoder (src/batch_decoder.cpp:47-71).  Per batch it
+//   1. walks the records in order on one thread: parses headers, draws the augmentation
+//      parameters from the record's slot engine (same draw order as the reference), parses
+//      annotations / labels, and lays out one pinned staging buffer;
+//   2. entropy-decodes all JPEG streams on a worker pool straight into that staging buffer,
+//      shipping it to the GPU in slices while the pool is still decoding;
+//   3. launches one JPEG back-end kernel and one image kernel per image-like stage
+//      (plus the spectrogram kernel for audio stages);
+//   4. delivers the outputs to device or host memory, transposed when batch_major is false.
+#pragma once
+
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../specgram_host.hpp"
+#include "config.hpp"
+#include "jpeg_host.hpp"
+#include "params.hpp"
+#include "runtime.hpp"
+
+namespace aeonb
+{
+    enum class stage_kind
+    {
+        image,
+        label,
+        video,
+        ssd,
+        audio
+    };
+
+    struct stage
+    {
+        stage_kind   kind;
+        int          first_output = 0; // index of the stage's first output buffer
+        image_config image;
+        label_config label;
+        video_config video;
+        ssd_config   ssd;
+        audio_config audio;
+        std::unordered_map<std::string, int> class_map;
+    };
+
+    struct output_info
+    {
+        std::string name;
+        shape_type  shape;
+        std::string axes;          // comma separated axis names
+        bool        host_produced; // small outputs computed on the CPU (labels, boxes)
+    };
+
+    // One JPEG stream to decode: where its bytes are and where its pieces live in the arenas.
+    struct jpeg_job
+    {
+        const uint8_t* data = nullptr;
+        size_t         size = 0;
+        jpeg_frame     frame;
+        size_t         stage_off = 0;    // quantiser tables, then the coefficient planes
+        size_t         plane_off[3]{};   // offsets of the planes inside the staging buffer
+        size_t         stage_bytes = 0;
+        size_t         pixel_off = 0;    // decoded picture inside the pixel arena
+        int            pitch = 0;
+    };
+}
+
+struct aeonb_provider
+{
+    aeonb_ctx*                           ctx = nullptr;
+    int                                  batch_size  = 0;
+    int                                  decode_size = 0;
+    uint32_t                             seed        = 0;
+    bool                                 batch_major = true;
+    int                                  pixel_stride = 4;
+    std::vector<aeonb::stage>            stages;
+    std::vector<aeonb::output_info>      outputs;
+    aeonb::param_factory                 factory;       // augmentation[0]
+    aeonb::param_factory                 video_factory; // augmentation[0]["frame"]
+    std::vector<aeonb::random_engine_t>  engines;
+    int                                  slot_cursor = 0;
+    std::unique_ptr<aeonb::worker_pool>  pool;
+
+    aeonb::pinned_buffer                 staging;      // coefficients / samples, host side
+    aeonb::device_buffer                 staging_dev;
+    aeonb::device_buffer                 pixels_dev;   // decoded pictures
+    std::vector<aeonb::device_buffer>    out_dev;      // per output, batch_size records
+    std::vector<aeonb::device_buffer>    out_dev_t;    // transposed copies (batch_major == false)
+    std::vector<std::vector<char>>       out_host;     // host-produced outputs
+    aeonb::pinned_buffer                 small_pinned;
+
+    int64_t h2d_bytes = 0, d2h_bytes = 0;
+    int32_t launches  = 0;
+
+    aeonb_provider(aeonb_ctx* c, const aeonb::json& cfg);
+    void run(const void* const* elems, const size_t* sizes, int n, void* const* outs, bool on_device);
+    int  input_count() const { return (int)stages.size(); }
+};

@@ -1,0 +1,593 @@
+// aeonb_provider::run -- one batch through the host stages and the GPU kernels.
+#include <algorithm>
+#include <atomic>
+#include <chrono>
+#include <cstring>
+#include <sstream>
+#include <thread>
+
+#include "avi.hpp"
+#include "photometric.hpp"
+#include "provider.hpp"
+
+using namespace aeonb;
+using std::string;
+using std::vector;
+
+namespace aeonb
+{
+    cudaError_t  launch_transpose(const void* src, void* dst, int64_t rows, int64_t cols, int elem_size, cudaStream_t stream);
+    vector<bbox> transform_boxes_for_ssd(const vector<bbox>& boxes, const image_params& p);
+    void parse_ssd_annotation(const void* data, size_t size, const std::unordered_map<string, int>& classes, int& width,
+                              int& height, vector<bbox>& boxes);
+
+    namespace
+    {
+        void check_status(int status)
+        {
+            if (status < 0)
+                throw error(status, aeonb_last_error());
+        }
+
+        // Geometry + photometric fields of a descriptor from aeon's params
+        // (image::transformer::transform_single_image, src/etl_image.cpp:146-202).
+        aeonb_image_desc make_desc(const image_params& p, int src_w, int src_h, int slot_w, int slot_h, bool exact_fit)
+        {
+            if (p.angle != 0)
+                throw error(AEONB_ERR_UNSUPPORTED, "rotation ('angle') is outside the accelerated path");
+            if (p.resize_short_size != 0)
+                throw error(AEONB_ERR_UNSUPPORTED, "'resize_short_size' is outside the accelerated path");
+            string m = p.interpolation_method;
+            std::transform(m.begin(), m.end(), m.begin(), ::toupper);
+            aeonb_image_desc d{};
+            if (m == "LINEAR")
+                d.interp = AEONB_INTERP_LINEAR;
+            else if (m == "NEAREST")
+                d.interp = AEONB_INTERP_NEAREST;
+            else if (m == "CUBIC" || m == "AREA" || m == "LANCZOS4")
+                throw error(AEONB_ERR_UNSUPPORTED, "interpolation method " + m + " is outside the accelerated path");
+            else
+                throw std::invalid_argument("Provided interpolation method (" + p.interpolation_method + " is unrecognized.");
+            d.src_w = src_w;
+            d.src_h = src_h;
+            if (p.expand_ratio > 1.0f)
+            {
+                d.canvas_w = p.expand_size.width;
+                d.canvas_h = p.expand_size.height;
+                d.canvas_x = p.expand_offset.width;
+                d.canvas_y = p.expand_offset.height;
+                if (src_w + d.canvas_x > d.canvas_w || src_h + d.canvas_y > d.canvas_h ||
+                    (int64_t)d.canvas_x * d.canvas_y < 0)
+                    throw std::invalid_argument("Invalid parameters to expand image");
+            }
+            else
+            {
+                d.canvas_w = src_w;
+                d.canvas_h = src_h;
+            }
+            d.crop_x = p.cropbox.x;
+            d.crop_y = p.cropbox.y;
+            d.crop_w = p.cropbox.width;
+            d.crop_h = p.cropbox.height;
+            if (p.padding != 0 && !(p.padding_crop_offset.width == p.padding && p.padding_crop_offset.height == p.padding))
+            {
+                // add_padding (src/image.cpp:77-91): black border of `padding`, then a window of the cropped size
+                if (p.expand_ratio > 1.0f || d.crop_x != 0 || d.crop_y != 0 || d.crop_w != src_w || d.crop_h != src_h)
+                    throw error(AEONB_ERR_UNSUPPORTED, "'padding' together with a crop or expand is outside the accelerated path");
+                d.canvas_w = src_w + 2 * p.padding;
+                d.canvas_h = src_h + 2 * p.padding;
+                d.canvas_x = d.canvas_y = p.padding;
+                d.crop_x = p.padding_crop_offset.width;
+                d.crop_y = p.padding_crop_offset.height;
+            }
+            d.out_w = p.output_size.width;
+            d.out_h = p.output_size.height;
+            if (exact_fit && (d.out_w != slot_w || d.out_h != slot_h))
+                throw error(AEONB_ERR_UNSUPPORTED,
+                            "output size differs from the configured size; set 'fixed_aspect_ratio' or enable cropping");
+            d.flip = p.flip ? 1 : 0;
+            set_photometric(d, p.contrast, p.brightness, p.saturation, p.hue, p.lighting.empty() ? nullptr : p.lighting.data(),
+                            p.color_noise_std);
+            return d;
+        }
+
+        const int16_t* wav_samples(const void* data, size_t size, size_t& count)
+        {
+            // Raw little-endian int16 samples, or a RIFF/WAVE file whose 'data' chunk holds them.
+            const uint8_t* p = static_cast<const uint8_t*>(data);
+            if (size >= 44 && !std::memcmp(p, "RIFF", 4) && !std::memcmp(p + 8, "WAVE", 4))
+            {
+                size_t pos = 12;
+                while (pos + 8 <= size)
+                {
+                    uint32_t len;
+                    std::memcpy(&len, p + pos + 4, 4);
+                    if (!std::memcmp(p + pos, "fmt ", 4) && pos + 8 + 16 <= size)
+                    {
+                        uint16_t fmt, bits;
+                        std::memcpy(&fmt, p + pos + 8, 2);
+                        std::memcpy(&bits, p + pos + 8 + 14, 2);
+                        if (fmt != 1 || bits != 16)
+                            throw std::runtime_error("Unsupported number of bytes per sample: " + std::to_string(bits / 8));
+                    }
+                    if (!std::memcmp(p + pos, "data", 4))
+                    {
+                        count = std::min<size_t>(len, size - pos - 8) / 2;
+                        return reinterpret_cast<const int16_t*>(p + pos + 8);
+                    }
+                    pos += 8 + len + (len & 1);
+                }
+                throw std::runtime_error("WAVE file without a data chunk");
+            }
+            count = size / 2;
+            return reinterpret_cast<const int16_t*>(p);
+        }
+    }
+}
+
+void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, void* const* outs, bool on_device)
+{
+    if (!elems || !sizes || !outs)
+        throw std::invalid_argument("aeonb_provider_run: NULL argument");
+    if (n <= 0 || n > batch_size)
+        throw std::invalid_argument("aeonb_provider_run: record count must be in [1, batch_size]");
+    AEONB_CUDA(cudaSetDevice(ctx->device));
+    cudaStream_t  st  = ctx->stream;
+    const int     nin = (int)stages.size();
+    const int64_t launches_before = ctx->launches;
+    h2d_bytes = d2h_bytes = 0;
+
+    struct copy_job
+    {
+        const void* src;
+        size_t      bytes, stage_off;
+    };
+    vector<jpeg_job>                 jobs;
+    vector<copy_job>                 copies;
+    vector<vector<aeonb_image_desc>> descs(nin);
+    vector<vector<int>>              desc_job(nin);
+    vector<vector<int64_t>>          desc_dst(nin);
+    vector<vector<aeonb_specgram_desc>> sdescs(nin);
+    vector<vector<size_t>>           sdesc_off(nin);
+    size_t stage_bytes = 0, pixel_bytes = 0;
+
+    for (size_t o = 0; o < outputs.size(); ++o)
+        if (outputs[o].host_produced)
+            out_host[o].assign((size_t)batch_size * outputs[o].shape.byte_size(), 0);
+
+    auto plan_jpeg = [&](const void* data, size_t size) -> int {
+        jpeg_job job;
+        job.data = static_cast<const uint8_t*>(data);
+        job.size = size;
+        jpeg_parse(data, size, job.frame);
+        const aeonb_jpeg_info& in = job.frame.info;
+        size_t off    = align_up(stage_bytes, 256);
+        job.stage_off = off;
+        off += 3 * 64 * sizeof(uint16_t);
+        for (int c = 0; c < in.ncomp; ++c)
+        {
+            off              = align_up(off, 256);
+            job.plane_off[c] = off;
+            off += (size_t)in.coef_count[c] * sizeof(int16_t);
+        }
+        job.stage_bytes = off - job.stage_off;
+        stage_bytes     = off;
+        job.pitch       = (int)align_up((size_t)in.width * pixel_stride, 16);
+        job.pixel_off   = align_up(pixel_bytes, 256);
+        pixel_bytes     = job.pixel_off + (size_t)job.pitch * in.height;
+        jobs.push_back(job);
+        return (int)jobs.size() - 1;
+    };
+
+    // ---- 1. sequential planning pass (record order == RNG order)
+    for (int r = 0; r < n; ++r)
+    {
+        random_engine_t& engine = engines[(slot_cursor + r) % decode_size];
+        bool             have_params = false;
+        image_params     params;
+        for (int s = 0; s < nin; ++s)
+        {
+            const stage& sg   = stages[s];
+            const void*  data = elems[(size_t)r * nin + s];
+            const size_t size = sizes[(size_t)r * nin + s];
+            auto empty = [&](const char* what) {
+                std::stringstream ss;
+                ss << "received " << what << " with size 0, at idx " << r;
+                throw std::runtime_error(ss.str());
+            };
+            switch (sg.kind)
+            {
+            case stage_kind::image:
+            {
+                if (size == 0)
+                    empty("encoded image");
+                const int  j  = plan_jpeg(data, size);
+                const auto& in = jobs[j].frame.info;
+                if (!have_params)
+                {
+                    params      = factory.make_params(engine, in.width, in.height, sg.image.width, sg.image.height);
+                    have_params = true;
+                }
+                aeonb_image_desc d = make_desc(params, in.width, in.height, sg.image.width, sg.image.height, !factory.fixed_aspect_ratio);
+                if (d.out_w > sg.image.width || d.out_h > sg.image.height)
+                    throw std::invalid_argument("transformed image does not fit the configured output size");
+                descs[s].push_back(d);
+                desc_job[s].push_back(j);
+                desc_dst[s].push_back((int64_t)r * outputs[sg.first_output].shape.byte_size());
+                break;
+            }
+            case stage_kind::video:
+            {
+                if (size == 0)
+                    empty("encoded video");
+                vector<avi_frame> frames = avi_mjpeg_frames(data, size);
+                if (frames.empty())
+                    throw std::runtime_error("Decoding video failed due to invalid data in the video file.");
+                const image_config& fc = sg.video.frame;
+                const int           T  = sg.video.max_frame_count;
+                const int64_t       rec = outputs[sg.first_output].shape.byte_size();
+                int                 prev = -1;
+                vector<int>         frame_jobs;
+                for (int t = 0; t < (int)frames.size() && t < T; ++t)
+                {
+                    if (frames[t].size == 0)
+                    {
+                        // a dropped-frame marker repeats the previous picture (src/cap_mjpeg_decoder.cpp:132-147)
+                        if (prev < 0)
+                            throw std::runtime_error("Decoding video failed due to invalid data in the video file.");
+                    }
+                    else
+                        prev = plan_jpeg(frames[t].data, frames[t].size);
+                    frame_jobs.push_back(prev);
+                }
+                const auto& first = jobs[frame_jobs[0]].frame.info;
+                if (!have_params)
+                {
+                    params      = video_factory.make_params(engine, first.width, first.height, fc.width, fc.height);
+                    have_params = true;
+                }
+                for (int t = 0; t < T; ++t)
+                {
+                    aeonb_image_desc d{};
+                    int              j = -1;
+                    if (t < (int)frame_jobs.size())
+                    {
+                        j              = frame_jobs[t];
+                        const auto& in = jobs[j].frame.info;
+                        d              = make_desc(params, in.width, in.height, fc.width, fc.height, true);
+                    }
+                    descs[s].push_back(d);
+                    desc_job[s].push_back(j);
+                    desc_dst[s].push_back((int64_t)r * rec + (int64_t)t * fc.height * fc.width);
+                }
+                break;
+            }
+            case stage_kind::ssd:
+            {
+                if (size == 0)
+                    empty("localization_ssd data");
+                vector<bbox> boxes;
+                int          w = 0, h = 0;
+                parse_ssd_annotation(data, size, sg.class_map, w, h, boxes);
+                if (!have_params)
+                {
+                    params      = factory.make_ssd_params(engine, w, h, sg.ssd.width, sg.ssd.height, boxes);
+                    have_params = true;
+                }
+                vector<bbox> gt = transform_boxes_for_ssd(boxes, params);
+                const int    o  = sg.first_output;
+                const int    M  = sg.ssd.max_gt_boxes;
+                int32_t* im_shape = reinterpret_cast<int32_t*>(out_host[o].data()) + (size_t)r * 2;
+                float*   gtb      = reinterpret_cast<float*>(out_host[o + 1].data()) + (size_t)r * M * 4;
+                int32_t* count    = reinterpret_cast<int32_t*>(out_host[o + 2].data()) + r;
+                int32_t* cls      = reinterpret_cast<int32_t*>(out_host[o + 3].data()) + (size_t)r * M;
+                int32_t* diff     = reinterpret_cast<int32_t*>(out_host[o + 4].data()) + (size_t)r * M;
+                im_shape[0]       = sg.ssd.width;
+                im_shape[1]       = sg.ssd.height;
+                *count            = std::min<int>(M, (int)gt.size());
+                for (int i = 0; i < *count; ++i)
+                {
+                    const nbox nb = bbox_normalize(gt[i], sg.ssd.width, sg.ssd.height);
+                    gtb[4 * i + 0] = nb.xmin;
+                    gtb[4 * i + 1] = nb.ymin;
+                    gtb[4 * i + 2] = nb.xmax;
+                    gtb[4 * i + 3] = nb.ymax;
+                    cls[i]         = gt[i].label;
+                    diff[i]        = gt[i].difficult;
+                }
+                break;
+            }
+            case stage_kind::label:
+            {
+                if (size == 0)
+                    empty("encoded image"); // aeon reuses the image wording here (src/provider.cpp:207-212)
+                int lbl;
+                if (sg.label.binary)
+                {
+                    if (size != 4)
+                    {
+                        std::stringstream ss;
+                        ss << "Only 4 byte buffers can be loaded as int32.  label_extractor::extract received " << size << " bytes";
+                        throw std::runtime_error(ss.str());
+                    }
+                    std::memcpy(&lbl, data, 4);
+                }
+                else
+                    lbl = std::stoi(string((const char*)data, size));
+                const size_t esz = outputs[sg.first_output].shape.otype.size;
+                std::memcpy(out_host[sg.first_output].data() + (size_t)r * esz, &lbl, std::min<size_t>(esz, 4));
+                break;
+            }
+            case stage_kind::audio:
+            {
+                if (size == 0)
+                    empty("encoded audio");
+                size_t         count   = 0;
+                const int16_t* samples = wav_samples(data, size, count);
+                const size_t   limit   = (size_t)(sg.audio.max_time_steps - 1) * sg.audio.frame_stride + sg.audio.frame_length;
+                count                  = std::min(count, limit);
+                const size_t off       = align_up(stage_bytes, 256);
+                stage_bytes            = off + count * 2;
+                copies.push_back(copy_job{samples, count * 2, off});
+                aeonb_specgram_desc d{};
+                d.n_samples = (int32_t)count;
+                sdescs[s].push_back(d);
+                sdesc_off[s].push_back(off);
+                break;
+            }
+            }
+        }
+    }
+    slot_cursor = (slot_cursor + n) % decode_size;
+
+    // ---- 2. arenas
+    staging.reserve(stage_bytes + 256);
+    staging_dev.reserve(stage_bytes + 256);
+    pixels_dev.reserve(pixel_bytes + 256);
+    vector<char*> produced(outputs.size(), nullptr); // where each device-produced output is written
+    for (size_t o = 0; o < outputs.size(); ++o)
+    {
+        if (outputs[o].host_produced)
+            continue;
+        const size_t bytes = (size_t)batch_size * outputs[o].shape.byte_size();
+        if (on_device && batch_major)
+            produced[o] = static_cast<char*>(outs[o]);
+        else
+        {
+            out_dev[o].reserve(bytes);
+            produced[o] = static_cast<char*>(out_dev[o].p);
+        }
+        if (!batch_major)
+            out_dev_t[o].reserve(bytes);
+    }
+
+    // ---- 3. entropy decode on the pool, shipping finished slices while the rest decode
+    char* const hstage = static_cast<char*>(staging.p);
+    char* const dstage = static_cast<char*>(staging_dev.p);
+    const int   njobs  = (int)jobs.size();
+    const int   nwork  = njobs + (int)copies.size();
+    if (nwork > 0)
+    {
+        const int                     groups = std::max(1, std::min(8, nwork));
+        vector<std::atomic<int>>      remaining(groups);
+        vector<int>                   first(groups + 1);
+        for (int g = 0; g <= groups; ++g)
+            first[g] = (int)((int64_t)nwork * g / groups);
+        for (int g = 0; g < groups; ++g)
+            remaining[g] = first[g + 1] - first[g];
+        auto group_of = [&](int i) { return (int)(std::upper_bound(first.begin(), first.end(), i) - first.begin()) - 1; };
+        auto offset_of = [&](int i) { return i < njobs ? jobs[i].stage_off : copies[i - njobs].stage_off; };
+        std::exception_ptr failure;
+        std::mutex         failure_mutex;
+        pool->start(nwork, [&](int i) {
+            try
+            {
+                if (i < njobs)
+                {
+                    jpeg_job& job = jobs[i];
+                    std::memcpy(hstage + job.stage_off, job.frame.quant, sizeof job.frame.quant);
+                    int16_t* planes[3] = {reinterpret_cast<int16_t*>(hstage + job.plane_off[0]),
+                                          reinterpret_cast<int16_t*>(hstage + job.plane_off[1]),
+                                          reinterpret_cast<int16_t*>(hstage + job.plane_off[2])};
+                    jpeg_entropy_decode(job.frame, planes);
+                }
+                else
+                {
+                    const copy_job& c = copies[i - njobs];
+                    std::memcpy(hstage + c.stage_off, c.src, c.bytes);
+                }
+            }
+            catch (...)
+            {
+                std::lock_guard<std::mutex> lk(failure_mutex);
+                if (!failure)
+                    failure = std::current_exception();
+            }
+            remaining[group_of(i)].fetch_sub(1, std::memory_order_release);
+        });
+        cudaError_t copy_error = cudaSuccess;
+        for (int g = 0; g < groups; ++g)
+        {
+            while (remaining[g].load(std::memory_order_acquire) > 0)
+                std::this_thread::sleep_for(std::chrono::microseconds(20));
+            const size_t begin = offset_of(first[g]);
+            const size_t end   = first[g + 1] < nwork ? offset_of(first[g + 1]) : stage_bytes;
+            if (end > begin && copy_error == cudaSuccess && !failure)
+            {
+                copy_error = cudaMemcpyAsync(dstage + begin, hstage + begin, end - begin, cudaMemcpyHostToDevice, st);
+                h2d_bytes += (int64_t)(end - begin);
+            }
+        }
+        pool->wait();
+        if (failure)
+            std::rethrow_exception(failure);
+        AEONB_CUDA(copy_error);
+    }
+
+    // ---- 4. kernels
+    if (njobs > 0)
+    {
+        vector<aeonb_jpeg_desc> jd(njobs);
+        for (int i = 0; i < njobs; ++i)
+        {
+            const jpeg_job&        job = jobs[i];
+            const aeonb_jpeg_info& in  = job.frame.info;
+            aeonb_jpeg_desc&       d   = jd[i];
+            d.width  = in.width;
+            d.height = in.height;
+            d.ncomp  = in.ncomp;
+            for (int c = 0; c < in.ncomp; ++c)
+            {
+                d.coef[c]     = reinterpret_cast<const int16_t*>(dstage + job.plane_off[c]);
+                d.quant[c]    = reinterpret_cast<const uint16_t*>(dstage + job.stage_off) + 64 * c;
+                d.hs[c]       = in.hs[c];
+                d.vs[c]       = in.vs[c];
+                d.blocks_w[c] = in.blocks_w[c];
+                d.blocks_h[c] = in.blocks_h[c];
+            }
+            d.dst              = static_cast<uint8_t*>(pixels_dev.p) + job.pixel_off;
+            d.dst_pitch        = job.pitch;
+            d.dst_pixel_stride = pixel_stride;
+        }
+        check_status(aeonb_jpeg_backend_batch(ctx, jd.data(), njobs));
+        h2d_bytes += (int64_t)(sizeof(aeonb_jpeg_desc) * njobs);
+    }
+    for (int s = 0; s < nin; ++s)
+    {
+        const stage& sg = stages[s];
+        if (sg.kind == stage_kind::image || sg.kind == stage_kind::video)
+        {
+            const bool          video = sg.kind == stage_kind::video;
+            const image_config& ic    = video ? sg.video.frame : sg.image;
+            const int           o     = sg.first_output;
+            aeonb_image_layout  L{};
+            L.slot_w   = ic.width;
+            L.slot_h   = ic.height;
+            L.channels = 3;
+            if (video)
+            {
+                // video::loader::load always writes uint8 planes without a channel swap (src/etl_video.cpp:76-107)
+                L.dtype    = AEONB_U8;
+                L.stride_c = (int64_t)sg.video.max_frame_count * ic.height * ic.width;
+                L.stride_y = ic.width;
+                L.stride_x = 1;
+                if (outputs[o].shape.otype.size != 1)
+                    AEONB_CUDA(cudaMemsetAsync(produced[o], 0, (size_t)n * outputs[o].shape.byte_size(), st));
+            }
+            else
+            {
+                L.dtype      = ic.shape.otype.dtype;
+                L.bgr_to_rgb = ic.bgr_to_rgb;
+                if (ic.channel_major)
+                {
+                    L.stride_c = (int64_t)ic.height * ic.width;
+                    L.stride_y = ic.width;
+                    L.stride_x = 1;
+                }
+                else
+                {
+                    L.stride_c = 1;
+                    L.stride_y = (int64_t)ic.width * 3;
+                    L.stride_x = 3;
+                }
+                if (!factory.mean.empty())
+                {
+                    L.standardize = 1;
+                    for (int c = 0; c < 3; ++c)
+                    {
+                        const double sd = factory.stddev[c];
+                        L.mean64[c]     = factory.mean[c];
+                        L.rstd64[c]     = sd ? 1. / sd : 1.;
+                        L.mean[c]       = (float)L.mean64[c];
+                        L.rstd[c]       = (float)L.rstd64[c];
+                    }
+                }
+            }
+            for (size_t i = 0; i < descs[s].size(); ++i)
+            {
+                aeonb_image_desc& d = descs[s][i];
+                const int         j = desc_job[s][i];
+                d.dst               = produced[o] + desc_dst[s][i];
+                if (j >= 0)
+                {
+                    d.src              = static_cast<const uint8_t*>(pixels_dev.p) + jobs[j].pixel_off;
+                    d.src_pitch        = jobs[j].pitch;
+                    d.src_pixel_stride = pixel_stride;
+                }
+            }
+            check_status(aeonb_image_batch(ctx, descs[s].data(), (int)descs[s].size(), &L));
+            h2d_bytes += (int64_t)(sizeof(aeonb_image_desc) * descs[s].size());
+        }
+        else if (sg.kind == stage_kind::audio)
+        {
+            const int             o = sg.first_output;
+            aeonb_specgram_config cfg{sg.audio.frame_length, sg.audio.frame_stride, sg.audio.max_time_steps,
+                                      sg.audio.feature_type == "mfsc" ? sg.audio.num_filters : 0, sg.audio.sample_rate,
+                                      sg.audio.window_code()};
+            for (size_t i = 0; i < sdescs[s].size(); ++i)
+            {
+                sdescs[s][i].samples = reinterpret_cast<const int16_t*>(dstage + sdesc_off[s][i]);
+                sdescs[s][i].dst     = reinterpret_cast<float*>(produced[o] + (int64_t)i * outputs[o].shape.byte_size());
+            }
+            check_status(aeonb_specgram_batch(ctx, sdescs[s].data(), (int)sdescs[s].size(), &cfg));
+            h2d_bytes += (int64_t)(sizeof(aeonb_specgram_desc) * sdescs[s].size());
+        }
+    }
+
+    // ---- 5. deliver
+    size_t small_total = 0;
+    for (size_t o = 0; o < outputs.size(); ++o)
+        if (outputs[o].host_produced && on_device)
+            small_total += align_up(out_host[o].size(), 256);
+    small_pinned.reserve(small_total + 256);
+    size_t small_off = 0;
+    for (size_t o = 0; o < outputs.size(); ++o)
+    {
+        const size_t  rec   = (size_t)outputs[o].shape.byte_size();
+        const int     esz   = (int)outputs[o].shape.otype.size;
+        const int64_t elems_per_rec = outputs[o].shape.element_count();
+        if (outputs[o].host_produced)
+        {
+            vector<char>  tmp;
+            const char*   src = out_host[o].data();
+            if (!batch_major)
+            {
+                tmp.resize(out_host[o].size());
+                for (int r = 0; r < batch_size; ++r)
+                    for (int64_t e = 0; e < elems_per_rec; ++e)
+                        std::memcpy(&tmp[((size_t)e * batch_size + r) * esz], src + ((size_t)r * elems_per_rec + e) * esz, esz);
+                src = tmp.data();
+            }
+            const size_t bytes = batch_major ? rec * n : rec * batch_size;
+            if (on_device)
+            {
+                char* pin = static_cast<char*>(small_pinned.p) + small_off;
+                small_off += align_up(out_host[o].size(), 256);
+                std::memcpy(pin, src, bytes);
+                AEONB_CUDA(cudaMemcpyAsync(outs[o], pin, bytes, cudaMemcpyHostToDevice, st));
+                h2d_bytes += (int64_t)bytes;
+            }
+            else
+                std::memcpy(outs[o], src, bytes);
+            continue;
+        }
+        if (!batch_major)
+        {
+            void* target = on_device ? outs[o] : out_dev_t[o].p;
+            AEONB_CUDA(launch_transpose(produced[o], target, batch_size, elems_per_rec, esz, st));
+            ctx->launches++;
+            if (!on_device)
+            {
+                AEONB_CUDA(cudaMemcpyAsync(outs[o], target, rec * batch_size, cudaMemcpyDeviceToHost, st));
+                d2h_bytes += (int64_t)(rec * batch_size);
+            }
+        }
+        else if (!on_device)
+        {
+            AEONB_CUDA(cudaMemcpyAsync(outs[o], produced[o], rec * n, cudaMemcpyDeviceToHost, st));
+            d2h_bytes += (int64_t)(rec * n);
+        }
+    }
+    AEONB_CUDA(cudaStreamSynchronize(st));
+    launches = (int32_t)(ctx->launches - launches_before);
+}

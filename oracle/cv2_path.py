@@ -35,15 +35,19 @@ def cbsjitter(img, contrast, brightness, saturation, hue):
         img = cv2.transform(img, ops.color_matrix(brightness, saturation))
     if int(hue) != 0:
         hsv = cv2.cvtColor(img, cv2.COLOR_BGR2HSV)
-        t = hsv[..., 0].astype(np.int32) + int(hue)
-        hsv[..., 0] = (np.fmod(t, 180).astype(np.int32) & 0xFF).astype(np.uint8)
+        # uint8((H + hue) % 180) with C remainder, as a 256-entry table
+        t = np.arange(256, dtype=np.int32) + int(hue)
+        lut = (np.fmod(t, 180).astype(np.int32) & 0xFF).astype(np.uint8)
+        hsv[..., 0] = cv2.LUT(np.ascontiguousarray(hsv[..., 0]), lut)
         img = cv2.cvtColor(hsv, cv2.COLOR_HSV2BGR)
     if np.float32(contrast) != 1.0:
         c = float(np.float32(contrast))
         mean = cv2.mean(img)
-        dst = img.astype(np.float32) * np.float32(c)
-        dst = cv2.add(dst, tuple((1.0 - c) * m for m in mean))
-        img = np.clip(np.rint(dst), 0, 255).astype(np.uint8)
+        add = np.array([(1.0 - c) * m for m in mean[:3]]).astype(np.float32)
+        # convertTo(CV_32F, c); += scalar; convertTo(CV_8U).  The scalar add is done by numpy (same float32
+        # addition) because the python binding of cv2.add with a scalar is far slower than the C++ call.
+        dst = img.astype(np.float32) * np.float32(c) + add
+        img = cv2.addWeighted(dst, 1.0, dst, 0.0, 0.0, dtype=cv2.CV_8U)  # saturating round-half-even cast
     return img
 
 
@@ -89,7 +93,7 @@ def load_image(img, channel_major=True, bgr_to_rgb=False, output_type="uint8_t",
     if mean is not None and len(mean):
         for c in range(len(planes)):
             t = cv2.multiply(planes[c], 1.0 / 255.0)
-            t = cv2.subtract(t, float(mean[c]))
+            t = t - dt(mean[c])  # cv::subtract with a scalar; numpy does the same subtraction far faster from python
             if stddev[c]:
                 t = cv2.multiply(t, 1.0 / float(stddev[c]))
             planes[c] = t.reshape(planes[c].shape)

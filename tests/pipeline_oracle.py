@@ -1,0 +1,68 @@
+"""Record-level oracle for a whole provider call: decode -> seeded params -> transform -> load.
+
+Built from the oracle modules only (cv2.imdecode is used for decoding because it is bit-identical
+to oracle.jpeg and far faster)."""
+import numpy as np
+
+from oracle import image_ops as ops
+from oracle import params as oparams
+
+
+class PipelineOracle:
+    def __init__(self, config):
+        self.cfg = config
+        aug = (config.get("augmentation") or [{}])[0]
+        self.aug = aug
+        self.factory = oparams.ParamFactory(aug)
+        self.video_factory = oparams.ParamFactory(aug.get("frame", {}))
+        self.decode_size = config.get("decode_size", config["batch_size"])
+        self.engines = oparams.slot_engines(config["random_seed"], self.decode_size)
+        self.cursor = 0
+
+    @staticmethod
+    def decode(blob):
+        import cv2
+        img = cv2.imdecode(np.frombuffer(blob, np.uint8), cv2.IMREAD_COLOR)
+        assert img is not None
+        return img
+
+    def image(self, etl, img, p):
+        out = ops.transform_single_image(img, p)
+        h, w = etl["height"], etl["width"]
+        kw = dict(channel_major=etl.get("channel_major", True), bgr_to_rgb=etl.get("bgr_to_rgb", False),
+                  output_type=etl.get("output_type", "uint8_t"), mean=self.aug.get("mean"), stddev=self.aug.get("stddev"))
+        if out.shape[:2] == (h, w):
+            return ops.load_image(out, **kw)
+        z = ops.load_image(np.zeros((h, w, 3), np.uint8), kw["channel_major"], kw["bgr_to_rgb"], kw["output_type"])
+        roi = ops.load_image(out, **kw)
+        if kw["channel_major"]:
+            z[:, :out.shape[0], :out.shape[1]] = roi
+        else:
+            z[:out.shape[0], :out.shape[1]] = roi
+        return z
+
+    def batch(self, records, video_frames=None):
+        """records: list of tuples of bytes.  video_frames(blob) -> list of BGR frames for video elements."""
+        outs = {}
+        for r, rec in enumerate(records):
+            g = self.engines[(self.cursor + r) % self.decode_size]
+            p = None
+            for etl, blob in zip(self.cfg["etl"], rec):
+                name = (etl.get("name", "") + "." if etl.get("name") else "")
+                if etl["type"] == "image":
+                    img = self.decode(blob)
+                    if p is None:
+                        p = self.factory.make_params(g, img.shape[1], img.shape[0], etl["width"], etl["height"])
+                    outs.setdefault(name + "image", []).append(self.image(etl, img, p))
+                elif etl["type"] == "label":
+                    v = int(np.frombuffer(blob, np.int32)[0]) if etl.get("binary") else int(blob.decode())
+                    outs.setdefault(name + "label", []).append(np.array([v], ops._DTYPES[etl.get("output_type", "uint32_t")]))
+                elif etl["type"] == "video":
+                    frames = video_frames(blob)
+                    fc = etl["frame"]
+                    if p is None:
+                        p = self.video_factory.make_params(g, frames[0].shape[1], frames[0].shape[0], fc["width"], fc["height"])
+                    tx = [ops.transform_single_image(f, p) for f in frames]
+                    outs.setdefault(name + "video", []).append(ops.load_video(tx, etl["max_frame_count"]))
+        self.cursor = (self.cursor + len(records)) % self.decode_size
+        return {k: np.stack(v) for k, v in outs.items()}

@@ -1,0 +1,158 @@
+"""End-to-end parity of the provider (host entropy decode + seeded draws + both kernels) with the
+record-level oracle, through the C ABI, on the benchmark configurations at reduced batch size."""
+import os
+import struct
+
+import numpy as np
+import pytest
+
+from tests.pipeline_oracle import PipelineOracle
+from tests.synth import gradient_image, jpeg_bytes
+
+pytestmark = pytest.mark.gpu
+
+AUG_C1 = {"type": "image", "crop_enable": True, "center": False, "do_area_scale": True, "scale": [0.08, 1.0],
+          "horizontal_distortion": [0.75, 1.3333334], "flip_enable": True}
+AUG_C2 = dict(AUG_C1, contrast=[0.6, 1.4], brightness=[0.6, 1.4], saturation=[0.6, 1.4], hue=[-18, 18],
+              lighting=[0.0, 0.1], mean=[123.7 / 255, 116.3 / 255, 103.5 / 255], stddev=[58.4 / 255, 57.1 / 255, 57.4 / 255])
+
+
+def image_records(seed, n):
+    rng = np.random.default_rng(seed)
+    recs = []
+    for _ in range(n):
+        h, w = (int(v) for v in rng.integers(256, 513, 2))
+        recs.append((jpeg_bytes(gradient_image(rng, h, w), 90), struct.pack("<i", int(rng.integers(0, 1000)))))
+    return recs
+
+
+def make_provider(ctx, cfg):
+    from aeon_b200.provider import Provider
+    return Provider(ctx, cfg)
+
+
+def test_config1_uint8_chw_two_batches_bit_exact(ctx):
+    cfg = {"batch_size": 16, "random_seed": 1234, "decode_size": 32,
+           "etl": [{"type": "image", "height": 224, "width": 224, "channels": 3, "channel_major": True, "output_type": "uint8_t"},
+                   {"type": "label", "binary": True}],
+           "augmentation": [AUG_C1]}
+    prov, orc = make_provider(ctx, cfg), PipelineOracle(cfg)
+    recs = image_records(41, 48)
+    for b in range(3):  # three batches: the third reuses the slot engines of the first
+        chunk = recs[16 * b:16 * (b + 1)]
+        got = prov.run_host(chunk)
+        want = orc.batch(chunk)
+        assert np.array_equal(got["image"], want["image"])
+        assert np.array_equal(got["label"].astype(np.int64), want["label"].astype(np.int64))
+    st = prov.stats()
+    assert st["launches"] == 2 and st["h2d_bytes"] > 0 and st["d2h_bytes"] == 16 * 3 * 224 * 224 + 0
+
+
+def test_config2_photometric_float_device_and_host_outputs(ctx):
+    cfg = {"batch_size": 16, "random_seed": 99,
+           "etl": [{"type": "image", "height": 224, "width": 224, "output_type": "float", "bgr_to_rgb": True},
+                   {"type": "label", "binary": True}],
+           "augmentation": [AUG_C2]}
+    recs = image_records(42, 16)
+    want = PipelineOracle(cfg).batch(recs)
+    got_h = make_provider(ctx, cfg).run_host(recs)
+    got_d = make_provider(ctx, cfg).run_device(recs)
+    for got in (got_h["image"], got_d["image"].cpu().numpy()):
+        assert np.abs(got - want["image"]).max() <= 1e-6
+    assert np.array_equal(got_d["label"].cpu().numpy().astype(np.int64), want["label"].astype(np.int64))
+
+
+@pytest.mark.parametrize("stride", [3, 4])
+def test_scratch_pixel_stride_does_not_change_results(ctx, stride):
+    cfg = {"batch_size": 8, "random_seed": 5, "scratch_pixel_stride": stride,
+           "etl": [{"type": "image", "height": 64, "width": 96, "channel_major": False}], "augmentation": [AUG_C2 | {"mean": [], "stddev": []}]}
+    recs = [(r[0],) for r in image_records(43, 8)]
+    got = make_provider(ctx, cfg).run_host(recs)
+    assert np.array_equal(got["image"], PipelineOracle(cfg).batch(recs)["image"])
+
+
+def test_batch_major_false_gives_transposed_buffers(ctx):
+    cfg = {"batch_size": 8, "random_seed": 7, "batch_major": False,
+           "etl": [{"type": "image", "height": 32, "width": 40}, {"type": "label", "binary": True}], "augmentation": [AUG_C1]}
+    recs = image_records(44, 8)
+    got = make_provider(ctx, cfg).run_host(recs)
+    want = PipelineOracle(cfg).batch(recs)
+    assert got["image"].shape == (3 * 32 * 40, 8)
+    assert np.array_equal(got["image"], want["image"].reshape(8, -1).T)
+    assert np.array_equal(got["label"].astype(np.int64), want["label"].reshape(8, -1).T.astype(np.int64))
+
+
+def avi_frames(blob, tmp):
+    import cv2
+    path = os.path.join(tmp, "clip.avi")
+    with open(path, "wb") as f:
+        f.write(blob)
+    cap = cv2.VideoCapture(path, cv2.CAP_OPENCV_MJPEG)
+    frames = []
+    while True:
+        ok, fr = cap.read()
+        if not ok:
+            break
+        frames.append(fr)
+    return frames
+
+
+def make_avi(rng, tmp, n_frames, w=171, h=128):
+    import cv2
+    path = os.path.join(tmp, "gen.avi")
+    vw = cv2.VideoWriter(path, cv2.CAP_OPENCV_MJPEG, cv2.VideoWriter_fourcc(*"MJPG"), 25, (w, h))
+    base = gradient_image(rng, h, w + 3 * n_frames)
+    for t in range(n_frames):
+        vw.write(np.ascontiguousarray(base[:, 3 * t:3 * t + w]))
+    vw.release()
+    return open(path, "rb").read()
+
+
+def test_config4_video_clips(ctx, tmp_path):
+    rng = np.random.default_rng(45)
+    cfg = {"batch_size": 4, "random_seed": 11,
+           "etl": [{"type": "video", "max_frame_count": 16, "frame": {"height": 112, "width": 112, "channels": 3}},
+                   {"type": "label", "binary": True}],
+           "augmentation": [{"type": "image", "frame": {"type": "image", "scale": [0.875, 0.875], "center": False, "flip_enable": True}}]}
+    recs = [(make_avi(rng, str(tmp_path), nf), struct.pack("<i", i)) for i, nf in enumerate((16, 16, 9, 20))]
+    got = make_provider(ctx, cfg).run_host(recs)
+    want = PipelineOracle(cfg).batch(recs, lambda b: avi_frames(b, str(tmp_path)))
+    assert got["video"].shape == (4, 3, 16, 112, 112)
+    assert np.array_equal(got["video"], want["video"])
+    assert not got["video"][2][:, 9:].any()  # a 9-frame clip is zero-padded to 16
+
+
+def test_reference_avi_fixture_with_dropped_frame(ctx, golden_dir, tmp_path):
+    """aeon test/test_util.cpp:144-184: bb8.avi has 6 index entries, one of length 0 (repeats the previous frame)."""
+    blob = open(os.path.join(golden_dir, "bb8.avi"), "rb").read()
+    cfg = {"batch_size": 1, "random_seed": 3,
+           "etl": [{"type": "video", "max_frame_count": 8, "frame": {"height": 60, "width": 80}}],
+           "augmentation": [{"type": "image", "frame": {"type": "image"}}]}
+    got = make_provider(ctx, cfg).run_host([(blob,)])["video"][0]
+    assert got[:, :6].any() and not got[:, 6:].any()
+    frames = avi_frames(blob, str(tmp_path))
+    # OpenCV's own reader skips the empty chunk; every decoded picture must appear, in order
+    ours = [got[:, t].transpose(1, 2, 0) for t in range(6)]
+    k = 0
+    for f in frames:
+        while k < 6 and not np.array_equal(ours[k], f):
+            k += 1
+        assert k < 6
+    dup = [t for t in range(1, 6) if np.array_equal(ours[t], ours[t - 1])]
+    assert len(dup) >= 1
+
+
+def test_errors_surface_with_reference_messages(ctx):
+    from aeon_b200._lib import AeonError
+    cfg = {"batch_size": 2, "random_seed": 1, "etl": [{"type": "image", "height": 32, "width": 32}], "augmentation": [AUG_C1]}
+    prov = make_provider(ctx, cfg)
+    good = image_records(46, 1)[0][0]
+    with pytest.raises(AeonError, match="size 0"):
+        prov.run_host([(good,), (b"",)])
+    with pytest.raises(AeonError, match="Decoding image failed"):
+        prov.run_host([(good,), (good[:2] + b"\x00" * 50,)])
+    assert prov.run_host([(good,), (good,)])["image"].shape == (2, 3, 32, 32)  # still usable afterwards
+    with pytest.raises(AeonError, match="not understood"):
+        make_provider(ctx, dict(cfg, etl=[{"type": "image", "height": 32, "width": 32, "heigth": 3}]))
+    with pytest.raises(AeonError, match="unsupported etl type"):
+        make_provider(ctx, dict(cfg, etl=[{"type": "hologram"}]))
