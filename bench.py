@@ -165,6 +165,8 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--pixel-stride", type=int, default=4)
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="time the resident-input kernels only (used for profiler captures; e2e and cpu_baseline are null)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
@@ -278,6 +280,13 @@ def main():
     aug_ms = float(np.mean([e[1].elapsed_time(e[2]) for e in evs]))
     jpeg_alg = float(np.mean([jpeg_bytes_alg[i % n_batches] for i in range(args.steps)]))
     aug_alg = float(np.mean([aug_bytes_alg[i % n_batches] for i in range(args.steps)]))
+
+    if args.kernels_only:
+        if rank == 0:
+            print(json.dumps({"kernels_only": True, "ms_per_step": kernel_ms / args.steps, "jpeg_ms": jpeg_ms, "aug_ms": aug_ms,
+                              "jpeg_gbs": jpeg_alg / jpeg_ms / 1e6, "aug_gbs": aug_alg / aug_ms / 1e6}), flush=True)
+            sampler.stop()
+        return
 
     # ---------------- end to end through the provider: encoded bytes in host memory -> batch in host memory
     threads = max(1, host_workers() // world)
