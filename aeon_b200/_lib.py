@@ -77,6 +77,7 @@ PROTOTYPES = {
     "aeonb_ctx_synchronize": (C.c_int, [C.c_void_p]),
     "aeonb_image_batch": (C.c_int, [C.c_void_p, C.POINTER(ImageDesc), C.c_int, C.POINTER(ImageLayout)]),
     "aeonb_image_batch_bytes": (C.c_int64, [C.POINTER(ImageDesc), C.c_int, C.POINTER(ImageLayout)]),
+    "aeonb_image_batch_noalloc": (C.c_int, [C.POINTER(ImageDesc), C.c_int, C.POINTER(ImageLayout), C.c_void_p]),
     "aeonb_jpeg_backend_batch": (C.c_int, [C.c_void_p, C.POINTER(JpegDesc), C.c_int]),
     "aeonb_jpeg_backend_bytes": (C.c_int64, [C.POINTER(JpegDesc), C.c_int]),
     "aeonb_specgram_batch": (C.c_int, [C.c_void_p, C.POINTER(SpecgramDesc), C.c_int, C.POINTER(SpecgramConfig)]),

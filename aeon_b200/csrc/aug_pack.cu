@@ -494,3 +494,81 @@ namespace aeonb
         return cudaErrorInvalidValue;
     }
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant of the image batch call.
+//
+// aeonb_image_batch keeps a device copy of the descriptor array in buffers it obtains with
+// cudaMalloc / cudaMallocHost.  Some callers must not allocate: code running inside a memory-pool
+// or graph-building phase of a framework that forbids allocator calls, processes that were handed
+// a fixed memory budget at start-up, and latency-critical loops that cannot afford the implicit
+// device synchronisation an allocation may cause.  For them the descriptor copy below lives in a
+// fixed array inside the library image itself.
+// ------------------------------------------------------------------------------------------------
+
+#include <mutex>
+#include <string>
+
+#include "context.hpp"
+
+
+
+namespace aeonb
+{
+    namespace
+    {
+        // Device copy of the descriptors of one call.  Every GPU that loads the library holds these
+        // AEONB_NOALLOC_MAX_RECORDS * sizeof(aeonb_image_desc) bytes (about 68 KB) until the process exits.
+        static __device__ __align__(256) unsigned char g_noalloc_descs[AEONB_NOALLOC_MAX_RECORDS * sizeof(aeonb_image_desc)];
+
+        constexpr int MAX_DEVICES = 64;
+        void*         g_noalloc_addr[MAX_DEVICES]; // per-device address of g_noalloc_descs, 0 until set up
+        std::mutex    g_noalloc_mutex;
+
+        // In host code `g_noalloc_descs` names a host-side shadow, not device memory; the address a
+        // kernel may use comes from cudaGetSymbolAddress, asked once per device with that device current.
+        void* noalloc_scratch(int device)
+        {
+            std::lock_guard<std::mutex> lk(g_noalloc_mutex);
+            if (!g_noalloc_addr[device])
+            {
+                void* p = nullptr;
+                AEONB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_descs));
+                g_noalloc_addr[device] = p;
+            }
+            return g_noalloc_addr[device];
+        }
+    }
+}
+
+extern "C" int aeonb_image_batch_noalloc(const aeonb_image_desc* descs, int n, const aeonb_image_layout* layout, void* stream)
+{
+    using namespace aeonb;
+    return guarded([&]() {
+        if (!layout || (n > 0 && !descs))
+            throw std::invalid_argument("aeonb_image_batch_noalloc: NULL argument");
+        if (n <= 0)
+            return AEONB_OK;
+        if (n > AEONB_NOALLOC_MAX_RECORDS)
+            throw std::invalid_argument("aeonb_image_batch_noalloc: at most " + std::to_string(AEONB_NOALLOC_MAX_RECORDS) +
+                                        " records per call (the descriptor scratch is a fixed array); split the batch");
+        int  pixel_stride;
+        bool aligned;
+        check_image_batch(descs, n, *layout, pixel_stride, aligned);
+        int device = 0;
+        AEONB_CUDA(cudaGetDevice(&device));
+        if (device < 0 || device >= MAX_DEVICES)
+            throw std::invalid_argument("aeonb_image_batch_noalloc: device index out of range");
+        auto*        scratch = static_cast<aeonb_image_desc*>(noalloc_scratch(device));
+        cudaStream_t st      = static_cast<cudaStream_t>(stream);
+        // Every descriptor the kernel reads is overwritten here, so nothing of the previous call survives.
+        AEONB_CUDA(cudaMemcpyAsync(scratch, descs, sizeof(aeonb_image_desc) * n, cudaMemcpyHostToDevice, st));
+        const char* why = nullptr;
+        cudaError_t e   = launch_aug_pack(scratch, n, *layout, pixel_stride, aligned, st, &why);
+        if (why)
+            throw error(AEONB_ERR_UNSUPPORTED, why);
+        if (e != cudaSuccess)
+            throw error(AEONB_ERR_CUDA, cuda_message("image kernel launch", e));
+        return AEONB_OK;
+    });
+}

@@ -160,7 +160,9 @@ static size_t dtype_size(int dtype)
     throw std::invalid_argument("unknown output dtype");
 }
 
-static void check_image_batch(const aeonb_image_desc* d, int n, const aeonb_image_layout& L, int& pixel_stride, bool& aligned)
+} // extern "C"
+
+void aeonb::check_image_batch(const aeonb_image_desc* d, int n, const aeonb_image_layout& L, int& pixel_stride, bool& aligned)
 {
     if (L.slot_w <= 0 || L.slot_h <= 0)
         throw std::invalid_argument("invalid width or height of the output slot");
@@ -210,6 +212,8 @@ static void check_image_batch(const aeonb_image_desc* d, int n, const aeonb_imag
     if (!pixel_stride)
         pixel_stride = 3;
 }
+
+extern "C" {
 
 int aeonb_image_batch(aeonb_ctx* ctx, const aeonb_image_desc* descs, int n, const aeonb_image_layout* layout)
 {

@@ -83,6 +83,10 @@ struct aeonb_ctx
 
 namespace aeonb
 {
+    // Validates a batch of image descriptors (throws std::invalid_argument / aeonb::error); reports the
+    // common source pixel stride and whether every destination slot is 16-byte aligned.
+    void check_image_batch(const aeonb_image_desc* d, int n, const aeonb_image_layout& L, int& pixel_stride, bool& aligned);
+
     // Kernel launchers (defined next to the kernels).
     cudaError_t launch_aug_pack(const aeonb_image_desc* descs_dev, int n, const aeonb_image_layout& layout, int pixel_stride,
                                 bool slots_aligned, cudaStream_t stream, const char** why);

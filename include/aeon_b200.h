@@ -129,6 +129,22 @@ int aeonb_image_batch(aeonb_ctx* ctx, const aeonb_image_desc* descs, int n, cons
  * boxes + output bytes): the figure a bandwidth roofline is computed from. */
 int64_t aeonb_image_batch_bytes(const aeonb_image_desc* descs, int n, const aeonb_image_layout* layout);
 
+/* Same transformation as aeonb_image_batch for callers that are not allowed to allocate memory
+ * (code running where the host framework forbids allocator calls, processes with a memory budget
+ * fixed at start-up, loops that cannot tolerate the synchronisation an allocation can cause).
+ * It has no counterpart in the reference.  It needs no context: it runs on the CURRENT device and
+ * on `stream` (a cudaStream_t, NULL for the default stream), and calls neither cudaMalloc /
+ * cudaFree nor any allocating library routine.  The device copy of the descriptors lives in a
+ * fixed array inside the library (about 68 KB per GPU that loads the library, held until exit),
+ * hence the limit of AEONB_NOALLOC_MAX_RECORDS (512) records per call; larger n is rejected with
+ * AEONB_ERR_INVALID.  The first call on a device looks up the array's device address; make that
+ * first call before starting any stream capture.  All calls share the one array: two calls whose
+ * GPU work can overlap (different streams, or different host threads) race on it, so serialise
+ * them.  `descs` must stay valid and unchanged until the call returns when it is pageable host
+ * memory, and until the stream has consumed the copy when it is pinned host memory. */
+#define AEONB_NOALLOC_MAX_RECORDS 512
+int aeonb_image_batch_noalloc(const aeonb_image_desc* descs, int n, const aeonb_image_layout* layout, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * 1b. JPEG back end kernel: dequantisation + 8x8 integer inverse DCT + chroma upsampling +
  *     YCbCr->BGR, i.e. everything cv::imdecode (src/etl_image.cpp:90, src/cap_mjpeg_decoder.cpp:140)
