@@ -23,6 +23,7 @@ class ImageDesc(C.Structure):
         ("crop_x", C.c_int32), ("crop_y", C.c_int32), ("crop_w", C.c_int32), ("crop_h", C.c_int32),
         ("out_w", C.c_int32), ("out_h", C.c_int32), ("interp", C.c_int32), ("flip", C.c_int32),
         ("color_enable", C.c_int32), ("color_matrix", C.c_int16 * 9), ("reserved0", C.c_int16),
+        ("color_scale", C.c_float * 3),
         ("hue", C.c_int32), ("hsv_vector_cols", C.c_int32), ("contrast", C.c_float),
         ("lighting_enable", C.c_int32), ("lighting_scale", C.c_float), ("lighting_offset", C.c_int32 * 3),
         ("dst", C.c_void_p),
@@ -140,6 +141,8 @@ def load():
             continue
         fn.restype = res
         fn.argtypes = args
+    if MISSING:
+        raise ImportError("libaeon_b200.so lacks %s; rebuild it with `python -m aeon_b200.build`" % ", ".join(MISSING))
     _lib = lib
     return lib
 

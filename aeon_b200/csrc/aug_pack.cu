@@ -115,6 +115,26 @@ namespace aeonb
             return p;
         }
 
+        template <int PIX>
+        __device__ __forceinline__ bgr load_px(const uint8_t* s)
+        {
+            bgr p;
+            if (PIX == 4)
+            {
+                const uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(s));
+                p.b              = v & 0xFF;
+                p.g              = (v >> 8) & 0xFF;
+                p.r              = (v >> 16) & 0xFF;
+            }
+            else
+            {
+                p.b = __ldg(s);
+                p.g = __ldg(s + 1);
+                p.r = __ldg(s + 2);
+            }
+            return p;
+        }
+
         // 8-bit BGR->HSV (H in [0,180)) with 12-bit reciprocal tables, then the hue shift with C
         // remainder semantics stored through a uint8_t, then float32 HSV->BGR.
         __device__ __forceinline__ bgr hue_rotate(bgr p, int hue, bool truncate, const int* sdiv, const int* hdiv)
@@ -146,16 +166,10 @@ namespace aeonb
             const float t1 = vf * (1.0f - sf);
             const float t2 = vf * __fmaf_rn(-sf, f, 1.0f);
             const float t3 = vf * __fmaf_rn(-sf, 1.0f - f, 1.0f);
-            float       fb, fg, fr;
-            switch (sector)
-            {
-            case 0: fb = t1; fg = t3; fr = vf; break;
-            case 1: fb = t1; fg = vf; fr = t2; break;
-            case 2: fb = t3; fg = vf; fr = t1; break;
-            case 3: fb = vf; fg = t2; fr = t1; break;
-            case 4: fb = vf; fg = t1; fr = t3; break;
-            default: fb = t2; fg = t1; fr = vf; break;
-            }
+            // sector -> (b, g, r): 0 (t1,t3,v) 1 (t1,v,t2) 2 (t3,v,t1) 3 (v,t2,t1) 4 (v,t1,t3) 5 (t2,t1,v); selects, no branches
+            const float fb = sector < 2 ? t1 : sector == 2 ? t3 : sector < 5 ? vf : t2;
+            const float fg = sector == 0 ? t3 : sector < 3 ? vf : sector == 3 ? t2 : t1;
+            const float fr = sector == 0 ? vf : sector == 1 ? t2 : sector < 4 ? t1 : sector == 4 ? t3 : vf;
             bgr o;
             if (truncate)
             {
@@ -196,6 +210,26 @@ namespace aeonb
             T                    v[N];
         };
 
+        // Final per-channel value map applied after the spatial stage: contrast (with the image mean),
+        // lighting, conversion to the output type and standardisation depend only on the channel and on
+        // the 8-bit value, so each CTA tabulates them once (3 x 256 entries) and the store loop is a lookup.
+        template <typename T>
+        __device__ __forceinline__ T final_value(int v, int c, int cin, const aeonb_image_desc& d, const aeonb_image_layout& lay,
+                                                 bool use_ctr, float ctr_add)
+        {
+            if (use_ctr)
+                v = clamp_u8(__float2int_rn((float)v * d.contrast + ctr_add));
+            if (d.lighting_enable)
+            {
+                v = clamp_u8(__float2int_rn((float)v * d.lighting_scale));
+                v = clamp_u8(v + d.lighting_offset[cin]);
+            }
+            T e = convert_out<T>(v);
+            if (lay.standardize)
+                e = standardize_value(e, lay, c);
+            return e;
+        }
+
         template <typename T, int PIX>
         __global__ void __launch_bounds__(AUG_THREADS) aug_pack_kernel(const aug_launch L)
         {
@@ -205,11 +239,15 @@ namespace aeonb
             __shared__ float            contrast_add[3];
             __shared__ int              hsv_sdiv[256];
             __shared__ int              hsv_hdiv[256];
+            __shared__ T                lut[3][256];
 
             cg::cluster_group cluster = cg::this_cluster();
             const int         band    = blockIdx.x;
             const int         bands   = gridDim.x;
             const int         tid     = threadIdx.x;
+            const int         lane    = tid & 31;
+            const int         warp    = tid >> 5;
+            constexpr int     WARPS   = AUG_THREADS / 32;
             const aeonb_image_layout& lay = L.layout;
 
             // ---- record descriptor -> shared memory
@@ -233,9 +271,13 @@ namespace aeonb
             const bool use_hue  = d.hue != 0;
             const bool use_ctr  = d.contrast != 1.0f;
             const bool swap_rb  = lay.bgr_to_rgb != 0;
+            const bool linear   = d.interp == AEONB_INTERP_LINEAR;
+            // the whole crop box lies on the source picture: no canvas test per tap
+            const bool inside = d.crop_x >= d.canvas_x && d.crop_y >= d.canvas_y && d.crop_x + d.crop_w <= d.canvas_x + d.src_w &&
+                                d.crop_y + d.crop_h <= d.canvas_y + d.src_h;
 
             unsigned char* tile = smem;                                            // [3][rows_per_band][pitch]
-            int*           xofs = reinterpret_cast<int*>(smem + 3 * plane);        // [out_w]
+            int2*          xofs = reinterpret_cast<int2*>(smem + 3 * plane);       // [out_w] byte offsets of the two taps
             short2*        xw   = reinterpret_cast<short2*>(xofs + lay.slot_w);    // [out_w]
             row_tap*       ytab = reinterpret_cast<row_tap*>(xw + lay.slot_w);     // [rows_per_band]
 
@@ -244,17 +286,18 @@ namespace aeonb
             {
                 int   s;
                 short a0 = 2048, a1 = 0;
-                if (d.interp == AEONB_INTERP_LINEAR)
+                if (linear)
                     linear_tap(x, d.crop_w, out_w, true, s, a0, a1);
                 else
                     s = nearest_tap(x, d.crop_w, out_w);
-                xofs[x] = s;
-                xw[x]   = make_short2(a0, a1);
+                const int s1 = min(s + 1, d.crop_w - 1);
+                xofs[x]      = inside ? make_int2(s * PIX, s1 * PIX) : make_int2(s, s1);
+                xw[x]        = make_short2(a0, a1);
             }
             for (int r = tid; r < img_end - row0; r += AUG_THREADS)
             {
                 row_tap t;
-                if (d.interp == AEONB_INTERP_LINEAR)
+                if (linear)
                 {
                     int s;
                     linear_tap(row0 + r, d.crop_h, out_h, false, s, t.b0, t.b1);
@@ -277,34 +320,55 @@ namespace aeonb
                     hsv_hdiv[i] = i ? __double2int_rn((double)(180 << 12) / (6.0 * (double)i)) : 0;
                 }
             }
-            // zero the tile so the padding columns/rows of the slot read as zero
-            for (int i = tid; i < 3 * plane / 16; i += AUG_THREADS)
-                reinterpret_cast<int4*>(tile)[i] = make_int4(0, 0, 0, 0);
+            // the slot may be larger than the image: clear what the spatial stage will not write
+            if (out_w < lay.slot_w || img_end < row_end)
+                for (int i = tid; i < 3 * plane / 16; i += AUG_THREADS)
+                    reinterpret_cast<int4*>(tile)[i] = make_int4(0, 0, 0, 0);
             __syncthreads();
 
-            // ---- resize + per-pixel photometric into the tile
+            // ---- resize + per-pixel photometric into the tile; a warp takes 32 consecutive pixels of a row
             unsigned int sum0 = 0, sum1 = 0, sum2 = 0;
             {
-                const int npix = max(img_end - row0, 0) * out_w;
-                int       r = 0, x = tid;
-                while (out_w > 0 && x >= out_w)
+                const int      rows  = max(img_end - row0, 0);
+                const int      nseg  = (out_w + 31) >> 5;
+                const int      units = rows * nseg;
+                const uint8_t* base  = d.src + (ptrdiff_t)(d.crop_y - d.canvas_y) * d.src_pitch + (ptrdiff_t)(d.crop_x - d.canvas_x) * PIX;
+                const short*   m     = d.color_matrix;
+                for (int u = warp; u < units; u += WARPS)
                 {
-                    x -= out_w;
-                    ++r;
-                }
-                for (int p = tid; p < npix; p += AUG_THREADS)
-                {
+                    const int r = u / nseg;
+                    const int x = (u - r * nseg) * 32 + lane;
+                    if (x >= out_w)
+                        continue;
                     const row_tap t  = ytab[r];
-                    const int     sx = xofs[x];
+                    const int2    xo = xofs[x];
                     const short2  a  = xw[x];
-                    bgr           px;
-                    if (d.interp == AEONB_INTERP_LINEAR)
+                    bgr           p00, p01, p10, p11;
+                    if (inside)
                     {
-                        const int sx1 = min(sx + 1, d.crop_w - 1);
-                        const bgr p00 = fetch<PIX>(d, sx, t.y0);
-                        const bgr p01 = fetch<PIX>(d, sx1, t.y0);
-                        const bgr p10 = fetch<PIX>(d, sx, t.y1);
-                        const bgr p11 = fetch<PIX>(d, sx1, t.y1);
+                        const uint8_t* r0 = base + (ptrdiff_t)t.y0 * d.src_pitch;
+                        const uint8_t* r1 = base + (ptrdiff_t)t.y1 * d.src_pitch;
+                        p00 = load_px<PIX>(r0 + xo.x);
+                        if (linear)
+                        {
+                            p01 = load_px<PIX>(r0 + xo.y);
+                            p10 = load_px<PIX>(r1 + xo.x);
+                            p11 = load_px<PIX>(r1 + xo.y);
+                        }
+                    }
+                    else
+                    {
+                        p00 = fetch<PIX>(d, xo.x, t.y0);
+                        if (linear)
+                        {
+                            p01 = fetch<PIX>(d, xo.y, t.y0);
+                            p10 = fetch<PIX>(d, xo.x, t.y1);
+                            p11 = fetch<PIX>(d, xo.y, t.y1);
+                        }
+                    }
+                    bgr px = p00;
+                    if (linear)
+                    {
                         // horizontal pass keeps 11 fractional bits; vertical pass as in OpenCV's 8-bit path
                         const int hb0 = p00.b * a.x + p01.b * a.y, hb1 = p10.b * a.x + p11.b * a.y;
                         const int hg0 = p00.g * a.x + p01.g * a.y, hg1 = p10.g * a.x + p11.g * a.y;
@@ -313,16 +377,17 @@ namespace aeonb
                         px.g = clamp_u8((((t.b0 * (hg0 >> 4)) >> 16) + ((t.b1 * (hg1 >> 4)) >> 16) + 2) >> 2);
                         px.r = clamp_u8((((t.b0 * (hr0 >> 4)) >> 16) + ((t.b1 * (hr1 >> 4)) >> 16) + 2) >> 2);
                     }
-                    else
+                    if (d.color_enable == 2)
                     {
-                        px = fetch<PIX>(d, sx, t.y0);
+                        px.b = clamp_u8(__float2int_rn((float)px.b * d.color_scale[0]));
+                        px.g = clamp_u8(__float2int_rn((float)px.g * d.color_scale[1]));
+                        px.r = clamp_u8(__float2int_rn((float)px.r * d.color_scale[2]));
                     }
-                    if (d.color_enable)
+                    else if (d.color_enable)
                     {
-                        const short* m = d.color_matrix;
-                        const int    b = (px.b * m[0] + px.g * m[1] + px.r * m[2] + 512) >> 10;
-                        const int    g = (px.b * m[3] + px.g * m[4] + px.r * m[5] + 512) >> 10;
-                        const int    rr = (px.b * m[6] + px.g * m[7] + px.r * m[8] + 512) >> 10;
+                        const int b  = (px.b * m[0] + px.g * m[1] + px.r * m[2] + 512) >> 10;
+                        const int g  = (px.b * m[3] + px.g * m[4] + px.r * m[5] + 512) >> 10;
+                        const int rr = (px.b * m[6] + px.g * m[7] + px.r * m[8] + 512) >> 10;
                         px.b = clamp_u8(b);
                         px.g = clamp_u8(g);
                         px.r = clamp_u8(rr);
@@ -330,23 +395,16 @@ namespace aeonb
                     if (use_hue)
                         px = hue_rotate(px, d.hue, x < d.hsv_vector_cols, hsv_sdiv, hsv_hdiv);
 
-                    const int xo = d.flip ? out_w - 1 - x : x;
-                    const int c0 = swap_rb ? px.r : px.b;
-                    const int c2 = swap_rb ? px.b : px.r;
-                    unsigned char* o = tile + r * pitch + xo;
+                    const int xo_t = d.flip ? out_w - 1 - x : x;
+                    const int c0   = swap_rb ? px.r : px.b;
+                    const int c2   = swap_rb ? px.b : px.r;
+                    unsigned char* o = tile + r * pitch + xo_t;
                     o[0]             = (unsigned char)c0;
                     o[plane]         = (unsigned char)px.g;
                     o[2 * plane]     = (unsigned char)c2;
                     sum0 += c0;
                     sum1 += px.g;
                     sum2 += c2;
-
-                    x += AUG_THREADS;
-                    while (x >= out_w)
-                    {
-                        x -= out_w;
-                        ++r;
-                    }
                 }
             }
 
@@ -356,7 +414,7 @@ namespace aeonb
                 sum0 = warp_sum(sum0);
                 sum1 = warp_sum(sum1);
                 sum2 = warp_sum(sum2);
-                if ((tid & 31) == 0)
+                if (lane == 0)
                 {
                     atomicAdd(&part_sum[0], sum0);
                     atomicAdd(&part_sum[1], sum1);
@@ -378,55 +436,53 @@ namespace aeonb
                 __syncthreads();
             }
 
-            // ---- contrast, lighting, conversion, standardisation, store
+            // ---- value map: contrast, lighting, conversion, standardisation
+            for (int i = tid; i < 768; i += AUG_THREADS)
             {
-                constexpr int VEC     = out_vec<T>::N;
-                const int     rows    = row_end - row0;
-                const int     chunks  = (lay.slot_w + VEC - 1) / VEC;
-                const int     total   = 3 * rows * chunks;
-                T*            dst     = reinterpret_cast<T*>(d.dst);
-                const bool    std_on  = lay.standardize != 0;
-                const bool    light   = d.lighting_enable != 0;
-                for (int i = tid; i < total; i += AUG_THREADS)
+                const int c   = i >> 8;
+                const int cin = swap_rb ? 2 - c : c; // channel index in BGR order
+                lut[c][i & 255] = final_value<T>(i & 255, c, cin, d, lay, use_ctr, use_ctr ? contrast_add[c] : 0.f);
+            }
+            __syncthreads();
+
+            // ---- store: a warp takes one (channel, row) line at a time, lanes take 16-byte chunks
+            {
+                constexpr int VEC    = out_vec<T>::N;
+                const int     rows   = row_end - row0;
+                const int     chunks = (lay.slot_w + VEC - 1) / VEC;
+                T*            dst    = reinterpret_cast<T*>(d.dst);
+                const T       zero   = convert_out<T>(0);
+                for (int line = warp; line < 3 * rows; line += WARPS)
                 {
-                    const int chunk = i % chunks;
-                    const int rc    = i / chunks;
-                    const int r     = rc % rows;
-                    const int c     = rc / rows;
-                    const int x0    = chunk * VEC;
-                    const int y     = row0 + r;
-                    const int cin   = swap_rb ? 2 - c : c; // channel index in BGR order
-                    const unsigned char* src = tile + c * plane + r * pitch + x0;
-                    out_vec<T>           o;
-#pragma unroll
-                    for (int k = 0; k < VEC; ++k)
+                    const int  c      = line / rows;
+                    const int  r      = line - c * rows;
+                    const int  y      = row0 + r;
+                    const bool row_in = y < out_h;
+                    const unsigned char* src = tile + c * plane + r * pitch;
+                    T*                   g0  = dst + (int64_t)c * lay.stride_c + (int64_t)y * lay.stride_y;
+                    for (int chunk = lane; chunk < chunks; chunk += 32)
                     {
-                        int        v       = src[k];
-                        const bool in_img  = (x0 + k < out_w) && (y < out_h);
-                        if (in_img)
+                        const int  x0 = chunk * VEC;
+                        out_vec<T> o;
+                        if (VEC == 4)
                         {
-                            if (use_ctr)
-                                v = clamp_u8(__float2int_rn((float)v * d.contrast + contrast_add[c]));
-                            if (light)
-                            {
-                                v = clamp_u8(__float2int_rn((float)v * d.lighting_scale));
-                                v = clamp_u8(v + d.lighting_offset[cin]);
-                            }
+                            const uint32_t v4 = *reinterpret_cast<const uint32_t*>(src + x0);
+#pragma unroll
+                            for (int k = 0; k < VEC; ++k)
+                                o.v[k] = (row_in && x0 + k < out_w) ? lut[c][(v4 >> (8 * k)) & 0xFF] : zero;
                         }
-                        T e = convert_out<T>(v);
-                        if (std_on && in_img)
-                            e = standardize_value(e, lay, c);
-                        o.v[k] = e;
-                    }
-                    T* g = dst + (int64_t)c * lay.stride_c + (int64_t)y * lay.stride_y + (int64_t)x0 * lay.stride_x;
-                    if (L.vector_ok && x0 + VEC <= lay.slot_w)
-                    {
-                        *reinterpret_cast<int4*>(g) = *reinterpret_cast<const int4*>(o.v);
-                    }
-                    else
-                    {
-                        for (int k = 0; k < VEC && x0 + k < lay.slot_w; ++k)
-                            g[(int64_t)k * lay.stride_x] = o.v[k];
+                        else
+                        {
+#pragma unroll
+                            for (int k = 0; k < VEC; ++k)
+                                o.v[k] = (row_in && x0 + k < out_w) ? lut[c][src[x0 + k]] : zero;
+                        }
+                        T* g = g0 + (int64_t)x0 * lay.stride_x;
+                        if (L.vector_ok && x0 + VEC <= lay.slot_w)
+                            *reinterpret_cast<int4*>(g) = *reinterpret_cast<const int4*>(o.v);
+                        else
+                            for (int k = 0; k < VEC && x0 + k < lay.slot_w; ++k)
+                                g[(int64_t)k * lay.stride_x] = o.v[k];
                     }
                 }
             }
@@ -473,7 +529,7 @@ namespace aeonb
                           : layout.dtype == AEONB_I16 || layout.dtype == AEONB_U16 ? 2 : 1;
         L.vector_ok = slots_aligned && layout.stride_x == 1 && (layout.stride_y * elem) % 16 == 0 &&
                       (layout.stride_c * elem) % 16 == 0;
-        const size_t smem = (size_t)3 * L.rows_per_band * L.tile_pitch + (size_t)layout.slot_w * (sizeof(int) + sizeof(short2)) +
+        const size_t smem = (size_t)3 * L.rows_per_band * L.tile_pitch + (size_t)layout.slot_w * (sizeof(int2) + sizeof(short2)) +
                             (size_t)L.rows_per_band * sizeof(row_tap) + 16;
         if (smem > 200 * 1024)
         {
@@ -518,7 +574,7 @@ namespace aeonb
     namespace
     {
         // Device copy of the descriptors of one call.  Every GPU that loads the library holds these
-        // AEONB_NOALLOC_MAX_RECORDS * sizeof(aeonb_image_desc) bytes (about 68 KB) until the process exits.
+        // AEONB_NOALLOC_MAX_RECORDS * sizeof(aeonb_image_desc) bytes (about 76 KB) until the process exits.
         static __device__ __align__(256) unsigned char g_noalloc_descs[AEONB_NOALLOC_MAX_RECORDS * sizeof(aeonb_image_desc)];
 
         constexpr int MAX_DEVICES = 64;

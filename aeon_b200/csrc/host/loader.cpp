@@ -1,0 +1,391 @@
+#include "loader.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <numeric>
+#include <sstream>
+
+using namespace aeonb;
+using std::string;
+using std::vector;
+
+namespace
+{
+    const vector<string> k_loader_keys = {"manifest_filename", "manifest_root", "batch_size", "cache_directory", "block_size",
+                                          "batch_major", "subset_fraction", "shuffle_enable", "shuffle_manifest", "cpu_list",
+                                          "pinned", "random_seed", "iteration_mode", "iteration_mode_count", "etl",
+                                          "augmentation", "node_id", "node_count", "ssd_config",
+                                          // keys of this implementation
+                                          "device_output", "decode_threads", "decode_size", "scratch_pixel_stride"};
+
+    template <typename T>
+    T get(const json& js, const char* key, T dflt)
+    {
+        const json* v = js.find(key);
+        if (!v)
+            return dflt;
+        if constexpr (std::is_same<T, bool>::value)
+            return v->as_bool();
+        else if constexpr (std::is_same<T, string>::value)
+            return v->as_string();
+        else if constexpr (std::is_floating_point<T>::value)
+            return (T)v->as_double();
+        else
+            return (T)v->as_int();
+    }
+
+    vector<char> read_file(const string& path)
+    {
+        std::ifstream f(path, std::ios::binary);
+        if (!f)
+            throw std::runtime_error("error opening file '" + path + "'");
+        f.seekg(0, std::ios::end);
+        std::streamoff n = f.tellg();
+        f.seekg(0);
+        vector<char> data((size_t)std::max<std::streamoff>(n, 0));
+        if (n > 0)
+            f.read(data.data(), n);
+        return data;
+    }
+}
+
+aeonb_loader::aeonb_loader(const json& cfg, int device) : m_device(device), m_block_random(1)
+{
+    for (const char* k : {"manifest_filename", "batch_size", "etl"})
+        if (!cfg.contains(k))
+            throw std::invalid_argument(string("Required Argument: '") + k + "' not set");
+    verify_config("loader", k_loader_keys, cfg);
+    const string manifest_filename = get<string>(cfg, "manifest_filename", "");
+    const string manifest_root     = get<string>(cfg, "manifest_root", "");
+    m_batch_size                   = get<int>(cfg, "batch_size", 0);
+    if (m_batch_size <= 0)
+        throw std::invalid_argument("batch_size must be positive");
+    m_block_size = get<int>(cfg, "block_size", 5000);
+    if (m_block_size == 0)
+        m_block_size = 2 * m_batch_size;
+    const float subset = get<float>(cfg, "subset_fraction", 1.0f);
+    if (!(subset <= 1.0f && subset >= 0.0f))
+        throw std::invalid_argument("value for 'subset_fraction' out of range");
+    m_shuffle                    = get<bool>(cfg, "shuffle_enable", false);
+    const bool shuffle_manifest  = get<bool>(cfg, "shuffle_manifest", false);
+    uint32_t   seed              = get<uint32_t>(cfg, "random_seed", 0);
+    const string mode            = get<string>(cfg, "iteration_mode", "ONCE");
+    const int    mode_count      = get<int>(cfg, "iteration_mode_count", 0);
+    const uint32_t node_id       = get<uint32_t>(cfg, "node_id", 0);
+    const uint32_t node_count    = get<uint32_t>(cfg, "node_count", 0);
+    m_device_output              = get<bool>(cfg, "device_output", false);
+    if (mode == "COUNT")
+    {
+        if (mode_count <= 0)
+            throw std::invalid_argument("iteration_mode_count must be a positive integer");
+    }
+    else if (mode != "ONCE" && mode != "INFINITE")
+        throw std::invalid_argument("iteration_mode must be one of ONCE, COUNT, or INFINITE");
+    if (node_count > 1)
+    {
+        if (node_id >= node_count)
+            throw std::runtime_error("node_id can't be greater than node_count");
+        if (seed == 0)
+            seed = 1; // aeon forces a seed for multi-node runs (src/loader.cpp:110-114)
+    }
+
+    std::ifstream in(manifest_filename);
+    if (!in.is_open())
+        throw std::runtime_error("Manifest file " + manifest_filename + " doesn't exist.");
+    m_manifest.parse(in, manifest_root, subset, shuffle_manifest, seed, node_id, node_count, m_batch_size);
+    if (m_manifest.record_count == 0)
+        throw std::runtime_error("manifest file is empty");
+    m_block_random.seed(seed ? seed : std::random_device{}());
+
+    m_batch_count = (int)((m_manifest.record_count + m_batch_size - 1) / m_batch_size);
+    m_infinite    = mode == "INFINITE";
+    if (mode == "COUNT")
+        m_batch_count = mode_count;
+
+    // Random-engine slots: aeon sizes its decode chunk from the worker-thread count (src/loader.cpp:159-164)
+    json pcfg = cfg;
+    if (!cfg.contains("decode_size"))
+    {
+        string cpu_list = get<string>(cfg, "cpu_list", "");
+        if (const char* env = std::getenv("AEON_CPU_LIST"))
+            if (*env)
+                cpu_list = env;
+        int threads = (int)parse_cpu_list(cpu_list).size();
+        if (threads == 0)
+            threads = default_worker_count();
+        pcfg["decode_size"] = json((int64_t)m_batch_size * ((threads * 8 - 1) / m_batch_size + 1));
+    }
+    pcfg["random_seed"] = json((int64_t)(seed + node_id)); // src/loader.cpp:174
+    if (seed == 0)
+        pcfg["random_seed"] = json((int64_t)0);
+    config_text = cfg.dump();
+
+    if (aeonb_ctx_create(device, nullptr, &m_ctx) != AEONB_OK)
+        throw error(AEONB_ERR_CUDA, aeonb_last_error());
+    try
+    {
+        m_provider = new aeonb_provider(m_ctx, pcfg);
+        if ((int)m_manifest.types.size() != m_provider->input_count())
+            throw std::invalid_argument("the manifest has " + std::to_string(m_manifest.types.size()) +
+                                        " elements per record but the etl list needs " + std::to_string(m_provider->input_count()));
+        for (const auto& o : m_provider->outputs)
+            axis_text.push_back(o.axes);
+        for (slot& s : m_slots)
+            for (const auto& o : m_provider->outputs)
+            {
+                void*        p     = nullptr;
+                const size_t bytes = (size_t)m_batch_size * o.shape.byte_size();
+                if (m_device_output)
+                {
+                    AEONB_CUDA(cudaMalloc(&p, bytes));
+                    AEONB_CUDA(cudaMemset(p, 0, bytes));
+                }
+                else
+                {
+                    AEONB_CUDA(cudaMallocHost(&p, bytes));
+                    std::memset(p, 0, bytes);
+                }
+                s.buffers.push_back(p);
+            }
+    }
+    catch (...)
+    {
+        delete m_provider;
+        aeonb_ctx_destroy(m_ctx);
+        throw;
+    }
+    m_order.resize(m_manifest.record_count);
+    std::iota(m_order.begin(), m_order.end(), 0);
+    start_producer();
+}
+
+aeonb_loader::~aeonb_loader()
+{
+    stop_producer();
+    cudaSetDevice(m_device);
+    for (slot& s : m_slots)
+        for (void* p : s.buffers)
+            m_device_output ? cudaFree(p) : cudaFreeHost(p);
+    delete m_provider;
+    aeonb_ctx_destroy(m_ctx);
+}
+
+void aeonb_loader::load_record(const vector<string>& fields, vector<vector<char>>& elems)
+{
+    // aeon block_loader_file::filler (src/block_loader_file.cpp:56-104)
+    elems.clear();
+    for (size_t j = 0; j < fields.size(); ++j)
+    {
+        const string& e = fields[j];
+        switch (m_manifest.types[j])
+        {
+        case element_t::FILE: elems.push_back(read_file(e)); break;
+        case element_t::BINARY: elems.push_back(base64_decode(e)); break;
+        case element_t::STRING: elems.emplace_back(e.begin(), e.end()); break;
+        case element_t::ASCII_INT:
+        {
+            int32_t v = (int32_t)std::stod(e);
+            elems.emplace_back((char*)&v, (char*)&v + sizeof v);
+            break;
+        }
+        case element_t::ASCII_FLOAT:
+        {
+            float v = std::stof(e);
+            elems.emplace_back((char*)&v, (char*)&v + sizeof v);
+            break;
+        }
+        }
+    }
+}
+
+void aeonb_loader::start_producer()
+{
+    m_stop = false;
+    for (slot& s : m_slots)
+    {
+        s.full  = false;
+        s.error = nullptr;
+    }
+    m_consume = 0;
+    m_holding = false;
+    m_thread  = std::thread([this] { producer(); });
+}
+
+void aeonb_loader::stop_producer()
+{
+    {
+        std::lock_guard<std::mutex> lk(m_mutex);
+        m_stop = true;
+    }
+    m_cv.notify_all();
+    if (m_thread.joinable())
+        m_thread.join();
+}
+
+void aeonb_loader::producer()
+{
+    cudaSetDevice(m_device);
+    const int nin = m_provider->input_count();
+    int       fill = 0;
+    vector<vector<vector<char>>> held(m_batch_size);
+    for (;;)
+    {
+        {
+            std::unique_lock<std::mutex> lk(m_mutex);
+            m_cv.wait(lk, [&] { return m_stop || !m_slots[fill].full; });
+            if (m_stop)
+                return;
+        }
+        slot& s = m_slots[fill];
+        try
+        {
+            vector<const void*> elems((size_t)m_batch_size * nin);
+            vector<size_t>      sizes((size_t)m_batch_size * nin);
+            for (int r = 0; r < m_batch_size; ++r)
+            {
+                if (m_cursor == m_order.size())
+                {
+                    // the record stream never ends: wrap to the start of the data set (src/block_manager.cpp:86-92),
+                    // reshuffling block order and block contents when shuffle_enable is set
+                    m_cursor = 0;
+                    if (m_shuffle)
+                    {
+                        const size_t n      = m_order.size();
+                        const size_t blocks = std::max<size_t>(1, (size_t)std::round((float)n / (float)m_block_size));
+                        const size_t bsz    = (size_t)std::ceil((float)n / (float)blocks);
+                        vector<size_t> seq(blocks);
+                        std::iota(seq.begin(), seq.end(), 0);
+                        std::shuffle(seq.begin(), seq.end(), m_block_random);
+                        vector<size_t> order;
+                        for (size_t b : seq)
+                        {
+                            const size_t lo = b * bsz, hi = std::min(n, lo + bsz);
+                            const size_t at = order.size();
+                            for (size_t i = lo; i < hi; ++i)
+                                order.push_back(i);
+                            std::shuffle(order.begin() + at, order.end(), m_block_random);
+                        }
+                        m_order.swap(order);
+                    }
+                }
+                load_record(m_manifest.records[m_order[m_cursor++]], held[r]);
+                for (int e = 0; e < nin; ++e)
+                {
+                    elems[(size_t)r * nin + e] = held[r][e].data();
+                    sizes[(size_t)r * nin + e] = held[r][e].size();
+                }
+            }
+            m_provider->run(elems.data(), sizes.data(), m_batch_size, s.buffers.data(), m_device_output);
+        }
+        catch (...)
+        {
+            s.error = std::current_exception();
+        }
+        {
+            std::lock_guard<std::mutex> lk(m_mutex);
+            s.full = true;
+        }
+        m_cv.notify_all();
+        fill ^= 1;
+    }
+}
+
+int aeonb_loader::next(void** buffers)
+{
+    if (!m_infinite && m_position >= m_batch_count)
+        return AEONB_END;
+    std::unique_lock<std::mutex> lk(m_mutex);
+    if (m_holding)
+    {
+        m_slots[m_consume ^ 1].full = false; // the batch handed out by the previous call is released now
+        m_holding                   = false;
+        m_cv.notify_all();
+    }
+    slot& s = m_slots[m_consume];
+    m_cv.wait(lk, [&] { return s.full; });
+    m_consume ^= 1;
+    m_holding = true;
+    if (s.error)
+    {
+        std::exception_ptr e = s.error;
+        s.error              = nullptr;
+        std::rethrow_exception(e);
+    }
+    for (size_t i = 0; i < s.buffers.size(); ++i)
+        buffers[i] = s.buffers[i];
+    m_position++;
+    if (m_infinite && m_position == m_batch_count)
+        m_position = 0;
+    return AEONB_OK;
+}
+
+void aeonb_loader::reset()
+{
+    // restart the epoch from the first record of the data set (src/loader.hpp:205-210)
+    stop_producer();
+    m_cursor   = 0;
+    m_position = 0;
+    m_provider->slot_cursor = 0;
+    std::iota(m_order.begin(), m_order.end(), 0);
+    start_producer();
+}
+
+extern "C" {
+
+int aeonb_loader_create(const char* config_json, int device, aeonb_loader** out)
+{
+    return guarded([&]() {
+        if (!config_json || !out)
+            throw std::invalid_argument("aeonb_loader_create: NULL argument");
+        *out = new aeonb_loader(json::parse(config_json), device);
+        return AEONB_OK;
+    });
+}
+
+void aeonb_loader_destroy(aeonb_loader* l)
+{
+    delete l;
+}
+
+int aeonb_loader_record_count(const aeonb_loader* l) { return l ? l->record_count() : 0; }
+int aeonb_loader_batch_size(const aeonb_loader* l) { return l ? l->batch_size() : 0; }
+int aeonb_loader_batch_count(const aeonb_loader* l) { return l ? l->batch_count() : 0; }
+int aeonb_loader_output_count(const aeonb_loader* l) { return l ? aeonb_provider_output_count(l->provider()) : 0; }
+const char* aeonb_loader_output_name(const aeonb_loader* l, int i) { return l ? aeonb_provider_output_name(l->provider(), i) : nullptr; }
+int aeonb_loader_output_shape(const aeonb_loader* l, int i, int64_t* dims, int32_t* dtype)
+{
+    return l ? aeonb_provider_output_shape(l->provider(), i, dims, dtype) : fail(AEONB_ERR_INVALID, "loader is NULL");
+}
+const char* aeonb_loader_axis_names(const aeonb_loader* l, int i)
+{
+    if (!l || i < 0 || i >= (int)l->axis_text.size())
+        return nullptr;
+    return l->axis_text[i].c_str();
+}
+const char* aeonb_loader_config(const aeonb_loader* l) { return l ? l->config_text.c_str() : nullptr; }
+
+int aeonb_loader_next(aeonb_loader* l, void** buffers)
+{
+    return guarded([&]() {
+        if (!l || !buffers)
+            throw std::invalid_argument("aeonb_loader_next: NULL argument");
+        return l->next(buffers);
+    });
+}
+
+int aeonb_loader_reset(aeonb_loader* l)
+{
+    return guarded([&]() {
+        if (!l)
+            throw std::invalid_argument("aeonb_loader_reset: loader is NULL");
+        l->reset();
+        return AEONB_OK;
+    });
+}
+
+int aeonb_loader_position(const aeonb_loader* l) { return l ? l->position() : 0; }
+
+} // extern "C"

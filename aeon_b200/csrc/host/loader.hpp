@@ -1,0 +1,91 @@
+// Thin host shell that keeps aeon's loader surface on top of the provider:
+// configuration keys and defaults of loader_config (src/loader.hpp:50-109), the TSV manifest
+// (src/manifest_file.cpp:115-320), record loading (src/block_loader_file.cpp:45-117), the
+// endless block stream with epoch wrap-around (src/block_manager.cpp:61-106) and the
+// ONCE / INFINITE / COUNT position logic (src/loader.cpp:141-155,234-257).
+// A producer thread fills one of two output buffer sets while the consumer holds the other,
+// as aeon's async_manager stages do (src/async_manager.hpp:91-117).
+#pragma once
+
+#include <condition_variable>
+#include <deque>
+#include <exception>
+#include <mutex>
+#include <random>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "provider.hpp"
+
+namespace aeonb
+{
+    enum class element_t
+    {
+        FILE,
+        BINARY,
+        STRING,
+        ASCII_INT,
+        ASCII_FLOAT
+    };
+
+    struct manifest
+    {
+        std::vector<element_t>                 types;
+        std::vector<std::vector<std::string>>  records; // after subset / node sharding
+        size_t                                 record_count = 0;
+        void parse(std::istream& in, const std::string& root, float subset_fraction, bool shuffle, uint32_t seed, uint32_t node_id,
+                   uint32_t node_count, int batch_size);
+    };
+
+    std::vector<char> base64_decode(const std::string& in);
+    std::vector<int>  parse_cpu_list(const std::string& s);
+}
+
+struct aeonb_loader
+{
+    explicit aeonb_loader(const aeonb::json& cfg, int device);
+    ~aeonb_loader();
+
+    int  record_count() const { return (int)m_manifest.record_count; }
+    int  batch_size() const { return m_batch_size; }
+    int  batch_count() const { return m_batch_count; }
+    int  position() const { return m_position; }
+    int  next(void** buffers); // AEONB_OK or AEONB_END
+    void reset();
+
+    aeonb_provider*  provider() const { return m_provider; }
+    std::string      config_text;
+    std::vector<std::string> axis_text;
+
+private:
+    struct slot
+    {
+        std::vector<void*> buffers; // per output: pinned host or device memory for one batch
+        std::exception_ptr error;
+        bool               full = false;
+    };
+    void producer();
+    void start_producer();
+    void stop_producer();
+    void load_record(const std::vector<std::string>& fields, std::vector<std::vector<char>>& elems);
+
+    aeonb::manifest m_manifest;
+    aeonb_ctx*      m_ctx      = nullptr;
+    aeonb_provider* m_provider = nullptr;
+    int             m_device   = 0;
+    int             m_batch_size = 0, m_batch_count = 0, m_position = 0;
+    bool            m_infinite = false, m_device_output = false, m_shuffle = false;
+    int             m_block_size = 5000;
+    std::minstd_rand0 m_block_random;
+
+    slot                    m_slots[2];
+    int                     m_consume = 0;    // slot the consumer reads next
+    bool                    m_holding = false; // consumer currently holds m_slots[m_consume ^ 1]... released on the next call
+    std::thread             m_thread;
+    std::mutex              m_mutex;
+    std::condition_variable m_cv;
+    bool                    m_stop = false;
+    size_t                  m_cursor = 0; // next record of the endless stream (producer side)
+    std::vector<size_t>     m_order;      // record order of the current epoch
+};

@@ -39,19 +39,32 @@ namespace aeonb
             // double-accumulating product, the sum as a float weighted add.
             const float oms = 1.0f - saturation;
             const float sb  = (float)((double)saturation * (double)brightness);
+            float       m[3][3];
+            bool        diagonal = true;
             for (int i = 0; i < 3; ++i)
                 for (int j = 0; j < 3; ++j)
                 {
                     const float gray = (float)((double)oms * (double)k_gray[j]);
                     volatile float a = (i == j) ? sb : 0.0f;
                     volatile float b = gray * brightness;
-                    const float    m = a + b;
-                    d.color_matrix[i * 3 + j] = sat_s16(std::lrintf(m * 1024.0f)); // cv::transform's 10-bit form
+                    m[i][j]          = a + b;
+                    d.color_matrix[i * 3 + j] = sat_s16(std::lrintf(m[i][j] * 1024.0f)); // cv::transform's 10-bit form
+                    if (i != j && std::fabs((double)m[i][j]) > 1.1920928955078125e-07)  // FLT_EPSILON
+                        diagonal = false;
                 }
+            if (diagonal)
+            {
+                // cv::transform sends a diagonal matrix (saturation == 1) to a per-channel float scale
+                d.color_enable = 2;
+                for (int i = 0; i < 3; ++i)
+                    d.color_scale[i] = m[i][i];
+            }
         }
         else
             for (int i = 0; i < 9; ++i)
                 d.color_matrix[i] = (i % 4 == 0) ? 1024 : 0;
+        if (d.color_enable != 2)
+            d.color_scale[0] = d.color_scale[1] = d.color_scale[2] = 1.0f;
         d.reserved0       = 0;
         d.hue             = hue;
         const int block   = hsv_vector_block();

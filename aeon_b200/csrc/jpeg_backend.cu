@@ -8,13 +8,13 @@
 // bits between the column and row passes, triangle-filter ("fancy") chroma upsampling and
 // 16-bit fixed-point colour conversion.
 //
-// Work decomposition: one CTA per (record, MCU row).  Eight threads cooperate on a block:
-// in the column pass thread c loads column c of the block with one 128-bit load (the host
-// stores blocks column-major for exactly this), in the row pass thread r owns row r; the
-// 8x8 transpose in between goes through a conflict-free padded shared-memory scratch.
-// Samples land in shared-memory component planes; the CTA also transforms the chroma
-// blocks of the MCU rows above and below, because the triangle filter needs one chroma
-// row on either side.  A second phase upsamples, converts and writes 4 pixels per thread
+// Work decomposition: one CTA per (record, MCU row).  The coefficient blocks the CTA needs are
+// staged in shared memory with coalesced 16-byte asynchronous copies (XOR-swizzled so that the
+// next step is free of bank conflicts); then ONE THREAD transforms ONE 8x8 BLOCK entirely in
+// registers: eight 128-bit shared loads (the host stores blocks column-major, so a load is a
+// block column), column pass, row pass (the transpose is register renaming), saturating pack,
+// 8-byte stores into shared component planes.  The CTA also transforms the chroma blocks of the
+// MCU rows above and below (only the one sample row the triangle filter needs on either side).  A second phase upsamples, converts and writes 4 pixels per thread
 // (one 128-bit store per thread for 4-byte pixels, three 32-bit stores for 3-byte pixels).
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -26,7 +26,6 @@ namespace aeonb
     namespace
     {
         constexpr int JPG_THREADS = 256;
-        constexpr int WS_BLOCK    = 72; // int32 words per block in the transpose scratch (8 rows * stride 9)
 
         struct jpeg_launch
         {
@@ -53,7 +52,7 @@ namespace aeonb
 
         // One 8-point inverse DCT (LLM factorisation); inputs x[0..7] are frequency samples,
         // outputs are descaled by `shift` with round-half-up.
-        template <int SHIFT>
+        template <int SHIFT, int LEVEL>
         __device__ __forceinline__ void idct8(const int (&x)[8], int (&o)[8])
         {
             int z1 = (x[2] + x[6]) * C_0_541196100;
@@ -81,7 +80,7 @@ namespace aeonb
             o1 += z2 + z4;
             o2 += z2 + z3;
             o3 += z1 + z4;
-            constexpr int RND = 1 << (SHIFT - 1);
+            constexpr int RND = (1 << (SHIFT - 1)) + LEVEL * (1 << SHIFT); // rounding, plus an optional level shift of the result
             o[0] = (e0 + o3 + RND) >> SHIFT;
             o[7] = (e0 - o3 + RND) >> SHIFT;
             o[1] = (e1 + o2 + RND) >> SHIFT;
@@ -90,6 +89,15 @@ namespace aeonb
             o[5] = (e2 - o1 + RND) >> SHIFT;
             o[3] = (e3 + o0 + RND) >> SHIFT;
             o[4] = (e3 - o0 + RND) >> SHIFT;
+        }
+
+        // Four signed values saturated to 0..255 and packed little-endian into one word (two instructions).
+        __device__ __forceinline__ uint32_t pack_sat_u8(int v0, int v1, int v2, int v3)
+        {
+            uint32_t hi, w;
+            asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(v3), "r"(v2), "r"(0));
+            asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(v1), "r"(v0), "r"(hi));
+            return w;
         }
 
         // A list of block rows to transform: component, block row in the coefficient plane,
@@ -133,13 +141,14 @@ namespace aeonb
             }
         }
 
-        __global__ void __launch_bounds__(JPG_THREADS) jpeg_backend_kernel(const jpeg_launch L)
+        __global__ void __launch_bounds__(JPG_THREADS, 3) jpeg_backend_kernel(const jpeg_launch L)
         {
             extern __shared__ __align__(16) unsigned char smem[];
             __shared__ aeonb_jpeg_desc d;
-            __shared__ uint16_t        quant[3][64];
+            __shared__ __align__(16) uint16_t quant[3][64];
             __shared__ block_row_job   jobs[8];
             __shared__ int             njobs;
+            __shared__ int             job_first[9]; // first work item of each job, and the total
 
             const int  tid  = threadIdx.x;
             const int2 wk   = L.work[blockIdx.x];
@@ -165,10 +174,11 @@ namespace aeonb
             uint8_t*  yplane  = smem;
             uint8_t*  cbplane = yplane + yrows * yw;
             uint8_t*  crplane = cbplane + crows * cwp;
-            int*      scratch = reinterpret_cast<int*>(smem + ((yrows * yw + 2 * crows * cwp + 15) & ~15));
+            unsigned char* coefs = smem + ((yrows * yw + 2 * crows * cwp + 127) & ~127); // staged coefficient blocks
 
             if (tid == 0)
             {
+                // full block rows first, halo rows (one sample row wanted) last, so that warps do not mix them
                 int n = 0;
                 for (int v = 0; v < vs0; ++v)
                     jobs[n++] = block_row_job{0, mrow * vs0 + v, v * 8, -1};
@@ -176,69 +186,91 @@ namespace aeonb
                 {
                     const int halo = fv == 2 ? 1 : 0;
                     for (int c = 1; c < 3; ++c)
-                    {
                         jobs[n++] = block_row_job{c, mrow, halo, -1};
-                        if (halo && mrow > 0)
+                    for (int c = 1; c < 3 && halo; ++c)
+                    {
+                        if (mrow > 0)
                             jobs[n++] = block_row_job{c, mrow - 1, halo - 8, 7};
-                        if (halo && mrow + 1 < d.blocks_h[c])
+                        if (mrow + 1 < d.blocks_h[c])
                             jobs[n++] = block_row_job{c, mrow + 1, halo + 8, 0};
                     }
                 }
-                njobs = n;
+                int total = 0;
+                for (int j = 0; j < n; ++j)
+                {
+                    job_first[j] = total;
+                    total += d.blocks_w[jobs[j].comp];
+                }
+                job_first[n] = total;
+                njobs        = n;
             }
             __syncthreads();
 
-            // ---- phase 1: dequantise + inverse DCT into the shared sample planes
+            // ---- phase 1a: stage the coefficient blocks of this CTA in shared memory with coalesced 16-byte
+            //      asynchronous copies.  Chunk c (one block column) of block b lands at chunk (c ^ (b & 7)) of the
+            //      block's 128 bytes, so that threads owning neighbouring blocks read different banks in phase 1b.
+            const int total = job_first[njobs];
             {
-                const int lane8 = tid & 7;                 // column in pass 1, row in pass 2
-                const int slot  = tid >> 3;                // block slot inside the CTA (32 per iteration)
-                int*      ws    = scratch + slot * WS_BLOCK;
-                for (int j = 0; j < njobs; ++j)
+                for (int i = tid; i < total * 8; i += JPG_THREADS)
                 {
-                    const block_row_job job = jobs[j];
-                    const int           bw  = d.blocks_w[job.comp];
-                    const int16_t*      src = d.coef[job.comp] + (size_t)job.block_row * bw * 64;
+                    const int item = i >> 3, c = i & 7;
+                    int       j    = 0;
+                    while (item >= job_first[j + 1])
+                        ++j;
+                    const int      b   = item - job_first[j];
+                    const int16_t* src = d.coef[jobs[j].comp] + ((size_t)jobs[j].block_row * d.blocks_w[jobs[j].comp] + b) * 64 + c * 8;
+                    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(coefs + item * 128 + ((c ^ (item & 7)) << 4));
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            }
+            __syncthreads();
+
+            // ---- phase 1b: dequantise + inverse DCT into the shared sample planes; one thread = one 8x8 block
+            {
+                for (int item = tid; item < total; item += JPG_THREADS)
+                {
+                    int j = 0;
+                    while (item >= job_first[j + 1])
+                        ++j;
+                    const block_row_job job   = jobs[j];
+                    const int           b     = item - job_first[j];
+                    const int4*         q4    = reinterpret_cast<const int4*>(quant[job.comp]);
                     uint8_t*            plane = job.comp == 0 ? yplane : job.comp == 1 ? cbplane : crplane;
                     const int           pitch = job.comp == 0 ? yw : cwp;
-                    const uint16_t*     q     = quant[job.comp] + lane8 * 8;
-                    for (int b0 = 0; b0 < bw; b0 += JPG_THREADS / 8)
+                    const unsigned char* blk  = coefs + item * 128;
+                    int                 ws[8][8]; // [row][column] after the column pass
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
                     {
-                        const int  b      = b0 + slot;
-                        const bool active = b < bw;
-                        int        col[8];
-                        if (active)
-                        {
-                            const int4 raw = __ldg(reinterpret_cast<const int4*>(src + (size_t)b * 64 + lane8 * 8));
-                            int        x[8];
-                            x[0] = (short)(raw.x & 0xFFFF) * q[0];
-                            x[1] = (raw.x >> 16) * q[1];
-                            x[2] = (short)(raw.y & 0xFFFF) * q[2];
-                            x[3] = (raw.y >> 16) * q[3];
-                            x[4] = (short)(raw.z & 0xFFFF) * q[4];
-                            x[5] = (raw.z >> 16) * q[5];
-                            x[6] = (short)(raw.w & 0xFFFF) * q[6];
-                            x[7] = (raw.w >> 16) * q[7];
-                            idct8<CONST_BITS - PASS1_BITS>(x, col);
+                        const int4 raw = *reinterpret_cast<const int4*>(blk + ((c ^ (item & 7)) << 4));
+                        const int4 q   = q4[c];
+                        int        x[8], o[8];
+                        x[0] = (short)(raw.x & 0xFFFF) * (q.x & 0xFFFF);
+                        x[1] = (raw.x >> 16) * (int)((unsigned)q.x >> 16);
+                        x[2] = (short)(raw.y & 0xFFFF) * (q.y & 0xFFFF);
+                        x[3] = (raw.y >> 16) * (int)((unsigned)q.y >> 16);
+                        x[4] = (short)(raw.z & 0xFFFF) * (q.z & 0xFFFF);
+                        x[5] = (raw.z >> 16) * (int)((unsigned)q.z >> 16);
+                        x[6] = (short)(raw.w & 0xFFFF) * (q.w & 0xFFFF);
+                        x[7] = (raw.w >> 16) * (int)((unsigned)q.w >> 16);
+                        idct8<CONST_BITS - PASS1_BITS, 0>(x, o);
 #pragma unroll
-                            for (int r = 0; r < 8; ++r)
-                                ws[r * 9 + lane8] = col[r];
-                        }
-                        __syncwarp();
-                        if (active && (job.only_row < 0 || job.only_row == lane8))
-                        {
-                            int x[8], o[8];
+                        for (int r = 0; r < 8; ++r)
+                            ws[r][c] = o[r];
+                    }
+                    uint8_t* out = plane + job.dst_row * pitch + b * 8;
 #pragma unroll
-                            for (int c = 0; c < 8; ++c)
-                                x[c] = ws[lane8 * 9 + c];
-                            idct8<CONST_BITS + PASS1_BITS + 3>(x, o);
-                            const uint32_t lo = clamp255(o[0] + 128) | (clamp255(o[1] + 128) << 8) | (clamp255(o[2] + 128) << 16) |
-                                                (clamp255(o[3] + 128) << 24);
-                            const uint32_t hi = clamp255(o[4] + 128) | (clamp255(o[5] + 128) << 8) | (clamp255(o[6] + 128) << 16) |
-                                                (clamp255(o[7] + 128) << 24);
-                            uint2* out = reinterpret_cast<uint2*>(plane + (job.dst_row + lane8) * pitch + b * 8);
-                            *out       = make_uint2(lo, hi);
-                        }
-                        __syncwarp();
+                    for (int r = 0; r < 8; ++r)
+                    {
+                        if (job.only_row >= 0 && job.only_row != r)
+                            continue;
+                        int o[8];
+                        // the +128 level shift rides on the rounding constant
+                        idct8<CONST_BITS + PASS1_BITS + 3, 128>(ws[r], o);
+                        *reinterpret_cast<uint2*>(out + r * pitch) = make_uint2(pack_sat_u8(o[0], o[1], o[2], o[3]),
+                                                                                pack_sat_u8(o[4], o[5], o[6], o[7]));
                     }
                 }
             }
@@ -254,10 +286,108 @@ namespace aeonb
                 const int chh   = ncomp == 3 ? (H * d.vs[1] + vs0 - 1) / vs0 : 0; // real chroma rows / cols
                 const int cw    = ncomp == 3 ? (W * d.hs[1] + hs0 - 1) / hs0 : 0;
                 const int crow_base = mrow * 8 - (fv == 2 ? 1 : 0); // chroma plane row of shared row 0
-                for (int i = tid; i < rows * quads; i += JPG_THREADS)
+                int       fast_cols = 0;
+                if (fh == 2 && fv == 2)
                 {
-                    const int ry = i / quads;
-                    const int x0 = (i - ry * quads) * 4;
+                    // 4:2:0 fast path: one thread = 8 x 2 output pixels (4 chroma samples of one chroma row).
+                    // The last column group of a row and partial groups take the generic path below.
+                    const int groups   = W >> 3;                       // full 8-pixel groups per row
+                    const int interior = min(groups, (cw - 1) >> 2);   // groups whose chroma columns cx0..cx0+4 all exist
+                    const int pairs    = (rows + 1) >> 1;
+                    for (int i = tid; i < pairs * interior; i += JPG_THREADS)
+                    {
+                        const int k   = i / interior;                  // chroma row inside the MCU row
+                        const int j   = i - k * interior;
+                        const int x0  = j << 3, cx0 = j << 2;
+                        const int cy  = mrow * 8 + k;
+                        const int cr  = cy - crow_base;
+                        const int up  = cy > 0 ? cr - 1 : cr;
+                        const int dn  = cy + 1 < chh ? cr + 1 : cr;
+                        const int lft = max(cx0 - 1, 0);
+                        int       sb_t[6], sb_b[6], sr_t[6], sr_b[6];  // vertical sums for columns cx0-1 .. cx0+4
+#pragma unroll
+                        for (int comp = 0; comp < 2; ++comp)
+                        {
+                            const uint8_t* pl = comp == 0 ? cbplane : crplane;
+                            int            cu[6], cm[6], cd[6];
+                            const uint32_t wu = *reinterpret_cast<const uint32_t*>(pl + up * cwp + cx0);
+                            const uint32_t wm = *reinterpret_cast<const uint32_t*>(pl + cr * cwp + cx0);
+                            const uint32_t wd = *reinterpret_cast<const uint32_t*>(pl + dn * cwp + cx0);
+                            cu[0] = pl[up * cwp + lft];
+                            cm[0] = pl[cr * cwp + lft];
+                            cd[0] = pl[dn * cwp + lft];
+                            cu[5] = pl[up * cwp + cx0 + 4];
+                            cm[5] = pl[cr * cwp + cx0 + 4];
+                            cd[5] = pl[dn * cwp + cx0 + 4];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+                            {
+                                cu[q + 1] = (wu >> (8 * q)) & 0xFF;
+                                cm[q + 1] = (wm >> (8 * q)) & 0xFF;
+                                cd[q + 1] = (wd >> (8 * q)) & 0xFF;
+                            }
+#pragma unroll
+                            for (int q = 0; q < 6; ++q)
+                            {
+                                const int t = 3 * cm[q];
+                                if (comp == 0)
+                                {
+                                    sb_t[q] = t + cu[q];
+                                    sb_b[q] = t + cd[q];
+                                }
+                                else
+                                {
+                                    sr_t[q] = t + cu[q];
+                                    sr_b[q] = t + cd[q];
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int half = 0; half < 2; ++half)
+                        {
+                            const int y = y0 + 2 * k + half;
+                            if (y >= H)
+                                break;
+                            const int* sb = half ? sb_b : sb_t;
+                            const int* sr = half ? sr_b : sr_t;
+                            const uint2 yy = *reinterpret_cast<const uint2*>(yplane + (2 * k + half) * yw + x0);
+                            uint32_t    px[8];
+#pragma unroll
+                            for (int p = 0; p < 8; ++p)
+                            {
+                                const int c  = (p >> 1) + 1;
+                                const int u  = (((p & 1) ? 3 * sb[c] + sb[c + 1] + 7 : 3 * sb[c] + sb[c - 1] + 8) >> 4) - 128;
+                                const int v  = (((p & 1) ? 3 * sr[c] + sr[c + 1] + 7 : 3 * sr[c] + sr[c - 1] + 8) >> 4) - 128;
+                                const int yv = ((p < 4 ? yy.x : yy.y) >> (8 * (p & 3))) & 0xFF;
+                                const int r  = yv + ((91881 * v + 32768) >> 16);
+                                const int g  = yv + ((-22554 * u - 46802 * v + 32768) >> 16);
+                                const int b  = yv + ((116130 * u + 32768) >> 16);
+                                px[p]        = pack_sat_u8(b, g, r, 0);
+                            }
+                            uint8_t* out = d.dst + (size_t)y * d.dst_pitch + (size_t)x0 * pix;
+                            if (pix == 4)
+                            {
+                                reinterpret_cast<uint4*>(out)[0] = make_uint4(px[0], px[1], px[2], px[3]);
+                                reinterpret_cast<uint4*>(out)[1] = make_uint4(px[4], px[5], px[6], px[7]);
+                            }
+                            else
+                            {
+                                uint2* o2 = reinterpret_cast<uint2*>(out); // 24 bytes, 8-byte aligned (x0 is a multiple of 8)
+                                o2[0] = make_uint2((px[0] & 0xFFFFFF) | (px[1] << 24), ((px[1] >> 8) & 0xFFFF) | (px[2] << 16));
+                                o2[1] = make_uint2(((px[2] >> 16) & 0xFF) | (px[3] << 8), (px[4] & 0xFFFFFF) | (px[5] << 24));
+                                o2[2] = make_uint2(((px[5] >> 8) & 0xFFFF) | (px[6] << 16), ((px[6] >> 16) & 0xFF) | (px[7] << 8));
+                            }
+                        }
+                    }
+                    fast_cols = interior << 3; // pixels [0, fast_cols) of every row are done
+                }
+                // generic path: one thread = 4 pixels of one row (all sampling modes, and the right edge of 4:2:0)
+                const int quad0  = fast_cols >> 2;
+                const int nquads = quads - quad0;
+                for (int i = tid; i < rows * nquads; i += JPG_THREADS)
+                {
+                    const int ry = i / nquads;
+                    const int x0 = (quad0 + i - ry * nquads) * 4;
                     const int y  = y0 + ry;
                     const int n  = min(4, W - x0);
                     int       b[4], g[4], r[4];
@@ -380,6 +510,7 @@ namespace aeonb
         const int fv    = d.ncomp == 3 ? d.vs[0] : 1;
         const int crows = 8 + (fv == 2 ? 2 : 0);
         const size_t planes = (size_t)yrows * d.blocks_w[0] * 8 + (d.ncomp == 3 ? (size_t)2 * crows * d.blocks_w[1] * 8 : 0);
-        return ((planes + 15) & ~(size_t)15) + (size_t)(JPG_THREADS / 8) * WS_BLOCK * sizeof(int);
+        const size_t blocks = (size_t)d.vs[0] * d.blocks_w[0] + (d.ncomp == 3 ? (size_t)2 * (fv == 2 ? 3 : 1) * d.blocks_w[1] : 0);
+        return ((planes + 127) & ~(size_t)127) + blocks * 128;
     }
 }

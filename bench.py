@@ -165,6 +165,8 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--pixel-stride", type=int, default=4)
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--stages", default="all",
+                    help="kernels-only experiments: comma list of photometric stages to keep (matrix,hue,contrast,lighting) or 'all'/'none'")
     ap.add_argument("--kernels-only", action="store_true",
                     help="time the resident-input kernels only (used for profiler captures; e2e and cpu_baseline are null)")
     args = ap.parse_args()
@@ -234,8 +236,11 @@ def main():
             d.crop_x, d.crop_y, d.crop_w, d.crop_h = (int(v) for v in p[i, 0:4])
             d.out_w, d.out_h, d.interp, d.flip = OUT, OUT, L.INTERP_LINEAR, int(p[i, 6])
             light = (C.c_float * 3)(*[float(v) for v in p[i, 12:15]])
-            L.check(lib.aeonb_image_desc_set_photometric(C.byref(d), float(p[i, 9]), float(p[i, 10]), float(p[i, 11]),
-                                                         int(p[i, 8]), light, float(p[i, 15])))
+            st_on = {"matrix", "hue", "contrast", "lighting"} if args.stages == "all" else set(args.stages.split(","))
+            L.check(lib.aeonb_image_desc_set_photometric(
+                C.byref(d), float(p[i, 9]) if "contrast" in st_on else 1.0, float(p[i, 10]) if "matrix" in st_on else 1.0,
+                float(p[i, 11]) if "matrix" in st_on else 1.0, int(p[i, 8]) if "hue" in st_on else 0,
+                light if "lighting" in st_on else None, float(p[i, 15])))
             d.dst = out.data_ptr() + i * 3 * OUT * OUT * 4
         batches.append((jd, idesc))
     torch.cuda.synchronize()

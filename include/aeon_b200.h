@@ -93,9 +93,10 @@ typedef struct aeonb_image_desc
     int32_t interp;       /* aeonb_interp */
     int32_t flip;         /* horizontal flip, applied last */
     /* photometric (src/image.cpp:358-406); every stage rounds to uint8 before the next */
-    int32_t color_enable; /* apply color_matrix (brightness / saturation) */
+    int32_t color_enable; /* 0: off; 1: dense 3x3 color_matrix; 2: diagonal matrix, per-channel color_scale */
     int16_t color_matrix[9]; /* round(m*1024), row-major, BGR order: the 10-bit form cv::transform uses */
     int16_t reserved0;
+    float   color_scale[3];  /* diagonal case (brightness alone): cv::transform then scales each channel in float */
     int32_t hue;          /* added to H (units of 2 degrees); 0 disables the HSV round trip */
     int32_t hsv_vector_cols; /* columns [0, hsv_vector_cols) of each row truncate in HSV->BGR, the rest round */
     float   contrast;     /* 1.0f disables; otherwise x*c + (1-c)*channel mean of the image */
@@ -135,7 +136,7 @@ int64_t aeonb_image_batch_bytes(const aeonb_image_desc* descs, int n, const aeon
  * It has no counterpart in the reference.  It needs no context: it runs on the CURRENT device and
  * on `stream` (a cudaStream_t, NULL for the default stream), and calls neither cudaMalloc /
  * cudaFree nor any allocating library routine.  The device copy of the descriptors lives in a
- * fixed array inside the library (about 68 KB per GPU that loads the library, held until exit),
+ * fixed array inside the library (about 76 KB per GPU that loads the library, held until exit),
  * hence the limit of AEONB_NOALLOC_MAX_RECORDS (512) records per call; larger n is rejected with
  * AEONB_ERR_INVALID.  The first call on a device looks up the array's device address; make that
  * first call before starting any stream capture.  All calls share the one array: two calls whose

@@ -139,14 +139,26 @@ def color_matrix(brightness, saturation):
 TRANSFORM_BITS = 10
 
 
+def is_diagonal(m):
+    """cv::transform's test: every off-diagonal entry is at most FLT_EPSILON in magnitude."""
+    m = np.asarray(m, f32)
+    off = np.abs(m[~np.eye(3, dtype=bool)])
+    return bool(np.all(off.astype(f64) <= np.finfo(f32).eps))
+
+
 def transform_u8(img, m):
     """``cv::transform`` of an 8-bit 3-channel image by a 3x3 float matrix.
 
-    OpenCV evaluates this case in 10-bit fixed point: coefficients are
+    OpenCV evaluates the dense case in 10-bit fixed point: coefficients are
     ``round_half_even(m*1024)`` saturated to int16, the dot product is rounded with
     ``+512 >> 10`` and saturated to uint8 (src/image.cpp:372 -> cv::transform).
     """
-    mi = np.clip(_rne(np.asarray(m, f32) * f32(1 << TRANSFORM_BITS)), -32768, 32767).astype(np.int32)
+    m = np.asarray(m, f32)
+    if is_diagonal(m):
+        # OpenCV routes a diagonal matrix (brightness alone) to a per-channel float scale instead
+        d = np.array([m[0, 0], m[1, 1], m[2, 2]], f32)
+        return _sat_u8(_rne(img.astype(f32) * d[None, None, :]))
+    mi = np.clip(_rne(m * f32(1 << TRANSFORM_BITS)), -32768, 32767).astype(np.int32)
     s = img.astype(np.int32)
     out = np.empty(img.shape, np.int32)
     for k in range(3):

@@ -1,0 +1,130 @@
+"""Pins of the numpy oracle: aeon's golden vectors and known answers, and the OpenCV binary (cv2 4.13)."""
+import os
+
+import cv2
+import numpy as np
+import pytest
+
+from oracle import cv2_path as cvp
+from oracle import image_ops as ops
+from tests.synth import gradient_image
+
+GOLD_MEAN, GOLD_STD = [0.485, 0.456, 0.406], [0.229, 0.224, 0.225]
+
+
+def _fixture(golden_dir):
+    return cv2.imdecode(np.fromfile(os.path.join(golden_dir, "img_2112_70.jpg"), np.uint8), cv2.IMREAD_COLOR)
+
+
+def test_reference_golden_train(golden_dir):
+    """aeon test/test_provider.cpp:96-179."""
+    img = _fixture(golden_dir)
+    p = ops.ImageParams(cropbox=(50, 50, 171, 201), output_size=(224, 224), flip=True)
+    got = ops.load_image(ops.transform_single_image(img, p), True, True, "float", GOLD_MEAN, GOLD_STD)
+    gold = np.fromfile(os.path.join(golden_dir, "augment_output_linear_train.bin"), np.float32).reshape(3, 224, 224)
+    assert np.abs(got - gold).max() <= 1e-5   # the reference's own bound is 1e-3
+
+
+def test_reference_golden_eval(golden_dir):
+    """aeon test/test_provider.cpp:181-261: resize_short 256 (-> 341x256), centre crop (58,16,224x224)."""
+    img = _fixture(golden_dir)
+    p = ops.ImageParams(cropbox=(58, 16, 224, 224), output_size=(224, 224), resize_short_size=256)
+    got = ops.load_image(ops.transform_single_image(img, p), True, True, "float", GOLD_MEAN, GOLD_STD)
+    gold = np.fromfile(os.path.join(golden_dir, "augment_output_linear_eval.bin"), np.float32).reshape(3, 224, 224)
+    assert np.abs(got - gold).max() <= 1e-5
+
+
+def test_reference_contrast_and_brightness_known_answers():
+    """aeon test/test_image.cpp:1367-1480."""
+    def three(b, g, r):
+        img = np.zeros((1, 3, 3), np.uint8)
+        img[0, 0], img[0, 1], img[0, 2] = b, g, r
+        return img
+    img = three((0, 0, 0), (127, 127, 127), (255, 255, 255))
+    assert ops.cbsjitter(img, 0.5, 1.0, 1.0, 0)[0, :, 0].tolist() == [64, 127, 191]
+    assert ops.cbsjitter(img, 0.1, 1.0, 1.0, 0)[0, :, 0].tolist() == [115, 127, 140]
+    img = three((0, 0, 0), (127, 127, 127), (255, 255, 255))
+    assert ops.cbsjitter(img, 1.0, 0.5, 1.0, 0)[0, :, 0].tolist() == [0, 64, 128]
+    assert ops.cbsjitter(img, 1.0, 0.1, 1.0, 0)[0, :, 0].tolist() == [0, 13, 26]
+    assert ops.cbsjitter(img, 1.0, 1.5, 1.0, 0)[0, :, 0].tolist() == [0, 190, 255]
+
+
+def test_resize_linear_matches_opencv_on_many_shapes():
+    rng = np.random.default_rng(1)
+    for _ in range(40):
+        h, w = (int(v) for v in rng.integers(1, 300, 2))
+        ow, oh = (int(v) for v in rng.integers(1, 300, 2))
+        src = rng.integers(0, 256, (h, w, 3), dtype=np.uint8)
+        assert np.array_equal(ops.resize_linear_u8(src, ow, oh), cv2.resize(src, (ow, oh), interpolation=cv2.INTER_LINEAR))
+    src = rng.integers(0, 256, (128, 96, 3), dtype=np.uint8)
+    assert np.array_equal(ops.resize_linear_u8(src, 48, 64), cv2.resize(src, (48, 64), interpolation=cv2.INTER_LINEAR))
+    assert np.array_equal(ops.resize_nearest_u8(src, 37, 51), cv2.resize(src, (37, 51), interpolation=cv2.INTER_NEAREST))
+
+
+def test_colour_matrix_transform_matches_opencv():
+    rng = np.random.default_rng(2)
+    img = rng.integers(0, 256, (64, 257, 3), dtype=np.uint8)
+    for _ in range(10):
+        m = ops.color_matrix(rng.uniform(0.3, 2.0), rng.uniform(0.0, 2.0))
+        assert np.array_equal(ops.transform_u8(img, m), cv2.transform(img, m))
+
+
+def _all_triples():
+    v = np.arange(256, dtype=np.uint8)
+    a, b, c = np.meshgrid(v, v, v, indexing="ij")
+    return np.stack([a, b, c], -1)
+
+
+def test_bgr2hsv_matches_opencv_exhaustively():
+    img = _all_triples().reshape(4096, 4096, 3)
+    assert np.array_equal(ops.bgr2hsv_u8(img), cv2.cvtColor(img, cv2.COLOR_BGR2HSV))
+
+
+@pytest.mark.parametrize("width", [4096, 1])
+def test_hsv2bgr_matches_opencv_exhaustively(width):
+    """width 4096 exercises OpenCV's truncating vector body, width 1 its rounding scalar tail."""
+    hsv = _all_triples().reshape(-1, width, 3)
+    assert np.array_equal(ops.hsv2bgr_u8(hsv), cv2.cvtColor(hsv, cv2.COLOR_HSV2BGR))
+
+
+def test_hsv_body_and_tail_boundary():
+    rng = np.random.default_rng(3)
+    for w in (31, 32, 33, 57, 64, 100, 224, 300):
+        hsv = rng.integers(0, 256, (5, w, 3), dtype=np.uint8)
+        assert np.array_equal(ops.hsv2bgr_u8(hsv), cv2.cvtColor(hsv, cv2.COLOR_HSV2BGR)), w
+
+
+def test_hue_wrap_examples():
+    """C remainder stored through a uint8_t: (5,-18)->243, (0,-1)->255, (18,-18)->0, (179,+18)->17."""
+    for h, hue, want in [(5, -18, 243), (0, -1, 255), (18, -18, 0), (179, 18, 17)]:
+        t = np.fmod(np.int32(h + hue), 180).astype(np.int32) & 0xFF
+        assert int(t) == want
+
+
+def test_full_pipeline_matches_opencv_call_sequence():
+    rng = np.random.default_rng(4)
+    for _ in range(25):
+        h, w = (int(v) for v in rng.integers(40, 400, 2))
+        src = rng.integers(0, 256, (h, w, 3), dtype=np.uint8)
+        cw, ch = int(rng.integers(8, w + 1)), int(rng.integers(8, h + 1))
+        p = ops.ImageParams(cropbox=(int(rng.integers(0, w - cw + 1)), int(rng.integers(0, h - ch + 1)), cw, ch),
+                            output_size=(int(rng.integers(16, 300)), int(rng.integers(16, 300))), flip=bool(rng.integers(2)),
+                            contrast=rng.uniform(0.6, 1.4), brightness=rng.uniform(0.6, 1.4), saturation=rng.uniform(0.6, 1.4),
+                            hue=int(rng.integers(-18, 19)), lighting=list(rng.normal(0, 0.1, 3).astype(np.float32)),
+                            color_noise_std=0.1)
+        a, b = ops.transform_single_image(src, p), cvp.transform_single_image(src, p)
+        assert np.array_equal(a, b)
+        fa = ops.load_image(a, True, True, "float", [0.4, 0.5, 0.6], [0.2, 0.3, 0.0])
+        fb = cvp.load_image(b, True, True, "float", [0.4, 0.5, 0.6], [0.2, 0.3, 0.0])
+        assert np.abs(fa - fb).max() <= 1e-6
+
+
+def test_expand_padding_and_video_layout():
+    rng = np.random.default_rng(5)
+    src = gradient_image(rng, 20, 30)
+    p = ops.ImageParams(expand_ratio=2.0, expand_offset=(7, 3), expand_size=(60, 40), cropbox=(0, 0, 60, 40), output_size=(60, 40))
+    out = ops.transform_single_image(src, p)
+    assert np.array_equal(out[3:23, 7:37], src) and out[:3].sum() == 0 and out[:, :7].sum() == 0
+    frames = [np.full((4, 5, 3), i, np.uint8) for i in range(3)]
+    v = ops.load_video(frames, 5)            # aeon test/test_video.cpp:119-180 layout: C x T x H x W
+    assert v.shape == (3, 5, 4, 5) and v[:, 2].min() == 2 and not v[:, 3:].any()
