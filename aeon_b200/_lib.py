@@ -87,6 +87,9 @@ PROTOTYPES = {
     "aeonb_jpeg_entropy_decode": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "aeonb_draw_params": (C.c_int, [C.c_char_p, C.c_uint32, C.c_int, C.c_int, C.POINTER(C.c_int32),
                                     C.POINTER(C.c_int32), C.c_int, C.c_int, C.POINTER(C.c_double)]),
+    "aeonb_draw_ssd_params": (C.c_int, [C.c_char_p, C.c_uint32, C.c_int, C.c_int, C.POINTER(C.c_int32),
+                                        C.POINTER(C.c_int32), C.c_int, C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_float),
+                                        C.POINTER(C.c_double)]),
     "aeonb_image_desc_set_photometric": (C.c_int, [C.POINTER(ImageDesc), C.c_float, C.c_float, C.c_float, C.c_int,
                                                    C.POINTER(C.c_float), C.c_float]),
     "aeonb_provider_create": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p)]),
@@ -98,6 +101,9 @@ PROTOTYPES = {
     "aeonb_provider_output_bytes": (C.c_int64, [C.c_void_p, C.c_int]),
     "aeonb_provider_run": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_size_t), C.c_int,
                                      C.POINTER(C.c_void_p), C.c_int]),
+    "aeonb_provider_run_async": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_size_t), C.c_int,
+                                           C.POINTER(C.c_void_p), C.c_int, C.POINTER(C.c_int64)]),
+    "aeonb_provider_wait": (C.c_int, [C.c_void_p, C.c_int64]),
     "aeonb_provider_stats": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int32)]),
     "aeonb_loader_create": (C.c_int, [C.c_char_p, C.c_int, C.POINTER(C.c_void_p)]),
     "aeonb_loader_destroy": (None, [C.c_void_p]),

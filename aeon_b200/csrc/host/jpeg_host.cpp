@@ -136,8 +136,28 @@ namespace aeonb
 
             bit_reader(const uint8_t* b, const uint8_t* e) : p(b), end(e) {}
 
+            // Tops the accumulator up to more than 32 valid bits (a code plus its value bits need at most 31).
+            // Fast path: four bytes at once when none of
+            // them is 0xFF (no stuffing, no marker) -- true for almost every refill of natural images.
             inline void refill()
             {
+                if (n > 32)
+                    return;
+                if (end - p >= 4)
+                {
+                    uint32_t w;
+                    std::memcpy(&w, p, 4);
+                    // any byte equal to 0xFF?  (classic zero-byte test on the complement)
+                    const uint32_t inv = ~w;
+                    if (!((inv - 0x01010101u) & ~inv & 0x80808080u))
+                    {
+                        const uint64_t be = __builtin_bswap32(w);
+                        acc |= be << (32 - n);
+                        n += 32;
+                        p += 4;
+                        return;
+                    }
+                }
                 while (n <= 56)
                 {
                     uint64_t b = 0;
@@ -375,7 +395,6 @@ namespace aeonb
         {
             dct[c].build(f.dc[f.dc_table[c]], false);
             act[c].build(f.ac[f.ac_table[c]], true);
-            std::memset(coef[c], 0, sizeof(int16_t) * in.coef_count[c]);
         }
         const int mcux = in.blocks_w[0] / in.hs[0];
         const int mcuy = in.blocks_h[0] / in.vs[0];
@@ -404,6 +423,7 @@ namespace aeonb
                         for (int bx = 0; bx < in.hs[c]; ++bx)
                         {
                             int16_t* blk = coef[c] + (static_cast<size_t>(my * in.vs[c] + by) * in.blocks_w[c] + (mx * in.hs[c] + bx)) * 64;
+                            std::memset(blk, 0, 64 * sizeof(int16_t));
                             br.refill();
                             const int t = br.decode(dt);
                             if (t > 15)

@@ -75,7 +75,7 @@ struct aeonb_provider
     int                                  decode_size = 0;
     uint32_t                             seed        = 0;
     bool                                 batch_major = true;
-    int                                  pixel_stride = 4;
+    int                                  pixel_stride = 3;
     std::vector<aeonb::stage>            stages;
     std::vector<aeonb::output_info>      outputs;
     aeonb::param_factory                 factory;       // augmentation[0]
@@ -92,10 +92,22 @@ struct aeonb_provider
     std::vector<std::vector<char>>       out_host;     // host-produced outputs
     aeonb::pinned_buffer                 small_pinned;
 
+    static constexpr int k_events = 4;
+    cudaEvent_t m_done[k_events]    = {nullptr, nullptr, nullptr, nullptr}; // batch t complete: m_done[t % k_events]
+    cudaEvent_t m_uploaded          = nullptr; // every H2D copy of the last call has left host memory
+    bool        m_uploaded_valid    = false;
+    int64_t     m_ticket            = 0;       // number of batches submitted so far
+
     int64_t h2d_bytes = 0, d2h_bytes = 0;
     int32_t launches  = 0;
 
     aeonb_provider(aeonb_ctx* c, const aeonb::json& cfg);
-    void run(const void* const* elems, const size_t* sizes, int n, void* const* outs, bool on_device);
+    // Processes one batch.  With wait == false the call returns once the GPU work (kernels and output
+    // copies) is enqueued; wait_ticket(ticket()) then blocks until that batch is complete.  The host
+    // stages of the next call overlap the GPU work of the previous one.
+    void    run(const void* const* elems, const size_t* sizes, int n, void* const* outs, bool on_device, bool wait = true);
+    int64_t ticket() const { return m_ticket; }
+    void    wait_ticket(int64_t t);
+    ~aeonb_provider();
     int  input_count() const { return (int)stages.size(); }
 };

@@ -72,6 +72,29 @@ int aeonb_provider_run(aeonb_provider* p, const void* const* elems, const size_t
     });
 }
 
+int aeonb_provider_run_async(aeonb_provider* p, const void* const* elems, const size_t* sizes, int n, void* const* outputs,
+                             int outputs_on_device, int64_t* ticket)
+{
+    return guarded([&]() {
+        if (!p)
+            throw std::invalid_argument("aeonb_provider_run_async: provider is NULL");
+        p->run(elems, sizes, n, outputs, outputs_on_device != 0, false);
+        if (ticket)
+            *ticket = p->ticket();
+        return AEONB_OK;
+    });
+}
+
+int aeonb_provider_wait(aeonb_provider* p, int64_t ticket)
+{
+    return guarded([&]() {
+        if (!p)
+            throw std::invalid_argument("aeonb_provider_wait: provider is NULL");
+        p->wait_ticket(ticket);
+        return AEONB_OK;
+    });
+}
+
 int aeonb_provider_stats(const aeonb_provider* p, int64_t* h2d_bytes, int64_t* d2h_bytes, int32_t* launches)
 {
     if (!p)

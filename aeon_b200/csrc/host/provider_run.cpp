@@ -125,7 +125,26 @@ namespace aeonb
     }
 }
 
-void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, void* const* outs, bool on_device)
+aeonb_provider::~aeonb_provider()
+{
+    for (cudaEvent_t e : m_done)
+        if (e)
+            cudaEventDestroy(e);
+    if (m_uploaded)
+        cudaEventDestroy(m_uploaded);
+}
+
+void aeonb_provider::wait_ticket(int64_t t)
+{
+    if (t <= 0 || t > m_ticket)
+        throw std::invalid_argument("aeonb_provider_wait: no such batch");
+    if (m_ticket - t >= k_events)
+        return; // its event slot was recycled, which only happens after the batch completed
+    AEONB_CUDA(cudaSetDevice(ctx->device));
+    AEONB_CUDA(cudaEventSynchronize(m_done[t % k_events]));
+}
+
+void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, void* const* outs, bool on_device, bool wait)
 {
     if (!elems || !sizes || !outs)
         throw std::invalid_argument("aeonb_provider_run: NULL argument");
@@ -134,6 +153,15 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     AEONB_CUDA(cudaSetDevice(ctx->device));
     cudaStream_t  st  = ctx->stream;
     const int     nin = (int)stages.size();
+    if (!m_uploaded)
+    {
+        AEONB_CUDA(cudaEventCreateWithFlags(&m_uploaded, cudaEventDisableTiming));
+        for (cudaEvent_t& e : m_done)
+            AEONB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
+    // The pinned staging buffers are reused: the previous call's uploads must have left host memory.
+    if (m_uploaded_valid)
+        AEONB_CUDA(cudaEventSynchronize(m_uploaded));
     const int64_t launches_before = ctx->launches;
     h2d_bytes = d2h_bytes = 0;
 
@@ -569,8 +597,19 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
             }
             else
                 std::memcpy(outs[o], src, bytes);
-            continue;
         }
+    }
+    // From here on nothing reads pinned host staging any more: the next call may start refilling it
+    // while the kernels and the output copies below are still running.
+    AEONB_CUDA(cudaEventRecord(m_uploaded, st));
+    m_uploaded_valid = true;
+    for (size_t o = 0; o < outputs.size(); ++o)
+    {
+        if (outputs[o].host_produced)
+            continue;
+        const size_t  rec   = (size_t)outputs[o].shape.byte_size();
+        const int     esz   = (int)outputs[o].shape.otype.size;
+        const int64_t elems_per_rec = outputs[o].shape.element_count();
         if (!batch_major)
         {
             void* target = on_device ? outs[o] : out_dev_t[o].p;
@@ -588,6 +627,12 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
             d2h_bytes += (int64_t)(rec * n);
         }
     }
-    AEONB_CUDA(cudaStreamSynchronize(st));
+    ++m_ticket;
+    // Recycling an event slot: the batch that used it (k_events submissions ago) is long complete on an
+    // in-order stream once the newer batches between were waited for; synchronise to make that certain.
+    AEONB_CUDA(cudaEventSynchronize(m_done[m_ticket % k_events]));
+    AEONB_CUDA(cudaEventRecord(m_done[m_ticket % k_events], st));
+    if (wait)
+        AEONB_CUDA(cudaStreamSynchronize(st));
     launches = (int32_t)(ctx->launches - launches_before);
 }

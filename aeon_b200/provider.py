@@ -75,6 +75,21 @@ class Provider:
         L.check(self.lib.aeonb_provider_run(self.handle, ptrs, sizes, len(records), outs, 0))
         return out
 
+    def submit_host(self, records, out):
+        """Pipelined run_host: enqueue the batch into the caller's (pinned) arrays `out` and return a ticket
+        for wait().  Records and `out` must stay alive and untouched until the ticket has been waited for."""
+        ptrs, sizes, keep = self._pack(records)
+        outs = (C.c_void_p * len(self.outputs))(*[out[name].ctypes.data for name, _, _, _ in self.outputs])
+        ticket = C.c_int64()
+        L.check(self.lib.aeonb_provider_run_async(self.handle, ptrs, sizes, len(records), outs, 0, C.byref(ticket)))
+        self._inflight = getattr(self, "_inflight", {})
+        self._inflight[ticket.value] = (keep, ptrs, sizes, outs)
+        return ticket.value
+
+    def wait(self, ticket):
+        L.check(self.lib.aeonb_provider_wait(self.handle, ticket))
+        getattr(self, "_inflight", {}).pop(ticket, None)
+
     def run_device(self, records, out=None):
         """Same, leaving the batch in device memory: returns {name: torch tensor on the context's GPU}."""
         import torch

@@ -222,6 +222,13 @@ int aeonb_jpeg_entropy_decode(const void* data, size_t size, int16_t* coef[3], u
 int aeonb_draw_params(const char* augmentation_json, uint32_t seed, int decode_size, int n, const int32_t* in_w,
                       const int32_t* in_h, int out_w, int out_h, double* out);
 
+/* Same for the SSD path (param_factory::make_ssd_params, src/augment_image.cpp:232-310): record i has
+ * box_counts[i] ground-truth boxes, given as consecutive (xmin, ymin, xmax, ymax) float quadruples in
+ * `boxes`.  The output layout is that of aeonb_draw_params. */
+int aeonb_draw_ssd_params(const char* augmentation_json, uint32_t seed, int decode_size, int n, const int32_t* in_w,
+                          const int32_t* in_h, int out_w, int out_h, const int32_t* box_counts, const float* boxes,
+                          double* out);
+
 /* Fills the photometric fields of `desc` (colour matrix, hue, HSV vector columns, contrast,
  * lighting scale/offsets) from aeon's parameter values, doing on the host what
  * photometric::cbsjitter / lighting do before they touch pixels (src/image.cpp:336-346,362-371).
@@ -254,6 +261,16 @@ int64_t aeonb_provider_output_bytes(const aeonb_provider* p, int i); /* bytes pe
  * The call returns after the batch is complete. */
 int aeonb_provider_run(aeonb_provider* p, const void* const* elems, const size_t* sizes, int n, void* const* outputs,
                        int outputs_on_device);
+
+/* Pipelined form: returns as soon as the GPU work of the batch (kernels and output copies) is enqueued
+ * and stores a ticket; aeonb_provider_wait(p, ticket) blocks until that batch is complete.  Calling
+ * run_async for batch k+1 before waiting for batch k overlaps the host entropy decoding of k+1 with the
+ * kernels and copies of k (aeon overlaps its stages with double-buffered async_manager threads,
+ * src/async_manager.hpp:91-117).  Each batch in flight needs its own output buffers; at most 3 batches
+ * may be waited for out of order. */
+int aeonb_provider_run_async(aeonb_provider* p, const void* const* elems, const size_t* sizes, int n, void* const* outputs,
+                             int outputs_on_device, int64_t* ticket);
+int aeonb_provider_wait(aeonb_provider* p, int64_t ticket);
 
 /* Statistics of the last aeonb_provider_run: host->device and device->host bytes, kernel launches. */
 int aeonb_provider_stats(const aeonb_provider* p, int64_t* h2d_bytes, int64_t* d2h_bytes, int32_t* launches);

@@ -6,6 +6,7 @@ import numpy as np
 
 from oracle import image_ops as ops
 from oracle import params as oparams
+from oracle import ssd as ossd
 
 
 class PipelineOracle:
@@ -13,7 +14,7 @@ class PipelineOracle:
         self.cfg = config
         aug = (config.get("augmentation") or [{}])[0]
         self.aug = aug
-        self.factory = oparams.ParamFactory(aug)
+        self.factory = ossd.SsdFactory(aug)
         self.video_factory = oparams.ParamFactory(aug.get("frame", {}))
         self.decode_size = config.get("decode_size", config["batch_size"])
         self.engines = oparams.slot_engines(config["random_seed"], self.decode_size)
@@ -57,6 +58,14 @@ class PipelineOracle:
                 elif etl["type"] == "label":
                     v = int(np.frombuffer(blob, np.int32)[0]) if etl.get("binary") else int(blob.decode())
                     outs.setdefault(name + "label", []).append(np.array([v], ops._DTYPES[etl.get("output_type", "uint32_t")]))
+                elif etl["type"] == "localization_ssd":
+                    w, h, boxes = ossd.parse_annotation(blob, etl["class_names"])
+                    if p is None:
+                        p = self.factory.make_ssd_params(g, w, h, etl["width"], etl["height"], boxes)
+                    gt = ossd.transform_boxes(boxes, p)
+                    bufs = ossd.load_buffers(gt, etl["width"], etl["height"], etl.get("max_gt_boxes", 64))
+                    for key, arr in zip(("image_shape", "gt_boxes", "gt_box_count", "gt_class_count", "difficult_flag"), bufs):
+                        outs.setdefault(name + key, []).append(arr)
                 elif etl["type"] == "video":
                     frames = video_frames(blob)
                     fc = etl["frame"]

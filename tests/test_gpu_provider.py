@@ -142,6 +142,45 @@ def test_reference_avi_fixture_with_dropped_frame(ctx, golden_dir, tmp_path):
     assert len(dup) >= 1
 
 
+SSD_SAMPLERS = [{"max_sample": 1, "max_trials": 1}] + [
+    {"max_sample": 1, "max_trials": 50, "sampler": {"scale": [0.3, 1.0], "aspect_ratio": [0.5, 2.0]}, "sample_constraint": c}
+    for c in ({"min_jaccard_overlap": 0.1}, {"min_jaccard_overlap": 0.3}, {"min_jaccard_overlap": 0.5},
+              {"min_jaccard_overlap": 0.7}, {"min_jaccard_overlap": 0.9}, {"max_jaccard_overlap": 1.0})]
+
+
+def ssd_records(seed, n, w=500, h=375):
+    import json
+    rng = np.random.default_rng(seed)
+    names = ["class%02d" % i for i in range(20)]
+    recs = []
+    for _ in range(n):
+        objs = []
+        for _ in range(int(rng.integers(1, 9))):
+            x0, y0 = int(rng.integers(0, w - 9)), int(rng.integers(0, h - 9))
+            objs.append({"name": names[int(rng.integers(0, 20))], "difficult": bool(rng.integers(2)),
+                         "bndbox": {"xmin": x0, "ymin": y0, "xmax": int(rng.integers(x0 + 8, w)), "ymax": int(rng.integers(y0 + 8, h))}})
+        ann = {"object": objs, "size": {"width": w, "height": h, "depth": 3}}
+        recs.append((json.dumps(ann).encode(), jpeg_bytes(gradient_image(rng, h, w), 90)))
+    return names, recs
+
+
+def test_config3_ssd_boxes_and_warped_image(ctx):
+    names, recs = ssd_records(47, 16)
+    cfg = {"batch_size": 16, "random_seed": 21,
+           "etl": [{"type": "localization_ssd", "height": 300, "width": 300, "max_gt_boxes": 64, "class_names": names},
+                   {"type": "image", "height": 300, "width": 300, "output_type": "float"}],
+           "augmentation": [{"type": "image", "crop_enable": False, "flip_enable": True, "expand_ratio": [1.0, 4.0],
+                             "expand_probability": 0.5, "emit_constraint_type": "center", "batch_samplers": SSD_SAMPLERS}]}
+    got = make_provider(ctx, cfg).run_host(recs)
+    want = PipelineOracle(cfg).batch(recs)
+    assert sorted(got) == ["difficult_flag", "gt_box_count", "gt_boxes", "gt_class_count", "image", "image_shape"]
+    for key in ("image_shape", "gt_box_count", "gt_class_count", "difficult_flag"):
+        assert np.array_equal(got[key], want[key]), key
+    assert np.array_equal(got["gt_boxes"], want["gt_boxes"])      # float32 box arithmetic restated op for op
+    assert np.array_equal(got["image"], want["image"])            # unnormalised float output of uint8 pixels
+    assert got["gt_box_count"].max() >= 1 and (want["image"][:, :, 0, 0] == 0).any()  # some crops start on the zero canvas
+
+
 def test_errors_surface_with_reference_messages(ctx):
     from aeon_b200._lib import AeonError
     cfg = {"batch_size": 2, "random_seed": 1, "etl": [{"type": "image", "height": 32, "width": 32}], "augmentation": [AUG_C1]}

@@ -73,3 +73,45 @@ def test_invalid_augmentation_is_rejected():
         draw({"scale": [0.5, 0.9]}, 1, 1, [(10, 10)], 4, 4)
     with pytest.raises(AeonError, match="batch_samplers"):
         draw({"type": "image", "crop_enable": True, "batch_samplers": [{}]}, 1, 1, [(10, 10)], 4, 4)
+
+
+def test_ssd_draws_and_patch_sampling_match_restatement():
+    """make_ssd_params (expand, patch samplers with IoU constraints) against oracle/ssd.py, value for value."""
+    from aeon_b200 import _lib as L
+    from oracle import ssd
+    lib = L.load()
+    samplers = [{"max_sample": 1, "max_trials": 1}] + [
+        {"max_sample": 1, "max_trials": 50, "sampler": {"scale": [0.3, 1.0], "aspect_ratio": [0.5, 2.0]}, "sample_constraint": c}
+        for c in ({"min_jaccard_overlap": 0.1}, {"min_jaccard_overlap": 0.5}, {"min_jaccard_overlap": 0.9},
+                  {"max_jaccard_overlap": 1.0}, {"min_sample_coverage": 0.3, "max_object_coverage": 0.9})]
+    aug = {"type": "image", "crop_enable": False, "flip_enable": True, "expand_ratio": [1.0, 4.0], "expand_probability": 0.5,
+           "emit_constraint_type": "center", "batch_samplers": samplers}
+    rng = np.random.default_rng(0)
+    n, W, H = 200, 500, 375
+    boxes, counts = [], []
+    for _ in range(n):
+        k = int(rng.integers(1, 9))
+        counts.append(k)
+        for _ in range(k):
+            x0, y0 = int(rng.integers(0, W - 9)), int(rng.integers(0, H - 9))
+            boxes.append((x0, y0, int(rng.integers(x0 + 8, W)), int(rng.integers(y0 + 8, H))))
+    flat = np.array(boxes, np.float32).ravel()
+    out = (C.c_double * (24 * n))()
+    w = (C.c_int32 * n)(*[W] * n)
+    h = (C.c_int32 * n)(*[H] * n)
+    cnt = (C.c_int32 * n)(*counts)
+    L.check(lib.aeonb_draw_ssd_params(json.dumps(aug).encode(), 1234, 32, n, w, h, 300, 300, cnt,
+                                      flat.ctypes.data_as(C.POINTER(C.c_float)), out))
+    got = np.array(out).reshape(n, 24)
+    f = ssd.SsdFactory(aug)
+    eng = op.slot_engines(1234, 32)
+    at = 0
+    for i in range(n):
+        bb = [ssd.Box(*boxes[at + j]) for j in range(counts[i])]
+        at += counts[i]
+        p = f.make_ssd_params(eng[i % 32], W, H, 300, 300, bb)
+        want = [*p.cropbox, *p.output_size, float(p.flip), p.angle, p.hue, float(p.contrast), float(p.brightness),
+                float(p.saturation), 0, 0, 0, 0, *p.padding_crop_offset, float(np.float32(p.expand_ratio)),
+                *p.expand_offset, *p.expand_size]
+        assert np.array_equal(np.array(want, np.float64), got[i, :23]), i
+    assert 60 < (got[:, 18] > 1).sum() < 140
