@@ -195,3 +195,56 @@ def test_errors_surface_with_reference_messages(ctx):
         make_provider(ctx, dict(cfg, etl=[{"type": "image", "height": 32, "width": 32, "heigth": 3}]))
     with pytest.raises(AeonError, match="unsupported etl type"):
         make_provider(ctx, dict(cfg, etl=[{"type": "hologram"}]))
+
+
+def test_config5_audio_log_mel_through_the_provider(ctx):
+    from oracle import specgram as ospec
+    from tests.test_gpu_specgram import assert_close, synth_clip
+    rng = np.random.default_rng(48)
+    clips = [synth_clip(rng, s) for s in (1.0, 2.5, 0.8, 1.7)]
+    cfg = {"batch_size": 4, "random_seed": 1,
+           "etl": [{"type": "audio", "frame_length": 320, "frame_stride": 160, "max_samples": 32000, "num_filters": 64,
+                    "sample_rate": 16000, "window_type": "hann", "feature_type": "mfsc"},
+                   {"type": "label", "binary": True}]}
+    recs = [(c.tobytes(), struct.pack("<i", i)) for i, c in enumerate(clips)]
+    got = make_provider(ctx, cfg).run_host(recs)
+    steps = (32000 - 320) // 160 + 1
+    assert got["audio"].shape == (4, steps, 64)
+    for i, c in enumerate(clips):
+        assert_close(got["audio"][i], ospec.log_mel(c[:32000], max_time_steps=steps))
+    # a RIFF/WAVE container around the same samples gives the same features
+    import io
+    import wave
+    buf = io.BytesIO()
+    with wave.open(buf, "wb") as w:
+        w.setnchannels(1)
+        w.setsampwidth(2)
+        w.setframerate(16000)
+        w.writeframes(clips[0].tobytes())
+    got2 = make_provider(ctx, cfg).run_host([(buf.getvalue(), recs[0][1])] + recs[1:])
+    assert np.array_equal(got2["audio"][0], got["audio"][0])
+
+
+def test_pipelined_calls_give_the_same_batches_as_blocking_calls(ctx):
+    import torch
+    cfg = {"batch_size": 16, "random_seed": 77,
+           "etl": [{"type": "image", "height": 96, "width": 96, "output_type": "float", "bgr_to_rgb": True},
+                   {"type": "label", "binary": True}],
+           "augmentation": [AUG_C2]}
+    recs = image_records(49, 64)
+    blocking = make_provider(ctx, cfg)
+    want = [{k: v.copy() for k, v in blocking.run_host(recs[16 * b:16 * b + 16]).items()} for b in range(4)]
+    prov = make_provider(ctx, cfg)
+    bufs = [{"image": torch.empty((16, 3, 96, 96), dtype=torch.float32).pin_memory().numpy(), "label": np.zeros((16, 1), np.int32)}
+            for _ in range(2)]
+    prev, got = None, []
+    for b in range(4):
+        t = prov.submit_host(recs[16 * b:16 * b + 16], bufs[b % 2])
+        if prev is not None:
+            prov.wait(prev)
+            got.append({k: v.copy() for k, v in bufs[(b - 1) % 2].items()})
+        prev = t
+    prov.wait(prev)
+    got.append({k: v.copy() for k, v in bufs[1].items()})
+    for b in range(4):
+        assert np.array_equal(got[b]["image"], want[b]["image"]) and np.array_equal(got[b]["label"], want[b]["label"])
