@@ -231,7 +231,7 @@ namespace aeonb
         }
 
         template <typename T, int PIX>
-        __global__ void __launch_bounds__(AUG_THREADS) aug_pack_kernel(const aug_launch L)
+        __global__ void __launch_bounds__(AUG_THREADS, 4) aug_pack_kernel(const aug_launch L)
         {
             extern __shared__ __align__(16) unsigned char smem[];
             __shared__ aeonb_image_desc d;
@@ -333,78 +333,136 @@ namespace aeonb
                 const int      nseg  = (out_w + 31) >> 5;
                 const int      units = rows * nseg;
                 const uint8_t* base  = d.src + (ptrdiff_t)(d.crop_y - d.canvas_y) * d.src_pitch + (ptrdiff_t)(d.crop_x - d.canvas_x) * PIX;
-                const short*   m     = d.color_matrix;
-                for (int u = warp; u < units; u += WARPS)
+                // Record constants live in shared memory; byte stores into the tile could alias them, so the
+                // ones the pixel loop needs are copied to registers once.
+                const int   src_pitch    = d.src_pitch;
+                const int   color_enable = d.color_enable;
+                const float cs0 = d.color_scale[0], cs1 = d.color_scale[1], cs2 = d.color_scale[2];
+                const int   m0 = d.color_matrix[0], m1 = d.color_matrix[1], m2 = d.color_matrix[2], m3 = d.color_matrix[3],
+                            m4 = d.color_matrix[4], m5 = d.color_matrix[5], m6 = d.color_matrix[6], m7 = d.color_matrix[7],
+                            m8 = d.color_matrix[8];
+                const int   hue = d.hue, hsv_cols = d.hsv_vector_cols;
+                const bool  flip = d.flip != 0;
+
+                struct taps
                 {
-                    const int r = u / nseg;
-                    const int x = (u - r * nseg) * 32 + lane;
-                    if (x >= out_w)
-                        continue;
-                    const row_tap t  = ytab[r];
-                    const int2    xo = xofs[x];
-                    const short2  a  = xw[x];
-                    bgr           p00, p01, p10, p11;
+                    bgr     p00, p01, p10, p11;
+                    short2  a;
+                    short   b0, b1;
+                    int     x, r;
+                    bool    valid;
+                };
+                // all global loads of one unit (32 pixels of a row), issued before any arithmetic on them
+                auto load_unit = [&](int r, int seg) {
+                    taps k;
+                    k.r     = r;
+                    k.x     = seg * 32 + lane;
+                    k.valid = r < rows && k.x < out_w;
+                    if (!k.valid)
+                        return k;
+                    const row_tap t  = ytab[k.r];
+                    const int2    xo = xofs[k.x];
+                    k.a  = xw[k.x];
+                    k.b0 = t.b0;
+                    k.b1 = t.b1;
                     if (inside)
                     {
-                        const uint8_t* r0 = base + (ptrdiff_t)t.y0 * d.src_pitch;
-                        const uint8_t* r1 = base + (ptrdiff_t)t.y1 * d.src_pitch;
-                        p00 = load_px<PIX>(r0 + xo.x);
+                        const uint8_t* r0 = base + (ptrdiff_t)t.y0 * src_pitch;
+                        const uint8_t* r1 = base + (ptrdiff_t)t.y1 * src_pitch;
+                        k.p00 = load_px<PIX>(r0 + xo.x);
                         if (linear)
                         {
-                            p01 = load_px<PIX>(r0 + xo.y);
-                            p10 = load_px<PIX>(r1 + xo.x);
-                            p11 = load_px<PIX>(r1 + xo.y);
+                            k.p01 = load_px<PIX>(r0 + xo.y);
+                            k.p10 = load_px<PIX>(r1 + xo.x);
+                            k.p11 = load_px<PIX>(r1 + xo.y);
                         }
                     }
                     else
                     {
-                        p00 = fetch<PIX>(d, xo.x, t.y0);
+                        k.p00 = fetch<PIX>(d, xo.x, t.y0);
                         if (linear)
                         {
-                            p01 = fetch<PIX>(d, xo.y, t.y0);
-                            p10 = fetch<PIX>(d, xo.x, t.y1);
-                            p11 = fetch<PIX>(d, xo.y, t.y1);
+                            k.p01 = fetch<PIX>(d, xo.y, t.y0);
+                            k.p10 = fetch<PIX>(d, xo.x, t.y1);
+                            k.p11 = fetch<PIX>(d, xo.y, t.y1);
                         }
                     }
-                    bgr px = p00;
+                    return k;
+                };
+                auto finish_unit = [&](const taps& k) {
+                    if (!k.valid)
+                        return;
+                    bgr px = k.p00;
                     if (linear)
                     {
                         // horizontal pass keeps 11 fractional bits; vertical pass as in OpenCV's 8-bit path
-                        const int hb0 = p00.b * a.x + p01.b * a.y, hb1 = p10.b * a.x + p11.b * a.y;
-                        const int hg0 = p00.g * a.x + p01.g * a.y, hg1 = p10.g * a.x + p11.g * a.y;
-                        const int hr0 = p00.r * a.x + p01.r * a.y, hr1 = p10.r * a.x + p11.r * a.y;
-                        px.b = clamp_u8((((t.b0 * (hb0 >> 4)) >> 16) + ((t.b1 * (hb1 >> 4)) >> 16) + 2) >> 2);
-                        px.g = clamp_u8((((t.b0 * (hg0 >> 4)) >> 16) + ((t.b1 * (hg1 >> 4)) >> 16) + 2) >> 2);
-                        px.r = clamp_u8((((t.b0 * (hr0 >> 4)) >> 16) + ((t.b1 * (hr1 >> 4)) >> 16) + 2) >> 2);
+                        const int      b0 = k.b0, b1 = k.b1;
+                        const unsigned aw = (unsigned)(unsigned short)k.a.x | ((unsigned)(unsigned short)k.a.y << 16);
+                        // two-way dot product: low 16 bits of aw times byte 0, high 16 bits times byte 1 (weights are 0..2048)
+                        const int hb0 = (int)__dp2a_lo(aw, (unsigned)(k.p00.b | (k.p01.b << 8)), 0u);
+                        const int hb1 = (int)__dp2a_lo(aw, (unsigned)(k.p10.b | (k.p11.b << 8)), 0u);
+                        const int hg0 = (int)__dp2a_lo(aw, (unsigned)(k.p00.g | (k.p01.g << 8)), 0u);
+                        const int hg1 = (int)__dp2a_lo(aw, (unsigned)(k.p10.g | (k.p11.g << 8)), 0u);
+                        const int hr0 = (int)__dp2a_lo(aw, (unsigned)(k.p00.r | (k.p01.r << 8)), 0u);
+                        const int hr1 = (int)__dp2a_lo(aw, (unsigned)(k.p10.r | (k.p11.r << 8)), 0u);
+                        px.b = clamp_u8((((b0 * (hb0 >> 4)) >> 16) + ((b1 * (hb1 >> 4)) >> 16) + 2) >> 2);
+                        px.g = clamp_u8((((b0 * (hg0 >> 4)) >> 16) + ((b1 * (hg1 >> 4)) >> 16) + 2) >> 2);
+                        px.r = clamp_u8((((b0 * (hr0 >> 4)) >> 16) + ((b1 * (hr1 >> 4)) >> 16) + 2) >> 2);
                     }
-                    if (d.color_enable == 2)
+                    if (color_enable == 2)
                     {
-                        px.b = clamp_u8(__float2int_rn((float)px.b * d.color_scale[0]));
-                        px.g = clamp_u8(__float2int_rn((float)px.g * d.color_scale[1]));
-                        px.r = clamp_u8(__float2int_rn((float)px.r * d.color_scale[2]));
+                        px.b = clamp_u8(__float2int_rn((float)px.b * cs0));
+                        px.g = clamp_u8(__float2int_rn((float)px.g * cs1));
+                        px.r = clamp_u8(__float2int_rn((float)px.r * cs2));
                     }
-                    else if (d.color_enable)
+                    else if (color_enable)
                     {
-                        const int b  = (px.b * m[0] + px.g * m[1] + px.r * m[2] + 512) >> 10;
-                        const int g  = (px.b * m[3] + px.g * m[4] + px.r * m[5] + 512) >> 10;
-                        const int rr = (px.b * m[6] + px.g * m[7] + px.r * m[8] + 512) >> 10;
+                        const int b  = (px.b * m0 + px.g * m1 + px.r * m2 + 512) >> 10;
+                        const int g  = (px.b * m3 + px.g * m4 + px.r * m5 + 512) >> 10;
+                        const int rr = (px.b * m6 + px.g * m7 + px.r * m8 + 512) >> 10;
                         px.b = clamp_u8(b);
                         px.g = clamp_u8(g);
                         px.r = clamp_u8(rr);
                     }
                     if (use_hue)
-                        px = hue_rotate(px, d.hue, x < d.hsv_vector_cols, hsv_sdiv, hsv_hdiv);
+                        px = hue_rotate(px, hue, k.x < hsv_cols, hsv_sdiv, hsv_hdiv);
 
-                    const int xo_t = d.flip ? out_w - 1 - x : x;
+                    const int xo_t = flip ? out_w - 1 - k.x : k.x;
                     const int c0   = swap_rb ? px.r : px.b;
                     const int c2   = swap_rb ? px.b : px.r;
-                    unsigned char* o = tile + r * pitch + xo_t;
+                    unsigned char* o = tile + k.r * pitch + xo_t;
                     o[0]             = (unsigned char)c0;
                     o[plane]         = (unsigned char)px.g;
                     o[2 * plane]     = (unsigned char)c2;
                     sum0 += c0;
                     sum1 += px.g;
                     sum2 += c2;
+                };
+                // two units in flight per warp: the loads of the second overlap the arithmetic of the first.
+                // Unit u = (row, 32-pixel segment); the warp steps through its units without dividing.
+                // (nseg >= 1 here; the wrap loop is bounded by the step because each wrap removes at least 1.)
+                auto advance = [&](int& r, int& seg, int by) {
+                    seg += by;
+                    for (int it = 0; it < 2 * WARPS && seg >= nseg; ++it)
+                    {
+                        seg -= nseg;
+                        ++r;
+                    }
+                };
+                int ra = 0, sa = 0;
+                advance(ra, sa, warp);
+                int rb = ra, sb = sa;
+                advance(rb, sb, WARPS);
+                (void)units;
+                // an empty image (zero-filled slot) has no units at all
+                for (int guard = 0; nseg > 0 && ra < rows && guard < units; ++guard)
+                {
+                    const taps ka = load_unit(ra, sa);
+                    const taps kb = load_unit(rb, sb);
+                    finish_unit(ka);
+                    finish_unit(kb);
+                    advance(ra, sa, 2 * WARPS);
+                    advance(rb, sb, 2 * WARPS);
                 }
             }
 
@@ -454,7 +512,7 @@ namespace aeonb
                 const T       zero   = convert_out<T>(0);
                 for (int line = warp; line < 3 * rows; line += WARPS)
                 {
-                    const int  c      = line / rows;
+                    const int  c      = (line >= rows) + (line >= 2 * rows);
                     const int  r      = line - c * rows;
                     const int  y      = row0 + r;
                     const bool row_in = y < out_h;

@@ -215,7 +215,7 @@ namespace aeonb
                 {
                     const int item = i >> 3, c = i & 7;
                     int       j    = 0;
-                    while (item >= job_first[j + 1])
+                    while (j + 1 < njobs && item >= job_first[j + 1])
                         ++j;
                     const int      b   = item - job_first[j];
                     const int16_t* src = d.coef[jobs[j].comp] + ((size_t)jobs[j].block_row * d.blocks_w[jobs[j].comp] + b) * 64 + c * 8;
@@ -232,7 +232,7 @@ namespace aeonb
                 for (int item = tid; item < total; item += JPG_THREADS)
                 {
                     int j = 0;
-                    while (item >= job_first[j + 1])
+                    while (j + 1 < njobs && item >= job_first[j + 1])
                         ++j;
                     const block_row_job job   = jobs[j];
                     const int           b     = item - job_first[j];
