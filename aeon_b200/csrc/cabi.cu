@@ -310,7 +310,7 @@ int aeonb_jpeg_backend_batch(aeonb_ctx* ctx, const aeonb_jpeg_desc* descs, int n
                 throw std::invalid_argument(msg);
             smem = std::max(smem, jpeg_backend_smem(r));
             const int mcu_rows = r.blocks_h[0] / r.vs[0];
-            for (int m = 0; m < mcu_rows; ++m)
+            for (int m = 0; m < mcu_rows; m += jpeg_backend_strip())
                 if (m * r.vs[0] * 8 < r.height)
                     work.push_back(make_int2(i, m));
         }

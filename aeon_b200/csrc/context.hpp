@@ -93,4 +93,5 @@ namespace aeonb
     cudaError_t launch_jpeg_backend(const aeonb_jpeg_desc* descs_dev, const int2* work_dev, int n_work, size_t smem,
                                     cudaStream_t stream);
     size_t      jpeg_backend_smem(const aeonb_jpeg_desc& d);
+    int         jpeg_backend_strip(); // MCU rows one CTA of the back-end kernel handles
 }

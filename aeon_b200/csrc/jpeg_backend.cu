@@ -8,13 +8,13 @@
 // bits between the column and row passes, triangle-filter ("fancy") chroma upsampling and
 // 16-bit fixed-point colour conversion.
 //
-// Work decomposition: one CTA per (record, MCU row).  The coefficient blocks the CTA needs are
+// Work decomposition: one CTA per (record, strip of two MCU rows).  The coefficient blocks the CTA needs are
 // staged in shared memory with coalesced 16-byte asynchronous copies (XOR-swizzled so that the
 // next step is free of bank conflicts); then ONE THREAD transforms ONE 8x8 BLOCK entirely in
 // registers: eight 128-bit shared loads (the host stores blocks column-major, so a load is a
 // block column), column pass, row pass (the transpose is register renaming), saturating pack,
 // 8-byte stores into shared component planes.  The CTA also transforms the chroma blocks of the
-// MCU rows above and below (only the one sample row the triangle filter needs on either side).  A second phase upsamples, converts and writes 4 pixels per thread
+// MCU rows above and below its strip (only the one sample row the triangle filter needs on either side).  A second phase upsamples, converts and writes 4 pixels per thread
 // (one 128-bit store per thread for 4-byte pixels, three 32-bit stores for 3-byte pixels).
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -26,6 +26,7 @@ namespace aeonb
     namespace
     {
         constexpr int JPG_THREADS = 256;
+        constexpr int JPG_STRIP   = 2; // MCU rows per CTA: the chroma context rows are transformed once per strip
 
         struct jpeg_launch
         {
@@ -146,13 +147,13 @@ namespace aeonb
             extern __shared__ __align__(16) unsigned char smem[];
             __shared__ aeonb_jpeg_desc d;
             __shared__ __align__(16) uint16_t quant[3][64];
-            __shared__ block_row_job   jobs[8];
+            __shared__ block_row_job   jobs[JPG_STRIP * 4 + 4];
             __shared__ int             njobs;
-            __shared__ int             job_first[9]; // first work item of each job, and the total
+            __shared__ int             job_first[JPG_STRIP * 4 + 5]; // first work item of each job, and the total
 
             const int  tid  = threadIdx.x;
             const int2 wk   = L.work[blockIdx.x];
-            const int  mrow = wk.y;
+            const int  mrow = wk.y; // first MCU row of this CTA's strip
             {
                 const int* g = reinterpret_cast<const int*>(L.descs + wk.x);
                 int*       s = reinterpret_cast<int*>(&d);
@@ -169,8 +170,10 @@ namespace aeonb
             const int fv = ncomp == 3 ? vs0 : 1;
             const int yw = d.blocks_w[0] * 8;                 // luma plane pitch (bytes)
             const int cwp = ncomp == 3 ? d.blocks_w[1] * 8 : 0; // chroma plane pitch
-            const int yrows = vs0 * 8;
-            const int crows = 8 + (fv == 2 ? 2 : 0);          // chroma rows kept, incl. one halo row above/below for 2x vertical
+            const int mcu_rows = d.blocks_h[0] / vs0;
+            const int strip = min(JPG_STRIP, mcu_rows - mrow); // MCU rows handled here
+            const int yrows = JPG_STRIP * vs0 * 8;             // plane capacity (rows)
+            const int crows = JPG_STRIP * 8 + (fv == 2 ? 2 : 0); // chroma rows kept, incl. one halo row above/below for 2x vertical
             uint8_t*  yplane  = smem;
             uint8_t*  cbplane = yplane + yrows * yw;
             uint8_t*  crplane = cbplane + crows * cwp;
@@ -180,19 +183,20 @@ namespace aeonb
             {
                 // full block rows first, halo rows (one sample row wanted) last, so that warps do not mix them
                 int n = 0;
-                for (int v = 0; v < vs0; ++v)
+                for (int v = 0; v < strip * vs0; ++v)
                     jobs[n++] = block_row_job{0, mrow * vs0 + v, v * 8, -1};
                 if (ncomp == 3)
                 {
                     const int halo = fv == 2 ? 1 : 0;
                     for (int c = 1; c < 3; ++c)
-                        jobs[n++] = block_row_job{c, mrow, halo, -1};
+                        for (int m = 0; m < strip; ++m)
+                            jobs[n++] = block_row_job{c, mrow + m, halo + 8 * m, -1};
                     for (int c = 1; c < 3 && halo; ++c)
                     {
                         if (mrow > 0)
                             jobs[n++] = block_row_job{c, mrow - 1, halo - 8, 7};
-                        if (mrow + 1 < d.blocks_h[c])
-                            jobs[n++] = block_row_job{c, mrow + 1, halo + 8, 0};
+                        if (mrow + strip < d.blocks_h[c])
+                            jobs[n++] = block_row_job{c, mrow + strip, halo + 8 * strip, 0};
                     }
                 }
                 int total = 0;
@@ -280,8 +284,8 @@ namespace aeonb
             {
                 const int W = d.width, H = d.height;
                 const int pix   = d.dst_pixel_stride;
-                const int y0    = mrow * yrows;
-                const int rows  = min(yrows, H - y0);
+                const int y0    = mrow * vs0 * 8;
+                const int rows  = min(strip * vs0 * 8, H - y0);
                 const int quads = (W + 3) / 4;
                 const int chh   = ncomp == 3 ? (H * d.vs[1] + vs0 - 1) / vs0 : 0; // real chroma rows / cols
                 const int cw    = ncomp == 3 ? (W * d.hs[1] + hs0 - 1) / hs0 : 0;
@@ -503,14 +507,17 @@ namespace aeonb
         return cudaGetLastError();
     }
 
+    int jpeg_backend_strip() { return JPG_STRIP; }
+
     // Shared memory one CTA needs for a record.
     size_t jpeg_backend_smem(const aeonb_jpeg_desc& d)
     {
-        const int yrows = d.vs[0] * 8;
+        const int yrows = JPG_STRIP * d.vs[0] * 8;
         const int fv    = d.ncomp == 3 ? d.vs[0] : 1;
-        const int crows = 8 + (fv == 2 ? 2 : 0);
+        const int crows = JPG_STRIP * 8 + (fv == 2 ? 2 : 0);
         const size_t planes = (size_t)yrows * d.blocks_w[0] * 8 + (d.ncomp == 3 ? (size_t)2 * crows * d.blocks_w[1] * 8 : 0);
-        const size_t blocks = (size_t)d.vs[0] * d.blocks_w[0] + (d.ncomp == 3 ? (size_t)2 * (fv == 2 ? 3 : 1) * d.blocks_w[1] : 0);
+        const size_t blocks = (size_t)JPG_STRIP * d.vs[0] * d.blocks_w[0] +
+                              (d.ncomp == 3 ? (size_t)2 * (JPG_STRIP + (fv == 2 ? 2 : 0)) * d.blocks_w[1] : 0);
         return ((planes + 127) & ~(size_t)127) + blocks * 128;
     }
 }
