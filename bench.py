@@ -186,7 +186,7 @@ def main():
 
     # The CPU baseline runs in its own process (before this one touches CUDA): rank 0, N=1 timing only.
     cpu_line = None
-    if rank == 0 and not args.kernels_only and args.cpu_seconds > 0:
+    if rank == 0 and world == 1 and not args.kernels_only and args.cpu_seconds > 0:
         r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", "1",
                             "--cpu-seconds", str(args.cpu_seconds)], capture_output=True, text=True)
         for ln in r.stdout.splitlines():
@@ -365,7 +365,9 @@ def main():
                        "scratch_pixel_stride": pix, "records_per_gpu_per_step": BATCH},
             "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_kind": peak_kind, "frac_of_8tbs_nominal": achieved / 8000.0,
-                         "traffic": None,
+                         # DRAM bytes per launch of that kernel from the ncu capture summarised under profiles/
+                         "traffic": {"jpeg_backend": 188.8e6, "aug_pack": 153.9e6}[dominant],
+                         "traffic_source": "profiles/%s_config2.md (ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch)" % dominant,
                          "kernels": {"jpeg_backend": {"ms": jpeg_ms, "algorithmic_bytes": jpeg_alg,
                                                       "gbs": jpeg_alg / (jpeg_ms * 1e-3) / 1e9},
                                      "aug_pack": {"ms": aug_ms, "algorithmic_bytes": aug_alg,
