@@ -87,6 +87,7 @@ struct aeonb_provider
     aeonb::pinned_buffer                 staging;      // coefficients / samples, host side
     aeonb::device_buffer                 staging_dev;
     aeonb::device_buffer                 pixels_dev;   // decoded pictures
+    aeonb::device_buffer                 resized_dev;  // pictures after the resize_short pass
     std::vector<aeonb::device_buffer>    out_dev;      // per output, batch_size records
     std::vector<aeonb::device_buffer>    out_dev_t;    // transposed copies (batch_major == false)
     std::vector<std::vector<char>>       out_host;     // host-produced outputs

@@ -35,8 +35,6 @@ namespace aeonb
         {
             if (p.angle != 0)
                 throw error(AEONB_ERR_UNSUPPORTED, "rotation ('angle') is outside the accelerated path");
-            if (p.resize_short_size != 0)
-                throw error(AEONB_ERR_UNSUPPORTED, "'resize_short_size' is outside the accelerated path");
             string m = p.interpolation_method;
             std::transform(m.begin(), m.end(), m.begin(), ::toupper);
             aeonb_image_desc d{};
@@ -175,6 +173,8 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     vector<vector<aeonb_image_desc>> descs(nin);
     vector<vector<int>>              desc_job(nin);
     vector<vector<int64_t>>          desc_dst(nin);
+    vector<vector<aeonb_image_desc>> pre_descs(nin);  // resize_short pass: whole (expanded) picture -> short-side size
+    vector<vector<int>>              pre_job(nin);
     vector<vector<aeonb_specgram_desc>> sdescs(nin);
     vector<vector<size_t>>           sdesc_off(nin);
     size_t stage_bytes = 0, pixel_bytes = 0;
@@ -236,7 +236,32 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                     params      = factory.make_params(engine, in.width, in.height, sg.image.width, sg.image.height);
                     have_params = true;
                 }
-                aeonb_image_desc d = make_desc(params, in.width, in.height, sg.image.width, sg.image.height, !factory.fixed_aspect_ratio);
+                aeonb_image_desc d;
+                if (params.resize_short_size != 0)
+                {
+                    // resize_short runs on the whole (expanded) picture before the crop (src/etl_image.cpp:160-168):
+                    // a first pass of the same kernel writes the resized picture, the crop pass reads it
+                    image_params whole = params;
+                    whole.resize_short_size = 0;
+                    whole.padding           = 0;
+                    whole.flip              = false;
+                    whole.contrast = whole.brightness = whole.saturation = 1.0f;
+                    whole.hue               = 0;
+                    whole.lighting.clear();
+                    const int cw = params.expand_ratio > 1.0f ? params.expand_size.width : in.width;
+                    const int ch = params.expand_ratio > 1.0f ? params.expand_size.height : in.height;
+                    whole.cropbox           = recti{0, 0, cw, ch};
+                    whole.output_size       = get_resized_short_size(cw, ch, params.resize_short_size);
+                    pre_descs[s].push_back(make_desc(whole, in.width, in.height, 0, 0, false));
+                    pre_job[s].push_back(j);
+                    image_params rest = params;
+                    rest.resize_short_size = 0;
+                    rest.expand_ratio      = 1.0f;
+                    d = make_desc(rest, whole.output_size.width, whole.output_size.height, sg.image.width, sg.image.height,
+                                  !factory.fixed_aspect_ratio);
+                }
+                else
+                    d = make_desc(params, in.width, in.height, sg.image.width, sg.image.height, !factory.fixed_aspect_ratio);
                 if (d.out_w > sg.image.width || d.out_h > sg.image.height)
                     throw std::invalid_argument("transformed image does not fit the configured output size");
                 descs[s].push_back(d);
@@ -282,6 +307,8 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                     {
                         j              = frame_jobs[t];
                         const auto& in = jobs[j].frame.info;
+                        if (params.resize_short_size != 0)
+                            throw error(AEONB_ERR_UNSUPPORTED, "'resize_short_size' for video frames is outside the accelerated path");
                         d              = make_desc(params, in.width, in.height, fc.width, fc.height, true);
                     }
                     descs[s].push_back(d);
@@ -531,12 +558,49 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                     }
                 }
             }
+            const bool pre = !pre_descs[s].empty();
+            size_t     pre_slot = 0;
+            int        pre_pitch = 0;
+            if (pre)
+            {
+                aeonb_image_layout P{};
+                for (const aeonb_image_desc& d : pre_descs[s])
+                {
+                    P.slot_w = std::max(P.slot_w, d.out_w);
+                    P.slot_h = std::max(P.slot_h, d.out_h);
+                }
+                P.channels = 3;
+                P.dtype    = AEONB_U8;
+                P.stride_c = 1;
+                P.stride_x = 3;
+                pre_pitch  = (int)align_up((size_t)P.slot_w * 3, 16);
+                P.stride_y = pre_pitch;
+                pre_slot   = align_up((size_t)pre_pitch * P.slot_h, 256);
+                resized_dev.reserve(pre_slot * pre_descs[s].size());
+                for (size_t i = 0; i < pre_descs[s].size(); ++i)
+                {
+                    aeonb_image_desc& d = pre_descs[s][i];
+                    const int         j = pre_job[s][i];
+                    d.src               = static_cast<const uint8_t*>(pixels_dev.p) + jobs[j].pixel_off;
+                    d.src_pitch         = jobs[j].pitch;
+                    d.src_pixel_stride  = pixel_stride;
+                    d.dst               = static_cast<char*>(resized_dev.p) + i * pre_slot;
+                }
+                check_status(aeonb_image_batch(ctx, pre_descs[s].data(), (int)pre_descs[s].size(), &P));
+                h2d_bytes += (int64_t)(sizeof(aeonb_image_desc) * pre_descs[s].size());
+            }
             for (size_t i = 0; i < descs[s].size(); ++i)
             {
                 aeonb_image_desc& d = descs[s][i];
                 const int         j = desc_job[s][i];
                 d.dst               = produced[o] + desc_dst[s][i];
-                if (j >= 0)
+                if (pre)
+                {
+                    d.src              = static_cast<const uint8_t*>(resized_dev.p) + i * pre_slot;
+                    d.src_pitch        = pre_pitch;
+                    d.src_pixel_stride = 3;
+                }
+                else if (j >= 0)
                 {
                     d.src              = static_cast<const uint8_t*>(pixels_dev.p) + jobs[j].pixel_off;
                     d.src_pitch        = jobs[j].pitch;

@@ -248,3 +248,25 @@ def test_pipelined_calls_give_the_same_batches_as_blocking_calls(ctx):
     got.append({k: v.copy() for k, v in bufs[1].items()})
     for b in range(4):
         assert np.array_equal(got[b]["image"], want[b]["image"]) and np.array_equal(got[b]["label"], want[b]["label"])
+
+
+def test_reference_golden_vectors_through_the_whole_gpu_path(ctx, golden_dir):
+    """aeon test/test_provider.cpp:181-261 (validation recipe: resize_short 256, centre crop 224 drawn by make_params)
+    and :96-179 (training recipe with the crop box forced by the test): encoded fixture -> host entropy decode ->
+    JPEG back-end kernel -> image kernel(s) -> float CHW, against the reference's own golden vectors."""
+    blob = open(os.path.join(golden_dir, "img_2112_70.jpg"), "rb").read()
+    etl = [{"type": "image", "height": 224, "width": 224, "channels": 3, "output_type": "float", "channel_major": True,
+            "bgr_to_rgb": True}]
+    aug = {"type": "image", "flip_enable": False, "center": True, "crop_enable": True, "scale": [224 / 256, 224 / 256],
+           "interpolation_method": "LINEAR", "mean": [0.485, 0.456, 0.406], "stddev": [0.229, 0.224, 0.225],
+           "resize_short_size": 256}
+    got = make_provider(ctx, {"batch_size": 1, "random_seed": 5, "etl": etl, "augmentation": [aug]}).run_host([(blob,)])["image"][0]
+    gold = np.fromfile(os.path.join(golden_dir, "augment_output_linear_eval.bin"), np.float32).reshape(3, 224, 224)
+    assert np.abs(got - gold).max() <= 1e-5          # the reference's own bound for this vector
+    # resize_short on a batch of differently sized pictures, against the record-level oracle
+    cfg = {"batch_size": 6, "random_seed": 9, "etl": [dict(etl[0], height=64, width=64)],
+           "augmentation": [dict(aug, resize_short_size=96, scale=[0.5, 0.9], center=False, flip_enable=True)]}
+    recs = [(r[0],) for r in image_records(50, 6)]
+    got = make_provider(ctx, cfg).run_host(recs)["image"]
+    want = PipelineOracle(cfg).batch(recs)["image"]
+    assert np.abs(got - want).max() <= 1e-6

@@ -115,3 +115,12 @@ def test_ssd_draws_and_patch_sampling_match_restatement():
                 *p.expand_offset, *p.expand_size]
         assert np.array_equal(np.array(want, np.float64), got[i, :23]), i
     assert 60 < (got[:, 18] > 1).sum() < 140
+
+
+def test_reference_validation_recipe_draws_the_centre_crop():
+    """aeon test/test_provider.cpp:202-221 with the 480x360 fixture: resize_short 256 -> 341x256, scale 224/256,
+    centred: the crop box the golden vector augment_output_linear_eval.bin was made with is (58, 16, 224, 224)."""
+    aug = {"type": "image", "flip_enable": False, "center": True, "crop_enable": True, "scale": [224 / 256, 224 / 256],
+           "resize_short_size": 256}
+    got = draw(aug, 1, 1, [(480, 360)], 224, 224)[0]
+    assert got[:6].tolist() == [58, 16, 224, 224, 224, 224]
