@@ -1,5 +1,6 @@
 #include "jpeg_host.hpp"
 
+#include <algorithm>
 #include <cstring>
 #include <vector>
 
@@ -387,7 +388,25 @@ namespace aeonb
         }
     }
 
-    void jpeg_entropy_decode(const jpeg_frame& f, int16_t* const coef[3])
+    jpeg_roi jpeg_roi_for_box(const aeonb_jpeg_info& in, int x0, int y0, int x1, int y1)
+    {
+        const int mw = 8 * in.hs[0], mh = 8 * in.vs[0];
+        const int mcux = in.blocks_w[0] / in.hs[0], mcuy = in.blocks_h[0] / in.vs[0];
+        x0 = std::max(x0, 0);
+        y0 = std::max(y0, 0);
+        x1 = std::min(x1, in.width);
+        y1 = std::min(y1, in.height);
+        if (x1 <= x0 || y1 <= y0)
+            return jpeg_roi{0, 0, 1, 1};
+        jpeg_roi r;
+        r.mx0 = std::max(x0 - 2, 0) / mw;
+        r.my0 = std::max(y0 - 2, 0) / mh;
+        r.mx1 = std::min(mcux, (x1 + 2 + mw - 1) / mw);
+        r.my1 = std::min(mcuy, (y1 + 2 + mh - 1) / mh);
+        return r;
+    }
+
+    void jpeg_entropy_decode(const jpeg_frame& f, int16_t* const coef[3], const jpeg_roi* roi)
     {
         const aeonb_jpeg_info& in = f.info;
         decode_table           dct[3], act[3];
@@ -398,14 +417,18 @@ namespace aeonb
         }
         const int mcux = in.blocks_w[0] / in.hs[0];
         const int mcuy = in.blocks_h[0] / in.vs[0];
+        const int mx0 = roi ? std::max(roi->mx0, 0) : 0, mx1 = roi ? std::min(roi->mx1, mcux) : mcux;
+        const int my0 = roi ? std::max(roi->my0, 0) : 0, my1 = roi ? std::min(roi->my1, mcuy) : mcuy;
+        int16_t    outside[64]; // blocks outside the region are decoded into this and dropped
         bit_reader br(f.scan, f.scan + f.scan_size);
         int        pred[3] = {0, 0, 0};
         int        until_restart = f.restart_interval ? f.restart_interval : -1;
         const uint8_t* zz = k_zz_colmajor.v;
-        for (int my = 0; my < mcuy; ++my)
+        for (int my = 0; my < my1; ++my)
         {
             for (int mx = 0; mx < mcux; ++mx)
             {
+                const bool keep = my >= my0 && mx >= mx0 && mx < mx1;
                 if (until_restart == 0)
                 {
                     br.restart();
@@ -422,7 +445,9 @@ namespace aeonb
                     {
                         for (int bx = 0; bx < in.hs[c]; ++bx)
                         {
-                            int16_t* blk = coef[c] + (static_cast<size_t>(my * in.vs[c] + by) * in.blocks_w[c] + (mx * in.hs[c] + bx)) * 64;
+                            int16_t* blk = keep ? coef[c] + (static_cast<size_t>((my - my0) * in.vs[c] + by) * ((mx1 - mx0) * in.hs[c]) +
+                                                             ((mx - mx0) * in.hs[c] + bx)) * 64
+                                                : outside;
                             std::memset(blk, 0, 64 * sizeof(int16_t));
                             br.refill();
                             const int t = br.decode(dt);
@@ -482,6 +507,42 @@ int aeonb_jpeg_parse(const void* data, size_t size, aeonb_jpeg_info* info)
         jpeg_frame f;
         jpeg_parse(data, size, f);
         *info = f.info;
+        return AEONB_OK;
+    });
+}
+
+int aeonb_jpeg_roi_for_crop(const aeonb_jpeg_info* info, int crop_x, int crop_y, int crop_w, int crop_h, int32_t roi[4])
+{
+    return guarded([&]() {
+        if (!info || !roi)
+            throw std::invalid_argument("aeonb_jpeg_roi_for_crop: NULL argument");
+        const jpeg_roi r = jpeg_roi_for_box(*info, crop_x, crop_y, crop_x + crop_w, crop_y + crop_h);
+        roi[0] = r.mx0;
+        roi[1] = r.my0;
+        roi[2] = r.mx1;
+        roi[3] = r.my1;
+        return AEONB_OK;
+    });
+}
+
+int aeonb_jpeg_entropy_decode_roi(const void* data, size_t size, const int32_t roi[4], int16_t* coef[3], uint16_t* quant[3])
+{
+    return guarded([&]() {
+        if (!data || !coef || !quant || !roi)
+            throw std::invalid_argument("aeonb_jpeg_entropy_decode_roi: NULL argument");
+        jpeg_frame f;
+        jpeg_parse(data, size, f);
+        const int mcux = f.info.blocks_w[0] / f.info.hs[0], mcuy = f.info.blocks_h[0] / f.info.vs[0];
+        if (roi[0] < 0 || roi[1] < 0 || roi[2] > mcux || roi[3] > mcuy || roi[0] >= roi[2] || roi[1] >= roi[3])
+            throw std::invalid_argument("aeonb_jpeg_entropy_decode_roi: region outside the picture");
+        for (int c = 0; c < f.info.ncomp; ++c)
+        {
+            if (!coef[c] || !quant[c])
+                throw std::invalid_argument("aeonb_jpeg_entropy_decode_roi: NULL plane");
+            std::memcpy(quant[c], f.quant[c], sizeof f.quant[c]);
+        }
+        jpeg_roi r{roi[0], roi[1], roi[2], roi[3]};
+        jpeg_entropy_decode(f, coef, &r);
         return AEONB_OK;
     });
 }

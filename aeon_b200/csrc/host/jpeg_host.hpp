@@ -38,7 +38,18 @@ namespace aeonb
     // anything that is not a baseline sequential 8-bit JPEG with 1 or 3 components.
     void jpeg_parse(const void* data, size_t size, jpeg_frame& frame);
 
-    // Entropy-decodes the scan.  coef[c] must hold info.coef_count[c] int16 values; they are
-    // fully overwritten (absent coefficients are zero).
-    void jpeg_entropy_decode(const jpeg_frame& frame, int16_t* const coef[3]);
+    // A rectangle of MCUs [mx0, mx1) x [my0, my1) to keep.  The bit stream is sequential, so everything
+    // before the rectangle's last MCU row is still parsed, but only blocks inside it are stored (as a
+    // compact plane of (mx1-mx0)*hs x (my1-my0)*vs blocks per component) and parsing stops after it.
+    struct jpeg_roi
+    {
+        int mx0 = 0, my0 = 0, mx1 = 1 << 30, my1 = 1 << 30;
+    };
+
+    // The MCU rectangle covering the pixel box [x0,x1) x [y0,y1) of the picture plus one chroma sample of context.
+    jpeg_roi jpeg_roi_for_box(const aeonb_jpeg_info& info, int x0, int y0, int x1, int y1);
+
+    // Entropy-decodes the scan.  Without a region coef[c] must hold info.coef_count[c] int16 values; with
+    // one, the compact plane described above.  The planes are fully overwritten (absent coefficients are zero).
+    void jpeg_entropy_decode(const jpeg_frame& frame, int16_t* const coef[3], const jpeg_roi* roi = nullptr);
 }

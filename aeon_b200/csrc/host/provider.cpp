@@ -161,6 +161,8 @@ aeonb_provider::aeonb_provider(aeonb_ctx* c, const json& cfg) : ctx(c)
     batch_major = cfg.contains("batch_major") ? cfg.find("batch_major")->as_bool() : true;
     if (cfg.contains("scratch_pixel_stride"))
         pixel_stride = (int)cfg.find("scratch_pixel_stride")->as_int();
+    if (cfg.contains("roi_decode"))
+        roi_decode = cfg.find("roi_decode")->as_bool();
     if (pixel_stride != 3 && pixel_stride != 4)
         throw std::invalid_argument("scratch_pixel_stride must be 3 or 4");
     int threads = cfg.contains("decode_threads") ? (int)cfg.find("decode_threads")->as_int() : default_worker_count();

@@ -65,6 +65,12 @@ namespace aeonb
         size_t         stage_bytes = 0;
         size_t         pixel_off = 0;    // decoded picture inside the pixel arena
         int            pitch = 0;
+        // Region of MCUs that is actually decoded (the part of the picture the crop box can touch) and the
+        // picture it yields: origin (rx, ry) in source pixels, size rw x rh, plane sizes in blocks.
+        jpeg_roi       roi;
+        bool           laid_out = false;
+        int            rx = 0, ry = 0, rw = 0, rh = 0;
+        int            roi_blocks_w[3]{}, roi_blocks_h[3]{};
     };
 }
 
@@ -75,6 +81,7 @@ struct aeonb_provider
     int                                  decode_size = 0;
     uint32_t                             seed        = 0;
     bool                                 batch_major = true;
+    bool                                 roi_decode  = true; // decode only the MCUs the crop box can touch
     int                                  pixel_stride = 3;
     std::vector<aeonb::stage>            stages;
     std::vector<aeonb::output_info>      outputs;

@@ -183,28 +183,52 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         if (outputs[o].host_produced)
             out_host[o].assign((size_t)batch_size * outputs[o].shape.byte_size(), 0);
 
+    // Parses the headers of one JPEG stream and registers it as a decode job (sizes only; no layout yet).
     auto plan_jpeg = [&](const void* data, size_t size) -> int {
         jpeg_job job;
         job.data = static_cast<const uint8_t*>(data);
         job.size = size;
         jpeg_parse(data, size, job.frame);
+        jobs.push_back(job);
+        return (int)jobs.size() - 1;
+    };
+    // Fixes the region of the picture a job has to produce -- the MCUs that the crop box of `d` (given in
+    // canvas coordinates, the picture sitting at canvas_x/canvas_y) can touch, plus one chroma sample of
+    // context -- and reserves its space in the staging buffer and in the pixel arena.  `d` == nullptr keeps
+    // the whole picture.  A job shared by several descriptors (repeated video frame) keeps its first layout.
+    auto layout_jpeg = [&](int j, const aeonb_image_desc* d) {
+        jpeg_job& job = jobs[j];
+        if (job.laid_out)
+            return;
         const aeonb_jpeg_info& in = job.frame.info;
+        const int mw = 8 * in.hs[0], mh = 8 * in.vs[0];
+        const int mcux = in.blocks_w[0] / in.hs[0], mcuy = in.blocks_h[0] / in.vs[0];
+        jpeg_roi roi{0, 0, mcux, mcuy};
+        if (d && roi_decode) // a crop box that lies on the zero canvas only reads nothing of the picture: one MCU is kept
+            roi = jpeg_roi_for_box(in, d->crop_x - d->canvas_x, d->crop_y - d->canvas_y, d->crop_x + d->crop_w - d->canvas_x,
+                                   d->crop_y + d->crop_h - d->canvas_y);
+        job.roi = roi;
+        job.rx  = roi.mx0 * mw;
+        job.ry  = roi.my0 * mh;
+        job.rw  = std::min(in.width, roi.mx1 * mw) - job.rx;
+        job.rh  = std::min(in.height, roi.my1 * mh) - job.ry;
         size_t off    = align_up(stage_bytes, 256);
         job.stage_off = off;
         off += 3 * 64 * sizeof(uint16_t);
         for (int c = 0; c < in.ncomp; ++c)
         {
-            off              = align_up(off, 256);
-            job.plane_off[c] = off;
-            off += (size_t)in.coef_count[c] * sizeof(int16_t);
+            job.roi_blocks_w[c] = (roi.mx1 - roi.mx0) * in.hs[c];
+            job.roi_blocks_h[c] = (roi.my1 - roi.my0) * in.vs[c];
+            off                 = align_up(off, 256);
+            job.plane_off[c]    = off;
+            off += (size_t)job.roi_blocks_w[c] * job.roi_blocks_h[c] * 64 * sizeof(int16_t);
         }
         job.stage_bytes = off - job.stage_off;
         stage_bytes     = off;
-        job.pitch       = (int)align_up((size_t)in.width * pixel_stride, 16);
+        job.pitch       = (int)align_up((size_t)job.rw * pixel_stride, 16);
         job.pixel_off   = align_up(pixel_bytes, 256);
-        pixel_bytes     = job.pixel_off + (size_t)job.pitch * in.height;
-        jobs.push_back(job);
-        return (int)jobs.size() - 1;
+        pixel_bytes     = job.pixel_off + (size_t)job.pitch * job.rh;
+        job.laid_out    = true;
     };
 
     // ---- 1. sequential planning pass (record order == RNG order)
@@ -254,6 +278,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                     whole.output_size       = get_resized_short_size(cw, ch, params.resize_short_size);
                     pre_descs[s].push_back(make_desc(whole, in.width, in.height, 0, 0, false));
                     pre_job[s].push_back(j);
+                    layout_jpeg(j, nullptr); // the resize pass reads the whole picture
                     image_params rest = params;
                     rest.resize_short_size = 0;
                     rest.expand_ratio      = 1.0f;
@@ -261,7 +286,10 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                                   !factory.fixed_aspect_ratio);
                 }
                 else
+                {
                     d = make_desc(params, in.width, in.height, sg.image.width, sg.image.height, !factory.fixed_aspect_ratio);
+                    layout_jpeg(j, &d);
+                }
                 if (d.out_w > sg.image.width || d.out_h > sg.image.height)
                     throw std::invalid_argument("transformed image does not fit the configured output size");
                 descs[s].push_back(d);
@@ -310,6 +338,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                         if (params.resize_short_size != 0)
                             throw error(AEONB_ERR_UNSUPPORTED, "'resize_short_size' for video frames is outside the accelerated path");
                         d              = make_desc(params, in.width, in.height, fc.width, fc.height, true);
+                        layout_jpeg(j, &d);
                     }
                     descs[s].push_back(d);
                     desc_job[s].push_back(j);
@@ -444,7 +473,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                     int16_t* planes[3] = {reinterpret_cast<int16_t*>(hstage + job.plane_off[0]),
                                           reinterpret_cast<int16_t*>(hstage + job.plane_off[1]),
                                           reinterpret_cast<int16_t*>(hstage + job.plane_off[2])};
-                    jpeg_entropy_decode(job.frame, planes);
+                    jpeg_entropy_decode(job.frame, planes, &job.roi);
                 }
                 else
                 {
@@ -488,8 +517,8 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
             const jpeg_job&        job = jobs[i];
             const aeonb_jpeg_info& in  = job.frame.info;
             aeonb_jpeg_desc&       d   = jd[i];
-            d.width  = in.width;
-            d.height = in.height;
+            d.width  = job.rw;
+            d.height = job.rh;
             d.ncomp  = in.ncomp;
             for (int c = 0; c < in.ncomp; ++c)
             {
@@ -497,8 +526,8 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                 d.quant[c]    = reinterpret_cast<const uint16_t*>(dstage + job.stage_off) + 64 * c;
                 d.hs[c]       = in.hs[c];
                 d.vs[c]       = in.vs[c];
-                d.blocks_w[c] = in.blocks_w[c];
-                d.blocks_h[c] = in.blocks_h[c];
+                d.blocks_w[c] = job.roi_blocks_w[c];
+                d.blocks_h[c] = job.roi_blocks_h[c];
             }
             d.dst              = static_cast<uint8_t*>(pixels_dev.p) + job.pixel_off;
             d.dst_pitch        = job.pitch;
@@ -602,9 +631,14 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                 }
                 else if (j >= 0)
                 {
+                    // the decoded region stands where that part of the picture stands on the canvas
                     d.src              = static_cast<const uint8_t*>(pixels_dev.p) + jobs[j].pixel_off;
                     d.src_pitch        = jobs[j].pitch;
                     d.src_pixel_stride = pixel_stride;
+                    d.src_w            = jobs[j].rw;
+                    d.src_h            = jobs[j].rh;
+                    d.canvas_x += jobs[j].rx;
+                    d.canvas_y += jobs[j].ry;
                 }
             }
             check_status(aeonb_image_batch(ctx, descs[s].data(), (int)descs[s].size(), &L));

@@ -213,6 +213,16 @@ int aeonb_jpeg_parse(const void* data, size_t size, aeonb_jpeg_info* info);
  * aeonb_jpeg_desc) and quantiser tables, all host memory supplied by the caller. */
 int aeonb_jpeg_entropy_decode(const void* data, size_t size, int16_t* coef[3], uint16_t* quant[3]);
 
+/* Region decoding.  Only the part of a picture that the crop box can touch has to be decoded.
+ * aeonb_jpeg_roi_for_crop turns a crop box (in picture pixels) into the rectangle of MCUs
+ * roi = {mx0, my0, mx1, my1} (half open) that covers it plus the one chroma sample of context the
+ * upsampling filter needs; aeonb_jpeg_entropy_decode_roi stores only the blocks of that rectangle, as compact
+ * planes of (mx1-mx0)*hs[c] x (my1-my0)*vs[c] blocks, and stops parsing after its last MCU row.  The back-end
+ * kernel is then given the region as if it were the picture: width/height = the region's extent in pixels
+ * (clipped to the picture), blocks_w/h = the compact plane sizes. */
+int aeonb_jpeg_roi_for_crop(const aeonb_jpeg_info* info, int crop_x, int crop_y, int crop_w, int crop_h, int32_t roi[4]);
+int aeonb_jpeg_entropy_decode_roi(const void* data, size_t size, const int32_t roi[4], int16_t* coef[3], uint16_t* quant[3]);
+
 /* Draws augmentation parameters exactly as aeon's param_factory::make_params does
  * (src/augment_image.cpp:107-230) for `n` records whose decoded sizes are in_w/in_h,
  * using per-slot std::minstd_rand0 engines seeded as aeon's batch_decoder seeds them

@@ -62,3 +62,51 @@ def test_corrupt_streams_raise(ctx):
     for blob in (b"", b"\x00" * 64, b"\xff\xd8\xff\xd9"):
         with pytest.raises(AeonError, match="Decoding image failed"):
             K.jpeg_entropy_decode(blob)
+
+
+def test_region_decode_equals_the_same_pixels_of_the_full_decode(ctx):
+    """Only the MCUs a crop box can touch are decoded; inside the box the pixels must equal the full decode."""
+    import ctypes as C
+    import cv2
+    import torch
+    from aeon_b200 import _lib as L, kernels as K
+    rng = np.random.default_rng(23)
+    dev = torch.device("cuda", ctx.device)
+    for (h, w), extra in [((300, 420), []), ((97, 131), []), ((256, 256), [cv2.IMWRITE_JPEG_SAMPLING_FACTOR, cv2.IMWRITE_JPEG_SAMPLING_FACTOR_422]),
+                          ((64, 64), [cv2.IMWRITE_JPEG_RST_INTERVAL, 5])]:
+        blob = jpeg_bytes(gradient_image(rng, h, w), 90, extra)
+        ref = cv2.imdecode(np.frombuffer(blob, np.uint8), cv2.IMREAD_COLOR)
+        info = K.jpeg_parse(blob)
+        for _ in range(6):
+            cw, ch = int(rng.integers(1, w + 1)), int(rng.integers(1, h + 1))
+            cx, cy = int(rng.integers(0, w - cw + 1)), int(rng.integers(0, h - ch + 1))
+            roi = (C.c_int32 * 4)()
+            L.check(ctx.lib.aeonb_jpeg_roi_for_crop(C.byref(info), cx, cy, cw, ch, roi))
+            mw, mh = 8 * info.hs[0], 8 * info.vs[0]
+            rx, ry = roi[0] * mw, roi[1] * mh
+            rw, rh = min(w, roi[2] * mw) - rx, min(h, roi[3] * mh) - ry
+            assert rx <= cx and ry <= cy and rx + rw >= cx + cw and ry + rh >= cy + ch
+            d = (L.JpegDesc * 1)()
+            d[0].width, d[0].height, d[0].ncomp = rw, rh, info.ncomp
+            coefs, quants, keep = [], [], []
+            for c in range(info.ncomp):
+                bw, bh = (roi[2] - roi[0]) * info.hs[c], (roi[3] - roi[1]) * info.vs[c]
+                coefs.append(np.zeros(bw * bh * 64, np.int16))
+                quants.append(np.zeros(64, np.uint16))
+                d[0].hs[c], d[0].vs[c], d[0].blocks_w[c], d[0].blocks_h[c] = info.hs[c], info.vs[c], bw, bh
+            cp = (C.c_void_p * 3)(*[c.ctypes.data for c in coefs])
+            qp = (C.c_void_p * 3)(*[q.ctypes.data for q in quants])
+            buf = (C.c_char * len(blob)).from_buffer_copy(blob)
+            L.check(ctx.lib.aeonb_jpeg_entropy_decode_roi(buf, len(blob), roi, cp, qp))
+            with torch.cuda.stream(ctx.torch_stream):
+                for c in range(info.ncomp):
+                    ct, qt = torch.from_numpy(coefs[c]).to(dev), torch.from_numpy(quants[c].view(np.int16)).to(dev)
+                    keep += [ct, qt]
+                    d[0].coef[c], d[0].quant[c] = ct.data_ptr(), qt.data_ptr()
+                pitch = (rw * 3 + 15) // 16 * 16
+                out = torch.zeros((rh, pitch), dtype=torch.uint8, device=dev)
+                d[0].dst, d[0].dst_pitch, d[0].dst_pixel_stride = out.data_ptr(), pitch, 3
+                L.check(ctx.lib.aeonb_jpeg_backend_batch(ctx.handle, d, 1))
+                ctx.synchronize()
+            got = out.cpu().numpy()[:, :rw * 3].reshape(rh, rw, 3)
+            assert np.array_equal(got[cy - ry:cy - ry + ch, cx - rx:cx - rx + cw], ref[cy:cy + ch, cx:cx + cw]), (h, w, cx, cy, cw, ch)

@@ -270,3 +270,14 @@ def test_reference_golden_vectors_through_the_whole_gpu_path(ctx, golden_dir):
     got = make_provider(ctx, cfg).run_host(recs)["image"]
     want = PipelineOracle(cfg).batch(recs)["image"]
     assert np.abs(got - want).max() <= 1e-6
+
+
+def test_region_decode_and_full_decode_give_identical_batches(ctx):
+    cfg = {"batch_size": 16, "random_seed": 31,
+           "etl": [{"type": "image", "height": 224, "width": 224, "output_type": "uint8_t"}], "augmentation": [AUG_C2 | {"mean": [], "stddev": []}]}
+    recs = [(r[0],) for r in image_records(52, 16)]
+    a = make_provider(ctx, dict(cfg, roi_decode=True))
+    b = make_provider(ctx, dict(cfg, roi_decode=False))
+    ga, gb = a.run_host(recs)["image"], b.run_host(recs)["image"]
+    assert np.array_equal(ga, gb)
+    assert a.stats()["h2d_bytes"] < 0.9 * b.stats()["h2d_bytes"]   # fewer coefficient bytes cross PCIe
