@@ -17,6 +17,8 @@
 // calls aeon makes (src/etl_image.cpp:146-202, src/image.cpp:336-406, src/etl_image.cpp:246-341);
 // this file is compiled with -fmad=false and uses explicit fused operations only where
 // OpenCV's own code is fused.
+#include <algorithm>
+
 #include <cooperative_groups.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -40,6 +42,7 @@ namespace aeonb
             int                     rows_per_band;
             int                     tile_pitch; // bytes per tile row (multiple of 16)
             int                     vector_ok;  // slots are 16-byte aligned with unit x stride
+            int                     n;          // records in the batch
         };
 
         struct row_tap
@@ -137,12 +140,46 @@ namespace aeonb
 
         // 8-bit BGR->HSV (H in [0,180)) with 12-bit reciprocal tables, then the hue shift with C
         // remainder semantics stored through a uint8_t, then float32 HSV->BGR.
-        __device__ __forceinline__ bgr hue_rotate(bgr p, int hue, bool truncate, const int* sdiv, const int* hdiv)
+        // Per-CTA tables of the hue stage (all exact restatements of the per-pixel arithmetic, tabulated once):
+        //   sdiv/hdiv : the 12-bit reciprocals of 8-bit BGR->HSV;
+        //   sector_f  : for a hue h in [0,180), after the shift uint8((h + hue) % 180): the HSV->BGR sector and
+        //               the fractional position inside it;
+        //   unit      : x * (1/255) for x in [0,255] (the float S and V).
+        struct hue_tables
+        {
+            int    sdiv[256];
+            int    hdiv[256];
+            float2 sector_f[180]; // .x = sector as a float bit pattern of an int, .y = f
+            float  unit[256];
+        };
+
+        __device__ __forceinline__ void build_hue_tables(hue_tables& t, int hue, int tid, int nthreads)
+        {
+            for (int i = tid; i < 256; i += nthreads)
+            {
+                t.sdiv[i] = i ? __double2int_rn((double)(255 << 12) / (double)i) : 0;
+                t.hdiv[i] = i ? __double2int_rn((double)(180 << 12) / (6.0 * (double)i)) : 0;
+                t.unit[i] = (float)i * (1.0f / 255.0f);
+            }
+            for (int h = tid; h < 180; h += nthreads)
+            {
+                const int   hs = ((h + hue) % 180) & 0xFF; // C remainder, stored through a uint8_t
+                const float hf = (float)hs * (6.0f / 180.0f);
+                const float fl = floorf(hf);
+                int         sector = (int)fl;
+                if (sector >= 6)
+                    sector -= 6; // hs <= 255 gives sector <= 8
+                t.sector_f[h] = make_float2(__int_as_float(sector), hf - fl);
+            }
+        }
+
+        // 8-bit BGR->HSV (H in [0,180)), hue shift, float32 HSV->BGR, as OpenCV computes them.
+        __device__ __forceinline__ bgr hue_rotate(bgr p, bool truncate, const hue_tables& t)
         {
             const int v    = max(max(p.b, p.g), p.r);
             const int vmin = min(min(p.b, p.g), p.r);
             const int diff = v - vmin;
-            const int s    = (diff * sdiv[v] + (1 << 11)) >> 12;
+            const int s    = (diff * t.sdiv[v] + (1 << 11)) >> 12;
             int       h;
             if (v == p.r)
                 h = p.g - p.b;
@@ -150,19 +187,14 @@ namespace aeonb
                 h = p.b - p.r + 2 * diff;
             else
                 h = p.r - p.g + 4 * diff;
-            h = (h * hdiv[diff] + (1 << 11)) >> 12;
+            h = (h * t.hdiv[diff] + (1 << 11)) >> 12;
             if (h < 0)
                 h += 180;
-            h = ((h + hue) % 180) & 0xFF;
-
-            const float hf     = (float)h * (6.0f / 180.0f);
-            const float sf     = (float)s * (1.0f / 255.0f);
-            const float vf     = (float)v * (1.0f / 255.0f);
-            const float fl     = floorf(hf);
-            const float f      = hf - fl;
-            int         sector = (int)fl;
-            if (sector >= 6)
-                sector -= 6; // h <= 255 gives sector <= 8
+            const float2 sf2    = t.sector_f[h];
+            const int    sector = __float_as_int(sf2.x);
+            const float  f      = sf2.y;
+            const float  sf     = t.unit[s];
+            const float  vf     = t.unit[v];
             const float t1 = vf * (1.0f - sf);
             const float t2 = vf * __fmaf_rn(-sf, f, 1.0f);
             const float t3 = vf * __fmaf_rn(-sf, 1.0f - f, 1.0f);
@@ -170,18 +202,18 @@ namespace aeonb
             const float fb = sector < 2 ? t1 : sector == 2 ? t3 : sector < 5 ? vf : t2;
             const float fg = sector == 0 ? t3 : sector < 3 ? vf : sector == 3 ? t2 : t1;
             const float fr = sector == 0 ? vf : sector == 1 ? t2 : sector < 4 ? t1 : sector == 4 ? t3 : vf;
-            bgr o;
+            bgr o; // products of two factors in [0,1] times 255: already inside 0..255
             if (truncate)
             {
-                o.b = clamp_u8(__float2int_rz(fb * 255.0f));
-                o.g = clamp_u8(__float2int_rz(fg * 255.0f));
-                o.r = clamp_u8(__float2int_rz(fr * 255.0f));
+                o.b = __float2int_rz(fb * 255.0f);
+                o.g = __float2int_rz(fg * 255.0f);
+                o.r = __float2int_rz(fr * 255.0f);
             }
             else
             {
-                o.b = clamp_u8(__float2int_rn(fb * 255.0f));
-                o.g = clamp_u8(__float2int_rn(fg * 255.0f));
-                o.r = clamp_u8(__float2int_rn(fr * 255.0f));
+                o.b = __float2int_rn(fb * 255.0f);
+                o.g = __float2int_rn(fg * 255.0f);
+                o.r = __float2int_rn(fr * 255.0f);
             }
             return o;
         }
@@ -237,8 +269,7 @@ namespace aeonb
             __shared__ aeonb_image_desc d;
             __shared__ unsigned int     part_sum[3];  // this CTA's per-channel sums (output channel order)
             __shared__ float            contrast_add[3];
-            __shared__ int              hsv_sdiv[256];
-            __shared__ int              hsv_hdiv[256];
+            __shared__ hue_tables       hue_tab;
             __shared__ T                lut[3][256];
 
             cg::cluster_group cluster = cg::this_cluster();
@@ -250,311 +281,312 @@ namespace aeonb
             constexpr int     WARPS   = AUG_THREADS / 32;
             const aeonb_image_layout& lay = L.layout;
 
-            // ---- record descriptor -> shared memory
+            // A cluster takes records rec, rec + gridDim.y, ...; the launcher starts one cluster per record.
+            for (int rec = blockIdx.y; rec < L.n; rec += gridDim.y)
             {
-                const int* g = reinterpret_cast<const int*>(L.descs + blockIdx.y);
-                int*       s = reinterpret_cast<int*>(&d);
-                for (int i = tid; i < (int)(sizeof(aeonb_image_desc) / sizeof(int)); i += AUG_THREADS)
-                    s[i] = g[i];
-                if (tid < 3)
-                    part_sum[tid] = 0;
-            }
-            __syncthreads();
-
-            const int  out_w    = d.src ? d.out_w : 0;
-            const int  out_h    = d.src ? d.out_h : 0;
-            const int  row0     = band * L.rows_per_band;
-            const int  row_end  = min(row0 + L.rows_per_band, lay.slot_h);
-            const int  img_end  = min(row_end, out_h); // rows that carry image data
-            const int  pitch    = L.tile_pitch;
-            const int  plane    = L.rows_per_band * pitch;
-            const bool use_hue  = d.hue != 0;
-            const bool use_ctr  = d.contrast != 1.0f;
-            const bool swap_rb  = lay.bgr_to_rgb != 0;
-            const bool linear   = d.interp == AEONB_INTERP_LINEAR;
-            // the whole crop box lies on the source picture: no canvas test per tap
-            const bool inside = d.crop_x >= d.canvas_x && d.crop_y >= d.canvas_y && d.crop_x + d.crop_w <= d.canvas_x + d.src_w &&
-                                d.crop_y + d.crop_h <= d.canvas_y + d.src_h;
-
-            unsigned char* tile = smem;                                            // [3][rows_per_band][pitch]
-            int2*          xofs = reinterpret_cast<int2*>(smem + 3 * plane);       // [out_w] byte offsets of the two taps
-            short2*        xw   = reinterpret_cast<short2*>(xofs + lay.slot_w);    // [out_w]
-            row_tap*       ytab = reinterpret_cast<row_tap*>(xw + lay.slot_w);     // [rows_per_band]
-
-            // ---- tap tables
-            for (int x = tid; x < out_w; x += AUG_THREADS)
-            {
-                int   s;
-                short a0 = 2048, a1 = 0;
-                if (linear)
-                    linear_tap(x, d.crop_w, out_w, true, s, a0, a1);
-                else
-                    s = nearest_tap(x, d.crop_w, out_w);
-                const int s1 = min(s + 1, d.crop_w - 1);
-                xofs[x]      = inside ? make_int2(s * PIX, s1 * PIX) : make_int2(s, s1);
-                xw[x]        = make_short2(a0, a1);
-            }
-            for (int r = tid; r < img_end - row0; r += AUG_THREADS)
-            {
-                row_tap t;
-                if (linear)
+                // ---- record descriptor -> shared memory
                 {
-                    int s;
-                    linear_tap(row0 + r, d.crop_h, out_h, false, s, t.b0, t.b1);
-                    t.y0 = min(max(s, 0), d.crop_h - 1);
-                    t.y1 = min(max(s + 1, 0), d.crop_h - 1);
+                    const int* g = reinterpret_cast<const int*>(L.descs + rec);
+                    int*       s = reinterpret_cast<int*>(&d);
+                    for (int i = tid; i < (int)(sizeof(aeonb_image_desc) / sizeof(int)); i += AUG_THREADS)
+                        s[i] = g[i];
+                    if (tid < 3)
+                        part_sum[tid] = 0;
                 }
-                else
-                {
-                    t.y0 = t.y1 = nearest_tap(row0 + r, d.crop_h, out_h);
-                    t.b0        = 2048;
-                    t.b1        = 0;
-                }
-                ytab[r] = t;
-            }
-            if (use_hue)
-            {
-                for (int i = tid; i < 256; i += AUG_THREADS)
-                {
-                    hsv_sdiv[i] = i ? __double2int_rn((double)(255 << 12) / (double)i) : 0;
-                    hsv_hdiv[i] = i ? __double2int_rn((double)(180 << 12) / (6.0 * (double)i)) : 0;
-                }
-            }
-            // the slot may be larger than the image: clear what the spatial stage will not write
-            if (out_w < lay.slot_w || img_end < row_end)
-                for (int i = tid; i < 3 * plane / 16; i += AUG_THREADS)
-                    reinterpret_cast<int4*>(tile)[i] = make_int4(0, 0, 0, 0);
-            __syncthreads();
+                __syncthreads();
 
-            // ---- resize + per-pixel photometric into the tile; a warp takes 32 consecutive pixels of a row
-            unsigned int sum0 = 0, sum1 = 0, sum2 = 0;
-            {
-                const int      rows  = max(img_end - row0, 0);
-                const int      nseg  = (out_w + 31) >> 5;
-                const int      units = rows * nseg;
-                const uint8_t* base  = d.src + (ptrdiff_t)(d.crop_y - d.canvas_y) * d.src_pitch + (ptrdiff_t)(d.crop_x - d.canvas_x) * PIX;
-                // Record constants live in shared memory; byte stores into the tile could alias them, so the
-                // ones the pixel loop needs are copied to registers once.
-                const int   src_pitch    = d.src_pitch;
-                const int   color_enable = d.color_enable;
-                const float cs0 = d.color_scale[0], cs1 = d.color_scale[1], cs2 = d.color_scale[2];
-                const int   m0 = d.color_matrix[0], m1 = d.color_matrix[1], m2 = d.color_matrix[2], m3 = d.color_matrix[3],
-                            m4 = d.color_matrix[4], m5 = d.color_matrix[5], m6 = d.color_matrix[6], m7 = d.color_matrix[7],
-                            m8 = d.color_matrix[8];
-                const int   hue = d.hue, hsv_cols = d.hsv_vector_cols;
-                const bool  flip = d.flip != 0;
+                const int  out_w    = d.src ? d.out_w : 0;
+                const int  out_h    = d.src ? d.out_h : 0;
+                const int  row0     = band * L.rows_per_band;
+                const int  row_end  = min(row0 + L.rows_per_band, lay.slot_h);
+                const int  img_end  = min(row_end, out_h); // rows that carry image data
+                const int  pitch    = L.tile_pitch;
+                const int  plane    = L.rows_per_band * pitch;
+                const bool use_hue  = d.hue != 0;
+                const bool use_ctr  = d.contrast != 1.0f;
+                const bool swap_rb  = lay.bgr_to_rgb != 0;
+                const bool linear   = d.interp == AEONB_INTERP_LINEAR;
+                // the whole crop box lies on the source picture: no canvas test per tap
+                const bool inside = d.crop_x >= d.canvas_x && d.crop_y >= d.canvas_y && d.crop_x + d.crop_w <= d.canvas_x + d.src_w &&
+                                    d.crop_y + d.crop_h <= d.canvas_y + d.src_h;
 
-                struct taps
+                unsigned char* tile = smem;                                            // [3][rows_per_band][pitch]
+                int2*          xofs = reinterpret_cast<int2*>(smem + 3 * plane);       // [out_w] byte offsets of the two taps
+                short2*        xw   = reinterpret_cast<short2*>(xofs + lay.slot_w);    // [out_w]
+                row_tap*       ytab = reinterpret_cast<row_tap*>(xw + lay.slot_w);     // [rows_per_band]
+
+                // ---- tap tables
+                for (int x = tid; x < out_w; x += AUG_THREADS)
                 {
-                    bgr     p00, p01, p10, p11;
-                    short2  a;
-                    short   b0, b1;
-                    int     x, r;
-                    bool    valid;
-                };
-                // all global loads of one unit (32 pixels of a row), issued before any arithmetic on them
-                auto load_unit = [&](int r, int seg) {
-                    taps k;
-                    k.r     = r;
-                    k.x     = seg * 32 + lane;
-                    k.valid = r < rows && k.x < out_w;
-                    if (!k.valid)
-                        return k;
-                    const row_tap t  = ytab[k.r];
-                    const int2    xo = xofs[k.x];
-                    k.a  = xw[k.x];
-                    k.b0 = t.b0;
-                    k.b1 = t.b1;
-                    if (inside)
+                    int   s;
+                    short a0 = 2048, a1 = 0;
+                    if (linear)
+                        linear_tap(x, d.crop_w, out_w, true, s, a0, a1);
+                    else
+                        s = nearest_tap(x, d.crop_w, out_w);
+                    const int s1 = min(s + 1, d.crop_w - 1);
+                    xofs[x]      = inside ? make_int2(s * PIX, s1 * PIX) : make_int2(s, s1);
+                    xw[x]        = make_short2(a0, a1);
+                }
+                for (int r = tid; r < img_end - row0; r += AUG_THREADS)
+                {
+                    row_tap t;
+                    if (linear)
                     {
-                        const uint8_t* r0 = base + (ptrdiff_t)t.y0 * src_pitch;
-                        const uint8_t* r1 = base + (ptrdiff_t)t.y1 * src_pitch;
-                        k.p00 = load_px<PIX>(r0 + xo.x);
-                        if (linear)
-                        {
-                            k.p01 = load_px<PIX>(r0 + xo.y);
-                            k.p10 = load_px<PIX>(r1 + xo.x);
-                            k.p11 = load_px<PIX>(r1 + xo.y);
-                        }
+                        int s;
+                        linear_tap(row0 + r, d.crop_h, out_h, false, s, t.b0, t.b1);
+                        t.y0 = min(max(s, 0), d.crop_h - 1);
+                        t.y1 = min(max(s + 1, 0), d.crop_h - 1);
                     }
                     else
                     {
-                        k.p00 = fetch<PIX>(d, xo.x, t.y0);
+                        t.y0 = t.y1 = nearest_tap(row0 + r, d.crop_h, out_h);
+                        t.b0        = 2048;
+                        t.b1        = 0;
+                    }
+                    ytab[r] = t;
+                }
+                if (use_hue)
+                    build_hue_tables(hue_tab, d.hue, tid, AUG_THREADS);
+                // the slot may be larger than the image: clear what the spatial stage will not write
+                if (out_w < lay.slot_w || img_end < row_end)
+                    for (int i = tid; i < 3 * plane / 16; i += AUG_THREADS)
+                        reinterpret_cast<int4*>(tile)[i] = make_int4(0, 0, 0, 0);
+                __syncthreads();
+
+                // ---- resize + per-pixel photometric into the tile; a warp takes 32 consecutive pixels of a row
+                unsigned int sum0 = 0, sum1 = 0, sum2 = 0;
+                {
+                    const int      rows  = max(img_end - row0, 0);
+                    const int      nseg  = (out_w + 31) >> 5;
+                    const int      units = rows * nseg;
+                    const uint8_t* base  = d.src + (ptrdiff_t)(d.crop_y - d.canvas_y) * d.src_pitch + (ptrdiff_t)(d.crop_x - d.canvas_x) * PIX;
+                    // Record constants live in shared memory; byte stores into the tile could alias them, so the
+                    // ones the pixel loop needs are copied to registers once.
+                    const int   src_pitch    = d.src_pitch;
+                    const int   color_enable = d.color_enable;
+                    const float cs0 = d.color_scale[0], cs1 = d.color_scale[1], cs2 = d.color_scale[2];
+                    const int   m0 = d.color_matrix[0], m1 = d.color_matrix[1], m2 = d.color_matrix[2], m3 = d.color_matrix[3],
+                                m4 = d.color_matrix[4], m5 = d.color_matrix[5], m6 = d.color_matrix[6], m7 = d.color_matrix[7],
+                                m8 = d.color_matrix[8];
+                    const int   hsv_cols = d.hsv_vector_cols;
+                    const bool  flip = d.flip != 0;
+
+                    struct taps
+                    {
+                        bgr     p00, p01, p10, p11;
+                        short2  a;
+                        short   b0, b1;
+                        int     x, r;
+                        bool    valid;
+                    };
+                    // all global loads of one unit (32 pixels of a row), issued before any arithmetic on them
+                    auto load_unit = [&](int r, int seg) {
+                        taps k;
+                        k.r     = r;
+                        k.x     = seg * 32 + lane;
+                        k.valid = r < rows && k.x < out_w;
+                        if (!k.valid)
+                            return k;
+                        const row_tap t  = ytab[k.r];
+                        const int2    xo = xofs[k.x];
+                        k.a  = xw[k.x];
+                        k.b0 = t.b0;
+                        k.b1 = t.b1;
+                        if (inside)
+                        {
+                            const uint8_t* r0 = base + (ptrdiff_t)t.y0 * src_pitch;
+                            const uint8_t* r1 = base + (ptrdiff_t)t.y1 * src_pitch;
+                            k.p00 = load_px<PIX>(r0 + xo.x);
+                            if (linear)
+                            {
+                                k.p01 = load_px<PIX>(r0 + xo.y);
+                                k.p10 = load_px<PIX>(r1 + xo.x);
+                                k.p11 = load_px<PIX>(r1 + xo.y);
+                            }
+                        }
+                        else
+                        {
+                            k.p00 = fetch<PIX>(d, xo.x, t.y0);
+                            if (linear)
+                            {
+                                k.p01 = fetch<PIX>(d, xo.y, t.y0);
+                                k.p10 = fetch<PIX>(d, xo.x, t.y1);
+                                k.p11 = fetch<PIX>(d, xo.y, t.y1);
+                            }
+                        }
+                        return k;
+                    };
+                    auto finish_unit = [&](const taps& k) {
+                        if (!k.valid)
+                            return;
+                        bgr px = k.p00;
                         if (linear)
                         {
-                            k.p01 = fetch<PIX>(d, xo.y, t.y0);
-                            k.p10 = fetch<PIX>(d, xo.x, t.y1);
-                            k.p11 = fetch<PIX>(d, xo.y, t.y1);
+                            // horizontal pass keeps 11 fractional bits; vertical pass as in OpenCV's 8-bit path
+                            const int      b0 = k.b0, b1 = k.b1;
+                            const unsigned aw = (unsigned)(unsigned short)k.a.x | ((unsigned)(unsigned short)k.a.y << 16);
+                            // two-way dot product: low 16 bits of aw times byte 0, high 16 bits times byte 1 (weights are 0..2048)
+                            const int hb0 = (int)__dp2a_lo(aw, (unsigned)(k.p00.b | (k.p01.b << 8)), 0u);
+                            const int hb1 = (int)__dp2a_lo(aw, (unsigned)(k.p10.b | (k.p11.b << 8)), 0u);
+                            const int hg0 = (int)__dp2a_lo(aw, (unsigned)(k.p00.g | (k.p01.g << 8)), 0u);
+                            const int hg1 = (int)__dp2a_lo(aw, (unsigned)(k.p10.g | (k.p11.g << 8)), 0u);
+                            const int hr0 = (int)__dp2a_lo(aw, (unsigned)(k.p00.r | (k.p01.r << 8)), 0u);
+                            const int hr1 = (int)__dp2a_lo(aw, (unsigned)(k.p10.r | (k.p11.r << 8)), 0u);
+                            // vertical pass as in OpenCV's 8-bit path; with weights summing to 2048 the result stays in 0..255
+                            px.b = (((b0 * (hb0 >> 4)) >> 16) + ((b1 * (hb1 >> 4)) >> 16) + 2) >> 2;
+                            px.g = (((b0 * (hg0 >> 4)) >> 16) + ((b1 * (hg1 >> 4)) >> 16) + 2) >> 2;
+                            px.r = (((b0 * (hr0 >> 4)) >> 16) + ((b1 * (hr1 >> 4)) >> 16) + 2) >> 2;
                         }
-                    }
-                    return k;
-                };
-                auto finish_unit = [&](const taps& k) {
-                    if (!k.valid)
-                        return;
-                    bgr px = k.p00;
-                    if (linear)
-                    {
-                        // horizontal pass keeps 11 fractional bits; vertical pass as in OpenCV's 8-bit path
-                        const int      b0 = k.b0, b1 = k.b1;
-                        const unsigned aw = (unsigned)(unsigned short)k.a.x | ((unsigned)(unsigned short)k.a.y << 16);
-                        // two-way dot product: low 16 bits of aw times byte 0, high 16 bits times byte 1 (weights are 0..2048)
-                        const int hb0 = (int)__dp2a_lo(aw, (unsigned)(k.p00.b | (k.p01.b << 8)), 0u);
-                        const int hb1 = (int)__dp2a_lo(aw, (unsigned)(k.p10.b | (k.p11.b << 8)), 0u);
-                        const int hg0 = (int)__dp2a_lo(aw, (unsigned)(k.p00.g | (k.p01.g << 8)), 0u);
-                        const int hg1 = (int)__dp2a_lo(aw, (unsigned)(k.p10.g | (k.p11.g << 8)), 0u);
-                        const int hr0 = (int)__dp2a_lo(aw, (unsigned)(k.p00.r | (k.p01.r << 8)), 0u);
-                        const int hr1 = (int)__dp2a_lo(aw, (unsigned)(k.p10.r | (k.p11.r << 8)), 0u);
-                        px.b = clamp_u8((((b0 * (hb0 >> 4)) >> 16) + ((b1 * (hb1 >> 4)) >> 16) + 2) >> 2);
-                        px.g = clamp_u8((((b0 * (hg0 >> 4)) >> 16) + ((b1 * (hg1 >> 4)) >> 16) + 2) >> 2);
-                        px.r = clamp_u8((((b0 * (hr0 >> 4)) >> 16) + ((b1 * (hr1 >> 4)) >> 16) + 2) >> 2);
-                    }
-                    if (color_enable == 2)
-                    {
-                        px.b = clamp_u8(__float2int_rn((float)px.b * cs0));
-                        px.g = clamp_u8(__float2int_rn((float)px.g * cs1));
-                        px.r = clamp_u8(__float2int_rn((float)px.r * cs2));
-                    }
-                    else if (color_enable)
-                    {
-                        const int b  = (px.b * m0 + px.g * m1 + px.r * m2 + 512) >> 10;
-                        const int g  = (px.b * m3 + px.g * m4 + px.r * m5 + 512) >> 10;
-                        const int rr = (px.b * m6 + px.g * m7 + px.r * m8 + 512) >> 10;
-                        px.b = clamp_u8(b);
-                        px.g = clamp_u8(g);
-                        px.r = clamp_u8(rr);
-                    }
-                    if (use_hue)
-                        px = hue_rotate(px, hue, k.x < hsv_cols, hsv_sdiv, hsv_hdiv);
+                        if (color_enable == 2)
+                        {
+                            px.b = clamp_u8(__float2int_rn((float)px.b * cs0));
+                            px.g = clamp_u8(__float2int_rn((float)px.g * cs1));
+                            px.r = clamp_u8(__float2int_rn((float)px.r * cs2));
+                        }
+                        else if (color_enable)
+                        {
+                            const int b  = (px.b * m0 + px.g * m1 + px.r * m2 + 512) >> 10;
+                            const int g  = (px.b * m3 + px.g * m4 + px.r * m5 + 512) >> 10;
+                            const int rr = (px.b * m6 + px.g * m7 + px.r * m8 + 512) >> 10;
+                            px.b = clamp_u8(b);
+                            px.g = clamp_u8(g);
+                            px.r = clamp_u8(rr);
+                        }
+                        if (use_hue)
+                            px = hue_rotate(px, k.x < hsv_cols, hue_tab);
 
-                    const int xo_t = flip ? out_w - 1 - k.x : k.x;
-                    const int c0   = swap_rb ? px.r : px.b;
-                    const int c2   = swap_rb ? px.b : px.r;
-                    unsigned char* o = tile + k.r * pitch + xo_t;
-                    o[0]             = (unsigned char)c0;
-                    o[plane]         = (unsigned char)px.g;
-                    o[2 * plane]     = (unsigned char)c2;
-                    sum0 += c0;
-                    sum1 += px.g;
-                    sum2 += c2;
-                };
-                // two units in flight per warp: the loads of the second overlap the arithmetic of the first.
-                // Unit u = (row, 32-pixel segment); the warp steps through its units without dividing.
-                // (nseg >= 1 here; the wrap loop is bounded by the step because each wrap removes at least 1.)
-                auto advance = [&](int& r, int& seg, int by) {
-                    seg += by;
-                    for (int it = 0; it < 2 * WARPS && seg >= nseg; ++it)
+                        const int xo_t = flip ? out_w - 1 - k.x : k.x;
+                        const int c0   = swap_rb ? px.r : px.b;
+                        const int c2   = swap_rb ? px.b : px.r;
+                        unsigned char* o = tile + k.r * pitch + xo_t;
+                        o[0]             = (unsigned char)c0;
+                        o[plane]         = (unsigned char)px.g;
+                        o[2 * plane]     = (unsigned char)c2;
+                        sum0 += c0;
+                        sum1 += px.g;
+                        sum2 += c2;
+                    };
+                    // two units in flight per warp: the loads of the second overlap the arithmetic of the first.
+                    // Unit u = (row, 32-pixel segment); the warp steps through its units without dividing.
+                    // (nseg >= 1 here; the wrap loop is bounded by the step because each wrap removes at least 1.)
+                    auto advance = [&](int& r, int& seg, int by) {
+                        seg += by;
+                        for (int it = 0; it < 2 * WARPS && seg >= nseg; ++it)
+                        {
+                            seg -= nseg;
+                            ++r;
+                        }
+                    };
+                    int ra = 0, sa = 0;
+                    advance(ra, sa, warp);
+                    int rb = ra, sb = sa;
+                    advance(rb, sb, WARPS);
+                    (void)units;
+                    // an empty image (zero-filled slot) has no units at all
+                    for (int guard = 0; nseg > 0 && ra < rows && guard < units; ++guard)
                     {
-                        seg -= nseg;
-                        ++r;
+                        const taps ka = load_unit(ra, sa);
+                        const taps kb = load_unit(rb, sb);
+                        finish_unit(ka);
+                        finish_unit(kb);
+                        advance(ra, sa, 2 * WARPS);
+                        advance(rb, sb, 2 * WARPS);
                     }
-                };
-                int ra = 0, sa = 0;
-                advance(ra, sa, warp);
-                int rb = ra, sb = sa;
-                advance(rb, sb, WARPS);
-                (void)units;
-                // an empty image (zero-filled slot) has no units at all
-                for (int guard = 0; nseg > 0 && ra < rows && guard < units; ++guard)
-                {
-                    const taps ka = load_unit(ra, sa);
-                    const taps kb = load_unit(rb, sb);
-                    finish_unit(ka);
-                    finish_unit(kb);
-                    advance(ra, sa, 2 * WARPS);
-                    advance(rb, sb, 2 * WARPS);
                 }
-            }
 
-            // ---- per-image channel means for contrast, exchanged across the cluster
-            if (use_ctr)
-            {
-                sum0 = warp_sum(sum0);
-                sum1 = warp_sum(sum1);
-                sum2 = warp_sum(sum2);
-                if (lane == 0)
+                // ---- per-image channel means for contrast, exchanged across the cluster
+                if (use_ctr)
                 {
-                    atomicAdd(&part_sum[0], sum0);
-                    atomicAdd(&part_sum[1], sum1);
-                    atomicAdd(&part_sum[2], sum2);
+                    sum0 = warp_sum(sum0);
+                    sum1 = warp_sum(sum1);
+                    sum2 = warp_sum(sum2);
+                    if (lane == 0)
+                    {
+                        atomicAdd(&part_sum[0], sum0);
+                        atomicAdd(&part_sum[1], sum1);
+                        atomicAdd(&part_sum[2], sum2);
+                    }
+                    cluster.sync(); // all partial sums of the record are in place (also a CTA barrier)
+                    if (tid < 3)
+                    {
+                        unsigned long long total = 0;
+                        for (int b = 0; b < bands; ++b)
+                            total += *cluster.map_shared_rank(&part_sum[tid], b);
+                        const double mean = (double)total / (double)((long long)out_w * out_h);
+                        contrast_add[tid] = (float)((1.0 - (double)d.contrast) * mean);
+                    }
+                    cluster.sync(); // remote reads done before any CTA of the cluster may exit
                 }
-                cluster.sync(); // all partial sums of the record are in place (also a CTA barrier)
-                if (tid < 3)
+                else
                 {
-                    unsigned long long total = 0;
-                    for (int b = 0; b < bands; ++b)
-                        total += *cluster.map_shared_rank(&part_sum[tid], b);
-                    const double mean = (double)total / (double)((long long)out_w * out_h);
-                    contrast_add[tid] = (float)((1.0 - (double)d.contrast) * mean);
+                    __syncthreads();
                 }
-                cluster.sync(); // remote reads done before any CTA of the cluster may exit
-            }
-            else
-            {
+
+                // ---- value map: contrast, lighting, conversion, standardisation
+                for (int i = tid; i < 768; i += AUG_THREADS)
+                {
+                    const int c   = i >> 8;
+                    const int cin = swap_rb ? 2 - c : c; // channel index in BGR order
+                    lut[c][i & 255] = final_value<T>(i & 255, c, cin, d, lay, use_ctr, use_ctr ? contrast_add[c] : 0.f);
+                }
                 __syncthreads();
-            }
 
-            // ---- value map: contrast, lighting, conversion, standardisation
-            for (int i = tid; i < 768; i += AUG_THREADS)
-            {
-                const int c   = i >> 8;
-                const int cin = swap_rb ? 2 - c : c; // channel index in BGR order
-                lut[c][i & 255] = final_value<T>(i & 255, c, cin, d, lay, use_ctr, use_ctr ? contrast_add[c] : 0.f);
-            }
-            __syncthreads();
-
-            // ---- store: a warp takes one (channel, row) line at a time, lanes take 16-byte chunks
-            {
-                constexpr int VEC    = out_vec<T>::N;
-                const int     rows   = row_end - row0;
-                const int     chunks = (lay.slot_w + VEC - 1) / VEC;
-                T*            dst    = reinterpret_cast<T*>(d.dst);
-                const T       zero   = convert_out<T>(0);
-                for (int line = warp; line < 3 * rows; line += WARPS)
+                // ---- store: a warp takes one (channel, row) line at a time, lanes take 16-byte chunks
                 {
-                    const int  c      = (line >= rows) + (line >= 2 * rows);
-                    const int  r      = line - c * rows;
-                    const int  y      = row0 + r;
-                    const bool row_in = y < out_h;
-                    const unsigned char* src = tile + c * plane + r * pitch;
-                    T*                   g0  = dst + (int64_t)c * lay.stride_c + (int64_t)y * lay.stride_y;
-                    for (int chunk = lane; chunk < chunks; chunk += 32)
+                    constexpr int VEC    = out_vec<T>::N;
+                    const int     rows   = row_end - row0;
+                    const int     chunks = (lay.slot_w + VEC - 1) / VEC;
+                    T*            dst    = reinterpret_cast<T*>(d.dst);
+                    const T       zero   = convert_out<T>(0);
+                    for (int line = warp; line < 3 * rows; line += WARPS)
                     {
-                        const int  x0 = chunk * VEC;
-                        out_vec<T> o;
-                        if (VEC == 4)
+                        const int  c      = (line >= rows) + (line >= 2 * rows);
+                        const int  r      = line - c * rows;
+                        const int  y      = row0 + r;
+                        const bool row_in = y < out_h;
+                        const unsigned char* src = tile + c * plane + r * pitch;
+                        T*                   g0  = dst + (int64_t)c * lay.stride_c + (int64_t)y * lay.stride_y;
+                        for (int chunk = lane; chunk < chunks; chunk += 32)
                         {
-                            const uint32_t v4 = *reinterpret_cast<const uint32_t*>(src + x0);
-#pragma unroll
-                            for (int k = 0; k < VEC; ++k)
-                                o.v[k] = (row_in && x0 + k < out_w) ? lut[c][(v4 >> (8 * k)) & 0xFF] : zero;
+                            const int  x0 = chunk * VEC;
+                            out_vec<T> o;
+                            if (VEC == 4)
+                            {
+                                const uint32_t v4 = *reinterpret_cast<const uint32_t*>(src + x0);
+    #pragma unroll
+                                for (int k = 0; k < VEC; ++k)
+                                    o.v[k] = (row_in && x0 + k < out_w) ? lut[c][(v4 >> (8 * k)) & 0xFF] : zero;
+                            }
+                            else
+                            {
+    #pragma unroll
+                                for (int k = 0; k < VEC; ++k)
+                                    o.v[k] = (row_in && x0 + k < out_w) ? lut[c][src[x0 + k]] : zero;
+                            }
+                            T* g = g0 + (int64_t)x0 * lay.stride_x;
+                            if (L.vector_ok && x0 + VEC <= lay.slot_w)
+                                *reinterpret_cast<int4*>(g) = *reinterpret_cast<const int4*>(o.v);
+                            else
+                                for (int k = 0; k < VEC && x0 + k < lay.slot_w; ++k)
+                                    g[(int64_t)k * lay.stride_x] = o.v[k];
                         }
-                        else
-                        {
-#pragma unroll
-                            for (int k = 0; k < VEC; ++k)
-                                o.v[k] = (row_in && x0 + k < out_w) ? lut[c][src[x0 + k]] : zero;
-                        }
-                        T* g = g0 + (int64_t)x0 * lay.stride_x;
-                        if (L.vector_ok && x0 + VEC <= lay.slot_w)
-                            *reinterpret_cast<int4*>(g) = *reinterpret_cast<const int4*>(o.v);
-                        else
-                            for (int k = 0; k < VEC && x0 + k < lay.slot_w; ++k)
-                                g[(int64_t)k * lay.stride_x] = o.v[k];
                     }
                 }
+        
+                __syncthreads(); // the next record reuses the descriptor, the tables and the tile
             }
         }
 
         template <typename T>
-        cudaError_t launch_typed(const aug_launch& L, int n, int bands, size_t smem, int pix, cudaStream_t stream)
+        cudaError_t launch_typed(const aug_launch& L, int clusters, int bands, size_t smem, int pix, cudaStream_t stream)
         {
             auto kern = pix == 4 ? aug_pack_kernel<T, 4> : aug_pack_kernel<T, 3>;
             cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (err != cudaSuccess)
                 return err;
             cudaLaunchConfig_t cfg = {};
-            cfg.gridDim            = dim3(bands, n, 1);
+            cfg.gridDim            = dim3(bands, clusters, 1);
             cfg.blockDim           = dim3(AUG_THREADS, 1, 1);
             cfg.dynamicSmemBytes   = smem;
             cfg.stream             = stream;
@@ -585,6 +617,7 @@ namespace aeonb
         L.tile_pitch    = (layout.slot_w + 15) / 16 * 16;
         const size_t elem = layout.dtype == AEONB_F64 ? 8 : layout.dtype == AEONB_F32 || layout.dtype == AEONB_I32 ? 4
                           : layout.dtype == AEONB_I16 || layout.dtype == AEONB_U16 ? 2 : 1;
+        L.n         = n;
         L.vector_ok = slots_aligned && layout.stride_x == 1 && (layout.stride_y * elem) % 16 == 0 &&
                       (layout.stride_c * elem) % 16 == 0;
         const size_t smem = (size_t)3 * L.rows_per_band * L.tile_pitch + (size_t)layout.slot_w * (sizeof(int2) + sizeof(short2)) +
@@ -594,15 +627,19 @@ namespace aeonb
             *why = "output image too large for the on-chip band tile (rows/8 * width * 3 must stay under 200 KB)";
             return cudaErrorInvalidValue;
         }
+        // One cluster per record.  (The kernel can also run as fewer, persistent clusters that loop over records;
+        // measured on B200 that was slower -- 0.228 ms against 0.181 ms for 256 records -- because records differ in
+        // cost and the hardware's own dispatch balances them better than a static round-robin.)
+        const int clusters = n;
         switch (layout.dtype)
         {
-        case AEONB_U8: return launch_typed<uint8_t>(L, n, bands, smem, pixel_stride, stream);
-        case AEONB_I8: return launch_typed<int8_t>(L, n, bands, smem, pixel_stride, stream);
-        case AEONB_I16: return launch_typed<int16_t>(L, n, bands, smem, pixel_stride, stream);
-        case AEONB_U16: return launch_typed<uint16_t>(L, n, bands, smem, pixel_stride, stream);
-        case AEONB_I32: return launch_typed<int32_t>(L, n, bands, smem, pixel_stride, stream);
-        case AEONB_F32: return launch_typed<float>(L, n, bands, smem, pixel_stride, stream);
-        case AEONB_F64: return launch_typed<double>(L, n, bands, smem, pixel_stride, stream);
+        case AEONB_U8: return launch_typed<uint8_t>(L, clusters, bands, smem, pixel_stride, stream);
+        case AEONB_I8: return launch_typed<int8_t>(L, clusters, bands, smem, pixel_stride, stream);
+        case AEONB_I16: return launch_typed<int16_t>(L, clusters, bands, smem, pixel_stride, stream);
+        case AEONB_U16: return launch_typed<uint16_t>(L, clusters, bands, smem, pixel_stride, stream);
+        case AEONB_I32: return launch_typed<int32_t>(L, clusters, bands, smem, pixel_stride, stream);
+        case AEONB_F32: return launch_typed<float>(L, clusters, bands, smem, pixel_stride, stream);
+        case AEONB_F64: return launch_typed<double>(L, clusters, bands, smem, pixel_stride, stream);
         }
         *why = "unknown output dtype";
         return cudaErrorInvalidValue;

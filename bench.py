@@ -174,6 +174,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--stages", default="all",
                     help="kernels-only experiments: comma list of photometric stages to keep (matrix,hue,contrast,lighting) or 'all'/'none'")
+    ap.add_argument("--null-source", action="store_true", help="kernels-only experiment: image kernel without sources (store path only)")
     ap.add_argument("--full-decode", action="store_true", help="decode whole pictures instead of the crop regions")
     ap.add_argument("--kernels-only", action="store_true",
                     help="time the resident-input kernels only (used for profiler captures; e2e and cpu_baseline are null)")
@@ -276,6 +277,8 @@ def main():
                 float(p[i, 11]) if "matrix" in st_on else 1.0, int(p[i, 8]) if "hue" in st_on else 0,
                 light if "lighting" in st_on else None, float(p[i, 15])))
             e.dst = out.data_ptr() + i * 3 * OUT * OUT * 4
+            if args.null_source:
+                e.src = None
         batches.append((jd, idesc))
     torch.cuda.synchronize()
     jpeg_bytes_alg = [int(lib.aeonb_jpeg_backend_bytes(jd, BATCH)) for jd, _ in batches]
