@@ -50,6 +50,16 @@ class JpegDesc(C.Structure):
     ]
 
 
+class EntropyDesc(C.Structure):
+    _fields_ = [
+        ("scan", C.c_void_p), ("scan_size", C.c_uint32), ("ncomp", C.c_int32), ("tables", C.c_void_p),
+        ("hs", C.c_int32 * 3), ("vs", C.c_int32 * 3), ("dc_table", C.c_int32 * 3), ("ac_table", C.c_int32 * 3),
+        ("mcux", C.c_int32), ("mcuy", C.c_int32), ("roi", C.c_int32 * 4), ("restart_interval", C.c_int32),
+        ("reserved0", C.c_int32), ("coef", C.c_void_p * 3), ("status", C.c_void_p),
+        ("scratch", C.c_void_p), ("scratch_bytes", C.c_uint64),
+    ]
+
+
 class JpegInfo(C.Structure):
     _fields_ = [
         ("width", C.c_int32), ("height", C.c_int32), ("ncomp", C.c_int32),
@@ -81,6 +91,10 @@ PROTOTYPES = {
     "aeonb_image_batch_noalloc": (C.c_int, [C.POINTER(ImageDesc), C.c_int, C.POINTER(ImageLayout), C.c_void_p]),
     "aeonb_jpeg_backend_batch": (C.c_int, [C.c_void_p, C.POINTER(JpegDesc), C.c_int]),
     "aeonb_jpeg_backend_bytes": (C.c_int64, [C.POINTER(JpegDesc), C.c_int]),
+    "aeonb_jpeg_entropy_batch": (C.c_int, [C.c_void_p, C.POINTER(EntropyDesc), C.c_int]),
+    "aeonb_jpeg_entropy_scratch_bytes": (C.c_int64, [C.POINTER(EntropyDesc)]),
+    "aeonb_jpeg_entropy_prepare": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(JpegInfo), C.POINTER(C.c_uint16),
+                                             C.POINTER(C.c_uint8), C.POINTER(EntropyDesc), C.POINTER(C.c_size_t)]),
     "aeonb_specgram_batch": (C.c_int, [C.c_void_p, C.POINTER(SpecgramDesc), C.c_int, C.POINTER(SpecgramConfig)]),
     "aeonb_specgram_bytes": (C.c_int64, [C.POINTER(SpecgramDesc), C.c_int, C.POINTER(SpecgramConfig)]),
     "aeonb_jpeg_parse": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(JpegInfo)]),

@@ -327,6 +327,57 @@ int aeonb_jpeg_backend_batch(aeonb_ctx* ctx, const aeonb_jpeg_desc* descs, int n
     });
 }
 
+int aeonb_jpeg_entropy_batch(aeonb_ctx* ctx, const aeonb_entropy_desc* descs, int n)
+{
+    return guarded([&]() {
+        if (!ctx || (n > 0 && !descs))
+            throw std::invalid_argument("aeonb_jpeg_entropy_batch: NULL argument");
+        if (n <= 0)
+            return AEONB_OK;
+        bool any_parallel = false, any_serial = false;
+        for (int i = 0; i < n; ++i)
+        {
+            const aeonb_entropy_desc& r = descs[i];
+            std::ostringstream        ss;
+            if (!r.scan || !r.tables || r.ncomp < 1 || r.ncomp > 3 || r.mcux <= 0 || r.mcuy <= 0)
+                ss << "record " << i << ": NULL stream or tables, or an empty picture";
+            else if (r.roi[0] < 0 || r.roi[1] < 0 || r.roi[2] > r.mcux || r.roi[3] > r.mcuy || r.roi[0] >= r.roi[2] || r.roi[1] >= r.roi[3])
+                ss << "record " << i << ": region outside the picture";
+            else if (r.restart_interval < 0)
+                ss << "record " << i << ": negative restart interval";
+            else
+                for (int c = 0; c < r.ncomp; ++c)
+                {
+                    if (!r.coef[c] || ((uintptr_t)r.coef[c] & 15))
+                        ss << "record " << i << ": coefficient planes must be 16-byte aligned device pointers";
+                    else if (r.hs[c] < 1 || r.hs[c] > 4 || r.vs[c] < 1 || r.vs[c] > 4 || (r.dc_table[c] & ~1) || (r.ac_table[c] & ~1))
+                        ss << "record " << i << ": sampling factors must be 1..4 and table slots 0 or 1";
+                }
+            if (ss.str().empty() && r.scratch && (((uintptr_t)r.scratch & 15) || (int64_t)r.scratch_bytes < jpeg_entropy_scratch_bytes(r)))
+                ss << "record " << i << ": the work area must be 16-byte aligned and hold aeonb_jpeg_entropy_scratch_bytes() bytes";
+            const std::string msg = ss.str();
+            if (!msg.empty())
+                throw std::invalid_argument(msg);
+            if (r.scratch && r.restart_interval == 0)
+                any_parallel = true;
+            else
+                any_serial = true;
+        }
+        AEONB_CUDA(cudaSetDevice(ctx->device));
+        auto* ddev = static_cast<const aeonb_entropy_desc*>(ctx->upload(descs, sizeof(aeonb_entropy_desc) * n));
+        cudaError_t e = launch_jpeg_entropy(ddev, n, any_parallel, any_serial, jpeg_entropy_min_segment(), ctx->stream);
+        if (e != cudaSuccess)
+            throw error(AEONB_ERR_CUDA, cuda_message("jpeg entropy kernel launch", e));
+        ctx->launches += (any_parallel ? 1 : 0) + (any_serial ? 1 : 0);
+        return AEONB_OK;
+    });
+}
+
+int64_t aeonb_jpeg_entropy_scratch_bytes(const aeonb_entropy_desc* desc)
+{
+    return desc ? jpeg_entropy_scratch_bytes(*desc) : 0;
+}
+
 int64_t aeonb_jpeg_backend_bytes(const aeonb_jpeg_desc* descs, int n)
 {
     int64_t total = 0;

@@ -493,6 +493,60 @@ namespace aeonb
             }
         }
     }
+
+    bool jpeg_entropy_prepare(const jpeg_frame& f, uint8_t tables[4 * 272], aeonb_entropy_desc& d)
+    {
+        std::memset(tables, 0, 4 * 272);
+        d                     = aeonb_entropy_desc{};
+        const aeonb_jpeg_info& in = f.info;
+        int dc_ids[2] = {-1, -1}, ac_ids[2] = {-1, -1};
+        auto slot_of = [](int ids[2], int id) {
+            for (int s = 0; s < 2; ++s)
+            {
+                if (ids[s] == id)
+                    return s;
+                if (ids[s] < 0)
+                {
+                    ids[s] = id;
+                    return s;
+                }
+            }
+            return -1;
+        };
+        for (int c = 0; c < in.ncomp; ++c)
+        {
+            const int ds = slot_of(dc_ids, f.dc_table[c]), as = slot_of(ac_ids, f.ac_table[c]);
+            if (ds < 0 || as < 0)
+                return false;
+            d.dc_table[c] = ds;
+            d.ac_table[c] = as;
+            d.hs[c]       = in.hs[c];
+            d.vs[c]       = in.vs[c];
+        }
+        for (int s = 0; s < 2; ++s)
+        {
+            if (dc_ids[s] >= 0)
+            {
+                std::memcpy(tables + s * 272, f.dc[dc_ids[s]].bits + 1, 16);
+                std::memcpy(tables + s * 272 + 16, f.dc[dc_ids[s]].vals, 256);
+            }
+            if (ac_ids[s] >= 0)
+            {
+                std::memcpy(tables + (2 + s) * 272, f.ac[ac_ids[s]].bits + 1, 16);
+                std::memcpy(tables + (2 + s) * 272 + 16, f.ac[ac_ids[s]].vals, 256);
+            }
+        }
+        d.ncomp            = in.ncomp;
+        d.scan_size        = static_cast<uint32_t>(f.scan_size);
+        d.mcux             = in.blocks_w[0] / in.hs[0];
+        d.mcuy             = in.blocks_h[0] / in.vs[0];
+        d.roi[0]           = 0;
+        d.roi[1]           = 0;
+        d.roi[2]           = d.mcux;
+        d.roi[3]           = d.mcuy;
+        d.restart_interval = f.restart_interval;
+        return true;
+    }
 }
 
 using namespace aeonb;
@@ -543,6 +597,23 @@ int aeonb_jpeg_entropy_decode_roi(const void* data, size_t size, const int32_t r
         }
         jpeg_roi r{roi[0], roi[1], roi[2], roi[3]};
         jpeg_entropy_decode(f, coef, &r);
+        return AEONB_OK;
+    });
+}
+
+int aeonb_jpeg_entropy_prepare(const void* data, size_t size, aeonb_jpeg_info* info, uint16_t quant[192], uint8_t tables[1088],
+                               aeonb_entropy_desc* desc, size_t* scan_offset)
+{
+    return guarded([&]() {
+        if (!data || !info || !quant || !tables || !desc || !scan_offset)
+            throw std::invalid_argument("aeonb_jpeg_entropy_prepare: NULL argument");
+        jpeg_frame f;
+        jpeg_parse(data, size, f);
+        if (!jpeg_entropy_prepare(f, tables, *desc))
+            throw error(AEONB_ERR_UNSUPPORTED, "the scan uses more than two DC or two AC Huffman tables");
+        *info = f.info;
+        std::memcpy(quant, f.quant, sizeof f.quant);
+        *scan_offset = static_cast<size_t>(f.scan - static_cast<const uint8_t*>(data));
         return AEONB_OK;
     });
 }

@@ -52,4 +52,10 @@ namespace aeonb
     // Entropy-decodes the scan.  Without a region coef[c] must hold info.coef_count[c] int16 values; with
     // one, the compact plane described above.  The planes are fully overwritten (absent coefficients are zero).
     void jpeg_entropy_decode(const jpeg_frame& frame, int16_t* const coef[3], const jpeg_roi* roi = nullptr);
+
+    // Prepares a parsed frame for the device entropy decoder: writes the four Huffman tables the scan uses in
+    // DHT form (4 x 272 bytes: DC slot 0, DC slot 1, AC slot 0, AC slot 1) and fills the shape fields of `desc`
+    // (ncomp, sampling, table slots, MCU counts, restart interval, scan_size; roi = whole picture).  Pointers are
+    // left NULL.  Returns false when the scan refers to more than two DC or two AC tables.
+    bool jpeg_entropy_prepare(const jpeg_frame& frame, uint8_t tables[4 * 272], aeonb_entropy_desc& desc);
 }

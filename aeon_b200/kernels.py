@@ -131,6 +131,54 @@ def jpeg_entropy_decode(data):
     return info, coefs[:info.ncomp], quants[:info.ncomp]
 
 
+def jpeg_entropy_decode_device(ctx, encoded, rois=None, parallel=True):
+    """Device entropy decode of JPEG byte strings: with `parallel` a thread block per stream (streams with
+    restart markers still take the one-warp serial kernel), without it the serial kernel for all.
+
+    Returns a list of (info, [coef planes as int16 tensors], quant uint16 numpy (3 x 64), status int) per
+    record; with `rois` (MCU rectangles) the planes are the compact region planes."""
+    dev = torch.device("cuda", ctx.device)
+    n = len(encoded)
+    descs = (L.EntropyDesc * n)()
+    status = torch.full((max(n, 1),), -1, dtype=torch.int32, device=dev)
+    keep, results = [], []
+    for i, data in enumerate(encoded):
+        info = L.JpegInfo()
+        quant = np.zeros(192, np.uint16)
+        tables = np.zeros(1088, np.uint8)
+        off = C.c_size_t()
+        buf = (C.c_char * len(data)).from_buffer_copy(data)
+        L.check(ctx.lib.aeonb_jpeg_entropy_prepare(buf, len(data), C.byref(info), quant.ctypes.data_as(C.POINTER(C.c_uint16)),
+                                                   tables.ctypes.data_as(C.POINTER(C.c_uint8)), C.byref(descs[i]),
+                                                   C.byref(off)))
+        d = descs[i]
+        scan = torch.from_numpy(np.frombuffer(data, np.uint8)[off.value:off.value + d.scan_size].copy()).to(dev)
+        tab = torch.from_numpy(tables).to(dev)
+        if rois is not None and rois[i] is not None:
+            for k in range(4):
+                d.roi[k] = int(rois[i][k])
+        planes = []
+        for c in range(info.ncomp):
+            nb = (d.roi[2] - d.roi[0]) * d.hs[c] * (d.roi[3] - d.roi[1]) * d.vs[c]
+            t = torch.full((nb * 64,), 0x5555, dtype=torch.int16, device=dev)
+            planes.append(t)
+            d.coef[c] = t.data_ptr()
+        d.scan, d.tables = scan.data_ptr(), tab.data_ptr()
+        d.status = status.data_ptr() + 4 * i
+        keep += [scan, tab]
+        if parallel:
+            nbytes = int(ctx.lib.aeonb_jpeg_entropy_scratch_bytes(C.byref(d)))
+            work = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+            keep.append(work)
+            d.scratch, d.scratch_bytes = work.data_ptr(), nbytes
+        results.append([info, planes, quant.reshape(3, 64)])
+    torch.cuda.synchronize(dev)
+    L.check(ctx.lib.aeonb_jpeg_entropy_batch(ctx.handle, descs, n))
+    ctx.synchronize()
+    st = status.cpu().numpy()
+    return [(info, planes, quant, int(st[i])) for i, (info, planes, quant) in enumerate(results)]
+
+
 def jpeg_decode_batch(ctx, encoded, pixel_stride=3):
     """Decode JPEG byte strings: host entropy decode, device back end.  Returns H x W x pixel_stride tensors."""
     dev = torch.device("cuda", ctx.device)

@@ -170,6 +170,39 @@ int aeonb_jpeg_backend_batch(aeonb_ctx* ctx, const aeonb_jpeg_desc* descs, int n
 int64_t aeonb_jpeg_backend_bytes(const aeonb_jpeg_desc* descs, int n);
 
 /* ------------------------------------------------------------------------------------------------
+ * 1b'. JPEG entropy decoding on the device: the Huffman stage of cv::imdecode
+ *      (src/etl_image.cpp:90), one warp per JPEG stream.  Fills the coefficient planes that
+ *      aeonb_jpeg_desc describes, so aeonb_jpeg_entropy_batch followed by aeonb_jpeg_backend_batch
+ *      decodes a batch of JPEG files without per-record host work beyond header parsing.
+ * ---------------------------------------------------------------------------------------------- */
+
+typedef struct aeonb_entropy_desc
+{
+    const uint8_t* scan;     /* device: entropy-coded bytes of the scan (after the SOS header) */
+    uint32_t scan_size;
+    int32_t  ncomp;
+    const uint8_t* tables;   /* device: 4 Huffman tables of 272 bytes each in DHT form (16 code counts, then the
+                                values, zero padded): DC slot 0, DC slot 1, AC slot 0, AC slot 1 */
+    int32_t hs[3], vs[3];    /* sampling factors */
+    int32_t dc_table[3], ac_table[3]; /* slot (0 or 1) used by each component */
+    int32_t mcux, mcuy;      /* picture size in MCUs */
+    int32_t roi[4];          /* MCU rectangle {mx0, my0, mx1, my1} to store; {0, 0, mcux, mcuy} for the whole picture */
+    int32_t restart_interval;/* MCUs between restart markers, 0 = none */
+    int32_t reserved0;
+    int16_t* coef[3];        /* device: compact planes of (mx1-mx0)*hs x (my1-my0)*vs blocks, layout as in aeonb_jpeg_desc,
+                                16-byte aligned */
+    int32_t* status;         /* device: set to 0 on success, 1 when the stream is malformed (may be NULL) */
+    void*    scratch;        /* device: work area of aeonb_jpeg_entropy_scratch_bytes() bytes, 16-byte aligned.  With it, a
+                                stream without restart markers is decoded by a whole thread block (speculative decoding
+                                of segments that synchronise on each other); without it (NULL), or with restart markers,
+                                by a single warp walking the stream serially */
+    uint64_t scratch_bytes;
+} aeonb_entropy_desc;
+
+int aeonb_jpeg_entropy_batch(aeonb_ctx* ctx, const aeonb_entropy_desc* descs, int n);
+int64_t aeonb_jpeg_entropy_scratch_bytes(const aeonb_entropy_desc* desc);
+
+/* ------------------------------------------------------------------------------------------------
  * 1c. Spectrogram kernel: framing + window + DFT magnitude + mel filter bank + log
  *     (specgram::wav_to_specgram / specgram_to_cepsgram, src/specgram.cpp:26-137).
  * ---------------------------------------------------------------------------------------------- */
@@ -222,6 +255,14 @@ int aeonb_jpeg_entropy_decode(const void* data, size_t size, int16_t* coef[3], u
  * (clipped to the picture), blocks_w/h = the compact plane sizes. */
 int aeonb_jpeg_roi_for_crop(const aeonb_jpeg_info* info, int crop_x, int crop_y, int crop_w, int crop_h, int32_t roi[4]);
 int aeonb_jpeg_entropy_decode_roi(const void* data, size_t size, const int32_t roi[4], int16_t* coef[3], uint16_t* quant[3]);
+
+/* Host side of aeonb_jpeg_entropy_batch: parses the headers of one JPEG file and fills `info`, the quantiser tables (3 x 64,
+ * column-major), the four Huffman tables in the 4 x 272-byte form aeonb_entropy_desc.tables wants, and every field
+ * of `desc` that does not depend on where the data will live (scan, tables, coef, status and roi are left for the
+ * caller; scan_offset tells where the scan starts inside `data`).  AEONB_ERR_UNSUPPORTED when the file uses more
+ * than two DC or two AC tables (decode such a file with aeonb_jpeg_entropy_decode). */
+int aeonb_jpeg_entropy_prepare(const void* data, size_t size, aeonb_jpeg_info* info, uint16_t quant[192], uint8_t tables[1088],
+                               aeonb_entropy_desc* desc, size_t* scan_offset);
 
 /* Draws augmentation parameters exactly as aeon's param_factory::make_params does
  * (src/augment_image.cpp:107-230) for `n` records whose decoded sizes are in_w/in_h,
