@@ -163,6 +163,13 @@ aeonb_provider::aeonb_provider(aeonb_ctx* c, const json& cfg) : ctx(c)
         pixel_stride = (int)cfg.find("scratch_pixel_stride")->as_int();
     if (cfg.contains("roi_decode"))
         roi_decode = cfg.find("roi_decode")->as_bool();
+    if (cfg.contains("entropy_decode"))
+    {
+        const std::string where = cfg.find("entropy_decode")->as_string();
+        if (where != "device" && where != "host")
+            throw std::invalid_argument("entropy_decode must be \"device\" or \"host\"");
+        device_entropy = where == "device";
+    }
     if (pixel_stride != 3 && pixel_stride != 4)
         throw std::invalid_argument("scratch_pixel_stride must be 3 or 4");
     int threads = cfg.contains("decode_threads") ? (int)cfg.find("decode_threads")->as_int() : default_worker_count();

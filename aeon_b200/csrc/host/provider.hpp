@@ -71,6 +71,14 @@ namespace aeonb
         bool           laid_out = false;
         int            rx = 0, ry = 0, rw = 0, rh = 0;
         int            roi_blocks_w[3]{}, roi_blocks_h[3]{};
+        // Device entropy decoding: the staging buffer then carries the quantiser tables, the Huffman tables and the
+        // scan bytes instead of coefficients; planes and the decoder's work area live in a device-only arena.
+        bool               on_device = false;
+        aeonb_entropy_desc edesc{};
+        uint8_t            tables[4 * 272]{};
+        size_t             tables_off = 0, scan_off = 0;
+        size_t             plane_dev_off[3]{};
+        size_t             scratch_off = 0, scratch_bytes = 0;
     };
 }
 
@@ -82,6 +90,7 @@ struct aeonb_provider
     uint32_t                             seed        = 0;
     bool                                 batch_major = true;
     bool                                 roi_decode  = true; // decode only the MCUs the crop box can touch
+    bool                                 device_entropy = true; // Huffman-decode on the GPU ("entropy_decode": "device" | "host")
     int                                  pixel_stride = 3;
     std::vector<aeonb::stage>            stages;
     std::vector<aeonb::output_info>      outputs;
@@ -93,6 +102,7 @@ struct aeonb_provider
 
     aeonb::pinned_buffer                 staging;      // coefficients / samples, host side
     aeonb::device_buffer                 staging_dev;
+    aeonb::device_buffer                 coef_dev;     // device entropy decoding: status words, coefficient planes, work areas
     aeonb::device_buffer                 pixels_dev;   // decoded pictures
     aeonb::device_buffer                 resized_dev;  // pictures after the resize_short pass
     std::vector<aeonb::device_buffer>    out_dev;      // per output, batch_size records
@@ -105,6 +115,9 @@ struct aeonb_provider
     cudaEvent_t m_uploaded          = nullptr; // every H2D copy of the last call has left host memory
     bool        m_uploaded_valid    = false;
     int64_t     m_ticket            = 0;       // number of batches submitted so far
+    aeonb::pinned_buffer m_status[k_events];   // per in-flight batch: the device entropy decoder's status words
+    int                  m_status_count[k_events] = {0, 0, 0, 0};
+    void                 check_entropy_status(int slot); // throws aeon's decode error if a stream was malformed
 
     int64_t h2d_bytes = 0, d2h_bytes = 0;
     int32_t launches  = 0;

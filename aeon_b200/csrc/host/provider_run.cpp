@@ -140,6 +140,17 @@ void aeonb_provider::wait_ticket(int64_t t)
         return; // its event slot was recycled, which only happens after the batch completed
     AEONB_CUDA(cudaSetDevice(ctx->device));
     AEONB_CUDA(cudaEventSynchronize(m_done[t % k_events]));
+    check_entropy_status((int)(t % k_events));
+}
+
+void aeonb_provider::check_entropy_status(int slot)
+{
+    const int32_t* status = static_cast<const int32_t*>(m_status[slot].p);
+    const int      count  = m_status_count[slot];
+    m_status_count[slot]  = 0;
+    for (int i = 0; i < count; ++i)
+        if (status[i] != 0)
+            throw error(AEONB_ERR_DECODE, "Decoding image failed due to invalid data in the image file. (entropy-coded data)");
 }
 
 void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, void* const* outs, bool on_device, bool wait)
@@ -177,7 +188,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     vector<vector<int>>              pre_job(nin);
     vector<vector<aeonb_specgram_desc>> sdescs(nin);
     vector<vector<size_t>>           sdesc_off(nin);
-    size_t stage_bytes = 0, pixel_bytes = 0;
+    size_t stage_bytes = 0, pixel_bytes = 0, coef_bytes = 0;
 
     for (size_t o = 0; o < outputs.size(); ++o)
         if (outputs[o].host_produced)
@@ -215,13 +226,40 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         size_t off    = align_up(stage_bytes, 256);
         job.stage_off = off;
         off += 3 * 64 * sizeof(uint16_t);
+        job.on_device = device_entropy && jpeg_entropy_prepare(job.frame, job.tables, job.edesc);
+        if (job.on_device)
+        {
+            job.tables_off = off;
+            off += sizeof job.tables;
+            job.scan_off = align_up(off, 16);
+            off          = job.scan_off + job.frame.scan_size;
+        }
         for (int c = 0; c < in.ncomp; ++c)
         {
             job.roi_blocks_w[c] = (roi.mx1 - roi.mx0) * in.hs[c];
             job.roi_blocks_h[c] = (roi.my1 - roi.my0) * in.vs[c];
-            off                 = align_up(off, 256);
-            job.plane_off[c]    = off;
-            off += (size_t)job.roi_blocks_w[c] * job.roi_blocks_h[c] * 64 * sizeof(int16_t);
+            const size_t bytes  = (size_t)job.roi_blocks_w[c] * job.roi_blocks_h[c] * 64 * sizeof(int16_t);
+            if (job.on_device)
+            {
+                job.plane_dev_off[c] = align_up(coef_bytes, 256);
+                coef_bytes           = job.plane_dev_off[c] + bytes;
+            }
+            else
+            {
+                off              = align_up(off, 256);
+                job.plane_off[c] = off;
+                off += bytes;
+            }
+        }
+        if (job.on_device)
+        {
+            job.edesc.roi[0]  = std::max(roi.mx0, 0);
+            job.edesc.roi[1]  = std::max(roi.my0, 0);
+            job.edesc.roi[2]  = std::min(roi.mx1, mcux);
+            job.edesc.roi[3]  = std::min(roi.my1, mcuy);
+            job.scratch_bytes = (size_t)jpeg_entropy_scratch_bytes(job.edesc);
+            job.scratch_off   = align_up(coef_bytes, 256);
+            coef_bytes        = job.scratch_off + job.scratch_bytes;
         }
         job.stage_bytes = off - job.stage_off;
         stage_bytes     = off;
@@ -428,6 +466,9 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     staging.reserve(stage_bytes + 256);
     staging_dev.reserve(stage_bytes + 256);
     pixels_dev.reserve(pixel_bytes + 256);
+    const size_t status_room = align_up(sizeof(int32_t) * (jobs.size() + 1), 256);
+    if (coef_bytes > 0)
+        coef_dev.reserve(status_room + coef_bytes + 256);
     vector<char*> produced(outputs.size(), nullptr); // where each device-produced output is written
     for (size_t o = 0; o < outputs.size(); ++o)
     {
@@ -470,6 +511,13 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                 {
                     jpeg_job& job = jobs[i];
                     std::memcpy(hstage + job.stage_off, job.frame.quant, sizeof job.frame.quant);
+                    if (job.on_device)
+                    {
+                        std::memcpy(hstage + job.tables_off, job.tables, sizeof job.tables);
+                        std::memcpy(hstage + job.scan_off, job.frame.scan, job.frame.scan_size);
+                        remaining[group_of(i)].fetch_sub(1, std::memory_order_release);
+                        return;
+                    }
                     int16_t* planes[3] = {reinterpret_cast<int16_t*>(hstage + job.plane_off[0]),
                                           reinterpret_cast<int16_t*>(hstage + job.plane_off[1]),
                                           reinterpret_cast<int16_t*>(hstage + job.plane_off[2])};
@@ -509,8 +557,32 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     }
 
     // ---- 4. kernels
+    int n_device_jobs = 0;
     if (njobs > 0)
     {
+        char* const cdev = static_cast<char*>(coef_dev.p);
+        vector<aeonb_entropy_desc> ed;
+        for (int i = 0; i < njobs; ++i)
+        {
+            const jpeg_job& job = jobs[i];
+            if (!job.on_device)
+                continue;
+            aeonb_entropy_desc d = job.edesc;
+            d.scan               = reinterpret_cast<const uint8_t*>(dstage + job.scan_off);
+            d.tables             = reinterpret_cast<const uint8_t*>(dstage + job.tables_off);
+            for (int c = 0; c < job.frame.info.ncomp; ++c)
+                d.coef[c] = reinterpret_cast<int16_t*>(cdev + status_room + job.plane_dev_off[c]);
+            d.scratch       = cdev + status_room + job.scratch_off;
+            d.scratch_bytes = job.scratch_bytes;
+            d.status        = reinterpret_cast<int32_t*>(cdev) + ed.size();
+            ed.push_back(d);
+        }
+        n_device_jobs = (int)ed.size();
+        if (n_device_jobs > 0)
+        {
+            check_status(aeonb_jpeg_entropy_batch(ctx, ed.data(), n_device_jobs));
+            h2d_bytes += (int64_t)(sizeof(aeonb_entropy_desc) * n_device_jobs);
+        }
         vector<aeonb_jpeg_desc> jd(njobs);
         for (int i = 0; i < njobs; ++i)
         {
@@ -522,7 +594,8 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
             d.ncomp  = in.ncomp;
             for (int c = 0; c < in.ncomp; ++c)
             {
-                d.coef[c]     = reinterpret_cast<const int16_t*>(dstage + job.plane_off[c]);
+                d.coef[c]     = job.on_device ? reinterpret_cast<const int16_t*>(cdev + status_room + job.plane_dev_off[c])
+                                              : reinterpret_cast<const int16_t*>(dstage + job.plane_off[c]);
                 d.quant[c]    = reinterpret_cast<const uint16_t*>(dstage + job.stage_off) + 64 * c;
                 d.hs[c]       = in.hs[c];
                 d.vs[c]       = in.vs[c];
@@ -728,9 +801,21 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     ++m_ticket;
     // Recycling an event slot: the batch that used it (k_events submissions ago) is long complete on an
     // in-order stream once the newer batches between were waited for; synchronise to make that certain.
-    AEONB_CUDA(cudaEventSynchronize(m_done[m_ticket % k_events]));
-    AEONB_CUDA(cudaEventRecord(m_done[m_ticket % k_events], st));
+    const int slot = (int)(m_ticket % k_events);
+    AEONB_CUDA(cudaEventSynchronize(m_done[slot]));
+    m_status_count[slot] = 0;
+    if (n_device_jobs > 0)
+    {
+        m_status[slot].reserve(sizeof(int32_t) * n_device_jobs);
+        AEONB_CUDA(cudaMemcpyAsync(m_status[slot].p, coef_dev.p, sizeof(int32_t) * n_device_jobs, cudaMemcpyDeviceToHost, st));
+        d2h_bytes += (int64_t)(sizeof(int32_t) * n_device_jobs);
+        m_status_count[slot] = n_device_jobs;
+    }
+    AEONB_CUDA(cudaEventRecord(m_done[slot], st));
     if (wait)
+    {
         AEONB_CUDA(cudaStreamSynchronize(st));
+        check_entropy_status(slot);
+    }
     launches = (int32_t)(ctx->launches - launches_before);
 }

@@ -39,6 +39,10 @@ ETL = [{"type": "image", "height": OUT, "width": OUT, "channels": 3, "channel_ma
 WORKLOAD = "config2: 1024 synthetic q90 4:2:0 JPEGs (W,H~U[256,512]), random-area crop + flip + full photometric, 224x224x3 float32 CHW normalised, batch 256"
 
 
+# DRAM bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum) from the captures summarised under profiles/
+TRAFFIC = {"jpeg_backend": 188.8e6, "aug_pack": 153.9e6, "jpeg_entropy": None}
+
+
 def make_dataset(seed, n):
     """Seeded stand-in for ImageNet-shaped inputs: smooth gradients + uniform +-20 noise, JPEG q=90."""
     import cv2
@@ -176,6 +180,9 @@ def main():
                     help="kernels-only experiments: comma list of photometric stages to keep (matrix,hue,contrast,lighting) or 'all'/'none'")
     ap.add_argument("--null-source", action="store_true", help="kernels-only experiment: image kernel without sources (store path only)")
     ap.add_argument("--full-decode", action="store_true", help="decode whole pictures instead of the crop regions")
+    ap.add_argument("--entropy", default="device", choices=["device", "host"],
+                    help="where JPEG Huffman decoding runs: on the GPU (the timed step then starts from the compressed scans "
+                         "resident in HBM) or on the host (the timed step starts from coefficient planes resident in HBM)")
     ap.add_argument("--kernels-only", action="store_true",
                     help="time the resident-input kernels only (used for profiler captures; e2e and cpu_baseline are null)")
     args = ap.parse_args()
@@ -213,9 +220,13 @@ def main():
     recs = make_dataset(1001 + rank, N_IMAGES)  # each rank owns its shard of records
     n_batches = N_IMAGES // BATCH
 
-    # ---------------- resident inputs: entropy-decode once, keep coefficient planes in HBM
+    # ---------------- resident inputs.  --entropy device: the compressed scans, Huffman and quantiser tables sit in HBM and
+    # the step is entropy kernel -> JPEG back end -> image kernel.  --entropy host: the coefficient planes sit in HBM
+    # (decoded once on the host) and the step is the last two kernels.
     pix = args.pixel_stride
+    on_dev = args.entropy == "device"
     batches = []
+    check_plane = None
     with torch.cuda.stream(ctx.torch_stream):
         out = torch.empty((BATCH, 3, OUT, OUT), dtype=torch.float32, device=dev)
     layout = K.make_layout(OUT, OUT, L.F32, True, True, MEAN, STD)
@@ -223,6 +234,10 @@ def main():
     for b in range(n_batches):
         jd = (L.JpegDesc * BATCH)()
         idesc = (L.ImageDesc * BATCH)()
+        ed = (L.EntropyDesc * BATCH)()
+        status = torch.zeros(BATCH, dtype=torch.int32, device=dev)
+        keep.append(status)
+        ent_bytes = 0
         ws = (C.c_int32 * BATCH)()
         hs = (C.c_int32 * BATCH)()
         infos = []
@@ -256,9 +271,29 @@ def main():
             qp = (C.c_void_p * 3)(*([q.ctypes.data for q in quants] + [None] * (3 - len(quants))))
             buf = (C.c_char * len(blob)).from_buffer_copy(blob)
             L.check(lib.aeonb_jpeg_entropy_decode_roi(buf, len(blob), roi, cp, qp))
+            if on_dev:
+                pinfo, pq, ptab, poff = L.JpegInfo(), np.zeros(192, np.uint16), np.zeros(1088, np.uint8), C.c_size_t()
+                L.check(lib.aeonb_jpeg_entropy_prepare(buf, len(blob), C.byref(pinfo), pq.ctypes.data_as(C.POINTER(C.c_uint16)),
+                                                       ptab.ctypes.data_as(C.POINTER(C.c_uint8)), C.byref(ed[i]), C.byref(poff)))
+                x = ed[i]
+                scan = torch.from_numpy(np.frombuffer(blob, np.uint8)[poff.value:poff.value + x.scan_size].copy()).to(dev)
+                tab = torch.from_numpy(ptab).to(dev)
+                work = torch.empty(int(lib.aeonb_jpeg_entropy_scratch_bytes(C.byref(x))), dtype=torch.uint8, device=dev)
+                keep += [scan, tab, work]
+                x.scan, x.tables, x.scratch, x.scratch_bytes = scan.data_ptr(), tab.data_ptr(), work.data_ptr(), work.numel()
+                x.status = status.data_ptr() + 4 * i
+                for k in range(4):
+                    x.roi[k] = roi[k]
+                ent_bytes += int(x.scan_size) + sum(c.nbytes for c in coefs)
             for c in range(info.ncomp):
-                ct = torch.from_numpy(coefs[c]).to(dev)
                 qt = torch.from_numpy(quants[c].view(np.int16)).to(dev)
+                if on_dev:   # the entropy kernel fills the plane every step; the host result is kept for one cross-check
+                    ct = torch.full((coefs[c].size,), 0x5555, dtype=torch.int16, device=dev)
+                    ed[i].coef[c] = ct.data_ptr()
+                    if check_plane is None:
+                        check_plane = (ct, coefs[c].copy())
+                else:
+                    ct = torch.from_numpy(coefs[c]).to(dev)
                 keep += [ct, qt]
                 d.coef[c], d.quant[c] = ct.data_ptr(), qt.data_ptr()
             pitch = (rw * pix + 15) // 16 * 16
@@ -279,15 +314,26 @@ def main():
             e.dst = out.data_ptr() + i * 3 * OUT * OUT * 4
             if args.null_source:
                 e.src = None
-        batches.append((jd, idesc))
+        batches.append((jd, idesc, ed, ent_bytes))
     torch.cuda.synchronize()
-    jpeg_bytes_alg = [int(lib.aeonb_jpeg_backend_bytes(jd, BATCH)) for jd, _ in batches]
-    aug_bytes_alg = [int(lib.aeonb_image_batch_bytes(idesc, BATCH, C.byref(layout))) for _, idesc in batches]
+    jpeg_bytes_alg = [int(lib.aeonb_jpeg_backend_bytes(b[0], BATCH)) for b in batches]
+    aug_bytes_alg = [int(lib.aeonb_image_batch_bytes(b[1], BATCH, C.byref(layout))) for b in batches]
+    ent_bytes_alg = [b[3] for b in batches]
 
     def kernel_step(b):
-        jd, idesc = batches[b % n_batches]
+        jd, idesc, ed, _ = batches[b % n_batches]
+        if on_dev:
+            L.check(lib.aeonb_jpeg_entropy_batch(ctx.handle, ed, BATCH))
         L.check(lib.aeonb_jpeg_backend_batch(ctx.handle, jd, BATCH))
         L.check(lib.aeonb_image_batch(ctx.handle, idesc, BATCH, C.byref(layout)))
+
+    if on_dev:   # one cross-check of the device decoder against the host decoder before anything is timed
+        kernel_step(0)
+        torch.cuda.synchronize()
+        if not np.array_equal(check_plane[0].cpu().numpy(), check_plane[1]):
+            raise SystemExit("device entropy decoder disagrees with the host decoder")
+        if keep[0].cpu().numpy().any():   # keep[0]: the first batch's status words
+            raise SystemExit("device entropy decoder flagged a stream of the synthetic set")
 
     def barrier():
         torch.cuda.synchronize()
@@ -309,23 +355,28 @@ def main():
     kernel_ms = ev[0].elapsed_time(ev[1])
 
     # per-kernel durations (same launches, events between the two kernels)
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     for i in range(args.steps):
-        jd, idesc = batches[i % n_batches]
+        jd, idesc, ed, _ = batches[i % n_batches]
         evs[i][0].record(ts)
-        L.check(lib.aeonb_jpeg_backend_batch(ctx.handle, jd, BATCH))
+        if on_dev:
+            L.check(lib.aeonb_jpeg_entropy_batch(ctx.handle, ed, BATCH))
         evs[i][1].record(ts)
-        L.check(lib.aeonb_image_batch(ctx.handle, idesc, BATCH, C.byref(layout)))
+        L.check(lib.aeonb_jpeg_backend_batch(ctx.handle, jd, BATCH))
         evs[i][2].record(ts)
+        L.check(lib.aeonb_image_batch(ctx.handle, idesc, BATCH, C.byref(layout)))
+        evs[i][3].record(ts)
     barrier()
-    jpeg_ms = float(np.mean([e[0].elapsed_time(e[1]) for e in evs]))
-    aug_ms = float(np.mean([e[1].elapsed_time(e[2]) for e in evs]))
+    ent_ms = float(np.mean([e[0].elapsed_time(e[1]) for e in evs])) if on_dev else 0.0
+    jpeg_ms = float(np.mean([e[1].elapsed_time(e[2]) for e in evs]))
+    aug_ms = float(np.mean([e[2].elapsed_time(e[3]) for e in evs]))
+    ent_alg = float(np.mean([ent_bytes_alg[i % n_batches] for i in range(args.steps)]))
     jpeg_alg = float(np.mean([jpeg_bytes_alg[i % n_batches] for i in range(args.steps)]))
     aug_alg = float(np.mean([aug_bytes_alg[i % n_batches] for i in range(args.steps)]))
 
     if args.kernels_only:
         if rank == 0:
-            print(json.dumps({"kernels_only": True, "ms_per_step": kernel_ms / args.steps, "jpeg_ms": jpeg_ms, "aug_ms": aug_ms,
+            print(json.dumps({"kernels_only": True, "ms_per_step": kernel_ms / args.steps, "entropy_ms": ent_ms, "jpeg_ms": jpeg_ms, "aug_ms": aug_ms,
                               "jpeg_gbs": jpeg_alg / jpeg_ms / 1e6, "aug_gbs": aug_alg / aug_ms / 1e6}), flush=True)
             sampler.stop()
         return
@@ -333,7 +384,7 @@ def main():
     # ---------------- end to end through the provider: encoded bytes in host memory -> batch in host memory
     threads = max(1, host_workers() // world)
     cfg = {"batch_size": BATCH, "random_seed": 1234, "etl": ETL, "augmentation": [AUG], "decode_threads": threads,
-           "scratch_pixel_stride": pix, "roi_decode": not args.full_decode}
+           "scratch_pixel_stride": pix, "roi_decode": not args.full_decode, "entropy_decode": args.entropy}
     prov = Provider(ctx, cfg)
     host_out = [{"image": torch.empty((BATCH, 3, OUT, OUT), dtype=torch.float32).pin_memory().numpy(),
                  "label": np.zeros((BATCH, 1), np.int32)} for _ in range(2)]
@@ -373,8 +424,11 @@ def main():
             pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
         peak_kind = "measured" if "hbm_gbs" in peaks else "fallback"
-        dominant = "jpeg_backend" if jpeg_ms >= aug_ms else "aug_pack"
-        d_ms, d_alg = (jpeg_ms, jpeg_alg) if dominant == "jpeg_backend" else (aug_ms, aug_alg)
+        per_kernel = {"jpeg_backend": (jpeg_ms, jpeg_alg), "aug_pack": (aug_ms, aug_alg)}
+        if on_dev:
+            per_kernel["jpeg_entropy"] = (ent_ms, ent_alg)
+        dominant = max(per_kernel, key=lambda k: per_kernel[k][0])
+        d_ms, d_alg = per_kernel[dominant]
         achieved = d_alg / (d_ms * 1e-3) / 1e9
         cpu_base = cpu_line["cpu_baseline"] if cpu_line else None
         value = world * BATCH * args.steps / (kernel_ms * 1e-3)
@@ -384,21 +438,21 @@ def main():
             "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
             "config": {"workload": WORKLOAD, "l2": "four distinct batches (1024 records) cycle; their inputs total several hundred MB, larger than the 126 MB L2",
                        "scratch_pixel_stride": pix, "records_per_gpu_per_step": BATCH,
-                       "decode": "whole pictures" if args.full_decode else "crop regions only (MCUs the crop box can touch)"},
+                       "decode": "whole pictures" if args.full_decode else "crop regions only (MCUs the crop box can touch)",
+                       "entropy_decode": args.entropy,
+                       "resident_input": "compressed JPEG scans + tables" if on_dev else "coefficient planes (Huffman-decoded on the host, untimed)"},
             "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_kind": peak_kind, "frac_of_8tbs_nominal": achieved / 8000.0,
                          # DRAM bytes per launch of that kernel from the ncu capture summarised under profiles/
-                         "traffic": {"jpeg_backend": 188.8e6, "aug_pack": 153.9e6}[dominant],
+                         "traffic": TRAFFIC.get(dominant),
                          "traffic_source": "profiles/%s_config2.md (ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch)" % dominant,
-                         "kernels": {"jpeg_backend": {"ms": jpeg_ms, "algorithmic_bytes": jpeg_alg,
-                                                      "gbs": jpeg_alg / (jpeg_ms * 1e-3) / 1e9},
-                                     "aug_pack": {"ms": aug_ms, "algorithmic_bytes": aug_alg,
-                                                  "gbs": aug_alg / (aug_ms * 1e-3) / 1e9}}},
+                         "kernels": {k: {"ms": v[0], "algorithmic_bytes": v[1], "gbs": v[1] / (v[0] * 1e-3) / 1e9,
+                                         "frac": v[1] / (v[0] * 1e-3) / 1e9 / peak} for k, v in per_kernel.items()}},
             "cpu_baseline": cpu_base,
             "e2e": {"value": world * BATCH * e2e_steps / (e2e_ms * 1e-3), "unit": "records/s",
                     "h2d_bytes_per_step": st["h2d_bytes"], "d2h_bytes_per_step": st["d2h_bytes"],
                     "steps": e2e_steps, "host_decode_threads_per_gpu": threads},
-            "gpu_launches": 2 * args.steps, "clocks": clocks,
+            "gpu_launches": (3 if on_dev else 2) * args.steps, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     prov.close()

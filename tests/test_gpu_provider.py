@@ -45,7 +45,8 @@ def test_config1_uint8_chw_two_batches_bit_exact(ctx):
         assert np.array_equal(got["image"], want["image"])
         assert np.array_equal(got["label"].astype(np.int64), want["label"].astype(np.int64))
     st = prov.stats()
-    assert st["launches"] == 2 and st["h2d_bytes"] > 0 and st["d2h_bytes"] == 16 * 3 * 224 * 224 + 0
+    # entropy kernel + JPEG back end + image kernel; the batch and one status word per stream come back
+    assert st["launches"] == 3 and st["h2d_bytes"] > 0 and st["d2h_bytes"] == 16 * 3 * 224 * 224 + 16 * 4
 
 
 def test_config2_photometric_float_device_and_host_outputs(ctx):
@@ -276,8 +277,35 @@ def test_region_decode_and_full_decode_give_identical_batches(ctx):
     cfg = {"batch_size": 16, "random_seed": 31,
            "etl": [{"type": "image", "height": 224, "width": 224, "output_type": "uint8_t"}], "augmentation": [AUG_C2 | {"mean": [], "stddev": []}]}
     recs = [(r[0],) for r in image_records(52, 16)]
-    a = make_provider(ctx, dict(cfg, roi_decode=True))
-    b = make_provider(ctx, dict(cfg, roi_decode=False))
+    a = make_provider(ctx, dict(cfg, roi_decode=True, entropy_decode="host"))
+    b = make_provider(ctx, dict(cfg, roi_decode=False, entropy_decode="host"))
     ga, gb = a.run_host(recs)["image"], b.run_host(recs)["image"]
     assert np.array_equal(ga, gb)
     assert a.stats()["h2d_bytes"] < 0.9 * b.stats()["h2d_bytes"]   # fewer coefficient bytes cross PCIe
+
+
+def test_device_and_host_entropy_decoding_give_identical_batches(ctx):
+    """"entropy_decode": "device" ships the compressed scans and Huffman-decodes on the GPU; "host" ships coefficients."""
+    cfg = {"batch_size": 16, "random_seed": 33,
+           "etl": [{"type": "image", "height": 224, "width": 224, "output_type": "uint8_t"}], "augmentation": [AUG_C2 | {"mean": [], "stddev": []}]}
+    recs = [(r[0],) for r in image_records(53, 16)]
+    for roi in (True, False):
+        a = make_provider(ctx, dict(cfg, entropy_decode="device", roi_decode=roi))
+        b = make_provider(ctx, dict(cfg, entropy_decode="host", roi_decode=roi))
+        ga, gb = a.run_host(recs)["image"], b.run_host(recs)["image"]
+        assert np.array_equal(ga, gb)
+        assert a.stats()["h2d_bytes"] < 0.5 * b.stats()["h2d_bytes"]   # compressed bytes instead of coefficients
+        assert a.stats()["launches"] == b.stats()["launches"] + 1
+
+
+def test_device_entropy_decoding_reports_malformed_streams(ctx):
+    cfg = {"batch_size": 2, "random_seed": 34, "entropy_decode": "device",
+           "etl": [{"type": "image", "height": 64, "width": 64, "output_type": "uint8_t"}], "augmentation": [{"type": "image"}]}
+    good = image_records(54, 1)[0][0]
+    sos = good.index(b"\xff\xda")
+    broken = good[:sos + 14 + 100] + b"\xff\xd9"      # scan cut short: the decoder runs out of blocks
+    p = make_provider(ctx, cfg)
+    with pytest.raises(Exception, match="Decoding image failed"):
+        p.run_host([(good,), (broken,)])
+    out = p.run_host([(good,), (good,)])["image"]      # the provider stays usable
+    assert np.array_equal(out[0], out[1])
