@@ -256,7 +256,10 @@ aeonb_provider::aeonb_provider(aeonb_ctx* c, const json& cfg) : ctx(c)
         }
         stages.push_back(std::move(st));
     }
-    out_dev.resize(outputs.size());
-    out_dev_t.resize(outputs.size());
+    for (int k = 0; k < 2; ++k)
+    {
+        out_dev[k].resize(outputs.size());
+        out_dev_t[k].resize(outputs.size());
+    }
     out_host.resize(outputs.size());
 }

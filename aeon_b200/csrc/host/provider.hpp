@@ -105,13 +105,17 @@ struct aeonb_provider
     aeonb::device_buffer                 coef_dev;     // device entropy decoding: status words, coefficient planes, work areas
     aeonb::device_buffer                 pixels_dev;   // decoded pictures
     aeonb::device_buffer                 resized_dev;  // pictures after the resize_short pass
-    std::vector<aeonb::device_buffer>    out_dev;      // per output, batch_size records
-    std::vector<aeonb::device_buffer>    out_dev_t;    // transposed copies (batch_major == false)
+    // Device-side outputs of batches delivered to host memory, double buffered: the copy of batch t to the host
+    // (on the copy stream) overlaps the kernels of batch t+1, which write the other set.
+    std::vector<aeonb::device_buffer>    out_dev[2];   // per output, batch_size records
+    std::vector<aeonb::device_buffer>    out_dev_t[2]; // transposed copies (batch_major == false)
     std::vector<std::vector<char>>       out_host;     // host-produced outputs
     aeonb::pinned_buffer                 small_pinned;
 
     static constexpr int k_events = 4;
     cudaEvent_t m_done[k_events]    = {nullptr, nullptr, nullptr, nullptr}; // batch t complete: m_done[t % k_events]
+    cudaEvent_t m_kernels[k_events] = {nullptr, nullptr, nullptr, nullptr}; // the kernels of batch t have finished
+    cudaStream_t m_copy             = nullptr; // device -> host copies of finished batches
     cudaEvent_t m_uploaded          = nullptr; // every H2D copy of the last call has left host memory
     bool        m_uploaded_valid    = false;
     int64_t     m_ticket            = 0;       // number of batches submitted so far

@@ -2,6 +2,8 @@
 #include <algorithm>
 #include <atomic>
 #include <chrono>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <sstream>
 #include <thread>
@@ -128,8 +130,16 @@ aeonb_provider::~aeonb_provider()
     for (cudaEvent_t e : m_done)
         if (e)
             cudaEventDestroy(e);
+    for (cudaEvent_t e : m_kernels)
+        if (e)
+            cudaEventDestroy(e);
     if (m_uploaded)
         cudaEventDestroy(m_uploaded);
+    if (m_copy)
+    {
+        cudaStreamSynchronize(m_copy);
+        cudaStreamDestroy(m_copy);
+    }
 }
 
 void aeonb_provider::wait_ticket(int64_t t)
@@ -159,6 +169,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         throw std::invalid_argument("aeonb_provider_run: NULL argument");
     if (n <= 0 || n > batch_size)
         throw std::invalid_argument("aeonb_provider_run: record count must be in [1, batch_size]");
+    const auto t_entry = std::chrono::steady_clock::now();
     AEONB_CUDA(cudaSetDevice(ctx->device));
     cudaStream_t  st  = ctx->stream;
     const int     nin = (int)stages.size();
@@ -167,7 +178,15 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         AEONB_CUDA(cudaEventCreateWithFlags(&m_uploaded, cudaEventDisableTiming));
         for (cudaEvent_t& e : m_done)
             AEONB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        for (cudaEvent_t& e : m_kernels)
+            AEONB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        AEONB_CUDA(cudaStreamCreateWithFlags(&m_copy, cudaStreamNonBlocking));
     }
+    // This batch is number m_ticket + 1.  Its device-side outputs use buffer set `par`, last used by batch
+    // m_ticket - 1, whose copy to the host may still be running on the copy stream: kernels wait for it.
+    const int par = (int)((m_ticket + 1) & 1);
+    if (!on_device && m_ticket >= 2)
+        AEONB_CUDA(cudaStreamWaitEvent(st, m_done[(m_ticket - 1) % k_events], 0));
     // The pinned staging buffers are reused: the previous call's uploads must have left host memory.
     if (m_uploaded_valid)
         AEONB_CUDA(cudaEventSynchronize(m_uploaded));
@@ -269,6 +288,16 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         job.laid_out    = true;
     };
 
+    // AEONB_TRACE=1 prints the host time of each phase of the call to stderr
+    static const bool trace = std::getenv("AEONB_TRACE") != nullptr;
+    auto              t_prev = t_entry;
+    double            t_phase[6] = {0, 0, 0, 0, 0, 0};
+    auto mark = [&](int k) {
+        const auto now = std::chrono::steady_clock::now();
+        t_phase[k]     = std::chrono::duration<double, std::milli>(now - t_prev).count();
+        t_prev         = now;
+    };
+    mark(0);
     // ---- 1. sequential planning pass (record order == RNG order)
     for (int r = 0; r < n; ++r)
     {
@@ -462,6 +491,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     }
     slot_cursor = (slot_cursor + n) % decode_size;
 
+    mark(1);
     // ---- 2. arenas
     staging.reserve(stage_bytes + 256);
     staging_dev.reserve(stage_bytes + 256);
@@ -479,13 +509,14 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
             produced[o] = static_cast<char*>(outs[o]);
         else
         {
-            out_dev[o].reserve(bytes);
-            produced[o] = static_cast<char*>(out_dev[o].p);
+            out_dev[par][o].reserve(bytes);
+            produced[o] = static_cast<char*>(out_dev[par][o].p);
         }
         if (!batch_major)
-            out_dev_t[o].reserve(bytes);
+            out_dev_t[par][o].reserve(bytes);
     }
 
+    mark(2);
     // ---- 3. entropy decode on the pool, shipping finished slices while the rest decode
     char* const hstage = static_cast<char*>(staging.p);
     char* const dstage = static_cast<char*>(staging_dev.p);
@@ -556,6 +587,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         AEONB_CUDA(copy_error);
     }
 
+    mark(3);
     // ---- 4. kernels
     int n_device_jobs = 0;
     if (njobs > 0)
@@ -733,6 +765,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         }
     }
 
+    mark(4);
     // ---- 5. deliver
     size_t small_total = 0;
     for (size_t o = 0; o < outputs.size(); ++o)
@@ -774,48 +807,65 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     // while the kernels and the output copies below are still running.
     AEONB_CUDA(cudaEventRecord(m_uploaded, st));
     m_uploaded_valid = true;
+    ++m_ticket;
+    // Recycling an event slot: the batch that used it (k_events submissions ago) is long complete once the
+    // newer batches between were waited for; synchronise to make that certain.
+    const int slot = (int)(m_ticket % k_events);
+    AEONB_CUDA(cudaEventSynchronize(m_done[slot]));
+    vector<void*> sources(outputs.size(), nullptr); // what is copied to the host, per device-produced output
     for (size_t o = 0; o < outputs.size(); ++o)
     {
         if (outputs[o].host_produced)
             continue;
-        const size_t  rec   = (size_t)outputs[o].shape.byte_size();
-        const int     esz   = (int)outputs[o].shape.otype.size;
-        const int64_t elems_per_rec = outputs[o].shape.element_count();
+        sources[o] = produced[o];
         if (!batch_major)
         {
-            void* target = on_device ? outs[o] : out_dev_t[o].p;
-            AEONB_CUDA(launch_transpose(produced[o], target, batch_size, elems_per_rec, esz, st));
+            void* target = on_device ? outs[o] : out_dev_t[par][o].p;
+            AEONB_CUDA(launch_transpose(produced[o], target, batch_size, outputs[o].shape.element_count(),
+                                        (int)outputs[o].shape.otype.size, st));
             ctx->launches++;
-            if (!on_device)
-            {
-                AEONB_CUDA(cudaMemcpyAsync(outs[o], target, rec * batch_size, cudaMemcpyDeviceToHost, st));
-                d2h_bytes += (int64_t)(rec * batch_size);
-            }
-        }
-        else if (!on_device)
-        {
-            AEONB_CUDA(cudaMemcpyAsync(outs[o], produced[o], rec * n, cudaMemcpyDeviceToHost, st));
-            d2h_bytes += (int64_t)(rec * n);
+            sources[o] = target;
         }
     }
-    ++m_ticket;
-    // Recycling an event slot: the batch that used it (k_events submissions ago) is long complete on an
-    // in-order stream once the newer batches between were waited for; synchronise to make that certain.
-    const int slot = (int)(m_ticket % k_events);
-    AEONB_CUDA(cudaEventSynchronize(m_done[slot]));
     m_status_count[slot] = 0;
     if (n_device_jobs > 0)
     {
+        // on the kernels' stream: the next batch's entropy kernel rewrites these words
         m_status[slot].reserve(sizeof(int32_t) * n_device_jobs);
         AEONB_CUDA(cudaMemcpyAsync(m_status[slot].p, coef_dev.p, sizeof(int32_t) * n_device_jobs, cudaMemcpyDeviceToHost, st));
         d2h_bytes += (int64_t)(sizeof(int32_t) * n_device_jobs);
         m_status_count[slot] = n_device_jobs;
     }
-    AEONB_CUDA(cudaEventRecord(m_done[slot], st));
+    // Batches delivered to host memory are copied on a second stream, so that the next batch's uploads and
+    // kernels do not queue behind this batch's (much longer) device -> host copy.
+    cudaStream_t cs = st;
+    if (!on_device)
+    {
+        cs = m_copy;
+        AEONB_CUDA(cudaEventRecord(m_kernels[slot], st));
+        AEONB_CUDA(cudaStreamWaitEvent(cs, m_kernels[slot], 0));
+        for (size_t o = 0; o < outputs.size(); ++o)
+        {
+            if (outputs[o].host_produced)
+                continue;
+            const size_t bytes = (size_t)outputs[o].shape.byte_size() * (batch_major ? n : batch_size);
+            AEONB_CUDA(cudaMemcpyAsync(outs[o], sources[o], bytes, cudaMemcpyDeviceToHost, cs));
+            d2h_bytes += (int64_t)bytes;
+        }
+    }
+    AEONB_CUDA(cudaEventRecord(m_done[slot], cs));
     if (wait)
     {
         AEONB_CUDA(cudaStreamSynchronize(st));
+        if (cs != st)
+            AEONB_CUDA(cudaStreamSynchronize(cs));
         check_entropy_status(slot);
     }
     launches = (int32_t)(ctx->launches - launches_before);
+    if (trace)
+    {
+        mark(5);
+        std::fprintf(stderr, "aeonb_provider_run: entry %.3f plan %.3f arenas %.3f stage %.3f kernels %.3f deliver %.3f ms\n", t_phase[0],
+                     t_phase[1], t_phase[2], t_phase[3], t_phase[4], t_phase[5]);
+    }
 }
