@@ -40,7 +40,9 @@ WORKLOAD = "config2: 1024 synthetic q90 4:2:0 JPEGs (W,H~U[256,512]), random-are
 
 
 # DRAM bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum) from the captures summarised under profiles/
-TRAFFIC = {"jpeg_backend": 188.8e6, "aug_pack": 153.9e6, "jpeg_entropy": None}
+# (in the three-kernel chain part of the coefficient planes and pictures stays in the 126 MB L2 between kernels, so the
+# back end's DRAM traffic is below its algorithmic bytes)
+TRAFFIC = {"jpeg_entropy": 81.2e6, "jpeg_backend": 72.0e6, "aug_pack": 150.9e6}
 
 
 def make_dataset(seed, n):
@@ -288,7 +290,7 @@ def main():
             for c in range(info.ncomp):
                 qt = torch.from_numpy(quants[c].view(np.int16)).to(dev)
                 if on_dev:   # the entropy kernel fills the plane every step; the host result is kept for one cross-check
-                    ct = torch.full((coefs[c].size,), 0x5555, dtype=torch.int16, device=dev)
+                    ct = torch.empty((coefs[c].size,), dtype=torch.int16, device=dev)
                     ed[i].coef[c] = ct.data_ptr()
                     if check_plane is None:
                         check_plane = (ct, coefs[c].copy())
