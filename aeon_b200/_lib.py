@@ -40,6 +40,14 @@ class ImageLayout(C.Structure):
     ]
 
 
+class RotateDesc(C.Structure):
+    _fields_ = [
+        ("src", C.c_void_p), ("src_pitch", C.c_int32), ("src_pixel_stride", C.c_int32), ("width", C.c_int32),
+        ("height", C.c_int32), ("angle", C.c_int32), ("dst", C.c_void_p), ("dst_pitch", C.c_int32),
+        ("dst_pixel_stride", C.c_int32),
+    ]
+
+
 class JpegDesc(C.Structure):
     _fields_ = [
         ("coef", C.c_void_p * 3), ("quant", C.c_void_p * 3),
@@ -89,6 +97,7 @@ PROTOTYPES = {
     "aeonb_image_batch": (C.c_int, [C.c_void_p, C.POINTER(ImageDesc), C.c_int, C.POINTER(ImageLayout)]),
     "aeonb_image_batch_bytes": (C.c_int64, [C.POINTER(ImageDesc), C.c_int, C.POINTER(ImageLayout)]),
     "aeonb_image_batch_noalloc": (C.c_int, [C.POINTER(ImageDesc), C.c_int, C.POINTER(ImageLayout), C.c_void_p]),
+    "aeonb_rotate_batch": (C.c_int, [C.c_void_p, C.POINTER(RotateDesc), C.c_int]),
     "aeonb_jpeg_backend_batch": (C.c_int, [C.c_void_p, C.POINTER(JpegDesc), C.c_int]),
     "aeonb_jpeg_backend_bytes": (C.c_int64, [C.POINTER(JpegDesc), C.c_int]),
     "aeonb_jpeg_entropy_batch": (C.c_int, [C.c_void_p, C.POINTER(EntropyDesc), C.c_int]),

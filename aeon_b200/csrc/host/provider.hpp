@@ -104,6 +104,7 @@ struct aeonb_provider
     aeonb::device_buffer                 staging_dev;
     aeonb::device_buffer                 coef_dev;     // device entropy decoding: status words, coefficient planes, work areas
     aeonb::device_buffer                 pixels_dev;   // decoded pictures
+    aeonb::device_buffer                 rotated_dev;  // pictures after the rotation pass
     aeonb::device_buffer                 resized_dev;  // pictures after the resize_short pass
     // Device-side outputs of batches delivered to host memory, double buffered: the copy of batch t to the host
     // (on the copy stream) overlaps the kernels of batch t+1, which write the other set.

@@ -35,8 +35,6 @@ namespace aeonb
         // (image::transformer::transform_single_image, src/etl_image.cpp:146-202).
         aeonb_image_desc make_desc(const image_params& p, int src_w, int src_h, int slot_w, int slot_h, bool exact_fit)
         {
-            if (p.angle != 0)
-                throw error(AEONB_ERR_UNSUPPORTED, "rotation ('angle') is outside the accelerated path");
             string m = p.interpolation_method;
             std::transform(m.begin(), m.end(), m.begin(), ::toupper);
             aeonb_image_desc d{};
@@ -205,6 +203,15 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     vector<vector<int64_t>>          desc_dst(nin);
     vector<vector<aeonb_image_desc>> pre_descs(nin);  // resize_short pass: whole (expanded) picture -> short-side size
     vector<vector<int>>              pre_job(nin);
+    // rotation pass (image::rotate, the first step of transform_single_image): whole decoded picture -> rotated copy
+    struct rotation
+    {
+        int    job, angle, pitch;
+        size_t off;
+    };
+    vector<rotation>    rotations;
+    vector<vector<int>> desc_rot(nin), pre_rot(nin); // per descriptor: index into `rotations`, or -1
+    size_t              rotated_bytes = 0;
     vector<vector<aeonb_specgram_desc>> sdescs(nin);
     vector<vector<size_t>>           sdesc_off(nin);
     size_t stage_bytes = 0, pixel_bytes = 0, coef_bytes = 0;
@@ -328,6 +335,19 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                     have_params = true;
                 }
                 aeonb_image_desc d;
+                int              rot = -1;
+                if (params.angle != 0)
+                {
+                    rotation ro;
+                    ro.job        = j;
+                    ro.angle      = params.angle;
+                    ro.pitch      = (int)align_up((size_t)in.width * 3, 16);
+                    ro.off        = align_up(rotated_bytes, 256);
+                    rotated_bytes = ro.off + (size_t)ro.pitch * in.height;
+                    rot           = (int)rotations.size();
+                    rotations.push_back(ro);
+                    layout_jpeg(j, nullptr); // the rotation reads the whole picture
+                }
                 if (params.resize_short_size != 0)
                 {
                     // resize_short runs on the whole (expanded) picture before the crop (src/etl_image.cpp:160-168):
@@ -345,6 +365,8 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                     whole.output_size       = get_resized_short_size(cw, ch, params.resize_short_size);
                     pre_descs[s].push_back(make_desc(whole, in.width, in.height, 0, 0, false));
                     pre_job[s].push_back(j);
+                    pre_rot[s].push_back(rot);
+                    rot = -1;                // the crop pass reads the resized picture
                     layout_jpeg(j, nullptr); // the resize pass reads the whole picture
                     image_params rest = params;
                     rest.resize_short_size = 0;
@@ -361,6 +383,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                     throw std::invalid_argument("transformed image does not fit the configured output size");
                 descs[s].push_back(d);
                 desc_job[s].push_back(j);
+                desc_rot[s].push_back(rot);
                 desc_dst[s].push_back((int64_t)r * outputs[sg.first_output].shape.byte_size());
                 break;
             }
@@ -404,11 +427,14 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                         const auto& in = jobs[j].frame.info;
                         if (params.resize_short_size != 0)
                             throw error(AEONB_ERR_UNSUPPORTED, "'resize_short_size' for video frames is outside the accelerated path");
+                        if (params.angle != 0)
+                            throw error(AEONB_ERR_UNSUPPORTED, "rotation ('angle') of video frames is outside the accelerated path");
                         d              = make_desc(params, in.width, in.height, fc.width, fc.height, true);
                         layout_jpeg(j, &d);
                     }
                     descs[s].push_back(d);
                     desc_job[s].push_back(j);
+                    desc_rot[s].push_back(-1);
                     desc_dst[s].push_back((int64_t)r * rec + (int64_t)t * fc.height * fc.width);
                 }
                 break;
@@ -496,6 +522,8 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     staging.reserve(stage_bytes + 256);
     staging_dev.reserve(stage_bytes + 256);
     pixels_dev.reserve(pixel_bytes + 256);
+    if (rotated_bytes > 0)
+        rotated_dev.reserve(rotated_bytes + 256);
     const size_t status_room = align_up(sizeof(int32_t) * (jobs.size() + 1), 256);
     if (coef_bytes > 0)
         coef_dev.reserve(status_room + coef_bytes + 256);
@@ -641,6 +669,26 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         check_status(aeonb_jpeg_backend_batch(ctx, jd.data(), njobs));
         h2d_bytes += (int64_t)(sizeof(aeonb_jpeg_desc) * njobs);
     }
+    if (!rotations.empty())
+    {
+        vector<aeonb_rotate_desc> rd(rotations.size());
+        for (size_t i = 0; i < rotations.size(); ++i)
+        {
+            const rotation& ro  = rotations[i];
+            const jpeg_job& job = jobs[ro.job];
+            rd[i].src              = static_cast<const uint8_t*>(pixels_dev.p) + job.pixel_off;
+            rd[i].src_pitch        = job.pitch;
+            rd[i].src_pixel_stride = pixel_stride;
+            rd[i].width            = job.rw;
+            rd[i].height           = job.rh;
+            rd[i].angle            = ro.angle;
+            rd[i].dst              = static_cast<uint8_t*>(rotated_dev.p) + ro.off;
+            rd[i].dst_pitch        = ro.pitch;
+            rd[i].dst_pixel_stride = 3;
+        }
+        check_status(aeonb_rotate_batch(ctx, rd.data(), (int)rd.size()));
+        h2d_bytes += (int64_t)(sizeof(aeonb_rotate_desc) * rd.size());
+    }
     for (int s = 0; s < nin; ++s)
     {
         const stage& sg = stages[s];
@@ -718,6 +766,12 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                     d.src               = static_cast<const uint8_t*>(pixels_dev.p) + jobs[j].pixel_off;
                     d.src_pitch         = jobs[j].pitch;
                     d.src_pixel_stride  = pixel_stride;
+                    if (pre_rot[s][i] >= 0)
+                    {
+                        d.src              = static_cast<const uint8_t*>(rotated_dev.p) + rotations[pre_rot[s][i]].off;
+                        d.src_pitch        = rotations[pre_rot[s][i]].pitch;
+                        d.src_pixel_stride = 3;
+                    }
                     d.dst               = static_cast<char*>(resized_dev.p) + i * pre_slot;
                 }
                 check_status(aeonb_image_batch(ctx, pre_descs[s].data(), (int)pre_descs[s].size(), &P));
@@ -732,6 +786,12 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                 {
                     d.src              = static_cast<const uint8_t*>(resized_dev.p) + i * pre_slot;
                     d.src_pitch        = pre_pitch;
+                    d.src_pixel_stride = 3;
+                }
+                else if (desc_rot[s][i] >= 0)
+                {
+                    d.src              = static_cast<const uint8_t*>(rotated_dev.p) + rotations[desc_rot[s][i]].off;
+                    d.src_pitch        = rotations[desc_rot[s][i]].pitch;
                     d.src_pixel_stride = 3;
                 }
                 else if (j >= 0)

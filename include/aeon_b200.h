@@ -146,6 +146,22 @@ int64_t aeonb_image_batch_bytes(const aeonb_image_desc* descs, int n, const aeon
 #define AEONB_NOALLOC_MAX_RECORDS 512
 int aeonb_image_batch_noalloc(const aeonb_image_desc* descs, int n, const aeonb_image_layout* layout, void* stream);
 
+/* Rotation pre-pass: image::rotate (src/image.cpp:53-75), i.e. cv::warpAffine with the matrix of
+ * cv::getRotationMatrix2D(Point2i(width/2, height/2), angle, 1.0), INTER_LINEAR, BORDER_CONSTANT 0, same size.
+ * aeon rotates the decoded picture before every other step (src/etl_image.cpp:150-151); the rotated picture is
+ * then the source of aeonb_image_batch. */
+typedef struct aeonb_rotate_desc
+{
+    const uint8_t* src;      /* device: interleaved B,G,R[,x] picture */
+    int32_t src_pitch, src_pixel_stride;
+    int32_t width, height;
+    int32_t angle;           /* degrees, counter-clockwise */
+    uint8_t* dst;            /* device: rotated picture, same size */
+    int32_t dst_pitch, dst_pixel_stride;
+} aeonb_rotate_desc;
+
+int aeonb_rotate_batch(aeonb_ctx* ctx, const aeonb_rotate_desc* descs, int n);
+
 /* ------------------------------------------------------------------------------------------------
  * 1b. JPEG back end kernel: dequantisation + 8x8 integer inverse DCT + chroma upsampling +
  *     YCbCr->BGR, i.e. everything cv::imdecode (src/etl_image.cpp:90, src/cap_mjpeg_decoder.cpp:140)

@@ -63,6 +63,10 @@ def lighting(img, alphas, color_noise_std):
 
 def transform_single_image(img, p):
     """src/etl_image.cpp:146-202 with OpenCV doing the pixel work."""
+    if p.angle != 0:   # image::rotate, src/image.cpp:53-75
+        rot = cv2.getRotationMatrix2D((img.shape[1] // 2, img.shape[0] // 2), p.angle, 1.0)
+        img = cv2.warpAffine(img, rot, (img.shape[1], img.shape[0]), flags=cv2.INTER_LINEAR, borderMode=cv2.BORDER_CONSTANT,
+                             borderValue=(0, 0, 0, 0))
     if np.float32(p.expand_ratio) > 1.0:
         img = ops.expand(img, p.expand_offset, p.expand_size)
     if p.resize_short_size != 0:

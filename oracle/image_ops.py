@@ -348,10 +348,69 @@ def _resize(img, size_wh, method):
     raise NotImplementedError("interpolation method %s has no oracle" % method)
 
 
+def rotation_matrix(width, height, angle):
+    """``cv::getRotationMatrix2D(Point2i(cols/2, rows/2), angle, 1.0)`` as aeon's ``image::rotate`` calls it
+    (src/image.cpp:62-63): 2x3 float64, angle in degrees, counter-clockwise."""
+    import math
+    cx, cy = float(width // 2), float(height // 2)
+    a = angle * (math.pi / 180.0)
+    alpha, beta = math.cos(a), math.sin(a)
+    return np.array([[alpha, beta, (1 - alpha) * cx - beta * cy], [-beta, alpha, beta * cx + (1 - alpha) * cy]], np.float64)
+
+
+def invert_affine(m):
+    """The inversion ``cv::warpAffine`` applies to the forward matrix (no WARP_INVERSE_MAP), same operation order."""
+    M = np.array(m, np.float64).ravel().copy()
+    D = M[0] * M[4] - M[1] * M[3]
+    D = 1.0 / D if D != 0 else 0.0
+    A11, A22 = M[4] * D, M[0] * D
+    M[0] = A11
+    M[1] *= -D
+    M[3] *= -D
+    M[4] = A22
+    b1 = -M[0] * M[2] - M[1] * M[5]
+    b2 = -M[3] * M[2] - M[4] * M[5]
+    M[2], M[5] = b1, b2
+    return M
+
+
+def warp_affine_linear_u8(src, forward):
+    """``cv::warpAffine(src, dst, M, src.size(), INTER_LINEAR, BORDER_CONSTANT, 0)`` for 8-bit images: source
+    coordinates in 10-bit fixed point (rounded half to even from float64), reduced to 5 fractional bits, bilinear
+    weights (32-fx)(32-fy)*32 ... summing to 2^15, result (sum + 2^14) >> 15; taps outside the picture are zero."""
+    h, w = src.shape[:2]
+    M = invert_affine(forward)
+    ab = 1024.0
+    xs = np.arange(w, dtype=np.float64)
+    ys = np.arange(h, dtype=np.float64)
+    adelta = np.rint(M[0] * xs * ab).astype(np.int64)
+    bdelta = np.rint(M[3] * xs * ab).astype(np.int64)
+    x0 = np.rint((M[1] * ys + M[2]) * ab).astype(np.int64) + 16
+    y0 = np.rint((M[4] * ys + M[5]) * ab).astype(np.int64) + 16
+    X = (x0[:, None] + adelta[None, :]) >> 5
+    Y = (y0[:, None] + bdelta[None, :]) >> 5
+    sx, sy, fx, fy = X >> 5, Y >> 5, X & 31, Y & 31
+    s = src.astype(np.int64)
+
+    def tap(yy, xx):
+        ok = (xx >= 0) & (xx < w) & (yy >= 0) & (yy < h)
+        return s[np.clip(yy, 0, h - 1), np.clip(xx, 0, w - 1)] * ok[..., None]
+
+    acc = (tap(sy, sx) * ((32 - fx) * (32 - fy) * 32)[..., None] + tap(sy, sx + 1) * (fx * (32 - fy) * 32)[..., None] +
+           tap(sy + 1, sx) * ((32 - fx) * fy * 32)[..., None] + tap(sy + 1, sx + 1) * (fx * fy * 32)[..., None])
+    return np.clip((acc + (1 << 14)) >> 15, 0, 255).astype(np.uint8)
+
+
+def rotate(img, angle):
+    """aeon ``image::rotate`` (src/image.cpp:53-75) with its defaults (linear interpolation, zero border)."""
+    if angle == 0:
+        return img
+    return warp_affine_linear_u8(img, rotation_matrix(img.shape[1], img.shape[0], angle))
+
+
 def transform_single_image(img, p):
     """aeon ``image::transformer::transform_single_image`` (src/etl_image.cpp:146-202)."""
-    if p.angle != 0:
-        raise NotImplementedError("rotation is outside the accelerated path")
+    img = rotate(img, p.angle)
     if f32(p.expand_ratio) > 1.0:
         img = expand(img, p.expand_offset, p.expand_size)
     if p.resize_short_size != 0:

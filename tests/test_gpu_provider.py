@@ -309,3 +309,17 @@ def test_device_entropy_decoding_reports_malformed_streams(ctx):
         p.run_host([(good,), (broken,)])
     out = p.run_host([(good,), (good,)])["image"]      # the provider stays usable
     assert np.array_equal(out[0], out[1])
+
+
+def test_rotation_angle_through_the_provider_bit_exact(ctx):
+    """'angle' (image::rotate before every other step, src/etl_image.cpp:150-151): with the random-area crop, and
+    with resize_short + linear-scale crop (the reference sizes an area-scale crop box for the unresized picture)."""
+    etl = [{"type": "image", "height": 96, "width": 96, "output_type": "uint8_t"}]
+    recs = [(r[0],) for r in image_records(57, 8)]
+    linear = {"type": "image", "crop_enable": True, "scale": [0.5, 0.9], "flip_enable": True, "resize_short_size": 128,
+              "interpolation_method": "LINEAR"}
+    for aug in (dict(AUG_C1, angle=[-20, 20]), dict(linear, angle=[-20, 20])):
+        cfg = {"batch_size": 8, "random_seed": 41, "etl": etl, "augmentation": [aug]}
+        got = make_provider(ctx, cfg).run_host(recs)["image"]
+        want = PipelineOracle(cfg).batch(recs)["image"]
+        assert np.array_equal(got, want)

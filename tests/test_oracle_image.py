@@ -128,3 +128,17 @@ def test_expand_padding_and_video_layout():
     frames = [np.full((4, 5, 3), i, np.uint8) for i in range(3)]
     v = ops.load_video(frames, 5)            # aeon test/test_video.cpp:119-180 layout: C x T x H x W
     assert v.shape == (3, 5, 4, 5) and v[:, 2].min() == 2 and not v[:, 3:].any()
+
+
+def test_rotation_matches_opencv_warp_affine():
+    """image::rotate (src/image.cpp:53-75): the restated fixed-point warpAffine against the OpenCV binary."""
+    import cv2
+    rng = np.random.default_rng(77)
+    for (h, w, angle) in [(40, 60, 7), (97, 131, -13), (64, 64, 20), (200, 150, 3), (33, 70, -20), (256, 384, 45), (50, 50, 90),
+                          (31, 17, 180), (120, 80, -1), (1, 1, 5), (2, 300, 11)]:
+        img = rng.integers(0, 256, (h, w, 3), dtype=np.uint8)
+        ref = cv2.warpAffine(img, cv2.getRotationMatrix2D((w // 2, h // 2), angle, 1.0), (w, h), flags=cv2.INTER_LINEAR,
+                             borderMode=cv2.BORDER_CONSTANT, borderValue=(0, 0, 0, 0))
+        assert np.array_equal(ops.rotate(img, angle), ref), (h, w, angle)
+    img = rng.integers(0, 256, (20, 30, 3), dtype=np.uint8)
+    assert ops.rotate(img, 0) is img
