@@ -83,7 +83,8 @@ class SpecgramDesc(C.Structure):
 
 class SpecgramConfig(C.Structure):
     _fields_ = [("frame_length", C.c_int32), ("frame_stride", C.c_int32), ("max_time_steps", C.c_int32),
-                ("num_filters", C.c_int32), ("sample_rate", C.c_int32), ("window", C.c_int32)]
+                ("num_filters", C.c_int32), ("sample_rate", C.c_int32), ("window", C.c_int32),
+                ("num_cepstra", C.c_int32), ("reserved0", C.c_int32)]
 
 
 # name -> (restype, argtypes); every symbol the header declares

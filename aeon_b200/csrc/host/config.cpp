@@ -234,10 +234,11 @@ namespace aeonb
         sample_rate    = get_int(js, "sample_rate", 16000);
         window_type    = get_string(js, "window_type", "hann");
         feature_type   = get_string(js, "feature_type", "mfsc");
+        num_cepstra    = get_int(js, "num_cepstra", 40);
         name           = get_string(js, "name", "");
         verify_config("audio",
                       {"frame_length", "frame_stride", "max_time_steps", "max_samples", "num_filters", "sample_rate",
-                       "window_type", "feature_type", "name"},
+                       "window_type", "feature_type", "num_cepstra", "name"},
                       js);
         if (frame_length <= 1 || frame_stride <= 0)
             throw invalid_argument("invalid frame_length or frame_stride");
@@ -245,10 +246,12 @@ namespace aeonb
             max_time_steps = (max_samples - frame_length) / frame_stride + 1;
         if (max_time_steps <= 0)
             throw invalid_argument("audio config needs 'max_time_steps' or 'max_samples'");
-        if (feature_type != "mfsc" && feature_type != "specgram")
-            throw invalid_argument("feature_type must be 'specgram' or 'mfsc'");
+        if (feature_type != "mfsc" && feature_type != "specgram" && feature_type != "mfcc")
+            throw invalid_argument("feature_type must be 'specgram', 'mfsc' or 'mfcc'");
+        if (feature_type == "mfcc" && (num_cepstra <= 0 || num_cepstra > num_filters))
+            throw invalid_argument("num_cepstra <= cepsgram.cols"); // the reference's affirm (src/specgram.cpp:141)
         window_code();
-        const int bins   = feature_type == "mfsc" ? num_filters : frame_length / 2 + 1;
+        const int bins   = feature_type == "mfcc" ? num_cepstra : feature_type == "mfsc" ? num_filters : frame_length / 2 + 1;
         shape.otype      = output_type::from_name("float");
         shape.shape      = {max_time_steps, bins};
         shape.axis_names = {"time", "frequency"};

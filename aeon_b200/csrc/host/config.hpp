@@ -95,7 +95,8 @@ namespace aeonb
         int         num_filters    = 64;
         int         sample_rate    = 16000;
         std::string window_type    = "hann";
-        std::string feature_type   = "mfsc"; // "specgram" (magnitudes) or "mfsc" (log mel)
+        std::string feature_type   = "mfsc"; // "specgram" (magnitudes), "mfsc" (log mel) or "mfcc" (DCT of log mel)
+        int         num_cepstra    = 40;
         std::string name;
         shape_type  shape;
         audio_config() = default;

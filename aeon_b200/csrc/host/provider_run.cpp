@@ -812,9 +812,10 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         else if (sg.kind == stage_kind::audio)
         {
             const int             o = sg.first_output;
+            const bool            mel = sg.audio.feature_type != "specgram";
             aeonb_specgram_config cfg{sg.audio.frame_length, sg.audio.frame_stride, sg.audio.max_time_steps,
-                                      sg.audio.feature_type == "mfsc" ? sg.audio.num_filters : 0, sg.audio.sample_rate,
-                                      sg.audio.window_code()};
+                                      mel ? sg.audio.num_filters : 0, sg.audio.sample_rate, sg.audio.window_code(),
+                                      sg.audio.feature_type == "mfcc" ? sg.audio.num_cepstra : 0, 0};
             for (size_t i = 0; i < sdescs[s].size(); ++i)
             {
                 sdescs[s][i].samples = reinterpret_cast<const int16_t*>(dstage + sdesc_off[s][i]);

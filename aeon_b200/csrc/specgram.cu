@@ -35,6 +35,8 @@ namespace aeonb
             const int*                 filt_start; // num_filters+1 offsets into filt_bin / filt_weight
             const int*                 filt_bin;
             const float*               filt_weight;
+            const float*               dct;       // num_cepstra x dct_n cosine table with the orthonormal scale, or nullptr
+            int                        dct_n;     // num_filters rounded up to even
             int                        n_out;     // floats per output row
         };
 
@@ -148,13 +150,29 @@ namespace aeonb
                 return;
             __syncwarp();
 
-            // ---- sparse mel filters + log
+            // ---- sparse mel filters + log (into the transform buffer when a DCT follows: it is free again)
+            float* const cep = reinterpret_cast<float*>(zbuf[warp]);
             for (int j = lane; j < P.cfg.num_filters; j += 32)
             {
                 float acc = 0.f;
                 for (int i = P.filt_start[j]; i < P.filt_start[j + 1]; ++i)
                     acc += pbuf[warp][P.filt_bin[i]] * P.filt_weight[i];
-                out[j] = logf(acc);
+                if (P.dct)
+                    cep[j] = logf(acc);
+                else
+                    out[j] = logf(acc);
+            }
+            if (!P.dct)
+                return;
+            __syncwarp();
+            // ---- MFCC: first num_cepstra rows of the orthonormal DCT-II of the log-mel vector (padding adds zeros only)
+            for (int j = lane; j < P.cfg.num_cepstra; j += 32)
+            {
+                const float* row = P.dct + (size_t)j * P.dct_n;
+                float        acc = 0.f;
+                for (int k = 0; k < P.cfg.num_filters; ++k)
+                    acc += cep[k] * __ldg(row + k);
+                out[j] = acc;
             }
         }
 
@@ -175,9 +193,10 @@ namespace aeonb
 
     cudaError_t launch_specgram(const aeonb_specgram_desc* descs_dev, int n, const aeonb_specgram_config& cfg,
                                 const float* window_dev, const float2* twiddle_dev, const int* filt_start_dev,
-                                const int* filt_bin_dev, const float* filt_weight_dev, int n_out, cudaStream_t stream)
+                                const int* filt_bin_dev, const float* filt_weight_dev, const float* dct_dev, int dct_n, int n_out,
+                                cudaStream_t stream)
     {
-        spec_launch P{descs_dev, cfg, window_dev, twiddle_dev, filt_start_dev, filt_bin_dev, filt_weight_dev, n_out};
+        spec_launch P{descs_dev, cfg, window_dev, twiddle_dev, filt_start_dev, filt_bin_dev, filt_weight_dev, dct_dev, dct_n, n_out};
         switch (cfg.frame_length / 64)
         {
         case 1: return launch_r<1>(P, n, stream);

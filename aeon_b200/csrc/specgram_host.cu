@@ -13,7 +13,8 @@ namespace aeonb
 {
     cudaError_t launch_specgram(const aeonb_specgram_desc* descs_dev, int n, const aeonb_specgram_config& cfg,
                                 const float* window_dev, const float2* twiddle_dev, const int* filt_start_dev,
-                                const int* filt_bin_dev, const float* filt_weight_dev, int n_out, cudaStream_t stream);
+                                const int* filt_bin_dev, const float* filt_weight_dev, const float* dct_dev, int dct_n, int n_out,
+                                cudaStream_t stream);
     bool specgram_frame_length_supported(int frame_length);
 
     // aeon specgram::create_window (src/specgram.cpp:156-189); code 0 = no window.
@@ -116,6 +117,21 @@ namespace aeonb
             filt_bin               = to_device(bin);
             filt_weight            = to_device(weight);
         }
+        if (cfg.num_cepstra != 0)
+        {
+            // cv::dct(DCT_ROWS) of the row padded to an even length N: y[j] = s_j * sum_k x[k] cos(pi (2k+1) j / (2N)),
+            // s_0 = sqrt(1/N), s_j = sqrt(2/N) (specgram::cepsgram_to_mfcc, src/specgram.cpp:139-154)
+            dct_n = (cfg.num_filters + 1) & ~1;
+            if (cfg.num_filters <= 0 || cfg.num_cepstra < 0 || cfg.num_cepstra > cfg.num_filters)
+                throw std::invalid_argument("num_cepstra <= cepsgram.cols");
+            std::vector<float> table((size_t)cfg.num_cepstra * dct_n);
+            for (int j = 0; j < cfg.num_cepstra; ++j)
+                for (int k = 0; k < dct_n; ++k)
+                    table[(size_t)j * dct_n + k] = (float)(std::sqrt((j == 0 ? 1.0 : 2.0) / dct_n) *
+                                                           std::cos(3.14159265358979323846 * (2 * k + 1) * j / (2.0 * dct_n)));
+            dct   = to_device(table);
+            n_out = cfg.num_cepstra;
+        }
     }
 
     specgram_tables::~specgram_tables()
@@ -125,17 +141,18 @@ namespace aeonb
         cudaFree(filt_start);
         cudaFree(filt_bin);
         cudaFree(filt_weight);
+        cudaFree(dct);
     }
 
     cudaError_t specgram_tables::launch(const aeonb_specgram_desc* descs_dev, int n, const aeonb_specgram_config& cfg,
                                         cudaStream_t stream) const
     {
-        return launch_specgram(descs_dev, n, cfg, window, twiddle, filt_start, filt_bin, filt_weight, n_out, stream);
+        return launch_specgram(descs_dev, n, cfg, window, twiddle, filt_start, filt_bin, filt_weight, dct, dct_n, n_out, stream);
     }
 
     namespace
     {
-        using key_t = std::tuple<int, int, int, int, int, int, int>;
+        using key_t = std::tuple<int, int, int, int, int, int, int, int>;
         std::mutex                               g_mutex;
         std::map<key_t, specgram_tables*>        g_tables; // lives until process exit
     }
@@ -143,7 +160,7 @@ namespace aeonb
     const specgram_tables& specgram_tables_for(int device, const aeonb_specgram_config& cfg)
     {
         std::lock_guard<std::mutex> lk(g_mutex);
-        key_t key{device, cfg.frame_length, cfg.frame_stride, cfg.max_time_steps, cfg.num_filters, cfg.sample_rate, cfg.window};
+        key_t key{device, cfg.frame_length, cfg.frame_stride, cfg.max_time_steps, cfg.num_filters, cfg.sample_rate, cfg.window, cfg.num_cepstra};
         auto  it = g_tables.find(key);
         if (it == g_tables.end())
             it = g_tables.emplace(key, new specgram_tables(cfg)).first;
@@ -180,7 +197,7 @@ int64_t aeonb_specgram_bytes(const aeonb_specgram_desc* descs, int n, const aeon
 {
     if (!descs || !cfg)
         return 0;
-    const int n_out = cfg->num_filters > 0 ? cfg->num_filters : cfg->frame_length / 2 + 1;
+    const int n_out = cfg->num_cepstra > 0 ? cfg->num_cepstra : cfg->num_filters > 0 ? cfg->num_filters : cfg->frame_length / 2 + 1;
     int64_t   total = 0;
     for (int i = 0; i < n; ++i)
         total += (int64_t)descs[i].n_samples * 2 + (int64_t)cfg->max_time_steps * n_out * 4;

@@ -19,6 +19,8 @@ namespace aeonb
         int*    filt_start  = nullptr;
         int*    filt_bin    = nullptr;
         float*  filt_weight = nullptr;
+        float*  dct         = nullptr; // MFCC: num_cepstra x dct_n
+        int     dct_n       = 0;
         int     n_out       = 0;
         explicit specgram_tables(const aeonb_specgram_config& cfg);
         ~specgram_tables();

@@ -219,8 +219,8 @@ int aeonb_jpeg_entropy_batch(aeonb_ctx* ctx, const aeonb_entropy_desc* descs, in
 int64_t aeonb_jpeg_entropy_scratch_bytes(const aeonb_entropy_desc* desc);
 
 /* ------------------------------------------------------------------------------------------------
- * 1c. Spectrogram kernel: framing + window + DFT magnitude + mel filter bank + log
- *     (specgram::wav_to_specgram / specgram_to_cepsgram, src/specgram.cpp:26-137).
+ * 1c. Spectrogram kernel: framing + window + DFT magnitude + mel filter bank + log [+ DCT]
+ *     (specgram::wav_to_specgram / specgram_to_cepsgram / cepsgram_to_mfcc, src/specgram.cpp:26-154).
  * ---------------------------------------------------------------------------------------------- */
 
 typedef struct aeonb_specgram_desc
@@ -238,6 +238,10 @@ typedef struct aeonb_specgram_config
     int32_t num_filters;    /* mel filters; 0 = output the magnitude spectrogram (frame_length/2+1 bins) */
     int32_t sample_rate;
     int32_t window;         /* 0 none, 1 hann, 2 hamming, 3 blackman, 4 bartlett (src/specgram.cpp:156-189) */
+    int32_t num_cepstra;    /* > 0 (needs num_filters > 0): MFCC, the first num_cepstra coefficients of the orthonormal
+                               DCT-II of the log-mel row, zero-padded to an even length (specgram::cepsgram_to_mfcc,
+                               src/specgram.cpp:139-154); rows are then num_cepstra floats */
+    int32_t reserved0;
 } aeonb_specgram_config;
 
 int aeonb_specgram_batch(aeonb_ctx* ctx, const aeonb_specgram_desc* descs, int n, const aeonb_specgram_config* cfg);

@@ -82,14 +82,32 @@ def specgram_to_cepsgram(spec, fbank):
         return np.log(power @ fbank.astype(np.float64)).astype(f32)
 
 
+def cepsgram_to_mfcc(cepsgram, num_cepstra):
+    """src/specgram.cpp:139-154: rows zero-padded to an even length N, ``cv::dct(..., DCT_ROWS)`` (orthonormal DCT-II:
+    y[j] = s_j sum_k x[k] cos(pi (2k+1) j / (2N)), s_0 = sqrt(1/N), s_j = sqrt(2/N)), first ``num_cepstra`` columns."""
+    if num_cepstra > cepsgram.shape[1]:
+        raise ValueError("num_cepstra <= cepsgram.cols")
+    x = cepsgram.astype(np.float64)
+    if x.shape[1] % 2:
+        x = np.concatenate([x, np.zeros((x.shape[0], 1))], 1)
+    n = x.shape[1]
+    k = np.arange(n)
+    j = np.arange(num_cepstra)[:, None]
+    basis = np.cos(np.pi * (2 * k + 1) * j / (2.0 * n)) * np.where(j == 0, np.sqrt(1.0 / n), np.sqrt(2.0 / n))
+    return (x @ basis.T).astype(f32)
+
+
 def log_mel(samples, frame_length=320, frame_stride=160, max_time_steps=1599, num_filters=64, sample_rate=16000,
-            window="hann"):
-    """Zero-padded [max_time_steps, num_filters] float32 slab for one clip of int16 samples."""
+            window="hann", num_cepstra=0):
+    """Zero-padded [max_time_steps, n_out] float32 slab for one clip of int16 samples: magnitudes (num_filters == 0),
+    log-mel energies, or with ``num_cepstra`` the MFCCs."""
     win = create_window(window, frame_length)
     spec = wav_to_specgram(np.asarray(samples), frame_length, frame_stride, max_time_steps, win)
-    out = np.zeros((max_time_steps, num_filters if num_filters else frame_length // 2 + 1), f32)
+    n_out = num_cepstra if num_cepstra else num_filters if num_filters else frame_length // 2 + 1
+    out = np.zeros((max_time_steps, n_out), f32)
     if num_filters:
-        out[:spec.shape[0]] = specgram_to_cepsgram(spec, create_filterbanks(num_filters, frame_length, sample_rate))
+        ceps = specgram_to_cepsgram(spec, create_filterbanks(num_filters, frame_length, sample_rate))
+        out[:spec.shape[0]] = cepsgram_to_mfcc(ceps, num_cepstra) if num_cepstra else ceps
     else:
         out[:spec.shape[0]] = spec
     return out

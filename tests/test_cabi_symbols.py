@@ -32,7 +32,7 @@ def test_struct_sizes_match_the_header_layout():
     assert ctypes.sizeof(_lib.ImageLayout) == 128
     assert ctypes.sizeof(_lib.JpegDesc) == 128
     assert ctypes.sizeof(_lib.SpecgramDesc) == 24
-    assert ctypes.sizeof(_lib.SpecgramConfig) == 24
+    assert ctypes.sizeof(_lib.SpecgramConfig) == 32
 
 
 def test_calls_without_a_gpu_fail_with_a_message_not_a_crash():

@@ -20,11 +20,12 @@ def synth_clip(rng, seconds, sr=16000):
     return np.clip(x * 32767 / 2, -32768, 32767).astype(np.int16)
 
 
-def run(ctx, clips, frame_length=320, frame_stride=160, max_time_steps=200, num_filters=64, sample_rate=16000, window=1):
+def run(ctx, clips, frame_length=320, frame_stride=160, max_time_steps=200, num_filters=64, sample_rate=16000, window=1,
+        num_cepstra=0):
     from aeon_b200 import _lib as L
     dev = torch.device("cuda", ctx.device)
-    n_out = num_filters if num_filters else frame_length // 2 + 1
-    cfg = L.SpecgramConfig(frame_length, frame_stride, max_time_steps, num_filters, sample_rate, window)
+    n_out = num_cepstra if num_cepstra else num_filters if num_filters else frame_length // 2 + 1
+    cfg = L.SpecgramConfig(frame_length, frame_stride, max_time_steps, num_filters, sample_rate, window, num_cepstra, 0)
     with torch.cuda.stream(ctx.torch_stream):
         out = torch.full((len(clips), max_time_steps, n_out), 7.0, dtype=torch.float32, device=dev)
         ts = [torch.from_numpy(c).to(dev) for c in clips]
@@ -77,3 +78,24 @@ def test_unsupported_frame_length_is_an_error(ctx):
     from aeon_b200._lib import AeonError
     with pytest.raises(AeonError, match="frame_length"):
         run(ctx, [np.zeros(1000, np.int16)], frame_length=400, frame_stride=160)
+
+
+def test_mfcc(ctx):
+    """specgram::cepsgram_to_mfcc (src/specgram.cpp:139-154): DCT-II of the log-mel rows, even and odd filter counts.
+    Tolerance: the log-mel bound (1e-4 relative + 2e-4) carried through a sum of num_filters terms: 1e-4 relative + 1e-3."""
+    rng = np.random.default_rng(35)
+    clips = [synth_clip(rng, s) for s in (0.9, 0.4)]
+    for nf, nc, L_ in [(40, 13, 512), (23, 23, 512), (32, 1, 256)]:
+        want = [ospec.log_mel(c, frame_length=L_, max_time_steps=60, num_filters=nf, num_cepstra=nc) for c in clips]
+        assert all(np.isfinite(w).all() for w in want)      # a bank without empty filters
+        got = run(ctx, clips, frame_length=L_, max_time_steps=60, num_filters=nf, num_cepstra=nc)
+        assert got.shape == (2, 60, nc)
+        for g, w in zip(got, want):
+            assert np.all(np.abs(g - w) <= 1e-4 * np.abs(w) + 1e-3), float(np.abs(g - w).max())
+    from aeon_b200 import _lib as L
+    cfg = L.SpecgramConfig(512, 160, 60, 20, 16000, 1, 21, 0)   # more cepstra than filters: the reference's affirm
+    d = (L.SpecgramDesc * 1)()
+    t = torch.zeros(2000, dtype=torch.int16, device="cuda")
+    o = torch.zeros(60 * 21, dtype=torch.float32, device="cuda")
+    d[0].samples, d[0].n_samples, d[0].dst = t.data_ptr(), 2000, o.data_ptr()
+    assert ctx.lib.aeonb_specgram_batch(ctx.handle, d, 1, C.byref(cfg)) == L.ERR_INVALID

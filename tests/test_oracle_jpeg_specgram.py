@@ -4,6 +4,7 @@ import os
 
 import cv2
 import numpy as np
+import pytest
 
 from oracle import jpeg as ojpeg
 from oracle import specgram as ospec
@@ -80,3 +81,16 @@ def test_specgram_oracle_matches_opencv_dft_and_log():
     m = ~np.isinf(mine)
     assert np.abs(ceps[m] - mine[m]).max() < 2e-4
     assert ospec.filterbank_edges(64, 320, 16000)[:8] == [0, 0, 1, 1, 2, 3, 3, 4]
+
+
+def test_mfcc_oracle_matches_opencv_dct():
+    """cepsgram_to_mfcc (src/specgram.cpp:139-154) against cv2.dct(DCT_ROWS) on even and odd (zero-padded) widths."""
+    import cv2
+    rng = np.random.default_rng(88)
+    for nf, nc in [(64, 40), (40, 13), (13, 13), (7, 3)]:
+        x = rng.normal(0, 3, (50, nf)).astype(np.float32)
+        pad = x if nf % 2 == 0 else np.concatenate([x, np.zeros((50, 1), np.float32)], 1)
+        ref = cv2.dct(pad, flags=cv2.DCT_ROWS)[:, :nc]
+        assert np.abs(ospec.cepsgram_to_mfcc(x, nc) - ref).max() <= 5e-6
+    with pytest.raises(ValueError):
+        ospec.cepsgram_to_mfcc(np.zeros((2, 4), np.float32), 5)
