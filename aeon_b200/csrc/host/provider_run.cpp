@@ -211,6 +211,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     };
     vector<rotation>    rotations;
     vector<vector<int>> desc_rot(nin), pre_rot(nin); // per descriptor: index into `rotations`, or -1
+    vector<vector<int>> desc_pre(nin);               // per descriptor: index into pre_descs[s], or -1
     size_t              rotated_bytes = 0;
     vector<vector<aeonb_specgram_desc>> sdescs(nin);
     vector<vector<size_t>>           sdesc_off(nin);
@@ -295,6 +296,68 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         job.laid_out    = true;
     };
 
+    // Plans the passes one picture (an image record, or a video frame) goes through before the main image kernel
+    // -- rotation (image::rotate, the first step of transform_single_image) and resize_short (applied to the whole,
+    // possibly expanded, picture before the crop; src/etl_image.cpp:160-168) -- and returns the main descriptor.
+    std::unordered_map<int, int> rotation_of_job; // a repeated video frame is rotated once
+    auto plan_picture = [&](int s, int j, const image_params& params, int slot_w, int slot_h, bool exact_fit) {
+        const aeonb_jpeg_info in = jobs[j].frame.info;
+        int                   rot = -1;
+        if (params.angle != 0)
+        {
+            auto it = rotation_of_job.find(j);
+            if (it != rotation_of_job.end())
+                rot = it->second;
+            else
+            {
+                rotation ro;
+                ro.job        = j;
+                ro.angle      = params.angle;
+                ro.pitch      = (int)align_up((size_t)in.width * 3, 16);
+                ro.off        = align_up(rotated_bytes, 256);
+                rotated_bytes = ro.off + (size_t)ro.pitch * in.height;
+                rot           = (int)rotations.size();
+                rotations.push_back(ro);
+                rotation_of_job[j] = rot;
+            }
+            layout_jpeg(j, nullptr); // the rotation reads the whole picture
+        }
+        aeonb_image_desc d;
+        int              pre = -1;
+        if (params.resize_short_size != 0)
+        {
+            image_params whole = params;
+            whole.resize_short_size = 0;
+            whole.padding           = 0;
+            whole.flip              = false;
+            whole.contrast = whole.brightness = whole.saturation = 1.0f;
+            whole.hue               = 0;
+            whole.lighting.clear();
+            const int cw = params.expand_ratio > 1.0f ? params.expand_size.width : in.width;
+            const int ch = params.expand_ratio > 1.0f ? params.expand_size.height : in.height;
+            whole.cropbox           = recti{0, 0, cw, ch};
+            whole.output_size       = get_resized_short_size(cw, ch, params.resize_short_size);
+            pre                     = (int)pre_descs[s].size();
+            pre_descs[s].push_back(make_desc(whole, in.width, in.height, 0, 0, false));
+            pre_job[s].push_back(j);
+            pre_rot[s].push_back(rot);
+            rot = -1;                // the crop pass reads the resized picture
+            layout_jpeg(j, nullptr); // the resize pass reads the whole picture
+            image_params rest = params;
+            rest.resize_short_size = 0;
+            rest.expand_ratio      = 1.0f;
+            d = make_desc(rest, whole.output_size.width, whole.output_size.height, slot_w, slot_h, exact_fit);
+        }
+        else
+        {
+            d = make_desc(params, in.width, in.height, slot_w, slot_h, exact_fit);
+            layout_jpeg(j, &d); // keeps an earlier whole-picture layout
+        }
+        desc_rot[s].push_back(rot);
+        desc_pre[s].push_back(pre);
+        return d;
+    };
+
     // AEONB_TRACE=1 prints the host time of each phase of the call to stderr
     static const bool trace = std::getenv("AEONB_TRACE") != nullptr;
     auto              t_prev = t_entry;
@@ -334,56 +397,11 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                     params      = factory.make_params(engine, in.width, in.height, sg.image.width, sg.image.height);
                     have_params = true;
                 }
-                aeonb_image_desc d;
-                int              rot = -1;
-                if (params.angle != 0)
-                {
-                    rotation ro;
-                    ro.job        = j;
-                    ro.angle      = params.angle;
-                    ro.pitch      = (int)align_up((size_t)in.width * 3, 16);
-                    ro.off        = align_up(rotated_bytes, 256);
-                    rotated_bytes = ro.off + (size_t)ro.pitch * in.height;
-                    rot           = (int)rotations.size();
-                    rotations.push_back(ro);
-                    layout_jpeg(j, nullptr); // the rotation reads the whole picture
-                }
-                if (params.resize_short_size != 0)
-                {
-                    // resize_short runs on the whole (expanded) picture before the crop (src/etl_image.cpp:160-168):
-                    // a first pass of the same kernel writes the resized picture, the crop pass reads it
-                    image_params whole = params;
-                    whole.resize_short_size = 0;
-                    whole.padding           = 0;
-                    whole.flip              = false;
-                    whole.contrast = whole.brightness = whole.saturation = 1.0f;
-                    whole.hue               = 0;
-                    whole.lighting.clear();
-                    const int cw = params.expand_ratio > 1.0f ? params.expand_size.width : in.width;
-                    const int ch = params.expand_ratio > 1.0f ? params.expand_size.height : in.height;
-                    whole.cropbox           = recti{0, 0, cw, ch};
-                    whole.output_size       = get_resized_short_size(cw, ch, params.resize_short_size);
-                    pre_descs[s].push_back(make_desc(whole, in.width, in.height, 0, 0, false));
-                    pre_job[s].push_back(j);
-                    pre_rot[s].push_back(rot);
-                    rot = -1;                // the crop pass reads the resized picture
-                    layout_jpeg(j, nullptr); // the resize pass reads the whole picture
-                    image_params rest = params;
-                    rest.resize_short_size = 0;
-                    rest.expand_ratio      = 1.0f;
-                    d = make_desc(rest, whole.output_size.width, whole.output_size.height, sg.image.width, sg.image.height,
-                                  !factory.fixed_aspect_ratio);
-                }
-                else
-                {
-                    d = make_desc(params, in.width, in.height, sg.image.width, sg.image.height, !factory.fixed_aspect_ratio);
-                    layout_jpeg(j, &d);
-                }
+                aeonb_image_desc d = plan_picture(s, j, params, sg.image.width, sg.image.height, !factory.fixed_aspect_ratio);
                 if (d.out_w > sg.image.width || d.out_h > sg.image.height)
                     throw std::invalid_argument("transformed image does not fit the configured output size");
                 descs[s].push_back(d);
                 desc_job[s].push_back(j);
-                desc_rot[s].push_back(rot);
                 desc_dst[s].push_back((int64_t)r * outputs[sg.first_output].shape.byte_size());
                 break;
             }
@@ -423,18 +441,16 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                     int              j = -1;
                     if (t < (int)frame_jobs.size())
                     {
-                        j              = frame_jobs[t];
-                        const auto& in = jobs[j].frame.info;
-                        if (params.resize_short_size != 0)
-                            throw error(AEONB_ERR_UNSUPPORTED, "'resize_short_size' for video frames is outside the accelerated path");
-                        if (params.angle != 0)
-                            throw error(AEONB_ERR_UNSUPPORTED, "rotation ('angle') of video frames is outside the accelerated path");
-                        d              = make_desc(params, in.width, in.height, fc.width, fc.height, true);
-                        layout_jpeg(j, &d);
+                        j = frame_jobs[t];
+                        d = plan_picture(s, j, params, fc.width, fc.height, true);
+                    }
+                    else
+                    {
+                        desc_rot[s].push_back(-1); // zero padding frame
+                        desc_pre[s].push_back(-1);
                     }
                     descs[s].push_back(d);
                     desc_job[s].push_back(j);
-                    desc_rot[s].push_back(-1);
                     desc_dst[s].push_back((int64_t)r * rec + (int64_t)t * fc.height * fc.width);
                 }
                 break;
@@ -782,9 +798,9 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                 aeonb_image_desc& d = descs[s][i];
                 const int         j = desc_job[s][i];
                 d.dst               = produced[o] + desc_dst[s][i];
-                if (pre)
+                if (desc_pre[s][i] >= 0)
                 {
-                    d.src              = static_cast<const uint8_t*>(resized_dev.p) + i * pre_slot;
+                    d.src              = static_cast<const uint8_t*>(resized_dev.p) + (size_t)desc_pre[s][i] * pre_slot;
                     d.src_pitch        = pre_pitch;
                     d.src_pixel_stride = 3;
                 }

@@ -323,3 +323,19 @@ def test_rotation_angle_through_the_provider_bit_exact(ctx):
         got = make_provider(ctx, cfg).run_host(recs)["image"]
         want = PipelineOracle(cfg).batch(recs)["image"]
         assert np.array_equal(got, want)
+
+
+def test_video_frames_with_rotation_and_resize_short(ctx, tmp_path):
+    """Every frame of a clip goes through transform_single_image with the clip's parameters (src/etl_video.cpp:56-74),
+    so 'angle' and 'resize_short_size' apply per frame, a short clip is still zero-padded."""
+    rng = np.random.default_rng(46)
+    frame_aug = {"type": "image", "crop_enable": True, "scale": [0.6, 0.9], "flip_enable": True, "angle": [-15, 15],
+                 "resize_short_size": 96, "interpolation_method": "LINEAR"}
+    cfg = {"batch_size": 3, "random_seed": 12,
+           "etl": [{"type": "video", "max_frame_count": 8, "frame": {"height": 64, "width": 64, "channels": 3}}],
+           "augmentation": [{"type": "image", "frame": frame_aug}]}
+    recs = [(make_avi(rng, str(tmp_path), nf),) for nf in (8, 5, 10)]
+    got = make_provider(ctx, cfg).run_host(recs)["video"]
+    want = PipelineOracle(cfg).batch(recs, lambda b: avi_frames(b, str(tmp_path)))["video"]
+    assert np.array_equal(got, want)
+    assert not got[1][:, 5:].any()
