@@ -279,9 +279,11 @@ namespace aeonb
                 break;
             case 0xC0:
             case 0xC1:
+            case 0xC2:
             {
+                f.progressive = m == 0xC2;
                 if (send - s < 6 || s[0] != 8)
-                    bad("only 8-bit baseline JPEG is supported");
+                    bad("only 8-bit JPEG is supported");
                 f.info.height = be16(s + 1);
                 f.info.width  = be16(s + 3);
                 f.info.ncomp  = s[5];
@@ -292,6 +294,7 @@ namespace aeonb
                 for (int i = 0; i < f.info.ncomp; ++i)
                 {
                     comp_id[i]   = s[6 + 3 * i];
+                    f.comp_id[i] = comp_id[i];
                     f.info.hs[i] = s[7 + 3 * i] >> 4;
                     f.info.vs[i] = s[7 + 3 * i] & 15;
                     comp_tq[i]   = s[8 + 3 * i];
@@ -301,8 +304,8 @@ namespace aeonb
                 have_sof = true;
                 break;
             }
-            case 0xC2: case 0xC3: case 0xC5: case 0xC6: case 0xC7: case 0xC9: case 0xCA: case 0xCB: case 0xCD: case 0xCE: case 0xCF:
-                bad("only baseline sequential Huffman JPEG is supported");
+            case 0xC3: case 0xC5: case 0xC6: case 0xC7: case 0xC9: case 0xCA: case 0xCB: case 0xCD: case 0xCE: case 0xCF:
+                bad("only baseline sequential and progressive Huffman JPEG are supported");
             case 0xC4:
                 while (s < send)
                 {
@@ -334,9 +337,11 @@ namespace aeonb
                 if (!have_sof)
                     bad("scan before frame header");
                 const int ns = s[0];
-                if (ns != f.info.ncomp || send - s < 1 + 2 * ns)
+                if (!f.progressive && (ns != f.info.ncomp || send - s < 1 + 2 * ns))
                     bad("non-interleaved scans are not supported");
-                for (int i = 0; i < ns; ++i)
+                f.first_sos  = p - 2;
+                f.stream_end = end;
+                for (int i = 0; i < ns && !f.progressive; ++i)
                 {
                     int c = -1;
                     for (int j = 0; j < f.info.ncomp; ++j)
@@ -406,8 +411,335 @@ namespace aeonb
         return r;
     }
 
+    namespace
+    {
+        // One scan of a progressive stream (ITU-T T.81 annex G): a band Ss..Se of the zig-zag sequence at bit position
+        // Al, either the first pass over it (Ah == 0) or a refinement that adds one bit (Ah == Al + 1).
+        struct progressive_scan
+        {
+            int ncomp = 0, comp[3]{}, dc_tab[3]{}, ac_tab[3]{};
+            int ss = 0, se = 0, ah = 0, al = 0;
+        };
+
+        inline int get_bits(bit_reader& br, int n)
+        {
+            br.refill();
+            const int v = static_cast<int>(br.peek(n));
+            br.skip(n);
+            return v;
+        }
+
+        // Refinement of the already non-zero coefficients from k on, until `zeros` still-zero positions have been
+        // passed (zeros < 0: to the end of the band): each gets one correction bit (figure G.7).
+        inline int refine_nonzeros(bit_reader& br, int16_t* blk, const uint8_t* zz, int k, int se, int zeros, int p1, int m1)
+        {
+            for (; k <= se; ++k)
+            {
+                int16_t& c = blk[zz[k]];
+                if (c != 0)
+                {
+                    if (get_bits(br, 1) && (c & p1) == 0)
+                        c = static_cast<int16_t>(c + (c >= 0 ? p1 : m1));
+                }
+                else if (zeros >= 0 && --zeros < 0)
+                    break;
+            }
+            return k;
+        }
+
+        void decode_progressive_scan(const jpeg_frame& f, const progressive_scan& sc, const jpeg_frame::huff* dc_tabs,
+                                     const jpeg_frame::huff* ac_tabs, int restart_interval, bit_reader& br, int16_t* const coef[3])
+        {
+            const aeonb_jpeg_info& in = f.info;
+            const uint8_t*         zz = k_zz_colmajor.v;
+            int hmax = 1, vmax = 1;
+            for (int c = 0; c < in.ncomp; ++c)
+            {
+                hmax = std::max(hmax, in.hs[c]);
+                vmax = std::max(vmax, in.vs[c]);
+            }
+            decode_table dct[3], act[3];
+            for (int i = 0; i < sc.ncomp; ++i)
+            {
+                if (sc.ss == 0 && sc.ah == 0)
+                    dct[i].build(dc_tabs[sc.dc_tab[i]], false);
+                if (sc.ss > 0)
+                    act[i].build(ac_tabs[sc.ac_tab[i]], true);
+            }
+            int       pred[3]       = {0, 0, 0};
+            int       eobrun        = 0;
+            int       until_restart = restart_interval ? restart_interval : -1;
+            const int p1 = 1 << sc.al, m1 = -(1 << sc.al);
+            auto restart_check = [&]() {
+                if (until_restart == 0)
+                {
+                    br.restart();
+                    pred[0] = pred[1] = pred[2] = 0;
+                    eobrun                      = 0;
+                    until_restart               = restart_interval;
+                }
+                if (until_restart > 0)
+                    --until_restart;
+            };
+            auto block_at = [&](int c, int bx, int by) { return coef[c] + (static_cast<size_t>(by) * in.blocks_w[c] + bx) * 64; };
+            auto decode_block = [&](int i, int16_t* blk) {
+                const int c = sc.comp[i];
+                if (sc.ss == 0)
+                {
+                    if (sc.ah == 0)
+                    {
+                        br.refill();
+                        const int t = br.decode(dct[i]);
+                        if (t > 15)
+                            bad("bad DC coefficient");
+                        if (t)
+                        {
+                            br.refill();
+                            pred[c] += br.receive_extend(t);
+                        }
+                        blk[0] = static_cast<int16_t>(pred[c] * (1 << sc.al));
+                    }
+                    else if (get_bits(br, 1))
+                        blk[0] = static_cast<int16_t>(blk[0] | p1);
+                    return;
+                }
+                if (sc.ah == 0)
+                {
+                    if (eobrun > 0)
+                    {
+                        --eobrun;
+                        return;
+                    }
+                    for (int k = sc.ss; k <= sc.se; ++k)
+                    {
+                        br.refill();
+                        const int rs = br.decode(act[i]);
+                        const int r = rs >> 4, s = rs & 15;
+                        if (s)
+                        {
+                            k += r;
+                            if (k > 63)
+                                bad("corrupt coefficient run");
+                            br.refill();
+                            blk[zz[k]] = static_cast<int16_t>(br.receive_extend(s) * (1 << sc.al));
+                        }
+                        else if (r == 15)
+                            k += 15;
+                        else
+                        {
+                            eobrun = 1 << r;
+                            if (r)
+                                eobrun += get_bits(br, r);
+                            --eobrun;
+                            break;
+                        }
+                    }
+                    return;
+                }
+                // refinement of an AC band
+                int k = sc.ss;
+                if (eobrun == 0)
+                {
+                    for (; k <= sc.se; ++k)
+                    {
+                        br.refill();
+                        const int rs = br.decode(act[i]);
+                        int       r = rs >> 4, s = rs & 15;
+                        int       value = 0;
+                        if (s)
+                            value = get_bits(br, 1) ? p1 : m1; // a newly non-zero coefficient has magnitude 1 at this bit
+                        else if (r != 15)
+                        {
+                            eobrun = 1 << r;
+                            if (r)
+                                eobrun += get_bits(br, r);
+                            break;
+                        }
+                        k = refine_nonzeros(br, blk, zz, k, sc.se, r, p1, m1);
+                        if (k > 63)
+                            bad("corrupt coefficient run");
+                        if (s)
+                            blk[zz[k]] = static_cast<int16_t>(value);
+                    }
+                }
+                if (eobrun > 0)
+                {
+                    refine_nonzeros(br, blk, zz, k, sc.se, -1, p1, m1);
+                    --eobrun;
+                }
+            };
+            if (sc.ncomp > 1)
+            {
+                // interleaved (DC scans only): MCU order, all hs x vs blocks of every component
+                const int mcux = in.blocks_w[0] / in.hs[0], mcuy = in.blocks_h[0] / in.vs[0];
+                for (int my = 0; my < mcuy; ++my)
+                    for (int mx = 0; mx < mcux; ++mx)
+                    {
+                        restart_check();
+                        for (int i = 0; i < sc.ncomp; ++i)
+                        {
+                            const int c = sc.comp[i];
+                            for (int by = 0; by < in.vs[c]; ++by)
+                                for (int bx = 0; bx < in.hs[c]; ++bx)
+                                    decode_block(i, block_at(c, mx * in.hs[c] + bx, my * in.vs[c] + by));
+                        }
+                    }
+            }
+            else
+            {
+                // non-interleaved: the component's own blocks in raster order, only those that hold picture samples
+                const int c  = sc.comp[0];
+                const int cw = (in.width * in.hs[c] + hmax - 1) / hmax, ch = (in.height * in.vs[c] + vmax - 1) / vmax;
+                const int bw = (cw + 7) / 8, bh = (ch + 7) / 8;
+                for (int by = 0; by < bh; ++by)
+                    for (int bx = 0; bx < bw; ++bx)
+                    {
+                        restart_check();
+                        decode_block(0, block_at(c, bx, by));
+                    }
+            }
+        }
+
+        // All scans of a progressive stream into whole-picture planes (zeroed here).
+        void jpeg_progressive_decode(const jpeg_frame& f, int16_t* const coef[3])
+        {
+            const aeonb_jpeg_info& in = f.info;
+            for (int c = 0; c < in.ncomp; ++c)
+                std::memset(coef[c], 0, static_cast<size_t>(in.coef_count[c]) * sizeof(int16_t));
+            jpeg_frame::huff dc[4], ac[4];
+            for (int i = 0; i < 4; ++i)
+            {
+                dc[i] = f.dc[i];
+                ac[i] = f.ac[i];
+            }
+            int            restart_interval = f.restart_interval;
+            const uint8_t* p   = f.first_sos;
+            const uint8_t* end = f.stream_end;
+            int            scans = 0;
+            while (p && p + 4 <= end)
+            {
+                // p stands on a marker (0xFF, code)
+                while (p < end && *p != 0xFF)
+                    ++p;
+                while (p < end && *p == 0xFF)
+                    ++p;
+                if (p >= end)
+                    break;
+                const int m = *p++;
+                if (m == 0xD9)
+                    break;
+                if ((m >= 0xD0 && m <= 0xD7) || m == 0x01 || m == 0x00)
+                    continue;
+                if (p + 2 > end)
+                    bad("truncated header");
+                const unsigned len = be16(p);
+                if (len < 2 || p + len > end)
+                    bad("truncated header");
+                const uint8_t* s    = p + 2;
+                const uint8_t* send = p + len;
+                p                   = send;
+                if (m == 0xC4)
+                {
+                    while (s < send)
+                    {
+                        const int tc = *s >> 4, th = *s & 15;
+                        ++s;
+                        if (tc > 1 || th > 3 || s + 16 > send)
+                            bad("bad Huffman table");
+                        jpeg_frame::huff& h = tc ? ac[th] : dc[th];
+                        h.present           = true;
+                        h.bits[0]           = 0;
+                        int n               = 0;
+                        for (int i = 1; i <= 16; ++i)
+                            n += (h.bits[i] = s[i - 1]);
+                        s += 16;
+                        if (n > 256 || s + n > send)
+                            bad("bad Huffman table");
+                        std::memset(h.vals, 0, 256);
+                        std::memcpy(h.vals, s, n);
+                        s += n;
+                    }
+                }
+                else if (m == 0xDD)
+                {
+                    if (send - s < 2)
+                        bad("bad restart interval");
+                    restart_interval = be16(s);
+                }
+                else if (m == 0xDA)
+                {
+                    progressive_scan sc;
+                    sc.ncomp = s[0];
+                    if (sc.ncomp < 1 || sc.ncomp > in.ncomp || send - s < 4 + 2 * sc.ncomp)
+                        bad("bad scan header");
+                    for (int i = 0; i < sc.ncomp; ++i)
+                    {
+                        int c = -1;
+                        for (int j = 0; j < in.ncomp; ++j)
+                            if (f.comp_id[j] == s[1 + 2 * i])
+                                c = j;
+                        if (c < 0)
+                            bad("bad scan header");
+                        sc.comp[i]   = c;
+                        sc.dc_tab[i] = s[2 + 2 * i] >> 4;
+                        sc.ac_tab[i] = s[2 + 2 * i] & 15;
+                        if (sc.dc_tab[i] > 3 || sc.ac_tab[i] > 3)
+                            bad("bad scan header");
+                    }
+                    const uint8_t* t = s + 1 + 2 * sc.ncomp;
+                    sc.ss = t[0];
+                    sc.se = t[1];
+                    sc.ah = t[2] >> 4;
+                    sc.al = t[2] & 15;
+                    const bool band_ok = sc.ss == 0 ? sc.se == 0 : (sc.ss <= sc.se && sc.se <= 63 && sc.ncomp == 1);
+                    if (!band_ok || sc.al > 13 || (sc.ah != 0 && sc.ah != sc.al + 1))
+                        bad("bad progressive scan parameters");
+                    bit_reader br(send, end);
+                    decode_progressive_scan(f, sc, dc, ac, restart_interval, br, coef);
+                    p = br.p; // at or before the marker that ends the scan's data
+                    // skip what is left of the entropy-coded segment: to the next marker that is not a restart marker
+                    while (p + 1 < end && !(p[0] == 0xFF && p[1] != 0x00 && p[1] != 0xFF && !(p[1] >= 0xD0 && p[1] <= 0xD7)))
+                        ++p;
+                    if (++scans > 1000)
+                        bad("too many scans");
+                }
+            }
+            if (scans == 0)
+                bad("no image data");
+        }
+    }
+
     void jpeg_entropy_decode(const jpeg_frame& f, int16_t* const coef[3], const jpeg_roi* roi)
     {
+        if (f.progressive)
+        {
+            const aeonb_jpeg_info& pin = f.info;
+            if (!roi)
+            {
+                jpeg_progressive_decode(f, coef);
+                return;
+            }
+            // the scans cover the whole picture: decode all of it, then keep the region's blocks
+            std::vector<int16_t> whole[3];
+            int16_t*             planes[3] = {nullptr, nullptr, nullptr};
+            for (int c = 0; c < pin.ncomp; ++c)
+            {
+                whole[c].resize(static_cast<size_t>(pin.coef_count[c]));
+                planes[c] = whole[c].data();
+            }
+            jpeg_progressive_decode(f, planes);
+            const int pmcux = pin.blocks_w[0] / pin.hs[0], pmcuy = pin.blocks_h[0] / pin.vs[0];
+            const int x0 = std::max(roi->mx0, 0), x1 = std::min(roi->mx1, pmcux), y0 = std::max(roi->my0, 0), y1 = std::min(roi->my1, pmcuy);
+            for (int c = 0; c < pin.ncomp; ++c)
+            {
+                const int bw = (x1 - x0) * pin.hs[c];
+                for (int by = 0; by < (y1 - y0) * pin.vs[c]; ++by)
+                    std::memcpy(coef[c] + static_cast<size_t>(by) * bw * 64,
+                                planes[c] + (static_cast<size_t>(y0 * pin.vs[c] + by) * pin.blocks_w[c] + x0 * pin.hs[c]) * 64,
+                                static_cast<size_t>(bw) * 64 * sizeof(int16_t));
+            }
+            return;
+        }
         const aeonb_jpeg_info& in = f.info;
         decode_table           dct[3], act[3];
         for (int c = 0; c < in.ncomp; ++c)
@@ -498,6 +830,8 @@ namespace aeonb
     {
         std::memset(tables, 0, 4 * 272);
         d                     = aeonb_entropy_desc{};
+        if (f.progressive)
+            return false; // several scans over the same coefficients: decoded on the host
         const aeonb_jpeg_info& in = f.info;
         int dc_ids[2] = {-1, -1}, ac_ids[2] = {-1, -1};
         auto slot_of = [](int ids[2], int id) {
@@ -610,7 +944,7 @@ int aeonb_jpeg_entropy_prepare(const void* data, size_t size, aeonb_jpeg_info* i
         jpeg_frame f;
         jpeg_parse(data, size, f);
         if (!jpeg_entropy_prepare(f, tables, *desc))
-            throw error(AEONB_ERR_UNSUPPORTED, "the scan uses more than two DC or two AC Huffman tables");
+            throw error(AEONB_ERR_UNSUPPORTED, "progressive stream, or a scan with more than two DC or two AC Huffman tables: use aeonb_jpeg_entropy_decode");
         *info = f.info;
         std::memcpy(quant, f.quant, sizeof f.quant);
         *scan_offset = static_cast<size_t>(f.scan - static_cast<const uint8_t*>(data));

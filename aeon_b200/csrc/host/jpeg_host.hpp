@@ -31,11 +31,18 @@ namespace aeonb
             uint8_t  bits[17]{};
             uint8_t  vals[256]{};
         } dc[4], ac[4];
+        // Progressive (SOF2) streams: several scans refine the coefficients; `first_sos` points at the first SOS
+        // marker (0xFF 0xDA), the Huffman tables above are those defined before it, `stream_end` ends the file.
+        bool           progressive = false;
+        const uint8_t* first_sos   = nullptr;
+        const uint8_t* stream_end  = nullptr;
+        int            comp_id[3]{};
     };
 
-    // Parses the headers up to the start of scan.  Throws aeonb::error(AEONB_ERR_DECODE) with
+    // Parses the headers up to the first start of scan.  Throws aeonb::error(AEONB_ERR_DECODE) with
     // aeon's message ("Decoding image failed due to invalid data in the image file.") on
-    // anything that is not a baseline sequential 8-bit JPEG with 1 or 3 components.
+    // anything that is not an 8-bit Huffman-coded JPEG (baseline sequential with one interleaved scan, or
+    // progressive) with 1 or 3 components.
     void jpeg_parse(const void* data, size_t size, jpeg_frame& frame);
 
     // A rectangle of MCUs [mx0, mx1) x [my0, my1) to keep.  The bit stream is sequential, so everything
@@ -49,7 +56,8 @@ namespace aeonb
     // The MCU rectangle covering the pixel box [x0,x1) x [y0,y1) of the picture plus one chroma sample of context.
     jpeg_roi jpeg_roi_for_box(const aeonb_jpeg_info& info, int x0, int y0, int x1, int y1);
 
-    // Entropy-decodes the scan.  Without a region coef[c] must hold info.coef_count[c] int16 values; with
+    // Entropy-decodes the scan (all scans of a progressive stream: spectral selection and successive approximation,
+    // ITU-T T.81 annex G).  Without a region coef[c] must hold info.coef_count[c] int16 values; with
     // one, the compact plane described above.  The planes are fully overwritten (absent coefficients are zero).
     void jpeg_entropy_decode(const jpeg_frame& frame, int16_t* const coef[3], const jpeg_roi* roi = nullptr);
 

@@ -110,3 +110,19 @@ def test_region_decode_equals_the_same_pixels_of_the_full_decode(ctx):
                 ctx.synchronize()
             got = out.cpu().numpy()[:, :rw * 3].reshape(rh, rw, 3)
             assert np.array_equal(got[cy - ry:cy - ry + ch, cx - rx:cx - rx + cw], ref[cy:cy + ch, cx:cx + cw]), (h, w, cx, cy, cw, ch)
+
+
+def test_progressive_streams_match_opencv(ctx):
+    """Progressive files (SOF2) are entropy-decoded on the host, scan by scan; the GPU back end is the same."""
+    import cv2
+    rng = np.random.default_rng(29)
+    cases = []
+    for (h, w) in [(64, 64), (37, 53), (200, 150), (8, 8), (1, 1), (375, 500), (33, 47)]:
+        for extra in ([], [cv2.IMWRITE_JPEG_SAMPLING_FACTOR, cv2.IMWRITE_JPEG_SAMPLING_FACTOR_444],
+                      [cv2.IMWRITE_JPEG_SAMPLING_FACTOR, cv2.IMWRITE_JPEG_SAMPLING_FACTOR_422], [cv2.IMWRITE_JPEG_RST_INTERVAL, 3]):
+            cases.append(jpeg_bytes(gradient_image(rng, h, w), int(rng.integers(30, 100)), [cv2.IMWRITE_JPEG_PROGRESSIVE, 1] + extra))
+    cases.append(jpeg_bytes(gradient_image(rng, 45, 30)[..., 0], 85, [cv2.IMWRITE_JPEG_PROGRESSIVE, 1]))
+    assert all(b"\xff\xc2" in c for c in cases)
+    got = decode_gpu(ctx, cases)
+    for i, b in enumerate(cases):
+        assert np.array_equal(got[i], cv2.imdecode(np.frombuffer(b, np.uint8), cv2.IMREAD_COLOR)), "case %d" % i

@@ -339,3 +339,19 @@ def test_video_frames_with_rotation_and_resize_short(ctx, tmp_path):
     want = PipelineOracle(cfg).batch(recs, lambda b: avi_frames(b, str(tmp_path)))["video"]
     assert np.array_equal(got, want)
     assert not got[1][:, 5:].any()
+
+
+def test_progressive_and_baseline_records_in_one_batch(ctx):
+    """A progressive file takes the host Huffman decoder (its scans revisit the same coefficients), a baseline one
+    the GPU decoder; both end in the same kernels and the batch equals the oracle's."""
+    import cv2
+    rng = np.random.default_rng(58)
+    recs = []
+    for i in range(8):
+        img = gradient_image(rng, int(rng.integers(200, 400)), int(rng.integers(200, 400)))
+        recs.append((jpeg_bytes(img, 90, [cv2.IMWRITE_JPEG_PROGRESSIVE, 1] if i % 2 else []),))
+    cfg = {"batch_size": 8, "random_seed": 43, "etl": [{"type": "image", "height": 96, "width": 96, "output_type": "uint8_t"}],
+           "augmentation": [AUG_C1]}
+    got = make_provider(ctx, cfg).run_host(recs)["image"]
+    want = PipelineOracle(cfg).batch(recs)["image"]
+    assert np.array_equal(got, want)

@@ -1,0 +1,55 @@
+"""Host decoder for progressive JPEG (ITU-T T.81 annex G: spectral selection + successive approximation).
+
+OpenCV writes the same quantised coefficients whether it codes them as one baseline scan or as libjpeg's ten
+progressive scans, so decoding both files must give the same coefficient planes (over the blocks that hold
+picture samples: baseline also codes the padding blocks of partial MCUs, a progressive AC scan does not)."""
+import numpy as np
+import pytest
+
+from tests.synth import gradient_image
+
+
+def planes(blob):
+    from aeon_b200 import kernels as K
+    return K.jpeg_entropy_decode(blob)
+
+
+@pytest.mark.parametrize("size", [(64, 64), (37, 53), (200, 150), (8, 8), (1, 1), (375, 500)])
+def test_progressive_and_baseline_files_hold_the_same_coefficients(size):
+    import cv2
+    h, w = size
+    rng = np.random.default_rng(h * 1000 + w)
+    for extra in ([], [cv2.IMWRITE_JPEG_SAMPLING_FACTOR, cv2.IMWRITE_JPEG_SAMPLING_FACTOR_444],
+                  [cv2.IMWRITE_JPEG_SAMPLING_FACTOR, cv2.IMWRITE_JPEG_SAMPLING_FACTOR_422], [cv2.IMWRITE_JPEG_RST_INTERVAL, 5],
+                  [cv2.IMWRITE_JPEG_OPTIMIZE, 1]):
+        img = gradient_image(rng, h, w)
+        q = int(rng.integers(40, 100))
+        base = cv2.imencode(".jpg", img, [cv2.IMWRITE_JPEG_QUALITY, q] + extra)[1].tobytes()
+        prog = cv2.imencode(".jpg", img, [cv2.IMWRITE_JPEG_QUALITY, q, cv2.IMWRITE_JPEG_PROGRESSIVE, 1] + extra)[1].tobytes()
+        assert b"\xff\xc2" in prog and b"\xff\xc2" not in base[:600]
+        ib, cb, qb = planes(base)
+        ip, cp, qp = planes(prog)
+        assert (ib.width, ib.height, ib.ncomp) == (ip.width, ip.height, ip.ncomp) == (w, h, 3)
+        hmax, vmax = max(ib.hs[:3]), max(ib.vs[:3])
+        for c in range(3):
+            bw, bh = ib.blocks_w[c], ib.blocks_h[c]
+            nbw, nbh = -(-(-(-w * ib.hs[c] // hmax)) // 8), -(-(-(-h * ib.vs[c] // vmax)) // 8)
+            a = cb[c].reshape(bh, bw, 64)[:nbh, :nbw]
+            b = cp[c].reshape(bh, bw, 64)[:nbh, :nbw]
+            assert np.array_equal(a, b), (size, extra, c)
+            assert np.array_equal(qb[c], qp[c])
+
+
+def test_grey_progressive_and_truncated_stream():
+    import cv2
+    from aeon_b200 import _lib as L
+    rng = np.random.default_rng(5)
+    img = gradient_image(rng, 45, 30)[..., 0]
+    base = cv2.imencode(".jpg", img, [cv2.IMWRITE_JPEG_QUALITY, 85])[1].tobytes()
+    prog = cv2.imencode(".jpg", img, [cv2.IMWRITE_JPEG_QUALITY, 85, cv2.IMWRITE_JPEG_PROGRESSIVE, 1])[1].tobytes()
+    ib, cb, _ = planes(base)
+    ip, cp, _ = planes(prog)
+    assert ip.ncomp == 1 and np.array_equal(cb[0], cp[0])   # one component: no padding blocks differ (both code ceil sizes)
+    sos = prog.index(b"\xff\xda")
+    with pytest.raises(L.AeonError, match="Decoding image failed"):
+        planes(prog[:sos])                                   # headers only
