@@ -48,6 +48,10 @@ class RotateDesc(C.Structure):
     ]
 
 
+class OrientDesc(C.Structure):
+    _fields_ = RotateDesc._fields_[:5] + [("orientation", C.c_int32)] + RotateDesc._fields_[6:]
+
+
 class JpegDesc(C.Structure):
     _fields_ = [
         ("coef", C.c_void_p * 3), ("quant", C.c_void_p * 3),
@@ -73,7 +77,7 @@ class JpegInfo(C.Structure):
         ("width", C.c_int32), ("height", C.c_int32), ("ncomp", C.c_int32),
         ("hs", C.c_int32 * 3), ("vs", C.c_int32 * 3),
         ("blocks_w", C.c_int32 * 3), ("blocks_h", C.c_int32 * 3),
-        ("coef_count", C.c_int64 * 3),
+        ("coef_count", C.c_int64 * 3), ("orientation", C.c_int32), ("reserved0", C.c_int32),
     ]
 
 
@@ -99,6 +103,7 @@ PROTOTYPES = {
     "aeonb_image_batch_bytes": (C.c_int64, [C.POINTER(ImageDesc), C.c_int, C.POINTER(ImageLayout)]),
     "aeonb_image_batch_noalloc": (C.c_int, [C.POINTER(ImageDesc), C.c_int, C.POINTER(ImageLayout), C.c_void_p]),
     "aeonb_rotate_batch": (C.c_int, [C.c_void_p, C.POINTER(RotateDesc), C.c_int]),
+    "aeonb_orient_batch": (C.c_int, [C.c_void_p, C.POINTER(OrientDesc), C.c_int]),
     "aeonb_jpeg_backend_batch": (C.c_int, [C.c_void_p, C.POINTER(JpegDesc), C.c_int]),
     "aeonb_jpeg_backend_bytes": (C.c_int64, [C.POINTER(JpegDesc), C.c_int]),
     "aeonb_jpeg_entropy_batch": (C.c_int, [C.c_void_p, C.POINTER(EntropyDesc), C.c_int]),

@@ -223,13 +223,52 @@ namespace aeonb
         inline unsigned be16(const uint8_t* p) { return (unsigned(p[0]) << 8) | p[1]; }
     }
 
+    namespace
+    {
+        // EXIF orientation (tag 0x0112 of IFD0) from the payload of an APP1 segment; 1 when absent or malformed.
+        int exif_orientation(const uint8_t* s, const uint8_t* send)
+        {
+            if (send - s < 14 || std::memcmp(s, "Exif\0\0", 6) != 0)
+                return 1;
+            const uint8_t* t  = s + 6; // TIFF header
+            const bool     le = t[0] == 'I' && t[1] == 'I';
+            if (!le && !(t[0] == 'M' && t[1] == 'M'))
+                return 1;
+            auto u16 = [&](const uint8_t* q) { return le ? unsigned(q[0]) | unsigned(q[1]) << 8 : unsigned(q[0]) << 8 | q[1]; };
+            auto u32 = [&](const uint8_t* q) {
+                return le ? unsigned(q[0]) | unsigned(q[1]) << 8 | unsigned(q[2]) << 16 | unsigned(q[3]) << 24
+                          : unsigned(q[0]) << 24 | unsigned(q[1]) << 16 | unsigned(q[2]) << 8 | q[3];
+            };
+            if (u16(t + 2) != 0x002A)
+                return 1;
+            const size_t room = static_cast<size_t>(send - t);
+            const size_t ifd  = u32(t + 4);
+            if (ifd + 2 > room)
+                return 1;
+            const unsigned count = u16(t + ifd);
+            for (unsigned i = 0; i < count; ++i)
+            {
+                const size_t e = ifd + 2 + 12 * static_cast<size_t>(i);
+                if (e + 12 > room)
+                    break;
+                if (u16(t + e) == 0x0112)
+                {
+                    const unsigned v = u16(t + e + 8);
+                    return v >= 1 && v <= 8 ? static_cast<int>(v) : 1;
+                }
+            }
+            return 1;
+        }
+    }
+
     void jpeg_parse(const void* data, size_t size, jpeg_frame& f)
     {
         const uint8_t* d   = static_cast<const uint8_t*>(data);
         const uint8_t* end = d + size;
         if (size < 4 || d[0] != 0xFF || d[1] != 0xD8)
             bad("not a JPEG stream");
-        f = jpeg_frame();
+        f                  = jpeg_frame();
+        f.info.orientation = 1;
         set_std(f.dc[0], k_std_dc_luma_bits, k_std_dc_vals, 12);
         set_std(f.dc[1], k_std_dc_chroma_bits, k_std_dc_vals, 12);
         set_std(f.ac[0], k_std_ac_luma_bits, k_std_ac_luma_vals, 162);
@@ -331,6 +370,10 @@ namespace aeonb
                 if (send - s < 2)
                     bad("bad restart interval");
                 f.restart_interval = be16(s);
+                break;
+            case 0xE1:
+                if (f.info.orientation == 1)
+                    f.info.orientation = exif_orientation(s, send);
                 break;
             case 0xDA:
             {

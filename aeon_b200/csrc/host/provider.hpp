@@ -73,6 +73,12 @@ namespace aeonb
         int            roi_blocks_w[3]{}, roi_blocks_h[3]{};
         // Device entropy decoding: the staging buffer then carries the quantiser tables, the Huffman tables and the
         // scan bytes instead of coefficients; planes and the decoder's work area live in a device-only arena.
+        // The picture as cv::imdecode delivers it: pw x ph after the EXIF orientation turn (sizes swapped for tags 5..8).
+        // A turned picture is decoded whole and turned by a pass of its own into the orientation arena.
+        int                pw = 0, ph = 0;
+        bool               oriented = false;
+        size_t             opixel_off = 0;
+        int                opitch = 0;
         bool               on_device = false;
         aeonb_entropy_desc edesc{};
         uint8_t            tables[4 * 272]{};
@@ -104,6 +110,7 @@ struct aeonb_provider
     aeonb::device_buffer                 staging_dev;
     aeonb::device_buffer                 coef_dev;     // device entropy decoding: status words, coefficient planes, work areas
     aeonb::device_buffer                 pixels_dev;   // decoded pictures
+    aeonb::device_buffer                 oriented_dev; // pictures after the EXIF orientation pass
     aeonb::device_buffer                 rotated_dev;  // pictures after the rotation pass
     aeonb::device_buffer                 resized_dev;  // pictures after the resize_short pass
     // Device-side outputs of batches delivered to host memory, double buffered: the copy of batch t to the host

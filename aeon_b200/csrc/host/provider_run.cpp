@@ -215,7 +215,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     size_t              rotated_bytes = 0;
     vector<vector<aeonb_specgram_desc>> sdescs(nin);
     vector<vector<size_t>>           sdesc_off(nin);
-    size_t stage_bytes = 0, pixel_bytes = 0, coef_bytes = 0;
+    size_t stage_bytes = 0, pixel_bytes = 0, coef_bytes = 0, oriented_bytes = 0;
 
     for (size_t o = 0; o < outputs.size(); ++o)
         if (outputs[o].host_produced)
@@ -227,6 +227,9 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         job.data = static_cast<const uint8_t*>(data);
         job.size = size;
         jpeg_parse(data, size, job.frame);
+        const bool swapped = job.frame.info.orientation >= 5;
+        job.pw             = swapped ? job.frame.info.height : job.frame.info.width;
+        job.ph             = swapped ? job.frame.info.width : job.frame.info.height;
         jobs.push_back(job);
         return (int)jobs.size() - 1;
     };
@@ -242,7 +245,14 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         const int mw = 8 * in.hs[0], mh = 8 * in.vs[0];
         const int mcux = in.blocks_w[0] / in.hs[0], mcuy = in.blocks_h[0] / in.vs[0];
         jpeg_roi roi{0, 0, mcux, mcuy};
-        if (d && roi_decode) // a crop box that lies on the zero canvas only reads nothing of the picture: one MCU is kept
+        job.oriented = in.orientation != 1;
+        if (job.oriented)
+        {
+            job.opitch     = (int)align_up((size_t)job.pw * 3, 16);
+            job.opixel_off = align_up(oriented_bytes, 256);
+            oriented_bytes = job.opixel_off + (size_t)job.opitch * job.ph;
+        }
+        else if (d && roi_decode) // a crop box that lies on the zero canvas only reads nothing of the picture: one MCU is kept
             roi = jpeg_roi_for_box(in, d->crop_x - d->canvas_x, d->crop_y - d->canvas_y, d->crop_x + d->crop_w - d->canvas_x,
                                    d->crop_y + d->crop_h - d->canvas_y);
         job.roi = roi;
@@ -301,8 +311,11 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     // possibly expanded, picture before the crop; src/etl_image.cpp:160-168) -- and returns the main descriptor.
     std::unordered_map<int, int> rotation_of_job; // a repeated video frame is rotated once
     auto plan_picture = [&](int s, int j, const image_params& params, int slot_w, int slot_h, bool exact_fit) {
-        const aeonb_jpeg_info in = jobs[j].frame.info;
-        int                   rot = -1;
+        struct
+        {
+            int width, height;
+        } const in{jobs[j].pw, jobs[j].ph}; // the picture as delivered (after the EXIF turn)
+        int rot = -1;
         if (params.angle != 0)
         {
             auto it = rotation_of_job.find(j);
@@ -391,10 +404,9 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                 if (size == 0)
                     empty("encoded image");
                 const int  j  = plan_jpeg(data, size);
-                const auto& in = jobs[j].frame.info;
                 if (!have_params)
                 {
-                    params      = factory.make_params(engine, in.width, in.height, sg.image.width, sg.image.height);
+                    params      = factory.make_params(engine, jobs[j].pw, jobs[j].ph, sg.image.width, sg.image.height);
                     have_params = true;
                 }
                 aeonb_image_desc d = plan_picture(s, j, params, sg.image.width, sg.image.height, !factory.fixed_aspect_ratio);
@@ -429,10 +441,10 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                         prev = plan_jpeg(frames[t].data, frames[t].size);
                     frame_jobs.push_back(prev);
                 }
-                const auto& first = jobs[frame_jobs[0]].frame.info;
+                const jpeg_job& first = jobs[frame_jobs[0]];
                 if (!have_params)
                 {
-                    params      = video_factory.make_params(engine, first.width, first.height, fc.width, fc.height);
+                    params      = video_factory.make_params(engine, first.pw, first.ph, fc.width, fc.height);
                     have_params = true;
                 }
                 for (int t = 0; t < T; ++t)
@@ -538,6 +550,8 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     staging.reserve(stage_bytes + 256);
     staging_dev.reserve(stage_bytes + 256);
     pixels_dev.reserve(pixel_bytes + 256);
+    if (oriented_bytes > 0)
+        oriented_dev.reserve(oriented_bytes + 256);
     if (rotated_bytes > 0)
         rotated_dev.reserve(rotated_bytes + 256);
     const size_t status_room = align_up(sizeof(int32_t) * (jobs.size() + 1), 256);
@@ -685,18 +699,53 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         check_status(aeonb_jpeg_backend_batch(ctx, jd.data(), njobs));
         h2d_bytes += (int64_t)(sizeof(aeonb_jpeg_desc) * njobs);
     }
+    // Where a decoded picture stands for the passes that read it: the decoded region, or the turned copy.
+    struct picture
+    {
+        const uint8_t* p;
+        int            pitch, stride, w, h, x, y; // (x, y): where the region's origin lies in the whole picture
+    };
+    auto picture_of = [&](int j) {
+        const jpeg_job& job = jobs[j];
+        if (job.oriented)
+            return picture{static_cast<const uint8_t*>(oriented_dev.p) + job.opixel_off, job.opitch, 3, job.pw, job.ph, 0, 0};
+        return picture{static_cast<const uint8_t*>(pixels_dev.p) + job.pixel_off, job.pitch, pixel_stride, job.rw, job.rh, job.rx, job.ry};
+    };
+    {
+        vector<aeonb_orient_desc> od;
+        for (const jpeg_job& job : jobs)
+            if (job.oriented)
+            {
+                aeonb_orient_desc o{};
+                o.src              = static_cast<const uint8_t*>(pixels_dev.p) + job.pixel_off;
+                o.src_pitch        = job.pitch;
+                o.src_pixel_stride = pixel_stride;
+                o.width            = job.rw;
+                o.height           = job.rh;
+                o.orientation      = job.frame.info.orientation;
+                o.dst              = static_cast<uint8_t*>(oriented_dev.p) + job.opixel_off;
+                o.dst_pitch        = job.opitch;
+                o.dst_pixel_stride = 3;
+                od.push_back(o);
+            }
+        if (!od.empty())
+        {
+            check_status(aeonb_orient_batch(ctx, od.data(), (int)od.size()));
+            h2d_bytes += (int64_t)(sizeof(aeonb_orient_desc) * od.size());
+        }
+    }
     if (!rotations.empty())
     {
         vector<aeonb_rotate_desc> rd(rotations.size());
         for (size_t i = 0; i < rotations.size(); ++i)
         {
             const rotation& ro  = rotations[i];
-            const jpeg_job& job = jobs[ro.job];
-            rd[i].src              = static_cast<const uint8_t*>(pixels_dev.p) + job.pixel_off;
-            rd[i].src_pitch        = job.pitch;
-            rd[i].src_pixel_stride = pixel_stride;
-            rd[i].width            = job.rw;
-            rd[i].height           = job.rh;
+            const picture   pic = picture_of(ro.job);
+            rd[i].src              = pic.p;
+            rd[i].src_pitch        = pic.pitch;
+            rd[i].src_pixel_stride = pic.stride;
+            rd[i].width            = pic.w;
+            rd[i].height           = pic.h;
             rd[i].angle            = ro.angle;
             rd[i].dst              = static_cast<uint8_t*>(rotated_dev.p) + ro.off;
             rd[i].dst_pitch        = ro.pitch;
@@ -779,9 +828,10 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                 {
                     aeonb_image_desc& d = pre_descs[s][i];
                     const int         j = pre_job[s][i];
-                    d.src               = static_cast<const uint8_t*>(pixels_dev.p) + jobs[j].pixel_off;
-                    d.src_pitch         = jobs[j].pitch;
-                    d.src_pixel_stride  = pixel_stride;
+                    const picture     pic = picture_of(j);
+                    d.src               = pic.p;
+                    d.src_pitch         = pic.pitch;
+                    d.src_pixel_stride  = pic.stride;
                     if (pre_rot[s][i] >= 0)
                     {
                         d.src              = static_cast<const uint8_t*>(rotated_dev.p) + rotations[pre_rot[s][i]].off;
@@ -813,13 +863,14 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                 else if (j >= 0)
                 {
                     // the decoded region stands where that part of the picture stands on the canvas
-                    d.src              = static_cast<const uint8_t*>(pixels_dev.p) + jobs[j].pixel_off;
-                    d.src_pitch        = jobs[j].pitch;
-                    d.src_pixel_stride = pixel_stride;
-                    d.src_w            = jobs[j].rw;
-                    d.src_h            = jobs[j].rh;
-                    d.canvas_x += jobs[j].rx;
-                    d.canvas_y += jobs[j].ry;
+                    const picture pic  = picture_of(j);
+                    d.src              = pic.p;
+                    d.src_pitch        = pic.pitch;
+                    d.src_pixel_stride = pic.stride;
+                    d.src_w            = pic.w;
+                    d.src_h            = pic.h;
+                    d.canvas_x += pic.x;
+                    d.canvas_y += pic.y;
                 }
             }
             check_status(aeonb_image_batch(ctx, descs[s].data(), (int)descs[s].size(), &L));

@@ -1,4 +1,8 @@
-// Rotation pre-pass of the image path for sm_100a: aeon's image::rotate (src/image.cpp:53-75), i.e.
+// Whole-picture pre-passes of the image path for sm_100a.
+//
+// orient_kernel: the EXIF orientation turn cv::imdecode applies after decoding (a pure permutation of pixels).
+//
+// rotate_kernel: aeon's image::rotate (src/image.cpp:53-75), i.e.
 // cv::warpAffine(src, dst, getRotationMatrix2D(centre, angle, 1), src.size(), INTER_LINEAR, BORDER_CONSTANT, 0)
 // on 8-bit interleaved pictures, bit for bit.
 //
@@ -59,6 +63,47 @@ namespace aeonb
                     const int p10 = in_y1 && in_x0 ? r1[o0 + c] : 0, p11 = in_y1 && in_x1 ? r1[o1 + c] : 0;
                     d[c] = (uint8_t)((p00 * w00 + p01 * w01 + p10 * w10 + p11 * w11 + (1 << 14)) >> 15);
                 }
+            }
+        }
+    }
+
+    namespace
+    {
+        struct orient_job
+        {
+            const uint8_t* src;
+            uint8_t*       dst;
+            int32_t        src_pitch, src_stride, dst_pitch, dst_stride, width, height, orientation;
+        };
+
+        // EXIF orientation as OpenCV applies it after decoding: destination pixel (x, y) comes from source column /
+        // row as below (w, h: source size; the destination is h wide and w high for the transposed cases 5..8).
+        __global__ void __launch_bounds__(256) orient_kernel(const orient_job* __restrict__ jobs)
+        {
+            const orient_job J  = jobs[blockIdx.y];
+            const int        w = J.width, h = J.height;
+            const bool       swapped = J.orientation >= 5;
+            const int        dw = swapped ? h : w, pixels = w * h;
+            for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < pixels; i += gridDim.x * blockDim.x)
+            {
+                const int y = i / dw, x = i - y * dw;
+                int       sc, sr;
+                switch (J.orientation)
+                {
+                case 2: sc = w - 1 - x, sr = y; break;         // mirror
+                case 3: sc = w - 1 - x, sr = h - 1 - y; break; // half turn
+                case 4: sc = x, sr = h - 1 - y; break;         // flip
+                case 5: sc = y, sr = x; break;                 // transpose
+                case 6: sc = y, sr = h - 1 - x; break;         // quarter turn clockwise
+                case 7: sc = w - 1 - y, sr = h - 1 - x; break; // transverse
+                case 8: sc = w - 1 - y, sr = x; break;         // quarter turn counter-clockwise
+                default: sc = x, sr = y; break;
+                }
+                const uint8_t* s = J.src + (size_t)sr * J.src_pitch + (size_t)sc * J.src_stride;
+                uint8_t*       d = J.dst + (size_t)y * J.dst_pitch + (size_t)x * J.dst_stride;
+                d[0] = s[0];
+                d[1] = s[1];
+                d[2] = s[2];
             }
         }
     }
@@ -131,6 +176,47 @@ extern "C" int aeonb_rotate_batch(aeonb_ctx* ctx, const aeonb_rotate_desc* descs
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess)
             throw error(AEONB_ERR_CUDA, cuda_message("rotate kernel launch", e));
+        ctx->launches++;
+        return AEONB_OK;
+    });
+}
+
+extern "C" int aeonb_orient_batch(aeonb_ctx* ctx, const aeonb_orient_desc* descs, int n)
+{
+    return guarded([&]() {
+        if (!ctx || (n > 0 && !descs))
+            throw std::invalid_argument("aeonb_orient_batch: NULL argument");
+        if (n <= 0)
+            return AEONB_OK;
+        std::vector<orient_job> jobs(n);
+        int64_t                 most = 0;
+        for (int i = 0; i < n; ++i)
+        {
+            const aeonb_orient_desc& r = descs[i];
+            std::ostringstream       ss;
+            const int                dw = r.orientation >= 5 ? r.height : r.width;
+            if (!r.src || !r.dst || r.width <= 0 || r.height <= 0 || (int64_t)r.width * r.height > (1ll << 30))
+                ss << "record " << i << ": NULL picture or bad size";
+            else if (r.orientation < 1 || r.orientation > 8)
+                ss << "record " << i << ": orientation must be 1..8";
+            else if ((r.src_pixel_stride != 3 && r.src_pixel_stride != 4) || (r.dst_pixel_stride != 3 && r.dst_pixel_stride != 4))
+                ss << "record " << i << ": pixel strides must be 3 or 4";
+            else if (r.src_pitch < r.width * r.src_pixel_stride || r.dst_pitch < dw * r.dst_pixel_stride)
+                ss << "record " << i << ": pitch smaller than a row";
+            const std::string msg = ss.str();
+            if (!msg.empty())
+                throw std::invalid_argument(msg);
+            jobs[i] = orient_job{r.src, r.dst, r.src_pitch, r.src_pixel_stride, r.dst_pitch, r.dst_pixel_stride, r.width, r.height, r.orientation};
+            most    = std::max<int64_t>(most, (int64_t)r.width * r.height);
+        }
+        AEONB_CUDA(cudaSetDevice(ctx->device));
+        auto*      jdev = static_cast<const orient_job*>(ctx->upload(jobs.data(), sizeof(orient_job) * n));
+        const int  per  = (int)std::min<int64_t>((most + 255) / 256, 148 * 8);
+        const dim3 grid((unsigned)std::max(per, 1), (unsigned)n);
+        orient_kernel<<<grid, 256, 0, ctx->stream>>>(jdev);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess)
+            throw error(AEONB_ERR_CUDA, cuda_message("orientation kernel launch", e));
         ctx->launches++;
         return AEONB_OK;
     });

@@ -185,7 +185,7 @@ def jpeg_decode_batch(ctx, encoded, pixel_stride=3):
     torch.cuda.synchronize(dev)
     n = len(encoded)
     descs = (L.JpegDesc * n)()
-    keep, outs = [], []
+    keep, outs, infos = [], [], []
     for i, data in enumerate(encoded):
         info, coefs, quants = jpeg_entropy_decode(data)
         d = descs[i]
@@ -202,7 +202,24 @@ def jpeg_decode_batch(ctx, encoded, pixel_stride=3):
         d.dst, d.dst_pitch, d.dst_pixel_stride = buf.data_ptr(), pitch, pixel_stride
         outs.append(torch.as_strided(buf, (info.height, info.width, pixel_stride), (pitch, pixel_stride, 1)))
         keep.append(buf)
+        infos.append(info)
     torch.cuda.synchronize(dev)
     L.check(ctx.lib.aeonb_jpeg_backend_batch(ctx.handle, descs, n))
+    # EXIF orientation, as cv::imdecode applies it after decoding
+    turned = [i for i in range(n) if infos[i].orientation != 1]
+    if turned:
+        od = (L.OrientDesc * len(turned))()
+        for k, i in enumerate(turned):
+            info = infos[i]
+            w, h = (info.height, info.width) if info.orientation >= 5 else (info.width, info.height)
+            pitch = (w * pixel_stride + 15) // 16 * 16
+            buf = torch.zeros((h, pitch), dtype=torch.uint8, device=dev)
+            keep.append(buf)
+            o = od[k]
+            o.src, o.src_pitch, o.src_pixel_stride = descs[i].dst, descs[i].dst_pitch, pixel_stride
+            o.width, o.height, o.orientation = info.width, info.height, info.orientation
+            o.dst, o.dst_pitch, o.dst_pixel_stride = buf.data_ptr(), pitch, pixel_stride
+            outs[i] = torch.as_strided(buf, (h, w, pixel_stride), (pitch, pixel_stride, 1))
+        L.check(ctx.lib.aeonb_orient_batch(ctx.handle, od, len(turned)))
     ctx.synchronize()
     return outs, descs

@@ -162,6 +162,21 @@ typedef struct aeonb_rotate_desc
 
 int aeonb_rotate_batch(aeonb_ctx* ctx, const aeonb_rotate_desc* descs, int n);
 
+/* EXIF orientation pass: what cv::imdecode (src/etl_image.cpp:90) applies after decoding when the file carries an
+ * orientation tag other than 1: 2 mirror, 3 half turn, 4 flip, 5 transpose, 6 quarter turn clockwise, 7 transverse,
+ * 8 quarter turn counter-clockwise.  width/height are those of the source; the destination is height x width for 5..8. */
+typedef struct aeonb_orient_desc
+{
+    const uint8_t* src;      /* device: interleaved B,G,R[,x] picture as stored */
+    int32_t src_pitch, src_pixel_stride;
+    int32_t width, height;
+    int32_t orientation;     /* 1..8 */
+    uint8_t* dst;            /* device */
+    int32_t dst_pitch, dst_pixel_stride;
+} aeonb_orient_desc;
+
+int aeonb_orient_batch(aeonb_ctx* ctx, const aeonb_orient_desc* descs, int n);
+
 /* ------------------------------------------------------------------------------------------------
  * 1b. JPEG back end kernel: dequantisation + 8x8 integer inverse DCT + chroma upsampling +
  *     YCbCr->BGR, i.e. everything cv::imdecode (src/etl_image.cpp:90, src/cap_mjpeg_decoder.cpp:140)
@@ -258,6 +273,10 @@ typedef struct aeonb_jpeg_info
     int32_t hs[3], vs[3];
     int32_t blocks_w[3], blocks_h[3];
     int64_t coef_count[3]; /* int16 elements per component plane */
+    int32_t orientation;   /* EXIF orientation tag (1..8), 1 when absent.  width/height above are the stored size;
+                              cv::imdecode hands aeon the picture turned as the tag says (sizes swapped for 5..8):
+                              aeonb_orient_batch below does that turn */
+    int32_t reserved0;
 } aeonb_jpeg_info;
 
 int aeonb_jpeg_parse(const void* data, size_t size, aeonb_jpeg_info* info);

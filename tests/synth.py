@@ -17,3 +17,13 @@ def jpeg_bytes(img, quality=90, extra=()):
     ok, enc = cv2.imencode(".jpg", img, [cv2.IMWRITE_JPEG_QUALITY, quality] + list(extra))
     assert ok
     return enc.tobytes()
+
+
+def with_exif_orientation(jpeg, orientation, big_endian=False):
+    """Insert an APP1 Exif segment whose IFD0 holds only the orientation tag (0x0112) after the SOI marker."""
+    import struct
+    e = ">" if big_endian else "<"
+    tiff = (b"MM\x00\x2a" if big_endian else b"II\x2a\x00") + struct.pack(e + "I", 8) + struct.pack(e + "H", 1) + \
+        struct.pack(e + "HHIHH", 0x0112, 3, 1, orientation, 0) + struct.pack(e + "I", 0)
+    payload = b"Exif\x00\x00" + tiff
+    return jpeg[:2] + b"\xff\xe1" + struct.pack(">H", len(payload) + 2) + payload + jpeg[2:]

@@ -126,3 +126,17 @@ def test_progressive_streams_match_opencv(ctx):
     got = decode_gpu(ctx, cases)
     for i, b in enumerate(cases):
         assert np.array_equal(got[i], cv2.imdecode(np.frombuffer(b, np.uint8), cv2.IMREAD_COLOR)), "case %d" % i
+
+
+def test_exif_orientation_is_applied_as_opencv_does(ctx):
+    import cv2
+    from tests.synth import with_exif_orientation
+    rng = np.random.default_rng(30)
+    cases = []
+    for o in range(1, 9):
+        h, w = (int(v) for v in rng.integers(20, 200, 2))
+        cases.append(with_exif_orientation(jpeg_bytes(gradient_image(rng, h, w), 90), o, big_endian=bool(o % 2)))
+    got = decode_gpu(ctx, cases)
+    for i, b in enumerate(cases):
+        ref = cv2.imdecode(np.frombuffer(b, np.uint8), cv2.IMREAD_COLOR)
+        assert got[i].shape == ref.shape and np.array_equal(got[i], ref), "orientation %d" % (i + 1)

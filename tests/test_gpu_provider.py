@@ -355,3 +355,19 @@ def test_progressive_and_baseline_records_in_one_batch(ctx):
     got = make_provider(ctx, cfg).run_host(recs)["image"]
     want = PipelineOracle(cfg).batch(recs)["image"]
     assert np.array_equal(got, want)
+
+
+def test_exif_orientation_through_the_provider(ctx):
+    """cv::imdecode turns the picture by its EXIF orientation before aeon sees it: sizes for make_params, crop, rotation."""
+    from tests.synth import with_exif_orientation
+    rng = np.random.default_rng(59)
+    recs = []
+    for o in (1, 2, 3, 4, 5, 6, 7, 8):
+        img = gradient_image(rng, int(rng.integers(200, 300)), int(rng.integers(300, 400)))
+        recs.append((with_exif_orientation(jpeg_bytes(img, 90), o),))
+    etl = [{"type": "image", "height": 96, "width": 96, "output_type": "uint8_t"}]
+    for aug in (AUG_C1, dict(AUG_C1, angle=[-20, 20])):
+        cfg = {"batch_size": 8, "random_seed": 44, "etl": etl, "augmentation": [aug]}
+        got = make_provider(ctx, cfg).run_host(recs)["image"]
+        want = PipelineOracle(cfg).batch(recs)["image"]
+        assert np.array_equal(got, want)

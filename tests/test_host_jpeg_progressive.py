@@ -53,3 +53,19 @@ def test_grey_progressive_and_truncated_stream():
     sos = prog.index(b"\xff\xda")
     with pytest.raises(L.AeonError, match="Decoding image failed"):
         planes(prog[:sos])                                   # headers only
+
+
+def test_exif_orientation_tag_is_parsed():
+    """aeonb_jpeg_parse reports the EXIF orientation (both byte orders); stored width/height stay those of the frame header."""
+    from aeon_b200 import kernels as K
+    from tests.synth import jpeg_bytes, with_exif_orientation
+    rng = np.random.default_rng(6)
+    blob = jpeg_bytes(gradient_image(rng, 24, 40), 90)
+    assert K.jpeg_parse(blob).orientation == 1
+    for o in range(1, 9):
+        for big in (False, True):
+            info = K.jpeg_parse(with_exif_orientation(blob, o, big))
+            assert (info.orientation, info.width, info.height) == (o, 40, 24)
+    assert K.jpeg_parse(with_exif_orientation(blob, 9)).orientation == 1          # out of range: ignored, as OpenCV does
+    broken = blob[:2] + b"\xff\xe1\x00\x0cExif\x00\x00II\x2a\x00" + blob[2:]        # truncated TIFF header
+    assert K.jpeg_parse(broken).orientation == 1
