@@ -86,6 +86,45 @@ namespace aeonb
         size_t             plane_dev_off[3]{};
         size_t             scratch_off = 0, scratch_bytes = 0;
     };
+    // What one call of aeonb_provider::run plans before any GPU work: the JPEG streams to decode, the passes every
+    // picture goes through, and where everything lives in the staging buffer and in the device arenas.
+    struct batch_plan
+    {
+        struct copy_job // bytes copied as they are into the staging buffer (audio samples)
+        {
+            const void* src;
+            size_t      bytes, stage_off;
+        };
+        // rotation pass (image::rotate, the first step of transform_single_image): whole decoded picture -> rotated copy
+        struct rotation
+        {
+            int    job, angle, pitch;
+            size_t off;
+        };
+        explicit batch_plan(int stages)
+            : descs(stages), desc_job(stages), desc_dst(stages), pre_descs(stages), pre_job(stages), desc_rot(stages),
+              pre_rot(stages), desc_pre(stages), sdescs(stages), sdesc_off(stages)
+        {
+        }
+        std::vector<jpeg_job>                      jobs;
+        std::vector<copy_job>                      copies;
+        // per stage: main image-kernel descriptors, the JPEG job each reads (-1: zero frame) and its offset in the output
+        std::vector<std::vector<aeonb_image_desc>> descs;
+        std::vector<std::vector<int>>              desc_job;
+        std::vector<std::vector<int64_t>>          desc_dst;
+        std::vector<std::vector<aeonb_image_desc>> pre_descs; // resize_short pass: whole (expanded) picture -> short-side size
+        std::vector<std::vector<int>>              pre_job;
+        std::vector<rotation>                      rotations;
+        std::unordered_map<int, int>               rotation_of_job; // a repeated video frame is rotated once
+        std::vector<std::vector<int>>              desc_rot, pre_rot; // per descriptor: index into `rotations`, or -1
+        std::vector<std::vector<int>>              desc_pre;          // per descriptor: index into pre_descs[s], or -1
+        std::vector<std::vector<aeonb_specgram_desc>> sdescs;
+        std::vector<std::vector<size_t>>           sdesc_off;
+        size_t stage_bytes = 0, pixel_bytes = 0, coef_bytes = 0, oriented_bytes = 0, rotated_bytes = 0;
+        size_t status_room   = 0; // bytes reserved for the entropy decoder's status words at the start of the coefficient arena
+        int    n_device_jobs = 0; // streams Huffman-decoded on the GPU
+        std::vector<char*> produced; // where each device-produced output is written
+    };
 }
 
 struct aeonb_provider
@@ -143,4 +182,12 @@ struct aeonb_provider
     void    wait_ticket(int64_t t);
     ~aeonb_provider();
     int  input_count() const { return (int)stages.size(); }
+
+private:
+    // the phases of run()
+    void plan_records(aeonb::batch_plan& plan, const void* const* elems, const size_t* sizes, int n);
+    void reserve_arenas(aeonb::batch_plan& plan, void* const* outs, bool on_device, int par);
+    void stage_inputs(aeonb::batch_plan& plan);
+    void launch_kernels(aeonb::batch_plan& plan, int n);
+    void deliver(aeonb::batch_plan& plan, void* const* outs, int n, bool on_device, bool wait, int par);
 };

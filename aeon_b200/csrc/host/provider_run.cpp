@@ -167,10 +167,17 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         throw std::invalid_argument("aeonb_provider_run: NULL argument");
     if (n <= 0 || n > batch_size)
         throw std::invalid_argument("aeonb_provider_run: record count must be in [1, batch_size]");
-    const auto t_entry = std::chrono::steady_clock::now();
+    // AEONB_TRACE=1 prints the host time of each phase of the call to stderr
+    static const bool trace = std::getenv("AEONB_TRACE") != nullptr;
+    auto              t_prev = std::chrono::steady_clock::now();
+    double            t_phase[6] = {0, 0, 0, 0, 0, 0};
+    auto mark = [&](int k) {
+        const auto now = std::chrono::steady_clock::now();
+        t_phase[k]     = std::chrono::duration<double, std::milli>(now - t_prev).count();
+        t_prev         = now;
+    };
     AEONB_CUDA(cudaSetDevice(ctx->device));
-    cudaStream_t  st  = ctx->stream;
-    const int     nin = (int)stages.size();
+    cudaStream_t st = ctx->stream;
     if (!m_uploaded)
     {
         AEONB_CUDA(cudaEventCreateWithFlags(&m_uploaded, cudaEventDisableTiming));
@@ -190,33 +197,32 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         AEONB_CUDA(cudaEventSynchronize(m_uploaded));
     const int64_t launches_before = ctx->launches;
     h2d_bytes = d2h_bytes = 0;
+    mark(0);
 
-    struct copy_job
+    batch_plan B((int)stages.size());
+    plan_records(B, elems, sizes, n); // 1. sequential planning pass (record order == RNG order)
+    mark(1);
+    reserve_arenas(B, outs, on_device, par);
+    mark(2);
+    stage_inputs(B); // 3. host work on the pool, uploads
+    mark(3);
+    launch_kernels(B, n);
+    mark(4);
+    deliver(B, outs, n, on_device, wait, par);
+    launches = (int32_t)(ctx->launches - launches_before);
+    if (trace)
     {
-        const void* src;
-        size_t      bytes, stage_off;
-    };
-    vector<jpeg_job>                 jobs;
-    vector<copy_job>                 copies;
-    vector<vector<aeonb_image_desc>> descs(nin);
-    vector<vector<int>>              desc_job(nin);
-    vector<vector<int64_t>>          desc_dst(nin);
-    vector<vector<aeonb_image_desc>> pre_descs(nin);  // resize_short pass: whole (expanded) picture -> short-side size
-    vector<vector<int>>              pre_job(nin);
-    // rotation pass (image::rotate, the first step of transform_single_image): whole decoded picture -> rotated copy
-    struct rotation
-    {
-        int    job, angle, pitch;
-        size_t off;
-    };
-    vector<rotation>    rotations;
-    vector<vector<int>> desc_rot(nin), pre_rot(nin); // per descriptor: index into `rotations`, or -1
-    vector<vector<int>> desc_pre(nin);               // per descriptor: index into pre_descs[s], or -1
-    size_t              rotated_bytes = 0;
-    vector<vector<aeonb_specgram_desc>> sdescs(nin);
-    vector<vector<size_t>>           sdesc_off(nin);
-    size_t stage_bytes = 0, pixel_bytes = 0, coef_bytes = 0, oriented_bytes = 0;
+        mark(5);
+        std::fprintf(stderr, "aeonb_provider_run: entry %.3f plan %.3f arenas %.3f stage %.3f kernels %.3f deliver %.3f ms\n", t_phase[0],
+                     t_phase[1], t_phase[2], t_phase[3], t_phase[4], t_phase[5]);
+    }
+}
 
+// Phase 1: parses headers, draws the augmentation parameters record by record (the order of the draws is the
+// reference's) and plans every pass; host-produced outputs (labels, boxes) are written here.
+void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const size_t* sizes, int n)
+{
+    const int nin = (int)stages.size();
     for (size_t o = 0; o < outputs.size(); ++o)
         if (outputs[o].host_produced)
             out_host[o].assign((size_t)batch_size * outputs[o].shape.byte_size(), 0);
@@ -230,15 +236,15 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         const bool swapped = job.frame.info.orientation >= 5;
         job.pw             = swapped ? job.frame.info.height : job.frame.info.width;
         job.ph             = swapped ? job.frame.info.width : job.frame.info.height;
-        jobs.push_back(job);
-        return (int)jobs.size() - 1;
+        B.jobs.push_back(job);
+        return (int)B.jobs.size() - 1;
     };
     // Fixes the region of the picture a job has to produce -- the MCUs that the crop box of `d` (given in
     // canvas coordinates, the picture sitting at canvas_x/canvas_y) can touch, plus one chroma sample of
     // context -- and reserves its space in the staging buffer and in the pixel arena.  `d` == nullptr keeps
     // the whole picture.  A job shared by several descriptors (repeated video frame) keeps its first layout.
     auto layout_jpeg = [&](int j, const aeonb_image_desc* d) {
-        jpeg_job& job = jobs[j];
+        jpeg_job& job = B.jobs[j];
         if (job.laid_out)
             return;
         const aeonb_jpeg_info& in = job.frame.info;
@@ -249,8 +255,8 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         if (job.oriented)
         {
             job.opitch     = (int)align_up((size_t)job.pw * 3, 16);
-            job.opixel_off = align_up(oriented_bytes, 256);
-            oriented_bytes = job.opixel_off + (size_t)job.opitch * job.ph;
+            job.opixel_off = align_up(B.oriented_bytes, 256);
+            B.oriented_bytes = job.opixel_off + (size_t)job.opitch * job.ph;
         }
         else if (d && roi_decode) // a crop box that lies on the zero canvas only reads nothing of the picture: one MCU is kept
             roi = jpeg_roi_for_box(in, d->crop_x - d->canvas_x, d->crop_y - d->canvas_y, d->crop_x + d->crop_w - d->canvas_x,
@@ -260,7 +266,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         job.ry  = roi.my0 * mh;
         job.rw  = std::min(in.width, roi.mx1 * mw) - job.rx;
         job.rh  = std::min(in.height, roi.my1 * mh) - job.ry;
-        size_t off    = align_up(stage_bytes, 256);
+        size_t off    = align_up(B.stage_bytes, 256);
         job.stage_off = off;
         off += 3 * 64 * sizeof(uint16_t);
         job.on_device = device_entropy && jpeg_entropy_prepare(job.frame, job.tables, job.edesc);
@@ -278,8 +284,8 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
             const size_t bytes  = (size_t)job.roi_blocks_w[c] * job.roi_blocks_h[c] * 64 * sizeof(int16_t);
             if (job.on_device)
             {
-                job.plane_dev_off[c] = align_up(coef_bytes, 256);
-                coef_bytes           = job.plane_dev_off[c] + bytes;
+                job.plane_dev_off[c] = align_up(B.coef_bytes, 256);
+                B.coef_bytes           = job.plane_dev_off[c] + bytes;
             }
             else
             {
@@ -295,43 +301,42 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
             job.edesc.roi[2]  = std::min(roi.mx1, mcux);
             job.edesc.roi[3]  = std::min(roi.my1, mcuy);
             job.scratch_bytes = (size_t)jpeg_entropy_scratch_bytes(job.edesc);
-            job.scratch_off   = align_up(coef_bytes, 256);
-            coef_bytes        = job.scratch_off + job.scratch_bytes;
+            job.scratch_off   = align_up(B.coef_bytes, 256);
+            B.coef_bytes        = job.scratch_off + job.scratch_bytes;
         }
         job.stage_bytes = off - job.stage_off;
-        stage_bytes     = off;
+        B.stage_bytes     = off;
         job.pitch       = (int)align_up((size_t)job.rw * pixel_stride, 16);
-        job.pixel_off   = align_up(pixel_bytes, 256);
-        pixel_bytes     = job.pixel_off + (size_t)job.pitch * job.rh;
+        job.pixel_off   = align_up(B.pixel_bytes, 256);
+        B.pixel_bytes     = job.pixel_off + (size_t)job.pitch * job.rh;
         job.laid_out    = true;
     };
 
     // Plans the passes one picture (an image record, or a video frame) goes through before the main image kernel
     // -- rotation (image::rotate, the first step of transform_single_image) and resize_short (applied to the whole,
     // possibly expanded, picture before the crop; src/etl_image.cpp:160-168) -- and returns the main descriptor.
-    std::unordered_map<int, int> rotation_of_job; // a repeated video frame is rotated once
     auto plan_picture = [&](int s, int j, const image_params& params, int slot_w, int slot_h, bool exact_fit) {
         struct
         {
             int width, height;
-        } const in{jobs[j].pw, jobs[j].ph}; // the picture as delivered (after the EXIF turn)
+        } const in{B.jobs[j].pw, B.jobs[j].ph}; // the picture as delivered (after the EXIF turn)
         int rot = -1;
         if (params.angle != 0)
         {
-            auto it = rotation_of_job.find(j);
-            if (it != rotation_of_job.end())
+            auto it = B.rotation_of_job.find(j);
+            if (it != B.rotation_of_job.end())
                 rot = it->second;
             else
             {
-                rotation ro;
+                batch_plan::rotation ro;
                 ro.job        = j;
                 ro.angle      = params.angle;
                 ro.pitch      = (int)align_up((size_t)in.width * 3, 16);
-                ro.off        = align_up(rotated_bytes, 256);
-                rotated_bytes = ro.off + (size_t)ro.pitch * in.height;
-                rot           = (int)rotations.size();
-                rotations.push_back(ro);
-                rotation_of_job[j] = rot;
+                ro.off        = align_up(B.rotated_bytes, 256);
+                B.rotated_bytes = ro.off + (size_t)ro.pitch * in.height;
+                rot           = (int)B.rotations.size();
+                B.rotations.push_back(ro);
+                B.rotation_of_job[j] = rot;
             }
             layout_jpeg(j, nullptr); // the rotation reads the whole picture
         }
@@ -350,10 +355,10 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
             const int ch = params.expand_ratio > 1.0f ? params.expand_size.height : in.height;
             whole.cropbox           = recti{0, 0, cw, ch};
             whole.output_size       = get_resized_short_size(cw, ch, params.resize_short_size);
-            pre                     = (int)pre_descs[s].size();
-            pre_descs[s].push_back(make_desc(whole, in.width, in.height, 0, 0, false));
-            pre_job[s].push_back(j);
-            pre_rot[s].push_back(rot);
+            pre                     = (int)B.pre_descs[s].size();
+            B.pre_descs[s].push_back(make_desc(whole, in.width, in.height, 0, 0, false));
+            B.pre_job[s].push_back(j);
+            B.pre_rot[s].push_back(rot);
             rot = -1;                // the crop pass reads the resized picture
             layout_jpeg(j, nullptr); // the resize pass reads the whole picture
             image_params rest = params;
@@ -366,21 +371,11 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
             d = make_desc(params, in.width, in.height, slot_w, slot_h, exact_fit);
             layout_jpeg(j, &d); // keeps an earlier whole-picture layout
         }
-        desc_rot[s].push_back(rot);
-        desc_pre[s].push_back(pre);
+        B.desc_rot[s].push_back(rot);
+        B.desc_pre[s].push_back(pre);
         return d;
     };
 
-    // AEONB_TRACE=1 prints the host time of each phase of the call to stderr
-    static const bool trace = std::getenv("AEONB_TRACE") != nullptr;
-    auto              t_prev = t_entry;
-    double            t_phase[6] = {0, 0, 0, 0, 0, 0};
-    auto mark = [&](int k) {
-        const auto now = std::chrono::steady_clock::now();
-        t_phase[k]     = std::chrono::duration<double, std::milli>(now - t_prev).count();
-        t_prev         = now;
-    };
-    mark(0);
     // ---- 1. sequential planning pass (record order == RNG order)
     for (int r = 0; r < n; ++r)
     {
@@ -406,15 +401,15 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                 const int  j  = plan_jpeg(data, size);
                 if (!have_params)
                 {
-                    params      = factory.make_params(engine, jobs[j].pw, jobs[j].ph, sg.image.width, sg.image.height);
+                    params      = factory.make_params(engine, B.jobs[j].pw, B.jobs[j].ph, sg.image.width, sg.image.height);
                     have_params = true;
                 }
                 aeonb_image_desc d = plan_picture(s, j, params, sg.image.width, sg.image.height, !factory.fixed_aspect_ratio);
                 if (d.out_w > sg.image.width || d.out_h > sg.image.height)
                     throw std::invalid_argument("transformed image does not fit the configured output size");
-                descs[s].push_back(d);
-                desc_job[s].push_back(j);
-                desc_dst[s].push_back((int64_t)r * outputs[sg.first_output].shape.byte_size());
+                B.descs[s].push_back(d);
+                B.desc_job[s].push_back(j);
+                B.desc_dst[s].push_back((int64_t)r * outputs[sg.first_output].shape.byte_size());
                 break;
             }
             case stage_kind::video:
@@ -441,7 +436,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                         prev = plan_jpeg(frames[t].data, frames[t].size);
                     frame_jobs.push_back(prev);
                 }
-                const jpeg_job& first = jobs[frame_jobs[0]];
+                const jpeg_job& first = B.jobs[frame_jobs[0]];
                 if (!have_params)
                 {
                     params      = video_factory.make_params(engine, first.pw, first.ph, fc.width, fc.height);
@@ -458,12 +453,12 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                     }
                     else
                     {
-                        desc_rot[s].push_back(-1); // zero padding frame
-                        desc_pre[s].push_back(-1);
+                        B.desc_rot[s].push_back(-1); // zero padding frame
+                        B.desc_pre[s].push_back(-1);
                     }
-                    descs[s].push_back(d);
-                    desc_job[s].push_back(j);
-                    desc_dst[s].push_back((int64_t)r * rec + (int64_t)t * fc.height * fc.width);
+                    B.descs[s].push_back(d);
+                    B.desc_job[s].push_back(j);
+                    B.desc_dst[s].push_back((int64_t)r * rec + (int64_t)t * fc.height * fc.width);
                 }
                 break;
             }
@@ -531,13 +526,13 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                 const int16_t* samples = wav_samples(data, size, count);
                 const size_t   limit   = (size_t)(sg.audio.max_time_steps - 1) * sg.audio.frame_stride + sg.audio.frame_length;
                 count                  = std::min(count, limit);
-                const size_t off       = align_up(stage_bytes, 256);
-                stage_bytes            = off + count * 2;
-                copies.push_back(copy_job{samples, count * 2, off});
+                const size_t off       = align_up(B.stage_bytes, 256);
+                B.stage_bytes            = off + count * 2;
+                B.copies.push_back(batch_plan::copy_job{samples, count * 2, off});
                 aeonb_specgram_desc d{};
                 d.n_samples = (int32_t)count;
-                sdescs[s].push_back(d);
-                sdesc_off[s].push_back(off);
+                B.sdescs[s].push_back(d);
+                B.sdesc_off[s].push_back(off);
                 break;
             }
             }
@@ -545,41 +540,51 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     }
     slot_cursor = (slot_cursor + n) % decode_size;
 
-    mark(1);
+}
+
+// Phase 2: grow-only arenas for everything the plan placed.
+void aeonb_provider::reserve_arenas(batch_plan& B, void* const* outs, bool on_device, int par)
+{
     // ---- 2. arenas
-    staging.reserve(stage_bytes + 256);
-    staging_dev.reserve(stage_bytes + 256);
-    pixels_dev.reserve(pixel_bytes + 256);
-    if (oriented_bytes > 0)
-        oriented_dev.reserve(oriented_bytes + 256);
-    if (rotated_bytes > 0)
-        rotated_dev.reserve(rotated_bytes + 256);
-    const size_t status_room = align_up(sizeof(int32_t) * (jobs.size() + 1), 256);
-    if (coef_bytes > 0)
-        coef_dev.reserve(status_room + coef_bytes + 256);
-    vector<char*> produced(outputs.size(), nullptr); // where each device-produced output is written
+    staging.reserve(B.stage_bytes + 256);
+    staging_dev.reserve(B.stage_bytes + 256);
+    pixels_dev.reserve(B.pixel_bytes + 256);
+    if (B.oriented_bytes > 0)
+        oriented_dev.reserve(B.oriented_bytes + 256);
+    if (B.rotated_bytes > 0)
+        rotated_dev.reserve(B.rotated_bytes + 256);
+    B.status_room = align_up(sizeof(int32_t) * (B.jobs.size() + 1), 256);
+    if (B.coef_bytes > 0)
+        coef_dev.reserve(B.status_room + B.coef_bytes + 256);
+    B.produced.assign(outputs.size(), nullptr); // where each device-produced output is written
     for (size_t o = 0; o < outputs.size(); ++o)
     {
         if (outputs[o].host_produced)
             continue;
         const size_t bytes = (size_t)batch_size * outputs[o].shape.byte_size();
         if (on_device && batch_major)
-            produced[o] = static_cast<char*>(outs[o]);
+            B.produced[o] = static_cast<char*>(outs[o]);
         else
         {
             out_dev[par][o].reserve(bytes);
-            produced[o] = static_cast<char*>(out_dev[par][o].p);
+            B.produced[o] = static_cast<char*>(out_dev[par][o].p);
         }
         if (!batch_major)
             out_dev_t[par][o].reserve(bytes);
     }
 
-    mark(2);
+}
+
+// Phase 3: the worker pool fills the pinned staging buffer (compressed scans and tables, or coefficient planes when
+// Huffman decoding runs on the host; audio samples), shipped to the device in slices while the pool is still working.
+void aeonb_provider::stage_inputs(batch_plan& B)
+{
+    cudaStream_t st = ctx->stream;
     // ---- 3. entropy decode on the pool, shipping finished slices while the rest decode
     char* const hstage = static_cast<char*>(staging.p);
     char* const dstage = static_cast<char*>(staging_dev.p);
-    const int   njobs  = (int)jobs.size();
-    const int   nwork  = njobs + (int)copies.size();
+    const int   njobs  = (int)B.jobs.size();
+    const int   nwork  = njobs + (int)B.copies.size();
     if (nwork > 0)
     {
         const int                     groups = std::max(1, std::min(8, nwork));
@@ -590,7 +595,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         for (int g = 0; g < groups; ++g)
             remaining[g] = first[g + 1] - first[g];
         auto group_of = [&](int i) { return (int)(std::upper_bound(first.begin(), first.end(), i) - first.begin()) - 1; };
-        auto offset_of = [&](int i) { return i < njobs ? jobs[i].stage_off : copies[i - njobs].stage_off; };
+        auto offset_of = [&](int i) { return i < njobs ? B.jobs[i].stage_off : B.copies[i - njobs].stage_off; };
         std::exception_ptr failure;
         std::mutex         failure_mutex;
         pool->start(nwork, [&](int i) {
@@ -598,7 +603,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
             {
                 if (i < njobs)
                 {
-                    jpeg_job& job = jobs[i];
+                    jpeg_job& job = B.jobs[i];
                     std::memcpy(hstage + job.stage_off, job.frame.quant, sizeof job.frame.quant);
                     if (job.on_device)
                     {
@@ -614,7 +619,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                 }
                 else
                 {
-                    const copy_job& c = copies[i - njobs];
+                    const batch_plan::copy_job& c = B.copies[i - njobs];
                     std::memcpy(hstage + c.stage_off, c.src, c.bytes);
                 }
             }
@@ -632,7 +637,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
             while (remaining[g].load(std::memory_order_acquire) > 0)
                 std::this_thread::sleep_for(std::chrono::microseconds(20));
             const size_t begin = offset_of(first[g]);
-            const size_t end   = first[g + 1] < nwork ? offset_of(first[g + 1]) : stage_bytes;
+            const size_t end   = first[g + 1] < nwork ? offset_of(first[g + 1]) : B.stage_bytes;
             if (end > begin && copy_error == cudaSuccess && !failure)
             {
                 copy_error = cudaMemcpyAsync(dstage + begin, hstage + begin, end - begin, cudaMemcpyHostToDevice, st);
@@ -645,38 +650,46 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         AEONB_CUDA(copy_error);
     }
 
-    mark(3);
+}
+
+// Phase 4: one launch per kernel for the whole batch.
+void aeonb_provider::launch_kernels(batch_plan& B, int n)
+{
+    cudaStream_t st     = ctx->stream;
+    const int    nin    = (int)stages.size();
+    const int    njobs  = (int)B.jobs.size();
+    char* const  dstage = static_cast<char*>(staging_dev.p);
     // ---- 4. kernels
-    int n_device_jobs = 0;
+    B.n_device_jobs = 0;
     if (njobs > 0)
     {
         char* const cdev = static_cast<char*>(coef_dev.p);
         vector<aeonb_entropy_desc> ed;
         for (int i = 0; i < njobs; ++i)
         {
-            const jpeg_job& job = jobs[i];
+            const jpeg_job& job = B.jobs[i];
             if (!job.on_device)
                 continue;
             aeonb_entropy_desc d = job.edesc;
             d.scan               = reinterpret_cast<const uint8_t*>(dstage + job.scan_off);
             d.tables             = reinterpret_cast<const uint8_t*>(dstage + job.tables_off);
             for (int c = 0; c < job.frame.info.ncomp; ++c)
-                d.coef[c] = reinterpret_cast<int16_t*>(cdev + status_room + job.plane_dev_off[c]);
-            d.scratch       = cdev + status_room + job.scratch_off;
+                d.coef[c] = reinterpret_cast<int16_t*>(cdev + B.status_room + job.plane_dev_off[c]);
+            d.scratch       = cdev + B.status_room + job.scratch_off;
             d.scratch_bytes = job.scratch_bytes;
             d.status        = reinterpret_cast<int32_t*>(cdev) + ed.size();
             ed.push_back(d);
         }
-        n_device_jobs = (int)ed.size();
-        if (n_device_jobs > 0)
+        B.n_device_jobs = (int)ed.size();
+        if (B.n_device_jobs > 0)
         {
-            check_status(aeonb_jpeg_entropy_batch(ctx, ed.data(), n_device_jobs));
-            h2d_bytes += (int64_t)(sizeof(aeonb_entropy_desc) * n_device_jobs);
+            check_status(aeonb_jpeg_entropy_batch(ctx, ed.data(), B.n_device_jobs));
+            h2d_bytes += (int64_t)(sizeof(aeonb_entropy_desc) * B.n_device_jobs);
         }
         vector<aeonb_jpeg_desc> jd(njobs);
         for (int i = 0; i < njobs; ++i)
         {
-            const jpeg_job&        job = jobs[i];
+            const jpeg_job&        job = B.jobs[i];
             const aeonb_jpeg_info& in  = job.frame.info;
             aeonb_jpeg_desc&       d   = jd[i];
             d.width  = job.rw;
@@ -684,7 +697,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
             d.ncomp  = in.ncomp;
             for (int c = 0; c < in.ncomp; ++c)
             {
-                d.coef[c]     = job.on_device ? reinterpret_cast<const int16_t*>(cdev + status_room + job.plane_dev_off[c])
+                d.coef[c]     = job.on_device ? reinterpret_cast<const int16_t*>(cdev + B.status_room + job.plane_dev_off[c])
                                               : reinterpret_cast<const int16_t*>(dstage + job.plane_off[c]);
                 d.quant[c]    = reinterpret_cast<const uint16_t*>(dstage + job.stage_off) + 64 * c;
                 d.hs[c]       = in.hs[c];
@@ -706,14 +719,14 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         int            pitch, stride, w, h, x, y; // (x, y): where the region's origin lies in the whole picture
     };
     auto picture_of = [&](int j) {
-        const jpeg_job& job = jobs[j];
+        const jpeg_job& job = B.jobs[j];
         if (job.oriented)
             return picture{static_cast<const uint8_t*>(oriented_dev.p) + job.opixel_off, job.opitch, 3, job.pw, job.ph, 0, 0};
         return picture{static_cast<const uint8_t*>(pixels_dev.p) + job.pixel_off, job.pitch, pixel_stride, job.rw, job.rh, job.rx, job.ry};
     };
     {
         vector<aeonb_orient_desc> od;
-        for (const jpeg_job& job : jobs)
+        for (const jpeg_job& job : B.jobs)
             if (job.oriented)
             {
                 aeonb_orient_desc o{};
@@ -734,12 +747,12 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
             h2d_bytes += (int64_t)(sizeof(aeonb_orient_desc) * od.size());
         }
     }
-    if (!rotations.empty())
+    if (!B.rotations.empty())
     {
-        vector<aeonb_rotate_desc> rd(rotations.size());
-        for (size_t i = 0; i < rotations.size(); ++i)
+        vector<aeonb_rotate_desc> rd(B.rotations.size());
+        for (size_t i = 0; i < B.rotations.size(); ++i)
         {
-            const rotation& ro  = rotations[i];
+            const batch_plan::rotation& ro  = B.rotations[i];
             const picture   pic = picture_of(ro.job);
             rd[i].src              = pic.p;
             rd[i].src_pitch        = pic.pitch;
@@ -774,7 +787,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                 L.stride_y = ic.width;
                 L.stride_x = 1;
                 if (outputs[o].shape.otype.size != 1)
-                    AEONB_CUDA(cudaMemsetAsync(produced[o], 0, (size_t)n * outputs[o].shape.byte_size(), st));
+                    AEONB_CUDA(cudaMemsetAsync(B.produced[o], 0, (size_t)n * outputs[o].shape.byte_size(), st));
             }
             else
             {
@@ -805,13 +818,13 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                     }
                 }
             }
-            const bool pre = !pre_descs[s].empty();
+            const bool pre = !B.pre_descs[s].empty();
             size_t     pre_slot = 0;
             int        pre_pitch = 0;
             if (pre)
             {
                 aeonb_image_layout P{};
-                for (const aeonb_image_desc& d : pre_descs[s])
+                for (const aeonb_image_desc& d : B.pre_descs[s])
                 {
                     P.slot_w = std::max(P.slot_w, d.out_w);
                     P.slot_h = std::max(P.slot_h, d.out_h);
@@ -823,41 +836,41 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                 pre_pitch  = (int)align_up((size_t)P.slot_w * 3, 16);
                 P.stride_y = pre_pitch;
                 pre_slot   = align_up((size_t)pre_pitch * P.slot_h, 256);
-                resized_dev.reserve(pre_slot * pre_descs[s].size());
-                for (size_t i = 0; i < pre_descs[s].size(); ++i)
+                resized_dev.reserve(pre_slot * B.pre_descs[s].size());
+                for (size_t i = 0; i < B.pre_descs[s].size(); ++i)
                 {
-                    aeonb_image_desc& d = pre_descs[s][i];
-                    const int         j = pre_job[s][i];
+                    aeonb_image_desc& d = B.pre_descs[s][i];
+                    const int         j = B.pre_job[s][i];
                     const picture     pic = picture_of(j);
                     d.src               = pic.p;
                     d.src_pitch         = pic.pitch;
                     d.src_pixel_stride  = pic.stride;
-                    if (pre_rot[s][i] >= 0)
+                    if (B.pre_rot[s][i] >= 0)
                     {
-                        d.src              = static_cast<const uint8_t*>(rotated_dev.p) + rotations[pre_rot[s][i]].off;
-                        d.src_pitch        = rotations[pre_rot[s][i]].pitch;
+                        d.src              = static_cast<const uint8_t*>(rotated_dev.p) + B.rotations[B.pre_rot[s][i]].off;
+                        d.src_pitch        = B.rotations[B.pre_rot[s][i]].pitch;
                         d.src_pixel_stride = 3;
                     }
                     d.dst               = static_cast<char*>(resized_dev.p) + i * pre_slot;
                 }
-                check_status(aeonb_image_batch(ctx, pre_descs[s].data(), (int)pre_descs[s].size(), &P));
-                h2d_bytes += (int64_t)(sizeof(aeonb_image_desc) * pre_descs[s].size());
+                check_status(aeonb_image_batch(ctx, B.pre_descs[s].data(), (int)B.pre_descs[s].size(), &P));
+                h2d_bytes += (int64_t)(sizeof(aeonb_image_desc) * B.pre_descs[s].size());
             }
-            for (size_t i = 0; i < descs[s].size(); ++i)
+            for (size_t i = 0; i < B.descs[s].size(); ++i)
             {
-                aeonb_image_desc& d = descs[s][i];
-                const int         j = desc_job[s][i];
-                d.dst               = produced[o] + desc_dst[s][i];
-                if (desc_pre[s][i] >= 0)
+                aeonb_image_desc& d = B.descs[s][i];
+                const int         j = B.desc_job[s][i];
+                d.dst               = B.produced[o] + B.desc_dst[s][i];
+                if (B.desc_pre[s][i] >= 0)
                 {
-                    d.src              = static_cast<const uint8_t*>(resized_dev.p) + (size_t)desc_pre[s][i] * pre_slot;
+                    d.src              = static_cast<const uint8_t*>(resized_dev.p) + (size_t)B.desc_pre[s][i] * pre_slot;
                     d.src_pitch        = pre_pitch;
                     d.src_pixel_stride = 3;
                 }
-                else if (desc_rot[s][i] >= 0)
+                else if (B.desc_rot[s][i] >= 0)
                 {
-                    d.src              = static_cast<const uint8_t*>(rotated_dev.p) + rotations[desc_rot[s][i]].off;
-                    d.src_pitch        = rotations[desc_rot[s][i]].pitch;
+                    d.src              = static_cast<const uint8_t*>(rotated_dev.p) + B.rotations[B.desc_rot[s][i]].off;
+                    d.src_pitch        = B.rotations[B.desc_rot[s][i]].pitch;
                     d.src_pixel_stride = 3;
                 }
                 else if (j >= 0)
@@ -873,8 +886,8 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
                     d.canvas_y += pic.y;
                 }
             }
-            check_status(aeonb_image_batch(ctx, descs[s].data(), (int)descs[s].size(), &L));
-            h2d_bytes += (int64_t)(sizeof(aeonb_image_desc) * descs[s].size());
+            check_status(aeonb_image_batch(ctx, B.descs[s].data(), (int)B.descs[s].size(), &L));
+            h2d_bytes += (int64_t)(sizeof(aeonb_image_desc) * B.descs[s].size());
         }
         else if (sg.kind == stage_kind::audio)
         {
@@ -883,17 +896,22 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
             aeonb_specgram_config cfg{sg.audio.frame_length, sg.audio.frame_stride, sg.audio.max_time_steps,
                                       mel ? sg.audio.num_filters : 0, sg.audio.sample_rate, sg.audio.window_code(),
                                       sg.audio.feature_type == "mfcc" ? sg.audio.num_cepstra : 0, 0};
-            for (size_t i = 0; i < sdescs[s].size(); ++i)
+            for (size_t i = 0; i < B.sdescs[s].size(); ++i)
             {
-                sdescs[s][i].samples = reinterpret_cast<const int16_t*>(dstage + sdesc_off[s][i]);
-                sdescs[s][i].dst     = reinterpret_cast<float*>(produced[o] + (int64_t)i * outputs[o].shape.byte_size());
+                B.sdescs[s][i].samples = reinterpret_cast<const int16_t*>(dstage + B.sdesc_off[s][i]);
+                B.sdescs[s][i].dst     = reinterpret_cast<float*>(B.produced[o] + (int64_t)i * outputs[o].shape.byte_size());
             }
-            check_status(aeonb_specgram_batch(ctx, sdescs[s].data(), (int)sdescs[s].size(), &cfg));
-            h2d_bytes += (int64_t)(sizeof(aeonb_specgram_desc) * sdescs[s].size());
+            check_status(aeonb_specgram_batch(ctx, B.sdescs[s].data(), (int)B.sdescs[s].size(), &cfg));
+            h2d_bytes += (int64_t)(sizeof(aeonb_specgram_desc) * B.sdescs[s].size());
         }
     }
 
-    mark(4);
+}
+
+// Phase 5: host-produced outputs, transposes, copies to the host on the copy stream, completion event.
+void aeonb_provider::deliver(batch_plan& B, void* const* outs, int n, bool on_device, bool wait, int par)
+{
+    cudaStream_t st = ctx->stream;
     // ---- 5. deliver
     size_t small_total = 0;
     for (size_t o = 0; o < outputs.size(); ++o)
@@ -945,24 +963,24 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     {
         if (outputs[o].host_produced)
             continue;
-        sources[o] = produced[o];
+        sources[o] = B.produced[o];
         if (!batch_major)
         {
             void* target = on_device ? outs[o] : out_dev_t[par][o].p;
-            AEONB_CUDA(launch_transpose(produced[o], target, batch_size, outputs[o].shape.element_count(),
+            AEONB_CUDA(launch_transpose(B.produced[o], target, batch_size, outputs[o].shape.element_count(),
                                         (int)outputs[o].shape.otype.size, st));
             ctx->launches++;
             sources[o] = target;
         }
     }
     m_status_count[slot] = 0;
-    if (n_device_jobs > 0)
+    if (B.n_device_jobs > 0)
     {
         // on the kernels' stream: the next batch's entropy kernel rewrites these words
-        m_status[slot].reserve(sizeof(int32_t) * n_device_jobs);
-        AEONB_CUDA(cudaMemcpyAsync(m_status[slot].p, coef_dev.p, sizeof(int32_t) * n_device_jobs, cudaMemcpyDeviceToHost, st));
-        d2h_bytes += (int64_t)(sizeof(int32_t) * n_device_jobs);
-        m_status_count[slot] = n_device_jobs;
+        m_status[slot].reserve(sizeof(int32_t) * B.n_device_jobs);
+        AEONB_CUDA(cudaMemcpyAsync(m_status[slot].p, coef_dev.p, sizeof(int32_t) * B.n_device_jobs, cudaMemcpyDeviceToHost, st));
+        d2h_bytes += (int64_t)(sizeof(int32_t) * B.n_device_jobs);
+        m_status_count[slot] = B.n_device_jobs;
     }
     // Batches delivered to host memory are copied on a second stream, so that the next batch's uploads and
     // kernels do not queue behind this batch's (much longer) device -> host copy.
@@ -988,12 +1006,5 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         if (cs != st)
             AEONB_CUDA(cudaStreamSynchronize(cs));
         check_entropy_status(slot);
-    }
-    launches = (int32_t)(ctx->launches - launches_before);
-    if (trace)
-    {
-        mark(5);
-        std::fprintf(stderr, "aeonb_provider_run: entry %.3f plan %.3f arenas %.3f stage %.3f kernels %.3f deliver %.3f ms\n", t_phase[0],
-                     t_phase[1], t_phase[2], t_phase[3], t_phase[4], t_phase[5]);
     }
 }

@@ -104,3 +104,13 @@ def test_malformed_stream_sets_status_and_returns(ctx, parallel):
     assert got[1][3] in (0, 1) and got[2][3] in (0, 1)
     # and the context is still usable
     check(ctx, [good], parallel=parallel)
+
+
+def test_large_picture_and_many_streams(ctx, parallel):
+    """A 2048x1536 picture (segments of several KB per thread) and a launch of 600 small streams (more blocks than fit at once)."""
+    rng = np.random.default_rng(66)
+    big = jpeg_bytes(gradient_image(rng, 1536, 2048), 92)
+    assert len(big) > 400_000
+    check(ctx, [big], parallel=parallel)
+    small = [jpeg_bytes(gradient_image(rng, int(rng.integers(16, 64)), int(rng.integers(16, 64))), 80) for _ in range(40)]
+    check(ctx, [small[i % 40] for i in range(600)], parallel=parallel)
