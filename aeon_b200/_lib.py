@@ -117,6 +117,8 @@ PROTOTYPES = {
     "aeonb_jpeg_roi_for_crop": (C.c_int, [C.POINTER(JpegInfo), C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int32)]),
     "aeonb_jpeg_entropy_decode_roi": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_int32), C.POINTER(C.c_void_p),
                                                 C.POINTER(C.c_void_p)]),
+    "aeonb_png_info": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "aeonb_png_decode_bgr": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t]),
     "aeonb_draw_params": (C.c_int, [C.c_char_p, C.c_uint32, C.c_int, C.c_int, C.POINTER(C.c_int32),
                                     C.POINTER(C.c_int32), C.c_int, C.c_int, C.POINTER(C.c_double)]),
     "aeonb_draw_ssd_params": (C.c_int, [C.c_char_p, C.c_uint32, C.c_int, C.c_int, C.POINTER(C.c_int32),

@@ -20,6 +20,7 @@
 #include "../specgram_host.hpp"
 #include "config.hpp"
 #include "jpeg_host.hpp"
+#include "png_host.hpp"
 #include "params.hpp"
 #include "runtime.hpp"
 
@@ -76,6 +77,10 @@ namespace aeonb
         // The picture as cv::imdecode delivers it: pw x ph after the EXIF orientation turn (sizes swapped for tags 5..8).
         // A turned picture is decoded whole and turned by a pass of its own into the orientation arena.
         int                pw = 0, ph = 0;
+        // A PNG record: decoded on the pool straight into the staging buffer as a B,G,R picture (stage_off, pitch),
+        // which the image kernel reads from the device copy; none of the JPEG fields apply.
+        bool               png = false;
+        png_info           pinfo;
         bool               oriented = false;
         size_t             opixel_off = 0;
         int                opitch = 0;

@@ -232,6 +232,16 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
         jpeg_job job;
         job.data = static_cast<const uint8_t*>(data);
         job.size = size;
+        if (is_png(data, size))
+        {
+            png_parse(data, size, job.pinfo);
+            job.png                    = true;
+            job.pw                     = job.pinfo.width;
+            job.ph                     = job.pinfo.height;
+            job.frame.info.orientation = 1;
+            B.jobs.push_back(job);
+            return (int)B.jobs.size() - 1;
+        }
         jpeg_parse(data, size, job.frame);
         const bool swapped = job.frame.info.orientation >= 5;
         job.pw             = swapped ? job.frame.info.height : job.frame.info.width;
@@ -247,6 +257,17 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
         jpeg_job& job = B.jobs[j];
         if (job.laid_out)
             return;
+        if (job.png)
+        {
+            job.pitch       = (int)align_up((size_t)job.pw * 3, 16);
+            job.stage_off   = align_up(B.stage_bytes, 256);
+            job.stage_bytes = (size_t)job.pitch * job.ph;
+            B.stage_bytes   = job.stage_off + job.stage_bytes;
+            job.rw          = job.pw;
+            job.rh          = job.ph;
+            job.laid_out    = true;
+            return;
+        }
         const aeonb_jpeg_info& in = job.frame.info;
         const int mw = 8 * in.hs[0], mh = 8 * in.vs[0];
         const int mcux = in.blocks_w[0] / in.hs[0], mcuy = in.blocks_h[0] / in.vs[0];
@@ -604,6 +625,12 @@ void aeonb_provider::stage_inputs(batch_plan& B)
                 if (i < njobs)
                 {
                     jpeg_job& job = B.jobs[i];
+                    if (job.png)
+                    {
+                        png_decode_bgr(job.data, job.size, job.pinfo, reinterpret_cast<uint8_t*>(hstage + job.stage_off), job.pitch);
+                        remaining[group_of(i)].fetch_sub(1, std::memory_order_release);
+                        return;
+                    }
                     std::memcpy(hstage + job.stage_off, job.frame.quant, sizeof job.frame.quant);
                     if (job.on_device)
                     {
@@ -686,12 +713,16 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n)
             check_status(aeonb_jpeg_entropy_batch(ctx, ed.data(), B.n_device_jobs));
             h2d_bytes += (int64_t)(sizeof(aeonb_entropy_desc) * B.n_device_jobs);
         }
-        vector<aeonb_jpeg_desc> jd(njobs);
+        vector<aeonb_jpeg_desc> jd;
+        jd.reserve(njobs);
         for (int i = 0; i < njobs; ++i)
         {
-            const jpeg_job&        job = B.jobs[i];
-            const aeonb_jpeg_info& in  = job.frame.info;
-            aeonb_jpeg_desc&       d   = jd[i];
+            const jpeg_job& job = B.jobs[i];
+            if (job.png)
+                continue; // already pixels
+            const aeonb_jpeg_info& in = job.frame.info;
+            jd.emplace_back();
+            aeonb_jpeg_desc& d = jd.back();
             d.width  = job.rw;
             d.height = job.rh;
             d.ncomp  = in.ncomp;
@@ -709,8 +740,8 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n)
             d.dst_pitch        = job.pitch;
             d.dst_pixel_stride = pixel_stride;
         }
-        check_status(aeonb_jpeg_backend_batch(ctx, jd.data(), njobs));
-        h2d_bytes += (int64_t)(sizeof(aeonb_jpeg_desc) * njobs);
+        check_status(aeonb_jpeg_backend_batch(ctx, jd.data(), (int)jd.size()));
+        h2d_bytes += (int64_t)(sizeof(aeonb_jpeg_desc) * jd.size());
     }
     // Where a decoded picture stands for the passes that read it: the decoded region, or the turned copy.
     struct picture
@@ -720,6 +751,8 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n)
     };
     auto picture_of = [&](int j) {
         const jpeg_job& job = B.jobs[j];
+        if (job.png)
+            return picture{reinterpret_cast<const uint8_t*>(dstage + job.stage_off), job.pitch, 3, job.pw, job.ph, 0, 0};
         if (job.oriented)
             return picture{static_cast<const uint8_t*>(oriented_dev.p) + job.opixel_off, job.opitch, 3, job.pw, job.ph, 0, 0};
         return picture{static_cast<const uint8_t*>(pixels_dev.p) + job.pixel_off, job.pitch, pixel_stride, job.rw, job.rh, job.rx, job.ry};

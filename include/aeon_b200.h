@@ -303,6 +303,12 @@ int aeonb_jpeg_entropy_decode_roi(const void* data, size_t size, const int32_t r
 int aeonb_jpeg_entropy_prepare(const void* data, size_t size, aeonb_jpeg_info* info, uint16_t quant[192], uint8_t tables[1088],
                                aeonb_entropy_desc* desc, size_t* scan_offset);
 
+/* PNG records (cv::imdecode reads them too, src/etl_image.cpp:90; aeon's own geometry tests feed PNG): decoded on the
+ * host into the B,G,R picture IMREAD_COLOR delivers (palette expanded, grey replicated, 16-bit samples cut to the high
+ * byte, alpha dropped).  dst: height rows of `pitch` >= 3*width bytes.  Interlaced files: AEONB_ERR_UNSUPPORTED. */
+int aeonb_png_info(const void* data, size_t size, int32_t* width, int32_t* height);
+int aeonb_png_decode_bgr(const void* data, size_t size, uint8_t* dst, size_t pitch);
+
 /* Draws augmentation parameters exactly as aeon's param_factory::make_params does
  * (src/augment_image.cpp:107-230) for `n` records whose decoded sizes are in_w/in_h,
  * using per-slot std::minstd_rand0 engines seeded as aeon's batch_decoder seeds them

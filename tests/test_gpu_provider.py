@@ -371,3 +371,40 @@ def test_exif_orientation_through_the_provider(ctx):
         got = make_provider(ctx, cfg).run_host(recs)["image"]
         want = PipelineOracle(cfg).batch(recs)["image"]
         assert np.array_equal(got, want)
+
+
+def test_png_records_lossless_geometry_like_the_reference_tests(ctx):
+    """aeon's geometry tests feed PNG-coded "indexed" pictures (pixel value = position, test/test_image.cpp:462-493,
+    564-595): with a crop of exactly the output size nothing is resampled, so every output pixel must be the source
+    pixel at the drawn crop offset, flipped when the draw says so; and the batch must equal the oracle's."""
+    import cv2
+    h, w = 200, 256
+    yy, xx = np.mgrid[0:h, 0:w]
+    indexed = np.dstack([xx, yy, (xx + yy) % 256]).astype(np.uint8)
+    blob = cv2.imencode(".png", indexed)[1].tobytes()
+    cfg = {"batch_size": 4, "random_seed": 71, "etl": [{"type": "image", "height": 100, "width": 128, "output_type": "uint8_t",
+                                                         "channel_major": False}],
+           "augmentation": [{"type": "image", "crop_enable": True, "scale": [0.5, 0.5], "center": False, "flip_enable": True}]}
+    recs = [(blob,)] * 4
+    got = make_provider(ctx, cfg).run_host(recs)["image"]
+    want = PipelineOracle(cfg).batch(recs)["image"]
+    assert np.array_equal(got, want)
+    for img in got:                                           # 100 x 128 x 3, values are source coordinates
+        x0 = int(min(img[0, 0, 0], img[0, -1, 0]))
+        y0 = int(img[0, 0, 1])
+        window = indexed[y0:y0 + 100, x0:x0 + 128]
+        assert np.array_equal(img, window) or np.array_equal(img, window[:, ::-1])
+
+
+def test_png_and_jpeg_records_in_one_batch(ctx):
+    import cv2
+    rng = np.random.default_rng(72)
+    recs = []
+    for i in range(8):
+        img = gradient_image(rng, int(rng.integers(200, 400)), int(rng.integers(200, 400)))
+        recs.append((cv2.imencode(".png", img)[1].tobytes() if i % 2 else jpeg_bytes(img, 90),))
+    cfg = {"batch_size": 8, "random_seed": 45, "etl": [{"type": "image", "height": 96, "width": 96, "output_type": "float"}],
+           "augmentation": [dict(AUG_C2, angle=[-10, 10])]}
+    got = make_provider(ctx, cfg).run_host(recs)["image"]
+    want = PipelineOracle(cfg).batch(recs)["image"]
+    assert np.abs(got - want).max() <= 1e-6
