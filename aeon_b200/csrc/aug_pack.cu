@@ -539,7 +539,7 @@ namespace aeonb
                     const int     chunks = (lay.slot_w + VEC - 1) / VEC;
                     T*            dst    = reinterpret_cast<T*>(d.dst);
                     const T       zero   = convert_out<T>(0);
-                    for (int line = warp; line < 3 * rows; line += WARPS)
+                    for (int line = warp; line < lay.channels * rows; line += WARPS) // 1 channel: the B plane of a grey picture
                     {
                         const int  c      = (line >= rows) + (line >= 2 * rows);
                         const int  r      = line - c * rows;

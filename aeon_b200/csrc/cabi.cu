@@ -166,8 +166,10 @@ void aeonb::check_image_batch(const aeonb_image_desc* d, int n, const aeonb_imag
 {
     if (L.slot_w <= 0 || L.slot_h <= 0)
         throw std::invalid_argument("invalid width or height of the output slot");
-    if (L.channels != 3)
-        throw error(AEONB_ERR_UNSUPPORTED, "the image kernel handles 3-channel images only");
+    if (L.channels != 3 && L.channels != 1)
+        throw std::invalid_argument("the output has 1 or 3 channels");
+    if (L.channels == 1 && L.bgr_to_rgb)
+        throw std::invalid_argument("invalid config: bgr_to_rgb can be 'true' only for channels set to '3'");
     if (L.standardize && !(L.dtype == AEONB_F32 || L.dtype == AEONB_F64))
         throw std::invalid_argument(
             "Standardization (mean, stddev) is supported only for float or double 'output_type'.");

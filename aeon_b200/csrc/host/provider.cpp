@@ -214,8 +214,6 @@ aeonb_provider::aeonb_provider(aeonb_ctx* c, const json& cfg) : ctx(c)
                 if ((int)factory.mean.size() != st.image.channels || (int)factory.stddev.size() != st.image.channels)
                     throw std::invalid_argument("Size of 'mean' and 'stddev' must be equal to number of channels or empty.");
             }
-            if (st.image.channels != 3)
-                throw error(AEONB_ERR_UNSUPPORTED, "single-channel image output is outside the accelerated path");
             add(prefixed(st.image.name, "image"), st.image.shape, false);
         }
         else if (t == "label")

@@ -81,6 +81,9 @@ namespace aeonb
         // which the image kernel reads from the device copy; none of the JPEG fields apply.
         bool               png = false;
         png_info           pinfo;
+        // A stage with "channels": 1 reads the picture as cv::imdecode(..., GRAYSCALE) delivers it: for a JPEG the luma
+        // plane alone goes through the back end (B = G = R = Y), the chroma planes are decoded but not used.
+        bool               grey = false;
         bool               oriented = false;
         size_t             opixel_off = 0;
         int                opitch = 0;

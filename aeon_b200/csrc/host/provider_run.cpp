@@ -420,11 +420,22 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
                 if (size == 0)
                     empty("encoded image");
                 const int  j  = plan_jpeg(data, size);
+                if (sg.image.channels == 1)
+                {
+                    // IMREAD_GRAYSCALE: a JPEG gives its luma plane; a colour PNG would go through libpng's own grey
+                    // conversion, which is not reproduced here
+                    if (B.jobs[j].png && (B.jobs[j].pinfo.color_type & 2))
+                        throw error(AEONB_ERR_UNSUPPORTED, "a colour PNG read as one channel is outside the accelerated path");
+                    B.jobs[j].grey = true;
+                }
                 if (!have_params)
                 {
                     params      = factory.make_params(engine, B.jobs[j].pw, B.jobs[j].ph, sg.image.width, sg.image.height);
                     have_params = true;
                 }
+                if (sg.image.channels == 1 && (params.brightness != 1.0f || params.saturation != 1.0f || params.hue != 0))
+                    throw std::invalid_argument("brightness, saturation and hue need a 3-channel picture (cv::transform / cv::cvtColor "
+                                                "reject one channel)");
                 aeonb_image_desc d = plan_picture(s, j, params, sg.image.width, sg.image.height, !factory.fixed_aspect_ratio);
                 if (d.out_w > sg.image.width || d.out_h > sg.image.height)
                     throw std::invalid_argument("transformed image does not fit the configured output size");
@@ -725,14 +736,14 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n)
             aeonb_jpeg_desc& d = jd.back();
             d.width  = job.rw;
             d.height = job.rh;
-            d.ncomp  = in.ncomp;
-            for (int c = 0; c < in.ncomp; ++c)
+            d.ncomp  = job.grey ? 1 : in.ncomp;
+            for (int c = 0; c < d.ncomp; ++c)
             {
                 d.coef[c]     = job.on_device ? reinterpret_cast<const int16_t*>(cdev + B.status_room + job.plane_dev_off[c])
                                               : reinterpret_cast<const int16_t*>(dstage + job.plane_off[c]);
                 d.quant[c]    = reinterpret_cast<const uint16_t*>(dstage + job.stage_off) + 64 * c;
-                d.hs[c]       = in.hs[c];
-                d.vs[c]       = in.vs[c];
+                d.hs[c]       = job.grey ? 1 : in.hs[c];
+                d.vs[c]       = job.grey ? 1 : in.vs[c];
                 d.blocks_w[c] = job.roi_blocks_w[c];
                 d.blocks_h[c] = job.roi_blocks_h[c];
             }
@@ -835,13 +846,14 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n)
                 else
                 {
                     L.stride_c = 1;
-                    L.stride_y = (int64_t)ic.width * 3;
-                    L.stride_x = 3;
+                    L.stride_y = (int64_t)ic.width * ic.channels;
+                    L.stride_x = ic.channels;
                 }
+                L.channels = ic.channels;
                 if (!factory.mean.empty())
                 {
                     L.standardize = 1;
-                    for (int c = 0; c < 3; ++c)
+                    for (int c = 0; c < ic.channels; ++c)
                     {
                         const double sd = factory.stddev[c];
                         L.mean64[c]     = factory.mean[c];

@@ -110,7 +110,7 @@ typedef struct aeonb_image_desc
 typedef struct aeonb_image_layout
 {
     int32_t slot_w, slot_h; /* spatial size of the slot */
-    int32_t channels;       /* 3 (1 is reserved) */
+    int32_t channels;       /* 3, or 1: only the first plane is written (grey pictures arrive as B = G = R) */
     int32_t dtype;          /* aeonb_dtype of the output elements */
     int32_t bgr_to_rgb;     /* reverse the channel order on output */
     int64_t stride_c, stride_y, stride_x; /* element strides of the slot; CHW: (H*W, W, 1); HWC: (1, W*C, C);

@@ -255,6 +255,9 @@ def contrast_u8(img, contrast):
 
 
 def cbsjitter(img, contrast, brightness, saturation, hue):
+    if img.shape[2] != 3 and (f32(brightness) != 1.0 or f32(saturation) != 1.0 or int(hue) != 0):
+        # cv::transform with a 3x3 matrix and cv::cvtColor(BGR2HSV) reject a one-channel picture
+        raise ValueError("brightness, saturation and hue need a 3-channel picture")
     if f32(brightness) != 1.0 or f32(saturation) != 1.0:
         img = transform_u8(img, color_matrix(brightness, saturation))
     if int(hue) != 0:
@@ -294,7 +297,7 @@ def lighting_u8(img, alphas, color_noise_std):
         return img
     scale, offs = lighting_terms(alphas, color_noise_std)
     t = _sat_u8(_rne(img.astype(f32) * scale)).astype(np.int32)
-    return _sat_u8(t + offs[None, None, :])
+    return _sat_u8(t + offs[None, None, :img.shape[2]])   # a one-channel picture takes the first element of the pixel
 
 
 # ---------------------------------------------------------------------------------------------

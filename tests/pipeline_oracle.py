@@ -21,11 +21,11 @@ class PipelineOracle:
         self.cursor = 0
 
     @staticmethod
-    def decode(blob):
+    def decode(blob, channels=3):
         import cv2
-        img = cv2.imdecode(np.frombuffer(blob, np.uint8), cv2.IMREAD_COLOR)
+        img = cv2.imdecode(np.frombuffer(blob, np.uint8), cv2.IMREAD_COLOR if channels == 3 else cv2.IMREAD_GRAYSCALE)
         assert img is not None
-        return img
+        return img if channels == 3 else img[..., None]
 
     def image(self, etl, img, p):
         out = ops.transform_single_image(img, p)
@@ -34,7 +34,7 @@ class PipelineOracle:
                   output_type=etl.get("output_type", "uint8_t"), mean=self.aug.get("mean"), stddev=self.aug.get("stddev"))
         if out.shape[:2] == (h, w):
             return ops.load_image(out, **kw)
-        z = ops.load_image(np.zeros((h, w, 3), np.uint8), kw["channel_major"], kw["bgr_to_rgb"], kw["output_type"])
+        z = ops.load_image(np.zeros((h, w, out.shape[2]), np.uint8), kw["channel_major"], kw["bgr_to_rgb"], kw["output_type"])
         roi = ops.load_image(out, **kw)
         if kw["channel_major"]:
             z[:, :out.shape[0], :out.shape[1]] = roi
@@ -51,7 +51,7 @@ class PipelineOracle:
             for etl, blob in zip(self.cfg["etl"], rec):
                 name = (etl.get("name", "") + "." if etl.get("name") else "")
                 if etl["type"] == "image":
-                    img = self.decode(blob)
+                    img = self.decode(blob, etl.get("channels", 3))
                     if p is None:
                         p = self.factory.make_params(g, img.shape[1], img.shape[0], etl["width"], etl["height"])
                     outs.setdefault(name + "image", []).append(self.image(etl, img, p))

@@ -408,3 +408,28 @@ def test_png_and_jpeg_records_in_one_batch(ctx):
     got = make_provider(ctx, cfg).run_host(recs)["image"]
     want = PipelineOracle(cfg).batch(recs)["image"]
     assert np.abs(got - want).max() <= 1e-6
+
+
+def test_one_channel_output_from_grey_png_and_from_jpeg_luma(ctx):
+    """"channels": 1 makes aeon call cv::imdecode(..., GRAYSCALE) (src/etl_image.cpp:63-99): a grey PNG as it is (the MNIST
+    shape), a colour JPEG as its luma plane; geometry, contrast, lighting and standardisation act on the one channel."""
+    import cv2
+    rng = np.random.default_rng(73)
+    digits = [cv2.imencode(".png", rng.integers(0, 256, (28, 28), dtype=np.uint8))[1].tobytes() for _ in range(8)]
+    cfg = {"batch_size": 8, "random_seed": 46, "etl": [{"type": "image", "height": 28, "width": 28, "channels": 1, "output_type": "uint8_t"}],
+           "augmentation": [{"type": "image", "flip_enable": True, "crop_enable": False}]}
+    got = make_provider(ctx, cfg).run_host([(b,) for b in digits])["image"]
+    assert got.shape == (8, 1, 28, 28)
+    assert np.array_equal(got, PipelineOracle(cfg).batch([(b,) for b in digits])["image"])
+    photos = [(jpeg_bytes(gradient_image(rng, int(rng.integers(200, 400)), int(rng.integers(200, 400))), 90),) for _ in range(8)]
+    for channel_major in (True, False):
+        cfg = {"batch_size": 8, "random_seed": 47,
+               "etl": [{"type": "image", "height": 64, "width": 80, "channels": 1, "output_type": "float", "channel_major": channel_major}],
+               "augmentation": [dict(AUG_C1, contrast=[0.6, 1.4], lighting=[0.0, 0.1], angle=[-10, 10], mean=[0.45], stddev=[0.22])]}
+        got = make_provider(ctx, cfg).run_host(photos)["image"]
+        want = PipelineOracle(cfg).batch(photos)["image"]
+        assert got.shape == ((8, 1, 64, 80) if channel_major else (8, 64, 80, 1))
+        assert np.abs(got - want).max() <= 1e-6
+    bad = dict(cfg, augmentation=[dict(AUG_C1, brightness=[0.5, 0.6])])
+    with pytest.raises(Exception, match="3-channel"):
+        make_provider(ctx, bad).run_host(photos)
