@@ -285,11 +285,12 @@ int aeonb_jpeg_backend_batch(aeonb_ctx* ctx, const aeonb_jpeg_desc* descs, int n
             std::ostringstream     ss;
             const bool sampling_ok = r.ncomp == 1 || (r.ncomp == 3 && r.hs[1] == 1 && r.vs[1] == 1 && r.hs[2] == 1 && r.vs[2] == 1 &&
                                                       ((r.hs[0] == 1 && r.vs[0] == 1) || (r.hs[0] == 2 && r.vs[0] == 1) ||
-                                                       (r.hs[0] == 2 && r.vs[0] == 2)));
+                                                       (r.hs[0] == 2 && r.vs[0] == 2) || (r.hs[0] == 1 && r.vs[0] == 2) ||
+                                                       (r.hs[0] == 4 && r.vs[0] == 1)));
             if (r.width <= 0 || r.height <= 0 || !r.dst)
                 ss << "record " << i << ": empty image or NULL destination";
             else if (!sampling_ok || (r.ncomp == 1 && (r.hs[0] != 1 || r.vs[0] != 1)))
-                ss << "record " << i << ": unsupported component layout (supported: grey, 4:4:4, 4:2:2, 4:2:0)";
+                ss << "record " << i << ": unsupported component layout (supported: grey, 4:4:4, 4:2:2, 4:2:0, 4:4:0, 4:1:1)";
             else if (r.dst_pixel_stride != 3 && r.dst_pixel_stride != 4)
                 ss << "record " << i << ": destination pixel stride must be 3 or 4";
             else if (r.dst_pitch < r.width * r.dst_pixel_stride || (r.dst_pitch & (r.dst_pixel_stride == 4 ? 15 : 3)) ||

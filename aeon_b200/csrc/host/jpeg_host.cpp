@@ -424,9 +424,10 @@ namespace aeonb
                 {
                     const bool chroma_ok = in.hs[1] == 1 && in.vs[1] == 1 && in.hs[2] == 1 && in.vs[2] == 1;
                     const bool luma_ok   = (in.hs[0] == 1 && in.vs[0] == 1) || (in.hs[0] == 2 && in.vs[0] == 1) ||
-                                         (in.hs[0] == 2 && in.vs[0] == 2);
+                                         (in.hs[0] == 2 && in.vs[0] == 2) || (in.hs[0] == 1 && in.vs[0] == 2) ||
+                                         (in.hs[0] == 4 && in.vs[0] == 1);
                     if (!chroma_ok || !luma_ok)
-                        bad("unsupported chroma subsampling (supported: 4:4:4, 4:2:2, 4:2:0)");
+                        bad("unsupported chroma subsampling (supported: 4:4:4, 4:2:2, 4:2:0, 4:4:0, 4:1:1)");
                 }
                 return;
             }

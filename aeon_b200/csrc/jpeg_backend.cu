@@ -405,7 +405,31 @@ namespace aeonb
                     else
                     {
                         int cb[4], cr[4];
-                        if (fh == 1)
+                        if (fh == 1 && fv == 2)
+                        {
+                            // 4:4:0: libjpeg's vertical triangle filter alone (3 near + 1 far, bias 1 upper / 2 lower row)
+                            const int cy   = y >> 1;
+                            const int far  = ((y & 1) ? min(cy + 1, chh - 1) : max(cy - 1, 0)) - crow_base;
+                            const int near = cy - crow_base, bias = (y & 1) ? 2 : 1;
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                            {
+                                cb[k] = (3 * cbplane[near * cwp + x0 + k] + cbplane[far * cwp + x0 + k] + bias) >> 2;
+                                cr[k] = (3 * crplane[near * cwp + x0 + k] + crplane[far * cwp + x0 + k] + bias) >> 2;
+                            }
+                        }
+                        else if (fh == 4)
+                        {
+                            // 4:1:1: four pixels share one chroma sample (libjpeg replicates when the factor is not 2)
+                            const int cy = y - crow_base;
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                            {
+                                cb[k] = cbplane[cy * cwp + (x0 >> 2)];
+                                cr[k] = crplane[cy * cwp + (x0 >> 2)];
+                            }
+                        }
+                        else if (fh == 1)
                         {
                             const int cy = y - crow_base;
                             const uint32_t u = *reinterpret_cast<const uint32_t*>(cbplane + cy * cwp + x0);

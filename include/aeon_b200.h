@@ -190,7 +190,7 @@ typedef struct aeonb_jpeg_desc
     const uint16_t* quant[3]; /* device: 64 quantiser steps per component, same column-major order */
     int32_t width, height;    /* image size in pixels */
     int32_t ncomp;            /* 1 (grey) or 3 (YCbCr) */
-    int32_t hs[3], vs[3];     /* sampling factors; supported: grey, 4:4:4, 4:2:2 (2x1), 4:2:0 (2x2) */
+    int32_t hs[3], vs[3];     /* sampling factors; supported: grey, 4:4:4, 4:2:2 (2x1), 4:2:0 (2x2), 4:4:0 (1x2), 4:1:1 (4x1) */
     int32_t blocks_w[3], blocks_h[3]; /* coefficient plane size in blocks (padded to whole MCUs) */
     uint8_t* dst;             /* device: interleaved B,G,R[,x] output */
     int32_t dst_pitch;

@@ -140,3 +140,18 @@ def test_exif_orientation_is_applied_as_opencv_does(ctx):
     for i, b in enumerate(cases):
         ref = cv2.imdecode(np.frombuffer(b, np.uint8), cv2.IMREAD_COLOR)
         assert got[i].shape == ref.shape and np.array_equal(got[i], ref), "orientation %d" % (i + 1)
+
+
+def test_440_and_411_sampling(ctx):
+    """4:4:0 (libjpeg's vertical-only triangle filter) and 4:1:1 (replication), baseline and progressive, odd sizes."""
+    import cv2
+    rng = np.random.default_rng(33)
+    cases = []
+    for (h, w) in [(8, 8), (1, 1), (17, 16), (37, 53), (64, 80), (33, 47), (15, 130), (200, 9), (375, 500)]:
+        for factor in (cv2.IMWRITE_JPEG_SAMPLING_FACTOR_440, cv2.IMWRITE_JPEG_SAMPLING_FACTOR_411):
+            for extra in ([], [cv2.IMWRITE_JPEG_PROGRESSIVE, 1], [cv2.IMWRITE_JPEG_RST_INTERVAL, 2]):
+                cases.append(jpeg_bytes(rng.integers(0, 256, (h, w, 3), dtype=np.uint8), int(rng.integers(30, 100)),
+                                        [cv2.IMWRITE_JPEG_SAMPLING_FACTOR, factor] + extra))
+    got = decode_gpu(ctx, cases)
+    for i, b in enumerate(cases):
+        assert np.array_equal(got[i], cv2.imdecode(np.frombuffer(b, np.uint8), cv2.IMREAD_COLOR)), "case %d" % i

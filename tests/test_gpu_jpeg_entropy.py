@@ -54,6 +54,8 @@ def test_sampling_modes_sizes_and_restarts(ctx, parallel):
     for (h, w) in [(8, 8), (1, 1), (17, 16), (37, 53), (64, 80), (33, 47), (15, 130), (200, 9), (256, 256)]:
         for extra in ([], [cv2.IMWRITE_JPEG_SAMPLING_FACTOR, cv2.IMWRITE_JPEG_SAMPLING_FACTOR_444],
                       [cv2.IMWRITE_JPEG_SAMPLING_FACTOR, cv2.IMWRITE_JPEG_SAMPLING_FACTOR_422],
+                      [cv2.IMWRITE_JPEG_SAMPLING_FACTOR, cv2.IMWRITE_JPEG_SAMPLING_FACTOR_440],
+                      [cv2.IMWRITE_JPEG_SAMPLING_FACTOR, cv2.IMWRITE_JPEG_SAMPLING_FACTOR_411],
                       [cv2.IMWRITE_JPEG_RST_INTERVAL, 3], [cv2.IMWRITE_JPEG_OPTIMIZE, 1]):
             blobs.append(jpeg_bytes(rng.integers(0, 256, (h, w, 3), dtype=np.uint8), int(rng.integers(30, 101)), extra))
     blobs.append(jpeg_bytes(gradient_image(rng, 45, 30)[..., 0], 85))
