@@ -45,6 +45,33 @@ namespace aeonb
             return make_float2(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x);
         }
 
+        // Power row -> sparse mel filters -> log [-> first num_cepstra rows of the orthonormal DCT-II].  `cep` is scratch for
+        // the log-mel vector when a DCT follows (num_filters floats, may not alias `power`).
+        __device__ __forceinline__ void finish_mel(const spec_launch& P, const float* power, float* cep, float* out, int lane)
+        {
+            for (int j = lane; j < P.cfg.num_filters; j += 32)
+            {
+                float acc = 0.f;
+                for (int i = P.filt_start[j]; i < P.filt_start[j + 1]; ++i)
+                    acc += power[P.filt_bin[i]] * P.filt_weight[i];
+                if (P.dct)
+                    cep[j] = logf(acc);
+                else
+                    out[j] = logf(acc);
+            }
+            if (!P.dct)
+                return;
+            __syncwarp();
+            for (int j = lane; j < P.cfg.num_cepstra; j += 32)
+            {
+                const float* row = P.dct + (size_t)j * P.dct_n;
+                float        acc = 0.f;
+                for (int k = 0; k < P.cfg.num_filters; ++k)
+                    acc += cep[k] * __ldg(row + k);
+                out[j] = acc;
+            }
+        }
+
         template <int R>
         __global__ void __launch_bounds__(SPEC_THREADS) specgram_kernel(const spec_launch P)
         {
@@ -150,30 +177,62 @@ namespace aeonb
                 return;
             __syncwarp();
 
-            // ---- sparse mel filters + log (into the transform buffer when a DCT follows: it is free again)
-            float* const cep = reinterpret_cast<float*>(zbuf[warp]);
-            for (int j = lane; j < P.cfg.num_filters; j += 32)
+            finish_mel(P, pbuf[warp], reinterpret_cast<float*>(zbuf[warp]), out, lane);
+        }
+
+        // Any frame length: one warp per frame, lanes take the bins, each bin a direct sum over the frame with the
+        // twiddles from a table of L entries (index k*n mod L kept by addition).  O(L^2) per frame instead of the
+        // O(L log L) of the kernel above, but the whole spectrogram stage is small next to the HBM traffic of its
+        // output, and frame lengths such as 400 (25 ms at 16 kHz) have no factor of 64.
+        constexpr int SPEC_GENERIC_WARPS = 4;
+        __global__ void __launch_bounds__(SPEC_GENERIC_WARPS * 32) specgram_generic_kernel(const spec_launch P)
+        {
+            extern __shared__ float gsm[];
+            const int L = P.cfg.frame_length, H = L / 2; // bins 0..H
+            float*    xs   = gsm + (size_t)(threadIdx.x >> 5) * (L + H + 1); // this warp's windowed samples, then its power row
+            float*    pw   = xs + L;
+            const int lane = threadIdx.x & 31;
+            const aeonb_specgram_desc d = P.descs[blockIdx.y];
+            const int frame = blockIdx.x * SPEC_GENERIC_WARPS + (threadIdx.x >> 5);
+            if (frame >= P.cfg.max_time_steps)
+                return;
+            float* out = d.dst + (size_t)frame * P.n_out;
+            int    frames = d.n_samples >= L ? (d.n_samples - L) / P.cfg.frame_stride + 1 : 0;
+            frames        = min(frames, P.cfg.max_time_steps);
+            if (frame >= frames)
             {
-                float acc = 0.f;
-                for (int i = P.filt_start[j]; i < P.filt_start[j + 1]; ++i)
-                    acc += pbuf[warp][P.filt_bin[i]] * P.filt_weight[i];
-                if (P.dct)
-                    cep[j] = logf(acc);
-                else
-                    out[j] = logf(acc);
+                for (int j = lane; j < P.n_out; j += 32)
+                    out[j] = 0.f;
+                return;
             }
-            if (!P.dct)
+            const int16_t* x = d.samples + (size_t)frame * P.cfg.frame_stride;
+            for (int n = lane; n < L; n += 32)
+                xs[n] = (float)x[n] * (P.window ? __ldg(P.window + n) : 1.f);
+            __syncwarp();
+            const float scale = 1.0f / (float)(2 * H);
+            for (int k = lane; k <= H; k += 32)
+            {
+                float re = 0.f, im = 0.f;
+                int   idx = 0; // k*n mod L
+                for (int n = 0; n < L; ++n)
+                {
+                    const float2 w = __ldg(P.twiddle + idx); // exp(-2*pi*i*idx/L)
+                    re += xs[n] * w.x;
+                    im += xs[n] * w.y;
+                    idx += k;
+                    if (idx >= L)
+                        idx -= L;
+                }
+                const float mag = sqrtf(re * re + im * im);
+                if (P.cfg.num_filters > 0)
+                    pw[k] = scale * mag * mag;
+                else
+                    out[k] = mag;
+            }
+            if (P.cfg.num_filters <= 0)
                 return;
             __syncwarp();
-            // ---- MFCC: first num_cepstra rows of the orthonormal DCT-II of the log-mel vector (padding adds zeros only)
-            for (int j = lane; j < P.cfg.num_cepstra; j += 32)
-            {
-                const float* row = P.dct + (size_t)j * P.dct_n;
-                float        acc = 0.f;
-                for (int k = 0; k < P.cfg.num_filters; ++k)
-                    acc += cep[k] * __ldg(row + k);
-                out[j] = acc;
-            }
+            finish_mel(P, pw, xs, out, lane);
         }
 
         template <int R>
@@ -209,5 +268,23 @@ namespace aeonb
         case 10: return launch_r<10>(P, n, stream);
         default: return cudaErrorInvalidValue;
         }
+    }
+
+    size_t specgram_generic_smem(int frame_length) { return (size_t)SPEC_GENERIC_WARPS * (frame_length + frame_length / 2 + 1) * sizeof(float); }
+
+    // Frame lengths the shuffle-FFT kernel does not take: `twiddle_dev` then holds frame_length entries exp(-2*pi*i*k/L).
+    cudaError_t launch_specgram_generic(const aeonb_specgram_desc* descs_dev, int n, const aeonb_specgram_config& cfg,
+                                        const float* window_dev, const float2* twiddle_dev, const int* filt_start_dev,
+                                        const int* filt_bin_dev, const float* filt_weight_dev, const float* dct_dev, int dct_n,
+                                        int n_out, cudaStream_t stream)
+    {
+        spec_launch  P{descs_dev, cfg, window_dev, twiddle_dev, filt_start_dev, filt_bin_dev, filt_weight_dev, dct_dev, dct_n, n_out};
+        const size_t smem = specgram_generic_smem(cfg.frame_length);
+        cudaError_t  err  = cudaFuncSetAttribute(specgram_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess)
+            return err;
+        dim3 grid((cfg.max_time_steps + SPEC_GENERIC_WARPS - 1) / SPEC_GENERIC_WARPS, n, 1);
+        specgram_generic_kernel<<<grid, SPEC_GENERIC_WARPS * 32, smem, stream>>>(P);
+        return cudaGetLastError();
     }
 }

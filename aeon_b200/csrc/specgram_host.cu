@@ -15,6 +15,11 @@ namespace aeonb
                                 const float* window_dev, const float2* twiddle_dev, const int* filt_start_dev,
                                 const int* filt_bin_dev, const float* filt_weight_dev, const float* dct_dev, int dct_n, int n_out,
                                 cudaStream_t stream);
+    cudaError_t launch_specgram_generic(const aeonb_specgram_desc* descs_dev, int n, const aeonb_specgram_config& cfg,
+                                        const float* window_dev, const float2* twiddle_dev, const int* filt_start_dev,
+                                        const int* filt_bin_dev, const float* filt_weight_dev, const float* dct_dev, int dct_n,
+                                        int n_out, cudaStream_t stream);
+    size_t      specgram_generic_smem(int frame_length);
     bool specgram_frame_length_supported(int frame_length);
 
     // aeon specgram::create_window (src/specgram.cpp:156-189); code 0 = no window.
@@ -78,22 +83,36 @@ namespace aeonb
     specgram_tables::specgram_tables(const aeonb_specgram_config& cfg)
     {
         const int L = cfg.frame_length, H = L / 2;
-        if (!specgram_frame_length_supported(L))
-            throw error(AEONB_ERR_UNSUPPORTED, "frame_length must be 64*R with R in {1,2,3,4,5,6,8,10}");
+        fast = specgram_frame_length_supported(L);
+        if (L < 2 || specgram_generic_smem(L) > 200 * 1024)
+            throw error(AEONB_ERR_UNSUPPORTED, "frame_length is limited to 12700 samples");
         if (cfg.frame_stride <= 0 || cfg.max_time_steps <= 0 || cfg.num_filters < 0 || cfg.num_filters > H + 1)
             throw std::invalid_argument("invalid spectrogram configuration");
         if (cfg.window)
             window = to_device(make_window(cfg.window, L));
-        std::vector<float2> tw(H + H + 1);
-        for (int k = 0; k < H; ++k)
+        std::vector<float2> tw;
+        if (fast)
         {
-            const double a = -2.0 * 3.14159265358979323846 * k / H;
-            tw[k]          = make_float2((float)std::cos(a), (float)std::sin(a));
+            tw.resize(H + H + 1);
+            for (int k = 0; k < H; ++k)
+            {
+                const double a = -2.0 * 3.14159265358979323846 * k / H;
+                tw[k]          = make_float2((float)std::cos(a), (float)std::sin(a));
+            }
+            for (int k = 0; k <= H; ++k)
+            {
+                const double a = -2.0 * 3.14159265358979323846 * k / L;
+                tw[H + k]      = make_float2((float)std::cos(a), (float)std::sin(a));
+            }
         }
-        for (int k = 0; k <= H; ++k)
+        else
         {
-            const double a = -2.0 * 3.14159265358979323846 * k / L;
-            tw[H + k]      = make_float2((float)std::cos(a), (float)std::sin(a));
+            tw.resize(L); // the direct-sum kernel: exp(-2*pi*i*k/L), k = 0..L-1
+            for (int k = 0; k < L; ++k)
+            {
+                const double a = -2.0 * 3.14159265358979323846 * k / L;
+                tw[k]          = make_float2((float)std::cos(a), (float)std::sin(a));
+            }
         }
         twiddle = to_device(tw);
         n_out   = cfg.num_filters > 0 ? cfg.num_filters : H + 1;
@@ -147,7 +166,8 @@ namespace aeonb
     cudaError_t specgram_tables::launch(const aeonb_specgram_desc* descs_dev, int n, const aeonb_specgram_config& cfg,
                                         cudaStream_t stream) const
     {
-        return launch_specgram(descs_dev, n, cfg, window, twiddle, filt_start, filt_bin, filt_weight, dct, dct_n, n_out, stream);
+        return fast ? launch_specgram(descs_dev, n, cfg, window, twiddle, filt_start, filt_bin, filt_weight, dct, dct_n, n_out, stream)
+                    : launch_specgram_generic(descs_dev, n, cfg, window, twiddle, filt_start, filt_bin, filt_weight, dct, dct_n, n_out, stream);
     }
 
     namespace

@@ -22,6 +22,7 @@ namespace aeonb
         float*  dct         = nullptr; // MFCC: num_cepstra x dct_n
         int     dct_n       = 0;
         int     n_out       = 0;
+        bool    fast        = true; // frame length 64*R: the shuffle-FFT kernel; otherwise the direct-sum kernel
         explicit specgram_tables(const aeonb_specgram_config& cfg);
         ~specgram_tables();
         specgram_tables(const specgram_tables&) = delete;

@@ -74,10 +74,10 @@ def test_short_and_empty_clips_zero_fill(ctx):
         assert_close(got[i], ospec.log_mel(c, max_time_steps=8))
 
 
-def test_unsupported_frame_length_is_an_error(ctx):
+def test_oversized_frame_length_is_an_error(ctx):
     from aeon_b200._lib import AeonError
     with pytest.raises(AeonError, match="frame_length"):
-        run(ctx, [np.zeros(1000, np.int16)], frame_length=400, frame_stride=160)
+        run(ctx, [np.zeros(1000, np.int16)], frame_length=20000, frame_stride=160, num_filters=0)
 
 
 def test_mfcc(ctx):
@@ -99,3 +99,22 @@ def test_mfcc(ctx):
     o = torch.zeros(60 * 21, dtype=torch.float32, device="cuda")
     d[0].samples, d[0].n_samples, d[0].dst = t.data_ptr(), 2000, o.data_ptr()
     assert ctx.lib.aeonb_specgram_batch(ctx.handle, d, 1, C.byref(cfg)) == L.ERR_INVALID
+
+
+def test_frame_lengths_without_a_factor_of_64(ctx):
+    """400 samples (25 ms at 16 kHz), odd and long frames take the direct-sum kernel: same tolerances as the FFT kernel."""
+    rng = np.random.default_rng(36)
+    clip = synth_clip(rng, 0.9)
+    for L_, win, name in [(400, 1, "hann"), (200, 0, "none"), (321, 2, "hamming"), (1000, 3, "blackman"), (7, 4, "bartlett"), (1024, 1, "hann")]:
+        got = run(ctx, [clip], frame_length=L_, frame_stride=max(L_ // 2, 1), max_time_steps=40, num_filters=0, window=win)[0]
+        want = ospec.log_mel(clip, L_, max(L_ // 2, 1), 40, 0, 16000, name)
+        assert got.shape == want.shape == (40, L_ // 2 + 1)
+        assert np.abs(got - want).max() <= 2e-5 * np.abs(want).max(), (L_, name)
+    clips = [synth_clip(rng, s) for s in (1.0, 0.3)]
+    got = run(ctx, clips, frame_length=400, frame_stride=160, max_time_steps=98, num_filters=40)
+    for g, c in zip(got, clips):
+        assert_close(g, ospec.log_mel(c, 400, 160, 98, 40))
+    got = run(ctx, clips, frame_length=400, frame_stride=160, max_time_steps=98, num_filters=40, num_cepstra=13)
+    for g, c in zip(got, clips):
+        w = ospec.log_mel(c, 400, 160, 98, 40, num_cepstra=13)
+        assert np.isfinite(w).all() and np.all(np.abs(g - w) <= 1e-4 * np.abs(w) + 1e-3)
