@@ -1,8 +1,11 @@
-// Host half of JPEG decoding: marker parsing and baseline Huffman entropy decoding.
+// Host half of JPEG decoding: marker parsing (always), and a Huffman entropy decoder for baseline and
+// progressive streams.
 //
 // aeon calls cv::imdecode per record (src/etl_image.cpp:83-99, src/cap_mjpeg_decoder.cpp:132-147).
-// The serial, bit-granular part of that work stays on the CPU here; it produces quantised
-// DCT coefficient blocks which the GPU back end turns into pixels.  Coefficients of a block
+// Baseline scans are normally Huffman-decoded on the GPU; this decoder takes progressive files (whose scans
+// revisit the same coefficients), streams with more Huffman tables than the device decoder holds, and
+// providers configured with "entropy_decode": "host".  It produces the same quantised
+// DCT coefficient blocks, which the GPU back end turns into pixels.  Coefficients of a block
 // are written in column-major order (element (row r, column c) at index c*8+r) so that a GPU
 // thread that owns one block column reads its eight values with a single 128-bit load.
 #pragma once

@@ -7,10 +7,10 @@
  * point stands in for (paths relative to the aeon tree).
  *
  * Levels, from the GPU up:
- *   1. batch kernels over device-resident data (aeonb_image_batch, aeonb_jpeg_backend_batch,
- *      aeonb_specgram_batch): one launch per batch;
- *   2. host helpers that stay on the CPU by design (JPEG entropy decode, AVI index parse,
- *      augmentation parameter draws);
+ *   1. batch kernels over device-resident data (aeonb_jpeg_entropy_batch, aeonb_jpeg_backend_batch,
+ *      aeonb_orient_batch, aeonb_rotate_batch, aeonb_image_batch, aeonb_specgram_batch): one launch per batch;
+ *   2. host helpers: header parsing, the host Huffman decoder (progressive files, or by choice), PNG decoding,
+ *      AVI index parsing, augmentation parameter draws;
  *   3. the provider: encoded records in host memory -> augmented batch, i.e. what
  *      aeon's batch_decoder + provider_interface::provide do per decode chunk;
  *   4. the loader: manifest -> batches, i.e. aeon's loader / DataLoader iterator.
