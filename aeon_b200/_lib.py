@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(HERE, "libaeon_b200.so")
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_DECODE, ERR_IO, END = 0, -1, -2, -3, -4, -5, 1
 
 U8, I8, I16, U16, I32, F32, F64 = range(7)
-INTERP_NEAREST, INTERP_LINEAR = 0, 1
+INTERP_NEAREST, INTERP_LINEAR, INTERP_CUBIC, INTERP_AREA = 0, 1, 2, 3
 
 
 class ImageDesc(C.Structure):
@@ -50,6 +50,15 @@ class RotateDesc(C.Structure):
 
 class OrientDesc(C.Structure):
     _fields_ = RotateDesc._fields_[:5] + [("orientation", C.c_int32)] + RotateDesc._fields_[6:]
+
+
+class ResizeDesc(C.Structure):
+    _fields_ = [
+        ("src", C.c_void_p), ("src_pitch", C.c_int32), ("src_pixel_stride", C.c_int32), ("src_w", C.c_int32), ("src_h", C.c_int32),
+        ("canvas_x", C.c_int32), ("canvas_y", C.c_int32), ("crop_x", C.c_int32), ("crop_y", C.c_int32), ("crop_w", C.c_int32),
+        ("crop_h", C.c_int32), ("interp", C.c_int32), ("out_w", C.c_int32), ("out_h", C.c_int32), ("dst", C.c_void_p),
+        ("dst_pitch", C.c_int32), ("dst_pixel_stride", C.c_int32), ("channels", C.c_int32), ("reserved0", C.c_int32),
+    ]
 
 
 class JpegDesc(C.Structure):
@@ -104,6 +113,7 @@ PROTOTYPES = {
     "aeonb_image_batch_noalloc": (C.c_int, [C.POINTER(ImageDesc), C.c_int, C.POINTER(ImageLayout), C.c_void_p]),
     "aeonb_rotate_batch": (C.c_int, [C.c_void_p, C.POINTER(RotateDesc), C.c_int]),
     "aeonb_orient_batch": (C.c_int, [C.c_void_p, C.POINTER(OrientDesc), C.c_int]),
+    "aeonb_resize_batch": (C.c_int, [C.c_void_p, C.POINTER(ResizeDesc), C.c_int]),
     "aeonb_jpeg_backend_batch": (C.c_int, [C.c_void_p, C.POINTER(JpegDesc), C.c_int]),
     "aeonb_jpeg_backend_bytes": (C.c_int64, [C.POINTER(JpegDesc), C.c_int]),
     "aeonb_jpeg_entropy_batch": (C.c_int, [C.c_void_p, C.POINTER(EntropyDesc), C.c_int]),

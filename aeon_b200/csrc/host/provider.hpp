@@ -111,7 +111,7 @@ namespace aeonb
         };
         explicit batch_plan(int stages)
             : descs(stages), desc_job(stages), desc_dst(stages), pre_descs(stages), pre_job(stages), desc_rot(stages),
-              pre_rot(stages), desc_pre(stages), sdescs(stages), sdesc_off(stages)
+              pre_rot(stages), desc_pre(stages), desc_area(stages), sdescs(stages), sdesc_off(stages)
         {
         }
         std::vector<jpeg_job>                      jobs;
@@ -126,6 +126,10 @@ namespace aeonb
         std::unordered_map<int, int>               rotation_of_job; // a repeated video frame is rotated once
         std::vector<std::vector<int>>              desc_rot, pre_rot; // per descriptor: index into `rotations`, or -1
         std::vector<std::vector<int>>              desc_pre;          // per descriptor: index into pre_descs[s], or -1
+        // INTER_AREA: the crop -> output resize runs as a pass of its own; the main kernel then reads a picture of the
+        // output size 1:1.  Per descriptor: offset of that picture in the area arena, or -1.
+        std::vector<std::vector<int64_t>>          desc_area;
+        size_t                                     area_bytes = 0;
         std::vector<std::vector<aeonb_specgram_desc>> sdescs;
         std::vector<std::vector<size_t>>           sdesc_off;
         size_t stage_bytes = 0, pixel_bytes = 0, coef_bytes = 0, oriented_bytes = 0, rotated_bytes = 0;
@@ -160,6 +164,7 @@ struct aeonb_provider
     aeonb::device_buffer                 oriented_dev; // pictures after the EXIF orientation pass
     aeonb::device_buffer                 rotated_dev;  // pictures after the rotation pass
     aeonb::device_buffer                 resized_dev;  // pictures after the resize_short pass
+    aeonb::device_buffer                 area_dev;     // pictures after an INTER_AREA crop -> output resize pass
     // Device-side outputs of batches delivered to host memory, double buffered: the copy of batch t to the host
     // (on the copy stream) overlaps the kernels of batch t+1, which write the other set.
     std::vector<aeonb::device_buffer>    out_dev[2];   // per output, batch_size records

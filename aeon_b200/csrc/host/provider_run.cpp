@@ -42,7 +42,11 @@ namespace aeonb
                 d.interp = AEONB_INTERP_LINEAR;
             else if (m == "NEAREST")
                 d.interp = AEONB_INTERP_NEAREST;
-            else if (m == "CUBIC" || m == "AREA" || m == "LANCZOS4")
+            else if (m == "AREA")
+                d.interp = AEONB_INTERP_AREA; // AREA and CUBIC run as a pass of their own (aeonb_resize_batch), never in the image kernel
+            else if (m == "CUBIC")
+                d.interp = AEONB_INTERP_CUBIC;
+            else if (m == "LANCZOS4")
                 throw error(AEONB_ERR_UNSUPPORTED, "interpolation method " + m + " is outside the accelerated path");
             else
                 throw std::invalid_argument("Provided interpolation method (" + p.interpolation_method + " is unrecognized.");
@@ -87,6 +91,31 @@ namespace aeonb
             set_photometric(d, p.contrast, p.brightness, p.saturation, p.hue, p.lighting.empty() ? nullptr : p.lighting.data(),
                             p.color_noise_std);
             return d;
+        }
+
+        // The geometry of an image descriptor as an INTER_AREA / INTER_CUBIC resize pass writing to dst.
+        aeonb_resize_desc area_pass_of(const aeonb_image_desc& d, void* dst, int dst_pitch, int channels)
+        {
+            aeonb_resize_desc r{};
+            r.channels         = channels;
+            r.src              = d.src;
+            r.src_pitch        = d.src_pitch;
+            r.src_pixel_stride = d.src_pixel_stride;
+            r.src_w            = d.src_w;
+            r.src_h            = d.src_h;
+            r.canvas_x         = d.canvas_x;
+            r.canvas_y         = d.canvas_y;
+            r.crop_x           = d.crop_x;
+            r.crop_y           = d.crop_y;
+            r.crop_w           = d.crop_w;
+            r.crop_h           = d.crop_h;
+            r.interp           = d.interp;
+            r.out_w            = d.out_w;
+            r.out_h            = d.out_h;
+            r.dst              = static_cast<uint8_t*>(dst);
+            r.dst_pitch        = dst_pitch;
+            r.dst_pixel_stride = 3;
+            return r;
         }
 
         const int16_t* wav_samples(const void* data, size_t size, size_t& count)
@@ -394,6 +423,14 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
         }
         B.desc_rot[s].push_back(rot);
         B.desc_pre[s].push_back(pre);
+        int64_t area = -1;
+        if ((d.interp == AEONB_INTERP_AREA || d.interp == AEONB_INTERP_CUBIC) &&
+            (d.crop_w != d.out_w || d.crop_h != d.out_h)) // same size: aeon skips the resize
+        {
+            area         = (int64_t)align_up(B.area_bytes, 256);
+            B.area_bytes = (size_t)area + align_up((size_t)d.out_w * 3, 16) * d.out_h;
+        }
+        B.desc_area[s].push_back(area);
         return d;
     };
 
@@ -487,6 +524,7 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
                     {
                         B.desc_rot[s].push_back(-1); // zero padding frame
                         B.desc_pre[s].push_back(-1);
+                        B.desc_area[s].push_back(-1);
                     }
                     B.descs[s].push_back(d);
                     B.desc_job[s].push_back(j);
@@ -585,6 +623,8 @@ void aeonb_provider::reserve_arenas(batch_plan& B, void* const* outs, bool on_de
         oriented_dev.reserve(B.oriented_bytes + 256);
     if (B.rotated_bytes > 0)
         rotated_dev.reserve(B.rotated_bytes + 256);
+    if (B.area_bytes > 0)
+        area_dev.reserve(B.area_bytes + 256);
     B.status_room = align_up(sizeof(int32_t) * (B.jobs.size() + 1), 256);
     if (B.coef_bytes > 0)
         coef_dev.reserve(B.status_room + B.coef_bytes + 256);
@@ -898,8 +938,19 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n)
                     }
                     d.dst               = static_cast<char*>(resized_dev.p) + i * pre_slot;
                 }
-                check_status(aeonb_image_batch(ctx, B.pre_descs[s].data(), (int)B.pre_descs[s].size(), &P));
-                h2d_bytes += (int64_t)(sizeof(aeonb_image_desc) * B.pre_descs[s].size());
+                if (B.pre_descs[s][0].interp == AEONB_INTERP_AREA || B.pre_descs[s][0].interp == AEONB_INTERP_CUBIC) // one method per configuration
+                {
+                    vector<aeonb_resize_desc> rd;
+                    for (const aeonb_image_desc& d : B.pre_descs[s])
+                        rd.push_back(area_pass_of(d, d.dst, pre_pitch, ic.channels));
+                    check_status(aeonb_resize_batch(ctx, rd.data(), (int)rd.size()));
+                    h2d_bytes += (int64_t)(sizeof(aeonb_resize_desc) * rd.size());
+                }
+                else
+                {
+                    check_status(aeonb_image_batch(ctx, B.pre_descs[s].data(), (int)B.pre_descs[s].size(), &P));
+                    h2d_bytes += (int64_t)(sizeof(aeonb_image_desc) * B.pre_descs[s].size());
+                }
             }
             for (size_t i = 0; i < B.descs[s].size(); ++i)
             {
@@ -930,6 +981,34 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n)
                     d.canvas_x += pic.x;
                     d.canvas_y += pic.y;
                 }
+            }
+            // INTER_AREA: the crop -> output resize is a pass of its own; the image kernel then reads its result 1:1
+            vector<aeonb_resize_desc> area;
+            for (size_t i = 0; i < B.descs[s].size(); ++i)
+            {
+                aeonb_image_desc& d = B.descs[s][i];
+                if (d.interp != AEONB_INTERP_AREA && d.interp != AEONB_INTERP_CUBIC)
+                    continue;
+                if (B.desc_area[s][i] < 0)
+                {
+                    d.interp = AEONB_INTERP_LINEAR; // same size: a copy
+                    continue;
+                }
+                const int pitch = (int)align_up((size_t)d.out_w * 3, 16);
+                uint8_t*  pic   = static_cast<uint8_t*>(area_dev.p) + B.desc_area[s][i];
+                area.push_back(area_pass_of(d, pic, pitch, ic.channels));
+                d.interp = AEONB_INTERP_LINEAR; // identity from here on
+                d.src              = pic;
+                d.src_pitch        = pitch;
+                d.src_pixel_stride = 3;
+                d.src_w = d.canvas_w = d.crop_w = d.out_w;
+                d.src_h = d.canvas_h = d.crop_h = d.out_h;
+                d.canvas_x = d.canvas_y = d.crop_x = d.crop_y = 0;
+            }
+            if (!area.empty())
+            {
+                check_status(aeonb_resize_batch(ctx, area.data(), (int)area.size()));
+                h2d_bytes += (int64_t)(sizeof(aeonb_resize_desc) * area.size());
             }
             check_status(aeonb_image_batch(ctx, B.descs[s].data(), (int)B.descs[s].size(), &L));
             h2d_bytes += (int64_t)(sizeof(aeonb_image_desc) * B.descs[s].size());

@@ -433,3 +433,28 @@ def test_one_channel_output_from_grey_png_and_from_jpeg_luma(ctx):
     bad = dict(cfg, augmentation=[dict(AUG_C1, brightness=[0.5, 0.6])])
     with pytest.raises(Exception, match="3-channel"):
         make_provider(ctx, bad).run_host(photos)
+
+
+@pytest.mark.parametrize("method", ["AREA", "CUBIC"])
+def test_area_and_cubic_interpolation_through_the_provider(ctx, tmp_path, method):
+    """interpolation_method "AREA" / "CUBIC" (cv::resize): crops that shrink, grow and mix, resize_short, video frames."""
+    recs = [(r[0],) for r in image_records(60, 8)]
+    etl = [{"type": "image", "height": 96, "width": 96, "output_type": "uint8_t"}]
+    configs = [dict(AUG_C1, interpolation_method=method),                                        # mostly shrinking
+               dict(AUG_C1, interpolation_method=method, scale=[0.02, 0.08]),                    # small crops: enlarging
+               {"type": "image", "crop_enable": True, "scale": [0.5, 0.9], "flip_enable": True, "resize_short_size": 128,
+                "interpolation_method": method, "angle": [-10, 10]}]
+    for aug in configs:
+        cfg = {"batch_size": 8, "random_seed": 48, "etl": etl, "augmentation": [aug]}
+        got = make_provider(ctx, cfg).run_host(recs)["image"]
+        want = PipelineOracle(cfg).batch(recs)["image"]
+        assert np.array_equal(got, want)
+    rng = np.random.default_rng(61)
+    frame_aug = {"type": "image", "crop_enable": True, "scale": [0.6, 0.9], "flip_enable": True, "interpolation_method": method}
+    cfg = {"batch_size": 2, "random_seed": 13,
+           "etl": [{"type": "video", "max_frame_count": 6, "frame": {"height": 48, "width": 64, "channels": 3}}],
+           "augmentation": [{"type": "image", "frame": frame_aug}]}
+    clips = [(make_avi(rng, str(tmp_path), nf),) for nf in (6, 4)]
+    got = make_provider(ctx, cfg).run_host(clips)["video"]
+    want = PipelineOracle(cfg).batch(clips, lambda b: avi_frames(b, str(tmp_path)))["video"]
+    assert np.array_equal(got, want)

@@ -142,3 +142,37 @@ def test_rotation_matches_opencv_warp_affine():
         assert np.array_equal(ops.rotate(img, angle), ref), (h, w, angle)
     img = rng.integers(0, 256, (20, 30, 3), dtype=np.uint8)
     assert ops.rotate(img, 0) is img
+
+
+def test_area_resize_matches_opencv_in_all_three_regimes():
+    """cv::resize INTER_AREA: whole-factor boxes (2x2 and others), weighted cells, and the enlarging / mixed case."""
+    import cv2
+    rng = np.random.default_rng(78)
+    cases = [(37, 53, 20, 31), (100, 130, 64, 64), (64, 64, 32, 32), (90, 90, 30, 30), (50, 70, 49, 69), (64, 96, 16, 32),
+             (60, 60, 30, 20), (33, 47, 33, 20), (20, 31, 37, 53), (64, 64, 100, 130), (32, 32, 64, 64), (30, 40, 45, 41),
+             (40, 30, 20, 45), (45, 50, 90, 25), (17, 19, 17, 19), (8, 9, 1, 1), (5, 5, 7, 3), (300, 411, 224, 224),
+             (448, 448, 224, 224), (96, 96, 32, 32), (1, 1, 4, 4), (2, 3, 1, 1)]
+    cases += [tuple(int(v) for v in rng.integers(1, 120, 4)) for _ in range(60)]
+    for (sh, sw, dh, dw) in cases:
+        img = rng.integers(0, 256, (sh, sw, 3), dtype=np.uint8)
+        assert np.array_equal(ops.resize_area_u8(img, dw, dh), cv2.resize(img, (dw, dh), interpolation=cv2.INTER_AREA)), (sh, sw, dh, dw)
+
+
+def test_cubic_resize_matches_opencvs_own_implementation():
+    """cv::resize INTER_CUBIC as OpenCV's own code computes it (IPP, which this cv2 build would otherwise hand 8-bit cubic
+    resizes to, is switched off for the comparison): three- and one-channel pictures, shrinking, enlarging, tiny sizes."""
+    import cv2
+    rng = np.random.default_rng(81)
+    cases = [(300, 411, 224, 224), (1, 6, 18, 119), (45, 81, 15, 104), (41, 28, 65, 107), (39, 118, 70, 23), (37, 53, 20, 31),
+             (100, 130, 64, 64), (1, 1, 5, 5), (3, 2, 9, 1), (8, 9, 1, 1)]
+    cases += [tuple(int(v) for v in rng.integers(1, 130, 4)) for _ in range(80)]
+    old = cv2.ipp.useIPP()
+    cv2.ipp.setUseIPP(False)
+    try:
+        for (sh, sw, dh, dw) in cases:
+            for cn in (3, 1):
+                img = rng.integers(0, 256, (sh, sw, cn), dtype=np.uint8)
+                ref = cv2.resize(img, (dw, dh), interpolation=cv2.INTER_CUBIC).reshape(dh, dw, cn)
+                assert np.array_equal(ops.resize_cubic_u8(img, dw, dh), ref), (sh, sw, dh, dw, cn)
+    finally:
+        cv2.ipp.setUseIPP(old)
