@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(HERE, "libaeon_b200.so")
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_DECODE, ERR_IO, END = 0, -1, -2, -3, -4, -5, 1
 
 U8, I8, I16, U16, I32, F32, F64 = range(7)
-INTERP_NEAREST, INTERP_LINEAR, INTERP_CUBIC, INTERP_AREA = 0, 1, 2, 3
+INTERP_NEAREST, INTERP_LINEAR, INTERP_CUBIC, INTERP_AREA, INTERP_LANCZOS4 = 0, 1, 2, 3, 4
 
 
 class ImageDesc(C.Structure):

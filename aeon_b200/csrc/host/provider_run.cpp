@@ -47,7 +47,7 @@ namespace aeonb
             else if (m == "CUBIC")
                 d.interp = AEONB_INTERP_CUBIC;
             else if (m == "LANCZOS4")
-                throw error(AEONB_ERR_UNSUPPORTED, "interpolation method " + m + " is outside the accelerated path");
+                d.interp = AEONB_INTERP_LANCZOS4;
             else
                 throw std::invalid_argument("Provided interpolation method (" + p.interpolation_method + " is unrecognized.");
             d.src_w = src_w;
@@ -424,7 +424,7 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
         B.desc_rot[s].push_back(rot);
         B.desc_pre[s].push_back(pre);
         int64_t area = -1;
-        if ((d.interp == AEONB_INTERP_AREA || d.interp == AEONB_INTERP_CUBIC) &&
+        if (d.interp >= AEONB_INTERP_CUBIC &&
             (d.crop_w != d.out_w || d.crop_h != d.out_h)) // same size: aeon skips the resize
         {
             area         = (int64_t)align_up(B.area_bytes, 256);
@@ -938,7 +938,7 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n)
                     }
                     d.dst               = static_cast<char*>(resized_dev.p) + i * pre_slot;
                 }
-                if (B.pre_descs[s][0].interp == AEONB_INTERP_AREA || B.pre_descs[s][0].interp == AEONB_INTERP_CUBIC) // one method per configuration
+                if (B.pre_descs[s][0].interp >= AEONB_INTERP_CUBIC) // CUBIC, AREA, LANCZOS4; one method per configuration
                 {
                     vector<aeonb_resize_desc> rd;
                     for (const aeonb_image_desc& d : B.pre_descs[s])
@@ -987,7 +987,7 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n)
             for (size_t i = 0; i < B.descs[s].size(); ++i)
             {
                 aeonb_image_desc& d = B.descs[s][i];
-                if (d.interp != AEONB_INTERP_AREA && d.interp != AEONB_INTERP_CUBIC)
+                if (d.interp < AEONB_INTERP_CUBIC)
                     continue;
                 if (B.desc_area[s][i] < 0)
                 {

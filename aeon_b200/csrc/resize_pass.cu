@@ -9,6 +9,11 @@
 // taps beyond the window repeat its edge.  (An OpenCV built with Intel IPP routes 8-bit cubic resizes to IPP, whose
 // results differ by one level in a few percent of the pixels; the target here is OpenCV's own implementation.)
 //
+// INTER_LANCZOS4: eight taps per axis; cv::interpolateLanczos4 forms the weights from double-precision sines and
+// cosines, so they are computed on the host with the C library OpenCV itself calls and shipped as tables (start
+// index + eight 11-bit weights per destination column and row); both passes are integer, the vertical one rounded
+// as (sum + 2^21) >> 22.
+//
 // INTER_AREA has three regimes and the kernel reproduces each per destination pixel:
 //   * both axes shrink by whole factors: box sums; a 2x2 box rounds as (sum + 2) >> 2, any other box as
 //     round-half-even(sum * float(1 / area));
@@ -23,6 +28,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <algorithm>
 #include <cfloat>
 #include <cmath>
 #include <sstream>
@@ -41,7 +47,8 @@ namespace aeonb
             int32_t        src_pitch, src_stride, src_w, src_h, canvas_x, canvas_y;
             int32_t        crop_x, crop_y, crop_w, crop_h;
             int32_t        dst_pitch, dst_stride, out_w, out_h;
-            int32_t        mode; // 0: whole-factor boxes, 1: weighted cells, 2: bilinear with area taps, 3: bicubic
+            int32_t        mode; // 0: whole-factor boxes, 1: weighted cells, 2: bilinear with area taps, 3: bicubic, 4: Lanczos
+            const int32_t* lanczos; // mode 4: out_w x (start, 8 weights), then out_h x (start, 8 weights), 9 ints each
             int32_t        ix, iy;
             int32_t        channels; // of the cv::Mat the reference resizes (3, or 1 for a grey picture carried as B = G = R)
             double         scale_x, scale_y, inv_x, inv_y;
@@ -185,6 +192,26 @@ namespace aeonb
                     for (int c = 0; c < 3; ++c)
                         out[c] = __float2int_rn(acc[c]);
                 }
+                else if (J.mode == 4)
+                {
+                    const int32_t* tx = J.lanczos + 9 * dx;
+                    const int32_t* ty = J.lanczos + 9 * (J.out_w + dy);
+#pragma unroll
+                    for (int c = 0; c < 3; ++c)
+                    {
+                        long long v = 0;
+                        for (int ky = 0; ky < 8; ++ky)
+                        {
+                            const int sy = max(0, min(J.crop_h - 1, ty[0] - 3 + ky));
+                            int       h  = 0;
+#pragma unroll
+                            for (int kx = 0; kx < 8; ++kx)
+                                h += window_pixel(J, max(0, min(J.crop_w - 1, tx[0] - 3 + kx)), sy, c) * tx[1 + kx];
+                            v += (long long)h * ty[1 + ky];
+                        }
+                        out[c] = (int)((v + (1ll << 21)) >> 22);
+                    }
+                }
                 else if (J.mode == 3)
                 {
                     const cubic_tap tx = cubic_taps(dx, J.scale_x, J.crop_w), ty = cubic_taps(dy, J.scale_y, J.crop_h);
@@ -241,6 +268,52 @@ namespace aeonb
     }
 }
 
+namespace aeonb
+{
+    namespace
+    {
+        // cv::interpolateLanczos4 and the tap position of cv::resize for one axis: per destination index the start
+        // index and eight weights rounded to 11-bit fixed point.
+        void lanczos_axis(int src_len, int dst_len, std::vector<int32_t>& out)
+        {
+            static const double s45      = 0.70710678118654752440084436210485;
+            static const double cs[8][2] = {{1, 0}, {-s45, -s45}, {0, 1}, {s45, -s45}, {-1, 0}, {s45, s45}, {0, -1}, {-s45, s45}};
+            const double        scale    = 1.0 / ((double)dst_len / (double)src_len);
+            const double        pi       = 3.1415926535897932384626433832795;
+            for (int d = 0; d < dst_len; ++d)
+            {
+                float     x = (float)(((double)d + 0.5) * scale - 0.5);
+                const int s = (int)std::floor(x);
+                x -= (float)s;
+                float c[8];
+                if (x < FLT_EPSILON)
+                {
+                    for (int i = 0; i < 8; ++i)
+                        c[i] = 0.f;
+                    c[3] = 1.f;
+                }
+                else
+                {
+                    float        sum = 0.f;
+                    const double y0 = -(x + 3) * pi * 0.25, s0 = std::sin(y0), c0 = std::cos(y0);
+                    for (int i = 0; i < 8; ++i)
+                    {
+                        const double y = -(x + 3 - i) * pi * 0.25;
+                        c[i]           = (float)((cs[i][0] * s0 + cs[i][1] * c0) / (y * y));
+                        sum += c[i];
+                    }
+                    sum = 1.f / sum;
+                    for (int i = 0; i < 8; ++i)
+                        c[i] *= sum;
+                }
+                out.push_back(s);
+                for (int i = 0; i < 8; ++i)
+                    out.push_back((int32_t)std::max(-32768l, std::min(32767l, std::lrint(c[i] * 2048.f))));
+            }
+        }
+    }
+}
+
 using namespace aeonb;
 
 extern "C" int aeonb_resize_batch(aeonb_ctx* ctx, const aeonb_resize_desc* descs, int n)
@@ -251,6 +324,8 @@ extern "C" int aeonb_resize_batch(aeonb_ctx* ctx, const aeonb_resize_desc* descs
         if (n <= 0)
             return AEONB_OK;
         std::vector<area_job> jobs(n);
+        std::vector<int32_t>  tables;      // Lanczos taps of every record that wants them
+        std::vector<size_t>   table_first(n, 0);
         int64_t               most = 0;
         for (int i = 0; i < n; ++i)
         {
@@ -258,8 +333,8 @@ extern "C" int aeonb_resize_batch(aeonb_ctx* ctx, const aeonb_resize_desc* descs
             std::ostringstream       ss;
             if (!r.dst || r.crop_w <= 0 || r.crop_h <= 0 || r.out_w <= 0 || r.out_h <= 0 || (int64_t)r.out_w * r.out_h > (1ll << 30))
                 ss << "record " << i << ": NULL destination or empty size";
-            else if (r.interp != AEONB_INTERP_AREA && r.interp != AEONB_INTERP_CUBIC)
-                ss << "record " << i << ": this pass handles INTER_AREA and INTER_CUBIC";
+            else if (r.interp != AEONB_INTERP_AREA && r.interp != AEONB_INTERP_CUBIC && r.interp != AEONB_INTERP_LANCZOS4)
+                ss << "record " << i << ": this pass handles INTER_AREA, INTER_CUBIC and INTER_LANCZOS4";
             else if (r.src && ((r.src_pixel_stride != 3 && r.src_pixel_stride != 4) || r.src_pitch < r.src_w * r.src_pixel_stride))
                 ss << "record " << i << ": source pixel stride must be 3 or 4 and the pitch at least a row";
             else if ((r.dst_pixel_stride != 3 && r.dst_pixel_stride != 4) || r.dst_pitch < r.out_w * r.dst_pixel_stride)
@@ -292,7 +367,15 @@ extern "C" int aeonb_resize_batch(aeonb_ctx* ctx, const aeonb_resize_desc* descs
             j.scale_y = 1.0 / j.inv_y;
             j.ix      = (int)std::lrint(j.scale_x);
             j.iy      = (int)std::lrint(j.scale_y);
-            if (r.interp == AEONB_INTERP_CUBIC)
+            j.lanczos = nullptr;
+            if (r.interp == AEONB_INTERP_LANCZOS4)
+            {
+                j.mode         = 4;
+                table_first[i] = tables.size();
+                lanczos_axis(r.crop_w, r.out_w, tables);
+                lanczos_axis(r.crop_h, r.out_h, tables);
+            }
+            else if (r.interp == AEONB_INTERP_CUBIC)
                 j.mode = 3;
             else if (j.scale_x >= 1 && j.scale_y >= 1)
                 j.mode = std::fabs(j.scale_x - j.ix) < DBL_EPSILON && std::fabs(j.scale_y - j.iy) < DBL_EPSILON ? 0 : 1;
@@ -301,6 +384,13 @@ extern "C" int aeonb_resize_batch(aeonb_ctx* ctx, const aeonb_resize_desc* descs
             most = std::max<int64_t>(most, (int64_t)r.out_w * r.out_h);
         }
         AEONB_CUDA(cudaSetDevice(ctx->device));
+        if (!tables.empty())
+        {
+            const int32_t* tdev = static_cast<const int32_t*>(ctx->upload(tables.data(), sizeof(int32_t) * tables.size()));
+            for (int i = 0; i < n; ++i)
+                if (jobs[i].mode == 4)
+                    jobs[i].lanczos = tdev + table_first[i];
+        }
         auto*      jdev = static_cast<const area_job*>(ctx->upload(jobs.data(), sizeof(area_job) * n));
         const int  per  = (int)std::min<int64_t>((most + 255) / 256, 148 * 8);
         const dim3 grid((unsigned)std::max(per, 1), (unsigned)n);

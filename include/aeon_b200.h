@@ -74,8 +74,9 @@ enum aeonb_interp
 {
     AEONB_INTERP_NEAREST = 0,
     AEONB_INTERP_LINEAR = 1,
-    AEONB_INTERP_CUBIC = 2, /* CUBIC and AREA only through aeonb_resize_batch; aeonb_image_batch takes NEAREST and LINEAR */
-    AEONB_INTERP_AREA = 3
+    AEONB_INTERP_CUBIC = 2, /* CUBIC, AREA and LANCZOS4 only through aeonb_resize_batch; aeonb_image_batch takes NEAREST and LINEAR */
+    AEONB_INTERP_AREA = 3,
+    AEONB_INTERP_LANCZOS4 = 4
 };
 
 /* One image (or video frame) to transform.  All coordinates are pixels.
@@ -179,8 +180,8 @@ typedef struct aeonb_orient_desc
 
 int aeonb_orient_batch(aeonb_ctx* ctx, const aeonb_orient_desc* descs, int n);
 
-/* Resize pass for INTER_AREA and INTER_CUBIC: cv::resize(window, out, Size(out_w, out_h), 0, 0, interp) (image::resize
- * with interpolation_method "AREA" / "CUBIC", src/image.cpp:93-106), where the window is the crop box of a canvas on which the
+/* Resize pass for INTER_AREA, INTER_CUBIC and INTER_LANCZOS4: cv::resize(window, out, Size(out_w, out_h), 0, 0, interp) (image::resize
+ * with interpolation_method "AREA" / "CUBIC" / "LANCZOS4", src/image.cpp:93-106), where the window is the crop box of a canvas on which the
  * source sits (zeros elsewhere), exactly as in aeonb_image_desc.  The output is an interleaved picture that
  * aeonb_image_batch then takes as a source of the same size (no further resampling). */
 typedef struct aeonb_resize_desc
@@ -190,7 +191,7 @@ typedef struct aeonb_resize_desc
     int32_t src_w, src_h;
     int32_t canvas_x, canvas_y;
     int32_t crop_x, crop_y, crop_w, crop_h;
-    int32_t interp;          /* AEONB_INTERP_AREA or AEONB_INTERP_CUBIC */
+    int32_t interp;          /* AEONB_INTERP_AREA, AEONB_INTERP_CUBIC or AEONB_INTERP_LANCZOS4 */
     int32_t out_w, out_h;
     uint8_t* dst;            /* device */
     int32_t dst_pitch, dst_pixel_stride;

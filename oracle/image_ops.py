@@ -224,6 +224,48 @@ def resize_cubic_u8(src, out_w, out_h, vector_block=CUBIC_VECTOR_BLOCK):
     return _sat_u8(out).reshape(out_h, out_w, src.shape[2])
 
 
+def _lanczos4_taps(src_len, dst_len):
+    """Tap indices (edge repeated) and 11-bit weights of ``cv::resize`` INTER_LANCZOS4 (``interpolateLanczos4``: weights
+    from double-precision sines / cosines of the C library, normalised in float32)."""
+    import math
+    s45 = 0.70710678118654752440084436210485
+    cs = [(1, 0), (-s45, -s45), (0, 1), (s45, -s45), (-1, 0), (s45, s45), (0, -1), (-s45, s45)]
+    scale = 1.0 / (f64(dst_len) / f64(src_len))
+    idx = np.zeros((dst_len, 8), np.int64)
+    w = np.zeros((dst_len, 8), np.int64)
+    for d in range(dst_len):
+        x = f32((d + 0.5) * scale - 0.5)
+        s = int(np.floor(x))
+        x = f32(x - f32(s))
+        if x < np.finfo(np.float32).eps:
+            c = [f32(0)] * 8
+            c[3] = f32(1)
+        else:
+            y0 = -(float(x) + 3) * math.pi * 0.25
+            s0, c0 = math.sin(y0), math.cos(y0)
+            c, total = [], f32(0)
+            for i in range(8):
+                y = -(float(x) + 3 - i) * math.pi * 0.25
+                c.append(f32((cs[i][0] * s0 + cs[i][1] * c0) / (y * y)))
+                total = f32(total + c[-1])
+            total = f32(f32(1) / total)
+            c = [f32(ci * total) for ci in c]
+        w[d] = [int(np.clip(_rne(ci * f32(RESIZE_COEF_ONE)), -32768, 32767)) for ci in c]
+        idx[d] = np.clip(s - 3 + np.arange(8), 0, src_len - 1)
+    return idx, w
+
+
+def resize_lanczos4_u8(src, out_w, out_h):
+    """``cv::resize(..., INTER_LANCZOS4)`` for uint8: integer 8-tap passes, the vertical one rounded as (sum + 2^21) >> 22."""
+    h, w = src.shape[:2]
+    ix, wx = _lanczos4_taps(w, out_w)
+    iy, wy = _lanczos4_taps(h, out_h)
+    s = src.astype(np.int64)
+    hor = sum(s[:, ix[:, k], :] * wx[None, :, k, None] for k in range(8))
+    ver = sum(hor[iy[:, k]] * wy[:, k, None, None] for k in range(8))
+    return _sat_u8((ver + (1 << 21)) >> 22)
+
+
 def resize_nearest_u8(src, out_w, out_h):
     """``cv::resize(..., INTER_NEAREST)``: source index = min(floor(d * src/dst), src-1)."""
     h, w = src.shape[:2]
@@ -484,6 +526,8 @@ def _resize(img, size_wh, method):
         return resize_area_u8(img, size_wh[0], size_wh[1])
     if m == "CUBIC":
         return resize_cubic_u8(img, size_wh[0], size_wh[1])
+    if m == "LANCZOS4":
+        return resize_lanczos4_u8(img, size_wh[0], size_wh[1])
     raise NotImplementedError("interpolation method %s has no oracle" % method)
 
 

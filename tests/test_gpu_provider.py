@@ -435,9 +435,9 @@ def test_one_channel_output_from_grey_png_and_from_jpeg_luma(ctx):
         make_provider(ctx, bad).run_host(photos)
 
 
-@pytest.mark.parametrize("method", ["AREA", "CUBIC"])
-def test_area_and_cubic_interpolation_through_the_provider(ctx, tmp_path, method):
-    """interpolation_method "AREA" / "CUBIC" (cv::resize): crops that shrink, grow and mix, resize_short, video frames."""
+@pytest.mark.parametrize("method", ["AREA", "CUBIC", "LANCZOS4"])
+def test_area_cubic_and_lanczos_interpolation_through_the_provider(ctx, tmp_path, method):
+    """interpolation_method "AREA" / "CUBIC" / "LANCZOS4" (cv::resize): crops that shrink, grow and mix, resize_short, video frames."""
     recs = [(r[0],) for r in image_records(60, 8)]
     etl = [{"type": "image", "height": 96, "width": 96, "output_type": "uint8_t"}]
     configs = [dict(AUG_C1, interpolation_method=method),                                        # mostly shrinking

@@ -90,3 +90,15 @@ def test_cubic_matches_the_oracle(ctx):
     for (img, _, _, (dw, dh)), g in zip(grey, got):
         want = ops.resize_cubic_u8(img[..., :1], dw, dh)
         assert np.array_equal(g, np.repeat(want, 3, 2)), (img.shape, dw, dh)
+
+
+def test_lanczos4_matches_the_oracle(ctx):
+    from aeon_b200 import _lib as L
+    rng = np.random.default_rng(84)
+    shapes = [(37, 53, 20, 31), (100, 130, 64, 64), (20, 31, 37, 53), (64, 64, 100, 130), (30, 40, 45, 41), (17, 19, 17, 40), (9, 9, 30, 30),
+              (1, 1, 5, 5), (3, 2, 9, 1), (300, 411, 224, 224)]
+    shapes += [tuple(int(v) for v in rng.integers(1, 120, 4)) for _ in range(30)]
+    jobs = [(rng.integers(0, 256, (sh, sw, 3), dtype=np.uint8), (0, 0), (0, 0, sw, sh), (dw, dh)) for (sh, sw, dh, dw) in shapes]
+    got = resize_gpu(ctx, jobs, interp=L.INTERP_LANCZOS4)
+    for (img, _, _, (dw, dh)), g in zip(jobs, got):
+        assert np.array_equal(g, ops.resize_lanczos4_u8(img, dw, dh)), (img.shape, dw, dh)

@@ -176,3 +176,14 @@ def test_cubic_resize_matches_opencvs_own_implementation():
                 assert np.array_equal(ops.resize_cubic_u8(img, dw, dh), ref), (sh, sw, dh, dw, cn)
     finally:
         cv2.ipp.setUseIPP(old)
+
+
+def test_lanczos4_resize_matches_opencv():
+    import cv2
+    rng = np.random.default_rng(83)
+    cases = [(37, 53, 20, 31), (100, 130, 64, 64), (20, 31, 37, 53), (64, 64, 100, 130), (30, 40, 45, 41), (17, 19, 17, 40), (50, 50, 25, 25),
+             (9, 9, 30, 30), (1, 1, 5, 5), (3, 2, 9, 1), (300, 411, 224, 224)]
+    cases += [tuple(int(v) for v in rng.integers(1, 100, 4)) for _ in range(40)]
+    for (sh, sw, dh, dw) in cases:
+        img = rng.integers(0, 256, (sh, sw, 3), dtype=np.uint8)
+        assert np.array_equal(ops.resize_lanczos4_u8(img, dw, dh), cv2.resize(img, (dw, dh), interpolation=cv2.INTER_LANCZOS4)), (sh, sw, dh, dw)
