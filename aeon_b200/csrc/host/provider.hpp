@@ -176,7 +176,10 @@ struct aeonb_provider
     cudaEvent_t m_done[k_events]    = {nullptr, nullptr, nullptr, nullptr}; // batch t complete: m_done[t % k_events]
     cudaEvent_t m_kernels[k_events] = {nullptr, nullptr, nullptr, nullptr}; // the kernels of batch t have finished
     cudaStream_t m_copy             = nullptr; // device -> host copies of finished batches
-    cudaEvent_t m_uploaded          = nullptr; // every H2D copy of the last call has left host memory
+    cudaEvent_t m_trace[k_events][3] = {};     // AEONB_TRACE: start of uploads, end of kernels, end of delivery (timing events)
+    cudaEvent_t m_staged            = nullptr; // the staging buffer of the last call has been copied to the device
+    bool        m_staged_valid      = false;
+    cudaEvent_t m_uploaded          = nullptr; // the small pinned buffer (host-produced outputs) of the last call has been copied
     bool        m_uploaded_valid    = false;
     int64_t     m_ticket            = 0;       // number of batches submitted so far
     aeonb::pinned_buffer m_status[k_events];   // per in-flight batch: the device entropy decoder's status words

@@ -160,8 +160,14 @@ aeonb_provider::~aeonb_provider()
     for (cudaEvent_t e : m_kernels)
         if (e)
             cudaEventDestroy(e);
+    for (auto& slot : m_trace)
+        for (cudaEvent_t e : slot)
+            if (e)
+                cudaEventDestroy(e);
     if (m_uploaded)
         cudaEventDestroy(m_uploaded);
+    if (m_staged)
+        cudaEventDestroy(m_staged);
     if (m_copy)
     {
         cudaStreamSynchronize(m_copy);
@@ -177,6 +183,16 @@ void aeonb_provider::wait_ticket(int64_t t)
         return; // its event slot was recycled, which only happens after the batch completed
     AEONB_CUDA(cudaSetDevice(ctx->device));
     AEONB_CUDA(cudaEventSynchronize(m_done[t % k_events]));
+    if (m_trace[t % k_events][2] && std::getenv("AEONB_TRACE"))
+    {
+        float up_to_kernels = 0, kernels_to_done = 0, since_prev = 0;
+        cudaEventElapsedTime(&up_to_kernels, m_trace[t % k_events][0], m_trace[t % k_events][1]);
+        cudaEventElapsedTime(&kernels_to_done, m_trace[t % k_events][1], m_trace[t % k_events][2]);
+        if (t >= 2 && m_trace[(t - 1) % k_events][2])
+            cudaEventElapsedTime(&since_prev, m_trace[(t - 1) % k_events][2], m_trace[t % k_events][2]);
+        std::fprintf(stderr, "aeonb_provider_wait %lld: GPU upload+kernels %.3f ms, kernels->delivered %.3f ms, delivered after previous batch %.3f ms\n",
+                     (long long)t, up_to_kernels, kernels_to_done, since_prev);
+    }
     check_entropy_status((int)(t % k_events));
 }
 
@@ -210,6 +226,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     if (!m_uploaded)
     {
         AEONB_CUDA(cudaEventCreateWithFlags(&m_uploaded, cudaEventDisableTiming));
+        AEONB_CUDA(cudaEventCreateWithFlags(&m_staged, cudaEventDisableTiming));
         for (cudaEvent_t& e : m_done)
             AEONB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         for (cudaEvent_t& e : m_kernels)
@@ -221,12 +238,21 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     const int par = (int)((m_ticket + 1) & 1);
     if (!on_device && m_ticket >= 2)
         AEONB_CUDA(cudaStreamWaitEvent(st, m_done[(m_ticket - 1) % k_events], 0));
-    // The pinned staging buffers are reused: the previous call's uploads must have left host memory.
-    if (m_uploaded_valid)
-        AEONB_CUDA(cudaEventSynchronize(m_uploaded));
+    // The pinned staging buffer is reused: the previous call's copy of it to the device must have finished.  (That copy
+    // is queued ahead of the previous batch's kernels, so the host runs a batch ahead of the GPU.)
+    if (m_staged_valid)
+        AEONB_CUDA(cudaEventSynchronize(m_staged));
     const int64_t launches_before = ctx->launches;
     h2d_bytes = d2h_bytes = 0;
     mark(0);
+    const int trace_slot = (int)((m_ticket + 1) % k_events);
+    if (trace)
+    {
+        for (cudaEvent_t& e : m_trace[trace_slot])
+            if (!e)
+                AEONB_CUDA(cudaEventCreate(&e));
+        AEONB_CUDA(cudaEventRecord(m_trace[trace_slot][0], st));
+    }
 
     batch_plan B((int)stages.size());
     plan_records(B, elems, sizes, n); // 1. sequential planning pass (record order == RNG order)
@@ -727,6 +753,8 @@ void aeonb_provider::stage_inputs(batch_plan& B)
             std::rethrow_exception(failure);
         AEONB_CUDA(copy_error);
     }
+    AEONB_CUDA(cudaEventRecord(m_staged, st));
+    m_staged_valid = true;
 
 }
 
@@ -1041,6 +1069,8 @@ void aeonb_provider::deliver(batch_plan& B, void* const* outs, int n, bool on_de
     for (size_t o = 0; o < outputs.size(); ++o)
         if (outputs[o].host_produced && on_device)
             small_total += align_up(out_host[o].size(), 256);
+    if (small_total > 0 && m_uploaded_valid)
+        AEONB_CUDA(cudaEventSynchronize(m_uploaded)); // the small pinned buffer is reused too
     small_pinned.reserve(small_total + 256);
     size_t small_off = 0;
     for (size_t o = 0; o < outputs.size(); ++o)
@@ -1073,10 +1103,11 @@ void aeonb_provider::deliver(batch_plan& B, void* const* outs, int n, bool on_de
                 std::memcpy(outs[o], src, bytes);
         }
     }
-    // From here on nothing reads pinned host staging any more: the next call may start refilling it
-    // while the kernels and the output copies below are still running.
-    AEONB_CUDA(cudaEventRecord(m_uploaded, st));
-    m_uploaded_valid = true;
+    if (small_total > 0)
+    {
+        AEONB_CUDA(cudaEventRecord(m_uploaded, st));
+        m_uploaded_valid = true;
+    }
     ++m_ticket;
     // Recycling an event slot: the batch that used it (k_events submissions ago) is long complete once the
     // newer batches between were waited for; synchronise to make that certain.
@@ -1122,6 +1153,12 @@ void aeonb_provider::deliver(batch_plan& B, void* const* outs, int n, bool on_de
             AEONB_CUDA(cudaMemcpyAsync(outs[o], sources[o], bytes, cudaMemcpyDeviceToHost, cs));
             d2h_bytes += (int64_t)bytes;
         }
+    }
+    static const bool trace_gpu = std::getenv("AEONB_TRACE") != nullptr;
+    if (trace_gpu && m_trace[slot][1])
+    {
+        AEONB_CUDA(cudaEventRecord(m_trace[slot][1], st));
+        AEONB_CUDA(cudaEventRecord(m_trace[slot][2], cs));
     }
     AEONB_CUDA(cudaEventRecord(m_done[slot], cs));
     if (wait)

@@ -388,26 +388,27 @@ def main():
     cfg = {"batch_size": BATCH, "random_seed": 1234, "etl": ETL, "augmentation": [AUG], "decode_threads": threads,
            "scratch_pixel_stride": pix, "roi_decode": not args.full_decode, "entropy_decode": args.entropy}
     prov = Provider(ctx, cfg)
+    DEPTH = 3   # batches in flight: the host prepares batch i while the GPU decodes i-1 and i-2 is copied to the host
     host_out = [{"image": torch.empty((BATCH, 3, OUT, OUT), dtype=torch.float32).pin_memory().numpy(),
-                 "label": np.zeros((BATCH, 1), np.int32)} for _ in range(2)]
+                 "label": np.zeros((BATCH, 1), np.int32)} for _ in range(DEPTH)]
     chunks = [recs[b * BATCH:(b + 1) * BATCH] for b in range(n_batches)]
-    e2e_steps = max(3, min(args.steps, 16))
+    e2e_steps = max(DEPTH + 1, min(args.steps, 16))
     for i in range(3):
         prov.run_host(chunks[i % n_batches], host_out[0])
     barrier()
-    # two batches in flight: the host entropy decode of batch i overlaps the kernels and copies of batch i-1;
-    # every batch's result is read back to host memory (wait) inside the timed region
+    # every batch's result is read back to host memory (wait) inside the timed region, oldest first
     t0 = time.perf_counter()
-    prev = None
+    tickets = []
     checksum = 0.0
     for i in range(e2e_steps):
-        t = prov.submit_host(chunks[i % n_batches], host_out[i % 2])
-        if prev is not None:
-            prov.wait(prev)
-            checksum += float(host_out[(i - 1) % 2]["image"][0, 0, 0, 0])
-        prev = t
-    prov.wait(prev)
-    checksum += float(host_out[(e2e_steps - 1) % 2]["image"][0, 0, 0, 0])
+        tickets.append(prov.submit_host(chunks[i % n_batches], host_out[i % DEPTH]))
+        if i >= DEPTH - 1:
+            j = i - (DEPTH - 1)
+            prov.wait(tickets[j])
+            checksum += float(host_out[j % DEPTH]["image"][0, 0, 0, 0])
+    for j in range(max(e2e_steps - (DEPTH - 1), 0), e2e_steps):
+        prov.wait(tickets[j])
+        checksum += float(host_out[j % DEPTH]["image"][0, 0, 0, 0])
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     st = prov.stats()
@@ -453,7 +454,7 @@ def main():
             "cpu_baseline": cpu_base,
             "e2e": {"value": world * BATCH * e2e_steps / (e2e_ms * 1e-3), "unit": "records/s",
                     "h2d_bytes_per_step": st["h2d_bytes"], "d2h_bytes_per_step": st["d2h_bytes"],
-                    "steps": e2e_steps, "host_decode_threads_per_gpu": threads},
+                    "steps": e2e_steps, "host_decode_threads_per_gpu": threads, "batches_in_flight": DEPTH},
             "gpu_launches": (3 if on_dev else 2) * args.steps, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
