@@ -458,3 +458,24 @@ def test_area_cubic_and_lanczos_interpolation_through_the_provider(ctx, tmp_path
     got = make_provider(ctx, cfg).run_host(clips)["video"]
     want = PipelineOracle(cfg).batch(clips, lambda b: avi_frames(b, str(tmp_path)))["video"]
     assert np.array_equal(got, want)
+
+
+def test_crop_disabled_branch_fixed_aspect_ratio_scaling_factor_and_padding(ctx):
+    """make_params with crop_enable false (src/augment_image.cpp:132-152): the picture is scaled to fit (or by
+    fixed_scaling_factor) and written top-left into a zero slot (fixed_aspect_ratio, src/etl_image.cpp:264-315); with
+    'padding' a window of the picture's size is cut from the picture framed in black (src/image.cpp:77-91)."""
+    rng = np.random.default_rng(74)
+    recs = [(jpeg_bytes(gradient_image(rng, int(rng.integers(120, 260)), int(rng.integers(120, 260))), 90),) for _ in range(8)]
+    etl = [{"type": "image", "height": 128, "width": 160, "output_type": "uint8_t"}]
+    for aug in ({"type": "image", "crop_enable": False, "fixed_aspect_ratio": True, "flip_enable": True},
+                {"type": "image", "crop_enable": False, "fixed_aspect_ratio": True, "fixed_scaling_factor": 0.4}):
+        cfg = {"batch_size": 8, "random_seed": 49, "etl": etl, "augmentation": [aug]}
+        got = make_provider(ctx, cfg).run_host(recs)["image"]
+        want = PipelineOracle(cfg).batch(recs)["image"]
+        assert np.array_equal(got, want)
+        assert (got == 0).all(axis=1).any()                       # part of every slot is the zero fill
+    same = [(jpeg_bytes(gradient_image(rng, 96, 96), 90),) for _ in range(8)]
+    cfg = {"batch_size": 8, "random_seed": 50, "etl": [{"type": "image", "height": 96, "width": 96, "output_type": "uint8_t"}],
+           "augmentation": [{"type": "image", "crop_enable": False, "padding": 8, "flip_enable": True}]}
+    got = make_provider(ctx, cfg).run_host(same)["image"]
+    assert np.array_equal(got, PipelineOracle(cfg).batch(same)["image"])
