@@ -234,7 +234,9 @@ int64_t aeonb_jpeg_backend_bytes(const aeonb_jpeg_desc* descs, int n);
 
 typedef struct aeonb_entropy_desc
 {
-    const uint8_t* scan;     /* device: entropy-coded bytes of the scan (after the SOS header) */
+    const uint8_t* scan;     /* device: entropy-coded bytes of the scan (after the SOS header).  Read in aligned 16-byte
+                                vectors: the 16-byte groups holding its first and last byte must be readable memory,
+                                which holds for any placement inside a cudaMalloc'd buffer */
     uint32_t scan_size;
     int32_t  ncomp;
     const uint8_t* tables;   /* device: 4 Huffman tables of 272 bytes each in DHT form (16 code counts, then the
