@@ -409,19 +409,34 @@ namespace aeonb
         // a warp decode different segments, so a slow path taken by one of them is paid by all), and the canonical-code
         // limits are kept monotonic so that the length of a longer code is a sum of comparisons, not a loop.
         constexpr int PLOOK = 12;
+        // One lookup gives everything the symbol loop needs, packed so that each field is one bit-field extract away:
+        //   bits 0-4   total bits the symbol takes (code + value bits)        bits 5-9   code length
+        //   bits 10-13 number of value bits (AC size / DC category)           bits 14-20 advance of the zig-zag index:
+        //   bit  21    DC table: the symbol is not a category (> 15)                     run + 1, 16 for ZRL, 64 for end of block
+        // 0 = the code is longer than the window.
+        __device__ __forceinline__ uint32_t pack_symbol(int len, int sym, bool is_ac)
+        {
+            const int s = sym & 15, r = sym >> 4;
+            const int kinc = is_ac ? (s ? r + 1 : (r == 15 ? 16 : 64)) : 0;
+            return (uint32_t)(len + s) | (uint32_t)len << 5 | (uint32_t)s << 10 | (uint32_t)kinc << 14 | (uint32_t)(!is_ac && r != 0) << 21;
+        }
+        constexpr uint32_t k_invalid_symbol = 16u | 16u << 5 | 64u << 14 | 1u << 22; // an invalid code: 16 bits, ends the block
+
         struct par_table
         {
-            uint16_t lookup[1 << PLOOK]; // (length << 8) | symbol for codes up to PLOOK bits, else 0
-            int      limit[17];          // limit[len]: exclusive upper bound of the codes of length <= len, left-justified to 16 bits
+            uint32_t lookup[1 << PLOOK];
+            int      limit[17]; // limit[len]: exclusive upper bound of the codes of length <= len, left-justified to 16 bits
             int      valoff[17];
             uint8_t  vals[256];
+            int      is_ac;
         };
 
         // One thread fills the canonical-code limits of a table from the DHT form (16 counts); the values are copied by the caller.
-        __device__ void build_par_table_head(par_table& T, const uint8_t* __restrict__ dht, int* bad)
+        __device__ void build_par_table_head(par_table& T, const uint8_t* __restrict__ dht, bool is_ac, int* bad)
         {
             int code = 0, k = 0;
             T.limit[0] = 0;
+            T.is_ac    = is_ac;
             for (int len = 1; len <= 16; ++len)
             {
                 const int n   = dht[len - 1];
@@ -444,11 +459,20 @@ namespace aeonb
 #pragma unroll
                 for (int l = 1; l < PLOOK; ++l)
                     len += i16 >= T.limit[l];
-                uint16_t e = 0;
+                uint32_t e = 0;
                 if (i16 < T.limit[len])
-                    e = (uint16_t)((len << 8) | T.vals[((i >> (PLOOK - len)) + T.valoff[len]) & 255]);
+                    e = pack_symbol(len, T.vals[((i >> (PLOOK - len)) + T.valoff[len]) & 255], T.is_ac != 0);
                 T.lookup[i] = e;
             }
+        }
+        // A code longer than the window (or an invalid one, which still consumes bits so that a decoder in a wrong state moves on).
+        __device__ __noinline__ uint32_t long_symbol(const par_table& T, uint32_t h)
+        {
+            const int c16 = (int)(h >> 16);
+            if (c16 >= T.limit[16])
+                return k_invalid_symbol;
+            const int len = PLOOK + 1 + (c16 >= T.limit[13]) + (c16 >= T.limit[14]) + (c16 >= T.limit[15]);
+            return pack_symbol(len, T.vals[((c16 >> (16 - len)) + T.valoff[len]) & 255], T.is_ac != 0);
         }
 
         constexpr int PAR_THREADS = 1024; // most threads (= segments) a stream can have; the launch picks the actual number
@@ -568,61 +592,58 @@ namespace aeonb
             {
                 // One block (or what is left of one) per pass of this loop, so that the threads of a warp reach the
                 // block-end work below together instead of one or two of them in every pass of a flat symbol loop.
-                const par_table* dct = S.dct_of[b];
-                const par_table* act = S.act_of[b];
+                if (k == 0)
+                {
+                    // the DC symbol opens the block
+                    const par_table* dct = S.dct_of[b];
+                    br.refill();
+                    const uint32_t h = (uint32_t)(br.acc >> 32); // 32 valid bits; a symbol takes at most 31
+                    uint32_t       e = dct->lookup[h >> (32 - PLOOK)];
+                    if (!e)
+                        e = long_symbol(*dct, h);
+                    const int tot = e & 31;
+                    if (WRITE)
+                    {
+                        const int len = (e >> 5) & 31, sz = (e >> 10) & 15;
+                        const int raw = sz ? (int)((h << len) >> (32 - sz)) : 0;
+                        const int v   = raw - (raw < ((1 << sz) >> 1) ? (1 << sz) - 1 : 0);
+                        if (e >> 21)
+                            bad = 1; // invalid code, or not a category
+                        if (g < S.total_blocks) // always true for a well-formed stream
+                            dcdiff[g] = (int16_t)v;
+                    }
+                    br.skip(tot);
+                    rem -= tot;
+                    k = 1;
+                }
+                const uint32_t* act = S.act_of[b]->lookup;
                 while (rem > 0 && k < 64)
                 {
                     br.refill();
-                    const uint32_t   h  = (uint32_t)(br.acc >> 32); // 32 valid bits; a symbol takes at most 31
-                    const bool       dc = k == 0;
-                    const par_table* t  = dc ? dct : act;
-                    const uint32_t   e  = t->lookup[h >> (32 - PLOOK)];
-                    int              len = e >> 8, sym = e & 255;
+                    const uint32_t h = (uint32_t)(br.acc >> 32);
+                    uint32_t       e = act[h >> (32 - PLOOK)];
                     if (!e)
+                        e = long_symbol(*S.act_of[b], h);
+                    const int tot = e & 31;
+                    if (WRITE)
                     {
-                        // a code longer than the lookup window, or an invalid one (which still consumes bits)
-                        const int c16 = (int)(h >> 16);
-                        len           = PLOOK + 1 + (c16 >= t->limit[13]) + (c16 >= t->limit[14]) + (c16 >= t->limit[15]);
-                        if (c16 >= t->limit[16])
+                        const int sz = (e >> 10) & 15;
+                        if (sz)
                         {
-                            bad = 1;
-                            sym = 0;
+                            const int len = (e >> 5) & 31, kk = k + (int)((e >> 14) & 127) - 1; // position of this coefficient
+                            const int raw = (int)((h << len) >> (32 - sz));
+                            const int v   = raw - (raw < ((1 << sz) >> 1) ? (1 << sz) - 1 : 0);
+                            if (kk > 63)
+                                bad = 1; // the run leaves the block
+                            else if (out)
+                                out[S.zz[kk]] = (int16_t)v;
                         }
-                        else
-                            sym = t->vals[((c16 >> (16 - len)) + t->valoff[len]) & 255];
+                        if (e >> 22)
+                            bad = 1; // invalid code
                     }
-                    const int s = sym & 15, r = sym >> 4;
-                    // s value bits follow, sign-extended the JPEG way (s == 0: none)
-                    const int raw  = s ? (int)((h << len) >> (32 - s)) : 0;
-                    const int half = (1 << s) >> 1;
-                    const int v    = raw - (raw < half ? (1 << s) - 1 : 0);
-                    br.skip(len + s);
-                    rem -= len + s;
-                    if (dc)
-                    {
-                        if (r)
-                            bad = 1; // DC sizes are 0..15
-                        if (WRITE && g < S.total_blocks) // always true for a well-formed stream
-                            dcdiff[g] = (int16_t)v;
-                        k = 1;
-                    }
-                    else if (s)
-                    {
-                        k += r;
-                        if (k > 63)
-                        {
-                            bad = 1;
-                            k   = 64;
-                        }
-                        else
-                        {
-                            if (WRITE && out)
-                                out[S.zz[k]] = (int16_t)v;
-                            ++k;
-                        }
-                    }
-                    else
-                        k = r == 15 ? k + 16 : 64;
+                    br.skip(tot);
+                    rem -= tot;
+                    k += (e >> 14) & 127;
                 }
                 if (k < 64)
                     break; // the segment ended inside the block
@@ -750,7 +771,7 @@ namespace aeonb
             }
             // ---- tables: a quarter of the threads builds each
             if (tid < 4)
-                build_par_table_head(S.tab[tid], d.tables + tid * 272, &S.bad);
+                build_par_table_head(S.tab[tid], d.tables + tid * 272, tid >= 2, &S.bad);
             for (int i = tid; i < 4 * 256; i += T)
                 S.tab[i >> 8].vals[i & 255] = d.tables[(i >> 8) * 272 + 16 + (i & 255)];
             __syncthreads();
