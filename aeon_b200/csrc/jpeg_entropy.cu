@@ -429,7 +429,9 @@ namespace aeonb
             int      valoff[17];
             uint8_t  vals[256];
             int      is_ac;
+            int      window; // bits of the lookup window in use: PLOOK for AC tables, DLOOK for DC tables (few, short codes)
         };
+        constexpr int DLOOK = 9;
 
         // One thread fills the canonical-code limits of a table from the DHT form (16 counts); the values are copied by the caller.
         __device__ void build_par_table_head(par_table& T, const uint8_t* __restrict__ dht, bool is_ac, int* bad)
@@ -437,6 +439,7 @@ namespace aeonb
             int code = 0, k = 0;
             T.limit[0] = 0;
             T.is_ac    = is_ac;
+            T.window   = is_ac ? PLOOK : DLOOK;
             for (int len = 1; len <= 16; ++len)
             {
                 const int n   = dht[len - 1];
@@ -452,16 +455,17 @@ namespace aeonb
         // `nth` threads (index `t`) fill the lookup window once limits and values are in place.
         __device__ void build_par_table_body(par_table& T, int t, int nth)
         {
-            for (int i = t; i < (1 << PLOOK); i += nth)
+            const int bits = T.window;
+            for (int i = t; i < (1 << bits); i += nth)
             {
-                const int i16 = i << (16 - PLOOK);
+                const int i16 = i << (16 - bits);
                 int       len = 1;
 #pragma unroll
                 for (int l = 1; l < PLOOK; ++l)
-                    len += i16 >= T.limit[l];
+                    len += l < bits && i16 >= T.limit[l];
                 uint32_t e = 0;
                 if (i16 < T.limit[len])
-                    e = pack_symbol(len, T.vals[((i >> (PLOOK - len)) + T.valoff[len]) & 255], T.is_ac != 0);
+                    e = pack_symbol(len, T.vals[((i >> (bits - len)) + T.valoff[len]) & 255], T.is_ac != 0);
                 T.lookup[i] = e;
             }
         }
@@ -471,7 +475,10 @@ namespace aeonb
             const int c16 = (int)(h >> 16);
             if (c16 >= T.limit[16])
                 return k_invalid_symbol;
-            const int len = PLOOK + 1 + (c16 >= T.limit[13]) + (c16 >= T.limit[14]) + (c16 >= T.limit[15]);
+            int len = T.window + 1;
+#pragma unroll
+            for (int l = DLOOK + 1; l < 16; ++l)
+                len += l > T.window && c16 >= T.limit[l];
             return pack_symbol(len, T.vals[((c16 >> (16 - len)) + T.valoff[len]) & 255], T.is_ac != 0);
         }
 
@@ -598,7 +605,7 @@ namespace aeonb
                     const par_table* dct = S.dct_of[b];
                     br.refill();
                     const uint32_t h = (uint32_t)(br.acc >> 32); // 32 valid bits; a symbol takes at most 31
-                    uint32_t       e = dct->lookup[h >> (32 - PLOOK)];
+                    uint32_t       e = dct->lookup[h >> (32 - DLOOK)];
                     if (!e)
                         e = long_symbol(*dct, h);
                     const int tot = e & 31;
@@ -796,6 +803,15 @@ namespace aeonb
                 w[0] = x.x, w[1] = x.y, w[2] = x.z, w[3] = x.w;
                 uint32_t prev = i > 0 ? (uint32_t)__ldg(reinterpret_cast<const uint8_t*>(vec) + 16 * i - 1) : 0;
                 valid = stuffed = marker = 0;
+                // Nearly every vector lies inside the stream and has no 0xFF in front of any of its bytes: all 16 are kept.
+                const bool inside = 16 * i >= lead && 16 * i + 16 - lead <= limit && 16 * i != lead;
+                const bool no_ff  = prev != 0xFF && !__vcmpeq4(w[0], 0xFFFFFFFFu) && !__vcmpeq4(w[1], 0xFFFFFFFFu) &&
+                                   !__vcmpeq4(w[2], 0xFFFFFFFFu) && !(__vcmpeq4(w[3], 0xFFFFFFFFu) & 0x00FFFFFFu);
+                if (inside && no_ff)
+                {
+                    valid = 0xFFFF;
+                    return;
+                }
 #pragma unroll
                 for (int b = 0; b < 16; ++b)
                 {
