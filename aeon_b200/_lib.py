@@ -43,13 +43,13 @@ class ImageLayout(C.Structure):
 class RotateDesc(C.Structure):
     _fields_ = [
         ("src", C.c_void_p), ("src_pitch", C.c_int32), ("src_pixel_stride", C.c_int32), ("width", C.c_int32),
-        ("height", C.c_int32), ("angle", C.c_int32), ("dst", C.c_void_p), ("dst_pitch", C.c_int32),
+        ("height", C.c_int32), ("angle", C.c_int32), ("nearest", C.c_int32), ("dst", C.c_void_p), ("dst_pitch", C.c_int32),
         ("dst_pixel_stride", C.c_int32),
     ]
 
 
 class OrientDesc(C.Structure):
-    _fields_ = RotateDesc._fields_[:5] + [("orientation", C.c_int32)] + RotateDesc._fields_[6:]
+    _fields_ = RotateDesc._fields_[:5] + [("orientation", C.c_int32)] + RotateDesc._fields_[7:]
 
 
 class ResizeDesc(C.Structure):
@@ -129,6 +129,7 @@ PROTOTYPES = {
                                                 C.POINTER(C.c_void_p)]),
     "aeonb_png_info": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "aeonb_png_decode_bgr": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t]),
+    "aeonb_png_decode_grey": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t]),
     "aeonb_draw_params": (C.c_int, [C.c_char_p, C.c_uint32, C.c_int, C.c_int, C.POINTER(C.c_int32),
                                     C.POINTER(C.c_int32), C.c_int, C.c_int, C.POINTER(C.c_double)]),
     "aeonb_draw_ssd_params": (C.c_int, [C.c_char_p, C.c_uint32, C.c_int, C.c_int, C.POINTER(C.c_int32),

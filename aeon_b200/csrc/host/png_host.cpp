@@ -316,11 +316,114 @@ namespace aeonb
                         ((info.color_type == 2 || info.color_type == 4 || info.color_type == 6) && (bd == 8 || bd == 16));
         if (!ok)
             bad("bad colour type / bit depth");
-        if (d[28] != 0)
-            throw error(AEONB_ERR_UNSUPPORTED, "interlaced PNG is outside the accelerated path");
+        if (d[28] > 1)
+            bad("bad interlace method");
+        info.interlaced = d[28] == 1;
     }
 
-    void png_decode_bgr(const void* data, size_t size, const png_info& info, uint8_t* dst, size_t pitch)
+    namespace
+    {
+        // Undoes the row filters of one image (or one interlace pass) in place: `rows` rows of a filter byte + `row` bytes.
+        void unfilter(uint8_t* raw, size_t row, int rows, int bpp)
+        {
+            std::vector<uint8_t> zero(row, 0);
+            const uint8_t*       prev = zero.data();
+            for (int y = 0; y < rows; ++y)
+            {
+                uint8_t*  cur    = raw + static_cast<size_t>(y) * (row + 1) + 1;
+                const int filter = cur[-1];
+                switch (filter)
+                {
+                case 0: break;
+                case 1:
+                    for (size_t i = bpp; i < row; ++i)
+                        cur[i] = static_cast<uint8_t>(cur[i] + cur[i - bpp]);
+                    break;
+                case 2:
+                    for (size_t i = 0; i < row; ++i)
+                        cur[i] = static_cast<uint8_t>(cur[i] + prev[i]);
+                    break;
+                case 3:
+                    for (size_t i = 0; i < row; ++i)
+                        cur[i] = static_cast<uint8_t>(cur[i] + (((i >= (size_t)bpp ? cur[i - bpp] : 0) + prev[i]) >> 1));
+                    break;
+                case 4:
+                    for (size_t i = 0; i < row; ++i)
+                        cur[i] = static_cast<uint8_t>(cur[i] + paeth(i >= (size_t)bpp ? cur[i - bpp] : 0, prev[i], i >= (size_t)bpp ? prev[i - bpp] : 0));
+                    break;
+                default: bad("bad filter type");
+                }
+                prev = cur;
+            }
+        }
+
+        // libpng's colour -> grey weights as cv::imdecode sets them (png_set_rgb_to_gray(.., 0.299, 0.587)): 15-bit
+        // integers, the blue weight being what is left of 32768.  8-bit samples are truncated, 16-bit samples rounded.
+        constexpr int k_grey_r = 9797, k_grey_g = 19234, k_grey_b = 3737;
+
+        // Writes `count` pixels of one unfiltered row to out[3 * (x0 + i * xstep)].
+        void emit_row(const uint8_t* cur, int count, int x0, int xstep, const png_info& info, const chunks& c, int channels,
+                      bool grey, uint8_t* out)
+        {
+            const int step = info.bit_depth == 16 ? 2 : 1; // 16-bit samples: the high byte comes first and is the one kept
+            auto put = [&](int i, int b, int g, int r) {
+                uint8_t* o = out + 3 * static_cast<size_t>(x0 + i * xstep);
+                if (grey && !(b == g && g == r))
+                    b = g = r = (k_grey_r * r + k_grey_g * g + k_grey_b * b) >> 15;
+                o[0] = static_cast<uint8_t>(b);
+                o[1] = static_cast<uint8_t>(g);
+                o[2] = static_cast<uint8_t>(r);
+            };
+            auto put_index = [&](int i, int v) {
+                if (v >= c.palette_size)
+                    bad("palette index out of range");
+                put(i, c.palette[v][2], c.palette[v][1], c.palette[v][0]);
+            };
+            if (info.color_type == 2 || info.color_type == 6)
+            {
+                for (int i = 0; i < count; ++i)
+                {
+                    const uint8_t* s = cur + static_cast<size_t>(i) * channels * step;
+                    if (grey && step == 2)
+                    {
+                        // the conversion runs on the 16-bit samples; the high byte of its result is kept
+                        const int r = s[0] << 8 | s[1], g = s[2] << 8 | s[3], b = s[4] << 8 | s[5];
+                        const int v = (r == g && g == b) ? r : (int)(((int64_t)k_grey_r * r + (int64_t)k_grey_g * g + (int64_t)k_grey_b * b + 16384) >> 15);
+                        uint8_t*  o = out + 3 * static_cast<size_t>(x0 + i * xstep);
+                        o[0] = o[1] = o[2] = static_cast<uint8_t>(v >> 8);
+                    }
+                    else
+                        put(i, s[2 * step], s[step], s[0]);
+                }
+            }
+            else if (info.bit_depth >= 8) // grey, grey + alpha, or an 8-bit palette index
+            {
+                for (int i = 0; i < count; ++i)
+                {
+                    const uint8_t v = cur[static_cast<size_t>(i) * channels * step];
+                    if (info.color_type == 3)
+                        put_index(i, v);
+                    else
+                        put(i, v, v, v);
+                }
+            }
+            else // 1, 2 or 4 bits per sample, most significant first: grey scaled to 0..255, or a palette index
+            {
+                const int bd = info.bit_depth, mask = (1 << bd) - 1, scale = 255 / mask;
+                for (int i = 0; i < count; ++i)
+                {
+                    const int bit = i * bd;
+                    const int v   = (cur[bit >> 3] >> (8 - bd - (bit & 7))) & mask;
+                    if (info.color_type == 3)
+                        put_index(i, v);
+                    else
+                        put(i, v * scale, v * scale, v * scale);
+                }
+            }
+        }
+    }
+
+    void png_decode_bgr(const void* data, size_t size, const png_info& info, uint8_t* dst, size_t pitch, bool grey)
     {
         const uint8_t* d = static_cast<const uint8_t*>(data);
         chunks         c;
@@ -329,87 +432,41 @@ namespace aeonb
         const int        channels = channels_of[info.color_type];
         const int        bits_pp  = channels * info.bit_depth;            // bits per pixel
         const int        bpp      = std::max(1, bits_pp / 8);             // filter unit in bytes
-        const size_t     row      = (static_cast<size_t>(info.width) * bits_pp + 7) / 8;
-        std::vector<uint8_t> raw((row + 1) * info.height);
-        zlib_inflate(c.idat.data(), c.idat.size(), raw.data(), raw.size());
         if (info.color_type == 3 && c.palette_size == 0)
             bad("palette image without a palette");
-        std::vector<uint8_t> zero(row, 0);
-        const uint8_t*       prev = zero.data();
-        for (int y = 0; y < info.height; ++y)
+        // A plain file is one pass over every pixel; an interlaced (Adam7) file is seven reduced images one after the
+        // other in the same zlib stream, each filtered on its own; empty passes take no bytes.
+        struct pass
         {
-            uint8_t*  cur    = raw.data() + static_cast<size_t>(y) * (row + 1) + 1;
-            const int filter = cur[-1];
-            switch (filter)
-            {
-            case 0: break;
-            case 1:
-                for (size_t i = bpp; i < row; ++i)
-                    cur[i] = static_cast<uint8_t>(cur[i] + cur[i - bpp]);
-                break;
-            case 2:
-                for (size_t i = 0; i < row; ++i)
-                    cur[i] = static_cast<uint8_t>(cur[i] + prev[i]);
-                break;
-            case 3:
-                for (size_t i = 0; i < row; ++i)
-                    cur[i] = static_cast<uint8_t>(cur[i] + (((i >= (size_t)bpp ? cur[i - bpp] : 0) + prev[i]) >> 1));
-                break;
-            case 4:
-                for (size_t i = 0; i < row; ++i)
-                    cur[i] = static_cast<uint8_t>(cur[i] + paeth(i >= (size_t)bpp ? cur[i - bpp] : 0, prev[i], i >= (size_t)bpp ? prev[i - bpp] : 0));
-                break;
-            default: bad("bad filter type");
-            }
-            prev         = cur;
-            uint8_t* out = dst + static_cast<size_t>(y) * pitch;
-            const int step = info.bit_depth == 16 ? 2 : 1; // 16-bit samples: the high byte comes first and is the one kept
-            if (info.color_type == 2 || info.color_type == 6)
-            {
-                for (int x = 0; x < info.width; ++x)
-                {
-                    const uint8_t* s = cur + static_cast<size_t>(x) * channels * step;
-                    out[3 * x + 0]   = s[2 * step];
-                    out[3 * x + 1]   = s[step];
-                    out[3 * x + 2]   = s[0];
-                }
-            }
-            else if (info.bit_depth >= 8) // grey or grey + alpha
-            {
-                for (int x = 0; x < info.width; ++x)
-                {
-                    const uint8_t v = cur[static_cast<size_t>(x) * channels * step];
-                    if (info.color_type == 3)
-                    {
-                        if (v >= c.palette_size)
-                            bad("palette index out of range");
-                        out[3 * x + 0] = c.palette[v][2];
-                        out[3 * x + 1] = c.palette[v][1];
-                        out[3 * x + 2] = c.palette[v][0];
-                    }
-                    else
-                        out[3 * x + 0] = out[3 * x + 1] = out[3 * x + 2] = v;
-                }
-            }
-            else // 1, 2 or 4 bits per sample, most significant first: grey scaled to 0..255, or a palette index
-            {
-                const int bd = info.bit_depth, mask = (1 << bd) - 1, scale = 255 / mask;
-                for (int x = 0; x < info.width; ++x)
-                {
-                    const int bit = x * bd;
-                    const int v   = (cur[bit >> 3] >> (8 - bd - (bit & 7))) & mask;
-                    if (info.color_type == 3)
-                    {
-                        if (v >= c.palette_size)
-                            bad("palette index out of range");
-                        out[3 * x + 0] = c.palette[v][2];
-                        out[3 * x + 1] = c.palette[v][1];
-                        out[3 * x + 2] = c.palette[v][0];
-                    }
-                    else
-                        out[3 * x + 0] = out[3 * x + 1] = out[3 * x + 2] = static_cast<uint8_t>(v * scale);
-                }
-            }
+            int x0, y0, dx, dy;
+        };
+        static const pass adam7[7] = {{0, 0, 8, 8}, {4, 0, 8, 8}, {0, 4, 4, 8}, {2, 0, 4, 4}, {0, 2, 2, 4}, {1, 0, 2, 2}, {0, 1, 1, 2}};
+        static const pass whole[1] = {{0, 0, 1, 1}};
+        const pass*       passes   = info.interlaced ? adam7 : whole;
+        const int         npass    = info.interlaced ? 7 : 1;
+        size_t            total    = 0;
+        for (int p = 0; p < npass; ++p)
+        {
+            const int pw = (info.width - passes[p].x0 + passes[p].dx - 1) / passes[p].dx;
+            const int ph = (info.height - passes[p].y0 + passes[p].dy - 1) / passes[p].dy;
+            if (pw > 0 && ph > 0)
+                total += ((static_cast<size_t>(pw) * bits_pp + 7) / 8 + 1) * ph;
+        }
+        std::vector<uint8_t> raw(total);
+        zlib_inflate(c.idat.data(), c.idat.size(), raw.data(), raw.size());
+        uint8_t* at = raw.data();
+        for (int p = 0; p < npass; ++p)
+        {
+            const int pw = (info.width - passes[p].x0 + passes[p].dx - 1) / passes[p].dx;
+            const int ph = (info.height - passes[p].y0 + passes[p].dy - 1) / passes[p].dy;
+            if (pw <= 0 || ph <= 0)
+                continue;
+            const size_t row = (static_cast<size_t>(pw) * bits_pp + 7) / 8;
+            unfilter(at, row, ph, bpp);
+            for (int y = 0; y < ph; ++y)
+                emit_row(at + static_cast<size_t>(y) * (row + 1) + 1, pw, passes[p].x0, passes[p].dx, info, c, channels, grey,
+                         dst + static_cast<size_t>(passes[p].y0 + y * passes[p].dy) * pitch);
+            at += (row + 1) * ph;
         }
     }
 }
@@ -441,6 +498,25 @@ int aeonb_png_decode_bgr(const void* data, size_t size, uint8_t* dst, size_t pit
         if (pitch < (size_t)info.width * 3)
             throw std::invalid_argument("aeonb_png_decode_bgr: pitch smaller than a row");
         png_decode_bgr(data, size, info, dst, pitch);
+        return AEONB_OK;
+    });
+}
+
+int aeonb_png_decode_grey(const void* data, size_t size, uint8_t* dst, size_t pitch)
+{
+    return guarded([&]() {
+        if (!data || !dst)
+            throw std::invalid_argument("aeonb_png_decode_grey: NULL argument");
+        png_info info;
+        png_parse(data, size, info);
+        if (pitch < (size_t)info.width)
+            throw std::invalid_argument("aeonb_png_decode_grey: pitch smaller than a row");
+        const size_t         wide = (size_t)info.width * 3;
+        std::vector<uint8_t> bgr(wide * info.height);
+        png_decode_bgr(data, size, info, bgr.data(), wide, true);
+        for (int y = 0; y < info.height; ++y)
+            for (int x = 0; x < info.width; ++x)
+                dst[(size_t)y * pitch + x] = bgr[(size_t)y * wide + 3 * (size_t)x];
         return AEONB_OK;
     });
 }

@@ -216,6 +216,17 @@ aeonb_provider::aeonb_provider(aeonb_ctx* c, const json& cfg) : ctx(c)
             }
             add(prefixed(st.image.name, "image"), st.image.shape, false);
         }
+        else if (t == "pixelmask")
+        {
+            // provider::pixelmask (src/provider.cpp:353-394): an image config, the image loader without mean / stddev.
+            // The extractor always yields one channel (src/etl_pixel_mask.cpp:39-55), and the loader's channel copy
+            // only works when the configuration says so too.
+            st.kind  = stage_kind::mask;
+            st.image = image_config(e);
+            if (st.image.channels != 1)
+                throw std::invalid_argument("pixelmask: the decoded mask has one channel; set 'channels' to 1");
+            add(prefixed(st.image.name, "pixelmask"), st.image.shape, false);
+        }
         else if (t == "label")
         {
             st.kind  = stage_kind::label;

@@ -29,6 +29,7 @@ namespace aeonb
     enum class stage_kind
     {
         image,
+        mask, // pixelmask: a one-channel target picture that follows the image's geometry
         label,
         video,
         ssd,
@@ -84,6 +85,7 @@ namespace aeonb
         // A stage with "channels": 1 reads the picture as cv::imdecode(..., GRAYSCALE) delivers it: for a JPEG the luma
         // plane alone goes through the back end (B = G = R = Y), the chroma planes are decoded but not used.
         bool               grey = false;
+        bool               mask = false; // a pixelmask record: rotated without interpolation
         bool               oriented = false;
         size_t             opixel_off = 0;
         int                opitch = 0;
@@ -108,6 +110,7 @@ namespace aeonb
         {
             int    job, angle, pitch;
             size_t off;
+            bool   nearest = false; // a mask is rotated without interpolation
         };
         explicit batch_plan(int stages)
             : descs(stages), desc_job(stages), desc_dst(stages), pre_descs(stages), pre_job(stages), desc_rot(stages),

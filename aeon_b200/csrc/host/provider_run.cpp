@@ -406,6 +406,7 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
             {
                 batch_plan::rotation ro;
                 ro.job        = j;
+                ro.nearest    = B.jobs[j].mask;
                 ro.angle      = params.angle;
                 ro.pitch      = (int)align_up((size_t)in.width * 3, 16);
                 ro.off        = align_up(B.rotated_bytes, 256);
@@ -485,10 +486,7 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
                 const int  j  = plan_jpeg(data, size);
                 if (sg.image.channels == 1)
                 {
-                    // IMREAD_GRAYSCALE: a JPEG gives its luma plane; a colour PNG would go through libpng's own grey
-                    // conversion, which is not reproduced here
-                    if (B.jobs[j].png && (B.jobs[j].pinfo.color_type & 2))
-                        throw error(AEONB_ERR_UNSUPPORTED, "a colour PNG read as one channel is outside the accelerated path");
+                    // IMREAD_GRAYSCALE: a JPEG gives its luma plane, a colour PNG goes through libpng's colour -> grey conversion
                     B.jobs[j].grey = true;
                 }
                 if (!have_params)
@@ -500,6 +498,42 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
                     throw std::invalid_argument("brightness, saturation and hue need a 3-channel picture (cv::transform / cv::cvtColor "
                                                 "reject one channel)");
                 aeonb_image_desc d = plan_picture(s, j, params, sg.image.width, sg.image.height, !factory.fixed_aspect_ratio);
+                if (d.out_w > sg.image.width || d.out_h > sg.image.height)
+                    throw std::invalid_argument("transformed image does not fit the configured output size");
+                B.descs[s].push_back(d);
+                B.desc_job[s].push_back(j);
+                B.desc_dst[s].push_back((int64_t)r * outputs[sg.first_output].shape.byte_size());
+                break;
+            }
+            case stage_kind::mask:
+            {
+                // provider::pixelmask::provide (src/provider.cpp:365-394): the mask is read as one channel
+                // (IMREAD_ANYDEPTH, src/etl_pixel_mask.cpp:39), shares the record's parameters and takes only their
+                // geometry: rotation without interpolation, crop box, NEAREST resize, flip (src/etl_pixel_mask.cpp:62-92).
+                if (size == 0)
+                    empty("pixelmask");
+                const int j = plan_jpeg(data, size);
+                jpeg_job& job = B.jobs[j];
+                if (job.png && job.pinfo.bit_depth == 16)
+                    throw error(AEONB_ERR_UNSUPPORTED, "a 16-bit mask (kept at 16 bits by IMREAD_ANYDEPTH) is outside the accelerated path");
+                job.grey = true;
+                job.mask = true;
+                if (!have_params)
+                {
+                    params      = factory.make_params(engine, job.pw, job.ph, sg.image.width, sg.image.height);
+                    have_params = true;
+                }
+                image_params geometry;
+                geometry.angle                = params.angle;
+                geometry.cropbox              = params.cropbox;
+                geometry.output_size          = params.output_size;
+                geometry.flip                 = params.flip;
+                geometry.interpolation_method = "NEAREST";
+                // the crop box is taken from the rotated mask itself; cv::Mat refuses a window that leaves the picture
+                const recti& cb = params.cropbox;
+                if (cb.x < 0 || cb.y < 0 || cb.width <= 0 || cb.height <= 0 || cb.x + cb.width > job.pw || cb.y + cb.height > job.ph)
+                    throw std::runtime_error("pixelmask: the crop box lies outside the mask picture");
+                aeonb_image_desc d = plan_picture(s, j, geometry, sg.image.width, sg.image.height, !factory.fixed_aspect_ratio);
                 if (d.out_w > sg.image.width || d.out_h > sg.image.height)
                     throw std::invalid_argument("transformed image does not fit the configured output size");
                 B.descs[s].push_back(d);
@@ -704,7 +738,8 @@ void aeonb_provider::stage_inputs(batch_plan& B)
                     jpeg_job& job = B.jobs[i];
                     if (job.png)
                     {
-                        png_decode_bgr(job.data, job.size, job.pinfo, reinterpret_cast<uint8_t*>(hstage + job.stage_off), job.pitch);
+                        png_decode_bgr(job.data, job.size, job.pinfo, reinterpret_cast<uint8_t*>(hstage + job.stage_off), job.pitch,
+                                       job.grey);
                         remaining[group_of(i)].fetch_sub(1, std::memory_order_release);
                         return;
                     }
@@ -872,6 +907,7 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n)
             rd[i].width            = pic.w;
             rd[i].height           = pic.h;
             rd[i].angle            = ro.angle;
+            rd[i].nearest          = ro.nearest ? 1 : 0;
             rd[i].dst              = static_cast<uint8_t*>(rotated_dev.p) + ro.off;
             rd[i].dst_pitch        = ro.pitch;
             rd[i].dst_pixel_stride = 3;
@@ -882,7 +918,7 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n)
     for (int s = 0; s < nin; ++s)
     {
         const stage& sg = stages[s];
-        if (sg.kind == stage_kind::image || sg.kind == stage_kind::video)
+        if (sg.kind == stage_kind::image || sg.kind == stage_kind::video || sg.kind == stage_kind::mask)
         {
             const bool          video = sg.kind == stage_kind::video;
             const image_config& ic    = video ? sg.video.frame : sg.image;
@@ -918,7 +954,7 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n)
                     L.stride_x = ic.channels;
                 }
                 L.channels = ic.channels;
-                if (!factory.mean.empty())
+                if (!factory.mean.empty() && sg.kind == stage_kind::image) // the mask's loader gets no mean / stddev
                 {
                     L.standardize = 1;
                     for (int c = 0; c < ic.channels; ++c)

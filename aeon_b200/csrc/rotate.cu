@@ -4,7 +4,9 @@
 //
 // rotate_kernel: aeon's image::rotate (src/image.cpp:53-75), i.e.
 // cv::warpAffine(src, dst, getRotationMatrix2D(centre, angle, 1), src.size(), INTER_LINEAR, BORDER_CONSTANT, 0)
-// on 8-bit interleaved pictures, bit for bit.
+// on 8-bit interleaved pictures, bit for bit; and its INTER_NEAREST form (interpolate == false), which the
+// pixelmask and depthmap transformers use (src/etl_pixel_mask.cpp:71-73): the same fixed-point source coordinates
+// rounded to the nearest whole pixel.
 //
 // OpenCV maps every destination pixel back through the inverted matrix in 10-bit fixed point -- the products are
 // formed in float64 and rounded half to even per column (M0*x*1024, M3*x*1024) and per row ((M1*y+M2)*1024,
@@ -32,6 +34,7 @@ namespace aeonb
             const uint8_t* src;
             uint8_t*       dst;
             int32_t        src_pitch, src_stride, dst_pitch, dst_stride, width, height;
+            int32_t        nearest; // INTER_NEAREST instead of INTER_LINEAR
             double         m[6]; // inverse map: source = m * (x, y, 1)
         };
 
@@ -44,8 +47,21 @@ namespace aeonb
                 const int y = i / J.width, x = i - y * J.width;
                 const int adelta = __double2int_rn(__dmul_rn(__dmul_rn(J.m[0], (double)x), 1024.0));
                 const int bdelta = __double2int_rn(__dmul_rn(__dmul_rn(J.m[3], (double)x), 1024.0));
-                const int x0     = __double2int_rn(__dmul_rn(__dadd_rn(__dmul_rn(J.m[1], (double)y), J.m[2]), 1024.0)) + 16;
-                const int y0     = __double2int_rn(__dmul_rn(__dadd_rn(__dmul_rn(J.m[4], (double)y), J.m[5]), 1024.0)) + 16;
+                const int round  = J.nearest ? 512 : 16; // half of the last kept bit: 10 bits dropped, or 5
+                const int x0     = __double2int_rn(__dmul_rn(__dadd_rn(__dmul_rn(J.m[1], (double)y), J.m[2]), 1024.0)) + round;
+                const int y0     = __double2int_rn(__dmul_rn(__dadd_rn(__dmul_rn(J.m[4], (double)y), J.m[5]), 1024.0)) + round;
+                if (J.nearest)
+                {
+                    // the source pixel the fixed-point coordinate rounds to, zero outside the picture
+                    const int nx = max(-32768, min(32767, (x0 + adelta) >> 10)), ny = max(-32768, min(32767, (y0 + bdelta) >> 10));
+                    const bool     in = nx >= 0 && nx < J.width && ny >= 0 && ny < J.height;
+                    const uint8_t* sp = J.src + (size_t)(in ? ny : 0) * J.src_pitch + (size_t)(in ? nx : 0) * J.src_stride;
+                    uint8_t*       dp = J.dst + (size_t)y * J.dst_pitch + (size_t)x * J.dst_stride;
+                    dp[0] = in ? sp[0] : 0;
+                    dp[1] = in ? sp[1] : 0;
+                    dp[2] = in ? sp[2] : 0;
+                    continue;
+                }
                 const int X = (x0 + adelta) >> 5, Y = (y0 + bdelta) >> 5;
                 const int sx = max(-32768, min(32767, X >> 5)), sy = max(-32768, min(32767, Y >> 5)); // saturate_cast<short>
                 const int fx = X & 31, fy = Y & 31;
@@ -165,6 +181,7 @@ extern "C" int aeonb_rotate_batch(aeonb_ctx* ctx, const aeonb_rotate_desc* descs
             j.dst_stride  = r.dst_pixel_stride;
             j.width       = r.width;
             j.height      = r.height;
+            j.nearest     = r.nearest != 0;
             rotation_inverse_map(r.width, r.height, r.angle, j.m);
             most = std::max<int64_t>(most, (int64_t)r.width * r.height);
         }

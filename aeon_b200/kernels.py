@@ -111,12 +111,17 @@ def image_batch(ctx, sources, params, out, layout, record_stride=None):
     return descs
 
 
-def png_decode(data):
-    """Host PNG decode -> H x W x 3 uint8 numpy array (B,G,R), as cv2.imdecode(IMREAD_COLOR) returns it."""
+def png_decode(data, grey=False):
+    """Host PNG decode -> H x W x 3 uint8 numpy array (B,G,R), as cv2.imdecode(IMREAD_COLOR) returns it; with `grey`
+    the H x W picture of cv2.imdecode(IMREAD_GRAYSCALE)."""
     lib = L.load()
     w, h = C.c_int32(), C.c_int32()
     buf = (C.c_char * len(data)).from_buffer_copy(data)
     L.check(lib.aeonb_png_info(buf, len(data), C.byref(w), C.byref(h)))
+    if grey:
+        out = np.zeros((h.value, w.value), np.uint8)
+        L.check(lib.aeonb_png_decode_grey(buf, len(data), out.ctypes.data, w.value))
+        return out
     out = np.zeros((h.value, w.value, 3), np.uint8)
     L.check(lib.aeonb_png_decode_bgr(buf, len(data), out.ctypes.data, w.value * 3))
     return out

@@ -159,6 +159,8 @@ typedef struct aeonb_rotate_desc
     int32_t src_pitch, src_pixel_stride;
     int32_t width, height;
     int32_t angle;           /* degrees, counter-clockwise */
+    int32_t nearest;         /* 0: INTER_LINEAR (image::rotate's default); 1: INTER_NEAREST (interpolate == false, as the
+                                pixelmask / depthmap transformers call it, src/etl_pixel_mask.cpp:71-73) */
     uint8_t* dst;            /* device: rotated picture, same size */
     int32_t dst_pitch, dst_pixel_stride;
 } aeonb_rotate_desc;
@@ -332,9 +334,13 @@ int aeonb_jpeg_entropy_prepare(const void* data, size_t size, aeonb_jpeg_info* i
 
 /* PNG records (cv::imdecode reads them too, src/etl_image.cpp:90; aeon's own geometry tests feed PNG): decoded on the
  * host into the B,G,R picture IMREAD_COLOR delivers (palette expanded, grey replicated, 16-bit samples cut to the high
- * byte, alpha dropped).  dst: height rows of `pitch` >= 3*width bytes.  Interlaced files: AEONB_ERR_UNSUPPORTED. */
+ * byte, alpha dropped; plain and Adam7-interlaced files).  dst: height rows of `pitch` >= 3*width bytes.
+ * aeonb_png_decode_grey gives the one-channel picture of IMREAD_GRAYSCALE, which is also what the pixelmask extractor's
+ * IMREAD_ANYDEPTH read (src/etl_pixel_mask.cpp:39) returns for 8-bit files: colour files go through libpng's integer
+ * colour -> grey conversion; dst: height rows of `pitch` >= width bytes. */
 int aeonb_png_info(const void* data, size_t size, int32_t* width, int32_t* height);
 int aeonb_png_decode_bgr(const void* data, size_t size, uint8_t* dst, size_t pitch);
+int aeonb_png_decode_grey(const void* data, size_t size, uint8_t* dst, size_t pitch);
 
 /* Draws augmentation parameters exactly as aeon's param_factory::make_params does
  * (src/augment_image.cpp:107-230) for `n` records whose decoded sizes are in_w/in_h,

@@ -267,10 +267,12 @@ def resize_lanczos4_u8(src, out_w, out_h):
 
 
 def resize_nearest_u8(src, out_w, out_h):
-    """``cv::resize(..., INTER_NEAREST)``: source index = min(floor(d * src/dst), src-1)."""
+    """``cv::resize(..., INTER_NEAREST)``: source index = min(floor(d * (1 / (dst/src))), src-1), the factor formed in
+    float64 as the reciprocal of dst/src (forming src/dst directly differs in the last place for about one size
+    pair in twenty, which moves a tap where d * src/dst is a whole number)."""
     h, w = src.shape[:2]
-    ix = np.minimum(np.floor(np.arange(out_w) * (f64(w) / out_w)).astype(np.int64), w - 1)
-    iy = np.minimum(np.floor(np.arange(out_h) * (f64(h) / out_h)).astype(np.int64), h - 1)
+    ix = np.minimum(np.floor(np.arange(out_w) * (f64(1.0) / (f64(out_w) / f64(w)))).astype(np.int64), w - 1)
+    iy = np.minimum(np.floor(np.arange(out_h) * (f64(1.0) / (f64(out_h) / f64(h)))).astype(np.int64), h - 1)
     return src[iy][:, ix]
 
 
@@ -584,11 +586,47 @@ def warp_affine_linear_u8(src, forward):
     return np.clip((acc + (1 << 14)) >> 15, 0, 255).astype(np.uint8)
 
 
-def rotate(img, angle):
-    """aeon ``image::rotate`` (src/image.cpp:53-75) with its defaults (linear interpolation, zero border)."""
+def warp_affine_nearest_u8(src, forward):
+    """``cv::warpAffine(src, dst, M, src.size(), INTER_NEAREST, BORDER_CONSTANT, 0)``: the same 10-bit fixed-point source
+    coordinates as the linear form, rounded to the nearest whole pixel (half of 2^10 added before the shift); a pixel
+    whose source lies outside the picture is zero."""
+    h, w = src.shape[:2]
+    M = invert_affine(forward)
+    ab = 1024.0
+    xs = np.arange(w, dtype=np.float64)
+    ys = np.arange(h, dtype=np.float64)
+    adelta = np.rint(M[0] * xs * ab).astype(np.int64)
+    bdelta = np.rint(M[3] * xs * ab).astype(np.int64)
+    x0 = np.rint((M[1] * ys + M[2]) * ab).astype(np.int64) + 512
+    y0 = np.rint((M[4] * ys + M[5]) * ab).astype(np.int64) + 512
+    X = np.clip((x0[:, None] + adelta[None, :]) >> 10, -32768, 32767)
+    Y = np.clip((y0[:, None] + bdelta[None, :]) >> 10, -32768, 32767)
+    ok = (X >= 0) & (X < w) & (Y >= 0) & (Y < h)
+    out = src[np.clip(Y, 0, h - 1), np.clip(X, 0, w - 1)]
+    return (out * (ok if src.ndim == 2 else ok[..., None])).astype(np.uint8)
+
+
+def rotate(img, angle, interpolate=True):
+    """aeon ``image::rotate`` (src/image.cpp:53-75): linear interpolation by default, nearest with
+    ``interpolate == false``; zero border."""
     if angle == 0:
         return img
-    return warp_affine_linear_u8(img, rotation_matrix(img.shape[1], img.shape[0], angle))
+    warp = warp_affine_linear_u8 if interpolate else warp_affine_nearest_u8
+    return warp(img, rotation_matrix(img.shape[1], img.shape[0], angle))
+
+
+def transform_pixel_mask(mask, p):
+    """aeon ``pixel_mask::transformer::transform`` (src/etl_pixel_mask.cpp:62-92; ``depthmap::transformer`` is the
+    same, src/etl_depthmap.cpp:62-92): rotation without interpolation, the crop box taken from the rotated mask itself,
+    NEAREST resize to the output size, flip.  Nothing else of the parameters applies to a mask."""
+    mask = rotate(mask, p.angle, interpolate=False)
+    x, y, w, h = p.cropbox
+    if x < 0 or y < 0 or w <= 0 or h <= 0 or x + w > mask.shape[1] or y + h > mask.shape[0]:
+        raise ValueError("cropbox outside the mask")
+    mask = _resize(mask[y:y + h, x:x + w], p.output_size, "NEAREST")
+    if p.flip:
+        mask = mask[:, ::-1]
+    return np.ascontiguousarray(mask)
 
 
 def transform_single_image(img, p):

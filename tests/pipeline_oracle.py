@@ -55,6 +55,16 @@ class PipelineOracle:
                     if p is None:
                         p = self.factory.make_params(g, img.shape[1], img.shape[0], etl["width"], etl["height"])
                     outs.setdefault(name + "image", []).append(self.image(etl, img, p))
+                elif etl["type"] == "pixelmask":
+                    import cv2
+                    mask = cv2.imdecode(np.frombuffer(blob, np.uint8), cv2.IMREAD_ANYDEPTH)   # src/etl_pixel_mask.cpp:39
+                    assert mask is not None and mask.dtype == np.uint8
+                    if p is None:
+                        p = self.factory.make_params(g, mask.shape[1], mask.shape[0], etl["width"], etl["height"])
+                    out = ops.transform_pixel_mask(mask[..., None], p)
+                    assert out.shape[:2] == (etl["height"], etl["width"])
+                    outs.setdefault(name + "pixelmask", []).append(ops.load_image(
+                        out, etl.get("channel_major", True), False, etl.get("output_type", "uint8_t")))
                 elif etl["type"] == "label":
                     v = int(np.frombuffer(blob, np.int32)[0]) if etl.get("binary") else int(blob.decode())
                     outs.setdefault(name + "label", []).append(np.array([v], ops._DTYPES[etl.get("output_type", "uint32_t")]))

@@ -479,3 +479,65 @@ def test_crop_disabled_branch_fixed_aspect_ratio_scaling_factor_and_padding(ctx)
            "augmentation": [{"type": "image", "crop_enable": False, "padding": 8, "flip_enable": True}]}
     got = make_provider(ctx, cfg).run_host(same)["image"]
     assert np.array_equal(got, PipelineOracle(cfg).batch(same)["image"])
+
+
+def mask_png(rng, h, w, colour=False, interlaced=False):
+    """A class-index mask with large flat regions, PNG coded (what segmentation data sets ship)."""
+    import cv2
+    from tests.test_host_png import write_png
+    yy, xx = np.mgrid[0:h, 0:w]
+    m = ((yy // int(rng.integers(9, 40)) + xx // int(rng.integers(9, 40))) % 21).astype(np.uint8)
+    if colour:
+        m = np.dstack([m * 12, 255 - m * 7, m * 3]).astype(np.uint8)
+        return cv2.imencode(".png", m)[1].tobytes()
+    if interlaced:
+        return write_png(m[..., None], 0, 8, interlaced=True)
+    return cv2.imencode(".png", m)[1].tobytes()
+
+
+def test_image_and_pixelmask_share_the_geometry(ctx):
+    """provider type image,pixelmask (src/provider.cpp:353-394, doc/source/provider_pixelmask.rst): the mask follows the
+    image's rotation, crop box and flip, without interpolation and without the photometric steps; int32 and uint8
+    outputs; PNG masks (grey, colour read as one channel, interlaced) and a JPEG mask (its luma plane)."""
+    rng = np.random.default_rng(71)
+    recs = []
+    for i in range(8):
+        h, w = int(rng.integers(200, 320)), int(rng.integers(200, 320))
+        img = jpeg_bytes(gradient_image(rng, h, w), 90)
+        if i == 6:
+            mask = jpeg_bytes(gradient_image(rng, h, w), 95)
+        else:
+            mask = mask_png(rng, h, w, colour=(i == 5), interlaced=(i == 4))
+        recs.append((img, mask))
+    for out_type, aug in (("int32_t", dict(AUG_C2, angle=[-25, 25])), ("uint8_t", AUG_C1),
+                          ("float", {"type": "image", "crop_enable": True, "scale": [0.6, 0.9], "flip_enable": True, "angle": [5, 40]})):
+        aug = {k: v for k, v in aug.items() if k not in ("mean", "stddev")}
+        cfg = {"batch_size": 8, "random_seed": 77,
+               "etl": [{"type": "image", "height": 96, "width": 112, "output_type": "uint8_t"},
+                       {"type": "pixelmask", "height": 96, "width": 112, "channels": 1, "output_type": out_type}],
+               "augmentation": [aug]}
+        got = make_provider(ctx, cfg).run_host(recs)
+        want = PipelineOracle(cfg).batch(recs)
+        assert got["pixelmask"].shape == (8, 1, 96, 112) and got["pixelmask"].dtype == want["pixelmask"].dtype
+        assert np.array_equal(got["image"], want["image"])
+        assert np.array_equal(got["pixelmask"], want["pixelmask"])
+
+
+def test_pixelmask_alone_and_its_errors(ctx):
+    """A pixelmask stage on its own draws the parameters itself; the configuration needs one channel; an empty record and
+    a crop box that leaves the mask are errors (src/provider.cpp:372-377; cv::Mat refuses the window)."""
+    from aeon_b200._lib import AeonError
+    rng = np.random.default_rng(72)
+    recs = [(mask_png(rng, 120 + 7 * i, 150 + 3 * i),) for i in range(4)]
+    cfg = {"batch_size": 4, "random_seed": 5, "etl": [{"type": "pixelmask", "height": 64, "width": 64, "channels": 1}],
+           "augmentation": [{"type": "image", "crop_enable": True, "scale": [0.5, 0.8], "flip_enable": True}]}
+    got = make_provider(ctx, cfg).run_host(recs)["pixelmask"]
+    assert np.array_equal(got, PipelineOracle(cfg).batch(recs)["pixelmask"])
+    with pytest.raises(AeonError, match="channels"):
+        make_provider(ctx, dict(cfg, etl=[{"type": "pixelmask", "height": 64, "width": 64}]))
+    with pytest.raises(AeonError, match="received pixelmask with size 0"):
+        make_provider(ctx, cfg).run_host([(b"",)] * 4)
+    two = dict(cfg, etl=[{"type": "image", "height": 64, "width": 64}, cfg["etl"][0]])
+    small = [(jpeg_bytes(gradient_image(rng, 300, 300), 90), mask_png(rng, 40, 40)) for _ in range(4)]
+    with pytest.raises(AeonError, match="crop box"):
+        make_provider(ctx, two).run_host(small)

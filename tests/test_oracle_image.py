@@ -61,6 +61,17 @@ def test_resize_linear_matches_opencv_on_many_shapes():
     assert np.array_equal(ops.resize_nearest_u8(src, 37, 51), cv2.resize(src, (37, 51), interpolation=cv2.INTER_NEAREST))
 
 
+def test_resize_nearest_matches_opencv_for_every_source_width():
+    """INTER_NEAREST tap positions for every source length 1..599 against a handful of output lengths: the pairs where
+    d * src/dst is a whole number decide between the two ways of forming the scale factor."""
+    for src_len in range(1, 600):
+        row = (np.arange(src_len) % 251).astype(np.uint8).reshape(1, src_len, 1).repeat(3, axis=2)
+        col = np.ascontiguousarray(row.transpose(1, 0, 2))
+        for dst_len in (7, 56, 96, 112, 224, 300):
+            assert np.array_equal(ops.resize_nearest_u8(row, dst_len, 1), cv2.resize(row, (dst_len, 1), interpolation=cv2.INTER_NEAREST))
+            assert np.array_equal(ops.resize_nearest_u8(col, 1, dst_len), cv2.resize(col, (1, dst_len), interpolation=cv2.INTER_NEAREST))
+
+
 def test_colour_matrix_transform_matches_opencv():
     rng = np.random.default_rng(2)
     img = rng.integers(0, 256, (64, 257, 3), dtype=np.uint8)
@@ -142,6 +153,48 @@ def test_rotation_matches_opencv_warp_affine():
         assert np.array_equal(ops.rotate(img, angle), ref), (h, w, angle)
     img = rng.integers(0, 256, (20, 30, 3), dtype=np.uint8)
     assert ops.rotate(img, 0) is img
+
+
+def test_nearest_rotation_and_pixel_mask_transform_match_opencv():
+    """image::rotate with interpolate == false, and pixel_mask::transformer::transform (src/etl_pixel_mask.cpp:62-92) as
+    the same OpenCV calls; the reference's own mask tests (test/test_pixel_mask.cpp:76-209) ask that a black / white
+    checkerboard stays black / white through scale up, scale down and rotation, and that values survive the loader."""
+    import cv2
+    rng = np.random.default_rng(79)
+    for _ in range(60):
+        h, w = int(rng.integers(1, 300)), int(rng.integers(1, 300))
+        angle = int(rng.integers(-180, 181)) or 9
+        img = rng.integers(0, 256, (h, w, 1) if rng.integers(2) else (h, w, 3), dtype=np.uint8)
+        ref = cv2.warpAffine(img, cv2.getRotationMatrix2D((w // 2, h // 2), angle, 1.0), (w, h), flags=cv2.INTER_NEAREST,
+                             borderMode=cv2.BORDER_CONSTANT, borderValue=(0, 0, 0, 0))
+        assert np.array_equal(ops.rotate(img, angle, interpolate=False), ref.reshape(img.shape)), (h, w, angle)
+    board = (((np.add.outer(np.arange(256), np.arange(256)) % 2) * 255).astype(np.uint8))[..., None]
+    for out_size, angle in (((300, 300), 0), ((100, 100), 0), ((256, 256), 45)):
+        p = ops.ImageParams()
+        p.cropbox, p.output_size, p.angle = (0, 0, 256, 256), out_size, angle
+        tx = ops.transform_pixel_mask(board, p)
+        assert tx.shape == (out_size[1], out_size[0], 1) and set(np.unique(tx)) <= {0, 255}
+    for _ in range(20):
+        h, w = int(rng.integers(40, 200)), int(rng.integers(40, 200))
+        mask = rng.integers(0, 21, (h, w, 1), dtype=np.uint8)
+        p = ops.ImageParams()
+        cw, ch = int(rng.integers(8, w + 1)), int(rng.integers(8, h + 1))
+        p.cropbox = (int(rng.integers(0, w - cw + 1)), int(rng.integers(0, h - ch + 1)), cw, ch)
+        p.output_size, p.angle, p.flip = (int(rng.integers(8, 120)), int(rng.integers(8, 120))), int(rng.integers(-30, 31)), bool(rng.integers(2))
+        ref = mask[..., 0]
+        if p.angle:
+            ref = cv2.warpAffine(ref, cv2.getRotationMatrix2D((w // 2, h // 2), p.angle, 1.0), (w, h), flags=cv2.INTER_NEAREST,
+                                 borderMode=cv2.BORDER_CONSTANT, borderValue=(0, 0, 0, 0))
+        x, y = p.cropbox[:2]
+        ref = cv2.resize(ref[y:y + ch, x:x + cw], p.output_size, interpolation=cv2.INTER_NEAREST)
+        if p.flip:
+            ref = cv2.flip(ref, 1)
+        assert np.array_equal(ops.transform_pixel_mask(mask, p)[..., 0], ref)
+    cols = np.broadcast_to(np.arange(256, dtype=np.uint8), (256, 256))[..., None]
+    p = ops.ImageParams()
+    p.cropbox, p.output_size = (0, 0, 256, 256), (256, 256)
+    loaded = ops.load_image(ops.transform_pixel_mask(cols, p), True, False, "int32_t")
+    assert loaded.dtype == np.int32 and np.array_equal(loaded[0], np.broadcast_to(np.arange(256), (256, 256)))
 
 
 def test_area_resize_matches_opencv_in_all_three_regimes():
