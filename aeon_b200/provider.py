@@ -48,17 +48,21 @@ class Provider:
     def _pack(self, records):
         n = len(records)
         k = self.input_count
-        ptrs = (C.c_void_p * (n * k))()
-        sizes = (C.c_size_t * (n * k))()
-        keep = []
         for r, rec in enumerate(records):
             if len(rec) != k:
                 raise ValueError("record %d has %d elements, the configuration needs %d" % (r, len(rec), k))
-            for e, blob in enumerate(rec):
-                buf = np.frombuffer(blob, np.uint8)
-                keep.append(buf)
-                ptrs[r * k + e] = buf.ctypes.data if len(buf) else None
-                sizes[r * k + e] = len(buf)
+        flat = [blob for rec in records for blob in rec]
+        sizes = (C.c_size_t * (n * k))(*map(len, flat))
+        if all(type(b) is bytes for b in flat):
+            # one pass inside ctypes: each element points at the bytes object's own buffer, which the array keeps alive
+            ptrs = (C.c_char_p * (n * k))(*flat)
+            return C.cast(ptrs, C.POINTER(C.c_void_p)), sizes, (ptrs, flat)
+        ptrs = (C.c_void_p * (n * k))()
+        keep = []
+        for i, blob in enumerate(flat):
+            buf = np.frombuffer(blob, np.uint8)
+            keep.append(buf)
+            ptrs[i] = buf.ctypes.data if len(buf) else None
         return ptrs, sizes, keep
 
     def _shape(self, dims):
