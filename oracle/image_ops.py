@@ -502,6 +502,8 @@ class ImageParams:
         self.brightness = 1.0
         self.saturation = 1.0
         self.hue = 0
+        self.emit_type = ""                   # emit_constraint_type: only make_ssd_params sets it
+        self.emit_min_overlap = 0.0
         for k, v in kw.items():
             if not hasattr(self, k):
                 raise AttributeError(k)
