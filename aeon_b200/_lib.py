@@ -61,6 +61,20 @@ class ResizeDesc(C.Structure):
     ]
 
 
+class RcnnConfig(C.Structure):
+    _fields_ = [
+        ("width", C.c_int32), ("height", C.c_int32), ("base_size", C.c_int32), ("n_ratios", C.c_int32), ("n_scales", C.c_int32),
+        ("scaling_factor", C.c_float), ("ratios", C.c_float * 8), ("scales", C.c_float * 8),
+    ]
+
+
+class RcnnDesc(C.Structure):
+    _fields_ = [
+        ("gt_boxes", C.c_void_p), ("n_gt", C.c_int32), ("im_width", C.c_int32), ("im_height", C.c_int32),
+        ("labels", C.c_void_p), ("best_box", C.c_void_p),
+    ]
+
+
 class JpegDesc(C.Structure):
     _fields_ = [
         ("coef", C.c_void_p * 3), ("quant", C.c_void_p * 3),
@@ -130,6 +144,9 @@ PROTOTYPES = {
     "aeonb_png_info": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "aeonb_png_decode_bgr": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t]),
     "aeonb_png_decode_grey": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t]),
+    "aeonb_rcnn_anchor_count": (C.c_int64, [C.POINTER(RcnnConfig)]),
+    "aeonb_rcnn_anchors": (C.c_int, [C.POINTER(RcnnConfig), C.c_void_p]),
+    "aeonb_rcnn_label_batch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(RcnnDesc), C.c_int, C.c_float, C.c_float]),
     "aeonb_draw_params": (C.c_int, [C.c_char_p, C.c_uint32, C.c_int, C.c_int, C.POINTER(C.c_int32),
                                     C.POINTER(C.c_int32), C.c_int, C.c_int, C.POINTER(C.c_double)]),
     "aeonb_draw_ssd_params": (C.c_int, [C.c_char_p, C.c_uint32, C.c_int, C.c_int, C.POINTER(C.c_int32),

@@ -1,4 +1,5 @@
 #include "config.hpp"
+#include "rcnn_host.hpp"
 
 #include <algorithm>
 #include <sstream>
@@ -219,6 +220,95 @@ namespace aeonb
             throw invalid_argument("invalid max_gt_boxes");
         if (class_names.empty())
             throw invalid_argument("class_names cannot be empty");
+    }
+
+    rcnn_config::rcnn_config(json js)
+    {
+        if (js.is_null())
+            throw runtime_error("missing localization_rcnn config in json config");
+        js.erase("type");
+        required(js, "height");
+        required(js, "width");
+        required(js, "class_names");
+        height         = get_int(js, "height", 0);
+        width          = get_int(js, "width", 0);
+        name           = get_string(js, "name", "");
+        rois_per_image = get_int(js, "rois_per_image", 256);
+        base_size      = get_int(js, "base_size", 16);
+        max_gt_boxes   = get_int(js, "max_gt_boxes", 64);
+        deterministic_sampling = get_bool(js, "debug_deterministic", false);
+        auto real = [&](const char* key, float dflt) {
+            const json* v = js.find(key);
+            return v ? (float)v->as_double() : dflt;
+        };
+        auto reals = [&](const char* key, vector<float>& out) {
+            if (const json* v = js.find(key))
+            {
+                out.clear();
+                for (const json& e : v->elements())
+                    out.push_back((float)e.as_double());
+            }
+        };
+        scaling_factor      = real("scaling_factor", scaling_factor);
+        negative_overlap    = real("negative_overlap", negative_overlap);
+        positive_overlap    = real("positive_overlap", positive_overlap);
+        foreground_fraction = real("foreground_fraction", foreground_fraction);
+        reals("ratios", ratios);
+        reals("scales", scales);
+        for (const json& c : js.find("class_names")->elements())
+            class_names.push_back(c.as_string());
+        verify_config("localization_rcnn",
+                      {"height", "width", "class_names", "name", "rois_per_image", "base_size", "scaling_factor", "ratios", "scales",
+                       "negative_overlap", "positive_overlap", "foreground_fraction", "max_gt_boxes", "debug_deterministic"},
+                      js);
+        for (const char* key : {"negative_overlap", "positive_overlap", "foreground_fraction"})
+        {
+            const float v = real(key, 0.5f);
+            if (!(v >= 0.0f && v <= 1.0f))
+                throw invalid_argument(string("value for '") + key + "' out of range");
+        }
+        if (width <= 0 || height <= 0 || base_size <= 0 || rois_per_image <= 0 || max_gt_boxes <= 0 || !(scaling_factor > 0))
+            throw invalid_argument("localization_rcnn: sizes, base_size, rois_per_image, max_gt_boxes and scaling_factor must be positive");
+        if (ratios.empty() || scales.empty() || ratios.size() > 8 || scales.size() > 8)
+            throw invalid_argument("localization_rcnn: between 1 and 8 ratios and scales");
+        const int64_t A = total_anchors();
+        auto set = [&](int i, vector<int64_t> dims, const char* t) {
+            shapes[i].shape = dims;
+            shapes[i].otype = output_type::from_name(t);
+        };
+        // the ten buffers of localization::rcnn::config::config (src/etl_localization_rcnn.cpp:44-70)
+        set(0, {A * 4}, "float");
+        set(1, {A * 4}, "float");
+        set(2, {1, A * 2}, "int32_t");
+        set(3, {A * 2, 1}, "int32_t");
+        set(4, {2, 1}, "int32_t");
+        set(5, {max_gt_boxes, 4}, "float");
+        set(6, {1, 1}, "int32_t");
+        set(7, {max_gt_boxes, 1}, "int32_t");
+        set(8, {1, 1}, "float");
+        set(9, {max_gt_boxes, 1}, "int32_t");
+    }
+
+    int rcnn_config::total_anchors() const
+    {
+        return (int)(ratios.size() * scales.size()) * (int)std::floor((float)height * scaling_factor) *
+               (int)std::floor((float)width * scaling_factor);
+    }
+
+    aeonb_rcnn_config rcnn_config::abi() const
+    {
+        aeonb_rcnn_config c{};
+        c.width          = width;
+        c.height         = height;
+        c.base_size      = base_size;
+        c.n_ratios       = (int)ratios.size();
+        c.n_scales       = (int)scales.size();
+        c.scaling_factor = scaling_factor;
+        for (size_t i = 0; i < ratios.size(); ++i)
+            c.ratios[i] = ratios[i];
+        for (size_t i = 0; i < scales.size(); ++i)
+            c.scales[i] = scales[i];
+        return c;
     }
 
     audio_config::audio_config(json js)

@@ -127,6 +127,51 @@ def png_decode(data, grey=False):
     return out
 
 
+def rcnn_config(width, height, base_size=16, scaling_factor=1.0 / 16.0, ratios=(0.5, 1, 2), scales=(8, 16, 32)):
+    c = L.RcnnConfig()
+    c.width, c.height, c.base_size, c.scaling_factor = width, height, base_size, scaling_factor
+    c.n_ratios, c.n_scales = len(ratios), len(scales)
+    for i, v in enumerate(ratios):
+        c.ratios[i] = v
+    for i, v in enumerate(scales):
+        c.scales[i] = v
+    return c
+
+
+def rcnn_anchors(cfg):
+    """Host anchor table of localization_rcnn -> (count, 4) float32 array."""
+    lib = L.load()
+    n = int(lib.aeonb_rcnn_anchor_count(C.byref(cfg)))
+    out = np.zeros((n, 4), np.float32)
+    L.check(lib.aeonb_rcnn_anchors(C.byref(cfg), out.ctypes.data))
+    return out
+
+
+def rcnn_label_batch(ctx, anchors, gt_boxes, im_sizes, negative_overlap=0.3, positive_overlap=0.7):
+    """Labels (-1 / 0 / 1) and best-box index per anchor for each record.  anchors: (A, 4) float32; gt_boxes: list of
+    (K_i, 4) float32 arrays; im_sizes: list of (width, height)."""
+    import torch
+    dev = torch.device("cuda", ctx.device)
+    n, A = len(gt_boxes), len(anchors)
+    with torch.cuda.stream(ctx.torch_stream):
+        a = torch.from_numpy(np.ascontiguousarray(anchors, np.float32)).to(dev)
+        labels = torch.full((n, A), 7, dtype=torch.int8, device=dev)
+        best = torch.full((n, A), -7, dtype=torch.int16, device=dev)
+        keep = []
+        descs = (L.RcnnDesc * n)()
+        for i, (g, (w, h)) in enumerate(zip(gt_boxes, im_sizes)):
+            g = np.ascontiguousarray(g, np.float32).reshape(-1, 4)
+            t = torch.from_numpy(g).to(dev) if len(g) else None
+            keep.append(t)
+            descs[i].gt_boxes, descs[i].n_gt = (t.data_ptr() if t is not None else None), len(g)
+            descs[i].im_width, descs[i].im_height = int(w), int(h)
+            descs[i].labels, descs[i].best_box = labels[i].data_ptr(), best[i].data_ptr()
+        ctx.torch_stream.synchronize()
+        L.check(ctx.lib.aeonb_rcnn_label_batch(ctx.handle, a.data_ptr(), A, descs, n, negative_overlap, positive_overlap))
+        ctx.synchronize()
+    return labels.cpu().numpy(), best.cpu().numpy()
+
+
 def jpeg_parse(data):
     info = L.JpegInfo()
     buf = (C.c_char * len(data)).from_buffer_copy(data)

@@ -342,6 +342,42 @@ int aeonb_png_info(const void* data, size_t size, int32_t* width, int32_t* heigh
 int aeonb_png_decode_bgr(const void* data, size_t size, uint8_t* dst, size_t pitch);
 int aeonb_png_decode_grey(const void* data, size_t size, uint8_t* dst, size_t pitch);
 
+/* localization_rcnn (src/etl_localization_rcnn.cpp): region-proposal training targets.
+ *
+ * aeonb_rcnn_anchors: anchor::generate (:434-472) -- every base anchor (ratios outermost, scales inner, :489-557) shifted
+ * over the floor(width * scaling_factor) x floor(height * scaling_factor) grid, anchor-major then y then x; `out` takes
+ * aeonb_rcnn_anchor_count() x 4 floats (xmin, ymin, xmax, ymax).  Host only.
+ *
+ * aeonb_rcnn_label_batch: the O(anchors x boxes) part of transformer::transform (:118-193) for a batch, one launch: for
+ * the anchors that lie inside the record's scaled picture, intersection over union with every ground-truth box
+ * (bbox_overlaps, :302-338, the same float32 operations), then the labels -- 0 below negative_overlap, 1 for every
+ * anchor that equals a box's best overlap (ties included) or reaches positive_overlap, -1 otherwise and for anchors
+ * outside the picture -- and the index of each anchor's best box (the first on ties, 0 when none overlaps).  A record
+ * without boxes gets -1 everywhere, as in the reference (:181-208).  Sampling (transformer::sample_anchors, :218-263) and
+ * the regression targets of the at most rois_per_image sampled anchors stay on the host. */
+typedef struct aeonb_rcnn_config
+{
+    int32_t width, height;     /* output picture size the anchors cover */
+    int32_t base_size;         /* 16 */
+    int32_t n_ratios, n_scales;
+    float   scaling_factor;    /* 1/16: the feature stride is its reciprocal */
+    float   ratios[8], scales[8];
+} aeonb_rcnn_config;
+
+typedef struct aeonb_rcnn_desc
+{
+    const float* gt_boxes;     /* device: n_gt x 4 floats, boxes already transformed to the output picture */
+    int32_t n_gt;              /* 0..1024 */
+    int32_t im_width, im_height; /* the scaled picture: anchors must lie inside [0, im_width) x [0, im_height) */
+    int8_t*  labels;           /* device: one per anchor: -1, 0, 1 */
+    int16_t* best_box;         /* device: one per anchor */
+} aeonb_rcnn_desc;
+
+int64_t aeonb_rcnn_anchor_count(const aeonb_rcnn_config* cfg);
+int     aeonb_rcnn_anchors(const aeonb_rcnn_config* cfg, float* out);
+int     aeonb_rcnn_label_batch(aeonb_ctx* ctx, const float* anchors_dev, int32_t n_anchors, const aeonb_rcnn_desc* descs, int n,
+                               float negative_overlap, float positive_overlap);
+
 /* Draws augmentation parameters exactly as aeon's param_factory::make_params does
  * (src/augment_image.cpp:107-230) for `n` records whose decoded sizes are in_w/in_h,
  * using per-slot std::minstd_rand0 engines seeded as aeon's batch_decoder seeds them

@@ -91,3 +91,14 @@ def test_no_ground_truth_boxes_leaves_every_anchor_unlabelled():
     out = orcnn.load(cfg, len(anchors), r)
     assert not out["bbtargets"].any() and not out["labels_mask"].any() and int(out["gt_box_count"][0, 0]) == 0
     assert out["labels_flat"].ravel()[:len(anchors)].all() and not out["labels_flat"].ravel()[len(anchors):].any()
+
+
+def test_host_anchor_table_equals_the_oracle():
+    """aeonb_rcnn_anchors (host C++) against the numpy restatement, default and odd configurations."""
+    from aeon_b200 import kernels as K
+    for kw in ({"width": 1000, "height": 1000}, {"width": 600, "height": 400, "base_size": 8, "scaling_factor": 1.0 / 8.0},
+               {"width": 300, "height": 333, "ratios": (0.33, 1, 3, 1.7), "scales": (2, 4.5)},
+               {"width": 100, "height": 50, "scaling_factor": 0.1, "base_size": 10}):
+        got = K.rcnn_anchors(K.rcnn_config(**kw))
+        want = orcnn.generate_anchors(kw)
+        assert got.shape == want.shape and np.array_equal(got, want), kw
