@@ -579,7 +579,7 @@ namespace aeonb
         }
 
         template <typename T>
-        cudaError_t launch_typed(const aug_launch& L, int clusters, int bands, size_t smem, int pix, cudaStream_t stream)
+        cudaError_t launch_typed(const aug_launch& L, int clusters, int bands, int cluster_size, size_t smem, int pix, cudaStream_t stream)
         {
             auto kern = pix == 4 ? aug_pack_kernel<T, 4> : aug_pack_kernel<T, 3>;
             cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -592,7 +592,7 @@ namespace aeonb
             cfg.stream             = stream;
             cudaLaunchAttribute attr[1];
             attr[0].id               = cudaLaunchAttributeClusterDimension;
-            attr[0].val.clusterDim.x = bands;
+            attr[0].val.clusterDim.x = cluster_size;
             attr[0].val.clusterDim.y = 1;
             attr[0].val.clusterDim.z = 1;
             cfg.attrs                = attr;
@@ -604,42 +604,57 @@ namespace aeonb
     // Host entry used by the C ABI: `descs_dev` is the device copy of the descriptors.
     // Returns a CUDA error; *why is set for configurations the kernel does not cover.
     cudaError_t launch_aug_pack(const aeonb_image_desc* descs_dev, int n, const aeonb_image_layout& layout, int pixel_stride,
-                                bool slots_aligned, cudaStream_t stream, const char** why)
+                                bool slots_aligned, bool any_contrast, cudaStream_t stream, const char** why)
     {
         *why = nullptr;
         int bands = 1;
         while (bands < AUG_MAX_BAND && layout.slot_h / (bands * 2) >= 8)
             bands *= 2;
         aug_launch L;
+        L.tile_pitch = (layout.slot_w + 15) / 16 * 16;
+        auto smem_for = [&](int nb) {
+            const int rows = (layout.slot_h + nb - 1) / nb;
+            return (size_t)3 * rows * L.tile_pitch + (size_t)layout.slot_w * (sizeof(int2) + sizeof(short2)) + (size_t)rows * sizeof(row_tap) + 16;
+        };
+        // A band has to fit the shared memory of one CTA.  Up to AUG_MAX_BAND bands form one cluster, which is what the
+        // contrast step needs (the per-image mean travels through distributed shared memory).  Larger outputs (a
+        // 1000 x 1000 detection input, say) take more, independent bands -- possible whenever no record of the batch
+        // changes the contrast.
+        while (smem_for(bands) > 200 * 1024 && bands < 256 && layout.slot_h / (bands * 2) >= 1)
+            bands *= 2;
+        if (bands > AUG_MAX_BAND && any_contrast)
+        {
+            *why = "a contrast change on an output too large for 8 on-chip bands (rows/8 * width * 3 over 200 KB) is outside the accelerated path";
+            return cudaErrorInvalidValue;
+        }
         L.descs         = descs_dev;
         L.layout        = layout;
         L.rows_per_band = (layout.slot_h + bands - 1) / bands;
-        L.tile_pitch    = (layout.slot_w + 15) / 16 * 16;
         const size_t elem = layout.dtype == AEONB_F64 ? 8 : layout.dtype == AEONB_F32 || layout.dtype == AEONB_I32 ? 4
                           : layout.dtype == AEONB_I16 || layout.dtype == AEONB_U16 ? 2 : 1;
         L.n         = n;
         L.vector_ok = slots_aligned && layout.stride_x == 1 && (layout.stride_y * elem) % 16 == 0 &&
                       (layout.stride_c * elem) % 16 == 0;
-        const size_t smem = (size_t)3 * L.rows_per_band * L.tile_pitch + (size_t)layout.slot_w * (sizeof(int2) + sizeof(short2)) +
-                            (size_t)L.rows_per_band * sizeof(row_tap) + 16;
+        const size_t smem = smem_for(bands);
         if (smem > 200 * 1024)
         {
-            *why = "output image too large for the on-chip band tile (rows/8 * width * 3 must stay under 200 KB)";
+            *why = "output image too large for the on-chip band tile (one row of width * 3 bytes must stay under 200 KB)";
             return cudaErrorInvalidValue;
         }
+        const int cluster_size = bands <= AUG_MAX_BAND ? bands : 1;
         // One cluster per record.  (The kernel can also run as fewer, persistent clusters that loop over records;
         // measured on B200 that was slower -- 0.228 ms against 0.181 ms for 256 records -- because records differ in
         // cost and the hardware's own dispatch balances them better than a static round-robin.)
         const int clusters = n;
         switch (layout.dtype)
         {
-        case AEONB_U8: return launch_typed<uint8_t>(L, clusters, bands, smem, pixel_stride, stream);
-        case AEONB_I8: return launch_typed<int8_t>(L, clusters, bands, smem, pixel_stride, stream);
-        case AEONB_I16: return launch_typed<int16_t>(L, clusters, bands, smem, pixel_stride, stream);
-        case AEONB_U16: return launch_typed<uint16_t>(L, clusters, bands, smem, pixel_stride, stream);
-        case AEONB_I32: return launch_typed<int32_t>(L, clusters, bands, smem, pixel_stride, stream);
-        case AEONB_F32: return launch_typed<float>(L, clusters, bands, smem, pixel_stride, stream);
-        case AEONB_F64: return launch_typed<double>(L, clusters, bands, smem, pixel_stride, stream);
+        case AEONB_U8: return launch_typed<uint8_t>(L, clusters, bands, cluster_size, smem, pixel_stride, stream);
+        case AEONB_I8: return launch_typed<int8_t>(L, clusters, bands, cluster_size, smem, pixel_stride, stream);
+        case AEONB_I16: return launch_typed<int16_t>(L, clusters, bands, cluster_size, smem, pixel_stride, stream);
+        case AEONB_U16: return launch_typed<uint16_t>(L, clusters, bands, cluster_size, smem, pixel_stride, stream);
+        case AEONB_I32: return launch_typed<int32_t>(L, clusters, bands, cluster_size, smem, pixel_stride, stream);
+        case AEONB_F32: return launch_typed<float>(L, clusters, bands, cluster_size, smem, pixel_stride, stream);
+        case AEONB_F64: return launch_typed<double>(L, clusters, bands, cluster_size, smem, pixel_stride, stream);
         }
         *why = "unknown output dtype";
         return cudaErrorInvalidValue;
@@ -715,7 +730,10 @@ extern "C" int aeonb_image_batch_noalloc(const aeonb_image_desc* descs, int n, c
         // Every descriptor the kernel reads is overwritten here, so nothing of the previous call survives.
         AEONB_CUDA(cudaMemcpyAsync(scratch, descs, sizeof(aeonb_image_desc) * n, cudaMemcpyHostToDevice, st));
         const char* why = nullptr;
-        cudaError_t e   = launch_aug_pack(scratch, n, *layout, pixel_stride, aligned, st, &why);
+        bool any_contrast = false;
+        for (int i = 0; i < n; ++i)
+            any_contrast |= descs[i].contrast != 1.0f;
+        cudaError_t e   = launch_aug_pack(scratch, n, *layout, pixel_stride, aligned, any_contrast, st, &why);
         if (why)
             throw error(AEONB_ERR_UNSUPPORTED, why);
         if (e != cudaSuccess)

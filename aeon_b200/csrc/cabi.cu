@@ -231,7 +231,10 @@ int aeonb_image_batch(aeonb_ctx* ctx, const aeonb_image_desc* descs, int n, cons
         AEONB_CUDA(cudaSetDevice(ctx->device));
         auto* dev = static_cast<const aeonb_image_desc*>(ctx->upload(descs, sizeof(aeonb_image_desc) * n));
         const char* why = nullptr;
-        cudaError_t e   = launch_aug_pack(dev, n, *layout, pixel_stride, aligned, ctx->stream, &why);
+        bool any_contrast = false;
+        for (int i = 0; i < n; ++i)
+            any_contrast |= descs[i].contrast != 1.0f;
+        cudaError_t e   = launch_aug_pack(dev, n, *layout, pixel_stride, aligned, any_contrast, ctx->stream, &why);
         if (why)
             throw error(AEONB_ERR_UNSUPPORTED, why);
         if (e != cudaSuccess)

@@ -251,6 +251,19 @@ aeonb_provider::aeonb_provider(aeonb_ctx* c, const json& cfg) : ctx(c)
             for (int i = 0; i < 5; ++i)
                 add(prefixed(st.ssd.name, names[i]), st.ssd.shapes[i], true);
         }
+        else if (t == "localization_rcnn")
+        {
+            // provider::localization::rcnn (src/provider.cpp:220-287): ten buffers per record
+            st.kind = stage_kind::rcnn;
+            st.rcnn = rcnn_config(e);
+            for (size_t i = 0; i < st.rcnn.class_names.size(); ++i)
+                st.class_map.insert({st.rcnn.class_names[i], (int)i});
+            st.anchors = rcnn_generate_anchors(st.rcnn.abi());
+            const char* names[10] = {"bbtargets", "bbtargets_mask", "labels_flat", "labels_mask", "image_shape", "gt_boxes",
+                                     "gt_box_count", "gt_class_count", "image_scale", "difficult_flag"};
+            for (int i = 0; i < 10; ++i)
+                add(prefixed(st.rcnn.name, names[i]), st.rcnn.shapes[i], true);
+        }
         else if (t == "audio")
         {
             st.kind  = stage_kind::audio;
@@ -271,4 +284,8 @@ aeonb_provider::aeonb_provider(aeonb_ctx* c, const json& cfg) : ctx(c)
         out_dev_t[k].resize(outputs.size());
     }
     out_host.resize(outputs.size());
+    rcnn_anchor_dev.resize(stages.size());
+    rcnn_result_dev.resize(stages.size());
+    rcnn_result_host.resize(stages.size());
+    rcnn_engine.seed(s);
 }

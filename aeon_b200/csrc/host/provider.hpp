@@ -21,6 +21,7 @@
 #include "config.hpp"
 #include "jpeg_host.hpp"
 #include "png_host.hpp"
+#include "rcnn_host.hpp"
 #include "params.hpp"
 #include "runtime.hpp"
 
@@ -33,7 +34,8 @@ namespace aeonb
         label,
         video,
         ssd,
-        audio
+        audio,
+        rcnn // localization_rcnn: anchor labels on the GPU, sampling and the ten buffers on the host
     };
 
     struct stage
@@ -45,6 +47,8 @@ namespace aeonb
         video_config video;
         ssd_config   ssd;
         audio_config audio;
+        rcnn_config  rcnn;
+        std::vector<box4> anchors; // localization_rcnn: the anchor table (anchor::generate), fixed per configuration
         std::unordered_map<std::string, int> class_map;
     };
 
@@ -114,7 +118,7 @@ namespace aeonb
         };
         explicit batch_plan(int stages)
             : descs(stages), desc_job(stages), desc_dst(stages), pre_descs(stages), pre_job(stages), desc_rot(stages),
-              pre_rot(stages), desc_pre(stages), desc_area(stages), sdescs(stages), sdesc_off(stages)
+              pre_rot(stages), desc_pre(stages), desc_area(stages), rcnn(stages), sdescs(stages), sdesc_off(stages)
         {
         }
         std::vector<jpeg_job>                      jobs;
@@ -133,6 +137,7 @@ namespace aeonb
         // output size 1:1.  Per descriptor: offset of that picture in the area arena, or -1.
         std::vector<std::vector<int64_t>>          desc_area;
         size_t                                     area_bytes = 0;
+        std::vector<std::vector<rcnn_record>>      rcnn; // per stage: what transformer::transform leaves for the loader
         std::vector<std::vector<aeonb_specgram_desc>> sdescs;
         std::vector<std::vector<size_t>>           sdesc_off;
         size_t stage_bytes = 0, pixel_bytes = 0, coef_bytes = 0, oriented_bytes = 0, rotated_bytes = 0;
@@ -168,6 +173,11 @@ struct aeonb_provider
     aeonb::device_buffer                 rotated_dev;  // pictures after the rotation pass
     aeonb::device_buffer                 resized_dev;  // pictures after the resize_short pass
     aeonb::device_buffer                 area_dev;     // pictures after an INTER_AREA crop -> output resize pass
+    // localization_rcnn, per stage: the anchor table on the device, the labels / best-box arrays of the batch on the
+    // device and their pinned host copies; one engine for the anchor sampling of all records
+    std::vector<aeonb::device_buffer>    rcnn_anchor_dev, rcnn_result_dev;
+    std::vector<aeonb::pinned_buffer>    rcnn_result_host;
+    aeonb::random_engine_t               rcnn_engine;
     // Device-side outputs of batches delivered to host memory, double buffered: the copy of batch t to the host
     // (on the copy stream) overlaps the kernels of batch t+1, which write the other set.
     std::vector<aeonb::device_buffer>    out_dev[2];   // per output, batch_size records

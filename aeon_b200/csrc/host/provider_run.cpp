@@ -627,6 +627,32 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
                 }
                 break;
             }
+            case stage_kind::rcnn:
+            {
+                // provider::localization::rcnn::provide (src/provider.cpp:254-287) and the host part of
+                // transformer::transform (src/etl_localization_rcnn.cpp:97-125): scale, scaled picture size, boxes
+                if (size == 0)
+                    empty("localization_rcnn data");
+                vector<bbox> boxes;
+                int          w = 0, h = 0;
+                parse_ssd_annotation(data, size, sg.class_map, w, h, boxes);
+                if (!have_params)
+                {
+                    params      = factory.make_params(engine, w, h, sg.rcnn.width, sg.rcnn.height);
+                    have_params = true;
+                }
+                rcnn_record rec;
+                const int   cw = params.cropbox.width, ch = params.cropbox.height;
+                rec.image_scale = factory.fixed_scaling_factor > 0 ? factory.fixed_scaling_factor
+                                                                   : calculate_scale(cw, ch, sg.rcnn.width, sg.rcnn.height);
+                rec.im_width  = unbiased_round((float)cw * rec.image_scale);
+                rec.im_height = unbiased_round((float)ch * rec.image_scale);
+                rec.gt_boxes  = transform_boxes_for_ssd(boxes, params);
+                if (rec.gt_boxes.size() > 1024)
+                    throw error(AEONB_ERR_UNSUPPORTED, "more than 1024 ground-truth boxes in a record is outside the accelerated path");
+                B.rcnn[s].push_back(std::move(rec));
+                break;
+            }
             case stage_kind::label:
             {
                 if (size == 0)
@@ -1077,6 +1103,50 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n)
             check_status(aeonb_image_batch(ctx, B.descs[s].data(), (int)B.descs[s].size(), &L));
             h2d_bytes += (int64_t)(sizeof(aeonb_image_desc) * B.descs[s].size());
         }
+        else if (sg.kind == stage_kind::rcnn)
+        {
+            // one launch labels every anchor of every record; labels and best boxes come back for the host's sampling
+            const size_t A = sg.anchors.size();
+            const int    m = (int)B.rcnn[s].size();
+            if (!rcnn_anchor_dev[s].p)
+            {
+                rcnn_anchor_dev[s].reserve(A * sizeof(box4));
+                AEONB_CUDA(cudaMemcpyAsync(rcnn_anchor_dev[s].p, sg.anchors.data(), A * sizeof(box4), cudaMemcpyHostToDevice, st));
+                AEONB_CUDA(cudaStreamSynchronize(st)); // the source is pageable memory owned by the stage
+                h2d_bytes += (int64_t)(A * sizeof(box4));
+            }
+            const size_t per = align_up(A, 16) + align_up(A * sizeof(int16_t), 16); // labels, then best boxes
+            rcnn_result_dev[s].reserve(per * m + 16);
+            rcnn_result_host[s].reserve(per * m + 16);
+            vector<box4>   gt;
+            vector<size_t> first(m);
+            for (int r = 0; r < m; ++r)
+            {
+                first[r] = gt.size();
+                for (const bbox& b : B.rcnn[s][r].gt_boxes)
+                    gt.push_back(box4{b.xmin, b.ymin, b.xmax, b.ymax});
+            }
+            gt.push_back(box4{0, 0, 0, 0}); // never empty
+            const box4* gt_dev = static_cast<const box4*>(ctx->upload(gt.data(), gt.size() * sizeof(box4)));
+            h2d_bytes += (int64_t)(gt.size() * sizeof(box4));
+            vector<aeonb_rcnn_desc> rd(m);
+            for (int r = 0; r < m; ++r)
+            {
+                const rcnn_record& rec = B.rcnn[s][r];
+                char*              out = static_cast<char*>(rcnn_result_dev[s].p) + per * r;
+                rd[r].gt_boxes  = reinterpret_cast<const float*>(gt_dev + first[r]);
+                rd[r].n_gt      = (int32_t)rec.gt_boxes.size();
+                rd[r].im_width  = rec.im_width;
+                rd[r].im_height = rec.im_height;
+                rd[r].labels    = reinterpret_cast<int8_t*>(out);
+                rd[r].best_box  = reinterpret_cast<int16_t*>(out + align_up(A, 16));
+            }
+            check_status(aeonb_rcnn_label_batch(ctx, static_cast<const float*>(rcnn_anchor_dev[s].p), (int32_t)A, rd.data(), m,
+                                                sg.rcnn.negative_overlap, sg.rcnn.positive_overlap));
+            h2d_bytes += (int64_t)(sizeof(aeonb_rcnn_desc) * m);
+            AEONB_CUDA(cudaMemcpyAsync(rcnn_result_host[s].p, rcnn_result_dev[s].p, per * m, cudaMemcpyDeviceToHost, st));
+            d2h_bytes += (int64_t)(per * m);
+        }
         else if (sg.kind == stage_kind::audio)
         {
             const int             o = sg.first_output;
@@ -1101,6 +1171,29 @@ void aeonb_provider::deliver(batch_plan& B, void* const* outs, int n, bool on_de
 {
     cudaStream_t st = ctx->stream;
     // ---- 5. deliver
+    // localization_rcnn: the labels of the GPU pass are needed on the host now -- sampling draws from them and the ten
+    // buffers are filled from the sample -- so a batch with such a stage waits for its kernels here.
+    for (size_t s = 0; s < stages.size(); ++s)
+    {
+        const stage& sg = stages[s];
+        if (sg.kind != stage_kind::rcnn)
+            continue;
+        AEONB_CUDA(cudaStreamSynchronize(st));
+        const size_t A   = sg.anchors.size();
+        const size_t per = align_up(A, 16) + align_up(A * sizeof(int16_t), 16);
+        for (size_t r = 0; r < B.rcnn[s].size(); ++r)
+        {
+            const char*    res    = static_cast<const char*>(rcnn_result_host[s].p) + per * r;
+            const int8_t*  labels = reinterpret_cast<const int8_t*>(res);
+            const int16_t* best   = reinterpret_cast<const int16_t*>(res + align_up(A, 16));
+            const vector<int> sampled = rcnn_sample_anchors(labels, (int)A, sg.rcnn.rois_per_image, sg.rcnn.foreground_fraction,
+                                                            sg.rcnn.deterministic_sampling ? nullptr : &rcnn_engine);
+            void* bufs[10];
+            for (int k = 0; k < 10; ++k)
+                bufs[k] = out_host[sg.first_output + k].data() + r * (size_t)outputs[sg.first_output + k].shape.byte_size();
+            rcnn_load(sg.rcnn, sg.anchors, B.rcnn[s][r], labels, best, sampled, bufs);
+        }
+    }
     size_t small_total = 0;
     for (size_t o = 0; o < outputs.size(); ++o)
         if (outputs[o].host_produced && on_device)

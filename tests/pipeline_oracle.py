@@ -6,6 +6,7 @@ import numpy as np
 
 from oracle import image_ops as ops
 from oracle import params as oparams
+from oracle import rcnn as orcnn
 from oracle import ssd as ossd
 
 
@@ -19,6 +20,7 @@ class PipelineOracle:
         self.decode_size = config.get("decode_size", config["batch_size"])
         self.engines = oparams.slot_engines(config["random_seed"], self.decode_size)
         self.cursor = 0
+        self._anchors = {}
 
     @staticmethod
     def decode(blob, channels=3):
@@ -75,6 +77,14 @@ class PipelineOracle:
                     gt = ossd.transform_boxes(boxes, p)
                     bufs = ossd.load_buffers(gt, etl["width"], etl["height"], etl.get("max_gt_boxes", 64))
                     for key, arr in zip(("image_shape", "gt_boxes", "gt_box_count", "gt_class_count", "difficult_flag"), bufs):
+                        outs.setdefault(name + key, []).append(arr)
+                elif etl["type"] == "localization_rcnn":
+                    w, h, boxes = ossd.parse_annotation(blob, etl["class_names"])
+                    if p is None:
+                        p = self.factory.make_params(g, w, h, etl["width"], etl["height"])
+                    anchors = self._anchors.setdefault(id(etl), orcnn.generate_anchors(etl))
+                    res = orcnn.transform(etl, anchors, boxes, p, self.aug.get("fixed_scaling_factor", -1.0))  # deterministic sampling
+                    for key, arr in orcnn.load(etl, len(anchors), res).items():
                         outs.setdefault(name + key, []).append(arr)
                 elif etl["type"] == "video":
                     frames = video_frames(blob)

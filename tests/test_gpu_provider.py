@@ -541,3 +541,19 @@ def test_pixelmask_alone_and_its_errors(ctx):
     small = [(jpeg_bytes(gradient_image(rng, 300, 300), 90), mask_png(rng, 40, 40)) for _ in range(4)]
     with pytest.raises(AeonError, match="crop box"):
         make_provider(ctx, two).run_host(small)
+
+
+def test_outputs_too_large_for_eight_bands(ctx):
+    """A 1000 x 800 output (detection-sized) does not fit eight on-chip bands: it runs as more, independent bands, which
+    covers everything but the contrast step (that one needs the whole-image mean inside one cluster)."""
+    from aeon_b200._lib import AeonError
+    etl = [{"type": "image", "height": 800, "width": 1000, "output_type": "uint8_t", "channel_major": False}]
+    recs = [(r[0],) for r in image_records(63, 4)]
+    aug = {"type": "image", "crop_enable": True, "scale": [0.6, 0.9], "flip_enable": True, "brightness": [0.7, 1.3],
+           "saturation": [0.7, 1.3], "hue": [-10, 10], "lighting": [0.0, 0.1]}
+    cfg = {"batch_size": 4, "random_seed": 21, "etl": etl, "augmentation": [aug]}
+    got = make_provider(ctx, cfg).run_host(recs)["image"]
+    assert np.array_equal(got, PipelineOracle(cfg).batch(recs)["image"])
+    cfg = {"batch_size": 4, "random_seed": 21, "etl": etl, "augmentation": [dict(aug, contrast=[0.6, 0.8])]}
+    with pytest.raises(AeonError, match="contrast"):
+        make_provider(ctx, cfg).run_host(recs)

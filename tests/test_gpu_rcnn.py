@@ -76,3 +76,85 @@ def test_bad_arguments(ctx):
     d = (L.RcnnDesc * 1)()
     assert ctx.lib.aeonb_rcnn_label_batch(ctx.handle, None, 10, d, 1, 0.3, 0.7) == L.ERR_INVALID
     assert ctx.lib.aeonb_rcnn_label_batch(ctx.handle, None, 10, d, 0, 0.3, 0.7) == 0
+
+
+RCNN_NAMES = ["bbtargets", "bbtargets_mask", "labels_flat", "labels_mask", "image_shape", "gt_boxes", "gt_box_count",
+              "gt_class_count", "image_scale", "difficult_flag"]
+
+
+def compare_rcnn(got, want):
+    for k in RCNN_NAMES:
+        assert got[k].shape == want[k].shape and got[k].dtype == want[k].dtype, k
+        if k == "bbtargets":     # the two log terms go through libm on either side: 1e-6 relative; the rest is exact
+            assert np.array_equal(got[k] != 0, want[k] != 0)
+            assert np.all(np.abs(got[k] - want[k]) <= 1e-6 * np.abs(want[k]) + 1e-7)
+        else:
+            assert np.array_equal(got[k], want[k]), k
+
+
+def test_provider_like_the_reference_test(ctx):
+    """TEST(localization_rcnn, provider), test/test_localization_rcnn.cpp:1373-1450: image + localization_rcnn,
+    fixed_aspect_ratio with a fixed scaling factor; the picture fills 800 x 600 of the 1000 x 1000 slot.  The ten buffers
+    in deterministic sampling mode equal the oracle's, and without a flip the reference's known foreground anchors."""
+    import cv2
+    from aeon_b200.provider import Provider
+    from tests.pipeline_oracle import PipelineOracle
+    g = golden()
+    img = np.empty((375, 500, 3), np.uint8)
+    img[:] = (50, 100, 200)
+    png = cv2.imencode(".png", img)[1].tobytes()
+    ann = g["annotation"].encode()
+    for flip in (True, False):
+        cfg = {"batch_size": 4, "random_seed": 3,
+               "etl": [{"type": "image", "height": 1000, "width": 1000, "channel_major": False},
+                       {"type": "localization_rcnn", "height": 1000, "width": 1000, "max_gt_boxes": 64,
+                        "class_names": g["class_names"], "debug_deterministic": True}],
+               "augmentation": [{"type": "image", "fixed_aspect_ratio": True, "fixed_scaling_factor": 1.6, "crop_enable": False,
+                                 "flip_enable": flip}]}
+        recs = [(png, ann)] * 4
+        prov = Provider(ctx, cfg)
+        assert len(prov.outputs) == 11
+        got = prov.run_host(recs)
+        image = got["image"]
+        assert image.shape == (4, 1000, 1000, 3)
+        assert (image[:, :600, :800] == np.array([50, 100, 200], np.uint8)).all()
+        assert not image[:, 600:].any() and not image[:, :, 800:].any()
+        oracle_cfg = dict(cfg, etl=[cfg["etl"][0], {k: v for k, v in cfg["etl"][1].items() if k != "debug_deterministic"}])
+        want = PipelineOracle(oracle_cfg).batch(recs)
+        compare_rcnn(got, want)
+        if not flip:
+            A = 34596
+            fg = np.nonzero(got["labels_flat"][0].ravel()[A:])[0].tolist()
+            assert fg == g["fg_idx"]
+            assert sorted(np.nonzero(got["labels_mask"][0].ravel())[0].tolist()) == sorted(g["labels_mask_idx"])
+
+
+def test_provider_random_sampling_is_a_valid_sample(ctx):
+    """Without debug_deterministic the sample is random (the reference draws it from an engine seeded by std::random_device):
+    check what every valid sample has in common -- sizes, labels of the chosen anchors, masks consistent with each other."""
+    import cv2
+    from aeon_b200.provider import Provider
+    g = golden()
+    png = cv2.imencode(".png", np.zeros((375, 500, 3), np.uint8))[1].tobytes()
+    cfg = {"batch_size": 2, "random_seed": 9,
+           "etl": [{"type": "image", "height": 1000, "width": 1000},
+                   {"type": "localization_rcnn", "height": 1000, "width": 1000, "class_names": g["class_names"]}],
+           "augmentation": [{"type": "image", "fixed_aspect_ratio": True, "fixed_scaling_factor": 1.6, "crop_enable": False}]}
+    got = Provider(ctx, cfg).run_host([(png, g["annotation"].encode())] * 2)
+    _, anchors, r = run_golden(g)
+    A = len(anchors)
+    picks = []
+    for i in range(2):
+        mask = got["labels_mask"][i].ravel()
+        chosen = np.nonzero(mask[:A])[0]
+        assert np.array_equal(mask[:A], mask[A:]) and len(chosen) == 256
+        assert (r.labels[chosen] >= 0).all()
+        fg = chosen[r.labels[chosen] == 1]
+        assert len(fg) == min(128, int((r.labels == 1).sum()))
+        assert np.array_equal(np.nonzero(got["labels_flat"][i].ravel()[A:])[0], fg)
+        bm = got["bbtargets_mask"][i].reshape(4, A)
+        assert np.array_equal(np.nonzero(bm[0])[0], fg) and (bm == bm[0]).all()
+        assert np.array_equal(np.nonzero(np.abs(got["bbtargets"][i].reshape(4, A)).sum(0))[0].tolist(),
+                              [c for c in chosen if np.abs(r.targets[c]).sum() != 0])
+        picks.append(chosen.tolist())
+    assert picks[0] != picks[1]      # two draws from one engine
