@@ -51,11 +51,17 @@ namespace aeonb
             return __fdiv_rn(inter, ua);
         }
 
+        // COMPACT: the indices of the anchors inside the picture (typically a third of the table) are first gathered into
+        // shared memory (16-bit, so for tables of up to 65 535 anchors), and both passes walk that list: every lane of a
+        // warp then has an anchor to work on.  Larger tables take the plain strided walk.
+        template <bool COMPACT>
         __global__ void __launch_bounds__(RCNN_THREADS) rcnn_label_kernel(const rcnn_launch L)
         {
+            extern __shared__ uint16_t inside_list[];
             __shared__ float4       gt[RCNN_MAX_GT];
             __shared__ float        gt_area[RCNN_MAX_GT];
             __shared__ unsigned int col_max[RCNN_MAX_GT]; // bit patterns of non-negative floats order like the floats
+            __shared__ int          n_inside;
 
             const aeonb_rcnn_desc d   = L.descs[blockIdx.x];
             const int             tid = threadIdx.x;
@@ -67,15 +73,44 @@ namespace aeonb
                 gt_area[k]     = __fmul_rn(extent(g.x, g.z), extent(g.y, g.w));
                 col_max[k]     = 0u;
             }
+            if (tid == 0)
+                n_inside = 0;
             __syncthreads();
             const float right = (float)d.im_width, bottom = (float)d.im_height;
+            auto is_inside = [&](const float4 a) { return a.x >= 0.0f && a.y >= 0.0f && a.z < right && a.w < bottom; }; // :474-487
+
+            if (COMPACT)
+            {
+                // every anchor gets its "outside / no boxes" answer; the inside ones are queued (order does not matter:
+                // each anchor's result depends on that anchor alone, and the per-box maximum is order-free)
+                const int rounds = (L.n_anchors + RCNN_THREADS - 1) / RCNN_THREADS;
+                for (int r = 0; r < rounds; ++r)
+                {
+                    const int  i  = r * RCNN_THREADS + tid;
+                    const bool in = i < L.n_anchors && K > 0 && is_inside(L.anchors[i]);
+                    if (i < L.n_anchors)
+                    {
+                        d.labels[i]   = -1;
+                        d.best_box[i] = 0;
+                    }
+                    const unsigned mask = __ballot_sync(0xFFFFFFFFu, in);
+                    int            base = 0;
+                    if ((tid & 31) == 0 && mask)
+                        base = atomicAdd(&n_inside, __popc(mask));
+                    base = __shfl_sync(0xFFFFFFFFu, base, 0);
+                    if (in)
+                        inside_list[base + __popc(mask & ((1u << (tid & 31)) - 1))] = (uint16_t)i;
+                }
+                __syncthreads();
+            }
+            const int count = COMPACT ? n_inside : L.n_anchors;
 
             if (K > 0)
-                for (int i = tid; i < L.n_anchors; i += RCNN_THREADS)
+                for (int j = tid; j < count; j += RCNN_THREADS)
                 {
-                    const float4 a = L.anchors[i];
-                    if (!(a.x >= 0.0f && a.y >= 0.0f && a.z < right && a.w < bottom))
-                        continue; // anchor::inside_image_bounds (:474-487)
+                    const float4 a = L.anchors[COMPACT ? (int)inside_list[j] : j];
+                    if (!COMPACT && !is_inside(a))
+                        continue;
                     const float a_area = __fmul_rn(extent(a.x, a.z), extent(a.y, a.w));
                     for (int k = 0; k < K; ++k)
                     {
@@ -86,10 +121,11 @@ namespace aeonb
                 }
             __syncthreads();
 
-            for (int i = tid; i < L.n_anchors; i += RCNN_THREADS)
+            for (int j = tid; j < count; j += RCNN_THREADS)
             {
+                const int    i      = COMPACT ? (int)inside_list[j] : j;
                 const float4 a      = L.anchors[i];
-                const bool   inside = a.x >= 0.0f && a.y >= 0.0f && a.z < right && a.w < bottom;
+                const bool   inside = COMPACT || is_inside(a);
                 int          label = -1, best = 0;
                 if (inside && K > 0)
                 {
@@ -153,8 +189,18 @@ extern "C" int aeonb_rcnn_label_batch(aeonb_ctx* ctx, const float* anchors_dev, 
         L.descs            = static_cast<const aeonb_rcnn_desc*>(ctx->upload(descs, sizeof(aeonb_rcnn_desc) * n));
         L.negative_overlap = negative_overlap;
         L.positive_overlap = positive_overlap;
-        rcnn_label_kernel<<<n, RCNN_THREADS, 0, ctx->stream>>>(L);
-        cudaError_t e = cudaGetLastError();
+        cudaError_t e = cudaSuccess;
+        if (n_anchors <= 65535)
+        {
+            const size_t smem = ((size_t)n_anchors * sizeof(uint16_t) + 15) & ~(size_t)15;
+            e = cudaFuncSetAttribute(rcnn_label_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e == cudaSuccess)
+                rcnn_label_kernel<true><<<n, RCNN_THREADS, smem, ctx->stream>>>(L);
+        }
+        else
+            rcnn_label_kernel<false><<<n, RCNN_THREADS, 0, ctx->stream>>>(L);
+        if (e == cudaSuccess)
+            e = cudaGetLastError();
         if (e != cudaSuccess)
             throw error(AEONB_ERR_CUDA, cuda_message("rcnn label kernel launch", e));
         ctx->launches++;

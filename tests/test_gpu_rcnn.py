@@ -71,6 +71,22 @@ def test_random_boxes_thresholds_and_a_box_nobody_overlaps(ctx):
     assert (labels3[0][inside] == 1).all() and (labels3[0][~inside] == -1).all()
 
 
+def test_anchor_table_beyond_the_16_bit_index_list(ctx):
+    """More than 65 535 anchors (a 2000 x 1500 configuration): the kernel's plain strided walk."""
+    from aeon_b200 import kernels as K
+    rng = np.random.default_rng(82)
+    anchors = K.rcnn_anchors(K.rcnn_config(2000, 1500))
+    assert len(anchors) == 9 * 125 * 93
+    gts = []
+    for k in (5, 40):
+        x0, y0 = rng.uniform(0, 1500, k), rng.uniform(0, 1100, k)
+        gts.append(np.stack([x0, y0, x0 + rng.uniform(30, 400, k), y0 + rng.uniform(30, 400, k)], 1).astype(np.float32))
+    labels, best = K.rcnn_label_batch(ctx, anchors, gts, [(1900, 1500), (2000, 1400)])
+    for i, s in enumerate([(1900, 1500), (2000, 1400)]):
+        want_l, want_b = oracle_labels(anchors, gts[i], s)
+        assert np.array_equal(labels[i], want_l) and np.array_equal(best[i], want_b)
+
+
 def test_bad_arguments(ctx):
     from aeon_b200 import _lib as L
     d = (L.RcnnDesc * 1)()
