@@ -123,3 +123,59 @@ def test_errors(ctx, dataset, tmp_path):
     (bad / "empty.tsv").write_text("@FILE\tASCII_INT\n")
     with pytest.raises(RuntimeError, match="manifest file is empty"):
         DataLoader(config=config(bad, manifest_filename=str(bad / "empty.tsv")))
+
+
+def test_segmentation_and_detection_manifests_through_the_loader(ctx, tmp_path):
+    """image,pixelmask and image,localization_rcnn data sets (doc/source/provider_pixelmask.rst, provider_localization_rcnn):
+    two files per manifest line; every buffer of a batch equals the record-level oracle's."""
+    import cv2
+    import json
+    from aeon_b200 import DataLoader
+    from tests.test_gpu_rcnn import compare_rcnn
+    rng = np.random.default_rng(52)
+    names = ["car", "person", "dog"]
+    lines_m, lines_d, recs_m, recs_d = ["@FILE\tFILE"], ["@FILE\tFILE"], [], []
+    for i in range(6):
+        h, w = int(rng.integers(120, 200)), int(rng.integers(150, 260))
+        img = jpeg_bytes(gradient_image(rng, h, w), 90)
+        yy, xx = np.mgrid[0:h, 0:w]
+        mask = cv2.imencode(".png", ((yy // 17 + xx // 23) % 5).astype(np.uint8))[1].tobytes()
+        objs = []
+        for _ in range(int(rng.integers(1, 5))):
+            x0, y0 = int(rng.integers(0, w - 40)), int(rng.integers(0, h - 40))
+            objs.append({"bndbox": {"xmin": x0, "ymin": y0, "xmax": x0 + int(rng.integers(20, 39)), "ymax": y0 + int(rng.integers(20, 39))},
+                         "name": names[int(rng.integers(3))], "difficult": bool(rng.integers(2))})
+        ann = json.dumps({"object": objs, "size": {"width": w, "height": h, "depth": 3}}).encode()
+        for name, blob in (("i%d.jpg" % i, img), ("m%d.png" % i, mask), ("a%d.json" % i, ann)):
+            (tmp_path / name).write_bytes(blob)
+        lines_m.append("i%d.jpg\tm%d.png" % (i, i))
+        lines_d.append("i%d.jpg\ta%d.json" % (i, i))
+        recs_m.append((img, mask))
+        recs_d.append((img, ann))
+    (tmp_path / "seg.tsv").write_text("\n".join(lines_m) + "\n")
+    (tmp_path / "det.tsv").write_text("\n".join(lines_d) + "\n")
+    base = {"manifest_root": str(tmp_path), "batch_size": 3, "random_seed": 7, "cpu_list": "0", "iteration_mode": "ONCE"}
+    seg = dict(base, manifest_filename=str(tmp_path / "seg.tsv"),
+               etl=[{"type": "image", "height": 64, "width": 80}, {"type": "pixelmask", "height": 64, "width": 80, "channels": 1}],
+               augmentation=[{"type": "image", "crop_enable": True, "scale": [0.5, 0.9], "flip_enable": True, "angle": [-10, 10]}])
+    dl = DataLoader(config=seg)
+    orc = PipelineOracle(dict(seg, decode_size=9))   # one worker thread: 8 slots rounded up to whole batches (src/loader.cpp:159-164)
+    for b, batch in enumerate(dl):
+        d, want = dict(batch), orc.batch(recs_m[3 * b:3 * b + 3])
+        assert [n for n, _ in batch] == ["image", "pixelmask"]
+        assert np.array_equal(d["image"], want["image"]) and np.array_equal(d["pixelmask"], want["pixelmask"])
+    dl.close()
+    det = dict(base, manifest_filename=str(tmp_path / "det.tsv"),
+               etl=[{"type": "image", "height": 320, "width": 400},
+                    {"type": "localization_rcnn", "height": 320, "width": 400, "class_names": names, "debug_deterministic": True,
+                     "rois_per_image": 64}],
+               augmentation=[{"type": "image", "crop_enable": False, "fixed_aspect_ratio": True, "flip_enable": True}])
+    dl = DataLoader(config=det)
+    oracle_cfg = dict(det, decode_size=9, etl=[det["etl"][0], {k: v for k, v in det["etl"][1].items() if k != "debug_deterministic"}])
+    orc = PipelineOracle(oracle_cfg)
+    for b, batch in enumerate(dl):
+        d, want = dict(batch), orc.batch(recs_d[3 * b:3 * b + 3])
+        assert len(batch) == 11 and batch[0][0] == "image" and batch[1][0] == "bbtargets"
+        assert np.array_equal(d["image"], want["image"])
+        compare_rcnn(d, want)
+    dl.close()
