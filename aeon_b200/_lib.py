@@ -144,6 +144,7 @@ PROTOTYPES = {
     "aeonb_png_info": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "aeonb_png_decode_bgr": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t]),
     "aeonb_png_decode_grey": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t]),
+    "aeonb_selftest_worker_pool": (C.c_int64, [C.c_int, C.c_int]),
     "aeonb_rcnn_anchor_count": (C.c_int64, [C.POINTER(RcnnConfig)]),
     "aeonb_rcnn_anchors": (C.c_int, [C.POINTER(RcnnConfig), C.c_void_p]),
     "aeonb_rcnn_label_batch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(RcnnDesc), C.c_int, C.c_float, C.c_float]),

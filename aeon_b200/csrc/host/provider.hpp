@@ -165,8 +165,11 @@ struct aeonb_provider
     int                                  slot_cursor = 0;
     std::unique_ptr<aeonb::worker_pool>  pool;
 
-    aeonb::pinned_buffer                 staging;      // coefficients / samples, host side
-    aeonb::device_buffer                 staging_dev;
+    // Staging: compressed scans + tables (or coefficients) / decoded PNG pictures / samples.  Two sets, taken in turn:
+    // the host fills set p for batch t while the upload stream still copies set 1-p of batch t-1 and the kernels of
+    // batch t-1 read its device copy.
+    aeonb::pinned_buffer                 staging[2];
+    aeonb::device_buffer                 staging_dev[2];
     aeonb::device_buffer                 coef_dev;     // device entropy decoding: status words, coefficient planes, work areas
     aeonb::device_buffer                 pixels_dev;   // decoded pictures
     aeonb::device_buffer                 oriented_dev; // pictures after the EXIF orientation pass
@@ -183,17 +186,20 @@ struct aeonb_provider
     std::vector<aeonb::device_buffer>    out_dev[2];   // per output, batch_size records
     std::vector<aeonb::device_buffer>    out_dev_t[2]; // transposed copies (batch_major == false)
     std::vector<std::vector<char>>       out_host;     // host-produced outputs
-    aeonb::pinned_buffer                 small_pinned;
+    aeonb::pinned_buffer                 small_pinned[2]; // host-produced outputs on their way to device memory, two sets as above
 
     static constexpr int k_events = 4;
     cudaEvent_t m_done[k_events]    = {nullptr, nullptr, nullptr, nullptr}; // batch t complete: m_done[t % k_events]
     cudaEvent_t m_kernels[k_events] = {nullptr, nullptr, nullptr, nullptr}; // the kernels of batch t have finished
     cudaStream_t m_copy             = nullptr; // device -> host copies of finished batches
     cudaEvent_t m_trace[k_events][3] = {};     // AEONB_TRACE: start of uploads, end of kernels, end of delivery (timing events)
-    cudaEvent_t m_staged            = nullptr; // the staging buffer of the last call has been copied to the device
-    bool        m_staged_valid      = false;
-    cudaEvent_t m_uploaded          = nullptr; // the small pinned buffer (host-produced outputs) of the last call has been copied
-    bool        m_uploaded_valid    = false;
+    cudaStream_t m_upload           = nullptr; // host -> device copies of the staging sets: they run under the previous batch's kernels
+    cudaEvent_t m_staged[2]         = {nullptr, nullptr}; // staging set p has been copied to the device (upload stream)
+    bool        m_staged_valid[2]   = {false, false};
+    cudaEvent_t m_consumed[2]       = {nullptr, nullptr}; // the kernels that read the device copy of set p have finished
+    bool        m_consumed_valid[2] = {false, false};
+    cudaEvent_t m_uploaded[2]       = {nullptr, nullptr}; // small pinned set p has been copied
+    bool        m_uploaded_valid[2] = {false, false};
     int64_t     m_ticket            = 0;       // number of batches submitted so far
     aeonb::pinned_buffer m_status[k_events];   // per in-flight batch: the device entropy decoder's status words
     int                  m_status_count[k_events] = {0, 0, 0, 0};
@@ -216,7 +222,7 @@ private:
     // the phases of run()
     void plan_records(aeonb::batch_plan& plan, const void* const* elems, const size_t* sizes, int n);
     void reserve_arenas(aeonb::batch_plan& plan, void* const* outs, bool on_device, int par);
-    void stage_inputs(aeonb::batch_plan& plan);
-    void launch_kernels(aeonb::batch_plan& plan, int n);
+    void stage_inputs(aeonb::batch_plan& plan, int par);
+    void launch_kernels(aeonb::batch_plan& plan, int n, int par);
     void deliver(aeonb::batch_plan& plan, void* const* outs, int n, bool on_device, bool wait, int par);
 };

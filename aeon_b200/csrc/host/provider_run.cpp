@@ -164,10 +164,15 @@ aeonb_provider::~aeonb_provider()
         for (cudaEvent_t e : slot)
             if (e)
                 cudaEventDestroy(e);
-    if (m_uploaded)
-        cudaEventDestroy(m_uploaded);
-    if (m_staged)
-        cudaEventDestroy(m_staged);
+    for (int k = 0; k < 2; ++k)
+        for (cudaEvent_t e : {m_uploaded[k], m_staged[k], m_consumed[k]})
+            if (e)
+                cudaEventDestroy(e);
+    if (m_upload)
+    {
+        cudaStreamSynchronize(m_upload);
+        cudaStreamDestroy(m_upload);
+    }
     if (m_copy)
     {
         cudaStreamSynchronize(m_copy);
@@ -223,10 +228,15 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     };
     AEONB_CUDA(cudaSetDevice(ctx->device));
     cudaStream_t st = ctx->stream;
-    if (!m_uploaded)
+    if (!m_upload)
     {
-        AEONB_CUDA(cudaEventCreateWithFlags(&m_uploaded, cudaEventDisableTiming));
-        AEONB_CUDA(cudaEventCreateWithFlags(&m_staged, cudaEventDisableTiming));
+        for (int k = 0; k < 2; ++k)
+        {
+            AEONB_CUDA(cudaEventCreateWithFlags(&m_uploaded[k], cudaEventDisableTiming));
+            AEONB_CUDA(cudaEventCreateWithFlags(&m_staged[k], cudaEventDisableTiming));
+            AEONB_CUDA(cudaEventCreateWithFlags(&m_consumed[k], cudaEventDisableTiming));
+        }
+        AEONB_CUDA(cudaStreamCreateWithFlags(&m_upload, cudaStreamNonBlocking));
         for (cudaEvent_t& e : m_done)
             AEONB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         for (cudaEvent_t& e : m_kernels)
@@ -238,10 +248,9 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     const int par = (int)((m_ticket + 1) & 1);
     if (!on_device && m_ticket >= 2)
         AEONB_CUDA(cudaStreamWaitEvent(st, m_done[(m_ticket - 1) % k_events], 0));
-    // The pinned staging buffer is reused: the previous call's copy of it to the device must have finished.  (That copy
-    // is queued ahead of the previous batch's kernels, so the host runs a batch ahead of the GPU.)
-    if (m_staged_valid)
-        AEONB_CUDA(cudaEventSynchronize(m_staged));
+    // The pinned staging set of this batch was last used two batches ago: its copy to the device must have finished.
+    if (m_staged_valid[par])
+        AEONB_CUDA(cudaEventSynchronize(m_staged[par]));
     const int64_t launches_before = ctx->launches;
     h2d_bytes = d2h_bytes = 0;
     mark(0);
@@ -259,9 +268,9 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
     mark(1);
     reserve_arenas(B, outs, on_device, par);
     mark(2);
-    stage_inputs(B); // 3. host work on the pool, uploads
+    stage_inputs(B, par); // 3. host work on the pool, uploads
     mark(3);
-    launch_kernels(B, n);
+    launch_kernels(B, n, par);
     mark(4);
     deliver(B, outs, n, on_device, wait, par);
     launches = (int32_t)(ctx->launches - launches_before);
@@ -702,8 +711,8 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
 void aeonb_provider::reserve_arenas(batch_plan& B, void* const* outs, bool on_device, int par)
 {
     // ---- 2. arenas
-    staging.reserve(B.stage_bytes + 256);
-    staging_dev.reserve(B.stage_bytes + 256);
+    staging[par].reserve(B.stage_bytes + 256);
+    staging_dev[par].reserve(B.stage_bytes + 256);
     pixels_dev.reserve(B.pixel_bytes + 256);
     if (B.oriented_bytes > 0)
         oriented_dev.reserve(B.oriented_bytes + 256);
@@ -735,12 +744,15 @@ void aeonb_provider::reserve_arenas(batch_plan& B, void* const* outs, bool on_de
 
 // Phase 3: the worker pool fills the pinned staging buffer (compressed scans and tables, or coefficient planes when
 // Huffman decoding runs on the host; audio samples), shipped to the device in slices while the pool is still working.
-void aeonb_provider::stage_inputs(batch_plan& B)
+void aeonb_provider::stage_inputs(batch_plan& B, int par)
 {
     cudaStream_t st = ctx->stream;
     // ---- 3. entropy decode on the pool, shipping finished slices while the rest decode
-    char* const hstage = static_cast<char*>(staging.p);
-    char* const dstage = static_cast<char*>(staging_dev.p);
+    char* const hstage = static_cast<char*>(staging[par].p);
+    char* const dstage = static_cast<char*>(staging_dev[par].p);
+    // the device copy of this set was read by the kernels of two batches ago
+    if (m_consumed_valid[par])
+        AEONB_CUDA(cudaStreamWaitEvent(m_upload, m_consumed[par], 0));
     const int   njobs  = (int)B.jobs.size();
     const int   nwork  = njobs + (int)B.copies.size();
     if (nwork > 0)
@@ -756,6 +768,12 @@ void aeonb_provider::stage_inputs(batch_plan& B)
         auto offset_of = [&](int i) { return i < njobs ? B.jobs[i].stage_off : B.copies[i - njobs].stage_off; };
         std::exception_ptr failure;
         std::mutex         failure_mutex;
+        // Jobs that only copy (scans and tables for the GPU's Huffman decoder, audio samples) are light: a few threads
+        // finish them sooner than the whole pool, whose wake-up takes the cores from the thread that plans and launches
+        // (measured with 256 records per batch and the batch left on the GPU: 195 k records/s with 3 threads, 105 k with 14).
+        bool heavy = false;
+        for (const jpeg_job& job : B.jobs)
+            heavy |= job.png || !job.on_device;
         pool->start(nwork, [&](int i) {
             try
             {
@@ -795,7 +813,7 @@ void aeonb_provider::stage_inputs(batch_plan& B)
                     failure = std::current_exception();
             }
             remaining[group_of(i)].fetch_sub(1, std::memory_order_release);
-        });
+        }, !heavy);
         cudaError_t copy_error = cudaSuccess;
         for (int g = 0; g < groups; ++g)
         {
@@ -805,7 +823,7 @@ void aeonb_provider::stage_inputs(batch_plan& B)
             const size_t end   = first[g + 1] < nwork ? offset_of(first[g + 1]) : B.stage_bytes;
             if (end > begin && copy_error == cudaSuccess && !failure)
             {
-                copy_error = cudaMemcpyAsync(dstage + begin, hstage + begin, end - begin, cudaMemcpyHostToDevice, st);
+                copy_error = cudaMemcpyAsync(dstage + begin, hstage + begin, end - begin, cudaMemcpyHostToDevice, m_upload);
                 h2d_bytes += (int64_t)(end - begin);
             }
         }
@@ -814,18 +832,19 @@ void aeonb_provider::stage_inputs(batch_plan& B)
             std::rethrow_exception(failure);
         AEONB_CUDA(copy_error);
     }
-    AEONB_CUDA(cudaEventRecord(m_staged, st));
-    m_staged_valid = true;
+    AEONB_CUDA(cudaEventRecord(m_staged[par], m_upload));
+    m_staged_valid[par] = true;
+    AEONB_CUDA(cudaStreamWaitEvent(st, m_staged[par], 0)); // the kernels of this batch start once its inputs have arrived
 
 }
 
 // Phase 4: one launch per kernel for the whole batch.
-void aeonb_provider::launch_kernels(batch_plan& B, int n)
+void aeonb_provider::launch_kernels(batch_plan& B, int n, int par)
 {
     cudaStream_t st     = ctx->stream;
     const int    nin    = (int)stages.size();
     const int    njobs  = (int)B.jobs.size();
-    char* const  dstage = static_cast<char*>(staging_dev.p);
+    char* const  dstage = static_cast<char*>(staging_dev[par].p);
     // ---- 4. kernels
     B.n_device_jobs = 0;
     if (njobs > 0)
@@ -1163,7 +1182,9 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n)
             h2d_bytes += (int64_t)(sizeof(aeonb_specgram_desc) * B.sdescs[s].size());
         }
     }
-
+    // every kernel that reads the device copy of this staging set is now enqueued
+    AEONB_CUDA(cudaEventRecord(m_consumed[par], st));
+    m_consumed_valid[par] = true;
 }
 
 // Phase 5: host-produced outputs, transposes, copies to the host on the copy stream, completion event.
@@ -1198,9 +1219,9 @@ void aeonb_provider::deliver(batch_plan& B, void* const* outs, int n, bool on_de
     for (size_t o = 0; o < outputs.size(); ++o)
         if (outputs[o].host_produced && on_device)
             small_total += align_up(out_host[o].size(), 256);
-    if (small_total > 0 && m_uploaded_valid)
-        AEONB_CUDA(cudaEventSynchronize(m_uploaded)); // the small pinned buffer is reused too
-    small_pinned.reserve(small_total + 256);
+    if (small_total > 0 && m_uploaded_valid[par])
+        AEONB_CUDA(cudaEventSynchronize(m_uploaded[par])); // the small pinned set is reused too (last used two batches ago)
+    small_pinned[par].reserve(small_total + 256);
     size_t small_off = 0;
     for (size_t o = 0; o < outputs.size(); ++o)
     {
@@ -1222,7 +1243,7 @@ void aeonb_provider::deliver(batch_plan& B, void* const* outs, int n, bool on_de
             const size_t bytes = batch_major ? rec * n : rec * batch_size;
             if (on_device)
             {
-                char* pin = static_cast<char*>(small_pinned.p) + small_off;
+                char* pin = static_cast<char*>(small_pinned[par].p) + small_off;
                 small_off += align_up(out_host[o].size(), 256);
                 std::memcpy(pin, src, bytes);
                 AEONB_CUDA(cudaMemcpyAsync(outs[o], pin, bytes, cudaMemcpyHostToDevice, st));
@@ -1234,8 +1255,8 @@ void aeonb_provider::deliver(batch_plan& B, void* const* outs, int n, bool on_de
     }
     if (small_total > 0)
     {
-        AEONB_CUDA(cudaEventRecord(m_uploaded, st));
-        m_uploaded_valid = true;
+        AEONB_CUDA(cudaEventRecord(m_uploaded[par], st));
+        m_uploaded_valid[par] = true;
     }
     ++m_ticket;
     // Recycling an event slot: the batch that used it (k_events submissions ago) is long complete once the

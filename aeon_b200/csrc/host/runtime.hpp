@@ -25,7 +25,10 @@ namespace aeonb
         int size() const { return (int)m_threads.size(); }
         // Starts fn(i) for i in [0,count) on the workers (indices handed out in increasing order) and
         // returns at once; wait() blocks until all are done and rethrows the first exception.
-        void start(int count, std::function<void(int)> fn);
+        // `light` wakes only the first k_light threads: a few hundred small copies finish sooner on three threads than on
+        // a whole pool whose wake-up competes with the calling thread for the cores.
+        static constexpr int k_light = 3;
+        void start(int count, std::function<void(int)> fn, bool light = false);
         void wait();
         void run(int count, std::function<void(int)> fn)
         {
@@ -34,14 +37,15 @@ namespace aeonb
         }
 
     private:
-        void loop();
+        void loop(int index);
         std::vector<std::thread>  m_threads;
         std::mutex                m_mutex;
-        std::condition_variable   m_wake, m_done;
+        std::condition_variable   m_wake, m_wake_rest, m_done; // the first k_light threads wait on m_wake, the others on m_wake_rest
         std::function<void(int)>  m_fn;
         std::atomic<int>          m_next{0};
         int                       m_count   = 0;
         int                       m_active  = 0;
+        int                       m_tickets = 0; // threads still to join the current job
         uint64_t                  m_epoch   = 0;
         bool                      m_stop    = false;
         std::exception_ptr        m_error;

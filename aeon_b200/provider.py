@@ -90,6 +90,17 @@ class Provider:
         self._inflight[ticket.value] = (keep, ptrs, sizes, outs)
         return ticket.value
 
+    def submit_device(self, records, out):
+        """Pipelined run_device: enqueue the batch into the caller's CUDA tensors `out` ({name: tensor}) and return a
+        ticket for wait().  The host stages of the next call overlap this batch's GPU work."""
+        ptrs, sizes, keep = self._pack(records)
+        outs = (C.c_void_p * len(self.outputs))(*[out[name].data_ptr() for name, _, _, _ in self.outputs])
+        ticket = C.c_int64()
+        L.check(self.lib.aeonb_provider_run_async(self.handle, ptrs, sizes, len(records), outs, 1, C.byref(ticket)))
+        self._inflight = getattr(self, "_inflight", {})
+        self._inflight[ticket.value] = (keep, ptrs, sizes, outs)
+        return ticket.value
+
     def wait(self, ticket):
         L.check(self.lib.aeonb_provider_wait(self.handle, ticket))
         getattr(self, "_inflight", {}).pop(ticket, None)

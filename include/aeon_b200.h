@@ -378,6 +378,10 @@ int     aeonb_rcnn_anchors(const aeonb_rcnn_config* cfg, float* out);
 int     aeonb_rcnn_label_batch(aeonb_ctx* ctx, const float* anchors_dev, int32_t n_anchors, const aeonb_rcnn_desc* descs, int n,
                                float negative_overlap, float positive_overlap);
 
+/* Host-only self-test of the worker pool that prepares the batches: `rounds` dispatches of 1 + (round mod 300) jobs,
+ * alternating between the whole pool and its light group; returns the sum of the job indices run, -1 on failure. */
+int64_t aeonb_selftest_worker_pool(int threads, int rounds);
+
 /* Draws augmentation parameters exactly as aeon's param_factory::make_params does
  * (src/augment_image.cpp:107-230) for `n` records whose decoded sizes are in_w/in_h,
  * using per-slot std::minstd_rand0 engines seeded as aeon's batch_decoder seeds them

@@ -3,6 +3,8 @@ import ctypes
 import os
 import re
 
+import pytest
+
 from tests.conftest import ROOT
 
 
@@ -44,3 +46,14 @@ def test_calls_without_a_gpu_fail_with_a_message_not_a_crash():
     h = ctypes.c_void_p()
     assert lib.aeonb_ctx_create(0, None, ctypes.byref(h)) < 0
     assert lib.aeonb_last_error()
+
+
+@pytest.mark.timeout(120)
+@pytest.mark.parametrize("threads", [1, 2, 3, 5, 14])
+def test_worker_pool_light_and_full_dispatches_complete(threads):
+    """The pool that stages the batches: thousands of alternating light (three threads) and full dispatches must all
+    complete and run every job exactly once."""
+    from aeon_b200 import _lib
+    rounds = 20000
+    want = sum((n * (n - 1)) // 2 for n in (1 + it % 300 for it in range(rounds)))
+    assert _lib.load().aeonb_selftest_worker_pool(threads, rounds) == want
