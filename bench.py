@@ -185,6 +185,8 @@ def main():
     ap.add_argument("--entropy", default="device", choices=["device", "host"],
                     help="where JPEG Huffman decoding runs: on the GPU (the timed step then starts from the compressed scans "
                          "resident in HBM) or on the host (the timed step starts from coefficient planes resident in HBM)")
+    ap.add_argument("--serial-kernels", action="store_true",
+                    help="time the three kernels of every step back to back on one stream (default: steps pipelined over two streams)")
     ap.add_argument("--kernels-only", action="store_true",
                     help="time the resident-input kernels only (used for profiler captures; e2e and cpu_baseline are null)")
     args = ap.parse_args()
@@ -344,15 +346,55 @@ def main():
         torch.cuda.synchronize()
 
     ts = ctx.torch_stream
-    for i in range(warmup):
-        kernel_step(i)
+    # Steps are software-pipelined over two streams of the library (two contexts): the entropy kernel of step i+1 runs on
+    # the first while the back end and the image kernel of step i run on the second, which fills the tail of the entropy
+    # kernel (few long streams left) with the other two kernels' blocks.  Every step still runs its three kernels in order
+    # on its own buffers (the four batch sets rotate; a set is reused only after its image kernel has finished).
+    two_streams = on_dev and not args.serial_kernels
+    ctx2 = K.Context(local_rank) if two_streams else None
+
+    def run_steps(count):
+        """Enqueues `count` steps; returns the stream whose tail marks the end of the work."""
+        if not two_streams:
+            for i in range(count):
+                kernel_step(i)
+            return ts
+        ts2 = ctx2.torch_stream
+        aug_done = []
+        for i in range(count):
+            jd, idesc, ed, _ = batches[i % n_batches]
+            if i >= n_batches:
+                ts.wait_event(aug_done[i - n_batches])
+            L.check(lib.aeonb_jpeg_entropy_batch(ctx.handle, ed, BATCH))
+            ent_done = torch.cuda.Event()
+            ent_done.record(ts)
+            ts2.wait_event(ent_done)
+            L.check(lib.aeonb_jpeg_backend_batch(ctx2.handle, jd, BATCH))
+            L.check(lib.aeonb_image_batch(ctx2.handle, idesc, BATCH, C.byref(layout)))
+            done = torch.cuda.Event()
+            done.record(ts2)
+            aug_done.append(done)
+        ts.wait_event(aug_done[-1])
+        return ts
+
+    run_steps(warmup)
+    barrier()
+    serial_out = None
+    if two_streams:   # the pipelined order must give what the plain order gives
+        kernel_step(warmup - 1)
+        torch.cuda.synchronize()
+        serial_out = out.clone()
+        run_steps(warmup)
+        torch.cuda.synchronize()
+        if not torch.equal(serial_out, out):
+            raise SystemExit("two-stream step order changed the output")
     barrier()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     ev[0].record(ts)
-    for i in range(args.steps):
-        kernel_step(i)
-    ev[1].record(ts)
+    if two_streams:
+        ctx2.torch_stream.wait_event(ev[0])
+    run_steps(args.steps).record_event(ev[1])
     barrier()
     kernel_ms = ev[0].elapsed_time(ev[1])
 
@@ -465,6 +507,7 @@ def main():
                        "scratch_pixel_stride": pix, "records_per_gpu_per_step": BATCH,
                        "decode": "whole pictures" if args.full_decode else "crop regions only (MCUs the crop box can touch)",
                        "entropy_decode": args.entropy,
+                       "kernel_streams": 2 if two_streams else 1,
                        "resident_input": "compressed JPEG scans + tables" if on_dev else "coefficient planes (Huffman-decoded on the host, untimed)"},
             "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_kind": peak_kind, "frac_of_8tbs_nominal": achieved / 8000.0,
