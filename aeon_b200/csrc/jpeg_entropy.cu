@@ -889,7 +889,7 @@ namespace aeonb
             uint32_t* const trail   = reinterpret_cast<uint32_t*>(clean + clean_room + dc_room) + (size_t)tid * 2 * TRAIL;
             int             cur_sel = 0, ncur = 0;
             uint32_t        cur_blocks = 0;
-            // round 0: guessed entry states (segment 0: the true one)
+            // first decoding pass: guessed entry states (segment 0: the true one)
             if (mine)
             {
                 const seg_result r = run_segment<false>(S, words, pbeg, 0, 0, pend, 0, nullptr, pbeg, trail, nullptr, 0, 0);
