@@ -174,3 +174,37 @@ def test_provider_random_sampling_is_a_valid_sample(ctx):
                               [c for c in chosen if np.abs(r.targets[c]).sum() != 0])
         picks.append(chosen.tolist())
     assert picks[0] != picks[1]      # two draws from one engine
+
+
+def test_provider_with_random_crops_thresholds_and_small_samples(ctx):
+    """Cropping enabled (boxes are cut, shifted and rescaled by the crop box before the anchors see them), other overlap
+    thresholds, fewer rois than foreground anchors, a record whose boxes all fall outside the crop."""
+    import cv2
+    from aeon_b200.provider import Provider
+    from tests.pipeline_oracle import PipelineOracle
+    rng = np.random.default_rng(83)
+    names = ["a", "b", "c"]
+    recs = []
+    for i in range(6):
+        h, w = int(rng.integers(200, 300)), int(rng.integers(260, 400))
+        png = cv2.imencode(".png", rng.integers(0, 256, (h, w, 3), dtype=np.uint8))[1].tobytes()
+        objs = []
+        for _ in range(int(rng.integers(1, 9))):
+            x0, y0 = int(rng.integers(0, w - 60)), int(rng.integers(0, h - 60))
+            if i == 5:
+                x0, y0 = 0, 0          # a sliver in the corner: usually outside the crop
+            objs.append({"bndbox": {"xmin": x0, "ymin": y0, "xmax": x0 + int(rng.integers(3 if i == 5 else 20, 6 if i == 5 else 59)),
+                                    "ymax": y0 + int(rng.integers(3 if i == 5 else 20, 6 if i == 5 else 59))},
+                         "name": names[int(rng.integers(3))], "difficult": bool(rng.integers(2))})
+        recs.append((png, json.dumps({"object": objs, "size": {"width": w, "height": h, "depth": 3}}).encode()))
+    for rc in ({"rois_per_image": 16, "foreground_fraction": 0.25}, {"negative_overlap": 0.2, "positive_overlap": 0.5},
+               {"scaling_factor": 0.125, "base_size": 8, "ratios": [0.5, 1, 2, 3], "scales": [4, 8]}):
+        etl_r = dict({"type": "localization_rcnn", "height": 240, "width": 320, "class_names": names, "debug_deterministic": True}, **rc)
+        cfg = {"batch_size": 6, "random_seed": 17,
+               "etl": [{"type": "image", "height": 240, "width": 320}, etl_r],
+               "augmentation": [{"type": "image", "crop_enable": True, "scale": [0.5, 0.8], "flip_enable": True, "center": False}]}
+        got = Provider(ctx, cfg).run_host(recs)
+        oracle_cfg = dict(cfg, etl=[cfg["etl"][0], {k: v for k, v in etl_r.items() if k != "debug_deterministic"}])
+        want = PipelineOracle(oracle_cfg).batch(recs)
+        assert np.array_equal(got["image"], want["image"])
+        compare_rcnn(got, want)
