@@ -222,6 +222,28 @@ namespace aeonb
             throw invalid_argument("class_names cannot be empty");
     }
 
+    bbox_config::bbox_config(json js)
+    {
+        if (js.is_null())
+            throw runtime_error("missing bbox config in json config");
+        js.erase("type");
+        for (const char* key : {"height", "width", "max_bbox_count", "class_names"})
+            required(js, key);
+        height           = get_int(js, "height", 0);
+        width            = get_int(js, "width", 0);
+        max_bbox_count   = get_int(js, "max_bbox_count", 0);
+        output_type_name = get_string(js, "output_type", "float");
+        name             = get_string(js, "name", "");
+        for (const json& c : js.find("class_names")->elements())
+            class_names.push_back(c.as_string());
+        check_output_type("output_type", output_type_name);
+        verify_config("bbox", {"height", "width", "max_bbox_count", "class_names", "output_type", "name"}, js);
+        if (max_bbox_count <= 0)
+            throw invalid_argument("invalid max_bbox_count");
+        shape.shape = {max_bbox_count, (int64_t)(4 * sizeof(float))};
+        shape.otype = output_type::from_name(output_type_name);
+    }
+
     rcnn_config::rcnn_config(json js)
     {
         if (js.is_null())

@@ -84,6 +84,21 @@ namespace aeonb
         explicit ssd_config(json js);
     };
 
+    // boundingbox block (src/etl_boundingbox.hpp:39-66): the transformed boxes of a record as max_bbox_count rows of four
+    // floats.  The reference declares the buffer as {max_bbox_count, 4 * sizeof(float)} elements of output_type and
+    // fills the first max_bbox_count * 4 floats of it; the same shape is kept.
+    struct bbox_config
+    {
+        int                      height = 0, width = 0;
+        int                      max_bbox_count = 0;
+        std::vector<std::string> class_names;
+        std::string              output_type_name = "float";
+        std::string              name;
+        shape_type               shape;
+        bbox_config() = default;
+        explicit bbox_config(json js);
+    };
+
     // Spectrogram block.  aeon's snapshot has the specgram routines (src/specgram.cpp) but no provider
     // wired to them; this block names their arguments.
     struct audio_config

@@ -251,6 +251,15 @@ aeonb_provider::aeonb_provider(aeonb_ctx* c, const json& cfg) : ctx(c)
             for (int i = 0; i < 5; ++i)
                 add(prefixed(st.ssd.name, names[i]), st.ssd.shapes[i], true);
         }
+        else if (t == "boundingbox")
+        {
+            // provider::boundingbox (src/provider.cpp:399-441)
+            st.kind = stage_kind::bbox;
+            st.bbox = bbox_config(e);
+            for (size_t i = 0; i < st.bbox.class_names.size(); ++i)
+                st.class_map.insert({st.bbox.class_names[i], (int)i});
+            add(prefixed(st.bbox.name, "boundingbox"), st.bbox.shape, true);
+        }
         else if (t == "localization_rcnn")
         {
             // provider::localization::rcnn (src/provider.cpp:220-287): ten buffers per record

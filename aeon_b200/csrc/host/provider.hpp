@@ -35,6 +35,7 @@ namespace aeonb
         video,
         ssd,
         audio,
+        bbox, // boundingbox: the transformed boxes as rows of four floats (host only)
         rcnn // localization_rcnn: anchor labels on the GPU, sampling and the ten buffers on the host
     };
 
@@ -48,6 +49,7 @@ namespace aeonb
         ssd_config   ssd;
         audio_config audio;
         rcnn_config  rcnn;
+        bbox_config  bbox;
         std::vector<box4> anchors; // localization_rcnn: the anchor table (anchor::generate), fixed per configuration
         std::unordered_map<std::string, int> class_map;
     };

@@ -636,6 +636,35 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
                 }
                 break;
             }
+            case stage_kind::bbox:
+            {
+                // provider::boundingbox::provide (src/provider.cpp:411-441) + boundingbox::loader::load
+                // (src/etl_boundingbox.cpp:296-318): the first max_bbox_count transformed boxes, zero rows after them
+                if (size == 0)
+                    empty("boundingbox");
+                vector<bbox> boxes;
+                int          w = 0, h = 0;
+                parse_ssd_annotation(data, size, sg.class_map, w, h, boxes);
+                if (!have_params)
+                {
+                    params      = factory.make_params(engine, w, h, sg.bbox.width, sg.bbox.height);
+                    have_params = true;
+                }
+                if (params.angle != 0) // the reference's transformer returns no boxes at all for a rotated record
+                    throw std::invalid_argument("boundingbox does not support 'angle'");
+                const vector<bbox> out   = transform_boxes_for_ssd(boxes, params);
+                const int          o     = sg.first_output;
+                float*             dst   = reinterpret_cast<float*>(out_host[o].data() + (size_t)r * outputs[o].shape.byte_size());
+                const int          count = std::min<int>(sg.bbox.max_bbox_count, (int)out.size());
+                for (int i = 0; i < count; ++i)
+                {
+                    dst[4 * i + 0] = out[i].xmin;
+                    dst[4 * i + 1] = out[i].ymin;
+                    dst[4 * i + 2] = out[i].xmax;
+                    dst[4 * i + 3] = out[i].ymax;
+                }
+                break;
+            }
             case stage_kind::rcnn:
             {
                 // provider::localization::rcnn::provide (src/provider.cpp:254-287) and the host part of

@@ -86,6 +86,15 @@ class PipelineOracle:
                     res = orcnn.transform(etl, anchors, boxes, p, self.aug.get("fixed_scaling_factor", -1.0))  # deterministic sampling
                     for key, arr in orcnn.load(etl, len(anchors), res).items():
                         outs.setdefault(name + key, []).append(arr)
+                elif etl["type"] == "boundingbox":
+                    w, h, boxes = ossd.parse_annotation(blob, etl["class_names"])
+                    if p is None:
+                        p = self.factory.make_params(g, w, h, etl["width"], etl["height"])
+                    rows = np.zeros((etl["max_bbox_count"], 16), ops._DTYPES[etl.get("output_type", "float")])
+                    flat = rows.view(np.uint8).reshape(-1).view(np.float32)     # the loader writes floats from the start
+                    for i, b in enumerate(ossd.transform_boxes(boxes, p)[:etl["max_bbox_count"]]):
+                        flat[4 * i:4 * i + 4] = (b.xmin, b.ymin, b.xmax, b.ymax)
+                    outs.setdefault(name + "boundingbox", []).append(rows)
                 elif etl["type"] == "video":
                     frames = video_frames(blob)
                     fc = etl["frame"]

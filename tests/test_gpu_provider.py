@@ -557,3 +557,37 @@ def test_outputs_too_large_for_eight_bands(ctx):
     cfg = {"batch_size": 4, "random_seed": 21, "etl": etl, "augmentation": [dict(aug, contrast=[0.6, 0.8])]}
     with pytest.raises(AeonError, match="contrast"):
         make_provider(ctx, cfg).run_host(recs)
+
+
+def test_image_and_boundingbox_stage(ctx):
+    """provider type image,boundingbox (src/provider.cpp:399-441): the record's boxes go through the same crop, flip and
+    rescale as the picture (boundingbox::transformer::transform_box) and fill the first max_bbox_count rows of four floats
+    of a buffer declared as {max_bbox_count, 16} elements; a rotated record is an error."""
+    import json
+    from aeon_b200._lib import AeonError
+    rng = np.random.default_rng(91)
+    names = ["cat", "dog"]
+    recs = []
+    for i in range(6):
+        h, w = int(rng.integers(150, 260)), int(rng.integers(200, 320))
+        objs = []
+        for _ in range(int(rng.integers(0, 7))):
+            x0, y0 = int(rng.integers(0, w - 50)), int(rng.integers(0, h - 50))
+            objs.append({"bndbox": {"xmin": x0, "ymin": y0, "xmax": x0 + int(rng.integers(5, 49)), "ymax": y0 + int(rng.integers(5, 49))},
+                         "name": names[int(rng.integers(2))]})
+        recs.append((jpeg_bytes(gradient_image(rng, h, w), 90),
+                     json.dumps({"object": objs, "size": {"width": w, "height": h, "depth": 3}}).encode()))
+    for out_type in ("float", "uint8_t"):
+        cfg = {"batch_size": 6, "random_seed": 31,
+               "etl": [{"type": "image", "height": 96, "width": 128},
+                       {"type": "boundingbox", "height": 96, "width": 128, "max_bbox_count": 4, "class_names": names, "output_type": out_type}],
+               "augmentation": [{"type": "image", "crop_enable": True, "scale": [0.5, 0.9], "flip_enable": True, "center": False}]}
+        got = make_provider(ctx, cfg).run_host(recs)
+        want = PipelineOracle(cfg).batch(recs)
+        assert got["boundingbox"].shape == (6, 4, 16) and got["boundingbox"].dtype == want["boundingbox"].dtype
+        assert np.array_equal(got["image"], want["image"])
+        assert np.array_equal(got["boundingbox"].view(np.uint8), want["boundingbox"].view(np.uint8))
+        assert got["boundingbox"].view(np.uint8).any()
+    cfg["augmentation"][0]["angle"] = [5, 10]
+    with pytest.raises(AeonError, match="angle"):
+        make_provider(ctx, cfg).run_host(recs)
