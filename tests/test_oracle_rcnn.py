@@ -102,3 +102,19 @@ def test_host_anchor_table_equals_the_oracle():
         got = K.rcnn_anchors(K.rcnn_config(**kw))
         want = orcnn.generate_anchors(kw)
         assert got.shape == want.shape and np.array_equal(got, want), kw
+
+
+def test_host_anchor_table_rejects_bad_configurations():
+    from aeon_b200 import _lib as L, kernels as K
+    import ctypes as C
+    lib = L.load()
+    out = np.zeros((16, 4), np.float32)
+    for kw in ({"width": 0, "height": 100}, {"width": 100, "height": 100, "scaling_factor": 0.0},
+               {"width": 100, "height": 100, "base_size": 0}):
+        cfg = K.rcnn_config(**kw)
+        assert lib.aeonb_rcnn_anchor_count(C.byref(cfg)) == 0 or kw.get("base_size") == 0
+        assert lib.aeonb_rcnn_anchors(C.byref(cfg), out.ctypes.data) == L.ERR_INVALID
+    cfg = K.rcnn_config(100, 100)
+    cfg.n_ratios = 9
+    assert lib.aeonb_rcnn_anchors(C.byref(cfg), out.ctypes.data) == L.ERR_INVALID
+    assert lib.aeonb_rcnn_anchors(None, out.ctypes.data) == L.ERR_INVALID
