@@ -400,9 +400,9 @@ namespace aeonb
         // segment once more from its now true entry state, this time storing the coefficients.  DC values
         // are stored as differences and summed up per component in a final scan.
         //
-        // Measured on a B200 with 256 streams of 25-85 KB (4:2:0, quality 90): 1.05 ms per batch with 512
-        // threads per block and segments of at least 192 bytes, against 20.9 ms for the one-warp kernel and
-        // about 10 ms for 14 host threads.  A wrong guess falls into step with the true decoder after about
+        // Measured on a B200 with 256 streams of 25-85 KB (4:2:0, quality 90): 1.05 ms per batch for whole pictures
+        // (0.83 ms for the crop regions of the benchmark configuration) with 512 threads per block and segments of
+        // at least 160 bytes, against 20.9 ms for the one-warp kernel and about 10 ms for 14 host threads.  A wrong guess falls into step with the true decoder after about
         // 10 blocks on average (the block's position inside the MCU has to match too), so shorter segments
         // need more rounds and longer ones leave threads idle; 96-256 bytes measured within 5 % of each other.
         // Tables of the block-parallel decoder: a 12-bit window decodes all but the rarest codes with one lookup (threads of
@@ -1010,7 +1010,7 @@ namespace aeonb
     int jpeg_entropy_min_segment()
     {
         static const int value = [] {
-            int v = 192;
+            int v = 160;
             if (const char* e = std::getenv("AEONB_ENTROPY_SEGMENT"))
                 v = std::atoi(e);
             return v < 64 ? 64 : v > (1 << 20) ? (1 << 20) : v;
