@@ -1,17 +1,26 @@
 // Image augmentation + packing kernel for sm_100a.
 //
 // One launch transforms a whole batch.  A record is handled by a thread-block cluster of
-// `bands` CTAs; CTA b owns a band of output rows.  Each CTA
-//   1. builds the horizontal / vertical bilinear tap tables of the crop->output resize
-//      (the 11-bit fixed-point form cv::resize(INTER_LINEAR) uses for 8-bit images),
-//   2. resizes its band straight from the source image in global memory, applies the
-//      brightness/saturation matrix and the HSV hue shift per pixel, and keeps the band
-//      as planar uint8 in shared memory, already flipped and in output channel order,
-//   3. if contrast is active, reduces per-channel sums (warp shuffles, then shared memory)
+// `bands` CTAs; CTA b owns a band of output rows, one thread per output column.  Each CTA
+//   1. builds the vertical tap table of the crop->output resize (the 11-bit fixed-point form
+//      cv::resize(INTER_LINEAR) uses for 8-bit images) and the list of distinct source rows
+//      its band touches; every thread keeps the horizontal taps of its column in registers,
+//   2. stages those source rows -- only the columns the band reads -- into shared memory with
+//      16-byte cp.async copies, double-buffered in groups of rows so that the copies of the
+//      next group run under the arithmetic of the current one,
+//   3. runs the horizontal pass ONCE per staged source row (two dot products per channel out
+//      of three aligned shared-memory words), keeps the last two horizontal results in
+//      registers and emits every output row whose taps are complete: vertical pass, colour
+//      matrix, HSV hue shift; the band is kept as planar uint8 in shared memory, already
+//      flipped and in output channel order,
+//   4. if contrast is active, reduces per-channel sums (warp shuffles, then shared memory)
 //      and exchanges the partial sums with the other CTAs of the cluster through
 //      distributed shared memory, so the per-image mean never touches global memory,
-//   4. applies contrast and lighting, converts to the output type, standardises and
-//      streams the band out with 128-bit stores into the record's slot of the batch buffer.
+//   5. applies contrast and lighting, converts to the output type, standardises and
+//      streams the band out with 128-bit stores, several in flight per thread.
+//
+// Pixels outside the source picture (expand canvas, padding) are never read: their taps get
+// weight zero, which gives the same sums as a zero pixel.
 //
 // The arithmetic of every stage is the integer / float32 arithmetic OpenCV applies for the
 // calls aeon makes (src/etl_image.cpp:146-202, src/image.cpp:336-406, src/etl_image.cpp:246-341);
@@ -32,37 +41,32 @@ namespace aeonb
 {
     namespace
     {
-        constexpr int AUG_THREADS  = 256;
-        constexpr int AUG_MAX_BAND = 8; // portable cluster size limit
+        constexpr int AUG_MAX_THREADS = 224;
+        constexpr int AUG_MAX_BAND    = 8;  // portable cluster size limit
+        constexpr int AUG_MAX_GROUP   = 16; // source rows staged per group, at most
+        constexpr int AUG_STAGE_PAD   = 16; // bytes kept free before and after a staged row
 
         struct aug_launch
         {
             const aeonb_image_desc* descs; // device copy
             aeonb_image_layout      layout;
             int                     rows_per_band;
-            int                     tile_pitch; // bytes per tile row (multiple of 16)
-            int                     vector_ok;  // slots are 16-byte aligned with unit x stride
-            int                     n;          // records in the batch
+            int                     tile_pitch;  // bytes per tile row (multiple of 16)
+            int                     vector_ok;   // slots are 16-byte aligned with unit x stride
+            int                     n;           // records in the batch
+            int                     stage_bytes; // shared memory for staged source rows (two buffers of half that)
         };
-
-        struct row_tap
-        {
-            int   y0, y1; // source rows inside the crop box (already clamped)
-            short b0, b1;
-        };
-
-        __device__ __forceinline__ int clamp_u8(int v) { return min(max(v, 0), 255); }
 
         __device__ __forceinline__ short sat_s16(int v) { return (short)min(max(v, -32768), 32767); }
 
-        // Source index and tap weights for destination index d (cv::resize, INTER_LINEAR, 8-bit).
-        __device__ __forceinline__ void linear_tap(int d, int src_len, int dst_len, bool clamp_weights, int& s, short& w0, short& w1)
+        // Source index and tap weights for destination index d (cv::resize, INTER_LINEAR, 8-bit);
+        // scale = 1 / (dst_len / src_len) in double, as cv::resize forms it.
+        __device__ __forceinline__ void linear_tap(int d, int src_len, double scale, bool clamp_weights, int& s, short& w0, short& w1)
         {
-            const double scale = 1.0 / ((double)dst_len / (double)src_len);
-            float        f     = (float)(((double)d + 0.5) * scale - 0.5);
-            float        fl    = floorf(f);
-            s                  = (int)fl;
-            f                  = f - fl;
+            float f  = (float)(((double)d + 0.5) * scale - 0.5);
+            float fl = floorf(f);
+            s        = (int)fl;
+            f        = f - fl;
             if (clamp_weights)
             {
                 if (s < 0)
@@ -80,9 +84,8 @@ namespace aeonb
             w1 = sat_s16(__float2int_rn(f * 2048.f));
         }
 
-        __device__ __forceinline__ int nearest_tap(int d, int src_len, int dst_len)
+        __device__ __forceinline__ int nearest_tap(int d, int src_len, double scale)
         {
-            const double scale = 1.0 / ((double)dst_len / (double)src_len);
             return min((int)floor((double)d * scale), src_len - 1);
         }
 
@@ -91,65 +94,38 @@ namespace aeonb
             int b, g, r;
         };
 
-        // Pixel of the (virtual) canvas at crop-relative coordinates.
-        template <int PIX>
-        __device__ __forceinline__ bgr fetch(const aeonb_image_desc& d, int x, int y)
-        {
-            const int sx = d.crop_x + x - d.canvas_x;
-            const int sy = d.crop_y + y - d.canvas_y;
-            bgr       p{0, 0, 0};
-            if ((unsigned)sx < (unsigned)d.src_w && (unsigned)sy < (unsigned)d.src_h)
-            {
-                const uint8_t* s = d.src + (size_t)sy * d.src_pitch + (size_t)sx * PIX;
-                if (PIX == 4)
-                {
-                    const uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(s));
-                    p.b              = v & 0xFF;
-                    p.g              = (v >> 8) & 0xFF;
-                    p.r              = (v >> 16) & 0xFF;
-                }
-                else
-                {
-                    p.b = __ldg(s);
-                    p.g = __ldg(s + 1);
-                    p.r = __ldg(s + 2);
-                }
-            }
-            return p;
-        }
+        // min(max(v, 0), 255) in one instruction (three-input integer min/max of sm_90 and later)
+        __device__ __forceinline__ int clamp_u8(int v) { return __vimin_s32_relu(v, 255); }
 
-        template <int PIX>
-        __device__ __forceinline__ bgr load_px(const uint8_t* s)
+        // The 12-bit reciprocals of 8-bit BGR->HSV: .x = round((255 << 12) / i), .y = round((180 << 12) / (6 i)).
+        // No quotient falls on a half for i in 1..255, so the integer form equals OpenCV's rounded double division.
+        struct hsv_div_table
         {
-            bgr p;
-            if (PIX == 4)
+            int2 v[256];
+        };
+        constexpr hsv_div_table make_hsv_div()
+        {
+            hsv_div_table t{};
+            for (int i = 1; i < 256; ++i)
             {
-                const uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(s));
-                p.b              = v & 0xFF;
-                p.g              = (v >> 8) & 0xFF;
-                p.r              = (v >> 16) & 0xFF;
+                t.v[i].x = (2 * (255 << 12) + i) / (2 * i);
+                t.v[i].y = (2 * ((180 << 12) / 6) + i) / (2 * i);
             }
-            else
-            {
-                p.b = __ldg(s);
-                p.g = __ldg(s + 1);
-                p.r = __ldg(s + 2);
-            }
-            return p;
+            return t;
         }
+        __device__ const hsv_div_table k_hsv_div = make_hsv_div();
 
-        // 8-bit BGR->HSV (H in [0,180)) with 12-bit reciprocal tables, then the hue shift with C
-        // remainder semantics stored through a uint8_t, then float32 HSV->BGR.
         // Per-CTA tables of the hue stage (all exact restatements of the per-pixel arithmetic, tabulated once):
-        //   sdiv/hdiv : the 12-bit reciprocals of 8-bit BGR->HSV;
-        //   sector_f  : for a hue h in [0,180), after the shift uint8((h + hue) % 180): the HSV->BGR sector and
-        //               the fractional position inside it;
-        //   unit      : x * (1/255) for x in [0,255] (the float S and V).
+        //   div      : the reciprocals above;
+        //   sector_f : for a hue h in [0,180), after the shift uint8((h + hue) % 180) (C remainder, stored through a
+        //              uint8_t): .x = byte selector that puts (p, q, v) of HSV->BGR into B,G,R order for the hue's
+        //              sector, .y = the factor f of the sector's middle term: the fractional position in odd sectors,
+        //              one minus it in even ones;
+        //   unit     : x * (1/255) for x in [0,255] (the float S and V).
         struct hue_tables
         {
-            int    sdiv[256];
-            int    hdiv[256];
-            float2 sector_f[180]; // .x = sector as a float bit pattern of an int, .y = f
+            int2   div[256];
+            float2 sector_f[180];
             float  unit[256];
         };
 
@@ -157,65 +133,68 @@ namespace aeonb
         {
             for (int i = tid; i < 256; i += nthreads)
             {
-                t.sdiv[i] = i ? __double2int_rn((double)(255 << 12) / (double)i) : 0;
-                t.hdiv[i] = i ? __double2int_rn((double)(180 << 12) / (6.0 * (double)i)) : 0;
+                t.div[i]  = k_hsv_div.v[i];
                 t.unit[i] = (float)i * (1.0f / 255.0f);
             }
             for (int h = tid; h < 180; h += nthreads)
             {
-                const int   hs = ((h + hue) % 180) & 0xFF; // C remainder, stored through a uint8_t
+                const int   hs = ((h + hue) % 180) & 0xFF;
                 const float hf = (float)hs * (6.0f / 180.0f);
                 const float fl = floorf(hf);
                 int         sector = (int)fl;
                 if (sector >= 6)
                     sector -= 6; // hs <= 255 gives sector <= 8
-                t.sector_f[h] = make_float2(__int_as_float(sector), hf - fl);
+                const float f = hf - fl;
+                // (B, G, R) = sector 0 (p, t, v)  1 (p, v, q)  2 (t, v, p)  3 (v, q, p)  4 (v, p, t)  5 (q, p, v), with
+                // p = v(1-s), q = v(1-sf), t = v(1-s(1-f)); the packed word holds p in byte 0, q or t in byte 1, v in byte 2
+                const unsigned sel = sector == 0 ? 0x3210u : sector == 1 ? 0x3120u : sector == 2 ? 0x3021u : sector == 3 ? 0x3012u
+                                   : sector == 4 ? 0x3102u : 0x3201u;
+                t.sector_f[h] = make_float2(__uint_as_float(sel), (sector & 1) ? f : 1.0f - f);
             }
         }
 
         // 8-bit BGR->HSV (H in [0,180)), hue shift, float32 HSV->BGR, as OpenCV computes them.
         __device__ __forceinline__ bgr hue_rotate(bgr p, bool truncate, const hue_tables& t)
         {
-            const int v    = max(max(p.b, p.g), p.r);
-            const int vmin = min(min(p.b, p.g), p.r);
-            const int diff = v - vmin;
-            const int s    = (diff * t.sdiv[v] + (1 << 11)) >> 12;
-            int       h;
+            const int  v    = __vimax3_s32(p.b, p.g, p.r);
+            const int  vmin = __vimin3_s32(p.b, p.g, p.r);
+            const int  diff = v - vmin;
+            const int2 dv   = t.div[v];
+            const int  s    = (diff * dv.x + (1 << 11)) >> 12;
+            int        h;
             if (v == p.r)
                 h = p.g - p.b;
             else if (v == p.g)
                 h = p.b - p.r + 2 * diff;
             else
                 h = p.r - p.g + 4 * diff;
-            h = (h * t.hdiv[diff] + (1 << 11)) >> 12;
-            if (h < 0)
-                h += 180;
-            const float2 sf2    = t.sector_f[h];
-            const int    sector = __float_as_int(sf2.x);
-            const float  f      = sf2.y;
-            const float  sf     = t.unit[s];
-            const float  vf     = t.unit[v];
-            const float t1 = vf * (1.0f - sf);
-            const float t2 = vf * __fmaf_rn(-sf, f, 1.0f);
-            const float t3 = vf * __fmaf_rn(-sf, 1.0f - f, 1.0f);
-            // sector -> (b, g, r): 0 (t1,t3,v) 1 (t1,v,t2) 2 (t3,v,t1) 3 (v,t2,t1) 4 (v,t1,t3) 5 (t2,t1,v); selects, no branches
-            const float fb = sector < 2 ? t1 : sector == 2 ? t3 : sector < 5 ? vf : t2;
-            const float fg = sector == 0 ? t3 : sector < 3 ? vf : sector == 3 ? t2 : t1;
-            const float fr = sector == 0 ? vf : sector == 1 ? t2 : sector < 4 ? t1 : sector == 4 ? t3 : vf;
-            bgr o; // products of two factors in [0,1] times 255: already inside 0..255
+            h = (h * t.div[diff].y + (1 << 11)) >> 12;
+            h += (h >> 31) & 180;
+            const float2 sf2 = t.sector_f[h];
+            const float  sf  = t.unit[s];
+            const float  vf  = t.unit[v];
+            const float  f1  = vf * (1.0f - sf);
+            const float  f2  = vf * __fmaf_rn(-sf, sf2.y, 1.0f);
+            int          a, b, c; // products of two factors in [0,1] times 255: already inside 0..255
             if (truncate)
             {
-                o.b = __float2int_rz(fb * 255.0f);
-                o.g = __float2int_rz(fg * 255.0f);
-                o.r = __float2int_rz(fr * 255.0f);
+                a = __float2int_rz(f1 * 255.0f);
+                b = __float2int_rz(f2 * 255.0f);
+                c = __float2int_rz(vf * 255.0f);
             }
             else
             {
-                o.b = __float2int_rn(fb * 255.0f);
-                o.g = __float2int_rn(fg * 255.0f);
-                o.r = __float2int_rn(fr * 255.0f);
+                a = __float2int_rn(f1 * 255.0f);
+                b = __float2int_rn(f2 * 255.0f);
+                c = __float2int_rn(vf * 255.0f);
             }
-            return o;
+            const unsigned packed = __byte_perm(__byte_perm(a, b, 0x3340), c, 0x3410);
+            const unsigned o      = __byte_perm(packed, 0u, __float_as_uint(sf2.x));
+            bgr            q;
+            q.b = o & 0xFF;
+            q.g = (o >> 8) & 0xFF;
+            q.r = o >> 16;
+            return q;
         }
 
         template <typename T>
@@ -236,7 +215,7 @@ namespace aeonb
         __device__ __forceinline__ double convert_out<double>(int v) { return (double)v; }
 
         template <typename T>
-        struct out_vec
+        struct alignas(16) out_vec
         {
             static constexpr int N = 16 / sizeof(T);
             T                    v[N];
@@ -262,24 +241,205 @@ namespace aeonb
             return e;
         }
 
-        template <typename T, int PIX>
-        __global__ void __launch_bounds__(AUG_THREADS, 4) aug_pack_kernel(const aug_launch L)
+        __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src)
         {
+            const unsigned s = (unsigned)__cvta_generic_to_shared(smem_dst);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem_src) : "memory");
+        }
+        __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+        __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+
+        // Horizontal result of one source row at one column: (S0*a0 + S1*a1) >> 4 per channel, as the vertical
+        // pass of cv::resize reads it.
+        struct hrow
+        {
+            int b, g, r;
+        };
+
+        // `at` = byte offset in shared memory of tap 0 of the column in the staged row.  The six (PIX 3) or eight
+        // (PIX 4) bytes of the two taps are cut out of the aligned words around them.
+        template <int PIX>
+        __device__ __forceinline__ hrow hpass_shared(const unsigned char* smem, int at, unsigned aw)
+        {
+            const uint32_t* p  = reinterpret_cast<const uint32_t*>(smem + (at & ~3));
+            uint32_t        lo = p[0], hi = p[1];
+            if (PIX == 3)
+            {
+                const uint32_t w2 = p[2];
+                const int      sh = at << 3; // the funnel shift takes the amount modulo 32
+                lo                = __funnelshift_r(lo, hi, sh);
+                hi                = __funnelshift_r(hi, w2, sh);
+            }
+            // byte pairs (tap 0, tap 1) of each channel in the low half of a word
+            const unsigned pb = __byte_perm(lo, hi, PIX == 3 ? 0x0030 : 0x0040);
+            const unsigned pg = __byte_perm(lo, hi, PIX == 3 ? 0x0041 : 0x0051);
+            const unsigned pr = __byte_perm(lo, hi, PIX == 3 ? 0x0052 : 0x0062);
+            hrow           h;
+            h.b = (int)__dp2a_lo(aw, pb, 0u) >> 4;
+            h.g = (int)__dp2a_lo(aw, pg, 0u) >> 4;
+            h.r = (int)__dp2a_lo(aw, pr, 0u) >> 4;
+            return h;
+        }
+
+        // Same from global memory, for crops too wide to stage a single row; a tap with weight zero is not read.
+        template <int PIX>
+        __device__ __forceinline__ hrow hpass_global(const uint8_t* tap0, unsigned aw)
+        {
+            int b0 = 0, g0 = 0, r0 = 0, b1 = 0, g1 = 0, r1 = 0;
+            if (aw & 0xFFFFu)
+                b0 = __ldg(tap0), g0 = __ldg(tap0 + 1), r0 = __ldg(tap0 + 2);
+            if (aw >> 16)
+                b1 = __ldg(tap0 + PIX), g1 = __ldg(tap0 + PIX + 1), r1 = __ldg(tap0 + PIX + 2);
+            hrow h;
+            h.b = (int)__dp2a_lo(aw, (unsigned)(b0 | (b1 << 8)), 0u) >> 4;
+            h.g = (int)__dp2a_lo(aw, (unsigned)(g0 | (g1 << 8)), 0u) >> 4;
+            h.r = (int)__dp2a_lo(aw, (unsigned)(r0 | (r1 << 8)), 0u) >> 4;
+            return h;
+        }
+
+        // Store phase of a band: its (channel, row) lines are cut into 16-byte output chunks.  A thread keeps its chunk
+        // column and walks down the lines, `lpp` lines apart (threads side by side write side by side), two lines at a
+        // time so that their loads and stores overlap; tile offset and output pointer are stepped, not recomputed.
+        // WHOLE: the band has no zero margin; IDENT: 8-bit output equal to the tile (margins of the tile are zero).
+        template <typename T>
+        struct store_args
+        {
+            const unsigned char* smem; // tile at offset 0
+            const T*             lut;  // [3][256]
+            T*                   dst;
+            int                  rows, row0, out_w, out_h, slot_w, channels, pitch, plane;
+            bool                 vec_ok;
+            int64_t              sc, sy, sx;
+        };
+
+        template <typename T, bool WHOLE, bool IDENT>
+        __device__ __forceinline__ void store_band(const store_args<T>& A, int tid, int nt)
+        {
+            constexpr int VEC    = out_vec<T>::N;
+            const int     chunks = (A.slot_w + VEC - 1) / VEC;
+            const int     lpp    = chunks <= nt ? nt / chunks : 1;
+            const int     chunk0 = chunks <= nt ? tid % chunks : tid;
+            const int     line0  = chunks <= nt ? tid / chunks : 0;
+            if (line0 >= lpp)
+                return;
+            const T zero = convert_out<T>(0);
+            struct cursor
+            {
+                int r, c, toff;
+                T*  g;
+            };
+            const int     t_step = 2 * lpp * A.pitch, t_wrap = A.plane - A.rows * A.pitch;
+            const int64_t g_step = 2 * lpp * A.sy, g_wrap = A.sc - A.rows * A.sy;
+            auto          place  = [&](int line, int x0) {
+                cursor q;
+                q.c    = (line >= A.rows) + (line >= 2 * A.rows) + (line >= 3 * A.rows);
+                q.r    = line - q.c * A.rows;
+                q.toff = q.c * A.plane + q.r * A.pitch + x0;
+                q.g    = A.dst + q.c * A.sc + (A.row0 + q.r) * A.sy + x0 * A.sx;
+                return q;
+            };
+            auto advance = [&](cursor& q) {
+                q.r += 2 * lpp;
+                q.toff += t_step;
+                q.g += g_step;
+                for (int it = 0; it < 3 && q.r >= A.rows; ++it)
+                {
+                    q.r -= A.rows;
+                    ++q.c;
+                    q.toff += t_wrap;
+                    q.g += g_wrap;
+                }
+            };
+            auto put = [&](const cursor& q, int x0) {
+                const unsigned char* px     = A.smem + q.toff;
+                const bool           row_in = A.row0 + q.r < A.out_h;
+                const T*             map    = A.lut + q.c * 256;
+                out_vec<T>           o;
+                if (VEC >= 4)
+                {
+                    uint32_t raw[VEC >= 4 ? VEC / 4 : 1];
+    #pragma unroll
+                    for (int w = 0; w < VEC / 4; ++w)
+                        raw[w] = reinterpret_cast<const uint32_t*>(px)[w];
+    #pragma unroll
+                    for (int k = 0; k < VEC; ++k)
+                    {
+                        const unsigned v = (raw[k >> 2] >> (8 * (k & 3))) & 0xFF;
+                        if (IDENT)
+                            o.v[k] = (T)v;
+                        else
+                            o.v[k] = (WHOLE || (row_in && x0 + k < A.out_w)) ? map[v] : zero;
+                    }
+                }
+                else
+                {
+    #pragma unroll
+                    for (int k = 0; k < VEC; ++k)
+                        o.v[k] = (WHOLE || (row_in && x0 + k < A.out_w)) ? map[px[k]] : zero;
+                }
+                if (A.vec_ok && x0 + VEC <= A.slot_w)
+                    *reinterpret_cast<int4*>(q.g) = *reinterpret_cast<const int4*>(o.v);
+                else
+                    for (int k = 0; k < VEC && x0 + k < A.slot_w; ++k)
+                        q.g[k * A.sx] = o.v[k];
+            };
+            for (int chunk = chunk0; chunk < chunks; chunk += nt)
+            {
+                const int x0 = chunk * VEC;
+                cursor    qa = place(line0, x0), qb = place(line0 + lpp, x0);
+                // every pass a cursor moves 2 * lpp lines down; c counts the planes passed (capped at 3 = past the end)
+                for (int guard = 0; guard < 3 * A.rows && qa.c < A.channels; ++guard)
+                {
+                    put(qa, x0);
+                    if (qb.c < A.channels)
+                        put(qb, x0);
+                    advance(qa);
+                    advance(qb);
+                }
+            }
+        }
+
+        template <typename T, int PIX>
+        __global__ void __launch_bounds__(AUG_MAX_THREADS, 5) aug_pack_kernel(const aug_launch L)
+        {
+            // Dynamic shared memory, addressed by 32-bit byte offsets:
+            //   tile     [3][rows_per_band][pitch]   the band, planar uint8, output channel order
+            //   ytab     int4[rows_per_band + 1]     per output row: k1 (position of tap 1 in the source row list; tap 0 is
+            //                                        the entry before it), unused, b0, b1; a last entry with k1 = -1 ends it
+            //   rowsrc   uint64[2 rows_per_band]     per listed source row: global address of its first staged byte
+            //   ysrc     int2[rows_per_band]         source rows of the two taps
+            //   srow     int[2 rows_per_band]        the source rows of the band in the order of the horizontal pass
+            //   rowaddr  int[2 rows_per_band]        per listed source row: offset of its first staged byte in shared memory
+            //   stage    two buffers of staged source rows
             extern __shared__ __align__(16) unsigned char smem[];
             __shared__ aeonb_image_desc d;
             __shared__ unsigned int     part_sum[3];  // this CTA's per-channel sums (output channel order)
             __shared__ float            contrast_add[3];
             __shared__ hue_tables       hue_tab;
             __shared__ T                lut[3][256];
+            __shared__ int              blk_cols[2];  // source column of tap 0 of the first / last column of the column block
+            __shared__ int              n_src_rows;   // listed source rows of the band
+            __shared__ double           tap_scale[2]; // source / output size, x and y
 
             cg::cluster_group cluster = cg::this_cluster();
             const int         band    = blockIdx.x;
             const int         bands   = gridDim.x;
             const int         tid     = threadIdx.x;
+            const int         nt      = blockDim.x;
             const int         lane    = tid & 31;
             const int         warp    = tid >> 5;
-            constexpr int     WARPS   = AUG_THREADS / 32;
+            const int         nwarps  = nt >> 5;
             const aeonb_image_layout& lay = L.layout;
+            const int         RPB     = L.rows_per_band;
+            const int         pitch   = L.tile_pitch;
+            const int         plane   = RPB * pitch;
+
+            int4*               ytab    = reinterpret_cast<int4*>(smem + 3 * plane);
+            unsigned long long* rowsrc  = reinterpret_cast<unsigned long long*>(ytab + RPB + 1);
+            int2*               ysrc    = reinterpret_cast<int2*>(rowsrc + 2 * RPB);
+            int*                srow    = reinterpret_cast<int*>(ysrc + RPB);
+            int*                rowaddr = srow + 2 * RPB;
+            const int           off_stage = (3 * plane + 56 * RPB + 16 + 15) & ~15;
 
             // A cluster takes records rec, rec + gridDim.y, ...; the launcher starts one cluster per record.
             for (int rec = blockIdx.y; rec < L.n; rec += gridDim.y)
@@ -288,224 +448,309 @@ namespace aeonb
                 {
                     const int* g = reinterpret_cast<const int*>(L.descs + rec);
                     int*       s = reinterpret_cast<int*>(&d);
-                    for (int i = tid; i < (int)(sizeof(aeonb_image_desc) / sizeof(int)); i += AUG_THREADS)
+                    for (int i = tid; i < (int)(sizeof(aeonb_image_desc) / sizeof(int)); i += nt)
                         s[i] = g[i];
                     if (tid < 3)
                         part_sum[tid] = 0;
+                    if (tid == 32 % nt) // the two scale factors of the resize, once per CTA (two double divisions each)
+                    {
+                        const aeonb_image_desc& gd = L.descs[rec];
+                        tap_scale[0] = 1.0 / ((double)gd.out_w / (double)gd.crop_w);
+                        tap_scale[1] = 1.0 / ((double)gd.out_h / (double)gd.crop_h);
+                    }
                 }
                 __syncthreads();
 
                 const int  out_w    = d.src ? d.out_w : 0;
                 const int  out_h    = d.src ? d.out_h : 0;
-                const int  row0     = band * L.rows_per_band;
-                const int  row_end  = min(row0 + L.rows_per_band, lay.slot_h);
+                const int  row0     = band * RPB;
+                const int  row_end  = min(row0 + RPB, lay.slot_h);
                 const int  img_end  = min(row_end, out_h); // rows that carry image data
-                const int  pitch    = L.tile_pitch;
-                const int  plane    = L.rows_per_band * pitch;
+                const int  nrows    = max(img_end - row0, 0);
                 const bool use_hue  = d.hue != 0;
                 const bool use_ctr  = d.contrast != 1.0f;
                 const bool swap_rb  = lay.bgr_to_rgb != 0;
                 const bool linear   = d.interp == AEONB_INTERP_LINEAR;
-                // the whole crop box lies on the source picture: no canvas test per tap
-                const bool inside = d.crop_x >= d.canvas_x && d.crop_y >= d.canvas_y && d.crop_x + d.crop_w <= d.canvas_x + d.src_w &&
-                                    d.crop_y + d.crop_h <= d.canvas_y + d.src_h;
 
-                unsigned char* tile = smem;                                            // [3][rows_per_band][pitch]
-                int2*          xofs = reinterpret_cast<int2*>(smem + 3 * plane);       // [out_w] byte offsets of the two taps
-                short2*        xw   = reinterpret_cast<short2*>(xofs + lay.slot_w);    // [out_w]
-                row_tap*       ytab = reinterpret_cast<row_tap*>(xw + lay.slot_w);     // [rows_per_band]
-
-                // ---- tap tables
-                for (int x = tid; x < out_w; x += AUG_THREADS)
+                // ---- vertical taps: source rows (clamped into the picture, weight zero when off it) and weights
+                for (int r = tid; r < nrows; r += nt)
                 {
-                    int   s;
-                    short a0 = 2048, a1 = 0;
-                    if (linear)
-                        linear_tap(x, d.crop_w, out_w, true, s, a0, a1);
-                    else
-                        s = nearest_tap(x, d.crop_w, out_w);
-                    const int s1 = min(s + 1, d.crop_w - 1);
-                    xofs[x]      = inside ? make_int2(s * PIX, s1 * PIX) : make_int2(s, s1);
-                    xw[x]        = make_short2(a0, a1);
-                }
-                for (int r = tid; r < img_end - row0; r += AUG_THREADS)
-                {
-                    row_tap t;
+                    int   y0, y1;
+                    short b0 = 2048, b1 = 0;
                     if (linear)
                     {
                         int s;
-                        linear_tap(row0 + r, d.crop_h, out_h, false, s, t.b0, t.b1);
-                        t.y0 = min(max(s, 0), d.crop_h - 1);
-                        t.y1 = min(max(s + 1, 0), d.crop_h - 1);
+                        linear_tap(row0 + r, d.crop_h, tap_scale[1], false, s, b0, b1);
+                        y0 = min(max(s, 0), d.crop_h - 1);
+                        y1 = min(max(s + 1, 0), d.crop_h - 1);
                     }
                     else
+                        y0 = y1 = nearest_tap(row0 + r, d.crop_h, tap_scale[1]);
+                    int sy0 = d.crop_y + y0 - d.canvas_y, sy1 = d.crop_y + y1 - d.canvas_y;
+                    if ((unsigned)sy0 >= (unsigned)d.src_h)
                     {
-                        t.y0 = t.y1 = nearest_tap(row0 + r, d.crop_h, out_h);
-                        t.b0        = 2048;
-                        t.b1        = 0;
+                        b0  = 0;
+                        sy0 = min(max(sy0, 0), d.src_h - 1);
                     }
-                    ytab[r] = t;
+                    if ((unsigned)sy1 >= (unsigned)d.src_h)
+                    {
+                        b1  = 0;
+                        sy1 = min(max(sy1, 0), d.src_h - 1);
+                    }
+                    ysrc[r] = make_int2(sy0, sy1);
+                    ytab[r] = make_int4(0, 0, b0, b1);
                 }
                 if (use_hue)
-                    build_hue_tables(hue_tab, d.hue, tid, AUG_THREADS);
+                    build_hue_tables(hue_tab, d.hue, tid, nt);
                 // the slot may be larger than the image: clear what the spatial stage will not write
                 if (out_w < lay.slot_w || img_end < row_end)
-                    for (int i = tid; i < 3 * plane / 16; i += AUG_THREADS)
-                        reinterpret_cast<int4*>(tile)[i] = make_int4(0, 0, 0, 0);
+                    for (int i = tid; i < 3 * plane / 16; i += nt)
+                        reinterpret_cast<int4*>(smem)[i] = make_int4(0, 0, 0, 0);
                 __syncthreads();
-
-                // ---- resize + per-pixel photometric into the tile; a warp takes 32 consecutive pixels of a row
-                unsigned int sum0 = 0, sum1 = 0, sum2 = 0;
+                // Source rows of the band in the order the horizontal pass takes them, such that every output row finds
+                // its tap 1 at some position k1 and its tap 0 right before it.  A row whose taps coincide (clamped at the
+                // picture's edge, or nearest) needs one listed row when a weight is zero -- the weight then moves to tap 1
+                // -- and the same row listed twice otherwise.
+                if (tid == 0)
                 {
-                    const int      rows  = max(img_end - row0, 0);
-                    const int      nseg  = (out_w + 31) >> 5;
-                    const int      units = rows * nseg;
-                    const uint8_t* base  = d.src + (ptrdiff_t)(d.crop_y - d.canvas_y) * d.src_pitch + (ptrdiff_t)(d.crop_x - d.canvas_x) * PIX;
-                    // Record constants live in shared memory; byte stores into the tile could alias them, so the
-                    // ones the pixel loop needs are copied to registers once.
-                    const int   src_pitch    = d.src_pitch;
-                    const int   color_enable = d.color_enable;
-                    const float cs0 = d.color_scale[0], cs1 = d.color_scale[1], cs2 = d.color_scale[2];
-                    const int   m0 = d.color_matrix[0], m1 = d.color_matrix[1], m2 = d.color_matrix[2], m3 = d.color_matrix[3],
-                                m4 = d.color_matrix[4], m5 = d.color_matrix[5], m6 = d.color_matrix[6], m7 = d.color_matrix[7],
-                                m8 = d.color_matrix[8];
-                    const int   hsv_cols = d.hsv_vector_cols;
-                    const bool  flip = d.flip != 0;
-
-                    struct taps
+                    int K = 0;
+                    for (int r = 0; r < nrows; ++r)
                     {
-                        bgr     p00, p01, p10, p11;
-                        short2  a;
-                        short   b0, b1;
-                        int     x, r;
-                        bool    valid;
-                    };
-                    // all global loads of one unit (32 pixels of a row), issued before any arithmetic on them
-                    auto load_unit = [&](int r, int seg) {
-                        taps k;
-                        k.r     = r;
-                        k.x     = seg * 32 + lane;
-                        k.valid = r < rows && k.x < out_w;
-                        if (!k.valid)
-                            return k;
-                        const row_tap t  = ytab[k.r];
-                        const int2    xo = xofs[k.x];
-                        k.a  = xw[k.x];
-                        k.b0 = t.b0;
-                        k.b1 = t.b1;
-                        if (inside)
+                        const int2 y = ysrc[r];
+                        int4       t = ytab[r];
+                        if (y.x != y.y)
                         {
-                            const uint8_t* r0 = base + (ptrdiff_t)t.y0 * src_pitch;
-                            const uint8_t* r1 = base + (ptrdiff_t)t.y1 * src_pitch;
-                            k.p00 = load_px<PIX>(r0 + xo.x);
-                            if (linear)
+                            if (K >= 2 && srow[K - 1] == y.y && srow[K - 2] == y.x)
+                                ;
+                            else if (K >= 1 && srow[K - 1] == y.x)
+                                srow[K++] = y.y;
+                            else
                             {
-                                k.p01 = load_px<PIX>(r0 + xo.y);
-                                k.p10 = load_px<PIX>(r1 + xo.x);
-                                k.p11 = load_px<PIX>(r1 + xo.y);
+                                srow[K++] = y.x;
+                                srow[K++] = y.y;
                             }
+                        }
+                        else if (t.z == 0 || t.w == 0)
+                        {
+                            if (t.w == 0)
+                            {
+                                t.w = t.z;
+                                t.z = 0;
+                            }
+                            if (!(K >= 1 && srow[K - 1] == y.x))
+                                srow[K++] = y.x;
                         }
                         else
                         {
-                            k.p00 = fetch<PIX>(d, xo.x, t.y0);
-                            if (linear)
+                            if (K >= 2 && srow[K - 1] == y.x && srow[K - 2] == y.x)
+                                ;
+                            else if (K >= 1 && srow[K - 1] == y.x)
+                                srow[K++] = y.x;
+                            else
                             {
-                                k.p01 = fetch<PIX>(d, xo.y, t.y0);
-                                k.p10 = fetch<PIX>(d, xo.x, t.y1);
-                                k.p11 = fetch<PIX>(d, xo.y, t.y1);
+                                srow[K++] = y.x;
+                                srow[K++] = y.x;
                             }
                         }
-                        return k;
-                    };
-                    auto finish_unit = [&](const taps& k) {
-                        if (!k.valid)
-                            return;
-                        bgr px = k.p00;
-                        if (linear)
-                        {
-                            // horizontal pass keeps 11 fractional bits; vertical pass as in OpenCV's 8-bit path
-                            const int      b0 = k.b0, b1 = k.b1;
-                            const unsigned aw = (unsigned)(unsigned short)k.a.x | ((unsigned)(unsigned short)k.a.y << 16);
-                            // two-way dot product: low 16 bits of aw times byte 0, high 16 bits times byte 1 (weights are 0..2048)
-                            const int hb0 = (int)__dp2a_lo(aw, (unsigned)(k.p00.b | (k.p01.b << 8)), 0u);
-                            const int hb1 = (int)__dp2a_lo(aw, (unsigned)(k.p10.b | (k.p11.b << 8)), 0u);
-                            const int hg0 = (int)__dp2a_lo(aw, (unsigned)(k.p00.g | (k.p01.g << 8)), 0u);
-                            const int hg1 = (int)__dp2a_lo(aw, (unsigned)(k.p10.g | (k.p11.g << 8)), 0u);
-                            const int hr0 = (int)__dp2a_lo(aw, (unsigned)(k.p00.r | (k.p01.r << 8)), 0u);
-                            const int hr1 = (int)__dp2a_lo(aw, (unsigned)(k.p10.r | (k.p11.r << 8)), 0u);
-                            // vertical pass as in OpenCV's 8-bit path; with weights summing to 2048 the result stays in 0..255
-                            px.b = (((b0 * (hb0 >> 4)) >> 16) + ((b1 * (hb1 >> 4)) >> 16) + 2) >> 2;
-                            px.g = (((b0 * (hg0 >> 4)) >> 16) + ((b1 * (hg1 >> 4)) >> 16) + 2) >> 2;
-                            px.r = (((b0 * (hr0 >> 4)) >> 16) + ((b1 * (hr1 >> 4)) >> 16) + 2) >> 2;
-                        }
-                        if (color_enable == 2)
-                        {
-                            px.b = clamp_u8(__float2int_rn((float)px.b * cs0));
-                            px.g = clamp_u8(__float2int_rn((float)px.g * cs1));
-                            px.r = clamp_u8(__float2int_rn((float)px.r * cs2));
-                        }
-                        else if (color_enable)
-                        {
-                            const int b  = (px.b * m0 + px.g * m1 + px.r * m2 + 512) >> 10;
-                            const int g  = (px.b * m3 + px.g * m4 + px.r * m5 + 512) >> 10;
-                            const int rr = (px.b * m6 + px.g * m7 + px.r * m8 + 512) >> 10;
-                            px.b = clamp_u8(b);
-                            px.g = clamp_u8(g);
-                            px.r = clamp_u8(rr);
-                        }
-                        if (use_hue)
-                            px = hue_rotate(px, k.x < hsv_cols, hue_tab);
+                        t.x     = K - 1;
+                        ytab[r] = t;
+                    }
+                    ytab[nrows] = make_int4(-1, 0, 0, 0);
+                    n_src_rows  = K;
+                }
+                __syncthreads();
 
-                        const int xo_t = flip ? out_w - 1 - k.x : k.x;
-                        const int c0   = swap_rb ? px.r : px.b;
-                        const int c2   = swap_rb ? px.b : px.r;
-                        unsigned char* o = tile + k.r * pitch + xo_t;
-                        o[0]             = (unsigned char)c0;
-                        o[plane]         = (unsigned char)px.g;
-                        o[2 * plane]     = (unsigned char)c2;
-                        sum0 += c0;
-                        sum1 += px.g;
-                        sum2 += c2;
-                    };
-                    // two units in flight per warp: the loads of the second overlap the arithmetic of the first.
-                    // Unit u = (row, 32-pixel segment); the warp steps through its units without dividing.
-                    // (nseg >= 1 here; the wrap loop is bounded by the step because each wrap removes at least 1.)
-                    auto advance = [&](int& r, int& seg, int by) {
-                        seg += by;
-                        for (int it = 0; it < 2 * WARPS && seg >= nseg; ++it)
-                        {
-                            seg -= nseg;
-                            ++r;
-                        }
-                    };
-                    int ra = 0, sa = 0;
-                    advance(ra, sa, warp);
-                    int rb = ra, sb = sa;
-                    advance(rb, sb, WARPS);
-                    (void)units;
-                    // an empty image (zero-filled slot) has no units at all
-                    for (int guard = 0; nseg > 0 && ra < rows && guard < units; ++guard)
+                // ---- resize + per-pixel photometric into the tile; a thread owns one output column of the band
+                unsigned int sum_b = 0, sum_g = 0, sum_r = 0;
+                {
+                    const int K = n_src_rows;
+                    // Record constants live in shared memory; byte stores into the tile could alias them, so the
+                    // ones the pixel loop needs are copied to registers once.
+                    const int      src_pitch    = d.src_pitch;
+                    const int      src_w        = d.src_w;
+                    const uint8_t* src          = d.src;
+                    const int      color_enable = d.color_enable;
+                    const float    cs0 = d.color_scale[0], cs1 = d.color_scale[1], cs2 = d.color_scale[2];
+                    const int      m0 = d.color_matrix[0], m1 = d.color_matrix[1], m2 = d.color_matrix[2], m3 = d.color_matrix[3],
+                                   m4 = d.color_matrix[4], m5 = d.color_matrix[5], m6 = d.color_matrix[6], m7 = d.color_matrix[7],
+                                   m8 = d.color_matrix[8];
+                    const int      hsv_cols = d.hsv_vector_cols;
+                    const bool     flip     = d.flip != 0;
+                    // the picture's bytes: a staged 16-byte group that is not wholly inside is fetched byte by byte
+                    const uint8_t* mem_lo = src;
+                    const uint8_t* mem_hi = src + (ptrdiff_t)(d.src_h - 1) * src_pitch + (ptrdiff_t)src_w * PIX;
+
+                    for (int xb = 0; xb < out_w; xb += nt)
                     {
-                        const taps ka = load_unit(ra, sa);
-                        const taps kb = load_unit(rb, sb);
-                        finish_unit(ka);
-                        finish_unit(kb);
-                        advance(ra, sa, 2 * WARPS);
-                        advance(rb, sb, 2 * WARPS);
+                        const int  x      = xb + tid;
+                        const bool active = x < out_w;
+                        int        sx0    = 0;
+                        short      a0 = 2048, a1 = 0;
+                        if (active)
+                        {
+                            int s;
+                            if (linear)
+                                linear_tap(x, d.crop_w, tap_scale[0], true, s, a0, a1);
+                            else
+                                s = nearest_tap(x, d.crop_w, tap_scale[0]);
+                            sx0 = d.crop_x + s - d.canvas_x;
+                            if (tid == 0)
+                                blk_cols[0] = sx0;
+                            if (x == min(xb + nt, out_w) - 1)
+                                blk_cols[1] = sx0;
+                        }
+                        __syncthreads();
+                        // columns staged for this block: the taps of its first to last column, cut to the picture
+                        const int bsa  = min(max(blk_cols[0], 0), src_w);
+                        const int bsb  = max(min(blk_cols[1] + 2, src_w), bsa);
+                        const int span = (bsb - bsa) * PIX;
+                        const int stage_pitch = ((span + 30) & ~15) + 2 * AUG_STAGE_PAD; // room for a lead of up to 15 bytes
+                        const int R = min(AUG_MAX_GROUP, (L.stage_bytes / 2) / stage_pitch);
+                        // where each listed source row starts in global memory and where it is staged (group g = k / R
+                        // goes to buffer g & 1); the staged copy keeps the row's alignment modulo 16
+                        for (int k = tid; k < K; k += nt)
+                        {
+                            const uint8_t* first = src + (ptrdiff_t)srow[k] * src_pitch + (ptrdiff_t)bsa * PIX;
+                            rowsrc[k]            = (unsigned long long)first;
+                            if (R >= 1)
+                            {
+                                const int g = k / R;
+                                rowaddr[k]  = off_stage + ((g & 1) * R + (k - g * R)) * stage_pitch + AUG_STAGE_PAD + (int)((uintptr_t)first & 15);
+                            }
+                        }
+                        if (a0 != 0 && (unsigned)sx0 >= (unsigned)src_w)
+                            a0 = 0;
+                        if (a1 != 0 && (unsigned)(sx0 + 1) >= (unsigned)src_w)
+                            a1 = 0;
+                        const unsigned aw  = (unsigned)(unsigned short)a0 | ((unsigned)(unsigned short)a1 << 16);
+                        const int      sxc = min(max(sx0, bsa - 1), max(bsb - 1, bsa - 1)); // keeps both taps next to the staged bytes
+                        const int      off = (sxc - bsa) * PIX;
+                        const bool     truncate = x < hsv_cols;
+                        const int      xo_t     = flip ? out_w - 1 - x : x;
+                        // tile positions of this column's B, G, R bytes (output channel order), stepped down a row per pixel
+                        int tb = (swap_rb ? 2 * plane : 0) + xo_t, tg = plane + xo_t, tr = (swap_rb ? 0 : 2 * plane) + xo_t;
+                        __syncthreads(); // rowsrc / rowaddr are complete
+
+                        hrow h_prev{0, 0, 0}, h_cur{0, 0, 0};
+                        int  r   = 0;
+                        int4 tap = ytab[0]; // taps of the next output row to emit
+                        // rows whose second tap is source row k are complete once that row's horizontal pass is done:
+                        // vertical pass, photometric stages, tile store
+                        auto emit_ready = [&](int k) {
+                            for (int guard = 0; guard <= nrows && tap.x == k; ++guard)
+                            {
+                                const int b0 = tap.z, b1 = tap.w;
+                                bgr       px;
+                                // as in OpenCV's 8-bit path; with weights summing to 2048 the result stays in 0..255
+                                px.b = (((b0 * h_prev.b) >> 16) + ((b1 * h_cur.b) >> 16) + 2) >> 2;
+                                px.g = (((b0 * h_prev.g) >> 16) + ((b1 * h_cur.g) >> 16) + 2) >> 2;
+                                px.r = (((b0 * h_prev.r) >> 16) + ((b1 * h_cur.r) >> 16) + 2) >> 2;
+                                ++r;
+                                tap = ytab[r];
+                                if (color_enable == 2)
+                                {
+                                    px.b = clamp_u8(__float2int_rn((float)px.b * cs0));
+                                    px.g = clamp_u8(__float2int_rn((float)px.g * cs1));
+                                    px.r = clamp_u8(__float2int_rn((float)px.r * cs2));
+                                }
+                                else if (color_enable)
+                                {
+                                    const int b  = (px.b * m0 + px.g * m1 + px.r * m2 + 512) >> 10;
+                                    const int g  = (px.b * m3 + px.g * m4 + px.r * m5 + 512) >> 10;
+                                    const int rr = (px.b * m6 + px.g * m7 + px.r * m8 + 512) >> 10;
+                                    px.b = clamp_u8(b);
+                                    px.g = clamp_u8(g);
+                                    px.r = clamp_u8(rr);
+                                }
+                                if (use_hue)
+                                    px = hue_rotate(px, truncate, hue_tab);
+                                smem[tb] = (unsigned char)px.b;
+                                smem[tg] = (unsigned char)px.g;
+                                smem[tr] = (unsigned char)px.r;
+                                tb += pitch;
+                                tg += pitch;
+                                tr += pitch;
+                                sum_b += px.b;
+                                sum_g += px.g;
+                                sum_r += px.r;
+                            }
+                        };
+
+                        if (R >= 1)
+                        {
+                            // copies of group g (listed rows g*R ...); a warp takes a row, a lane 16 bytes at a time
+                            auto issue = [&](int g) {
+                                const int k_end = min((g + 1) * R, K);
+                                for (int k = g * R + warp; k < k_end; k += nwarps)
+                                {
+                                    const uint8_t* first = reinterpret_cast<const uint8_t*>(rowsrc[k]);
+                                    const int      lead  = (int)((uintptr_t)first & 15);
+                                    const uint8_t* g0    = first - lead;
+                                    const int      s0    = rowaddr[k] - lead;
+                                    const int      nck   = span ? (lead + span + 15) >> 4 : 0;
+                                    if (g0 >= mem_lo && g0 + nck * 16 <= mem_hi)
+                                        for (int c = lane; c < nck; c += 32)
+                                            cp_async_16(smem + s0 + c * 16, g0 + c * 16);
+                                    else // first or last row of a picture that is not 16-byte aligned
+                                        for (int c = lane; c < nck; c += 32)
+                                        {
+                                            const uint8_t* gp = g0 + c * 16;
+                                            if (gp >= mem_lo && gp + 16 <= mem_hi)
+                                                cp_async_16(smem + s0 + c * 16, gp);
+                                            else
+                                                for (int b = 0; b < 16; ++b)
+                                                    smem[s0 + c * 16 + b] = (gp + b >= mem_lo && gp + b < mem_hi) ? __ldg(gp + b) : (uint8_t)0;
+                                        }
+                                }
+                                cp_async_commit();
+                            };
+                            const int ngroups = (K + R - 1) / R;
+                            if (ngroups > 0)
+                                issue(0);
+                            for (int g = 0; g < ngroups; ++g)
+                            {
+                                cp_async_wait_all();
+                                __syncthreads(); // group g is in shared memory for every thread; group g - 1 has been consumed
+                                if (g + 1 < ngroups)
+                                    issue(g + 1); // into the buffer group g - 1 used; lands while group g is processed
+                                if (active)
+                                {
+                                    const int k_end = min((g + 1) * R, K);
+    #pragma unroll 2
+                                    for (int k = g * R; k < k_end; ++k)
+                                    {
+                                        h_prev = h_cur;
+                                        h_cur  = hpass_shared<PIX>(smem, rowaddr[k] + off, aw);
+                                        emit_ready(k);
+                                    }
+                                }
+                            }
+                        }
+                        else if (active)
+                        {
+                            // a single source row of this block does not fit the staging buffer: taps straight from global memory
+                            for (int k = 0; k < K; ++k)
+                            {
+                                h_prev = h_cur;
+                                h_cur  = hpass_global<PIX>(reinterpret_cast<const uint8_t*>(rowsrc[k]) + off, aw);
+                                emit_ready(k);
+                            }
+                        }
+                        __syncthreads(); // the next column block (or record) rewrites blk_cols, the row tables and the staging buffers
                     }
                 }
 
                 // ---- per-image channel means for contrast, exchanged across the cluster
                 if (use_ctr)
                 {
-                    sum0 = warp_sum(sum0);
-                    sum1 = warp_sum(sum1);
-                    sum2 = warp_sum(sum2);
+                    sum_b = warp_sum(sum_b);
+                    sum_g = warp_sum(sum_g);
+                    sum_r = warp_sum(sum_r);
                     if (lane == 0)
                     {
-                        atomicAdd(&part_sum[0], sum0);
-                        atomicAdd(&part_sum[1], sum1);
-                        atomicAdd(&part_sum[2], sum2);
+                        atomicAdd(&part_sum[swap_rb ? 2 : 0], sum_b);
+                        atomicAdd(&part_sum[1], sum_g);
+                        atomicAdd(&part_sum[swap_rb ? 0 : 2], sum_r);
                     }
                     cluster.sync(); // all partial sums of the record are in place (also a CTA barrier)
                     if (tid < 3)
@@ -518,68 +763,44 @@ namespace aeonb
                     }
                     cluster.sync(); // remote reads done before any CTA of the cluster may exit
                 }
-                else
-                {
-                    __syncthreads();
-                }
 
                 // ---- value map: contrast, lighting, conversion, standardisation
-                for (int i = tid; i < 768; i += AUG_THREADS)
+                // (8-bit output without contrast or lighting is the identity: the store loop then skips the lookup)
+                const bool identity = sizeof(T) == 1 && !use_ctr && !d.lighting_enable && lay.dtype == AEONB_U8;
+                if (!identity)
                 {
-                    const int c   = i >> 8;
-                    const int cin = swap_rb ? 2 - c : c; // channel index in BGR order
-                    lut[c][i & 255] = final_value<T>(i & 255, c, cin, d, lay, use_ctr, use_ctr ? contrast_add[c] : 0.f);
-                }
-                __syncthreads();
-
-                // ---- store: a warp takes one (channel, row) line at a time, lanes take 16-byte chunks
-                {
-                    constexpr int VEC    = out_vec<T>::N;
-                    const int     rows   = row_end - row0;
-                    const int     chunks = (lay.slot_w + VEC - 1) / VEC;
-                    T*            dst    = reinterpret_cast<T*>(d.dst);
-                    const T       zero   = convert_out<T>(0);
-                    for (int line = warp; line < lay.channels * rows; line += WARPS) // 1 channel: the B plane of a grey picture
+                    for (int i = tid; i < 768; i += nt)
                     {
-                        const int  c      = (line >= rows) + (line >= 2 * rows);
-                        const int  r      = line - c * rows;
-                        const int  y      = row0 + r;
-                        const bool row_in = y < out_h;
-                        const unsigned char* src = tile + c * plane + r * pitch;
-                        T*                   g0  = dst + (int64_t)c * lay.stride_c + (int64_t)y * lay.stride_y;
-                        for (int chunk = lane; chunk < chunks; chunk += 32)
-                        {
-                            const int  x0 = chunk * VEC;
-                            out_vec<T> o;
-                            if (VEC == 4)
-                            {
-                                const uint32_t v4 = *reinterpret_cast<const uint32_t*>(src + x0);
-    #pragma unroll
-                                for (int k = 0; k < VEC; ++k)
-                                    o.v[k] = (row_in && x0 + k < out_w) ? lut[c][(v4 >> (8 * k)) & 0xFF] : zero;
-                            }
-                            else
-                            {
-    #pragma unroll
-                                for (int k = 0; k < VEC; ++k)
-                                    o.v[k] = (row_in && x0 + k < out_w) ? lut[c][src[x0 + k]] : zero;
-                            }
-                            T* g = g0 + (int64_t)x0 * lay.stride_x;
-                            if (L.vector_ok && x0 + VEC <= lay.slot_w)
-                                *reinterpret_cast<int4*>(g) = *reinterpret_cast<const int4*>(o.v);
-                            else
-                                for (int k = 0; k < VEC && x0 + k < lay.slot_w; ++k)
-                                    g[(int64_t)k * lay.stride_x] = o.v[k];
-                        }
+                        const int c   = i >> 8;
+                        const int cin = swap_rb ? 2 - c : c; // channel index in BGR order
+                        lut[c][i & 255] = final_value<T>(i & 255, c, cin, d, lay, use_ctr, use_ctr ? contrast_add[c] : 0.f);
                     }
                 }
-        
+                __syncthreads(); // tile and value map complete
+
+                // ---- store
+                {
+                    store_args<T> A;
+                    A.smem = smem, A.lut = &lut[0][0], A.dst = reinterpret_cast<T*>(d.dst);
+                    A.rows = row_end - row0, A.row0 = row0, A.out_w = out_w, A.out_h = out_h, A.slot_w = lay.slot_w;
+                    A.channels = lay.channels, A.pitch = pitch, A.plane = plane, A.vec_ok = L.vector_ok != 0;
+                    A.sc = lay.stride_c, A.sy = lay.stride_y, A.sx = lay.stride_x;
+                    const bool whole = out_w == lay.slot_w && img_end == row_end; // no zero margin in this band
+                    if (identity)
+                        store_band<T, true, true>(A, tid, nt);
+                    else if (whole)
+                        store_band<T, true, false>(A, tid, nt);
+                    else
+                        store_band<T, false, false>(A, tid, nt);
+                }
+
                 __syncthreads(); // the next record reuses the descriptor, the tables and the tile
             }
         }
 
         template <typename T>
-        cudaError_t launch_typed(const aug_launch& L, int clusters, int bands, int cluster_size, size_t smem, int pix, cudaStream_t stream)
+        cudaError_t launch_typed(const aug_launch& L, int clusters, int bands, int cluster_size, int threads, size_t smem, int pix,
+                                 cudaStream_t stream)
         {
             auto kern = pix == 4 ? aug_pack_kernel<T, 4> : aug_pack_kernel<T, 3>;
             cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -587,7 +808,7 @@ namespace aeonb
                 return err;
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim            = dim3(bands, clusters, 1);
-            cfg.blockDim           = dim3(AUG_THREADS, 1, 1);
+            cfg.blockDim           = dim3(threads, 1, 1);
             cfg.dynamicSmemBytes   = smem;
             cfg.stream             = stream;
             cudaLaunchAttribute attr[1];
@@ -601,20 +822,38 @@ namespace aeonb
         }
     }
 
-    // Host entry used by the C ABI: `descs_dev` is the device copy of the descriptors.
+    // Host entry used by the C ABI: `descs_dev` is the device copy of the descriptors `descs_host`.
     // Returns a CUDA error; *why is set for configurations the kernel does not cover.
-    cudaError_t launch_aug_pack(const aeonb_image_desc* descs_dev, int n, const aeonb_image_layout& layout, int pixel_stride,
-                                bool slots_aligned, bool any_contrast, cudaStream_t stream, const char** why)
+    cudaError_t launch_aug_pack(const aeonb_image_desc* descs_dev, const aeonb_image_desc* descs_host, int n,
+                                const aeonb_image_layout& layout, int pixel_stride, bool slots_aligned, cudaStream_t stream,
+                                const char** why)
     {
         *why = nullptr;
+        bool any_contrast = false;
+        int  max_cols     = 1; // widest stretch of source columns any record reads
+        for (int i = 0; i < n; ++i)
+        {
+            const aeonb_image_desc& r = descs_host[i];
+            any_contrast |= r.contrast != 1.0f;
+            if (r.src)
+                max_cols = std::max(max_cols, std::min(r.crop_w, r.src_w));
+        }
         int bands = 1;
         while (bands < AUG_MAX_BAND && layout.slot_h / (bands * 2) >= 8)
             bands *= 2;
         aug_launch L;
         L.tile_pitch = (layout.slot_w + 15) / 16 * 16;
+        // One thread per output column; wider outputs are cut into equal column blocks.
+        const int col_blocks = (layout.slot_w + AUG_MAX_THREADS - 1) / AUG_MAX_THREADS;
+        const int threads    = std::min(AUG_MAX_THREADS, std::max(64, ((layout.slot_w + col_blocks - 1) / col_blocks + 31) / 32 * 32));
+        // Staging: two buffers of up to 8 source rows of the widest crop (a column block of a wide output reads a part
+        // of the row only), at most 16 KB each; a record whose rows are longer stages fewer rows per group.
+        const int row_bytes = std::min(max_cols, (max_cols + col_blocks - 1) / col_blocks + 2) * pixel_stride + 30 + 2 * AUG_STAGE_PAD;
+        L.stage_bytes       = std::min(2 * 8 * ((row_bytes + 15) & ~15), 16 * 1024);
         auto smem_for = [&](int nb) {
             const int rows = (layout.slot_h + nb - 1) / nb;
-            return (size_t)3 * rows * L.tile_pitch + (size_t)layout.slot_w * (sizeof(int2) + sizeof(short2)) + (size_t)rows * sizeof(row_tap) + 16;
+            size_t    s    = (size_t)3 * rows * L.tile_pitch + (size_t)rows * 56 + 16; // tile + the row tables of the kernel
+            return ((s + 15) & ~(size_t)15) + L.stage_bytes;
         };
         // A band has to fit the shared memory of one CTA.  Up to AUG_MAX_BAND bands form one cluster, which is what the
         // contrast step needs (the per-image mean travels through distributed shared memory).  Larger outputs (a
@@ -643,18 +882,18 @@ namespace aeonb
         }
         const int cluster_size = bands <= AUG_MAX_BAND ? bands : 1;
         // One cluster per record.  (The kernel can also run as fewer, persistent clusters that loop over records;
-        // measured on B200 that was slower -- 0.228 ms against 0.181 ms for 256 records -- because records differ in
-        // cost and the hardware's own dispatch balances them better than a static round-robin.)
+        // measured on B200 that was slower because records differ in cost and the hardware's own dispatch balances
+        // them better than a static round-robin.)
         const int clusters = n;
         switch (layout.dtype)
         {
-        case AEONB_U8: return launch_typed<uint8_t>(L, clusters, bands, cluster_size, smem, pixel_stride, stream);
-        case AEONB_I8: return launch_typed<int8_t>(L, clusters, bands, cluster_size, smem, pixel_stride, stream);
-        case AEONB_I16: return launch_typed<int16_t>(L, clusters, bands, cluster_size, smem, pixel_stride, stream);
-        case AEONB_U16: return launch_typed<uint16_t>(L, clusters, bands, cluster_size, smem, pixel_stride, stream);
-        case AEONB_I32: return launch_typed<int32_t>(L, clusters, bands, cluster_size, smem, pixel_stride, stream);
-        case AEONB_F32: return launch_typed<float>(L, clusters, bands, cluster_size, smem, pixel_stride, stream);
-        case AEONB_F64: return launch_typed<double>(L, clusters, bands, cluster_size, smem, pixel_stride, stream);
+        case AEONB_U8: return launch_typed<uint8_t>(L, clusters, bands, cluster_size, threads, smem, pixel_stride, stream);
+        case AEONB_I8: return launch_typed<int8_t>(L, clusters, bands, cluster_size, threads, smem, pixel_stride, stream);
+        case AEONB_I16: return launch_typed<int16_t>(L, clusters, bands, cluster_size, threads, smem, pixel_stride, stream);
+        case AEONB_U16: return launch_typed<uint16_t>(L, clusters, bands, cluster_size, threads, smem, pixel_stride, stream);
+        case AEONB_I32: return launch_typed<int32_t>(L, clusters, bands, cluster_size, threads, smem, pixel_stride, stream);
+        case AEONB_F32: return launch_typed<float>(L, clusters, bands, cluster_size, threads, smem, pixel_stride, stream);
+        case AEONB_F64: return launch_typed<double>(L, clusters, bands, cluster_size, threads, smem, pixel_stride, stream);
         }
         *why = "unknown output dtype";
         return cudaErrorInvalidValue;
@@ -730,10 +969,7 @@ extern "C" int aeonb_image_batch_noalloc(const aeonb_image_desc* descs, int n, c
         // Every descriptor the kernel reads is overwritten here, so nothing of the previous call survives.
         AEONB_CUDA(cudaMemcpyAsync(scratch, descs, sizeof(aeonb_image_desc) * n, cudaMemcpyHostToDevice, st));
         const char* why = nullptr;
-        bool any_contrast = false;
-        for (int i = 0; i < n; ++i)
-            any_contrast |= descs[i].contrast != 1.0f;
-        cudaError_t e   = launch_aug_pack(scratch, n, *layout, pixel_stride, aligned, any_contrast, st, &why);
+        cudaError_t e   = launch_aug_pack(scratch, descs, n, *layout, pixel_stride, aligned, st, &why);
         if (why)
             throw error(AEONB_ERR_UNSUPPORTED, why);
         if (e != cudaSuccess)

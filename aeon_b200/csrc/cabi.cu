@@ -229,12 +229,15 @@ int aeonb_image_batch(aeonb_ctx* ctx, const aeonb_image_desc* descs, int n, cons
         bool aligned;
         check_image_batch(descs, n, *layout, pixel_stride, aligned);
         AEONB_CUDA(cudaSetDevice(ctx->device));
-        auto* dev = static_cast<const aeonb_image_desc*>(ctx->upload(descs, sizeof(aeonb_image_desc) * n));
+        // Launch order: the kernel's blocks start in descriptor order and the launch ends with its last block, so the
+        // records with the most source rows to filter go first and the cheap ones fill the tail.  Every descriptor
+        // carries its own destination, so the order is free.
+        std::vector<aeonb_image_desc> ordered(descs, descs + n);
+        auto cost = [](const aeonb_image_desc& r) { return r.src ? std::min(r.crop_h, 2 * r.out_h) : 0; };
+        std::stable_sort(ordered.begin(), ordered.end(), [&](const aeonb_image_desc& a, const aeonb_image_desc& b) { return cost(a) > cost(b); });
+        auto* dev = static_cast<const aeonb_image_desc*>(ctx->upload(ordered.data(), sizeof(aeonb_image_desc) * n));
         const char* why = nullptr;
-        bool any_contrast = false;
-        for (int i = 0; i < n; ++i)
-            any_contrast |= descs[i].contrast != 1.0f;
-        cudaError_t e   = launch_aug_pack(dev, n, *layout, pixel_stride, aligned, any_contrast, ctx->stream, &why);
+        cudaError_t e   = launch_aug_pack(dev, ordered.data(), n, *layout, pixel_stride, aligned, ctx->stream, &why);
         if (why)
             throw error(AEONB_ERR_UNSUPPORTED, why);
         if (e != cudaSuccess)

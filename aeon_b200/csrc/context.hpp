@@ -88,8 +88,9 @@ namespace aeonb
     void check_image_batch(const aeonb_image_desc* d, int n, const aeonb_image_layout& L, int& pixel_stride, bool& aligned);
 
     // Kernel launchers (defined next to the kernels).
-    cudaError_t launch_aug_pack(const aeonb_image_desc* descs_dev, int n, const aeonb_image_layout& layout, int pixel_stride,
-                                bool slots_aligned, bool any_contrast, cudaStream_t stream, const char** why);
+    cudaError_t launch_aug_pack(const aeonb_image_desc* descs_dev, const aeonb_image_desc* descs_host, int n,
+                                const aeonb_image_layout& layout, int pixel_stride, bool slots_aligned, cudaStream_t stream,
+                                const char** why);
     cudaError_t launch_jpeg_backend(const aeonb_jpeg_desc* descs_dev, const int2* work_dev, int n_work, size_t smem,
                                     cudaStream_t stream);
     size_t      jpeg_backend_smem(const aeonb_jpeg_desc& d);
