@@ -2,22 +2,22 @@
 //
 // One launch transforms a whole batch.  A record is handled by a thread-block cluster of
 // `bands` CTAs; CTA b owns a band of output rows, one thread per output column.  Each CTA
-//   1. builds the vertical tap table of the crop->output resize (the 11-bit fixed-point form
-//      cv::resize(INTER_LINEAR) uses for 8-bit images) and the list of distinct source rows
-//      its band touches; every thread keeps the horizontal taps of its column in registers,
-//   2. stages those source rows -- only the columns the band reads -- into shared memory with
-//      16-byte cp.async copies, double-buffered in groups of rows so that the copies of the
-//      next group run under the arithmetic of the current one,
+//   1. builds its tables in one phase: warp 0 the vertical taps of the crop->output resize (the
+//      11-bit fixed-point form cv::resize(INTER_LINEAR) uses for 8-bit images) and the list of
+//      source rows the band touches, every thread the horizontal taps of its column (registers),
+//   2. stages the listed source rows -- only the columns the band reads -- into shared memory
+//      with 16-byte cp.async copies, double-buffered in groups of rows so that the copies of the
+//      next group run under the arithmetic of the current one (one barrier per group),
 //   3. runs the horizontal pass ONCE per staged source row (two dot products per channel out
-//      of three aligned shared-memory words), keeps the last two horizontal results in
-//      registers and emits every output row whose taps are complete: vertical pass, colour
-//      matrix, HSV hue shift; the band is kept as planar uint8 in shared memory, already
-//      flipped and in output channel order,
+//      of three aligned shared-memory words, fetched one row ahead), keeps the last two
+//      horizontal results in registers and emits every output row whose taps are complete:
+//      vertical pass, colour matrix, HSV hue shift; the band is kept as planar uint8 in shared
+//      memory, already flipped and in output channel order,
 //   4. if contrast is active, reduces per-channel sums (warp shuffles, then shared memory)
-//      and exchanges the partial sums with the other CTAs of the cluster through
-//      distributed shared memory, so the per-image mean never touches global memory,
+//      and adds them into every CTA of the cluster through distributed shared memory, so the
+//      per-image mean never touches global memory,
 //   5. applies contrast and lighting, converts to the output type, standardises and
-//      streams the band out with 128-bit stores, several in flight per thread.
+//      streams the band out with 128-bit stores, two in flight per thread.
 //
 // Pixels outside the source picture (expand canvas, padding) are never read: their taps get
 // weight zero, which gives the same sums as a zero pixel.
@@ -256,19 +256,32 @@ namespace aeonb
             int b, g, r;
         };
 
-        // `at` = byte offset in shared memory of tap 0 of the column in the staged row.  The six (PIX 3) or eight
-        // (PIX 4) bytes of the two taps are cut out of the aligned words around them.
-        template <int PIX>
-        __device__ __forceinline__ hrow hpass_shared(const unsigned char* smem, int at, unsigned aw)
+        // The staged bytes around the two taps of a column: `at` = byte offset in shared memory of tap 0.  Six (PIX 3)
+        // or eight (PIX 4) bytes are needed; the aligned words around them are fetched and cut later.
+        struct tap_words
         {
-            const uint32_t* p  = reinterpret_cast<const uint32_t*>(smem + (at & ~3));
-            uint32_t        lo = p[0], hi = p[1];
+            uint32_t w0, w1, w2;
+            int      sh;
+        };
+        template <int PIX>
+        __device__ __forceinline__ tap_words load_taps(const unsigned char* smem, int at)
+        {
+            const uint32_t* p = reinterpret_cast<const uint32_t*>(smem + (at & ~3));
+            tap_words       t;
+            t.w0 = p[0];
+            t.w1 = p[1];
+            t.w2 = PIX == 3 ? p[2] : 0u;
+            t.sh = at << 3; // the funnel shift takes the amount modulo 32
+            return t;
+        }
+        template <int PIX>
+        __device__ __forceinline__ hrow hpass_words(const tap_words& t, unsigned aw)
+        {
+            uint32_t lo = t.w0, hi = t.w1;
             if (PIX == 3)
             {
-                const uint32_t w2 = p[2];
-                const int      sh = at << 3; // the funnel shift takes the amount modulo 32
-                lo                = __funnelshift_r(lo, hi, sh);
-                hi                = __funnelshift_r(hi, w2, sh);
+                lo = __funnelshift_r(t.w0, t.w1, t.sh);
+                hi = __funnelshift_r(t.w1, t.w2, t.sh);
             }
             // byte pairs (tap 0, tap 1) of each channel in the low half of a word
             const unsigned pb = __byte_perm(lo, hi, PIX == 3 ? 0x0030 : 0x0040);
@@ -406,14 +419,15 @@ namespace aeonb
             //   tile     [3][rows_per_band][pitch]   the band, planar uint8, output channel order
             //   ytab     int4[rows_per_band + 1]     per output row: k1 (position of tap 1 in the source row list; tap 0 is
             //                                        the entry before it), unused, b0, b1; a last entry with k1 = -1 ends it
-            //   rowsrc   uint64[2 rows_per_band]     per listed source row: global address of its first staged byte
             //   ysrc     int2[rows_per_band]         source rows of the two taps
             //   srow     int[2 rows_per_band]        the source rows of the band in the order of the horizontal pass
             //   rowaddr  int[2 rows_per_band]        per listed source row: offset of its first staged byte in shared memory
             //   stage    two buffers of staged source rows
             extern __shared__ __align__(16) unsigned char smem[];
             __shared__ aeonb_image_desc d;
-            __shared__ unsigned int     part_sum[3];  // this CTA's per-channel sums (output channel order)
+            __shared__ unsigned int     part_sum[3];  // per-channel sums of the whole picture (output channel order); every
+                                                      // CTA of the cluster adds its band's sums into every CTA's copy
+            __shared__ unsigned int     cta_sum[3];   // this band's sums
             __shared__ float            contrast_add[3];
             __shared__ hue_tables       hue_tab;
             __shared__ T                lut[3][256];
@@ -434,12 +448,11 @@ namespace aeonb
             const int         pitch   = L.tile_pitch;
             const int         plane   = RPB * pitch;
 
-            int4*               ytab    = reinterpret_cast<int4*>(smem + 3 * plane);
-            unsigned long long* rowsrc  = reinterpret_cast<unsigned long long*>(ytab + RPB + 1);
-            int2*               ysrc    = reinterpret_cast<int2*>(rowsrc + 2 * RPB);
-            int*                srow    = reinterpret_cast<int*>(ysrc + RPB);
-            int*                rowaddr = srow + 2 * RPB;
-            const int           off_stage = (3 * plane + 56 * RPB + 16 + 15) & ~15;
+            int4*     ytab      = reinterpret_cast<int4*>(smem + 3 * plane);
+            int2*     ysrc      = reinterpret_cast<int2*>(ytab + RPB + 1);
+            int*      srow      = reinterpret_cast<int*>(ysrc + RPB);
+            int*      rowaddr   = srow + 2 * RPB;
+            const int off_stage = (3 * plane + 40 * RPB + 16 + 15) & ~15;
 
             // A cluster takes records rec, rec + gridDim.y, ...; the launcher starts one cluster per record.
             for (int rec = blockIdx.y; rec < L.n; rec += gridDim.y)
@@ -451,7 +464,7 @@ namespace aeonb
                     for (int i = tid; i < (int)(sizeof(aeonb_image_desc) / sizeof(int)); i += nt)
                         s[i] = g[i];
                     if (tid < 3)
-                        part_sum[tid] = 0;
+                        part_sum[tid] = cta_sum[tid] = 0;
                     if (tid == 32 % nt) // the two scale factors of the resize, once per CTA (two double divisions each)
                     {
                         const aeonb_image_desc& gd = L.descs[rec];
@@ -471,35 +484,119 @@ namespace aeonb
                 const bool use_ctr  = d.contrast != 1.0f;
                 const bool swap_rb  = lay.bgr_to_rgb != 0;
                 const bool linear   = d.interp == AEONB_INTERP_LINEAR;
+                const bool flip     = d.flip != 0;
+                const int  src_w    = d.src_w;
+                // The contrast step needs the sums of all bands.  This first arrival says "my part_sum is cleared"; the
+                // matching wait comes right before the band's sums are sent, long after every CTA has got here.
+                if (use_ctr)
+                    cluster.barrier_arrive();
 
-                // ---- vertical taps: source rows (clamped into the picture, weight zero when off it) and weights
-                for (int r = tid; r < nrows; r += nt)
-                {
-                    int   y0, y1;
-                    short b0 = 2048, b1 = 0;
-                    if (linear)
+                // horizontal taps of this thread's column in the column block starting at xb
+                int   sx0 = 0;
+                short a0 = 2048, a1 = 0;
+                auto  column_taps = [&](int xb) {
+                    const int x = xb + tid;
+                    sx0 = 0, a0 = 2048, a1 = 0;
+                    if (x < out_w)
                     {
                         int s;
-                        linear_tap(row0 + r, d.crop_h, tap_scale[1], false, s, b0, b1);
-                        y0 = min(max(s, 0), d.crop_h - 1);
-                        y1 = min(max(s + 1, 0), d.crop_h - 1);
+                        if (linear)
+                            linear_tap(x, d.crop_w, tap_scale[0], true, s, a0, a1);
+                        else
+                            s = nearest_tap(x, d.crop_w, tap_scale[0]);
+                        sx0 = d.crop_x + s - d.canvas_x;
+                        if (tid == 0)
+                            blk_cols[0] = sx0;
+                        if (x == min(xb + nt, out_w) - 1)
+                            blk_cols[1] = sx0;
                     }
-                    else
-                        y0 = y1 = nearest_tap(row0 + r, d.crop_h, tap_scale[1]);
-                    int sy0 = d.crop_y + y0 - d.canvas_y, sy1 = d.crop_y + y1 - d.canvas_y;
-                    if ((unsigned)sy0 >= (unsigned)d.src_h)
+                };
+
+                // ---- tables.  Warp 0: vertical taps, then the list of source rows; meanwhile every thread: its horizontal taps.
+                if (warp == 0)
+                {
+                    // source rows (clamped into the picture, weight zero when off it) and weights
+                    for (int r = lane; r < nrows; r += 32)
                     {
-                        b0  = 0;
-                        sy0 = min(max(sy0, 0), d.src_h - 1);
+                        int   y0, y1;
+                        short b0 = 2048, b1 = 0;
+                        if (linear)
+                        {
+                            int s;
+                            linear_tap(row0 + r, d.crop_h, tap_scale[1], false, s, b0, b1);
+                            y0 = min(max(s, 0), d.crop_h - 1);
+                            y1 = min(max(s + 1, 0), d.crop_h - 1);
+                        }
+                        else
+                            y0 = y1 = nearest_tap(row0 + r, d.crop_h, tap_scale[1]);
+                        int sy0 = d.crop_y + y0 - d.canvas_y, sy1 = d.crop_y + y1 - d.canvas_y;
+                        if ((unsigned)sy0 >= (unsigned)d.src_h)
+                        {
+                            b0  = 0;
+                            sy0 = min(max(sy0, 0), d.src_h - 1);
+                        }
+                        if ((unsigned)sy1 >= (unsigned)d.src_h)
+                        {
+                            b1  = 0;
+                            sy1 = min(max(sy1, 0), d.src_h - 1);
+                        }
+                        ysrc[r] = make_int2(sy0, sy1);
+                        ytab[r] = make_int4(0, 0, b0, b1);
                     }
-                    if ((unsigned)sy1 >= (unsigned)d.src_h)
+                    __syncwarp();
+                    // Source rows of the band in the order the horizontal pass takes them, such that every output row finds
+                    // its tap 1 at some position k1 and its tap 0 right before it.  A row whose taps coincide (clamped at the
+                    // picture's edge, or nearest) needs one listed row when a weight is zero -- the weight then moves to tap 1
+                    // -- and the same row listed twice otherwise.
+                    if (lane == 0)
                     {
-                        b1  = 0;
-                        sy1 = min(max(sy1, 0), d.src_h - 1);
+                        int K = 0;
+                        for (int r = 0; r < nrows; ++r)
+                        {
+                            const int2 y = ysrc[r];
+                            int4       t = ytab[r];
+                            if (y.x != y.y)
+                            {
+                                if (K >= 2 && srow[K - 1] == y.y && srow[K - 2] == y.x)
+                                    ;
+                                else if (K >= 1 && srow[K - 1] == y.x)
+                                    srow[K++] = y.y;
+                                else
+                                {
+                                    srow[K++] = y.x;
+                                    srow[K++] = y.y;
+                                }
+                            }
+                            else if (t.z == 0 || t.w == 0)
+                            {
+                                if (t.w == 0)
+                                {
+                                    t.w = t.z;
+                                    t.z = 0;
+                                }
+                                if (!(K >= 1 && srow[K - 1] == y.x))
+                                    srow[K++] = y.x;
+                            }
+                            else
+                            {
+                                if (K >= 2 && srow[K - 1] == y.x && srow[K - 2] == y.x)
+                                    ;
+                                else if (K >= 1 && srow[K - 1] == y.x)
+                                    srow[K++] = y.x;
+                                else
+                                {
+                                    srow[K++] = y.x;
+                                    srow[K++] = y.x;
+                                }
+                            }
+                            t.x     = K - 1;
+                            ytab[r] = t;
+                        }
+                        ytab[nrows] = make_int4(-1, 0, 0, 0);
+                        n_src_rows  = K;
                     }
-                    ysrc[r] = make_int2(sy0, sy1);
-                    ytab[r] = make_int4(0, 0, b0, b1);
                 }
+                column_taps(0);
                 if (use_hue)
                     build_hue_tables(hue_tab, d.hue, tid, nt);
                 // the slot may be larger than the image: clear what the spatial stage will not write
@@ -507,117 +604,40 @@ namespace aeonb
                     for (int i = tid; i < 3 * plane / 16; i += nt)
                         reinterpret_cast<int4*>(smem)[i] = make_int4(0, 0, 0, 0);
                 __syncthreads();
-                // Source rows of the band in the order the horizontal pass takes them, such that every output row finds
-                // its tap 1 at some position k1 and its tap 0 right before it.  A row whose taps coincide (clamped at the
-                // picture's edge, or nearest) needs one listed row when a weight is zero -- the weight then moves to tap 1
-                // -- and the same row listed twice otherwise.
-                if (tid == 0)
-                {
-                    int K = 0;
-                    for (int r = 0; r < nrows; ++r)
-                    {
-                        const int2 y = ysrc[r];
-                        int4       t = ytab[r];
-                        if (y.x != y.y)
-                        {
-                            if (K >= 2 && srow[K - 1] == y.y && srow[K - 2] == y.x)
-                                ;
-                            else if (K >= 1 && srow[K - 1] == y.x)
-                                srow[K++] = y.y;
-                            else
-                            {
-                                srow[K++] = y.x;
-                                srow[K++] = y.y;
-                            }
-                        }
-                        else if (t.z == 0 || t.w == 0)
-                        {
-                            if (t.w == 0)
-                            {
-                                t.w = t.z;
-                                t.z = 0;
-                            }
-                            if (!(K >= 1 && srow[K - 1] == y.x))
-                                srow[K++] = y.x;
-                        }
-                        else
-                        {
-                            if (K >= 2 && srow[K - 1] == y.x && srow[K - 2] == y.x)
-                                ;
-                            else if (K >= 1 && srow[K - 1] == y.x)
-                                srow[K++] = y.x;
-                            else
-                            {
-                                srow[K++] = y.x;
-                                srow[K++] = y.x;
-                            }
-                        }
-                        t.x     = K - 1;
-                        ytab[r] = t;
-                    }
-                    ytab[nrows] = make_int4(-1, 0, 0, 0);
-                    n_src_rows  = K;
-                }
-                __syncthreads();
 
-                // ---- resize + per-pixel photometric into the tile; a thread owns one output column of the band
+                // ---- resize + per-pixel photometric stages into the tile; a thread owns one output column of the band
                 unsigned int sum_b = 0, sum_g = 0, sum_r = 0;
                 {
-                    const int K = n_src_rows;
                     // Record constants live in shared memory; byte stores into the tile could alias them, so the
                     // ones the pixel loop needs are copied to registers once.
-                    const int      src_pitch    = d.src_pitch;
-                    const int      src_w        = d.src_w;
-                    const uint8_t* src          = d.src;
-                    const int      color_enable = d.color_enable;
-                    const float    cs0 = d.color_scale[0], cs1 = d.color_scale[1], cs2 = d.color_scale[2];
-                    const int      m0 = d.color_matrix[0], m1 = d.color_matrix[1], m2 = d.color_matrix[2], m3 = d.color_matrix[3],
-                                   m4 = d.color_matrix[4], m5 = d.color_matrix[5], m6 = d.color_matrix[6], m7 = d.color_matrix[7],
-                                   m8 = d.color_matrix[8];
-                    const int      hsv_cols = d.hsv_vector_cols;
-                    const bool     flip     = d.flip != 0;
+                    const int   color_enable = d.color_enable;
+                    const float cs0 = d.color_scale[0], cs1 = d.color_scale[1], cs2 = d.color_scale[2];
+                    const int   m0 = d.color_matrix[0], m1 = d.color_matrix[1], m2 = d.color_matrix[2], m3 = d.color_matrix[3],
+                                m4 = d.color_matrix[4], m5 = d.color_matrix[5], m6 = d.color_matrix[6], m7 = d.color_matrix[7],
+                                m8 = d.color_matrix[8];
+                    const int   hsv_cols = d.hsv_vector_cols;
+                    const int      K         = n_src_rows;
+                    const int      src_pitch = d.src_pitch;
+                    const uint8_t* src       = d.src;
                     // the picture's bytes: a staged 16-byte group that is not wholly inside is fetched byte by byte
                     const uint8_t* mem_lo = src;
                     const uint8_t* mem_hi = src + (ptrdiff_t)(d.src_h - 1) * src_pitch + (ptrdiff_t)src_w * PIX;
 
                     for (int xb = 0; xb < out_w; xb += nt)
                     {
+                        if (xb > 0)
+                        {
+                            column_taps(xb);
+                            __syncthreads();
+                        }
                         const int  x      = xb + tid;
                         const bool active = x < out_w;
-                        int        sx0    = 0;
-                        short      a0 = 2048, a1 = 0;
-                        if (active)
-                        {
-                            int s;
-                            if (linear)
-                                linear_tap(x, d.crop_w, tap_scale[0], true, s, a0, a1);
-                            else
-                                s = nearest_tap(x, d.crop_w, tap_scale[0]);
-                            sx0 = d.crop_x + s - d.canvas_x;
-                            if (tid == 0)
-                                blk_cols[0] = sx0;
-                            if (x == min(xb + nt, out_w) - 1)
-                                blk_cols[1] = sx0;
-                        }
-                        __syncthreads();
                         // columns staged for this block: the taps of its first to last column, cut to the picture
                         const int bsa  = min(max(blk_cols[0], 0), src_w);
                         const int bsb  = max(min(blk_cols[1] + 2, src_w), bsa);
                         const int span = (bsb - bsa) * PIX;
                         const int stage_pitch = ((span + 30) & ~15) + 2 * AUG_STAGE_PAD; // room for a lead of up to 15 bytes
                         const int R = min(AUG_MAX_GROUP, (L.stage_bytes / 2) / stage_pitch);
-                        // where each listed source row starts in global memory and where it is staged (group g = k / R
-                        // goes to buffer g & 1); the staged copy keeps the row's alignment modulo 16
-                        for (int k = tid; k < K; k += nt)
-                        {
-                            const uint8_t* first = src + (ptrdiff_t)srow[k] * src_pitch + (ptrdiff_t)bsa * PIX;
-                            rowsrc[k]            = (unsigned long long)first;
-                            if (R >= 1)
-                            {
-                                const int g = k / R;
-                                rowaddr[k]  = off_stage + ((g & 1) * R + (k - g * R)) * stage_pitch + AUG_STAGE_PAD + (int)((uintptr_t)first & 15);
-                            }
-                        }
                         if (a0 != 0 && (unsigned)sx0 >= (unsigned)src_w)
                             a0 = 0;
                         if (a1 != 0 && (unsigned)(sx0 + 1) >= (unsigned)src_w)
@@ -625,28 +645,26 @@ namespace aeonb
                         const unsigned aw  = (unsigned)(unsigned short)a0 | ((unsigned)(unsigned short)a1 << 16);
                         const int      sxc = min(max(sx0, bsa - 1), max(bsb - 1, bsa - 1)); // keeps both taps next to the staged bytes
                         const int      off = (sxc - bsa) * PIX;
+                        const int      xo_t = flip ? out_w - 1 - x : x;
                         const bool     truncate = x < hsv_cols;
-                        const int      xo_t     = flip ? out_w - 1 - x : x;
                         // tile positions of this column's B, G, R bytes (output channel order), stepped down a row per pixel
                         int tb = (swap_rb ? 2 * plane : 0) + xo_t, tg = plane + xo_t, tr = (swap_rb ? 0 : 2 * plane) + xo_t;
-                        __syncthreads(); // rowsrc / rowaddr are complete
 
                         hrow h_prev{0, 0, 0}, h_cur{0, 0, 0};
                         int  r   = 0;
                         int4 tap = ytab[0]; // taps of the next output row to emit
-                        // rows whose second tap is source row k are complete once that row's horizontal pass is done:
-                        // vertical pass, photometric stages, tile store
+                        // rows whose second tap is listed row k are complete once that row's horizontal pass is done
                         auto emit_ready = [&](int k) {
                             for (int guard = 0; guard <= nrows && tap.x == k; ++guard)
                             {
                                 const int b0 = tap.z, b1 = tap.w;
-                                bgr       px;
-                                // as in OpenCV's 8-bit path; with weights summing to 2048 the result stays in 0..255
-                                px.b = (((b0 * h_prev.b) >> 16) + ((b1 * h_cur.b) >> 16) + 2) >> 2;
-                                px.g = (((b0 * h_prev.g) >> 16) + ((b1 * h_cur.g) >> 16) + 2) >> 2;
-                                px.r = (((b0 * h_prev.r) >> 16) + ((b1 * h_cur.r) >> 16) + 2) >> 2;
+                                // vertical pass as in OpenCV's 8-bit path; with weights summing to 2048 the result stays in 0..255
+                                const int pb = (((b0 * h_prev.b) >> 16) + ((b1 * h_cur.b) >> 16) + 2) >> 2;
+                                const int pg = (((b0 * h_prev.g) >> 16) + ((b1 * h_cur.g) >> 16) + 2) >> 2;
+                                const int pr = (((b0 * h_prev.r) >> 16) + ((b1 * h_cur.r) >> 16) + 2) >> 2;
                                 ++r;
                                 tap = ytab[r];
+                                bgr px{pb, pg, pr};
                                 if (color_enable == 2)
                                 {
                                     px.b = clamp_u8(__float2int_rn((float)px.b * cs0));
@@ -678,16 +696,19 @@ namespace aeonb
 
                         if (R >= 1)
                         {
-                            // copies of group g (listed rows g*R ...); a warp takes a row, a lane 16 bytes at a time
+                            // copies of group g (listed rows g*R ...) into buffer g & 1; a warp takes a row, a lane 16 bytes at a
+                            // time; the staged copy keeps the row's alignment modulo 16
                             auto issue = [&](int g) {
                                 const int k_end = min((g + 1) * R, K);
                                 for (int k = g * R + warp; k < k_end; k += nwarps)
                                 {
-                                    const uint8_t* first = reinterpret_cast<const uint8_t*>(rowsrc[k]);
+                                    const uint8_t* first = src + (ptrdiff_t)srow[k] * src_pitch + (ptrdiff_t)bsa * PIX;
                                     const int      lead  = (int)((uintptr_t)first & 15);
                                     const uint8_t* g0    = first - lead;
-                                    const int      s0    = rowaddr[k] - lead;
+                                    const int      s0    = off_stage + ((g & 1) * R + (k - g * R)) * stage_pitch + AUG_STAGE_PAD;
                                     const int      nck   = span ? (lead + span + 15) >> 4 : 0;
+                                    if (lane == 0)
+                                        rowaddr[k] = s0 + lead;
                                     if (g0 >= mem_lo && g0 + nck * 16 <= mem_hi)
                                         for (int c = lane; c < nck; c += 32)
                                             cp_async_16(smem + s0 + c * 16, g0 + c * 16);
@@ -716,11 +737,15 @@ namespace aeonb
                                 if (active)
                                 {
                                     const int k_end = min((g + 1) * R, K);
-    #pragma unroll 2
+                                    // the words of the next row are fetched before the tile stores of this one
+                                    tap_words next = load_taps<PIX>(smem, rowaddr[g * R] + off);
                                     for (int k = g * R; k < k_end; ++k)
                                     {
+                                        const tap_words cur = next;
+                                        if (k + 1 < k_end)
+                                            next = load_taps<PIX>(smem, rowaddr[k + 1] + off);
                                         h_prev = h_cur;
-                                        h_cur  = hpass_shared<PIX>(smem, rowaddr[k] + off, aw);
+                                        h_cur  = hpass_words<PIX>(cur, aw);
                                         emit_ready(k);
                                     }
                                 }
@@ -732,15 +757,14 @@ namespace aeonb
                             for (int k = 0; k < K; ++k)
                             {
                                 h_prev = h_cur;
-                                h_cur  = hpass_global<PIX>(reinterpret_cast<const uint8_t*>(rowsrc[k]) + off, aw);
+                                h_cur  = hpass_global<PIX>(src + (ptrdiff_t)srow[k] * src_pitch + (ptrdiff_t)sxc * PIX, aw);
                                 emit_ready(k);
                             }
                         }
-                        __syncthreads(); // the next column block (or record) rewrites blk_cols, the row tables and the staging buffers
+                        __syncthreads(); // the band's pixels are in the tile; blk_cols, the row table and the staging buffers are free
                     }
                 }
 
-                // ---- per-image channel means for contrast, exchanged across the cluster
                 if (use_ctr)
                 {
                     sum_b = warp_sum(sum_b);
@@ -748,20 +772,30 @@ namespace aeonb
                     sum_r = warp_sum(sum_r);
                     if (lane == 0)
                     {
-                        atomicAdd(&part_sum[swap_rb ? 2 : 0], sum_b);
-                        atomicAdd(&part_sum[1], sum_g);
-                        atomicAdd(&part_sum[swap_rb ? 0 : 2], sum_r);
+                        atomicAdd(&cta_sum[swap_rb ? 2 : 0], sum_b);
+                        atomicAdd(&cta_sum[1], sum_g);
+                        atomicAdd(&cta_sum[swap_rb ? 0 : 2], sum_r);
                     }
-                    cluster.sync(); // all partial sums of the record are in place (also a CTA barrier)
+                }
+
+                // ---- per-image channel means for contrast: every CTA adds its sums into every CTA of the cluster through
+                // distributed shared memory, so the mean never touches global memory
+                if (use_ctr)
+                {
+                    __syncthreads();        // cta_sum complete
+                    cluster.barrier_wait(); // every CTA of the cluster has cleared its part_sum (arrival at the top)
+                    if (tid < 3 * bands)
+                    {
+                        const int peer = tid / 3, c = tid - 3 * peer;
+                        atomicAdd(cluster.map_shared_rank(&part_sum[c], peer), cta_sum[c]);
+                    }
+                    cluster.sync(); // all bands' sums have arrived here; nothing touches another CTA's memory afterwards
                     if (tid < 3)
                     {
-                        unsigned long long total = 0;
-                        for (int b = 0; b < bands; ++b)
-                            total += *cluster.map_shared_rank(&part_sum[tid], b);
-                        const double mean = (double)total / (double)((long long)out_w * out_h);
+                        const double mean = (double)part_sum[tid] / (double)((long long)out_w * out_h);
                         contrast_add[tid] = (float)((1.0 - (double)d.contrast) * mean);
                     }
-                    cluster.sync(); // remote reads done before any CTA of the cluster may exit
+                    __syncthreads();
                 }
 
                 // ---- value map: contrast, lighting, conversion, standardisation
@@ -852,7 +886,7 @@ namespace aeonb
         L.stage_bytes       = std::min(2 * 8 * ((row_bytes + 15) & ~15), 16 * 1024);
         auto smem_for = [&](int nb) {
             const int rows = (layout.slot_h + nb - 1) / nb;
-            size_t    s    = (size_t)3 * rows * L.tile_pitch + (size_t)rows * 56 + 16; // tile + the row tables of the kernel
+            size_t    s    = (size_t)3 * rows * L.tile_pitch + (size_t)rows * 40 + 16; // tile + the row tables of the kernel
             return ((s + 15) & ~(size_t)15) + L.stage_bytes;
         };
         // A band has to fit the shared memory of one CTA.  Up to AUG_MAX_BAND bands form one cluster, which is what the
