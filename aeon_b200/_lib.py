@@ -144,7 +144,6 @@ PROTOTYPES = {
     "aeonb_png_info": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "aeonb_png_decode_bgr": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t]),
     "aeonb_png_decode_grey": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t]),
-    "aeonb_selftest_worker_pool": (C.c_int64, [C.c_int, C.c_int]),
     "aeonb_rcnn_anchor_count": (C.c_int64, [C.POINTER(RcnnConfig)]),
     "aeonb_rcnn_anchors": (C.c_int, [C.POINTER(RcnnConfig), C.c_void_p]),
     "aeonb_rcnn_label_batch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(RcnnDesc), C.c_int, C.c_float, C.c_float]),
@@ -153,6 +152,10 @@ PROTOTYPES = {
     "aeonb_draw_ssd_params": (C.c_int, [C.c_char_p, C.c_uint32, C.c_int, C.c_int, C.POINTER(C.c_int32),
                                         C.POINTER(C.c_int32), C.c_int, C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_float),
                                         C.POINTER(C.c_double)]),
+    "aeonb_box_overlap": (C.c_int, [C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "aeonb_transform_boxes": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "aeonb_ssd_load_boxes": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "aeonb_image_desc_set_photometric": (C.c_int, [C.POINTER(ImageDesc), C.c_float, C.c_float, C.c_float, C.c_int,
                                                    C.POINTER(C.c_float), C.c_float]),
     "aeonb_provider_create": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p)]),
@@ -183,6 +186,11 @@ PROTOTYPES = {
     "aeonb_loader_position": (C.c_int, [C.c_void_p]),
 }
 
+# exported for the test suite only, not part of the public header
+TEST_HOOKS = {
+    "aeonb_selftest_worker_pool": (C.c_int64, [C.c_int, C.c_int]),
+}
+
 _lib = None
 MISSING = []  # declared in the header but absent from the built library (must stay empty)
 
@@ -203,7 +211,7 @@ def load():
     if not os.path.exists(LIB_PATH):
         raise ImportError("libaeon_b200.so is not built; run `python -m aeon_b200.build` (there is no CPU fallback)")
     lib = C.CDLL(LIB_PATH)
-    for name, (res, args) in PROTOTYPES.items():
+    for name, (res, args) in list(PROTOTYPES.items()) + list(TEST_HOOKS.items()):
         fn = getattr(lib, name, None)
         if fn is None:
             MISSING.append(name)

@@ -169,6 +169,50 @@ namespace aeonb
         return nbox(b.xmin / width, b.ymin / height, (b.xmax + 1) / width, (b.ymax + 1) / height);
     }
 
+    bbox bbox_intersect(const bbox& a, const bbox& b)
+    {
+        if (b.xmin > a.xmax || b.xmax < a.xmin || b.ymin > a.ymax || b.ymax < a.ymin)
+            return bbox();
+        bbox i;
+        i.xmin = max(a.xmin, b.xmin);
+        i.ymin = max(a.ymin, b.ymin);
+        i.xmax = min(a.xmax, b.xmax);
+        i.ymax = min(a.ymax, b.ymax);
+        return i;
+    }
+
+    float bbox_jaccard(const bbox& a, const bbox& b)
+    {
+        const float inter = bbox_intersect(a, b).size();
+        if (inter == 0.f)
+            return 0.f;
+        return inter / (a.size() + b.size() - inter);
+    }
+
+    float bbox_coverage(const bbox& a, const bbox& b)
+    {
+        const float inter = bbox_intersect(a, b).size();
+        return inter > 0 ? inter / a.size() : 0.f;
+    }
+
+    void ssd_fill_buffers(const vector<bbox>& gt, int width, int height, int max_gt_boxes, int32_t* image_shape, float* gt_boxes,
+                          int32_t* gt_box_count, int32_t* gt_class, int32_t* gt_difficult)
+    {
+        image_shape[0] = width;
+        image_shape[1] = height;
+        *gt_box_count  = std::min<int>(max_gt_boxes, (int)gt.size());
+        for (int i = 0; i < *gt_box_count; ++i)
+        {
+            const nbox nb = bbox_normalize(gt[i], width, height);
+            gt_boxes[4 * i + 0] = nb.xmin;
+            gt_boxes[4 * i + 1] = nb.ymin;
+            gt_boxes[4 * i + 2] = nb.xmax;
+            gt_boxes[4 * i + 3] = nb.ymax;
+            gt_class[i]         = gt[i].label;
+            gt_difficult[i]     = gt[i].difficult;
+        }
+    }
+
     // ------------------------------------------------------------------------------------------
     // crop-box helpers
     // ------------------------------------------------------------------------------------------

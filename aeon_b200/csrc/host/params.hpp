@@ -202,4 +202,15 @@ namespace aeonb
     // Box transforms used by the SSD path (aeon src/boundingbox.cpp:78-163).
     bbox bbox_expand(const bbox& b, size2i offset, size2i size, float ratio);
     nbox bbox_normalize(const bbox& b, float width, float height);
+    // aeon boundingbox::box::intersect / jaccard_overlap / coverage (src/boundingbox.cpp:105-148); an empty
+    // intersection is the default box (0, 0, -1, -1)
+    bbox  bbox_intersect(const bbox& a, const bbox& b);
+    float bbox_jaccard(const bbox& a, const bbox& b);
+    float bbox_coverage(const bbox& a, const bbox& b);
+    // aeon boundingbox::transformer::transform_box for every box of a record (src/etl_boundingbox.cpp:146-261):
+    // expand shift, emit constraint, clip to the crop box, flip, rescale to the output size
+    std::vector<bbox> transform_boxes_for_ssd(const std::vector<bbox>& boxes, const image_params& p);
+    // aeon localization::ssd::loader::load (src/etl_localization_ssd.cpp:116-149): the five buffers of one record
+    void ssd_fill_buffers(const std::vector<bbox>& gt, int width, int height, int max_gt_boxes, int32_t* image_shape, float* gt_boxes,
+                          int32_t* gt_box_count, int32_t* gt_class, int32_t* gt_difficult);
 }

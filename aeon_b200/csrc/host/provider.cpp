@@ -72,23 +72,6 @@ namespace aeonb
             }
         }
 
-    namespace
-    {
-        float bbox_coverage(const bbox& a, const bbox& b) // a.coverage(b), src/boundingbox.cpp:120-135
-        {
-            if (b.xmin > a.xmax || b.xmax < a.xmin || b.ymin > a.ymax || b.ymax < a.ymin)
-                return 0.f;
-            bbox i;
-            i.xmin = std::max(a.xmin, b.xmin);
-            i.ymin = std::max(a.ymin, b.ymin);
-            i.xmax = std::min(a.xmax, b.xmax);
-            i.ymax = std::min(a.ymax, b.ymax);
-            const float s = i.size();
-            return s > 0 ? s / a.size() : 0.f;
-        }
-
-    }
-
     // aeon boundingbox::transformer::transform_box (src/etl_boundingbox.cpp:146-261)
     vector<bbox> transform_boxes_for_ssd(const vector<bbox>& boxes, const image_params& p)
     {

@@ -19,7 +19,6 @@ using std::vector;
 namespace aeonb
 {
     cudaError_t  launch_transpose(const void* src, void* dst, int64_t rows, int64_t cols, int elem_size, cudaStream_t stream);
-    vector<bbox> transform_boxes_for_ssd(const vector<bbox>& boxes, const image_params& p);
     void parse_ssd_annotation(const void* data, size_t size, const std::unordered_map<string, int>& classes, int& width,
                               int& height, vector<bbox>& boxes);
 
@@ -621,19 +620,7 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
                 int32_t* count    = reinterpret_cast<int32_t*>(out_host[o + 2].data()) + r;
                 int32_t* cls      = reinterpret_cast<int32_t*>(out_host[o + 3].data()) + (size_t)r * M;
                 int32_t* diff     = reinterpret_cast<int32_t*>(out_host[o + 4].data()) + (size_t)r * M;
-                im_shape[0]       = sg.ssd.width;
-                im_shape[1]       = sg.ssd.height;
-                *count            = std::min<int>(M, (int)gt.size());
-                for (int i = 0; i < *count; ++i)
-                {
-                    const nbox nb = bbox_normalize(gt[i], sg.ssd.width, sg.ssd.height);
-                    gtb[4 * i + 0] = nb.xmin;
-                    gtb[4 * i + 1] = nb.ymin;
-                    gtb[4 * i + 2] = nb.xmax;
-                    gtb[4 * i + 3] = nb.ymax;
-                    cls[i]         = gt[i].label;
-                    diff[i]        = gt[i].difficult;
-                }
+                ssd_fill_buffers(gt, sg.ssd.width, sg.ssd.height, M, im_shape, gtb, count, cls, diff);
                 break;
             }
             case stage_kind::bbox:

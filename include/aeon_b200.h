@@ -378,10 +378,6 @@ int     aeonb_rcnn_anchors(const aeonb_rcnn_config* cfg, float* out);
 int     aeonb_rcnn_label_batch(aeonb_ctx* ctx, const float* anchors_dev, int32_t n_anchors, const aeonb_rcnn_desc* descs, int n,
                                float negative_overlap, float positive_overlap);
 
-/* Host-only self-test of the worker pool that prepares the batches: `rounds` dispatches of 1 + (round mod 300) jobs,
- * alternating between the whole pool and its light group; returns the sum of the job indices run, -1 on failure. */
-int64_t aeonb_selftest_worker_pool(int threads, int rounds);
-
 /* Draws augmentation parameters exactly as aeon's param_factory::make_params does
  * (src/augment_image.cpp:107-230) for `n` records whose decoded sizes are in_w/in_h,
  * using per-slot std::minstd_rand0 engines seeded as aeon's batch_decoder seeds them
@@ -397,6 +393,38 @@ int aeonb_draw_params(const char* augmentation_json, uint32_t seed, int decode_s
 int aeonb_draw_ssd_params(const char* augmentation_json, uint32_t seed, int decode_size, int n, const int32_t* in_w,
                           const int32_t* in_h, int out_w, int out_h, const int32_t* box_counts, const float* boxes,
                           double* out);
+
+/* Host box arithmetic of the localisation providers.
+ *
+ * aeonb_box_overlap: intersect / jaccard_overlap / coverage of two boxes a, b = (xmin, ymin, xmax, ymax), either pixel
+ * boxes with an inclusive max corner (boundingbox::box, src/boundingbox.cpp:105-148) or, with `normalized` != 0, boxes
+ * in [0,1] with an exclusive max corner (normalized_box::box, src/normalized_box.cpp:47-88; AEONB_ERR_INVALID when a
+ * box is not within [0,1]).  out = intersection (4 floats; the default box (0,0,-1,-1) resp. (0,0,0,0) when empty),
+ * a.jaccard_overlap(b), a.coverage(b).
+ *
+ * aeonb_transform_boxes: boundingbox::transformer::transform_box (src/etl_boundingbox.cpp:146-261) for n pixel boxes:
+ * expand shift, emit constraint, clip to the crop box, flip, rescale to the output size.  `out` takes up to n boxes,
+ * `kept` (may be NULL) the input index of each surviving box, *n_out their number.
+ *
+ * aeonb_ssd_load_boxes: localization::ssd::loader::load (src/etl_localization_ssd.cpp:116-149): image_shape int32[2],
+ * gt_boxes float[max_gt_boxes * 4] (normalised, zero rows after the boxes), gt_box_count int32, gt_class and
+ * gt_difficult int32[max_gt_boxes]. */
+typedef struct aeonb_box_params
+{
+    int32_t crop_x, crop_y, crop_w, crop_h;
+    int32_t out_w, out_h;
+    int32_t flip;
+    float   expand_ratio;      /* boxes are shifted by the expand offset when > 1 */
+    int32_t expand_off_x, expand_off_y, expand_w, expand_h;
+    int32_t emit_type;         /* 0 none, 1 center, 2 min_overlap */
+    float   emit_min_overlap;
+} aeonb_box_params;
+
+int aeonb_box_overlap(int normalized, const float a[4], const float b[4], float out[6]);
+int aeonb_transform_boxes(const aeonb_box_params* p, const float* boxes, int n, float* out, int32_t* kept, int32_t* n_out);
+int aeonb_ssd_load_boxes(const float* boxes, const int32_t* labels, const int32_t* difficult, int n, int width, int height,
+                         int max_gt_boxes, int32_t* image_shape, float* gt_boxes, int32_t* gt_box_count, int32_t* gt_class,
+                         int32_t* gt_difficult);
 
 /* Fills the photometric fields of `desc` (colour matrix, hue, HSV vector columns, contrast,
  * lighting scale/offsets) from aeon's parameter values, doing on the host what

@@ -4,9 +4,13 @@ Restates, in float32 arithmetic, ``param_factory::make_ssd_params`` and the patc
 (aeon src/augment_image.cpp:232-586), the box classes (src/box.hpp, src/boundingbox.cpp:78-163,
 src/normalized_box.cpp:47-107), ``boundingbox::transformer::transform_box``
 (src/etl_boundingbox.cpp:146-261) and ``localization::ssd::loader::load``
-(src/etl_localization_ssd.cpp:116-149).  The reference's tests for this path check properties
-only (test/test_augmentation.cpp, test/test_localization_ssd.cpp), so seeded values are
-PARITY UNPINNED by the reference.  Nothing in the shipped package imports this file.
+(src/etl_localization_ssd.cpp:116-149).  Pinned (tests/test_oracle_ssd.py) against the known answers the
+reference's own tests hold: box crop / expand / rescale / flip and their combinations, intersect /
+jaccard / coverage of both box kinds (test/test_bbox.cpp:283-637,761-912), the SSD transform and
+loader buffers (test/test_localization_ssd.cpp:158-271) and make_ssd_params
+(test/test_augmentation.cpp:246-317).  What the reference does not pin is the SEEDED patch sampling
+(its sampler tests check properties of a random-device seeded engine): those values are compared
+between this file and the C++ host code only.  Nothing in the shipped package imports this file.
 """
 import json
 import math
@@ -211,11 +215,24 @@ def expand_box(b, p):
     return Box(f32(b.xmin + f32(ox)), f32(b.ymin + f32(oy)), f32(b.xmax + f32(ox)), f32(b.ymax + f32(oy)), b.label, b.difficult)
 
 
-def box_coverage(a, b):
+def box_intersect(a, b):
+    """boundingbox::box::intersect (src/boundingbox.cpp:134-148); no intersection gives the default box (0, 0, -1, -1)."""
     if b.xmin > a.xmax or b.xmax < a.xmin or b.ymin > a.ymax or b.ymax < a.ymin:
+        return Box(0, 0, -1, -1)
+    return Box(max(a.xmin, b.xmin), max(a.ymin, b.ymin), min(a.xmax, b.xmax), min(a.ymax, b.ymax))
+
+
+def box_jaccard(a, b):
+    """boundingbox::box::jaccard_overlap (src/boundingbox.cpp:105-116)."""
+    inter = box_intersect(a, b).size()
+    if inter == 0:
         return f32(0)
-    i = Box(max(a.xmin, b.xmin), max(a.ymin, b.ymin), min(a.xmax, b.xmax), min(a.ymax, b.ymax))
-    s = i.size()
+    return f32(inter / f32(f32(a.size() + b.size()) - inter))
+
+
+def box_coverage(a, b):
+    """boundingbox::box::coverage (src/boundingbox.cpp:118-132)."""
+    s = box_intersect(a, b).size()
     return f32(s / a.size()) if s > 0 else f32(0)
 
 
