@@ -184,6 +184,13 @@ PROTOTYPES = {
     "aeonb_loader_next": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
     "aeonb_loader_reset": (C.c_int, [C.c_void_p]),
     "aeonb_loader_position": (C.c_int, [C.c_void_p]),
+    "aeonb_stream_create": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "aeonb_stream_destroy": (None, [C.c_void_p]),
+    "aeonb_stream_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.POINTER(C.c_int32),
+                                    C.POINTER(C.c_int32), C.c_char_p, C.c_size_t]),
+    "aeonb_stream_next": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_size_t)]),
+    "aeonb_stream_reset": (C.c_int, [C.c_void_p]),
+    "aeonb_node_record_indices": (C.c_int64, [C.c_int64, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int64)]),
 }
 
 # exported for the test suite only, not part of the public header

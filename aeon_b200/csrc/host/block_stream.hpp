@@ -1,0 +1,80 @@
+// The endless stream of encoded records behind the loader: aeon's manifest blocks -> block_loader_file ->
+// block_manager chain (src/block_loader_file.cpp:45-117, src/block_manager.cpp:61-106) with the CPIO block cache
+// (src/cache_system.cpp:69-146, src/cpio.cpp), as one pull-style object: the loader's producer thread asks for the
+// next record and the stream loads, caches and shuffles whole blocks behind it.
+#pragma once
+
+#include <cstdint>
+#include <functional>
+#include <random>
+#include <string>
+#include <vector>
+
+#include "loader.hpp"
+
+namespace aeonb
+{
+    typedef std::vector<std::vector<char>> encoded_record; // the elements of one record
+
+    // One block of records as a CPIO archive in aeon's layout (src/cpio.cpp): old binary cpio members "cpiohdr" (64-byte
+    // file header: "MACR", format 1, writer 1, data type, record count, elements per record), one member
+    // "rec_NNNNNNN.EE" per element, "cpiotlr" (16 bytes) and "TRAILER!!!".
+    void cpio_write_block(const std::string& path, const std::vector<encoded_record>& records);
+    std::vector<encoded_record> cpio_read_block(const std::string& path, size_t elements_per_record);
+
+    // aeon cache_system: a directory aeon_cache_<crc> under the cache root holding block_<n>.cpio files.  The process
+    // that takes the lock file "caching_in_progress" writes the blocks during its first pass and marks the directory with
+    // "cache_complete"; from then on every process reads blocks from the cache instead of the manifest's files.
+    class block_cache
+    {
+    public:
+        block_cache(uint32_t uid, size_t block_count, size_t elements_per_record, const std::string& root, bool shuffle, uint32_t seed);
+        ~block_cache();
+        bool is_complete() const { return m_stage == stage::complete; }
+        bool is_ownership() const { return m_stage == stage::ownership; }
+        void restart() { m_current = 0; }
+        void try_get_access();
+        std::vector<encoded_record> load_block();
+        void store_block(const std::vector<encoded_record>& block);
+        const std::string& directory() const { return m_dir; }
+
+    private:
+        enum class stage
+        {
+            complete,
+            ownership,
+            blocked
+        };
+        std::string block_path(size_t n) const;
+        size_t              m_block_count, m_elements, m_current = 0;
+        std::string         m_dir;
+        bool                m_shuffle;
+        std::minstd_rand0   m_random;
+        std::vector<size_t> m_sequence;
+        stage               m_stage = stage::blocked;
+        int                 m_lock  = -1;
+    };
+
+    class block_stream
+    {
+    public:
+        // `load` turns the manifest fields of one record into its elements (file reads, base64, ...)
+        block_stream(manifest& m, const std::string& cache_root, bool shuffle, uint32_t seed,
+                     std::function<void(const std::vector<std::string>&, encoded_record&)> load);
+        encoded_record        next(); // the next record of the stream (moved out); loads the next block when one is used up
+        void                  reset(); // aeon loader::reset: back to the first block; generators keep their state
+        const block_cache*    cache() const { return m_cache.get(); }
+
+    private:
+        void next_block();
+        manifest&                    m_manifest;
+        std::function<void(const std::vector<std::string>&, encoded_record&)> m_load;
+        bool                         m_shuffle;
+        std::minstd_rand0            m_random;
+        std::unique_ptr<block_cache> m_cache;
+        size_t                       m_block_number = 0; // blocks read from the manifest in this pass
+        size_t                       m_manifest_at  = 0; // position in the manifest's block sequence
+        std::vector<encoded_record>  m_block;
+        size_t                       m_at = 0;
+    };
+}

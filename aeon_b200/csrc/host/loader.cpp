@@ -1,4 +1,5 @@
 #include "loader.hpp"
+#include "block_stream.hpp"
 
 #include <algorithm>
 #include <cmath>
@@ -52,31 +53,97 @@ namespace
     }
 }
 
-aeonb_loader::aeonb_loader(const json& cfg, int device) : m_device(device), m_block_random(1)
+namespace
 {
-    for (const char* k : {"manifest_filename", "batch_size", "etl"})
+    // The source side of the loader configuration (src/loader.hpp:77-106, src/loader.cpp:94-139): manifest, node split,
+    // blocks, shuffle switches, cache directory.
+    struct source_config
+    {
+        int      batch_size = 0, block_size = 5000;
+        bool     shuffle_enable = false;
+        uint32_t seed = 0, node_id = 0, node_count = 0;
+        string   cache_directory;
+    };
+
+    source_config open_source(const json& cfg, manifest& m)
+    {
+        source_config sc;
+        for (const char* k : {"manifest_filename", "batch_size"})
+            if (!cfg.contains(k))
+                throw std::invalid_argument(string("Required Argument: '") + k + "' not set");
+        const string manifest_filename = get<string>(cfg, "manifest_filename", "");
+        const string manifest_root     = get<string>(cfg, "manifest_root", "");
+        sc.batch_size                  = get<int>(cfg, "batch_size", 0);
+        if (sc.batch_size <= 0)
+            throw std::invalid_argument("batch_size must be positive");
+        sc.block_size = get<int>(cfg, "block_size", 5000);
+        if (sc.block_size == 0)
+            sc.block_size = 2 * sc.batch_size;
+        const float subset = get<float>(cfg, "subset_fraction", 1.0f);
+        if (!(subset <= 1.0f && subset >= 0.0f))
+            throw std::invalid_argument("value for 'subset_fraction' out of range");
+        sc.shuffle_enable           = get<bool>(cfg, "shuffle_enable", false);
+        const bool shuffle_manifest = get<bool>(cfg, "shuffle_manifest", false);
+        sc.seed                     = get<uint32_t>(cfg, "random_seed", 0);
+        sc.node_id                  = get<uint32_t>(cfg, "node_id", 0);
+        sc.node_count               = get<uint32_t>(cfg, "node_count", 0);
+        sc.cache_directory          = get<string>(cfg, "cache_directory", "");
+        if (sc.node_count > 1)
+        {
+            if (sc.node_id >= sc.node_count)
+                throw std::runtime_error("node_id can't be greater than node_count");
+            if (sc.seed == 0)
+                sc.seed = 1; // aeon forces a seed for multi-node runs (src/loader.cpp:110-114)
+        }
+        std::ifstream in(manifest_filename);
+        if (!in.is_open())
+            throw std::runtime_error("Manifest file " + manifest_filename + " doesn't exist.");
+        m.parse(in, manifest_root, subset, shuffle_manifest, sc.seed, sc.node_id, sc.node_count, sc.batch_size, sc.block_size);
+        if (m.record_count == 0)
+            throw std::runtime_error("manifest file is empty");
+        return sc;
+    }
+
+    // aeon block_loader_file::filler (src/block_loader_file.cpp:56-104): the elements of one record
+    void load_fields(const manifest& m, const vector<string>& fields, vector<vector<char>>& elems)
+    {
+        elems.clear();
+        for (size_t j = 0; j < fields.size(); ++j)
+        {
+            const string& e = fields[j];
+            switch (m.types[j])
+            {
+            case element_t::FILE: elems.push_back(read_file(e)); break;
+            case element_t::BINARY: elems.push_back(base64_decode(e)); break;
+            case element_t::STRING: elems.emplace_back(e.begin(), e.end()); break;
+            case element_t::ASCII_INT:
+            {
+                int32_t v = (int32_t)std::stod(e);
+                elems.emplace_back((char*)&v, (char*)&v + sizeof v);
+                break;
+            }
+            case element_t::ASCII_FLOAT:
+            {
+                float v = std::stof(e);
+                elems.emplace_back((char*)&v, (char*)&v + sizeof v);
+                break;
+            }
+            }
+        }
+    }
+}
+
+aeonb_loader::aeonb_loader(const json& cfg, int device) : m_device(device)
+{
+    if (!cfg.contains("etl"))
+        throw std::invalid_argument("Required Argument: 'etl' not set");
+    for (const char* k : {"manifest_filename", "batch_size"})
         if (!cfg.contains(k))
             throw std::invalid_argument(string("Required Argument: '") + k + "' not set");
     verify_config("loader", k_loader_keys, cfg);
-    const string manifest_filename = get<string>(cfg, "manifest_filename", "");
-    const string manifest_root     = get<string>(cfg, "manifest_root", "");
-    m_batch_size                   = get<int>(cfg, "batch_size", 0);
-    if (m_batch_size <= 0)
-        throw std::invalid_argument("batch_size must be positive");
-    m_block_size = get<int>(cfg, "block_size", 5000);
-    if (m_block_size == 0)
-        m_block_size = 2 * m_batch_size;
-    const float subset = get<float>(cfg, "subset_fraction", 1.0f);
-    if (!(subset <= 1.0f && subset >= 0.0f))
-        throw std::invalid_argument("value for 'subset_fraction' out of range");
-    m_shuffle                    = get<bool>(cfg, "shuffle_enable", false);
-    const bool shuffle_manifest  = get<bool>(cfg, "shuffle_manifest", false);
-    uint32_t   seed              = get<uint32_t>(cfg, "random_seed", 0);
-    const string mode            = get<string>(cfg, "iteration_mode", "ONCE");
-    const int    mode_count      = get<int>(cfg, "iteration_mode_count", 0);
-    const uint32_t node_id       = get<uint32_t>(cfg, "node_id", 0);
-    const uint32_t node_count    = get<uint32_t>(cfg, "node_count", 0);
-    m_device_output              = get<bool>(cfg, "device_output", false);
+    const string mode       = get<string>(cfg, "iteration_mode", "ONCE");
+    const int    mode_count = get<int>(cfg, "iteration_mode_count", 0);
+    m_device_output         = get<bool>(cfg, "device_output", false);
     if (mode == "COUNT")
     {
         if (mode_count <= 0)
@@ -84,21 +151,15 @@ aeonb_loader::aeonb_loader(const json& cfg, int device) : m_device(device), m_bl
     }
     else if (mode != "ONCE" && mode != "INFINITE")
         throw std::invalid_argument("iteration_mode must be one of ONCE, COUNT, or INFINITE");
-    if (node_count > 1)
-    {
-        if (node_id >= node_count)
-            throw std::runtime_error("node_id can't be greater than node_count");
-        if (seed == 0)
-            seed = 1; // aeon forces a seed for multi-node runs (src/loader.cpp:110-114)
-    }
-
-    std::ifstream in(manifest_filename);
-    if (!in.is_open())
-        throw std::runtime_error("Manifest file " + manifest_filename + " doesn't exist.");
-    m_manifest.parse(in, manifest_root, subset, shuffle_manifest, seed, node_id, node_count, m_batch_size);
-    if (m_manifest.record_count == 0)
-        throw std::runtime_error("manifest file is empty");
-    m_block_random.seed(seed ? seed : std::random_device{}());
+    const source_config sc = open_source(cfg, m_manifest);
+    m_batch_size           = sc.batch_size;
+    m_block_size           = sc.block_size;
+    m_shuffle              = sc.shuffle_enable;
+    const uint32_t seed = sc.seed, node_id = sc.node_id;
+    // block_manager and cache_system draw from generators of their own, seeded alike (src/block_manager.cpp:37,
+    // src/cache_system.cpp:41)
+    m_stream.reset(new block_stream(m_manifest, sc.cache_directory, m_shuffle, seed,
+                                    [this](const vector<string>& fields, encoded_record& elems) { load_fields(m_manifest, fields, elems); }));
 
     m_batch_count = (int)((m_manifest.record_count + m_batch_size - 1) / m_batch_size);
     m_infinite    = mode == "INFINITE";
@@ -157,8 +218,6 @@ aeonb_loader::aeonb_loader(const json& cfg, int device) : m_device(device), m_bl
         aeonb_ctx_destroy(m_ctx);
         throw;
     }
-    m_order.resize(m_manifest.record_count);
-    std::iota(m_order.begin(), m_order.end(), 0);
     start_producer();
 }
 
@@ -171,34 +230,6 @@ aeonb_loader::~aeonb_loader()
             m_device_output ? cudaFree(p) : cudaFreeHost(p);
     delete m_provider;
     aeonb_ctx_destroy(m_ctx);
-}
-
-void aeonb_loader::load_record(const vector<string>& fields, vector<vector<char>>& elems)
-{
-    // aeon block_loader_file::filler (src/block_loader_file.cpp:56-104)
-    elems.clear();
-    for (size_t j = 0; j < fields.size(); ++j)
-    {
-        const string& e = fields[j];
-        switch (m_manifest.types[j])
-        {
-        case element_t::FILE: elems.push_back(read_file(e)); break;
-        case element_t::BINARY: elems.push_back(base64_decode(e)); break;
-        case element_t::STRING: elems.emplace_back(e.begin(), e.end()); break;
-        case element_t::ASCII_INT:
-        {
-            int32_t v = (int32_t)std::stod(e);
-            elems.emplace_back((char*)&v, (char*)&v + sizeof v);
-            break;
-        }
-        case element_t::ASCII_FLOAT:
-        {
-            float v = std::stof(e);
-            elems.emplace_back((char*)&v, (char*)&v + sizeof v);
-            break;
-        }
-        }
-    }
 }
 
 void aeonb_loader::start_producer()
@@ -246,32 +277,7 @@ void aeonb_loader::producer()
             vector<size_t>      sizes((size_t)m_batch_size * nin);
             for (int r = 0; r < m_batch_size; ++r)
             {
-                if (m_cursor == m_order.size())
-                {
-                    // the record stream never ends: wrap to the start of the data set (src/block_manager.cpp:86-92),
-                    // reshuffling block order and block contents when shuffle_enable is set
-                    m_cursor = 0;
-                    if (m_shuffle)
-                    {
-                        const size_t n      = m_order.size();
-                        const size_t blocks = std::max<size_t>(1, (size_t)std::round((float)n / (float)m_block_size));
-                        const size_t bsz    = (size_t)std::ceil((float)n / (float)blocks);
-                        vector<size_t> seq(blocks);
-                        std::iota(seq.begin(), seq.end(), 0);
-                        std::shuffle(seq.begin(), seq.end(), m_block_random);
-                        vector<size_t> order;
-                        for (size_t b : seq)
-                        {
-                            const size_t lo = b * bsz, hi = std::min(n, lo + bsz);
-                            const size_t at = order.size();
-                            for (size_t i = lo; i < hi; ++i)
-                                order.push_back(i);
-                            std::shuffle(order.begin() + at, order.end(), m_block_random);
-                        }
-                        m_order.swap(order);
-                    }
-                }
-                load_record(m_manifest.records[m_order[m_cursor++]], held[r]);
+                held[r] = m_stream->next();
                 for (int e = 0; e < nin; ++e)
                 {
                     elems[(size_t)r * nin + e] = held[r][e].data();
@@ -326,10 +332,9 @@ void aeonb_loader::reset()
 {
     // restart the epoch from the first record of the data set (src/loader.hpp:205-210)
     stop_producer();
-    m_cursor   = 0;
+    m_stream->reset();
     m_position = 0;
     m_provider->slot_cursor = 0;
-    std::iota(m_order.begin(), m_order.end(), 0);
     start_producer();
 }
 
@@ -387,5 +392,84 @@ int aeonb_loader_reset(aeonb_loader* l)
 }
 
 int aeonb_loader_position(const aeonb_loader* l) { return l ? l->position() : 0; }
+
+int aeonb_stream_create(const char* config_json, aeonb_stream** out)
+{
+    return guarded([&]() {
+        if (!config_json || !out)
+            throw std::invalid_argument("aeonb_stream_create: NULL argument");
+        std::unique_ptr<aeonb_stream> st(new aeonb_stream());
+        const json          cfg = json::parse(config_json);
+        const source_config sc  = open_source(cfg, st->m);
+        aeonb_stream*       raw = st.get();
+        st->stream.reset(new block_stream(st->m, sc.cache_directory, sc.shuffle_enable, sc.seed,
+                                          [raw](const vector<string>& fields, encoded_record& elems) { load_fields(raw->m, fields, elems); }));
+        *out = st.release();
+        return AEONB_OK;
+    });
+}
+
+void aeonb_stream_destroy(aeonb_stream* s) { delete s; }
+
+int aeonb_stream_info(const aeonb_stream* s, int64_t* record_count, int32_t* elements_per_record, int32_t* block_count,
+                      int32_t* cache_state, char* cache_dir, size_t cache_dir_size)
+{
+    return guarded([&]() {
+        if (!s)
+            throw std::invalid_argument("aeonb_stream_info: stream is NULL");
+        if (record_count)
+            *record_count = (int64_t)s->m.record_count;
+        if (elements_per_record)
+            *elements_per_record = (int32_t)s->m.types.size();
+        if (block_count)
+            *block_count = (int32_t)s->m.blocks.size();
+        const block_cache* c = s->stream->cache();
+        if (cache_state)
+            *cache_state = !c ? 0 : c->is_complete() ? 3 : c->is_ownership() ? 2 : 1;
+        if (cache_dir && cache_dir_size)
+        {
+            const string d = c ? c->directory() : string();
+            std::strncpy(cache_dir, d.c_str(), cache_dir_size - 1);
+            cache_dir[cache_dir_size - 1] = 0;
+        }
+        return AEONB_OK;
+    });
+}
+
+int aeonb_stream_next(aeonb_stream* s, const void** elems, size_t* sizes)
+{
+    return guarded([&]() {
+        if (!s || !elems || !sizes)
+            throw std::invalid_argument("aeonb_stream_next: NULL argument");
+        s->held = s->stream->next();
+        for (size_t e = 0; e < s->held.size(); ++e)
+        {
+            elems[e] = s->held[e].data();
+            sizes[e] = s->held[e].size();
+        }
+        return AEONB_OK;
+    });
+}
+
+int aeonb_stream_reset(aeonb_stream* s)
+{
+    return guarded([&]() {
+        if (!s)
+            throw std::invalid_argument("aeonb_stream_reset: stream is NULL");
+        s->stream->reset();
+        return AEONB_OK;
+    });
+}
+
+int64_t aeonb_node_record_indices(int64_t total, int node_id, int node_count, int batch_size, int64_t* out)
+{
+    if (total < 0 || batch_size <= 0 || node_id < 0 || (node_count > 1 && node_id >= node_count))
+        return fail(AEONB_ERR_INVALID, "aeonb_node_record_indices: bad argument");
+    const vector<size_t> idx = node_record_indices((size_t)total, (uint32_t)node_id, (uint32_t)std::max(node_count, 0), batch_size);
+    if (out)
+        for (size_t i = 0; i < idx.size(); ++i)
+            out[i] = (int64_t)idx[i];
+    return (int64_t)idx.size();
+}
 
 } // extern "C"

@@ -29,17 +29,40 @@ namespace aeonb
         ASCII_FLOAT
     };
 
+    // aeon manifest_file (src/manifest_file.cpp): the record list of this node, cut into blocks, with the order in
+    // which the blocks of the current epoch are read.
     struct manifest
     {
-        std::vector<element_t>                 types;
-        std::vector<std::vector<std::string>>  records; // after subset / node sharding
-        size_t                                 record_count = 0;
+        std::vector<element_t>                   types;
+        std::vector<std::vector<std::string>>    records; // this node's records (after subset, shuffle, node split)
+        size_t                                   record_count = 0;
+        uint32_t                                 crc          = 0; // CRC32C over all fields: the identity of a block cache
+        std::vector<std::pair<size_t, size_t>>   blocks;          // [first, last) into records
+        std::vector<size_t>                      block_sequence;  // block order of the current epoch
         void parse(std::istream& in, const std::string& root, float subset_fraction, bool shuffle, uint32_t seed, uint32_t node_id,
-                   uint32_t node_count, int batch_size);
+                   uint32_t node_count, int batch_size, int block_size);
+        void reset(); // next epoch
+
+    private:
+        void generate();
+        std::vector<std::vector<std::string>> m_all; // every record of the manifest (after subset)
+        std::minstd_rand0                     m_random;
+        bool                                  m_shuffle    = false;
+        uint32_t                              m_node_id = 0, m_node_count = 0;
+        int                                   m_batch_size = 1, m_block_size = 5000;
     };
+
+    std::vector<size_t> node_record_indices(size_t total, uint32_t node_id, uint32_t node_count, int batch_size);
+    std::vector<std::pair<size_t, size_t>> block_ranges(size_t record_count, size_t block_size);
+    uint32_t crc32c_update(uint32_t crc, const void* data, size_t size);
 
     std::vector<char> base64_decode(const std::string& in);
     std::vector<int>  parse_cpu_list(const std::string& s);
+}
+
+namespace aeonb
+{
+    class block_stream;
 }
 
 struct aeonb_loader
@@ -68,7 +91,6 @@ private:
     void producer();
     void start_producer();
     void stop_producer();
-    void load_record(const std::vector<std::string>& fields, std::vector<std::vector<char>>& elems);
 
     aeonb::manifest m_manifest;
     aeonb_ctx*      m_ctx      = nullptr;
@@ -77,7 +99,7 @@ private:
     int             m_batch_size = 0, m_batch_count = 0, m_position = 0;
     bool            m_infinite = false, m_device_output = false, m_shuffle = false;
     int             m_block_size = 5000;
-    std::minstd_rand0 m_block_random;
+    std::unique_ptr<aeonb::block_stream> m_stream; // the endless record stream (blocks, shuffle, CPIO cache)
 
     slot                    m_slots[2];
     int                     m_consume = 0;    // slot the consumer reads next
@@ -86,6 +108,13 @@ private:
     std::mutex              m_mutex;
     std::condition_variable m_cv;
     bool                    m_stop = false;
-    size_t                  m_cursor = 0; // next record of the endless stream (producer side)
-    std::vector<size_t>     m_order;      // record order of the current epoch
+};
+
+// The source side alone (manifest -> blocks -> cache -> shuffled record stream), host only.
+struct aeonb_stream
+{
+    aeonb::manifest                       m;
+    std::unique_ptr<aeonb::block_stream>  stream;
+    std::vector<std::vector<char>>        held; // the record handed out by the last aeonb_stream_next
+    ~aeonb_stream();
 };

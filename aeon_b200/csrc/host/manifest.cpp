@@ -1,5 +1,7 @@
 // TSV manifest, base64 and cpu-list parsing for the loader shell.
 #include <algorithm>
+#include <array>
+#include <cmath>
 #include <fstream>
 #include <sstream>
 #include <stdexcept>
@@ -95,7 +97,7 @@ namespace aeonb
     }
 
     void manifest::parse(istream& in, const string& root, float subset_fraction, bool shuffle, uint32_t seed, uint32_t node_id,
-                         uint32_t node_count, int batch_size)
+                         uint32_t node_count, int batch_size, int block_size)
     {
         string line;
         size_t line_number = 0;
@@ -172,34 +174,124 @@ namespace aeonb
                 }
             }
         }
+        // cache identity: CRC32C over every field as written in the manifest, before the root is joined on
+        // (src/manifest_file.cpp:208-219)
+        {
+            uint32_t c = 0xFFFFFFFFu;
+            for (const auto& rec : list)
+                for (const string& f : rec)
+                    c = crc32c_update(c, f.data(), f.size());
+            crc = ~c;
+        }
         if (!root.empty())
             for (auto& rec : list)
                 for (size_t i = 0; i < types.size(); i++)
                     if (types[i] == element_t::FILE)
                         rec[i] = path_join(root, rec[i]);
-        if (shuffle)
+        m_all.swap(list);
+        m_random.seed(seed ? seed : random_device{}());
+        m_shuffle    = shuffle;
+        m_node_id    = node_id;
+        m_node_count = node_count;
+        m_batch_size = batch_size;
+        m_block_size = block_size;
+        generate();
+    }
+
+    // Which records of the full list one node of a multi-node run reads (src/manifest_file.cpp:278-295): the list is
+    // cut into rounds of node_count batches, node g takes batch g of every round; what is left after the last whole
+    // round of this node's share is divided into node_count equal runs, node g taking run g.
+    vector<size_t> node_record_indices(size_t total, uint32_t node_id, uint32_t node_count, int batch_size)
+    {
+        vector<size_t> out;
+        if (node_count <= 1)
         {
-            minstd_rand0 rnd(seed ? seed : random_device{}());
-            std::shuffle(list.begin(), list.end(), rnd);
+            out.resize(total);
+            for (size_t i = 0; i < total; ++i)
+                out[i] = i;
+            return out;
         }
-        record_count = list.size();
-        if (node_count > 1)
+        const size_t share  = total / node_count;        // records of this node
+        const size_t rounds = share / (size_t)batch_size; // whole batches of this node
+        out.reserve(share);
+        for (size_t round = 0; round < rounds; ++round)
         {
-            // interleaved batch-sized slices per node (src/manifest_file.cpp:278-295)
-            record_count = list.size() / node_count;
-            int batches  = (int)(record_count / batch_size);
-            records.resize(record_count);
-            for (int i = 0; i < batches * batch_size; i++)
+            const size_t first = (round * node_count + node_id) * (size_t)batch_size;
+            for (size_t k = 0; k < (size_t)batch_size; ++k)
+                out.push_back(first + k);
+        }
+        const size_t run   = share - rounds * (size_t)batch_size;
+        const size_t first = rounds * node_count * (size_t)batch_size + run * node_id;
+        for (size_t k = 0; k < run; ++k)
+            out.push_back(first + k);
+        return out;
+    }
+
+    // aeon generate_block_list (src/block.cpp:23-44): about block_size records per block, all blocks but the last equal
+    vector<pair<size_t, size_t>> block_ranges(size_t record_count, size_t block_size)
+    {
+        size_t count = (size_t)std::round((float)record_count / (float)block_size);
+        count        = std::max<size_t>(count, 1);
+        const size_t size = (size_t)std::ceil((float)record_count / (float)count);
+        vector<pair<size_t, size_t>> out;
+        for (size_t b = 0; b < count; ++b)
+        {
+            const size_t lo = size * b;
+            if (lo + size > record_count)
             {
-                int batch_num = i / batch_size, in_batch = i % batch_size;
-                records[i]    = list[(size_t)batch_num * batch_size * node_count + (size_t)batch_size * node_id + in_batch];
+                out.emplace_back(lo, record_count);
+                break;
             }
-            int tail_count = (int)record_count - batches * batch_size;
-            int tail_src   = batches * batch_size * node_count + tail_count * node_id;
-            for (int i = 0; i < tail_count; i++)
-                records[i + batches * batch_size] = list[i + tail_src];
+            out.emplace_back(lo, lo + size);
         }
-        else
-            records.swap(list);
+        return out;
+    }
+
+    // aeon manifest_file::generate_blocks (src/manifest_file.cpp:270-318)
+    void manifest::generate()
+    {
+        if (m_shuffle)
+            std::shuffle(m_all.begin(), m_all.end(), m_random);
+        const vector<size_t> mine = node_record_indices(m_all.size(), m_node_id, m_node_count, m_batch_size);
+        records.clear();
+        records.reserve(mine.size());
+        for (size_t i : mine)
+            records.push_back(m_all[i]);
+        record_count = records.size();
+        blocks       = block_ranges(record_count, (size_t)m_block_size);
+        block_sequence.resize(blocks.size());
+        for (size_t i = 0; i < blocks.size(); ++i)
+            block_sequence[i] = i;
+    }
+
+    // aeon manifest_file::reset (src/manifest_file.cpp:320-329): with shuffle_manifest a new block order, and for a
+    // multi-node run a new shuffle of the whole list
+    void manifest::reset()
+    {
+        if (m_shuffle)
+        {
+            std::shuffle(block_sequence.begin(), block_sequence.end(), m_random);
+            if (m_node_count > 1)
+                generate();
+        }
+    }
+
+    uint32_t crc32c_update(uint32_t crc, const void* data, size_t size)
+    {
+        static const auto table = [] {
+            std::array<uint32_t, 256> t{};
+            for (uint32_t i = 0; i < 256; ++i)
+            {
+                uint32_t c = i;
+                for (int k = 0; k < 8; ++k)
+                    c = (c & 1) ? (c >> 1) ^ 0x82F63B78u : c >> 1; // Castagnoli polynomial, reflected
+                t[i] = c;
+            }
+            return t;
+        }();
+        const unsigned char* p = static_cast<const unsigned char*>(data);
+        for (size_t i = 0; i < size; ++i)
+            crc = table[(crc ^ p[i]) & 0xFF] ^ (crc >> 8);
+        return crc;
     }
 }

@@ -4,19 +4,15 @@ works on its own records.  The split is aeon's multi-node manifest split
 
 
 def shard_indices(n_records, batch_size, rank, world):
-    """Indices (into the unsharded record list) that rank `rank` of `world` processes."""
-    if world <= 1:
-        return list(range(n_records))
-    count = n_records // world
-    batches = count // batch_size
-    out = []
-    for i in range(batches * batch_size):
-        b, k = divmod(i, batch_size)
-        out.append(b * batch_size * world + batch_size * rank + k)
-    tail = count - batches * batch_size
-    src = batches * batch_size * world + tail * rank
-    out.extend(range(src, src + tail))
-    return out
+    """Indices (into the unsharded record list) that rank `rank` of `world` processes: the library's own node split
+    (aeonb_node_record_indices), so python and the C++ loader cannot drift apart."""
+    import ctypes as C
+    from . import _lib as L
+    lib = L.load()
+    n = int(L.check(lib.aeonb_node_record_indices(n_records, rank, world, batch_size, None)))
+    out = (C.c_int64 * max(n, 1))()
+    L.check(lib.aeonb_node_record_indices(n_records, rank, world, batch_size, out))
+    return list(out[:n])
 
 
 def max_over_ranks(value, group=None):

@@ -494,6 +494,32 @@ int aeonb_loader_next(aeonb_loader* l, void** buffers);
 int aeonb_loader_reset(aeonb_loader* l);
 int aeonb_loader_position(const aeonb_loader* l);
 
+/* ------------------------------------------------------------------------------------------------
+ * 5. Source side alone, host only (no GPU needed): the stream of encoded records the loader decodes --
+ *    manifest_file -> block_loader_file -> block_manager with the CPIO block cache
+ *    (src/manifest_file.cpp:115-330, src/block_loader_file.cpp:45-117, src/block_manager.cpp:61-106,
+ *    src/cache_system.cpp:69-146, src/cpio.cpp).  Takes the loader's own JSON (manifest_filename, manifest_root,
+ *    batch_size, block_size, subset_fraction, shuffle_enable, shuffle_manifest, random_seed, node_id, node_count,
+ *    cache_directory); other keys are ignored here.  The stream never ends: after the last block it starts over,
+ *    reshuffled as the configuration says.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct aeonb_stream aeonb_stream;
+int  aeonb_stream_create(const char* config_json, aeonb_stream** out);
+void aeonb_stream_destroy(aeonb_stream* s);
+/* cache_state: 0 no cache_directory, 1 another process is writing the cache (this one reads the manifest's files),
+ * 2 this process writes the cache during its first pass, 3 the cache is complete and is what gets read. */
+int  aeonb_stream_info(const aeonb_stream* s, int64_t* record_count, int32_t* elements_per_record, int32_t* block_count,
+                       int32_t* cache_state, char* cache_dir, size_t cache_dir_size);
+/* The next record: elems[e] / sizes[e] for each of its elements, valid until the next call. */
+int  aeonb_stream_next(aeonb_stream* s, const void** elems, size_t* sizes);
+int  aeonb_stream_reset(aeonb_stream* s);
+
+/* Which records of a manifest of `total` records node `node_id` of `node_count` reads (src/manifest_file.cpp:278-295):
+ * batch-sized slices dealt round-robin, then an evenly divided tail.  Writes the indices to `out` (may be NULL) and
+ * returns their number (total / node_count; total when node_count <= 1), negative on a bad argument.  It is also how
+ * the records of a batch are sharded over the GPUs of one box. */
+int64_t aeonb_node_record_indices(int64_t total, int node_id, int node_count, int batch_size, int64_t* out);
+
 #ifdef __cplusplus
 }
 #endif
