@@ -114,6 +114,12 @@ class SpecgramConfig(C.Structure):
                 ("num_cepstra", C.c_int32), ("reserved0", C.c_int32)]
 
 
+class KernelProfile(C.Structure):
+    _fields_ = [("launches", C.c_int64), ("ms", C.c_double), ("algorithmic_bytes", C.c_int64)]
+
+
+KERNEL_KINDS = ("jpeg_entropy", "jpeg_backend", "aug_pack", "specgram", "other")
+
 # name -> (restype, argtypes); every symbol the header declares
 PROTOTYPES = {
     "aeonb_last_error": (C.c_char_p, []),
@@ -122,6 +128,8 @@ PROTOTYPES = {
     "aeonb_ctx_destroy": (None, [C.c_void_p]),
     "aeonb_ctx_stream": (C.c_void_p, [C.c_void_p]),
     "aeonb_ctx_synchronize": (C.c_int, [C.c_void_p]),
+    "aeonb_ctx_profile": (C.c_int, [C.c_void_p, C.c_int]),
+    "aeonb_ctx_profile_read": (C.c_int, [C.c_void_p, C.POINTER(KernelProfile)]),
     "aeonb_image_batch": (C.c_int, [C.c_void_p, C.POINTER(ImageDesc), C.c_int, C.POINTER(ImageLayout)]),
     "aeonb_image_batch_bytes": (C.c_int64, [C.POINTER(ImageDesc), C.c_int, C.POINTER(ImageLayout)]),
     "aeonb_image_batch_noalloc": (C.c_int, [C.POINTER(ImageDesc), C.c_int, C.POINTER(ImageLayout), C.c_void_p]),

@@ -27,6 +27,7 @@
 // this file is compiled with -fmad=false and uses explicit fused operations only where
 // OpenCV's own code is fused.
 #include <algorithm>
+#include <atomic>
 
 #include <cooperative_groups.h>
 #include <cuda_runtime.h>
@@ -837,9 +838,20 @@ namespace aeonb
                                  cudaStream_t stream)
         {
             auto kern = pix == 4 ? aug_pack_kernel<T, 4> : aug_pack_kernel<T, 3>;
-            cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            // the dynamic shared-memory limit of a kernel is a per-device setting: raised only when a launch needs more
+            static std::atomic<int> limit[2][64];
+            int                     device = 0;
+            cudaError_t             err    = cudaGetDevice(&device);
             if (err != cudaSuccess)
                 return err;
+            std::atomic<int>& have = limit[pix == 4][device & 63];
+            if ((int)smem > have.load(std::memory_order_relaxed))
+            {
+                err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (err != cudaSuccess)
+                    return err;
+                have.store((int)smem, std::memory_order_relaxed);
+            }
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim            = dim3(bands, clusters, 1);
             cfg.blockDim           = dim3(threads, 1, 1);

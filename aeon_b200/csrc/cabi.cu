@@ -53,6 +53,35 @@ namespace aeonb
     }
 }
 
+namespace aeonb
+{
+    launch_timer::launch_timer(aeonb_ctx* c, int kind, int64_t algorithmic_bytes) : ctx(c)
+    {
+        if (!ctx->profiling)
+            return;
+        profile_span sp{kind, nullptr, nullptr, algorithmic_bytes};
+        for (cudaEvent_t* e : {&sp.begin, &sp.end})
+        {
+            if (!ctx->event_pool.empty())
+            {
+                *e = ctx->event_pool.back();
+                ctx->event_pool.pop_back();
+            }
+            else
+                AEONB_CUDA(cudaEventCreate(e));
+        }
+        AEONB_CUDA(cudaEventRecord(sp.begin, ctx->stream));
+        ctx->spans.push_back(sp);
+        span = (int)ctx->spans.size() - 1;
+    }
+
+    launch_timer::~launch_timer()
+    {
+        if (span >= 0)
+            cudaEventRecord(ctx->spans[span].end, ctx->stream);
+    }
+}
+
 using namespace aeonb;
 
 void* aeonb_ctx::upload(const void* host, size_t bytes)
@@ -126,9 +155,62 @@ void aeonb_ctx_destroy(aeonb_ctx* ctx)
         if (s.copied)
             cudaEventDestroy(s.copied);
     }
+    for (const profile_span& sp : ctx->spans)
+    {
+        cudaEventDestroy(sp.begin);
+        cudaEventDestroy(sp.end);
+    }
+    for (cudaEvent_t e : ctx->event_pool)
+        cudaEventDestroy(e);
     if (ctx->own_stream)
         cudaStreamDestroy(ctx->stream);
     delete ctx;
+}
+
+int aeonb_ctx_profile(aeonb_ctx* ctx, int enable)
+{
+    return guarded([&]() {
+        if (!ctx)
+            throw std::invalid_argument("context is NULL");
+        AEONB_CUDA(cudaSetDevice(ctx->device));
+        AEONB_CUDA(cudaStreamSynchronize(ctx->stream));
+        for (const profile_span& sp : ctx->spans)
+        {
+            ctx->event_pool.push_back(sp.begin);
+            ctx->event_pool.push_back(sp.end);
+        }
+        ctx->spans.clear();
+        ctx->profiling = enable != 0;
+        if (enable)
+            for (aeonb_kernel_profile& t : ctx->totals)
+                t = aeonb_kernel_profile{0, 0.0, 0};
+        return AEONB_OK;
+    });
+}
+
+int aeonb_ctx_profile_read(aeonb_ctx* ctx, aeonb_kernel_profile out[AEONB_KERNEL_KINDS])
+{
+    return guarded([&]() {
+        if (!ctx || !out)
+            throw std::invalid_argument("aeonb_ctx_profile_read: NULL argument");
+        AEONB_CUDA(cudaSetDevice(ctx->device));
+        AEONB_CUDA(cudaStreamSynchronize(ctx->stream));
+        for (const profile_span& sp : ctx->spans)
+        {
+            float ms = 0;
+            AEONB_CUDA(cudaEventElapsedTime(&ms, sp.begin, sp.end));
+            aeonb_kernel_profile& t = ctx->totals[sp.kind];
+            t.launches++;
+            t.ms += ms;
+            t.algorithmic_bytes += sp.bytes;
+            ctx->event_pool.push_back(sp.begin);
+            ctx->event_pool.push_back(sp.end);
+        }
+        ctx->spans.clear();
+        for (int k = 0; k < AEONB_KERNEL_KINDS; ++k)
+            out[k] = ctx->totals[k];
+        return AEONB_OK;
+    });
 }
 
 void* aeonb_ctx_stream(aeonb_ctx* ctx)
@@ -236,8 +318,9 @@ int aeonb_image_batch(aeonb_ctx* ctx, const aeonb_image_desc* descs, int n, cons
         auto cost = [](const aeonb_image_desc& r) { return r.src ? std::min(r.crop_h, 2 * r.out_h) : 0; };
         std::stable_sort(ordered.begin(), ordered.end(), [&](const aeonb_image_desc& a, const aeonb_image_desc& b) { return cost(a) > cost(b); });
         auto* dev = static_cast<const aeonb_image_desc*>(ctx->upload(ordered.data(), sizeof(aeonb_image_desc) * n));
-        const char* why = nullptr;
-        cudaError_t e   = launch_aug_pack(dev, ordered.data(), n, *layout, pixel_stride, aligned, ctx->stream, &why);
+        const char*  why = nullptr;
+        launch_timer timer(ctx, AEONB_KERNEL_IMAGE, ctx->profiling ? aeonb_image_batch_bytes(descs, n, layout) : 0);
+        cudaError_t  e   = launch_aug_pack(dev, ordered.data(), n, *layout, pixel_stride, aligned, ctx->stream, &why);
         if (why)
             throw error(AEONB_ERR_UNSUPPORTED, why);
         if (e != cudaSuccess)
@@ -329,7 +412,8 @@ int aeonb_jpeg_backend_batch(aeonb_ctx* ctx, const aeonb_jpeg_desc* descs, int n
         AEONB_CUDA(cudaSetDevice(ctx->device));
         auto* ddev = static_cast<const aeonb_jpeg_desc*>(ctx->upload(descs, sizeof(aeonb_jpeg_desc) * n));
         auto* wdev = static_cast<const int2*>(ctx->upload(work.data(), sizeof(int2) * work.size()));
-        cudaError_t e = launch_jpeg_backend(ddev, wdev, (int)work.size(), smem, ctx->stream);
+        launch_timer timer(ctx, AEONB_KERNEL_JPEG_BACKEND, ctx->profiling ? aeonb_jpeg_backend_bytes(descs, n) : 0);
+        cudaError_t  e = launch_jpeg_backend(ddev, wdev, (int)work.size(), smem, ctx->stream);
         if (e != cudaSuccess)
             throw error(AEONB_ERR_CUDA, cuda_message("jpeg back-end kernel launch", e));
         ctx->launches++;
@@ -406,7 +490,17 @@ int aeonb_jpeg_entropy_batch(aeonb_ctx* ctx, const aeonb_entropy_desc* descs, in
             descs = ordered.data();
         }
         auto* ddev = static_cast<const aeonb_entropy_desc*>(ctx->upload(descs, sizeof(aeonb_entropy_desc) * n));
-        cudaError_t e = launch_jpeg_entropy(ddev, n, any_parallel, any_serial, jpeg_entropy_min_segment(), ctx->stream);
+        int64_t bytes = 0; // compressed scan in + the coefficient blocks of the region out
+        if (ctx->profiling)
+            for (int i = 0; i < n; ++i)
+            {
+                const aeonb_entropy_desc& r = descs[i];
+                bytes += r.scan_size;
+                for (int c = 0; c < r.ncomp; ++c)
+                    bytes += (int64_t)(r.roi[2] - r.roi[0]) * r.hs[c] * (r.roi[3] - r.roi[1]) * r.vs[c] * 128;
+            }
+        launch_timer timer(ctx, AEONB_KERNEL_ENTROPY, bytes);
+        cudaError_t  e = launch_jpeg_entropy(ddev, n, any_parallel, any_serial, jpeg_entropy_min_segment(), ctx->stream);
         if (e != cudaSuccess)
             throw error(AEONB_ERR_CUDA, cuda_message("jpeg entropy kernel launch", e));
         ctx->launches += (any_parallel ? 1 : 0) + (any_serial ? 1 : 0);

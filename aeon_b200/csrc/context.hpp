@@ -67,6 +67,17 @@ namespace aeonb
     };
 }
 
+namespace aeonb
+{
+    // one timed kernel launch of a context whose profile is switched on
+    struct profile_span
+    {
+        int         kind;
+        cudaEvent_t begin, end;
+        int64_t     bytes;
+    };
+}
+
 struct aeonb_ctx
 {
     int                                device     = 0;
@@ -75,6 +86,10 @@ struct aeonb_ctx
     std::vector<aeonb::staging_slot>   ring;      // descriptor staging
     size_t                             ring_next  = 0;
     int64_t                            launches   = 0; // kernels launched through this context
+    bool                               profiling  = false; // aeonb_ctx_profile: time every kernel with a pair of events
+    std::vector<aeonb::profile_span>   spans;              // launches not yet added to the totals
+    std::vector<cudaEvent_t>           event_pool;
+    aeonb_kernel_profile               totals[AEONB_KERNEL_KINDS] = {};
 
     // Copies `bytes` of host data to the device on the stream; the returned device pointer is
     // valid for kernels enqueued after this call.
@@ -83,6 +98,17 @@ struct aeonb_ctx
 
 namespace aeonb
 {
+    // Brackets the launch(es) of one batch call: counts them and, when the context's profile is on, records a timing
+    // event on the context's stream before and after.
+    struct launch_timer
+    {
+        launch_timer(aeonb_ctx* ctx, int kind, int64_t algorithmic_bytes);
+        ~launch_timer();
+        launch_timer(const launch_timer&) = delete;
+        aeonb_ctx* ctx;
+        int        span = -1;
+    };
+
     // Validates a batch of image descriptors (throws std::invalid_argument / aeonb::error); reports the
     // common source pixel stride and whether every destination slot is 16-byte aligned.
     void check_image_batch(const aeonb_image_desc* d, int n, const aeonb_image_layout& L, int& pixel_stride, bool& aligned);

@@ -379,8 +379,12 @@ namespace aeonb
             {
                 if (!have_sof)
                     bad("scan before frame header");
+                if (send - s < 1)
+                    bad("bad scan header");
                 const int ns = s[0];
-                if (!f.progressive && (ns != f.info.ncomp || send - s < 1 + 2 * ns))
+                if (send - s < 1 + 2 * ns + 3) // component selectors, then Ss, Se, Ah/Al
+                    bad("bad scan header");
+                if (!f.progressive && ns != f.info.ncomp)
                     bad("non-interleaved scans are not supported");
                 f.first_sos  = p - 2;
                 f.stream_end = end;

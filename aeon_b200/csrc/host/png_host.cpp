@@ -263,7 +263,7 @@ namespace aeonb
         struct chunks
         {
             std::vector<uint8_t> idat;
-            uint8_t              palette[256][3];
+            uint8_t              palette[256][3] = {};
             int                  palette_size = 0;
         };
 

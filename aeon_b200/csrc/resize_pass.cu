@@ -394,6 +394,7 @@ extern "C" int aeonb_resize_batch(aeonb_ctx* ctx, const aeonb_resize_desc* descs
         auto*      jdev = static_cast<const area_job*>(ctx->upload(jobs.data(), sizeof(area_job) * n));
         const int  per  = (int)std::min<int64_t>((most + 255) / 256, 148 * 8);
         const dim3 grid((unsigned)std::max(per, 1), (unsigned)n);
+        launch_timer timer(ctx, AEONB_KERNEL_OTHER, 0);
         resize_area_kernel<<<grid, 256, 0, ctx->stream>>>(jdev);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess)

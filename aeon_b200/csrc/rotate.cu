@@ -189,6 +189,7 @@ extern "C" int aeonb_rotate_batch(aeonb_ctx* ctx, const aeonb_rotate_desc* descs
         auto*      jdev = static_cast<const rotate_job*>(ctx->upload(jobs.data(), sizeof(rotate_job) * n));
         const int  per  = (int)std::min<int64_t>((most + 255) / 256, 148 * 8); // blocks per record
         const dim3 grid((unsigned)std::max(per, 1), (unsigned)n);
+        launch_timer timer(ctx, AEONB_KERNEL_OTHER, 0);
         rotate_kernel<<<grid, 256, 0, ctx->stream>>>(jdev);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess)
@@ -230,6 +231,7 @@ extern "C" int aeonb_orient_batch(aeonb_ctx* ctx, const aeonb_orient_desc* descs
         auto*      jdev = static_cast<const orient_job*>(ctx->upload(jobs.data(), sizeof(orient_job) * n));
         const int  per  = (int)std::min<int64_t>((most + 255) / 256, 148 * 8);
         const dim3 grid((unsigned)std::max(per, 1), (unsigned)n);
+        launch_timer timer(ctx, AEONB_KERNEL_OTHER, 0);
         orient_kernel<<<grid, 256, 0, ctx->stream>>>(jdev);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess)

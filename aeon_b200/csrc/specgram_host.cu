@@ -205,7 +205,8 @@ int aeonb_specgram_batch(aeonb_ctx* ctx, const aeonb_specgram_desc* descs, int n
         AEONB_CUDA(cudaSetDevice(ctx->device));
         const specgram_tables& t = specgram_tables_for(ctx->device, *cfg);
         auto* dev = static_cast<const aeonb_specgram_desc*>(ctx->upload(descs, sizeof(aeonb_specgram_desc) * n));
-        cudaError_t e = t.launch(dev, n, *cfg, ctx->stream);
+        launch_timer timer(ctx, AEONB_KERNEL_SPECGRAM, ctx->profiling ? aeonb_specgram_bytes(descs, n, cfg) : 0);
+        cudaError_t  e = t.launch(dev, n, *cfg, ctx->stream);
         if (e != cudaSuccess)
             throw error(AEONB_ERR_CUDA, cuda_message("spectrogram kernel launch", e));
         ctx->launches++;

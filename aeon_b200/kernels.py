@@ -33,6 +33,17 @@ class Context:
     def synchronize(self):
         L.check(self.lib.aeonb_ctx_synchronize(self.handle))
 
+    def profile(self, enable=True):
+        """Switches the per-kernel timing of this context on (clearing the totals) or off."""
+        L.check(self.lib.aeonb_ctx_profile(self.handle, int(bool(enable))))
+
+    def profile_read(self):
+        """{kernel kind: {"launches", "ms", "algorithmic_bytes"}} of the launches since the profile was switched on."""
+        out = (L.KernelProfile * len(L.KERNEL_KINDS))()
+        L.check(self.lib.aeonb_ctx_profile_read(self.handle, out))
+        return {name: {"launches": int(out[i].launches), "ms": float(out[i].ms), "algorithmic_bytes": int(out[i].algorithmic_bytes)}
+                for i, name in enumerate(L.KERNEL_KINDS)}
+
     @property
     def stream(self):
         return self.lib.aeonb_ctx_stream(self.handle)

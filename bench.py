@@ -3,11 +3,14 @@ configuration (batch 256, float32 normalised output), next to the CPU path on th
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-A step is one batch of 256 synthetic records through JPEG back end + augmentation/packing.
-`value` times the two kernels with the entropy-decoded coefficients already resident in HBM;
-`e2e` times the provider call from encoded JPEG bytes in host memory to the finished batch in
-host memory (entropy decode on the host, H2D, kernels, D2H).  Under torchrun every rank runs
-its own batches on its own GPU (no collective on the data path).
+A step is one batch of 256 synthetic records.  `value` times the three kernels of a step -- JPEG entropy
+decoding, JPEG back end, augmentation / packing -- with the compressed scans already resident in HBM; `e2e`
+times the provider call from encoded JPEG bytes in host memory to the finished batch in pinned host memory
+(header parsing and parameter draws on the host, H2D of the scans, kernels, D2H).  Both regions are repeated
+and the median repeat is reported.  The other four benchmark configurations (uint8 classification, SSD, video,
+audio) are measured through the same provider call and reported under `configs`, with per-kernel device times
+from the library's own event profile.  Under torchrun every rank runs its own batches on its own GPU (no
+collective on the data path).
 """
 import argparse
 import ctypes as C
@@ -16,6 +19,7 @@ import os
 import struct
 import subprocess
 import sys
+import tempfile
 import threading
 import time
 
@@ -25,46 +29,144 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-BATCH = 256
-N_IMAGES = 1024
-OUT = 224
 MEAN = [123.7 / 255, 116.3 / 255, 103.5 / 255]
 STD = [58.4 / 255, 57.1 / 255, 57.4 / 255]
-AUG = {"type": "image", "crop_enable": True, "center": False, "do_area_scale": True, "scale": [0.08, 1.0],
-       "horizontal_distortion": [0.75, 1.3333334], "flip_enable": True, "contrast": [0.6, 1.4],
-       "brightness": [0.6, 1.4], "saturation": [0.6, 1.4], "hue": [-18, 18], "lighting": [0.0, 0.1],
-       "mean": MEAN, "stddev": STD}
-ETL = [{"type": "image", "height": OUT, "width": OUT, "channels": 3, "channel_major": True, "output_type": "float",
-        "bgr_to_rgb": True}, {"type": "label", "binary": True}]
-WORKLOAD = "config2: 1024 synthetic q90 4:2:0 JPEGs (W,H~U[256,512]), random-area crop + flip + full photometric, 224x224x3 float32 CHW normalised, batch 256"
+AUG_C1 = {"type": "image", "crop_enable": True, "center": False, "do_area_scale": True, "scale": [0.08, 1.0],
+          "horizontal_distortion": [0.75, 1.3333334], "flip_enable": True}
+AUG_C2 = dict(AUG_C1, contrast=[0.6, 1.4], brightness=[0.6, 1.4], saturation=[0.6, 1.4], hue=[-18, 18], lighting=[0.0, 0.1],
+              mean=MEAN, stddev=STD)
+SSD_CLASSES = ["class%02d" % i for i in range(20)]
+SSD_SAMPLERS = [{"max_sample": 1, "max_trials": 1}] + [
+    {"max_sample": 1, "max_trials": 50, "sampler": {"scale": [0.3, 1.0], "aspect_ratio": [0.5, 2.0]}, "sample_constraint": c}
+    for c in ({"min_jaccard_overlap": 0.1}, {"min_jaccard_overlap": 0.3}, {"min_jaccard_overlap": 0.5},
+              {"min_jaccard_overlap": 0.7}, {"min_jaccard_overlap": 0.9}, {"max_jaccard_overlap": 1.0})]
+
+# The five benchmark configurations: aeon's own JSON (etl + augmentation blocks), batch size, and how many synthetic
+# records the benchmark cycles through (`records`; the data sets the configurations name are larger: 1024 pictures,
+# 512 SSD pictures, 256 clips, 512 audio clips -- the parity tests use the generators below at any size).
+WORKLOADS = {
+    "config1": {
+        "batch": 128, "records": 512, "seed": 1001, "kind": "image",
+        "describe": "config1: synthetic q90 4:2:0 JPEGs (W,H~U[256,512]), random-area crop + flip, 224x224x3 uint8 CHW, batch 128",
+        "etl": [{"type": "image", "height": 224, "width": 224, "channels": 3, "channel_major": True, "output_type": "uint8_t"},
+                {"type": "label", "binary": True}],
+        "augmentation": [AUG_C1]},
+    "config2": {
+        "batch": 256, "records": 1024, "seed": 1001, "kind": "image",
+        "describe": "config2: 1024 synthetic q90 4:2:0 JPEGs (W,H~U[256,512]), random-area crop + flip + full photometric, "
+                    "224x224x3 float32 CHW normalised, batch 256",
+        "etl": [{"type": "image", "height": 224, "width": 224, "channels": 3, "channel_major": True, "output_type": "float",
+                 "bgr_to_rgb": True}, {"type": "label", "binary": True}],
+        "augmentation": [AUG_C2]},
+    "config3": {
+        "batch": 32, "records": 128, "seed": 1003, "kind": "ssd",
+        "describe": "config3: synthetic 500x375 q90 JPEGs with 1-8 boxes over 20 classes, expand [1,4] p=0.5, IoU-constrained "
+                    "patch sampling, 300x300x3 float32 + box buffers, batch 32",
+        "etl": [{"type": "localization_ssd", "height": 300, "width": 300, "max_gt_boxes": 64, "class_names": SSD_CLASSES},
+                {"type": "image", "height": 300, "width": 300, "output_type": "float"}],
+        "augmentation": [{"type": "image", "crop_enable": False, "flip_enable": True, "expand_ratio": [1.0, 4.0],
+                          "expand_probability": 0.5, "emit_constraint_type": "center", "batch_samplers": SSD_SAMPLERS}]},
+    "config4": {
+        "batch": 32, "records": 64, "seed": 1004, "kind": "video",
+        "describe": "config4: synthetic MJPEG AVI clips of 16 frames 171x128, per-frame crop to 112x112 + flip, uint8 CxTxHxW, batch 32",
+        "etl": [{"type": "video", "max_frame_count": 16, "frame": {"height": 112, "width": 112, "channels": 3}},
+                {"type": "label", "binary": True}],
+        "augmentation": [{"type": "image", "frame": {"type": "image", "scale": [0.875, 0.875], "center": False, "flip_enable": True}}]},
+    "config5": {
+        "batch": 64, "records": 128, "seed": 1005, "kind": "audio",
+        "describe": "config5: synthetic 16 kHz int16 clips of 1-16 s, 20 ms Hann frames at 10 ms stride, 320-point DFT, 64 mel "
+                    "filters, log, 1599 x 64 float32 per clip, batch 64",
+        "etl": [{"type": "audio", "frame_length": 320, "frame_stride": 160, "max_samples": 256000, "num_filters": 64,
+                 "sample_rate": 16000, "window_type": "hann", "feature_type": "mfsc"}, {"type": "label", "binary": True}],
+        "augmentation": []},
+}
+HEADLINE = "config2"
 
 
-# DRAM bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum) from the captures summarised under profiles/
-# (in the three-kernel chain part of the coefficient planes and pictures stays in the 126 MB L2 between kernels, so the
-# back end's DRAM traffic is below its algorithmic bytes)
-TRAFFIC = {"jpeg_entropy": 92.9e6, "jpeg_backend": 72.0e6, "aug_pack": 150.9e6}
+def gradient_picture(rng, h, w):
+    """Smooth random gradients per channel + uniform +-20 noise (stands in for ImageNet / VOC / UCF101 frames)."""
+    yy, xx = np.mgrid[0:h, 0:w]
+    img = np.empty((h, w, 3), np.float32)
+    for c in range(3):
+        a, b = rng.uniform(-0.4, 0.4, 2)
+        img[..., c] = rng.uniform(40, 215) + a * xx + b * yy
+    img += rng.uniform(-20, 20, img.shape).astype(np.float32)
+    return np.clip(img, 0, 255).astype(np.uint8)
 
 
-def make_dataset(seed, n):
-    """Seeded stand-in for ImageNet-shaped inputs: smooth gradients + uniform +-20 noise, JPEG q=90."""
+def make_records(name, n, seed=None):
+    """Seeded synthetic records of a benchmark configuration: a list of tuples of bytes, one element per etl entry."""
     import cv2
-    rng = np.random.default_rng(seed)
+    w = WORKLOADS[name]
+    rng = np.random.default_rng(w["seed"] if seed is None else seed)
     recs = []
-    for _ in range(n):
-        h, w = (int(v) for v in rng.integers(256, 513, 2))
-        yy, xx = np.mgrid[0:h, 0:w]
-        img = np.empty((h, w, 3), np.float32)
-        for c in range(3):
-            a, b = rng.uniform(-0.4, 0.4, 2)
-            img[..., c] = rng.uniform(40, 215) + a * xx + b * yy
-        img += rng.uniform(-20, 20, img.shape).astype(np.float32)
-        ok, enc = cv2.imencode(".jpg", np.clip(img, 0, 255).astype(np.uint8), [cv2.IMWRITE_JPEG_QUALITY, 90])
-        recs.append((enc.tobytes(), struct.pack("<i", int(rng.integers(0, 1000)))))
+    if w["kind"] == "image":
+        for _ in range(n):
+            h, wd = (int(v) for v in rng.integers(256, 513, 2))
+            enc = cv2.imencode(".jpg", gradient_picture(rng, h, wd), [cv2.IMWRITE_JPEG_QUALITY, 90])[1]
+            recs.append((enc.tobytes(), struct.pack("<i", int(rng.integers(0, 1000)))))
+    elif w["kind"] == "ssd":
+        for _ in range(n):
+            objs = []
+            for _ in range(int(rng.integers(1, 9))):
+                x0, y0 = int(rng.integers(0, 500 - 9)), int(rng.integers(0, 375 - 9))
+                objs.append({"name": SSD_CLASSES[int(rng.integers(0, 20))], "difficult": bool(rng.integers(2)),
+                             "bndbox": {"xmin": x0, "ymin": y0, "xmax": int(rng.integers(x0 + 8, 500)), "ymax": int(rng.integers(y0 + 8, 375))}})
+            ann = {"object": objs, "size": {"width": 500, "height": 375, "depth": 3}}
+            enc = cv2.imencode(".jpg", gradient_picture(rng, 375, 500), [cv2.IMWRITE_JPEG_QUALITY, 90])[1]
+            recs.append((json.dumps(ann).encode(), enc.tobytes()))
+    elif w["kind"] == "video":
+        with tempfile.TemporaryDirectory() as tmp:
+            path = os.path.join(tmp, "clip.avi")
+            for i in range(n):
+                vw = cv2.VideoWriter(path, cv2.CAP_OPENCV_MJPEG, cv2.VideoWriter_fourcc(*"MJPG"), 25, (171, 128))
+                base = gradient_picture(rng, 128, 171 + 3 * 16)   # a gradient moving 3 pixels per frame
+                for t in range(16):
+                    vw.write(np.ascontiguousarray(base[:, 3 * t:3 * t + 171]))
+                vw.release()
+                recs.append((open(path, "rb").read(), struct.pack("<i", int(rng.integers(0, 101)))))
+    elif w["kind"] == "audio":
+        for i in range(n):
+            seconds = float(rng.uniform(1.0, 16.0))
+            t = np.arange(int(seconds * 16000)) / 16000.0
+            x = np.zeros_like(t)
+            for _ in range(int(rng.integers(1, 6))):
+                x += rng.uniform(0.05, 0.3) * np.sin(2 * np.pi * rng.uniform(80, 7000) * t + rng.uniform(0, 6.28))
+            x += rng.normal(0, 0.05, len(t))
+            recs.append((np.clip(x * 32767 / 2, -32768, 32767).astype(np.int16).tobytes(), struct.pack("<i", i)))
     return recs
 
 
+def provider_config(name, seed=1234, **extra):
+    w = WORKLOADS[name]
+    cfg = {"batch_size": w["batch"], "random_seed": seed, "etl": w["etl"], "augmentation": w["augmentation"]}
+    cfg.update(extra)
+    return cfg
+
+
+def video_frames(blob):
+    """The frames of an MJPEG AVI clip the way aeon's MotionJpegCapture reads them (src/cap_mjpeg_decoder.cpp:132-147,
+    src/avi.cpp): every '00dc' chunk of the 'movi' list through cv::imdecode; an empty chunk repeats the previous frame.
+    (CPU arm and parity oracle; the clips of the benchmark are plain RIFF files written by OpenCV's MJPEG writer.)"""
+    import cv2
+    frames = []
+    at = blob.find(b"movi")
+    end = blob.find(b"idx1", at)
+    end = len(blob) if end < 0 else end
+    at += 4
+    while at + 8 <= end:
+        tag, size = blob[at:at + 4], struct.unpack_from("<I", blob, at + 4)[0]
+        if tag[2:] in (b"dc", b"db"):
+            if size:
+                frames.append(cv2.imdecode(np.frombuffer(blob, np.uint8, size, at + 8), cv2.IMREAD_COLOR))
+            elif frames:
+                frames.append(frames[-1].copy())
+        at += 8 + size + (size & 1)
+    return frames
+
+
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed regions run."""
 
     def __init__(self, index):
         self.rows = []
@@ -100,44 +202,42 @@ class ClockSampler:
                 "samples": len(rows)}
 
 
+def host_workers():
+    """aeon's worker count: hardware threads minus min(2, threads / 8) (src/util.cpp:360-370)."""
+    hw = os.cpu_count() or 1
+    return max(1, hw - min(2, hw // 8))
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# CPU arm: the reference's per-record call sequence on the OpenCV binary (oracle/pipeline.py with fast=True), one process
+# per core, records dealt round-robin -- aeon's thread pool takes records the same way (src/thread_pool.hpp:155-162).
+# ---------------------------------------------------------------------------------------------------------------------
+
 _CPU_STATE = {}
 
 
 def _cpu_worker(args):
-    """One worker process: the reference's per-record call sequence (OpenCV binary) over its share of the
-    records, repeated until the deadline.  Returns the number of records it finished."""
     import cv2
-    from oracle import cv2_path as cvp
+    from oracle.pipeline import PipelineOracle
     rank, workers, deadline = args
-    blobs, params = _CPU_STATE["blobs"], _CPU_STATE["params"]
+    name, recs = _CPU_STATE["name"], _CPU_STATE["recs"]
     cv2.setNumThreads(1)
-    out = np.empty((3, OUT, OUT), np.float32)
+    orc = PipelineOracle(provider_config(name, decode_size=len(recs)), fast=True)
     done = 0
     while True:
-        for i in range(rank, len(blobs), workers):
-            img = cvp.extract(blobs[i])
-            out[...] = cvp.load_image(cvp.transform_single_image(img, params[i]), True, True, "float", MEAN, STD)
+        for i in range(rank, len(recs), workers):
+            orc.cursor = i     # record i draws from engine slot i: the same parameters whichever process takes it
+            orc.batch([recs[i]], video_frames)
             done += 1
         if time.time() >= deadline:
             return done
 
 
-def cpu_path(workers, recs, seconds, seed=1234):
-    """The reference's CPU path on the host cores: `workers` processes (aeon uses pinned threads; processes keep
-    the python glue of this port from serialising on the interpreter lock), one record per task, for about
-    `seconds` of wall time.  Returns (records/s, records)."""
+def cpu_path(name, workers, recs, seconds):
+    """`workers` processes (aeon uses pinned threads; processes keep the python glue of this port from serialising on
+    the interpreter lock) for about `seconds` of wall time.  Returns (records/s, records)."""
     import multiprocessing as mp
-    import cv2
-    from oracle import params as oparams
-    factory = oparams.ParamFactory(AUG)
-    engines = oparams.slot_engines(seed, BATCH)
-    blobs = [np.frombuffer(blob, np.uint8) for blob, _ in recs]
-    # the seeded parameter draws are sequential host work in both arms; they are drawn up front here
-    params = []
-    for i, arr in enumerate(blobs):
-        h, w = cv2.imdecode(arr, cv2.IMREAD_COLOR).shape[:2]
-        params.append(factory.make_params(engines[i % BATCH], w, h, OUT, OUT))
-    _CPU_STATE["blobs"], _CPU_STATE["params"] = blobs, params
+    _CPU_STATE["name"], _CPU_STATE["recs"] = name, recs
     with mp.get_context("fork").Pool(workers) as pool:
         pool.map(_cpu_worker, [(r, workers, 0.0) for r in range(workers)])  # warm the workers up (one pass each)
         t0 = time.time()
@@ -146,120 +246,76 @@ def cpu_path(workers, recs, seconds, seed=1234):
     return sum(counts) / dt, sum(counts)
 
 
-def host_workers():
-    hw = os.cpu_count() or 1
-    return max(1, hw - min(2, hw // 8))
-
-
 def run_reference(args, rank, world):
     if rank != 0:
         return
-    recs = make_dataset(1001, N_IMAGES)
+    name = args.workload
+    w = WORKLOADS[name]
+    n = min(w["records"], 256 if w["kind"] != "image" else w["records"])
+    if w["kind"] == "video":
+        # OpenCV's video writer starts threads of its own; worker processes forked after that can block in OpenCV, so
+        # the clips are written in a process of their own
+        import multiprocessing as mp
+        with mp.get_context("spawn").Pool(1) as pool:
+            recs = pool.apply(make_records, (name, n))
+    else:
+        recs = make_records(name, n)
     workers = host_workers()
     t0 = time.perf_counter()
-    value, total = cpu_path(workers, recs, args.cpu_seconds)
+    value, total = cpu_path(name, workers, recs, args.cpu_seconds)
     wall = time.perf_counter() - t0
     line = {"impl": "reference", "metric": "augmented records/sec at 224^2", "value": value, "unit": "records/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * BATCH / value,
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * w["batch"] / value,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-            "config": {"workload": WORKLOAD},
+            "config": {"workload": w["describe"]},
             "cpu_baseline": {"value": value, "unit": "records/s", "cores": workers, "kind": "port",
-                             "sample": "%d records in %.1f s; the reference's OpenCV call sequence (imdecode, resize, transform, "
-                                       "cvtColor, convertTo, split) through python cv2, one process per core" % (total, wall)},
+                             "sample": "%d records in %.1f s; the reference's per-record call sequence (imdecode, resize, transform, "
+                                       "cvtColor, convertTo, split; box arithmetic; DFT) on the OpenCV binary through python, one "
+                                       "process per core" % (total, wall)},
             "e2e": {"value": value, "unit": "records/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=40)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="b200")
-    ap.add_argument("--pixel-stride", type=int, default=3)
-    ap.add_argument("--cpu-seconds", type=float, default=12.0)
-    ap.add_argument("--stages", default="all",
-                    help="kernels-only experiments: comma list of photometric stages to keep (matrix,hue,contrast,lighting) or 'all'/'none'")
-    ap.add_argument("--null-source", action="store_true", help="kernels-only experiment: image kernel without sources (store path only)")
-    ap.add_argument("--full-decode", action="store_true", help="decode whole pictures instead of the crop regions")
-    ap.add_argument("--entropy", default="device", choices=["device", "host"],
-                    help="where JPEG Huffman decoding runs: on the GPU (the timed step then starts from the compressed scans "
-                         "resident in HBM) or on the host (the timed step starts from coefficient planes resident in HBM)")
-    ap.add_argument("--serial-kernels", action="store_true",
-                    help="time the three kernels of every step back to back on one stream (default: steps pipelined over two streams)")
-    ap.add_argument("--kernels-only", action="store_true",
-                    help="time the resident-input kernels only (used for profiler captures; e2e and cpu_baseline are null)")
-    args = ap.parse_args()
-    rank = int(os.environ.get("RANK", 0))
-    local_rank = int(os.environ.get("LOCAL_RANK", 0))
-    world = int(os.environ.get("WORLD_SIZE", 1))
-    if args.impl == "reference":
-        run_reference(args, rank, world)
-        return
+def cpu_arm(name, seconds):
+    """The CPU arm of one configuration in a process of its own (before this one touches CUDA)."""
+    r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", "1", "--workload", name,
+                        "--cpu-seconds", str(seconds)], capture_output=True, text=True)
+    for ln in r.stdout.splitlines():
+        if ln.startswith("{"):
+            return json.loads(ln)["cpu_baseline"]
+    return None
 
-    # The CPU baseline runs in its own process (before this one touches CUDA): rank 0, N=1 timing only.
-    cpu_line = None
-    if rank == 0 and world == 1 and not args.kernels_only and args.cpu_seconds > 0:
-        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", "1",
-                            "--cpu-seconds", str(args.cpu_seconds)], capture_output=True, text=True)
-        for ln in r.stdout.splitlines():
-            if ln.startswith("{"):
-                cpu_line = json.loads(ln)
 
+# ---------------------------------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------------------------------
+
+def resident_batches(ctx, recs, batch, on_dev, out, keep):
+    """Descriptor sets for the headline configuration with every input of the kernels resident in HBM: per batch the
+    entropy descriptors (compressed scans + tables; `on_dev`) or host-decoded coefficient planes, the back-end descriptors
+    and the image descriptors, built the way the provider builds them (region decoding, seeded draws).  Returns
+    (batches, check) where check = (device plane, host-decoded plane) of one component for a cross-check."""
     import torch
-    import torch.distributed as dist
     from aeon_b200 import _lib as L, kernels as K
-    from aeon_b200.provider import Provider
-
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    ctx = K.Context(local_rank)
-    lib = ctx.lib
-    dev = torch.device("cuda", local_rank)
-    warmup = max(args.warmup, 3)
-
-    recs = make_dataset(1001 + rank, N_IMAGES)  # each rank owns its shard of records
-    n_batches = N_IMAGES // BATCH
-
-    # ---------------- resident inputs.  --entropy device: the compressed scans, Huffman and quantiser tables sit in HBM and
-    # the step is entropy kernel -> JPEG back end -> image kernel.  --entropy host: the coefficient planes sit in HBM
-    # (decoded once on the host) and the step is the last two kernels.
-    pix = args.pixel_stride
-    on_dev = args.entropy == "device"
-    batches = []
-    check_plane = None
-    with torch.cuda.stream(ctx.torch_stream):
-        out = torch.empty((BATCH, 3, OUT, OUT), dtype=torch.float32, device=dev)
-    layout = K.make_layout(OUT, OUT, L.F32, True, True, MEAN, STD)
-    keep = []
-    for b in range(n_batches):
-        jd = (L.JpegDesc * BATCH)()
-        idesc = (L.ImageDesc * BATCH)()
-        ed = (L.EntropyDesc * BATCH)()
-        status = torch.zeros(BATCH, dtype=torch.int32, device=dev)
+    lib, dev = ctx.lib, torch.device("cuda", ctx.device)
+    aug = WORKLOADS[HEADLINE]["augmentation"][0]
+    OUT = 224
+    batches, check = [], None
+    for b in range(len(recs) // batch):
+        jd, idesc, ed = (L.JpegDesc * batch)(), (L.ImageDesc * batch)(), (L.EntropyDesc * batch)()
+        status = torch.zeros(batch, dtype=torch.int32, device=dev)
         keep.append(status)
         ent_bytes = 0
-        ws = (C.c_int32 * BATCH)()
-        hs = (C.c_int32 * BATCH)()
-        infos = []
-        for i in range(BATCH):
-            infos.append(K.jpeg_parse(recs[b * BATCH + i][0]))
-            ws[i], hs[i] = infos[i].width, infos[i].height
-        drawn = (C.c_double * (24 * BATCH))()
-        L.check(lib.aeonb_draw_params(json.dumps(AUG).encode(), 1234 + b, BATCH, BATCH, ws, hs, OUT, OUT, drawn))
-        p = np.array(drawn).reshape(BATCH, 24)
-        st_on = {"matrix", "hue", "contrast", "lighting"} if args.stages == "all" else set(args.stages.split(","))
-        for i in range(BATCH):
-            info = infos[i]
-            blob = recs[b * BATCH + i][0]
+        infos = [K.jpeg_parse(recs[b * batch + i][0]) for i in range(batch)]
+        ws, hs = (C.c_int32 * batch)(*[i.width for i in infos]), (C.c_int32 * batch)(*[i.height for i in infos])
+        drawn = (C.c_double * (24 * batch))()
+        L.check(lib.aeonb_draw_params(json.dumps(aug).encode(), 1234 + b, batch, batch, ws, hs, OUT, OUT, drawn))
+        p = np.array(drawn).reshape(batch, 24)
+        for i in range(batch):
+            info, blob = infos[i], recs[b * batch + i][0]
             cx, cy, cw, ch = (int(v) for v in p[i, 0:4])
-            # only the MCUs the crop box can touch are decoded (what the provider does for every record)
-            roi = (C.c_int32 * 4)(0, 0, info.blocks_w[0] // info.hs[0], info.blocks_h[0] // info.vs[0])
-            if not args.full_decode:
-                L.check(lib.aeonb_jpeg_roi_for_crop(C.byref(info), cx, cy, cw, ch, roi))
+            roi = (C.c_int32 * 4)()   # only the MCUs the crop box can touch are decoded (what the provider does)
+            L.check(lib.aeonb_jpeg_roi_for_crop(C.byref(info), cx, cy, cw, ch, roi))
             mw, mh = 8 * info.hs[0], 8 * info.vs[0]
             rx, ry = roi[0] * mw, roi[1] * mh
             rw, rh = min(info.width, roi[2] * mw) - rx, min(info.height, roi[3] * mh) - ry
@@ -288,51 +344,196 @@ def main():
                 x.status = status.data_ptr() + 4 * i
                 for k in range(4):
                     x.roi[k] = roi[k]
-                ent_bytes += int(x.scan_size) + sum(c.nbytes for c in coefs)
             for c in range(info.ncomp):
                 qt = torch.from_numpy(quants[c].view(np.int16)).to(dev)
                 if on_dev:   # the entropy kernel fills the plane every step; the host result is kept for one cross-check
                     ct = torch.empty((coefs[c].size,), dtype=torch.int16, device=dev)
                     ed[i].coef[c] = ct.data_ptr()
-                    if check_plane is None:
-                        check_plane = (ct, coefs[c].copy())
+                    if check is None:
+                        check = (ct, coefs[c].copy())
                 else:
                     ct = torch.from_numpy(coefs[c]).to(dev)
                 keep += [ct, qt]
                 d.coef[c], d.quant[c] = ct.data_ptr(), qt.data_ptr()
-            pitch = (rw * pix + 15) // 16 * 16
+            pitch = (rw * 3 + 15) // 16 * 16
             pbuf = torch.empty((rh, pitch), dtype=torch.uint8, device=dev)
             keep.append(pbuf)
-            d.dst, d.dst_pitch, d.dst_pixel_stride = pbuf.data_ptr(), pitch, pix
+            d.dst, d.dst_pitch, d.dst_pixel_stride = pbuf.data_ptr(), pitch, 3
             e = idesc[i]
-            e.src, e.src_pitch, e.src_w, e.src_h = pbuf.data_ptr(), pitch, rw, rh
-            e.src_pixel_stride = pix
+            e.src, e.src_pitch, e.src_w, e.src_h, e.src_pixel_stride = pbuf.data_ptr(), pitch, rw, rh, 3
             e.canvas_w, e.canvas_h, e.canvas_x, e.canvas_y = info.width, info.height, rx, ry
             e.crop_x, e.crop_y, e.crop_w, e.crop_h = cx, cy, cw, ch
             e.out_w, e.out_h, e.interp, e.flip = OUT, OUT, L.INTERP_LINEAR, int(p[i, 6])
             light = (C.c_float * 3)(*[float(v) for v in p[i, 12:15]])
-            L.check(lib.aeonb_image_desc_set_photometric(
-                C.byref(e), float(p[i, 9]) if "contrast" in st_on else 1.0, float(p[i, 10]) if "matrix" in st_on else 1.0,
-                float(p[i, 11]) if "matrix" in st_on else 1.0, int(p[i, 8]) if "hue" in st_on else 0,
-                light if "lighting" in st_on else None, float(p[i, 15])))
+            L.check(lib.aeonb_image_desc_set_photometric(C.byref(e), float(p[i, 9]), float(p[i, 10]), float(p[i, 11]), int(p[i, 8]),
+                                                         light, float(p[i, 15])))
             e.dst = out.data_ptr() + i * 3 * OUT * OUT * 4
-            if args.null_source:
-                e.src = None
-        batches.append((jd, idesc, ed, ent_bytes))
-    torch.cuda.synchronize()
-    jpeg_bytes_alg = [int(lib.aeonb_jpeg_backend_bytes(b[0], BATCH)) for b in batches]
-    aug_bytes_alg = [int(lib.aeonb_image_batch_bytes(b[1], BATCH, C.byref(layout))) for b in batches]
-    ent_bytes_alg = [b[3] for b in batches]
+        batches.append((jd, idesc, ed))
+    return batches, check
 
-    def kernel_step(b):
-        jd, idesc, ed, _ = batches[b % n_batches]
+
+def summarize(times_ms):
+    """Median / min / max of repeated timings of the same region."""
+    a = np.sort(np.asarray(times_ms, np.float64))
+    return {"median": float(np.median(a)), "min": float(a[0]), "max": float(a[-1]), "repeats": int(len(a))}
+
+
+def pipelined(prov, chunks, bufs, steps, depth, to_device):
+    """`steps` provider calls with `depth` batches in flight, every result waited for, oldest first; returns seconds."""
+    import torch
+    submit = prov.submit_device if to_device else prov.submit_host
+    t0 = time.perf_counter()
+    tickets = []
+    for i in range(steps):
+        tickets.append(submit(chunks[i % len(chunks)], bufs[i % depth]))
+        if i >= depth - 1:
+            prov.wait(tickets[i - (depth - 1)])
+    for j in range(max(steps - (depth - 1), 0), steps):
+        prov.wait(tickets[j])
+    torch.cuda.synchronize()
+    return time.perf_counter() - t0
+
+
+def provider_buffers(prov, depth, device, dev):
+    """`depth` sets of output buffers for a provider: pinned host memory, or device memory."""
+    import torch
+    from aeon_b200.kernels import _TORCH_DTYPE
+    sets = []
+    for _ in range(depth):
+        s = {}
+        for name, dims, dt, _ in prov.outputs:
+            shape = (prov.batch_size,) + dims
+            t = torch.zeros(shape, dtype=_TORCH_DTYPE[dt], device=dev) if device else torch.zeros(shape, dtype=_TORCH_DTYPE[dt]).pin_memory()
+            s[name] = t if device else t.numpy()
+        sets.append(s)
+    return sets
+
+
+def measure_config(ctx, name, threads, peak, repeats, dev):
+    """One of the other benchmark configurations through the provider: records/s with the batch left in device memory
+    and copied to pinned host memory (pipelined calls, median of `repeats`), and the device time of each kernel with
+    its algorithmic bytes from the context's event profile."""
+    from aeon_b200.provider import Provider
+    w = WORKLOADS[name]
+    recs = make_records(name, w["records"])
+    batch = w["batch"]
+    chunks = [recs[i:i + batch] for i in range(0, len(recs), batch)]
+    prov = Provider(ctx, provider_config(name, decode_threads=threads))
+    DEPTH = 3
+    steps = max(2 * len(chunks), DEPTH + 1)
+    out = {"workload": w["describe"], "batch": batch, "batches_cycled": len(chunks)}
+    for key, to_device in (("e2e_device_output", True), ("e2e", False)):
+        bufs = provider_buffers(prov, DEPTH, to_device, dev)
+        pipelined(prov, chunks, bufs, DEPTH + 1, DEPTH, to_device)   # warm-up
+        secs = [pipelined(prov, chunks, bufs, steps, DEPTH, to_device) for _ in range(repeats)]
+        s = summarize([1e3 * t / steps for t in secs])
+        st = prov.stats()
+        out[key] = {"value": batch / (s["median"] * 1e-3), "unit": "records/s", "ms_per_batch": s,
+                    "h2d_bytes_per_step": st["h2d_bytes"], "d2h_bytes_per_step": st["d2h_bytes"]}
+    # per-kernel device time: blocking calls, so that nothing else of this process runs beside the timed kernel
+    bufs = provider_buffers(prov, 1, True, dev)
+    ctx.profile(True)
+    n_prof = max(len(chunks), 4)
+    for i in range(n_prof):
+        prov.wait(prov.submit_device(chunks[i % len(chunks)], bufs[0]))
+    prof = ctx.profile_read()
+    ctx.profile(False)
+    out["kernels"] = {}
+    for k, v in prof.items():
+        if v["launches"]:
+            ms = v["ms"] / v["launches"]
+            alg = v["algorithmic_bytes"] / v["launches"]
+            gbs = alg / (ms * 1e-3) / 1e9
+            out["kernels"][k] = {"ms": ms, "launches_per_batch": v["launches"] / n_prof, "algorithmic_bytes": alg, "gbs": gbs,
+                                 "frac": gbs / peak}
+    prov.close()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS), help="configuration the reference arm times")
+    ap.add_argument("--repeats", type=int, default=10, help="how often each timed region is repeated (the median is reported)")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--entropy", default="device", choices=["device", "host"],
+                    help="where JPEG Huffman decoding runs: on the GPU (the timed step then starts from the compressed scans "
+                         "resident in HBM) or on the host (the timed step starts from coefficient planes resident in HBM)")
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="time the resident-input kernels of the headline configuration only (used for profiler captures)")
+    ap.add_argument("--only-config", default=None, choices=sorted(WORKLOADS),
+                    help="measure one configuration through the provider and print its entry (used for profiler captures)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", 0))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    # The CPU arms run in processes of their own (before this one touches CUDA): rank 0, N=1 only.
+    cpu_lines = {}
+    if rank == 0 and world == 1 and not args.kernels_only and not args.only_config and args.cpu_seconds > 0:
+        cpu_lines[HEADLINE] = cpu_arm(HEADLINE, args.cpu_seconds)
+        for name in sorted(WORKLOADS):
+            if name != HEADLINE:
+                cpu_lines[name] = cpu_arm(name, max(2.0, args.cpu_seconds / 4))
+
+    import torch
+    import torch.distributed as dist
+    from aeon_b200 import _lib as L, kernels as K
+    from aeon_b200.provider import Provider
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = K.Context(local_rank)
+    lib = ctx.lib
+    dev = torch.device("cuda", local_rank)
+    warmup = max(args.warmup, 3)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    peak_kind = "measured" if "hbm_gbs" in peaks else "fallback"
+    threads = max(1, host_workers() // world)
+
+    if args.only_config:
+        print(json.dumps(measure_config(ctx, args.only_config, threads, peak, max(args.repeats, 1), dev)), flush=True)
+        return
+
+    W = WORKLOADS[HEADLINE]
+    BATCH, OUT = W["batch"], 224
+    recs = make_records(HEADLINE, W["records"], W["seed"] + rank)  # each rank owns its shard of records
+    n_batches = len(recs) // BATCH
+
+    # ---------------- resident inputs.  --entropy device: the compressed scans, Huffman and quantiser tables sit in HBM and
+    # the step is entropy kernel -> JPEG back end -> image kernel.  --entropy host: the coefficient planes sit in HBM
+    # (decoded once on the host) and the step is the last two kernels.
+    on_dev = args.entropy == "device"
+    keep = []
+    with torch.cuda.stream(ctx.torch_stream):
+        out = torch.empty((BATCH, 3, OUT, OUT), dtype=torch.float32, device=dev)
+    layout = K.make_layout(OUT, OUT, L.F32, True, True, MEAN, STD)
+    batches, check_plane = resident_batches(ctx, recs, BATCH, on_dev, out, keep)
+    torch.cuda.synchronize()
+
+    def kernel_step(c, b):
+        jd, idesc, ed = batches[b % n_batches]
         if on_dev:
-            L.check(lib.aeonb_jpeg_entropy_batch(ctx.handle, ed, BATCH))
-        L.check(lib.aeonb_jpeg_backend_batch(ctx.handle, jd, BATCH))
-        L.check(lib.aeonb_image_batch(ctx.handle, idesc, BATCH, C.byref(layout)))
+            L.check(lib.aeonb_jpeg_entropy_batch(c.handle, ed, BATCH))
+        L.check(lib.aeonb_jpeg_backend_batch(c.handle, jd, BATCH))
+        L.check(lib.aeonb_image_batch(c.handle, idesc, BATCH, C.byref(layout)))
 
     if on_dev:   # one cross-check of the device decoder against the host decoder before anything is timed
-        kernel_step(0)
+        kernel_step(ctx, 0)
         torch.cuda.synchronize()
         if not np.array_equal(check_plane[0].cpu().numpy(), check_plane[1]):
             raise SystemExit("device entropy decoder disagrees with the host decoder")
@@ -350,19 +551,19 @@ def main():
     # the first while the back end and the image kernel of step i run on the second, which fills the tail of the entropy
     # kernel (few long streams left) with the other two kernels' blocks.  Every step still runs its three kernels in order
     # on its own buffers (the four batch sets rotate; a set is reused only after its image kernel has finished).
-    two_streams = on_dev and not args.serial_kernels
+    two_streams = on_dev
     ctx2 = K.Context(local_rank) if two_streams else None
 
     def run_steps(count):
         """Enqueues `count` steps; returns the stream whose tail marks the end of the work."""
         if not two_streams:
             for i in range(count):
-                kernel_step(i)
+                kernel_step(ctx, i)
             return ts
         ts2 = ctx2.torch_stream
         aug_done = []
         for i in range(count):
-            jd, idesc, ed, _ = batches[i % n_batches]
+            jd, idesc, ed = batches[i % n_batches]
             if i >= n_batches:
                 ts.wait_event(aug_done[i - n_batches])
             L.check(lib.aeonb_jpeg_entropy_batch(ctx.handle, ed, BATCH))
@@ -379,9 +580,8 @@ def main():
 
     run_steps(warmup)
     barrier()
-    serial_out = None
     if two_streams:   # the pipelined order must give what the plain order gives
-        kernel_step(warmup - 1)
+        kernel_step(ctx, warmup - 1)
         torch.cuda.synchronize()
         serial_out = out.clone()
         run_steps(warmup)
@@ -390,145 +590,115 @@ def main():
             raise SystemExit("two-stream step order changed the output")
     barrier()
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    ev[0].record(ts)
-    if two_streams:
-        ctx2.torch_stream.wait_event(ev[0])
-    run_steps(args.steps).record_event(ev[1])
-    barrier()
-    kernel_ms = ev[0].elapsed_time(ev[1])
+    # the timed region: exactly `steps` steps between a barrier + synchronize on both sides, CUDA events on the
+    # launching stream; repeated, the median repeat is the reported one
+    repeats = max(args.repeats, 1)
+    kernel_times = []
+    for _ in range(repeats):
+        barrier()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        ev[0].record(ts)
+        if two_streams:
+            ctx2.torch_stream.wait_event(ev[0])
+        run_steps(args.steps).record_event(ev[1])
+        barrier()
+        t = torch.tensor([ev[0].elapsed_time(ev[1])], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)   # the slowest rank ends the step
+        kernel_times.append(float(t.item()))
+    kernel_stat = summarize([t / args.steps for t in kernel_times])
+    kernel_ms = kernel_stat["median"] * args.steps
 
-    # per-kernel durations (same launches, events between the two kernels)
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
-    for i in range(args.steps):
-        jd, idesc, ed, _ = batches[i % n_batches]
-        evs[i][0].record(ts)
-        if on_dev:
-            L.check(lib.aeonb_jpeg_entropy_batch(ctx.handle, ed, BATCH))
-        evs[i][1].record(ts)
-        L.check(lib.aeonb_jpeg_backend_batch(ctx.handle, jd, BATCH))
-        evs[i][2].record(ts)
-        L.check(lib.aeonb_image_batch(ctx.handle, idesc, BATCH, C.byref(layout)))
-        evs[i][3].record(ts)
-    barrier()
-    ent_ms = float(np.mean([e[0].elapsed_time(e[1]) for e in evs])) if on_dev else 0.0
-    jpeg_ms = float(np.mean([e[1].elapsed_time(e[2]) for e in evs]))
-    aug_ms = float(np.mean([e[2].elapsed_time(e[3]) for e in evs]))
-    ent_alg = float(np.mean([ent_bytes_alg[i % n_batches] for i in range(args.steps)]))
-    jpeg_alg = float(np.mean([jpeg_bytes_alg[i % n_batches] for i in range(args.steps)]))
-    aug_alg = float(np.mean([aug_bytes_alg[i % n_batches] for i in range(args.steps)]))
+    # per-kernel device times of the same launches, one kernel at a time on one stream (the library's event profile)
+    ctx.profile(True)
+    for i in range(max(args.steps, n_batches)):
+        kernel_step(ctx, i)
+    prof = ctx.profile_read()
+    ctx.profile(False)
+    per_kernel = {k: (v["ms"] / v["launches"], v["algorithmic_bytes"] / v["launches"]) for k, v in prof.items() if v["launches"]}
 
     if args.kernels_only:
         if rank == 0:
-            print(json.dumps({"kernels_only": True, "ms_per_step": kernel_ms / args.steps, "entropy_ms": ent_ms, "jpeg_ms": jpeg_ms, "aug_ms": aug_ms,
-                              "jpeg_gbs": jpeg_alg / jpeg_ms / 1e6, "aug_gbs": aug_alg / aug_ms / 1e6}), flush=True)
+            print(json.dumps({"kernels_only": True, "ms_per_step": kernel_stat, "kernels": {k: {"ms": v[0], "gbs": v[1] / v[0] / 1e6}
+                                                                                            for k, v in per_kernel.items()}}), flush=True)
             sampler.stop()
         return
 
     # ---------------- end to end through the provider: encoded bytes in host memory -> batch in host memory
-    threads = max(1, host_workers() // world)
-    cfg = {"batch_size": BATCH, "random_seed": 1234, "etl": ETL, "augmentation": [AUG], "decode_threads": threads,
-           "scratch_pixel_stride": pix, "roi_decode": not args.full_decode, "entropy_decode": args.entropy}
+    cfg = provider_config(HEADLINE, decode_threads=threads, entropy_decode=args.entropy)
     prov = Provider(ctx, cfg)
     DEPTH = 3   # batches in flight: the host prepares batch i while the GPU decodes i-1 and i-2 is copied to the host
-    host_out = [{"image": torch.empty((BATCH, 3, OUT, OUT), dtype=torch.float32).pin_memory().numpy(),
-                 "label": np.zeros((BATCH, 1), np.int32)} for _ in range(DEPTH)]
     chunks = [recs[b * BATCH:(b + 1) * BATCH] for b in range(n_batches)]
     e2e_steps = max(DEPTH + 1, min(args.steps, 48))
-    # warm-up through the same pipelined call, touching every host buffer of the rotation
-    warm = [prov.submit_host(chunks[i % n_batches], host_out[i % DEPTH]) for i in range(DEPTH)]
-    for t in warm:
-        prov.wait(t)
-    for i in range(max(warmup, 3)):
-        prov.wait(prov.submit_host(chunks[i % n_batches], host_out[i % DEPTH]))
-    barrier()
-    # every batch's result is read back to host memory (wait) inside the timed region, oldest first
-    t0 = time.perf_counter()
-    tickets = []
-    checksum = 0.0
-    for i in range(e2e_steps):
-        tickets.append(prov.submit_host(chunks[i % n_batches], host_out[i % DEPTH]))
-        if i >= DEPTH - 1:
-            j = i - (DEPTH - 1)
-            prov.wait(tickets[j])
-            checksum += float(host_out[j % DEPTH]["image"][0, 0, 0, 0])
-    for j in range(max(e2e_steps - (DEPTH - 1), 0), e2e_steps):
-        prov.wait(tickets[j])
-        checksum += float(host_out[j % DEPTH]["image"][0, 0, 0, 0])
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    st = prov.stats()
+    results = {}
+    stats = {}
+    for key, to_device in (("e2e", False), ("e2e_device_output", True)):
+        bufs = provider_buffers(prov, DEPTH, to_device, dev)
+        pipelined(prov, chunks, bufs, max(warmup, DEPTH + 1), DEPTH, to_device)   # warm-up touches every buffer of the rotation
+        times = []
+        for _ in range(repeats):
+            barrier()
+            t = torch.tensor([1e3 * pipelined(prov, chunks, bufs, e2e_steps, DEPTH, to_device)], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            times.append(float(t.item()))
+        results[key] = summarize([t / e2e_steps for t in times])
+        stats[key] = prov.stats()
+    prov.close()
 
-    # the same call with the batch left in device memory (what a consumer on the GPU takes): no device -> host copy
-    dev_out = [{"image": torch.empty((BATCH, 3, OUT, OUT), dtype=torch.float32, device=dev),
-                "label": torch.zeros((BATCH, 1), dtype=torch.int32, device=dev)} for _ in range(DEPTH)]
-    for i in range(3):
-        prov.wait(prov.submit_device(chunks[i % n_batches], dev_out[0]))
-    barrier()
-    t0 = time.perf_counter()
-    tickets = []
-    for i in range(e2e_steps):
-        tickets.append(prov.submit_device(chunks[i % n_batches], dev_out[i % DEPTH]))
-        if i >= DEPTH - 1:
-            prov.wait(tickets[i - (DEPTH - 1)])
-    for j in range(max(e2e_steps - (DEPTH - 1), 0), e2e_steps):
-        prov.wait(tickets[j])
-    torch.cuda.synchronize()
-    dev_s = time.perf_counter() - t0
-    st_dev = prov.stats()
+    # ---------------- the other configurations (one GPU: they are not part of the scaling runs)
+    configs = {}
+    if world == 1:
+        for name in sorted(WORKLOADS):
+            if name != HEADLINE:
+                configs[name] = measure_config(ctx, name, threads, peak, max(3, repeats // 2), dev)
+                configs[name]["cpu_baseline"] = cpu_lines.get(name)
     clocks = sampler.stop() if sampler else None
 
-    times = torch.tensor([kernel_ms, e2e_s * 1e3, dev_s * 1e3], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    kernel_ms, e2e_ms, dev_ms = (float(v) for v in times.cpu())
-
     if rank == 0:
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except OSError:
-            pass
-        peak = float(peaks.get("hbm_gbs", 6650.0))
-        peak_kind = "measured" if "hbm_gbs" in peaks else "fallback"
-        per_kernel = {"jpeg_backend": (jpeg_ms, jpeg_alg), "aug_pack": (aug_ms, aug_alg)}
-        if on_dev:
-            per_kernel["jpeg_entropy"] = (ent_ms, ent_alg)
         dominant = max(per_kernel, key=lambda k: per_kernel[k][0])
         d_ms, d_alg = per_kernel[dominant]
         achieved = d_alg / (d_ms * 1e-3) / 1e9
-        cpu_base = cpu_line["cpu_baseline"] if cpu_line else None
-        value = world * BATCH * args.steps / (kernel_ms * 1e-3)
+        value = world * BATCH / (kernel_stat["median"] * 1e-3)
         line = {
             "metric": "augmented records/sec at 224^2", "value": value, "unit": "records/s", "n_gpus": world,
-            "steps": args.steps, "warmup": warmup, "ms_per_step": kernel_ms / args.steps, "higher_is_better": True,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": kernel_stat["median"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "l2": "four distinct batches (1024 records) cycle; their inputs total several hundred MB, larger than the 126 MB L2",
-                       "scratch_pixel_stride": pix, "records_per_gpu_per_step": BATCH,
-                       "decode": "whole pictures" if args.full_decode else "crop regions only (MCUs the crop box can touch)",
-                       "entropy_decode": args.entropy,
-                       "kernel_streams": 2 if two_streams else 1,
+            "ms_per_step_repeats": kernel_stat,
+            "config": {"workload": W["describe"],
+                       "l2": "four distinct batches (1024 records) cycle; their inputs total several hundred MB, larger than the 126 MB L2",
+                       "records_per_gpu_per_step": BATCH, "decode": "crop regions only (MCUs the crop box can touch)",
+                       "entropy_decode": args.entropy, "kernel_streams": 2 if two_streams else 1,
                        "resident_input": "compressed JPEG scans + tables" if on_dev else "coefficient planes (Huffman-decoded on the host, untimed)"},
             "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_kind": peak_kind, "frac_of_8tbs_nominal": achieved / 8000.0,
-                         # DRAM bytes per launch of that kernel from the ncu capture summarised under profiles/
-                         "traffic": TRAFFIC.get(dominant),
-                         "traffic_source": "profiles/%s_config2.md (ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch)" % dominant,
+                         "traffic": TRAFFIC["bytes"].get(dominant) if args.entropy == "device" else None,
+                         "traffic_source": TRAFFIC["source"],
                          "kernels": {k: {"ms": v[0], "algorithmic_bytes": v[1], "gbs": v[1] / (v[0] * 1e-3) / 1e9,
                                          "frac": v[1] / (v[0] * 1e-3) / 1e9 / peak} for k, v in per_kernel.items()}},
-            "cpu_baseline": cpu_base,
-            "e2e": {"value": world * BATCH * e2e_steps / (e2e_ms * 1e-3), "unit": "records/s",
-                    "h2d_bytes_per_step": st["h2d_bytes"], "d2h_bytes_per_step": st["d2h_bytes"],
-                    "steps": e2e_steps, "host_decode_threads_per_gpu": threads, "batches_in_flight": DEPTH},
+            "cpu_baseline": cpu_lines.get(HEADLINE),
+            "e2e": {"value": world * BATCH / (results["e2e"]["median"] * 1e-3), "unit": "records/s",
+                    "h2d_bytes_per_step": stats["e2e"]["h2d_bytes"], "d2h_bytes_per_step": stats["e2e"]["d2h_bytes"],
+                    "steps": e2e_steps, "ms_per_step_repeats": results["e2e"], "host_threads_per_gpu": threads, "batches_in_flight": DEPTH},
             # not part of the contract: encoded bytes in host memory -> batch left in device memory, same pipelined call
-            "e2e_device_output": {"value": world * BATCH * e2e_steps / (dev_ms * 1e-3), "unit": "records/s",
-                                  "h2d_bytes_per_step": st_dev["h2d_bytes"], "d2h_bytes_per_step": st_dev["d2h_bytes"]},
+            "e2e_device_output": {"value": world * BATCH / (results["e2e_device_output"]["median"] * 1e-3), "unit": "records/s",
+                                  "h2d_bytes_per_step": stats["e2e_device_output"]["h2d_bytes"],
+                                  "d2h_bytes_per_step": stats["e2e_device_output"]["d2h_bytes"],
+                                  "ms_per_step_repeats": results["e2e_device_output"]},
+            "configs": configs,
             "gpu_launches": (3 if on_dev else 2) * args.steps, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
-    prov.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+# DRAM bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum) of the kernels of the headline step, from the
+# captures summarised under profiles/ (same workload, same batch size; in the three-kernel chain part of the coefficient
+# planes and pictures stays in the 126 MB L2 between kernels, so a kernel's DRAM traffic can be below its algorithmic bytes).
+# Reported beside, never inside, the achieved figure, which comes from the algorithmic bytes and the time of this run.
+TRAFFIC = {"bytes": {"jpeg_entropy": 92.9e6, "jpeg_backend": 72.0e6, "aug_pack": 148.3e6},
+           "source": "profiles/*_config2.md (one launch each under ncu, config2 batch 256, device entropy decoding)"}
 
 
 if __name__ == "__main__":

@@ -51,6 +51,29 @@ void aeonb_ctx_destroy(aeonb_ctx* ctx);
 void* aeonb_ctx_stream(aeonb_ctx* ctx);
 int  aeonb_ctx_synchronize(aeonb_ctx* ctx);
 
+/* Per-kernel timing of a context: with the profile on, every batch call records a pair of CUDA events around its
+ * kernel on the context's stream.  aeonb_ctx_profile_read waits for the stream, adds the finished launches up and
+ * fills one entry per kernel kind: launches, summed device time, and the algorithmic bytes of those launches (each
+ * unique input byte once + each output byte once: what a bandwidth roofline divides by the time).  Switching the
+ * profile on clears the totals.  Works through every path that uses the context, the provider included. */
+enum aeonb_kernel_kind
+{
+    AEONB_KERNEL_ENTROPY = 0,      /* jpeg_entropy_parallel_kernel / jpeg_entropy_kernel */
+    AEONB_KERNEL_JPEG_BACKEND = 1, /* jpeg_backend_kernel */
+    AEONB_KERNEL_IMAGE = 2,        /* aug_pack_kernel */
+    AEONB_KERNEL_SPECGRAM = 3,     /* specgram_kernel / specgram_generic_kernel */
+    AEONB_KERNEL_OTHER = 4,        /* rotate, orient, resize passes, rcnn labels */
+    AEONB_KERNEL_KINDS = 5
+};
+typedef struct aeonb_kernel_profile
+{
+    int64_t launches;
+    double  ms;
+    int64_t algorithmic_bytes;
+} aeonb_kernel_profile;
+int aeonb_ctx_profile(aeonb_ctx* ctx, int enable);
+int aeonb_ctx_profile_read(aeonb_ctx* ctx, aeonb_kernel_profile out[AEONB_KERNEL_KINDS]);
+
 /* ------------------------------------------------------------------------------------------------
  * 1a. Image augmentation + packing kernel
  *     replaces image::transformer::transform_single_image (src/etl_image.cpp:146-202),
@@ -145,7 +168,9 @@ int64_t aeonb_image_batch_bytes(const aeonb_image_desc* descs, int n, const aeon
  * first call before starting any stream capture.  All calls share the one array: two calls whose
  * GPU work can overlap (different streams, or different host threads) race on it, so serialise
  * them.  `descs` must stay valid and unchanged until the call returns when it is pageable host
- * memory, and until the stream has consumed the copy when it is pinned host memory. */
+ * memory -- the copy of a pageable array is staged by the driver and the call then waits for it on
+ * the host -- and until the stream has consumed the copy when it is pinned host memory (the call
+ * then returns at once). */
 #define AEONB_NOALLOC_MAX_RECORDS 512
 int aeonb_image_batch_noalloc(const aeonb_image_desc* descs, int n, const aeonb_image_layout* layout, void* stream);
 

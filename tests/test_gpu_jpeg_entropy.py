@@ -1,4 +1,5 @@
-"""Device entropy decoder (one warp per JPEG stream) against the host decoder: identical coefficient planes."""
+"""Device entropy decoders (a thread block per JPEG stream decoding segments speculatively; one warp per stream for streams with
+restart markers) against the host decoder and against the oracle: identical coefficient planes."""
 import ctypes as C
 import os
 
@@ -116,3 +117,22 @@ def test_large_picture_and_many_streams(ctx, parallel):
     check(ctx, [big], parallel=parallel)
     small = [jpeg_bytes(gradient_image(rng, int(rng.integers(16, 64)), int(rng.integers(16, 64))), 80) for _ in range(40)]
     check(ctx, [small[i % 40] for i in range(600)], parallel=parallel)
+
+
+def test_device_decoder_against_the_oracle_planes(ctx, golden_dir, parallel):
+    """Both device kernels against oracle/jpeg.py's own Huffman decoder (not only against the library's host decoder)."""
+    import cv2
+    from aeon_b200 import kernels as K
+    from oracle import jpeg as ojpeg
+    rng = np.random.default_rng(67)
+    blobs = [jpeg_bytes(gradient_image(rng, 40, 56), 90), jpeg_bytes(gradient_image(rng, 33, 47), 75, [cv2.IMWRITE_JPEG_RST_INTERVAL, 2]),
+             jpeg_bytes(rng.integers(0, 256, (24, 24, 3), dtype=np.uint8), 100, [cv2.IMWRITE_JPEG_SAMPLING_FACTOR, cv2.IMWRITE_JPEG_SAMPLING_FACTOR_444]),
+             open(os.path.join(golden_dir, "img_2112_70.jpg"), "rb").read()]
+    got = K.jpeg_entropy_decode_device(ctx, blobs, None, parallel)
+    for i, blob in enumerate(blobs):
+        info, planes, quant, status = got[i]
+        co = ojpeg.entropy_decode(blob)
+        assert status == 0 and (info.width, info.height, info.ncomp) == (co.width, co.height, co.ncomp)
+        for c in range(info.ncomp):
+            mine = planes[c].cpu().numpy().reshape(info.blocks_h[c], info.blocks_w[c], 8, 8).transpose(0, 1, 3, 2)  # column-major blocks
+            assert np.array_equal(mine, co.blocks[c]), (i, c)

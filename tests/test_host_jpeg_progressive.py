@@ -69,3 +69,16 @@ def test_exif_orientation_tag_is_parsed():
     assert K.jpeg_parse(with_exif_orientation(blob, 9)).orientation == 1          # out of range: ignored, as OpenCV does
     broken = blob[:2] + b"\xff\xe1\x00\x0cExif\x00\x00II\x2a\x00" + blob[2:]        # truncated TIFF header
     assert K.jpeg_parse(broken).orientation == 1
+
+
+def test_truncated_scan_headers_are_rejected_not_read_past():
+    """A scan header cut short (its length field says 2, or fewer selector bytes than components) is a decode error."""
+    import cv2
+    from aeon_b200._lib import AeonError
+    img = gradient_image(np.random.default_rng(5), 24, 24)
+    for extra in ([], [cv2.IMWRITE_JPEG_PROGRESSIVE, 1]):
+        blob = cv2.imencode(".jpg", img, [cv2.IMWRITE_JPEG_QUALITY, 80] + extra)[1].tobytes()
+        at = blob.index(b"\xff\xda")
+        for cut in (blob[:at + 2] + b"\x00\x02", blob[:at + 2] + b"\x00\x03\x03", blob[:at + 2] + b"\x00\x08\x03\x01\x00\x02\x11\x03"):
+            with pytest.raises(AeonError):
+                planes(cut)

@@ -63,3 +63,32 @@ def test_noalloc_entry_rejects_oversized_batches(ctx):
     status = ctx.lib.aeonb_image_batch_noalloc(descs, n, C.byref(lay), None)
     assert status == L.ERR_INVALID
     assert b"at most 512" in ctx.lib.aeonb_last_error()
+
+
+def test_noalloc_entry_with_pinned_descriptors(ctx):
+    """Descriptors in pinned host memory: the copy is then truly asynchronous, and the array must stay unchanged until the
+    stream has consumed it -- which the test honours by synchronising before it touches the array again."""
+    from aeon_b200 import _lib as L, kernels as K
+    lib = ctx.lib
+    rng = np.random.default_rng(78)
+    dev = torch.device("cuda", ctx.device)
+    torch.cuda.set_device(ctx.device)
+    lay = K.make_layout(96, 80, L.U8, False)
+    stream = ctx.torch_stream
+    n = 7
+    srcs = [gradient_image(rng, int(rng.integers(64, 200)), int(rng.integers(64, 200))) for _ in range(n)]
+    params = [_params(rng, s.shape[1], s.shape[0], True) for s in srcs]
+    pinned = torch.zeros(n * C.sizeof(L.ImageDesc), dtype=torch.uint8).pin_memory()
+    descs = (L.ImageDesc * n).from_address(pinned.data_ptr())
+    with torch.cuda.stream(stream):
+        tsrc = [torch.from_numpy(s).to(dev) for s in srcs]
+        want = torch.zeros((n, 80, 96, 3), dtype=torch.uint8, device=dev)
+        got = torch.full((n, 80, 96, 3), 9, dtype=torch.uint8, device=dev)
+        K.image_batch(ctx, tsrc, params, want, lay)
+        for i in range(n):
+            K.fill_desc(descs[i], tsrc[i], params[i], got.data_ptr() + i * got.stride(0), lib)
+        L.check(lib.aeonb_image_batch_noalloc(descs, n, C.byref(lay), C.c_void_p(stream.cuda_stream)))
+        stream.synchronize()
+    assert torch.equal(got, want)
+    for i in range(n):
+        assert np.array_equal(got[i].cpu().numpy(), ops.transform_single_image(srcs[i], params[i]))
