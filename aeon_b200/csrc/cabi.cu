@@ -84,6 +84,18 @@ namespace aeonb
 
 using namespace aeonb;
 
+namespace aeonb
+{
+    // Descriptor arrays reach the device through this kernel, which reads the pinned host copy directly (pinned memory
+    // is mapped into the device's address space) -- not through the copy engine, where a few KB of descriptors would
+    // queue behind the megabytes of the next batch's staging upload and hold up the kernel that waits for them.
+    static __global__ void upload_kernel(int4* __restrict__ dst, const int4* __restrict__ src, size_t n16)
+    {
+        for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x)
+            dst[i] = src[i];
+    }
+}
+
 void* aeonb_ctx::upload(const void* host, size_t bytes)
 {
     staging_slot& slot = ring[ring_next];
@@ -100,7 +112,10 @@ void* aeonb_ctx::upload(const void* host, size_t bytes)
         slot.reserve(bytes);
     }
     std::memcpy(slot.host, host, bytes);
-    AEONB_CUDA(cudaMemcpyAsync(slot.dev, slot.host, bytes, cudaMemcpyHostToDevice, stream));
+    const size_t n16 = (bytes + 15) / 16; // both buffers are at least 64 KB and 256-byte aligned
+    upload_kernel<<<(unsigned)std::min<size_t>((n16 + 255) / 256, 32), 256, 0, stream>>>(static_cast<int4*>(slot.dev),
+                                                                                      static_cast<const int4*>(slot.host), n16);
+    AEONB_CUDA(cudaGetLastError());
     AEONB_CUDA(cudaEventRecord(slot.copied, stream));
     slot.busy = true;
     return slot.dev;

@@ -172,7 +172,13 @@ struct aeonb_provider
     // batch t-1 read its device copy.
     aeonb::pinned_buffer                 staging[2];
     aeonb::device_buffer                 staging_dev[2];
-    aeonb::device_buffer                 coef_dev;     // device entropy decoding: status words, coefficient planes, work areas
+    // device entropy decoding: status words, coefficient planes, work areas.  Two sets, taken in turn, so that the
+    // entropy kernel of batch t+1 (on a stream of its own) can run beside the back end and image kernel of batch t
+    aeonb::device_buffer                 coef_dev[2];
+    aeonb_ctx*                           m_entropy_ctx = nullptr;            // context whose stream carries the entropy kernels
+    cudaEvent_t                          m_entropy_done[2] = {nullptr, nullptr}; // planes of set p are complete
+    cudaEvent_t                          m_coef_free[2]    = {nullptr, nullptr}; // the back end has read set p (batch t-2)
+    bool                                 m_coef_free_valid[2] = {false, false};
     aeonb::device_buffer                 pixels_dev;   // decoded pictures
     aeonb::device_buffer                 oriented_dev; // pictures after the EXIF orientation pass
     aeonb::device_buffer                 rotated_dev;  // pictures after the rotation pass
@@ -194,7 +200,10 @@ struct aeonb_provider
     cudaEvent_t m_done[k_events]    = {nullptr, nullptr, nullptr, nullptr}; // batch t complete: m_done[t % k_events]
     cudaEvent_t m_kernels[k_events] = {nullptr, nullptr, nullptr, nullptr}; // the kernels of batch t have finished
     cudaStream_t m_copy             = nullptr; // device -> host copies of finished batches
-    cudaEvent_t m_trace[k_events][3] = {};     // AEONB_TRACE: start of uploads, end of kernels, end of delivery (timing events)
+    // AEONB_TRACE timing events per batch: 0 call start on the kernels' stream, 1 end of kernels, 2 end of delivery,
+    // 3 / 4 first and last byte of the staging upload, 5 / 6 entropy kernel begin / end, 7 back end begin
+    cudaEvent_t m_trace[k_events][8] = {};
+    int         m_trace_slot = 0; // slot of the batch being enqueued
     cudaStream_t m_upload           = nullptr; // host -> device copies of the staging sets: they run under the previous batch's kernels
     cudaEvent_t m_staged[2]         = {nullptr, nullptr}; // staging set p has been copied to the device (upload stream)
     bool        m_staged_valid[2]   = {false, false};

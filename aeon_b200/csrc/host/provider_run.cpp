@@ -167,6 +167,12 @@ aeonb_provider::~aeonb_provider()
         for (cudaEvent_t e : {m_uploaded[k], m_staged[k], m_consumed[k]})
             if (e)
                 cudaEventDestroy(e);
+    for (int k = 0; k < 2; ++k)
+        for (cudaEvent_t e : {m_entropy_done[k], m_coef_free[k]})
+            if (e)
+                cudaEventDestroy(e);
+    if (m_entropy_ctx)
+        aeonb_ctx_destroy(m_entropy_ctx);
     if (m_upload)
     {
         cudaStreamSynchronize(m_upload);
@@ -194,8 +200,20 @@ void aeonb_provider::wait_ticket(int64_t t)
         cudaEventElapsedTime(&kernels_to_done, m_trace[t % k_events][1], m_trace[t % k_events][2]);
         if (t >= 2 && m_trace[(t - 1) % k_events][2])
             cudaEventElapsedTime(&since_prev, m_trace[(t - 1) % k_events][2], m_trace[t % k_events][2]);
-        std::fprintf(stderr, "aeonb_provider_wait %lld: GPU upload+kernels %.3f ms, kernels->delivered %.3f ms, delivered after previous batch %.3f ms\n",
-                     (long long)t, up_to_kernels, kernels_to_done, since_prev);
+        float upload = 0, entropy = 0, rest = 0, ent_after_upload = 0;
+        cudaEvent_t* e = m_trace[t % k_events];
+        if (cudaEventQuery(e[4]) == cudaSuccess)
+            cudaEventElapsedTime(&upload, e[3], e[4]);
+        if (cudaEventQuery(e[6]) == cudaSuccess && cudaEventQuery(e[5]) == cudaSuccess)
+        {
+            cudaEventElapsedTime(&entropy, e[5], e[6]);
+            cudaEventElapsedTime(&ent_after_upload, e[4], e[5]);
+        }
+        if (cudaEventQuery(e[7]) == cudaSuccess)
+            cudaEventElapsedTime(&rest, e[7], e[1]);
+        std::fprintf(stderr, "aeonb_provider_wait %lld: GPU upload+kernels %.3f ms, kernels->delivered %.3f ms, delivered after previous batch %.3f ms"
+                             " | staging upload %.3f, upload end -> entropy begin %.3f, entropy %.3f, back end + image %.3f ms\n",
+                     (long long)t, up_to_kernels, kernels_to_done, since_prev, upload, ent_after_upload, entropy, rest);
     }
     check_entropy_status((int)(t % k_events));
 }
@@ -241,6 +259,13 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         for (cudaEvent_t& e : m_kernels)
             AEONB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         AEONB_CUDA(cudaStreamCreateWithFlags(&m_copy, cudaStreamNonBlocking));
+        for (int k = 0; k < 2; ++k)
+        {
+            AEONB_CUDA(cudaEventCreateWithFlags(&m_entropy_done[k], cudaEventDisableTiming));
+            AEONB_CUDA(cudaEventCreateWithFlags(&m_coef_free[k], cudaEventDisableTiming));
+        }
+        if (aeonb_ctx_create(ctx->device, nullptr, &m_entropy_ctx) != AEONB_OK)
+            throw error(AEONB_ERR_CUDA, aeonb_last_error());
     }
     // This batch is number m_ticket + 1.  Its device-side outputs use buffer set `par`, last used by batch
     // m_ticket - 1, whose copy to the host may still be running on the copy stream: kernels wait for it.
@@ -260,6 +285,7 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
             if (!e)
                 AEONB_CUDA(cudaEventCreate(&e));
         AEONB_CUDA(cudaEventRecord(m_trace[trace_slot][0], st));
+        m_trace_slot = trace_slot;
     }
 
     batch_plan B((int)stages.size());
@@ -738,7 +764,7 @@ void aeonb_provider::reserve_arenas(batch_plan& B, void* const* outs, bool on_de
         area_dev.reserve(B.area_bytes + 256);
     B.status_room = align_up(sizeof(int32_t) * (B.jobs.size() + 1), 256);
     if (B.coef_bytes > 0)
-        coef_dev.reserve(B.status_room + B.coef_bytes + 256);
+        coef_dev[par].reserve(B.status_room + B.coef_bytes + 256);
     B.produced.assign(outputs.size(), nullptr); // where each device-produced output is written
     for (size_t o = 0; o < outputs.size(); ++o)
     {
@@ -830,11 +856,17 @@ void aeonb_provider::stage_inputs(batch_plan& B, int par)
             }
             remaining[group_of(i)].fetch_sub(1, std::memory_order_release);
         }, !heavy);
+        // the calling thread copies too (it is awake already), then ships the slices as their last job finishes
+        pool->help();
+        static const bool trace = std::getenv("AEONB_TRACE") != nullptr;
+        if (trace && m_trace[m_trace_slot][3])
+            AEONB_CUDA(cudaEventRecord(m_trace[m_trace_slot][3], m_upload));
         cudaError_t copy_error = cudaSuccess;
         for (int g = 0; g < groups; ++g)
         {
-            while (remaining[g].load(std::memory_order_acquire) > 0)
-                std::this_thread::sleep_for(std::chrono::microseconds(20));
+            for (int spin = 0; remaining[g].load(std::memory_order_acquire) > 0; ++spin)
+                if (spin > 2000)
+                    std::this_thread::sleep_for(std::chrono::microseconds(20));
             const size_t begin = offset_of(first[g]);
             const size_t end   = first[g + 1] < nwork ? offset_of(first[g + 1]) : B.stage_bytes;
             if (end > begin && copy_error == cudaSuccess && !failure)
@@ -847,6 +879,11 @@ void aeonb_provider::stage_inputs(batch_plan& B, int par)
         if (failure)
             std::rethrow_exception(failure);
         AEONB_CUDA(copy_error);
+    }
+    {
+        static const bool trace = std::getenv("AEONB_TRACE") != nullptr;
+        if (trace && m_trace[m_trace_slot][4])
+            AEONB_CUDA(cudaEventRecord(m_trace[m_trace_slot][4], m_upload));
     }
     AEONB_CUDA(cudaEventRecord(m_staged[par], m_upload));
     m_staged_valid[par] = true;
@@ -865,7 +902,7 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n, int par)
     B.n_device_jobs = 0;
     if (njobs > 0)
     {
-        char* const cdev = static_cast<char*>(coef_dev.p);
+        char* const cdev = static_cast<char*>(coef_dev[par].p);
         vector<aeonb_entropy_desc> ed;
         for (int i = 0; i < njobs; ++i)
         {
@@ -885,8 +922,39 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n, int par)
         B.n_device_jobs = (int)ed.size();
         if (B.n_device_jobs > 0)
         {
-            check_status(aeonb_jpeg_entropy_batch(ctx, ed.data(), B.n_device_jobs));
+            // The entropy kernel runs on a stream of its own: it needs this batch's staged inputs and the coefficient set
+            // that the back end of two batches ago has read, nothing else -- so it runs beside the previous batch's back
+            // end and image kernel, whose blocks fill the SMs its last long streams leave idle.  (With the per-kernel
+            // profile on, everything stays on one stream: a timed kernel then runs alone.)
+            static const bool own_stream = [] {
+                const char* e = std::getenv("AEONB_ENTROPY_STREAM"); // 0: everything on the context's stream
+                return !e || std::atoi(e) != 0;
+            }();
+            aeonb_ctx* ectx = ctx->profiling || !own_stream ? ctx : m_entropy_ctx;
+            if (ectx != ctx)
+            {
+                AEONB_CUDA(cudaStreamWaitEvent(ectx->stream, m_staged[par], 0));
+                if (m_coef_free_valid[par])
+                    AEONB_CUDA(cudaStreamWaitEvent(ectx->stream, m_coef_free[par], 0));
+            }
+            static const bool trace = std::getenv("AEONB_TRACE") != nullptr;
+            if (trace && m_trace[m_trace_slot][5])
+                AEONB_CUDA(cudaEventRecord(m_trace[m_trace_slot][5], ectx->stream));
+            check_status(aeonb_jpeg_entropy_batch(ectx, ed.data(), B.n_device_jobs));
             h2d_bytes += (int64_t)(sizeof(aeonb_entropy_desc) * B.n_device_jobs);
+            if (trace && m_trace[m_trace_slot][6])
+                AEONB_CUDA(cudaEventRecord(m_trace[m_trace_slot][6], ectx->stream));
+            if (ectx != ctx)
+            {
+                ctx->launches += 1;
+                AEONB_CUDA(cudaEventRecord(m_entropy_done[par], ectx->stream));
+                AEONB_CUDA(cudaStreamWaitEvent(st, m_entropy_done[par], 0));
+            }
+        }
+        {
+            static const bool trace = std::getenv("AEONB_TRACE") != nullptr;
+            if (trace && m_trace[m_trace_slot][7])
+                AEONB_CUDA(cudaEventRecord(m_trace[m_trace_slot][7], st));
         }
         vector<aeonb_jpeg_desc> jd;
         jd.reserve(njobs);
@@ -917,6 +985,7 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n, int par)
         }
         check_status(aeonb_jpeg_backend_batch(ctx, jd.data(), (int)jd.size()));
         h2d_bytes += (int64_t)(sizeof(aeonb_jpeg_desc) * jd.size());
+
     }
     // Where a decoded picture stands for the passes that read it: the decoded region, or the turned copy.
     struct picture
@@ -1299,9 +1368,12 @@ void aeonb_provider::deliver(batch_plan& B, void* const* outs, int n, bool on_de
     {
         // on the kernels' stream: the next batch's entropy kernel rewrites these words
         m_status[slot].reserve(sizeof(int32_t) * B.n_device_jobs);
-        AEONB_CUDA(cudaMemcpyAsync(m_status[slot].p, coef_dev.p, sizeof(int32_t) * B.n_device_jobs, cudaMemcpyDeviceToHost, st));
+        AEONB_CUDA(cudaMemcpyAsync(m_status[slot].p, coef_dev[par].p, sizeof(int32_t) * B.n_device_jobs, cudaMemcpyDeviceToHost, st));
         d2h_bytes += (int64_t)(sizeof(int32_t) * B.n_device_jobs);
         m_status_count[slot] = B.n_device_jobs;
+        // from here on the entropy kernel of the batch after next may rewrite this coefficient set
+        AEONB_CUDA(cudaEventRecord(m_coef_free[par], st));
+        m_coef_free_valid[par] = true;
     }
     // Batches delivered to host memory are copied on a second stream, so that the next batch's uploads and
     // kernels do not queue behind this batch's (much longer) device -> host copy.

@@ -52,6 +52,28 @@ namespace aeonb
             m_wake_rest.notify_all();
     }
 
+    int worker_pool::help()
+    {
+        int ran = 0;
+        for (;;)
+        {
+            const int i = m_next.fetch_add(1);
+            if (i >= m_count)
+                return ran;
+            try
+            {
+                m_fn(i);
+            }
+            catch (...)
+            {
+                std::lock_guard<std::mutex> lk(m_mutex);
+                if (!m_error)
+                    m_error = std::current_exception();
+            }
+            ++ran;
+        }
+    }
+
     void worker_pool::wait()
     {
         std::unique_lock<std::mutex> lk(m_mutex);

@@ -30,6 +30,9 @@ namespace aeonb
         static constexpr int k_light = 3;
         void start(int count, std::function<void(int)> fn, bool light = false);
         void wait();
+        // The calling thread takes part in the job started last: runs fn(i) for indices it draws from the same counter until
+        // none is left.  Returns how many it ran.  (The workers' wake-up takes tens of microseconds; the caller is already awake.)
+        int help();
         void run(int count, std::function<void(int)> fn)
         {
             start(count, std::move(fn));
@@ -63,6 +66,7 @@ namespace aeonb
             if (bytes <= cap)
                 return;
             release();
+            bytes += bytes / 4; // head room: batch sizes wander with the drawn crop boxes, and growing stalls the pipeline
             AEONB_CUDA(cudaMallocHost(&p, bytes));
             cap = bytes;
         }
@@ -86,6 +90,7 @@ namespace aeonb
             if (bytes <= cap)
                 return;
             release();
+            bytes += bytes / 4; // head room, as above (cudaFree waits for the whole device)
             AEONB_CUDA(cudaMalloc(&p, bytes));
             cap = bytes;
         }
