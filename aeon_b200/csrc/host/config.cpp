@@ -168,6 +168,21 @@ namespace aeonb
         shape.shape = {1};
     }
 
+    blob_config::blob_config(json js)
+    {
+        js.erase("type");
+        required(js, "output_count");
+        output_count     = get_int(js, "output_count", 0);
+        output_type_name = get_string(js, "output_type", "float");
+        name             = get_string(js, "name", "");
+        check_output_type("output_type", output_type_name);
+        verify_config("blob", {"output_count", "output_type", "name", "type"}, js);
+        if (output_count <= 0)
+            throw invalid_argument("blob: output_count must be positive");
+        shape.otype = output_type::from_name(output_type_name);
+        shape.shape = {(int64_t)output_count};
+    }
+
     video_config::video_config(json js)
     {
         if (js.is_null())

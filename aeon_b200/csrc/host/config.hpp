@@ -63,6 +63,17 @@ namespace aeonb
         explicit label_config(json js);
     };
 
+    // aeon blob::config (src/etl_blob.hpp:36-63): bytes copied as they are into a buffer of output_count elements
+    struct blob_config
+    {
+        std::string output_type_name = "float";
+        int         output_count     = 0;
+        std::string name;
+        shape_type  shape;
+        blob_config() = default;
+        explicit blob_config(json js);
+    };
+
     struct video_config
     {
         int          max_frame_count = 0;

@@ -216,6 +216,13 @@ aeonb_provider::aeonb_provider(aeonb_ctx* c, const json& cfg) : ctx(c)
             st.label = label_config(e);
             add(prefixed(st.label.name, "label"), st.label.shape, true);
         }
+        else if (t == "blob")
+        {
+            // provider::blob (src/provider.cpp:445-470)
+            st.kind = stage_kind::blob;
+            st.blob = blob_config(e);
+            add(prefixed(st.blob.name, "blob"), st.blob.shape, true);
+        }
         else if (t == "video")
         {
             st.kind  = stage_kind::video;

@@ -32,6 +32,7 @@ namespace aeonb
         image,
         mask, // pixelmask: a one-channel target picture that follows the image's geometry
         label,
+        blob, // bytes copied as they are (host only)
         video,
         ssd,
         audio,
@@ -45,6 +46,7 @@ namespace aeonb
         int          first_output = 0; // index of the stage's first output buffer
         image_config image;
         label_config label;
+        blob_config  blob;
         video_config video;
         ssd_config   ssd;
         audio_config audio;
@@ -173,9 +175,10 @@ struct aeonb_provider
     aeonb::pinned_buffer                 staging[2];
     aeonb::device_buffer                 staging_dev[2];
     // device entropy decoding: status words, coefficient planes, work areas.  Two sets, taken in turn, so that the
-    // entropy kernel of batch t+1 (on a stream of its own) can run beside the back end and image kernel of batch t
+    // entropy kernel of batch t+1 (on a stream of its own) can run beside the back end and image kernel of batch t,
+    // and beside the last long streams of batch t's own entropy kernel
     aeonb::device_buffer                 coef_dev[2];
-    aeonb_ctx*                           m_entropy_ctx = nullptr;            // context whose stream carries the entropy kernels
+    aeonb_ctx*                           m_entropy_ctx[2] = {nullptr, nullptr}; // contexts whose streams carry the entropy kernels, in turn
     cudaEvent_t                          m_entropy_done[2] = {nullptr, nullptr}; // planes of set p are complete
     cudaEvent_t                          m_coef_free[2]    = {nullptr, nullptr}; // the back end has read set p (batch t-2)
     bool                                 m_coef_free_valid[2] = {false, false};

@@ -171,8 +171,9 @@ aeonb_provider::~aeonb_provider()
         for (cudaEvent_t e : {m_entropy_done[k], m_coef_free[k]})
             if (e)
                 cudaEventDestroy(e);
-    if (m_entropy_ctx)
-        aeonb_ctx_destroy(m_entropy_ctx);
+    for (aeonb_ctx* e : m_entropy_ctx)
+        if (e)
+            aeonb_ctx_destroy(e);
     if (m_upload)
     {
         cudaStreamSynchronize(m_upload);
@@ -264,8 +265,9 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
             AEONB_CUDA(cudaEventCreateWithFlags(&m_entropy_done[k], cudaEventDisableTiming));
             AEONB_CUDA(cudaEventCreateWithFlags(&m_coef_free[k], cudaEventDisableTiming));
         }
-        if (aeonb_ctx_create(ctx->device, nullptr, &m_entropy_ctx) != AEONB_OK)
-            throw error(AEONB_ERR_CUDA, aeonb_last_error());
+        for (aeonb_ctx*& e : m_entropy_ctx)
+            if (aeonb_ctx_create(ctx->device, nullptr, &e) != AEONB_OK)
+                throw error(AEONB_ERR_CUDA, aeonb_last_error());
     }
     // This batch is number m_ticket + 1.  Its device-side outputs use buffer set `par`, last used by batch
     // m_ticket - 1, whose copy to the host may still be running on the copy stream: kernels wait for it.
@@ -725,6 +727,20 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
                 std::memcpy(out_host[sg.first_output].data() + (size_t)r * esz, &lbl, std::min<size_t>(esz, 4));
                 break;
             }
+            case stage_kind::blob:
+            {
+                if (size == 0)
+                    empty("blob");
+                const size_t room = outputs[sg.first_output].shape.byte_size();
+                if (size > room) // aeon copies without looking (src/etl_blob.hpp:98-102); a longer blob would overrun the buffer
+                {
+                    std::stringstream ss;
+                    ss << "blob of " << size << " bytes does not fit the " << room << " bytes of its output buffer, at idx " << r;
+                    throw std::runtime_error(ss.str());
+                }
+                std::memcpy(out_host[sg.first_output].data() + (size_t)r * room, data, size);
+                break;
+            }
             case stage_kind::audio:
             {
                 if (size == 0)
@@ -924,13 +940,14 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n, int par)
         {
             // The entropy kernel runs on a stream of its own: it needs this batch's staged inputs and the coefficient set
             // that the back end of two batches ago has read, nothing else -- so it runs beside the previous batch's back
-            // end and image kernel, whose blocks fill the SMs its last long streams leave idle.  (With the per-kernel
+            // end and image kernel, and (two such streams, taken in turn) beside the last long streams of the previous
+            // batch's entropy kernel: a launch lasts as long as its longest stream, the SMs of the others fall idle.  (With the per-kernel
             // profile on, everything stays on one stream: a timed kernel then runs alone.)
             static const bool own_stream = [] {
                 const char* e = std::getenv("AEONB_ENTROPY_STREAM"); // 0: everything on the context's stream
                 return !e || std::atoi(e) != 0;
             }();
-            aeonb_ctx* ectx = ctx->profiling || !own_stream ? ctx : m_entropy_ctx;
+            aeonb_ctx* ectx = ctx->profiling || !own_stream ? ctx : m_entropy_ctx[par];
             if (ectx != ctx)
             {
                 AEONB_CUDA(cudaStreamWaitEvent(ectx->stream, m_staged[par], 0));

@@ -254,7 +254,9 @@ int64_t aeonb_jpeg_backend_bytes(const aeonb_jpeg_desc* descs, int n);
 
 /* ------------------------------------------------------------------------------------------------
  * 1b'. JPEG entropy decoding on the device: the Huffman stage of cv::imdecode
- *      (src/etl_image.cpp:90), one warp per JPEG stream.  Fills the coefficient planes that
+ *      (src/etl_image.cpp:90).  A stream without restart markers that is given a work area is decoded by a whole
+ *      thread block (segments decoded speculatively, then synchronised on each other); other streams by one
+ *      warp that walks the stream serially.  Fills the coefficient planes that
  *      aeonb_jpeg_desc describes, so aeonb_jpeg_entropy_batch followed by aeonb_jpeg_backend_batch
  *      decodes a batch of JPEG files without per-record host work beyond header parsing.
  * ---------------------------------------------------------------------------------------------- */

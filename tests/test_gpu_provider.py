@@ -1,5 +1,6 @@
-"""End-to-end parity of the provider (host entropy decode + seeded draws + both kernels) with the
-record-level oracle, through the C ABI, on the benchmark configurations at reduced batch size."""
+"""End-to-end parity of the provider (header parsing and seeded draws on the host; entropy decoding, JPEG back end and
+image kernel on the GPU) with the record-level oracle, through the C ABI, on the benchmark configurations at reduced
+batch size and on every other stage the provider offers (tests/test_gpu_configs_full.py runs the stated batch sizes)."""
 import os
 import struct
 
@@ -591,3 +592,22 @@ def test_image_and_boundingbox_stage(ctx):
     cfg["augmentation"][0]["angle"] = [5, 10]
     with pytest.raises(AeonError, match="angle"):
         make_provider(ctx, cfg).run_host(recs)
+
+
+def test_blob_stage_copies_bytes_next_to_an_image(ctx):
+    """provider::blob (aeon src/provider.cpp:445-470): the element's bytes land unchanged in a buffer of output_count elements."""
+    from aeon_b200._lib import AeonError
+    cfg = {"batch_size": 4, "random_seed": 3,
+           "etl": [{"type": "image", "height": 32, "width": 32}, {"type": "blob", "output_count": 5, "output_type": "float"}],
+           "augmentation": [AUG_C1]}
+    rng = np.random.default_rng(50)
+    vecs = [rng.normal(size=5).astype(np.float32) for _ in range(4)]
+    recs = [(image_records(51 + i, 1)[0][0], v.tobytes()) for i, v in enumerate(vecs)]
+    got = make_provider(ctx, cfg).run_host(recs)
+    assert got["blob"].shape == (4, 5) and got["blob"].dtype == np.float32
+    assert np.array_equal(got["blob"], np.stack(vecs))
+    assert np.array_equal(got["image"], PipelineOracle({**cfg, "etl": cfg["etl"][:1]}).batch([(r[0],) for r in recs])["image"])
+    with pytest.raises(AeonError, match="does not fit"):
+        make_provider(ctx, cfg).run_host([(recs[0][0], b"x" * 21)] + recs[1:])
+    with pytest.raises(AeonError, match="received blob with size 0"):
+        make_provider(ctx, cfg).run_host([(recs[0][0], b"")] + recs[1:])
