@@ -389,49 +389,58 @@ namespace aeonb
         // positions are plain offsets), then cut into one segment per thread.  Every thread decodes its
         // segment starting from a guessed state (block 0 of an MCU, DC coefficient next) and records the
         // state in which it leaves the segment: the bit position of the first symbol that starts past the
-        // segment's end, the block's index inside the MCU and the zig-zag index.  It also remembers the
-        // block ends it passed (its "trail").  Rounds follow in which every thread takes its left
+        // segment's end, the block's index inside the MCU and the zig-zag index.  At seven evenly spaced
+        // checkpoints inside the segment it also notes the state of the first symbol at or past the
+        // checkpoint and the blocks completed so far.  Rounds follow in which every thread takes its left
         // neighbour's exit state as its entry state and, if that differs from the entry it used before,
-        // decodes again -- but only until it reaches a block end that is on its trail, because from there
-        // on it would repeat the earlier run and leave the segment in the same state.  Segment 0 always
+        // decodes again -- but only until it arrives at a checkpoint in the state noted there, because from
+        // there on it would repeat the earlier run and leave the segment in the same state.  Segment 0 always
         // starts in the true state, so after round r the first r+1 exits are true, and the rounds stop as
         // soon as nothing changes (at most one round per segment).  A prefix sum over the blocks each
         // segment completed gives every segment its first block number, and a last pass decodes each
         // segment once more from its now true entry state, this time storing the coefficients.  DC values
         // are stored as differences and summed up per component in a final scan.
         //
-        // Measured on a B200 with 256 streams of 25-85 KB (4:2:0, quality 90): 1.05 ms per batch for whole pictures
-        // (0.83 ms for the crop regions of the benchmark configuration) with 512 threads per block and segments of
-        // at least 160 bytes, against 20.9 ms for the one-warp kernel and about 10 ms for 14 host threads.  A wrong guess falls into step with the true decoder after about
-        // 10 blocks on average (the block's position inside the MCU has to match too), so shorter segments
-        // need more rounds and longer ones leave threads idle; 96-256 bytes measured within 5 % of each other.
-        // Tables of the block-parallel decoder: a 12-bit window decodes all but the rarest codes with one lookup (threads of
-        // a warp decode different segments, so a slow path taken by one of them is paid by all), and the canonical-code
-        // limits are kept monotonic so that the length of a longer code is a sum of comparisons, not a loop.
-        constexpr int PLOOK = 12;
-        // One lookup gives everything the symbol loop needs, packed so that each field is one bit-field extract away:
-        //   bits 0-4   total bits the symbol takes (code + value bits)        bits 5-9   code length
-        //   bits 10-13 number of value bits (AC size / DC category)           bits 14-20 advance of the zig-zag index:
-        //   bit  21    DC table: the symbol is not a category (> 15)                     run + 1, 16 for ZRL, 64 for end of block
+        // The threads of a warp sit in different segments, so the symbol loop is flat -- every pass of it
+        // decodes one symbol in every lane, whatever kind (DC category, AC run/size, end of block, zero run),
+        // with the block-end bookkeeping predicated.  With every warp of an SM decoding, the loop is bound by
+        // trips through the L1 pipeline (a load by 32 lanes in 32 places of the stream takes one per cache
+        // line), so the bits under the read position live in a 64-bit register and a lane loads one word when
+        // it has used one up; the checkpoints live in shared memory, lane-major, for the same reason.
+        //
+        // Measured on a B200 with 256 streams of 25-85 KB (4:2:0, quality 90, crop regions stored): 0.61 ms per batch
+        // with 512 threads per block and segments of at least 160 bytes (128-192 bytes within 3 %), against 20.9 ms
+        // for the one-warp kernel and about 10 ms for 14 host threads.  A wrong guess falls into step with the true
+        // decoder after about 10 blocks on average (the block's position inside the MCU has to match too), and not
+        // at all inside flat regions, where every block looks the same: there a chain of segments is settled one
+        // round per segment, which is what the slowest streams of a batch spend their time on (6.4 rounds on
+        // average, 11 at most in that batch).  Tried and no faster: warming up on the tail of the left neighbour's
+        // segment before the guess, a per-lane ring of stream words in shared memory topped up by asynchronous
+        // copies, reading the two words under the bit position afresh for every symbol.
+        constexpr int PLOOK = 12; // bits of the lookup window: AC tables
+        constexpr int DLOOK = 9;  //                            DC tables (few, short codes)
+        // One 16-bit lookup gives everything the symbol loop needs:
+        //   bits 0-4  total bits the symbol takes (code + value bits)     bits 5-8  number of value bits (AC size / DC category)
+        //   bits 9-15 advance of the zig-zag index: run + 1, 16 for ZRL, 64 for end of block, 1 for a DC category,
+        //             127 for an invalid code (which still takes bits and ends the block, so that a decoder in a wrong state moves on)
         // 0 = the code is longer than the window.
         __device__ __forceinline__ uint32_t pack_symbol(int len, int sym, bool is_ac)
         {
             const int s = sym & 15, r = sym >> 4;
-            const int kinc = is_ac ? (s ? r + 1 : (r == 15 ? 16 : 64)) : 0;
-            return (uint32_t)(len + s) | (uint32_t)len << 5 | (uint32_t)s << 10 | (uint32_t)kinc << 14 | (uint32_t)(!is_ac && r != 0) << 21;
+            const int kinc = is_ac ? (s ? r + 1 : (r == 15 ? 16 : 64)) : (r == 0 ? 1 : 127);
+            return (uint32_t)(len + s) | (uint32_t)s << 5 | (uint32_t)kinc << 9;
         }
-        constexpr uint32_t k_invalid_symbol = 16u | 16u << 5 | 64u << 14 | 1u << 22; // an invalid code: 16 bits, ends the block
+        constexpr uint32_t k_invalid_symbol = 16u | 127u << 9;
 
         struct par_table
         {
-            uint32_t lookup[1 << PLOOK];
+            uint16_t lookup[1 << PLOOK];
             int      limit[17]; // limit[len]: exclusive upper bound of the codes of length <= len, left-justified to 16 bits
             int      valoff[17];
             uint8_t  vals[256];
             int      is_ac;
-            int      window; // bits of the lookup window in use: PLOOK for AC tables, DLOOK for DC tables (few, short codes)
+            int      window; // bits of the lookup window in use
         };
-        constexpr int DLOOK = 9;
 
         // One thread fills the canonical-code limits of a table from the DHT form (16 counts); the values are copied by the caller.
         __device__ void build_par_table_head(par_table& T, const uint8_t* __restrict__ dht, bool is_ac, int* bad)
@@ -466,10 +475,10 @@ namespace aeonb
                 uint32_t e = 0;
                 if (i16 < T.limit[len])
                     e = pack_symbol(len, T.vals[((i >> (bits - len)) + T.valoff[len]) & 255], T.is_ac != 0);
-                T.lookup[i] = e;
+                T.lookup[i] = (uint16_t)e;
             }
         }
-        // A code longer than the window (or an invalid one, which still consumes bits so that a decoder in a wrong state moves on).
+        // A code longer than the window, or an invalid one.
         __device__ __noinline__ uint32_t long_symbol(const par_table& T, uint32_t h)
         {
             const int c16 = (int)(h >> 16);
@@ -483,6 +492,7 @@ namespace aeonb
         }
 
         constexpr int PAR_THREADS = 1024; // most threads (= segments) a stream can have; the launch picks the actual number
+        constexpr int NCHECK      = 7;    // checkpoints inside a segment
 
         struct par_state
         {
@@ -491,9 +501,13 @@ namespace aeonb
             uint16_t   ent_bk[PAR_THREADS], ext_bk[PAR_THREADS];
             uint32_t   warp_sums[3][32];
             uint8_t    zz[64];
-            uint8_t    comp[16], bx[16], by[16]; // per block of an MCU: component and position inside the MCU
-            const par_table* dct_of[16];         //                       and its DC / AC table
+            uint8_t    comp[16], bx[16], by[16]; // per block of an MCU: component and position inside the MCU,
+            const par_table* dct_of[16];         //                       its DC / AC table,
             const par_table* act_of[16];
+            uint32_t   dc_look[16], ac_look[16]; //                       the shared-memory addresses of their lookup windows,
+            int16_t*   blk_base[16];             //                       where its coefficients go: blk_base + (mcu row - first row) * blk_dy
+            int64_t    blk_dy[16];               //                                                           + (mcu column - first column) * blk_dx
+            int        blk_dx[16];
             aeonb_entropy_desc d;
             int        bpm;                      // blocks per MCU
             uint32_t   total_blocks;
@@ -501,57 +515,21 @@ namespace aeonb
             uint32_t   marker_at;                // first marker byte in the raw scan (or its size)
         };
 
-        // Bit reader over the copy without stuffed bytes; reads 32-bit words (the copy is padded with zeros).
-        struct clean_reader
+        __device__ __forceinline__ uint32_t lds_u16(uint32_t addr)
         {
-            const uint32_t* words;
-            uint64_t        acc;
-            int             n;
-            uint32_t        wp;
-
-            uint32_t        nextw; // the word after the accumulator's, loaded one refill ahead so that its latency is hidden
-
-            // plain loads: this block wrote the copy
-            __device__ __forceinline__ void start(const uint32_t* w, uint32_t bitpos)
-            {
-                words = w;
-                wp    = bitpos >> 5;
-                acc   = (uint64_t)__byte_perm(words[wp], 0, 0x0123) << 32;
-                nextw = words[wp + 1];
-                wp += 2;
-                const int r = bitpos & 31;
-                acc <<= r;
-                n = 32 - r;
-            }
-            __device__ __forceinline__ void refill()
-            {
-                if (n <= 32)
-                {
-                    acc |= (uint64_t)__byte_perm(nextw, 0, 0x0123) << (32 - n);
-                    n += 32;
-                    nextw = words[wp];
-                    ++wp;
-                }
-            }
-            __device__ __forceinline__ void skip(int k)
-            {
-                acc <<= k;
-                n -= k;
-            }
-        };
+            uint16_t v;
+            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+            return v;
+        }
 
         // Where block `b` of MCU (mx, my) lives in the compact coefficient planes, or NULL outside the region.
-        __device__ __forceinline__ int16_t* locate_block(const par_state& S, int mx, int my, int b)
+        __device__ __forceinline__ int16_t* block_home(const par_state& S, int mx, int my, int b)
         {
             const aeonb_entropy_desc& d = S.d;
             if (my < d.roi[1] || my >= d.roi[3] || mx < d.roi[0] || mx >= d.roi[2])
                 return nullptr;
-            const int c = S.comp[b];
-            return d.coef[c] + ((size_t)((my - d.roi[1]) * d.vs[c] + S.by[b]) * ((d.roi[2] - d.roi[0]) * d.hs[c]) +
-                                ((mx - d.roi[0]) * d.hs[c] + S.bx[b])) * 64;
+            return S.blk_base[b] + (my - d.roi[1]) * S.blk_dy[b] + (mx - d.roi[0]) * S.blk_dx[b];
         }
-
-        constexpr int TRAIL = 64; // block ends a thread remembers of its last run
 
         struct seg_result
         {
@@ -562,20 +540,19 @@ namespace aeonb
             bool     merged; // the run fell into step with the remembered run: the exit state is that run's (p, b, k unset)
         };
 
-        // Decodes symbols from bit position p0 in state (b, k) until the first symbol that starts at or past pend.
-        // Every symbol -- DC size, AC run/size, end of block, zero run -- takes the same path through the loop, so
-        // that the threads of a warp, each in its own segment, diverge as little as possible.
+        // Decodes symbols from bit position p in state (b, k) until the first symbol that starts at or past pend.  The copy of the
+        // stream holds big-endian words, so the 32 bits under p are one funnel shift of two words.
         // WRITE: stores coefficients and DC differences, `g` being the number of the block in progress.
-        // Otherwise, with `rec`, the block ends passed (bit position relative to pbase, and block index) are written
-        // to rec[0..TRAIL); with `cur`, the block ends of an earlier run over this segment, the run stops as soon as
-        // it reaches one of them: from there on it would repeat that run.
+        // Otherwise the state at the checkpoints (first one at bit check_at, then every check_step bits) goes to chk[0],
+        // chk[check_stride], ... and the blocks completed by then NCHECK rows further on; with `compare`, the run stops at the
+        // first checkpoint that an earlier run over this segment (old_blocks blocks in all) passed in the same state, and the
+        // block counts from there on are renumbered for this run.
         template <bool WRITE>
-        __device__ __forceinline__ seg_result run_segment(const par_state& S, const uint32_t* words, uint32_t p0, int b, int k, uint32_t pend,
-                                                          uint32_t g, int16_t* __restrict__ dcdiff, uint32_t pbase, uint32_t* rec,
-                                                          const uint32_t* cur, int ncur, uint32_t cur_blocks)
+        __device__ __forceinline__ seg_result run_segment(const par_state& S, const uint32_t* __restrict__ words, uint32_t p, int b, int k,
+                                                          uint32_t pend, uint32_t g, int16_t* __restrict__ dcdiff, uint32_t* chk,
+                                                          uint32_t check_stride, uint32_t check_at, uint32_t check_step, bool compare,
+                                                          uint32_t old_blocks)
         {
-            clean_reader br;
-            br.start(words, p0);
             seg_result R;
             R.merged         = false;
             uint32_t  blocks = 0;
@@ -591,106 +568,97 @@ namespace aeonb
                 if (my >= S.d.roi[3])
                     pend = 0; // nothing of this segment is wanted
                 else
-                    out = locate_block(S, mx, my, b);
+                    out = block_home(S, mx, my, b);
             }
-            int      rem    = (int)pend - (int)p0; // bits left before the segment's end
-            uint32_t curkey = cur && ncur > 0 ? cur[0] : 0xffffffffu;
-            while (rem > 0)
+            uint32_t dc_look = S.dc_look[b], ac_look = S.ac_look[b];
+            // The bits under p: `n` of them (33 to 64) at the top of `acc`; `next` is word `wp` of the copy, loaded a pass ahead.
+            uint32_t wp   = (p >> 5) + 2;
+            uint64_t acc  = ((uint64_t)words[wp - 2] << 32 | words[wp - 1]) << (p & 31);
+            int      n    = 64 - (int)(p & 31);
+            uint32_t next = words[wp];
+            while (p < pend)
             {
-                // One block (or what is left of one) per pass of this loop, so that the threads of a warp reach the
-                // block-end work below together instead of one or two of them in every pass of a flat symbol loop.
-                if (k == 0)
+                const uint32_t h = (uint32_t)(acc >> 32); // 32 valid bits; a symbol takes at most 31
+                const bool     dc = k == 0;
+                uint32_t       e  = lds_u16((dc ? dc_look : ac_look) + ((h >> (dc ? 32 - DLOOK : 32 - PLOOK)) << 1));
+                if (!e)
+                    e = long_symbol(dc ? *S.dct_of[b] : *S.act_of[b], h);
+                const int tot = e & 31, kinc = e >> 9;
+                if (WRITE)
                 {
-                    // the DC symbol opens the block
-                    const par_table* dct = S.dct_of[b];
-                    br.refill();
-                    const uint32_t h = (uint32_t)(br.acc >> 32); // 32 valid bits; a symbol takes at most 31
-                    uint32_t       e = dct->lookup[h >> (32 - DLOOK)];
-                    if (!e)
-                        e = long_symbol(*dct, h);
-                    const int tot = e & 31;
-                    if (WRITE)
+                    const int sz  = (e >> 5) & 15;
+                    const int raw = sz ? (int)((h << (tot - sz)) >> (32 - sz)) : 0;
+                    const int v   = raw - (sz && raw < ((1 << sz) >> 1) ? (1 << sz) - 1 : 0);
+                    if (kinc == 127)
+                        bad = 1; // invalid code, or a DC symbol that is no category
+                    if (dc)
                     {
-                        const int len = (e >> 5) & 31, sz = (e >> 10) & 15;
-                        const int raw = sz ? (int)((h << len) >> (32 - sz)) : 0;
-                        const int v   = raw - (raw < ((1 << sz) >> 1) ? (1 << sz) - 1 : 0);
-                        if (e >> 21)
-                            bad = 1; // invalid code, or not a category
                         if (g < S.total_blocks) // always true for a well-formed stream
                             dcdiff[g] = (int16_t)v;
                     }
-                    br.skip(tot);
-                    rem -= tot;
-                    k = 1;
+                    else if (sz)
+                    {
+                        const int kk = k + kinc - 1; // position of this coefficient
+                        if (kk > 63)
+                            bad = 1; // the run leaves the block
+                        else if (out)
+                            out[S.zz[kk]] = (int16_t)v;
+                    }
                 }
-                const uint32_t* act = S.act_of[b]->lookup;
-                while (rem > 0 && k < 64)
+                p += tot;
+                k += kinc;
+                acc <<= tot;
+                n -= tot;
+                if (n <= 32)
                 {
-                    br.refill();
-                    const uint32_t h = (uint32_t)(br.acc >> 32);
-                    uint32_t       e = act[h >> (32 - PLOOK)];
-                    if (!e)
-                        e = long_symbol(*S.act_of[b], h);
-                    const int tot = e & 31;
+                    // only lanes that took the word ask for the next one: few trips through the L1 pipeline per pass, and a
+                    // pass is longer than a hit takes, so `next` has arrived when a lane wants it
+                    acc |= (uint64_t)next << (32 - n);
+                    n += 32;
+                    next = words[++wp];
+                }
+                if (k >= 64)
+                {
+                    k = 0;
+                    ++blocks;
+                    b       = b + 1 == bpm ? 0 : b + 1;
+                    dc_look = S.dc_look[b];
+                    ac_look = S.ac_look[b];
                     if (WRITE)
                     {
-                        const int sz = (e >> 10) & 15;
-                        if (sz)
+                        ++g;
+                        if (b == 0 && ++mx == S.d.mcux)
                         {
-                            const int len = (e >> 5) & 31, kk = k + (int)((e >> 14) & 127) - 1; // position of this coefficient
-                            const int raw = (int)((h << len) >> (32 - sz));
-                            const int v   = raw - (raw < ((1 << sz) >> 1) ? (1 << sz) - 1 : 0);
-                            if (kk > 63)
-                                bad = 1; // the run leaves the block
-                            else if (out)
-                                out[S.zz[kk]] = (int16_t)v;
+                            mx = 0;
+                            ++my;
+                            if (my >= S.d.roi[3])
+                                break;
                         }
-                        if (e >> 22)
-                            bad = 1; // invalid code
-                    }
-                    br.skip(tot);
-                    rem -= tot;
-                    k += (e >> 14) & 127;
-                }
-                if (k < 64)
-                    break; // the segment ended inside the block
-                k = 0;
-                ++blocks;
-                if (++b == bpm)
-                {
-                    b = 0;
-                    if (WRITE && ++mx == S.d.mcux)
-                    {
-                        mx = 0;
-                        ++my;
+                        out = block_home(S, mx, my, b);
                     }
                 }
-                if (WRITE)
+                if (!WRITE && p >= check_at && j < NCHECK)
                 {
-                    ++g;
-                    if (my >= S.d.roi[3])
-                        break;
-                    out = locate_block(S, mx, my, b);
-                }
-                else if (rec)
-                {
-                    const uint32_t key = ((uint32_t)((int)pend - rem) - pbase) << 4 | (uint32_t)b;
-                    if (blocks <= (uint32_t)TRAIL)
-                        rec[blocks - 1] = key;
-                    while (j < ncur && (curkey >> 4) < (key >> 4))
+                    const uint32_t  key  = (p - check_at) << 10 | (uint32_t)b << 6 | (uint32_t)k; // p - check_at <= 30
+                    uint32_t* const slot = chk + (uint32_t)j * check_stride;                      // state; the blocks so far NCHECK rows on
+                    const uint32_t  rows = NCHECK * check_stride;
+                    if (compare && *slot == key)
                     {
-                        ++j;
-                        curkey = j < ncur ? cur[j] : 0xffffffffu;
-                    }
-                    if (j < ncur && curkey == key)
-                    {
+                        // in step with the earlier run: its blocks from here on are this run's too
+                        const uint32_t was = slot[rows];
+                        for (int jj = j; jj < NCHECK; ++jj)
+                            chk[(uint32_t)jj * check_stride + rows] += blocks - was;
+                        blocks += old_blocks - was;
                         R.merged = true;
-                        blocks += cur_blocks - (uint32_t)(j + 1);
                         break;
                     }
+                    slot[0]    = key;
+                    slot[rows] = blocks;
+                    ++j;
+                    check_at += check_step;
                 }
             }
-            R.p      = (uint32_t)((int)pend - rem);
+            R.p      = p;
             R.b      = b;
             R.k      = k;
             R.blocks = blocks;
@@ -731,8 +699,9 @@ namespace aeonb
         {
             const uint32_t T = blockDim.x; // threads = most segments of this launch
             extern __shared__ __align__(16) unsigned char smem_raw[];
-            par_state& S    = *reinterpret_cast<par_state*>(smem_raw);
-            const int  tid  = threadIdx.x;
+            par_state&      S       = *reinterpret_cast<par_state*>(smem_raw);
+            uint32_t* const chk_all = reinterpret_cast<uint32_t*>(smem_raw + sizeof(par_state)); // 2 x NCHECK rows of T words
+            const int       tid     = threadIdx.x;
             for (int i = tid; i < (int)(sizeof(aeonb_entropy_desc) / 4); i += T)
                 reinterpret_cast<uint32_t*>(&S.d)[i] = reinterpret_cast<const uint32_t*>(descs + blockIdx.x)[i];
             if (tid < 64)
@@ -751,8 +720,8 @@ namespace aeonb
             const uint64_t clean_room     = ((uint64_t)d.scan_size + 32 + 15) & ~15ull;
             const uint64_t dc_room        = (total_blocks64 * 2 + 15) & ~15ull;
             const bool     shape_ok = d.ncomp >= 1 && d.ncomp <= 3 && d.mcux > 0 && d.mcuy > 0 && d.scan && d.tables && bpm <= 16 &&
-                                  d.scan_size < (1u << 27) && total_blocks64 < (1ull << 30) &&
-                                  d.scratch_bytes >= clean_room + dc_room + (uint64_t)T * 2 * TRAIL * sizeof(uint32_t);
+                                  d.scan_size < (1u << 27) && total_blocks64 < (1ull << 30) && d.scratch_bytes >= clean_room + dc_room &&
+                                  (reinterpret_cast<uintptr_t>(d.scratch) & 3) == 0;
             if (!shape_ok)
             {
                 if (tid == 0 && d.status)
@@ -763,15 +732,23 @@ namespace aeonb
             {
                 int b = 0;
                 for (int c = 0; c < d.ncomp; ++c)
+                {
+                    const int64_t row_blocks = (int64_t)(d.roi[2] - d.roi[0]) * d.hs[c]; // blocks in a row of the compact plane
                     for (int y = 0; y < d.vs[c]; ++y)
                         for (int x = 0; x < d.hs[c]; ++x, ++b)
                         {
-                            S.comp[b]   = (uint8_t)c;
-                            S.bx[b]     = (uint8_t)x;
-                            S.by[b]     = (uint8_t)y;
-                            S.dct_of[b] = &S.tab[d.dc_table[c] & 1];
-                            S.act_of[b] = &S.tab[2 + (d.ac_table[c] & 1)];
+                            S.comp[b]     = (uint8_t)c;
+                            S.bx[b]       = (uint8_t)x;
+                            S.by[b]       = (uint8_t)y;
+                            S.dct_of[b]   = &S.tab[d.dc_table[c] & 1];
+                            S.act_of[b]   = &S.tab[2 + (d.ac_table[c] & 1)];
+                            S.dc_look[b]  = (uint32_t)__cvta_generic_to_shared(S.dct_of[b]->lookup);
+                            S.ac_look[b]  = (uint32_t)__cvta_generic_to_shared(S.act_of[b]->lookup);
+                            S.blk_base[b] = d.coef[c] + (y * row_blocks + x) * 64;
+                            S.blk_dy[b]   = d.vs[c] * row_blocks * 64;
+                            S.blk_dx[b]   = d.hs[c] * 64;
                         }
+                }
                 S.bpm          = b;
                 S.total_blocks = (uint32_t)total_blocks64;
                 S.marker_at    = d.scan_size;
@@ -788,7 +765,7 @@ namespace aeonb
             }
             __syncthreads();
 
-            // ---- copy without stuffed bytes.  Thread t owns raw bytes [c0, c1).
+            // ---- copy without stuffed bytes, as big-endian 32-bit words (byte i of the stream is byte i ^ 3 of the copy)
             uint8_t* const  clean  = static_cast<uint8_t*>(d.scratch);
             int16_t* const  dcdiff = reinterpret_cast<int16_t*>(clean + clean_room);
             const uint32_t  N      = d.scan_size;
@@ -859,12 +836,12 @@ namespace aeonb
 #pragma unroll
                 for (int b = 0; b < 16; ++b)
                     if (keep >> b & 1)
-                        clean[o++] = (uint8_t)(w[b >> 2] >> (8 * (b & 3)));
+                        clean[o++ ^ 3] = (uint8_t)(w[b >> 2] >> (8 * (b & 3)));
                 clean_size += tile_total;
             }
             {
                 if (tid < 32)
-                    clean[clean_size + tid] = 0; // padding the readers may run into
+                    clean[(clean_size + tid) ^ 3] = 0; // padding the readers may run into
             }
             __syncthreads();
             const uint32_t* words = reinterpret_cast<const uint32_t*>(clean);
@@ -880,26 +857,24 @@ namespace aeonb
             }
             // ---- segments: one per thread, a multiple of 4 bytes, at least min_segment bytes
             uint32_t seg = (clean_size + T - 1) / T;
-            seg          = max((seg + 3u) & ~3u, (uint32_t)max(min_segment, 16) & ~3u);
+            seg          = max((seg + 3u) & ~3u, (uint32_t)max(min_segment, 64) & ~3u);
             const uint32_t nseg      = (clean_size + seg - 1) / seg; // <= T
             const uint32_t total_bit = clean_size * 8;
             const bool     mine      = (uint32_t)tid < nseg;
             const uint32_t pbeg = (uint32_t)tid * seg * 8, pend = min(total_bit, pbeg + seg * 8);
-            // each thread's two trail buffers (block ends of its last run / of the run in progress)
-            uint32_t* const trail   = reinterpret_cast<uint32_t*>(clean + clean_room + dc_room) + (size_t)tid * 2 * TRAIL;
-            int             cur_sel = 0, ncur = 0;
-            uint32_t        cur_blocks = 0;
+            // checkpoints of this thread's segment: one every eighth of it (seg bits; a symbol is shorter, so it passes at most one)
+            uint32_t* const chk        = chk_all + tid;
+            uint32_t        run_blocks = 0; // blocks of this thread's latest run
             // first decoding pass: guessed entry states (segment 0: the true one)
             if (mine)
             {
-                const seg_result r = run_segment<false>(S, words, pbeg, 0, 0, pend, 0, nullptr, pbeg, trail, nullptr, 0, 0);
+                const seg_result r = run_segment<false>(S, words, pbeg, 0, 0, pend, 0, nullptr, chk, T, pbeg + seg, seg, false, 0);
                 S.ent_p[tid]  = pbeg;
                 S.ent_bk[tid] = 0;
                 S.ext_p[tid]  = r.p;
                 S.ext_bk[tid] = (uint16_t)((r.b << 8) | r.k);
                 S.cnt[tid]    = r.blocks;
-                cur_blocks    = r.blocks;
-                ncur          = (int)min(r.blocks, (uint32_t)TRAIL);
+                run_blocks    = r.blocks;
             }
             else
                 S.cnt[tid] = 0;
@@ -918,18 +893,16 @@ namespace aeonb
                 __syncthreads(); // every candidate has been read before any exit state changes
                 if (redo)
                 {
-                    const seg_result r = run_segment<false>(S, words, cand_p, cand_bk >> 8, cand_bk & 255, pend, 0, nullptr, pbeg,
-                                                            trail + (cur_sel ^ 1) * TRAIL, trail + cur_sel * TRAIL, ncur, cur_blocks);
+                    const seg_result r =
+                        run_segment<false>(S, words, cand_p, cand_bk >> 8, cand_bk & 255, pend, 0, nullptr, chk, T, pbeg + seg, seg, true, run_blocks);
                     S.ent_p[tid]  = cand_p;
                     S.ent_bk[tid] = cand_bk;
                     S.cnt[tid]    = r.blocks;
+                    run_blocks    = r.blocks;
                     if (!r.merged)
                     {
                         S.ext_p[tid]  = r.p;
                         S.ext_bk[tid] = (uint16_t)((r.b << 8) | r.k);
-                        cur_sel ^= 1;
-                        cur_blocks = r.blocks;
-                        ncur       = (int)min(r.blocks, (uint32_t)TRAIL);
                     }
                 }
                 if (!__syncthreads_or(redo))
@@ -944,11 +917,29 @@ namespace aeonb
             if (tid == 0 && counted < needed_blocks)
                 S.bad = 1;
 
-            // ---- decode once more from the true entry states, storing (the planes were cleared above)
-            if (mine)
+            // ---- decode once more from the true entry states, storing (the planes were cleared above).  The checkpoints now
+            // describe every segment's final run, so each segment falls into NCHECK + 1 pieces with known entry states and block
+            // numbers, and the pieces -- not the segments -- are dealt out to the threads: streams with fewer segments than
+            // threads keep every warp busy, and neighbouring lanes work on neighbouring pieces.
+            S.ext_p[tid] = g0; // the exit states have served
+            __syncthreads();
+            for (uint32_t q = tid; q < nseg * (NCHECK + 1); q += T)
             {
-                const seg_result r = run_segment<true>(S, words, S.ent_p[tid], S.ent_bk[tid] >> 8, S.ent_bk[tid] & 255, pend, g0, dcdiff, 0,
-                                                       nullptr, nullptr, 0, 0);
+                const uint32_t t = q / (NCHECK + 1), piece = q % (NCHECK + 1);
+                const uint32_t seg_beg = t * seg * 8, seg_end = min(total_bit, seg_beg + seg * 8);
+                const uint32_t at = seg_beg + piece * seg; // the checkpoint this piece starts from (a segment is 8 * seg bits long)
+                if (at >= seg_end)
+                    continue;
+                uint32_t p0 = S.ent_p[t], bk = S.ent_bk[t], before = 0;
+                if (piece > 0)
+                {
+                    const uint32_t key = chk_all[(piece - 1) * T + t];
+                    p0                 = at + (key >> 10);
+                    bk                 = (key >> 6 & 15) << 8 | (key & 63);
+                    before             = chk_all[(NCHECK + piece - 1) * T + t];
+                }
+                const seg_result r = run_segment<true>(S, words, p0, bk >> 8, bk & 255, min(seg_end, at + seg), S.ext_p[t] + before, dcdiff,
+                                                       nullptr, 0, 0, 0, false, 0);
                 if (r.bad)
                     S.bad = 1;
             }
@@ -990,7 +981,7 @@ namespace aeonb
                             now = pred[1] += v;
                         else
                             now = pred[2] += v;
-                        int16_t* out = locate_block(S, mx, my, b);
+                        int16_t* out = block_home(S, mx, my, b);
                         if (out)
                             out[0] = (int16_t)now;
                     }
@@ -1036,8 +1027,7 @@ namespace aeonb
         for (int c = 0; c < d.ncomp && c < 3; ++c)
             bpm += (int64_t)d.hs[c] * d.vs[c];
         const int64_t blocks = (int64_t)d.mcux * d.mcuy * bpm;
-        return (((int64_t)d.scan_size + 32 + 15) & ~15ll) + ((blocks * 2 + 15) & ~15ll) +
-               (int64_t)jpeg_entropy_threads() * 2 * TRAIL * (int64_t)sizeof(uint32_t);
+        return (((int64_t)d.scan_size + 32 + 15) & ~15ll) + ((blocks * 2 + 15) & ~15ll);
     }
 
     cudaError_t launch_jpeg_entropy(const aeonb_entropy_desc* descs_dev, int n, bool any_parallel, bool any_serial, int min_segment,
@@ -1047,7 +1037,7 @@ namespace aeonb
             return cudaSuccess;
         if (any_parallel)
         {
-            const size_t smem = sizeof(par_state);
+            const size_t smem = sizeof(par_state) + (size_t)2 * NCHECK * jpeg_entropy_threads() * sizeof(uint32_t);
             cudaError_t  err  = cudaFuncSetAttribute(jpeg_entropy_parallel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (err != cudaSuccess)
                 return err;
