@@ -282,7 +282,6 @@ aeonb_provider::aeonb_provider(aeonb_ctx* c, const json& cfg) : ctx(c)
         out_dev[k].resize(outputs.size());
         out_dev_t[k].resize(outputs.size());
     }
-    out_host.resize(outputs.size());
     rcnn_anchor_dev.resize(stages.size());
     rcnn_result_dev.resize(stages.size());
     rcnn_result_host.resize(stages.size());

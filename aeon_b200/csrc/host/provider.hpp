@@ -15,6 +15,11 @@
 #include <memory>
 #include <string>
 #include <unordered_map>
+#include <condition_variable>
+#include <deque>
+#include <exception>
+#include <mutex>
+#include <thread>
 #include <vector>
 
 #include "../specgram_host.hpp"
@@ -126,6 +131,7 @@ namespace aeonb
         {
         }
         std::vector<jpeg_job>                      jobs;
+        std::vector<std::vector<char>>             out_host; // host-produced outputs of this batch (labels, boxes), per output
         std::vector<copy_job>                      copies;
         // per stage: main image-kernel descriptors, the JPEG job each reads (-1: zero frame) and its offset in the output
         std::vector<std::vector<aeonb_image_desc>> descs;
@@ -196,12 +202,11 @@ struct aeonb_provider
     // (on the copy stream) overlaps the kernels of batch t+1, which write the other set.
     std::vector<aeonb::device_buffer>    out_dev[2];   // per output, batch_size records
     std::vector<aeonb::device_buffer>    out_dev_t[2]; // transposed copies (batch_major == false)
-    std::vector<std::vector<char>>       out_host;     // host-produced outputs
     aeonb::pinned_buffer                 small_pinned[2]; // host-produced outputs on their way to device memory, two sets as above
 
-    static constexpr int k_events = 4;
-    cudaEvent_t m_done[k_events]    = {nullptr, nullptr, nullptr, nullptr}; // batch t complete: m_done[t % k_events]
-    cudaEvent_t m_kernels[k_events] = {nullptr, nullptr, nullptr, nullptr}; // the kernels of batch t have finished
+    static constexpr int k_events = 8;
+    cudaEvent_t m_done[k_events]    = {}; // batch t complete: m_done[t % k_events]
+    cudaEvent_t m_kernels[k_events] = {}; // the kernels of batch t have finished
     cudaStream_t m_copy             = nullptr; // device -> host copies of finished batches
     // AEONB_TRACE timing events per batch: 0 call start on the kernels' stream, 1 end of kernels, 2 end of delivery,
     // 3 / 4 first and last byte of the staging upload, 5 / 6 entropy kernel begin / end, 7 back end begin
@@ -214,18 +219,40 @@ struct aeonb_provider
     bool        m_consumed_valid[2] = {false, false};
     cudaEvent_t m_uploaded[2]       = {nullptr, nullptr}; // small pinned set p has been copied
     bool        m_uploaded_valid[2] = {false, false};
-    int64_t     m_ticket            = 0;       // number of batches submitted so far
+    int64_t     m_ticket            = 0;       // number of batches submitted so far (calling thread)
+    // A submitted batch is planned on the calling thread (headers, draws: the only phase that needs the records in
+    // record order) and handed to the driver thread, which reserves memory, stages, launches and delivers one batch
+    // at a time in submission order; the caller plans batch t+1 meanwhile.
+    struct batch_job
+    {
+        explicit batch_job(int stages) : plan(stages) {}
+        aeonb::batch_plan  plan;
+        std::vector<void*> outs;
+        int                n = 0;
+        bool               on_device = false;
+        int64_t            ticket = 0;
+        double             plan_ms = 0;
+    };
+    std::thread                             m_driver;
+    std::mutex                              m_job_mutex;
+    std::condition_variable                 m_job_cv, m_done_cv;
+    std::deque<std::unique_ptr<batch_job>>  m_jobs;
+    int64_t                                 m_processed = 0; // last batch the driver has finished enqueuing (or failed on)
+    bool                                    m_driver_stop = false;
+    std::exception_ptr                      m_failed[k_events]; // what the driver threw for the batch of that slot
+    void driver_loop();
+    void process(batch_job& job);
     aeonb::pinned_buffer m_status[k_events];   // per in-flight batch: the device entropy decoder's status words
-    int                  m_status_count[k_events] = {0, 0, 0, 0};
+    int                  m_status_count[k_events] = {};
     void                 check_entropy_status(int slot); // throws aeon's decode error if a stream was malformed
 
     int64_t h2d_bytes = 0, d2h_bytes = 0;
     int32_t launches  = 0;
 
     aeonb_provider(aeonb_ctx* c, const aeonb::json& cfg);
-    // Processes one batch.  With wait == false the call returns once the GPU work (kernels and output
-    // copies) is enqueued; wait_ticket(ticket()) then blocks until that batch is complete.  The host
-    // stages of the next call overlap the GPU work of the previous one.
+    // Processes one batch.  With wait == false the call returns once the batch is planned and queued for the driver
+    // thread; wait_ticket(ticket()) then blocks until that batch is complete.  Records and output buffers must stay
+    // valid until then.  At most two batches wait for the driver: a third submission blocks until it has caught up.
     void    run(const void* const* elems, const size_t* sizes, int n, void* const* outs, bool on_device, bool wait = true);
     int64_t ticket() const { return m_ticket; }
     void    wait_ticket(int64_t t);
@@ -238,5 +265,5 @@ private:
     void reserve_arenas(aeonb::batch_plan& plan, void* const* outs, bool on_device, int par);
     void stage_inputs(aeonb::batch_plan& plan, int par);
     void launch_kernels(aeonb::batch_plan& plan, int n, int par);
-    void deliver(aeonb::batch_plan& plan, void* const* outs, int n, bool on_device, bool wait, int par);
+    void deliver(aeonb::batch_plan& plan, void* const* outs, int n, bool on_device, int par, int64_t ticket);
 };

@@ -153,6 +153,13 @@ namespace aeonb
 
 aeonb_provider::~aeonb_provider()
 {
+    {
+        std::lock_guard<std::mutex> lk(m_job_mutex);
+        m_driver_stop = true; // the driver finishes what is queued, then leaves
+    }
+    m_job_cv.notify_all();
+    if (m_driver.joinable())
+        m_driver.join();
     for (cudaEvent_t e : m_done)
         if (e)
             cudaEventDestroy(e);
@@ -192,6 +199,17 @@ void aeonb_provider::wait_ticket(int64_t t)
         throw std::invalid_argument("aeonb_provider_wait: no such batch");
     if (m_ticket - t >= k_events)
         return; // its event slot was recycled, which only happens after the batch completed
+    {
+        // the driver thread has enqueued (or given up on) the batch
+        std::unique_lock<std::mutex> lk(m_job_mutex);
+        m_done_cv.wait(lk, [&] { return m_processed >= t; });
+        if (m_failed[t % k_events])
+        {
+            std::exception_ptr e    = m_failed[t % k_events];
+            m_failed[t % k_events] = nullptr;
+            std::rethrow_exception(e);
+        }
+    }
     AEONB_CUDA(cudaSetDevice(ctx->device));
     AEONB_CUDA(cudaEventSynchronize(m_done[t % k_events]));
     if (m_trace[t % k_events][2] && std::getenv("AEONB_TRACE"))
@@ -235,10 +253,70 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         throw std::invalid_argument("aeonb_provider_run: NULL argument");
     if (n <= 0 || n > batch_size)
         throw std::invalid_argument("aeonb_provider_run: record count must be in [1, batch_size]");
+    const auto t0 = std::chrono::steady_clock::now();
+    auto job = std::make_unique<batch_job>((int)stages.size());
+    plan_records(job->plan, elems, sizes, n); // sequential planning pass (record order == RNG order), on the calling thread
+    job->outs.assign(outs, outs + outputs.size());
+    job->n         = n;
+    job->on_device = on_device;
+    job->plan_ms   = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    int64_t ticket;
+    {
+        std::unique_lock<std::mutex> lk(m_job_mutex);
+        if (!m_driver.joinable())
+            m_driver = std::thread([this] { driver_loop(); });
+        m_done_cv.wait(lk, [&] { return m_ticket - m_processed < 2; }); // the driver is at most two batches behind
+        ticket = job->ticket = ++m_ticket;
+        m_jobs.push_back(std::move(job));
+    }
+    m_job_cv.notify_one();
+    if (wait)
+        wait_ticket(ticket);
+}
+
+void aeonb_provider::driver_loop()
+{
+    for (;;)
+    {
+        std::unique_ptr<batch_job> job;
+        {
+            std::unique_lock<std::mutex> lk(m_job_mutex);
+            m_job_cv.wait(lk, [&] { return m_driver_stop || !m_jobs.empty(); });
+            if (m_jobs.empty())
+                return;
+            job = std::move(m_jobs.front());
+            m_jobs.pop_front();
+        }
+        const int          slot = (int)(job->ticket % k_events);
+        std::exception_ptr failed;
+        try
+        {
+            process(*job);
+        }
+        catch (...)
+        {
+            failed = std::current_exception();
+        }
+        {
+            std::lock_guard<std::mutex> lk(m_job_mutex);
+            m_failed[slot] = failed;
+            m_processed    = job->ticket;
+        }
+        m_done_cv.notify_all();
+    }
+}
+
+// Everything of a batch after planning, on the driver thread: memory, staging, launches, delivery.
+void aeonb_provider::process(batch_job& job)
+{
+    batch_plan&   B         = job.plan;
+    const int     n         = job.n;
+    const bool    on_device = job.on_device;
+    const int64_t T         = job.ticket;
     // AEONB_TRACE=1 prints the host time of each phase of the call to stderr
     static const bool trace = std::getenv("AEONB_TRACE") != nullptr;
     auto              t_prev = std::chrono::steady_clock::now();
-    double            t_phase[6] = {0, 0, 0, 0, 0, 0};
+    double            t_phase[6] = {0, job.plan_ms, 0, 0, 0, 0};
     auto mark = [&](int k) {
         const auto now = std::chrono::steady_clock::now();
         t_phase[k]     = std::chrono::duration<double, std::milli>(now - t_prev).count();
@@ -269,18 +347,21 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
             if (aeonb_ctx_create(ctx->device, nullptr, &e) != AEONB_OK)
                 throw error(AEONB_ERR_CUDA, aeonb_last_error());
     }
-    // This batch is number m_ticket + 1.  Its device-side outputs use buffer set `par`, last used by batch
-    // m_ticket - 1, whose copy to the host may still be running on the copy stream: kernels wait for it.
-    const int par = (int)((m_ticket + 1) & 1);
-    if (!on_device && m_ticket >= 2)
-        AEONB_CUDA(cudaStreamWaitEvent(st, m_done[(m_ticket - 1) % k_events], 0));
+    // Batch T writes its device-side outputs into buffer set `par`, last used by batch T - 2, whose copy to the
+    // host may still be running on the copy stream: kernels wait for it.
+    const int par = (int)(T & 1);
+    if (!on_device && T >= 3)
+        AEONB_CUDA(cudaStreamWaitEvent(st, m_done[(T - 2) % k_events], 0));
     // The pinned staging set of this batch was last used two batches ago: its copy to the device must have finished.
     if (m_staged_valid[par])
         AEONB_CUDA(cudaEventSynchronize(m_staged[par]));
     const int64_t launches_before = ctx->launches;
+    int64_t       h2d_before = h2d_bytes, d2h_before = d2h_bytes;
     h2d_bytes = d2h_bytes = 0;
+    (void)h2d_before;
+    (void)d2h_before;
     mark(0);
-    const int trace_slot = (int)((m_ticket + 1) % k_events);
+    const int trace_slot = (int)(T % k_events);
     if (trace)
     {
         for (cudaEvent_t& e : m_trace[trace_slot])
@@ -289,17 +370,13 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
         AEONB_CUDA(cudaEventRecord(m_trace[trace_slot][0], st));
         m_trace_slot = trace_slot;
     }
-
-    batch_plan B((int)stages.size());
-    plan_records(B, elems, sizes, n); // 1. sequential planning pass (record order == RNG order)
-    mark(1);
-    reserve_arenas(B, outs, on_device, par);
+    reserve_arenas(B, job.outs.data(), on_device, par);
     mark(2);
-    stage_inputs(B, par); // 3. host work on the pool, uploads
+    stage_inputs(B, par); // host work on the pool, uploads
     mark(3);
     launch_kernels(B, n, par);
     mark(4);
-    deliver(B, outs, n, on_device, wait, par);
+    deliver(B, job.outs.data(), n, on_device, par, T);
     launches = (int32_t)(ctx->launches - launches_before);
     if (trace)
     {
@@ -314,9 +391,10 @@ void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, v
 void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const size_t* sizes, int n)
 {
     const int nin = (int)stages.size();
+    B.out_host.resize(outputs.size());
     for (size_t o = 0; o < outputs.size(); ++o)
         if (outputs[o].host_produced)
-            out_host[o].assign((size_t)batch_size * outputs[o].shape.byte_size(), 0);
+            B.out_host[o].assign((size_t)batch_size * outputs[o].shape.byte_size(), 0);
 
     // Parses the headers of one JPEG stream and registers it as a decode job (sizes only; no layout yet).
     auto plan_jpeg = [&](const void* data, size_t size) -> int {
@@ -643,11 +721,11 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
                 vector<bbox> gt = transform_boxes_for_ssd(boxes, params);
                 const int    o  = sg.first_output;
                 const int    M  = sg.ssd.max_gt_boxes;
-                int32_t* im_shape = reinterpret_cast<int32_t*>(out_host[o].data()) + (size_t)r * 2;
-                float*   gtb      = reinterpret_cast<float*>(out_host[o + 1].data()) + (size_t)r * M * 4;
-                int32_t* count    = reinterpret_cast<int32_t*>(out_host[o + 2].data()) + r;
-                int32_t* cls      = reinterpret_cast<int32_t*>(out_host[o + 3].data()) + (size_t)r * M;
-                int32_t* diff     = reinterpret_cast<int32_t*>(out_host[o + 4].data()) + (size_t)r * M;
+                int32_t* im_shape = reinterpret_cast<int32_t*>(B.out_host[o].data()) + (size_t)r * 2;
+                float*   gtb      = reinterpret_cast<float*>(B.out_host[o + 1].data()) + (size_t)r * M * 4;
+                int32_t* count    = reinterpret_cast<int32_t*>(B.out_host[o + 2].data()) + r;
+                int32_t* cls      = reinterpret_cast<int32_t*>(B.out_host[o + 3].data()) + (size_t)r * M;
+                int32_t* diff     = reinterpret_cast<int32_t*>(B.out_host[o + 4].data()) + (size_t)r * M;
                 ssd_fill_buffers(gt, sg.ssd.width, sg.ssd.height, M, im_shape, gtb, count, cls, diff);
                 break;
             }
@@ -669,7 +747,7 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
                     throw std::invalid_argument("boundingbox does not support 'angle'");
                 const vector<bbox> out   = transform_boxes_for_ssd(boxes, params);
                 const int          o     = sg.first_output;
-                float*             dst   = reinterpret_cast<float*>(out_host[o].data() + (size_t)r * outputs[o].shape.byte_size());
+                float*             dst   = reinterpret_cast<float*>(B.out_host[o].data() + (size_t)r * outputs[o].shape.byte_size());
                 const int          count = std::min<int>(sg.bbox.max_bbox_count, (int)out.size());
                 for (int i = 0; i < count; ++i)
                 {
@@ -724,7 +802,7 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
                 else
                     lbl = std::stoi(string((const char*)data, size));
                 const size_t esz = outputs[sg.first_output].shape.otype.size;
-                std::memcpy(out_host[sg.first_output].data() + (size_t)r * esz, &lbl, std::min<size_t>(esz, 4));
+                std::memcpy(B.out_host[sg.first_output].data() + (size_t)r * esz, &lbl, std::min<size_t>(esz, 4));
                 break;
             }
             case stage_kind::blob:
@@ -738,7 +816,7 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
                     ss << "blob of " << size << " bytes does not fit the " << room << " bytes of its output buffer, at idx " << r;
                     throw std::runtime_error(ss.str());
                 }
-                std::memcpy(out_host[sg.first_output].data() + (size_t)r * room, data, size);
+                std::memcpy(B.out_host[sg.first_output].data() + (size_t)r * room, data, size);
                 break;
             }
             case stage_kind::audio:
@@ -1290,7 +1368,7 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n, int par)
 }
 
 // Phase 5: host-produced outputs, transposes, copies to the host on the copy stream, completion event.
-void aeonb_provider::deliver(batch_plan& B, void* const* outs, int n, bool on_device, bool wait, int par)
+void aeonb_provider::deliver(batch_plan& B, void* const* outs, int n, bool on_device, int par, int64_t ticket)
 {
     cudaStream_t st = ctx->stream;
     // ---- 5. deliver
@@ -1313,14 +1391,14 @@ void aeonb_provider::deliver(batch_plan& B, void* const* outs, int n, bool on_de
                                                             sg.rcnn.deterministic_sampling ? nullptr : &rcnn_engine);
             void* bufs[10];
             for (int k = 0; k < 10; ++k)
-                bufs[k] = out_host[sg.first_output + k].data() + r * (size_t)outputs[sg.first_output + k].shape.byte_size();
+                bufs[k] = B.out_host[sg.first_output + k].data() + r * (size_t)outputs[sg.first_output + k].shape.byte_size();
             rcnn_load(sg.rcnn, sg.anchors, B.rcnn[s][r], labels, best, sampled, bufs);
         }
     }
     size_t small_total = 0;
     for (size_t o = 0; o < outputs.size(); ++o)
         if (outputs[o].host_produced && on_device)
-            small_total += align_up(out_host[o].size(), 256);
+            small_total += align_up(B.out_host[o].size(), 256);
     if (small_total > 0 && m_uploaded_valid[par])
         AEONB_CUDA(cudaEventSynchronize(m_uploaded[par])); // the small pinned set is reused too (last used two batches ago)
     small_pinned[par].reserve(small_total + 256);
@@ -1333,10 +1411,10 @@ void aeonb_provider::deliver(batch_plan& B, void* const* outs, int n, bool on_de
         if (outputs[o].host_produced)
         {
             vector<char>  tmp;
-            const char*   src = out_host[o].data();
+            const char*   src = B.out_host[o].data();
             if (!batch_major)
             {
-                tmp.resize(out_host[o].size());
+                tmp.resize(B.out_host[o].size());
                 for (int r = 0; r < batch_size; ++r)
                     for (int64_t e = 0; e < elems_per_rec; ++e)
                         std::memcpy(&tmp[((size_t)e * batch_size + r) * esz], src + ((size_t)r * elems_per_rec + e) * esz, esz);
@@ -1346,7 +1424,7 @@ void aeonb_provider::deliver(batch_plan& B, void* const* outs, int n, bool on_de
             if (on_device)
             {
                 char* pin = static_cast<char*>(small_pinned[par].p) + small_off;
-                small_off += align_up(out_host[o].size(), 256);
+                small_off += align_up(B.out_host[o].size(), 256);
                 std::memcpy(pin, src, bytes);
                 AEONB_CUDA(cudaMemcpyAsync(outs[o], pin, bytes, cudaMemcpyHostToDevice, st));
                 h2d_bytes += (int64_t)bytes;
@@ -1360,10 +1438,9 @@ void aeonb_provider::deliver(batch_plan& B, void* const* outs, int n, bool on_de
         AEONB_CUDA(cudaEventRecord(m_uploaded[par], st));
         m_uploaded_valid[par] = true;
     }
-    ++m_ticket;
     // Recycling an event slot: the batch that used it (k_events submissions ago) is long complete once the
     // newer batches between were waited for; synchronise to make that certain.
-    const int slot = (int)(m_ticket % k_events);
+    const int slot = (int)(ticket % k_events);
     AEONB_CUDA(cudaEventSynchronize(m_done[slot]));
     vector<void*> sources(outputs.size(), nullptr); // what is copied to the host, per device-produced output
     for (size_t o = 0; o < outputs.size(); ++o)
@@ -1416,11 +1493,4 @@ void aeonb_provider::deliver(batch_plan& B, void* const* outs, int n, bool on_de
         AEONB_CUDA(cudaEventRecord(m_trace[slot][2], cs));
     }
     AEONB_CUDA(cudaEventRecord(m_done[slot], cs));
-    if (wait)
-    {
-        AEONB_CUDA(cudaStreamSynchronize(st));
-        if (cs != st)
-            AEONB_CUDA(cudaStreamSynchronize(cs));
-        check_entropy_status(slot);
-    }
 }

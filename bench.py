@@ -409,6 +409,36 @@ def provider_buffers(prov, depth, device, dev):
     return sets
 
 
+def host_link_ceiling(dev, world, d2h_bytes, h2d_bytes, barrier):
+    """Aggregate bandwidth of plain copies with all ranks copying at once: a block the size of one delivered batch device ->
+    pinned host, a block the size of one batch's staged input pinned host -> device.  Returns GB/s summed over the ranks and
+    the records/s that the device -> host figure allows `e2e`."""
+    import torch
+    import torch.distributed as dist
+    out = {}
+    for key, nbytes, to_host in (("d2h_gbs_all_ranks", int(d2h_bytes), True), ("h2d_gbs_all_ranks", int(h2d_bytes), False)):
+        on_dev = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
+        on_host = torch.empty(max(nbytes, 1), dtype=torch.uint8).pin_memory()
+        src, dst = (on_dev, on_host) if to_host else (on_host, on_dev)
+        reps = 12
+        for _ in range(2):
+            dst.copy_(src, non_blocking=True)
+        barrier()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        ev[0].record()
+        for _ in range(reps):
+            dst.copy_(src, non_blocking=True)
+        ev[1].record()
+        barrier()
+        t = torch.tensor([nbytes * reps / (ev[0].elapsed_time(ev[1]) * 1e-3) / 1e9], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t)
+        out[key] = float(t.item())
+    batch = WORKLOADS[HEADLINE]["batch"]
+    out["e2e_ceiling_records_per_s"] = out["d2h_gbs_all_ranks"] * 1e9 / max(int(d2h_bytes), 1) * batch
+    return out
+
+
 def measure_config(ctx, name, threads, peak, repeats, dev):
     """One of the other benchmark configurations through the provider: records/s with the batch left in device memory
     and copied to pinned host memory (pipelined calls, median of `repeats`), and the device time of each kernel with
@@ -419,7 +449,7 @@ def measure_config(ctx, name, threads, peak, repeats, dev):
     batch = w["batch"]
     chunks = [recs[i:i + batch] for i in range(0, len(recs), batch)]
     prov = Provider(ctx, provider_config(name, decode_threads=threads))
-    DEPTH = 3
+    DEPTH = 5
     steps = max(2 * len(chunks), DEPTH + 1)
     out = {"workload": w["describe"], "batch": batch, "batches_cycled": len(chunks)}
     for key, to_device in (("e2e_device_output", True), ("e2e", False)):
@@ -466,6 +496,7 @@ def main():
                     help="time the resident-input kernels of the headline configuration only (used for profiler captures)")
     ap.add_argument("--only-config", default=None, choices=sorted(WORKLOADS),
                     help="measure one configuration through the provider and print its entry (used for profiler captures)")
+    ap.add_argument("--headline-only", action="store_true", help="skip the four other configurations (they run at N=1 only)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
@@ -479,7 +510,7 @@ def main():
     if rank == 0 and world == 1 and not args.kernels_only and not args.only_config and args.cpu_seconds > 0:
         cpu_lines[HEADLINE] = cpu_arm(HEADLINE, args.cpu_seconds)
         for name in sorted(WORKLOADS):
-            if name != HEADLINE:
+            if name != HEADLINE and not args.headline_only:
                 cpu_lines[name] = cpu_arm(name, max(2.0, args.cpu_seconds / 4))
 
     import torch
@@ -632,7 +663,8 @@ def main():
     # ---------------- end to end through the provider: encoded bytes in host memory -> batch in host memory
     cfg = provider_config(HEADLINE, decode_threads=threads, entropy_decode=args.entropy)
     prov = Provider(ctx, cfg)
-    DEPTH = 3   # batches in flight: the host prepares batch i while the GPU decodes i-1 and i-2 is copied to the host
+    DEPTH = 5   # batches in flight: the caller plans batch i while the library's driver thread stages and launches i-1, the GPU
+                # decodes i-2 and i-3 and i-4 is copied to the host; a batch takes about 2 ms from submission to completion
     chunks = [recs[b * BATCH:(b + 1) * BATCH] for b in range(n_batches)]
     e2e_steps = max(DEPTH + 1, min(args.steps, 48))
     results = {}
@@ -651,9 +683,13 @@ def main():
         stats[key] = prov.stats()
     prov.close()
 
+    # ---------------- what the host link carries with every rank copying at once, none of this library's code involved:
+    # one float32 batch device -> pinned host, one batch of compressed scans pinned host -> device (the ceiling of `e2e`)
+    link = host_link_ceiling(dev, world, stats["e2e"]["d2h_bytes"], stats["e2e"]["h2d_bytes"], barrier)
+
     # ---------------- the other configurations (one GPU: they are not part of the scaling runs)
     configs = {}
-    if world == 1:
+    if world == 1 and not args.headline_only:
         for name in sorted(WORKLOADS):
             if name != HEADLINE:
                 configs[name] = measure_config(ctx, name, threads, peak, max(3, repeats // 2), dev)
@@ -690,6 +726,7 @@ def main():
                                   "h2d_bytes_per_step": stats["e2e_device_output"]["h2d_bytes"],
                                   "d2h_bytes_per_step": stats["e2e_device_output"]["d2h_bytes"],
                                   "ms_per_step_repeats": results["e2e_device_output"]},
+            "host_link": link,
             "configs": configs,
             "gpu_launches": (3 if on_dev else 2) * args.steps, "clocks": clocks,
         }
@@ -702,7 +739,7 @@ def main():
 # captures summarised under profiles/ (same workload, same batch size; in the three-kernel chain part of the coefficient
 # planes and pictures stays in the 126 MB L2 between kernels, so a kernel's DRAM traffic can be below its algorithmic bytes).
 # Reported beside, never inside, the achieved figure, which comes from the algorithmic bytes and the time of this run.
-TRAFFIC = {"bytes": {"jpeg_entropy": 92.9e6, "jpeg_backend": 72.0e6, "aug_pack": 148.3e6},
+TRAFFIC = {"bytes": {"jpeg_entropy": 57.4e6, "jpeg_backend": 72.1e6, "aug_pack": 147.2e6},
            "source": "profiles/*_config2.md (one launch each under ncu, config2 batch 256, device entropy decoding)"}
 
 

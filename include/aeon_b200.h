@@ -486,12 +486,13 @@ int64_t aeonb_provider_output_bytes(const aeonb_provider* p, int i); /* bytes pe
 int aeonb_provider_run(aeonb_provider* p, const void* const* elems, const size_t* sizes, int n, void* const* outputs,
                        int outputs_on_device);
 
-/* Pipelined form: returns as soon as the GPU work of the batch (kernels and output copies) is enqueued
- * and stores a ticket; aeonb_provider_wait(p, ticket) blocks until that batch is complete.  Calling
- * run_async for batch k+1 before waiting for batch k overlaps the host entropy decoding of k+1 with the
- * kernels and copies of k (aeon overlaps its stages with double-buffered async_manager threads,
- * src/async_manager.hpp:91-117).  Each batch in flight needs its own output buffers; at most 3 batches
- * may be waited for out of order. */
+/* Pipelined form: plans the batch on the calling thread (headers, seeded draws), hands it to the provider's driver
+ * thread (staging, uploads, launches, output copies) and stores a ticket; aeonb_provider_wait(p, ticket) blocks until
+ * that batch is complete and reports its errors.  Calling run_async for batch k+1 before waiting for batch k overlaps
+ * the planning of k+1 with the staging of k and the kernels and copies of k-1 (aeon overlaps its stages with
+ * double-buffered async_manager threads, src/async_manager.hpp:91-117).  Records and output buffers of a batch must
+ * stay valid and untouched until its ticket has been waited for; each batch in flight needs its own output buffers;
+ * at most 7 batches may be in flight, and a call blocks while the driver thread is two batches behind. */
 int aeonb_provider_run_async(aeonb_provider* p, const void* const* elems, const size_t* sizes, int n, void* const* outputs,
                              int outputs_on_device, int64_t* ticket);
 int aeonb_provider_wait(aeonb_provider* p, int64_t ticket);
