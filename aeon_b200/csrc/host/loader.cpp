@@ -237,11 +237,11 @@ void aeonb_loader::start_producer()
     m_stop = false;
     for (slot& s : m_slots)
     {
-        s.full  = false;
+        s.state = slot_state::FREE;
         s.error = nullptr;
     }
     m_consume = 0;
-    m_holding = false;
+    m_held    = -1;
     m_thread  = std::thread([this] { producer(); });
 }
 
@@ -254,37 +254,52 @@ void aeonb_loader::stop_producer()
     m_cv.notify_all();
     if (m_thread.joinable())
         m_thread.join();
+    // batches still in the provider's pipeline read this loader's records and write its buffers: let them finish
+    for (slot& s : m_slots)
+        if (s.state == slot_state::SUBMITTED && !s.error && s.ticket > 0)
+        {
+            try
+            {
+                m_provider->wait_ticket(s.ticket);
+            }
+            catch (...)
+            {
+            }
+        }
 }
 
 void aeonb_loader::producer()
 {
     cudaSetDevice(m_device);
-    const int nin = m_provider->input_count();
+    const int nin  = m_provider->input_count();
     int       fill = 0;
-    vector<vector<vector<char>>> held(m_batch_size);
     for (;;)
     {
         {
             std::unique_lock<std::mutex> lk(m_mutex);
-            m_cv.wait(lk, [&] { return m_stop || !m_slots[fill].full; });
+            m_cv.wait(lk, [&] { return m_stop || m_slots[fill].state == slot_state::FREE; });
             if (m_stop)
                 return;
         }
         slot& s = m_slots[fill];
+        s.ticket = 0;
         try
         {
             vector<const void*> elems((size_t)m_batch_size * nin);
             vector<size_t>      sizes((size_t)m_batch_size * nin);
+            s.held.resize(m_batch_size);
             for (int r = 0; r < m_batch_size; ++r)
             {
-                held[r] = m_stream->next();
+                s.held[r] = m_stream->next();
                 for (int e = 0; e < nin; ++e)
                 {
-                    elems[(size_t)r * nin + e] = held[r][e].data();
-                    sizes[(size_t)r * nin + e] = held[r][e].size();
+                    elems[(size_t)r * nin + e] = s.held[r][e].data();
+                    sizes[(size_t)r * nin + e] = s.held[r][e].size();
                 }
             }
-            m_provider->run(elems.data(), sizes.data(), m_batch_size, s.buffers.data(), m_device_output);
+            // planned here, then staged and launched by the provider's driver thread while this thread reads the next batch
+            m_provider->run(elems.data(), sizes.data(), m_batch_size, s.buffers.data(), m_device_output, false);
+            s.ticket = m_provider->ticket();
         }
         catch (...)
         {
@@ -292,10 +307,10 @@ void aeonb_loader::producer()
         }
         {
             std::lock_guard<std::mutex> lk(m_mutex);
-            s.full = true;
+            s.state = slot_state::SUBMITTED;
         }
         m_cv.notify_all();
-        fill ^= 1;
+        fill = (fill + 1) % k_slots;
     }
 }
 
@@ -304,22 +319,25 @@ int aeonb_loader::next(void** buffers)
     if (!m_infinite && m_position >= m_batch_count)
         return AEONB_END;
     std::unique_lock<std::mutex> lk(m_mutex);
-    if (m_holding)
+    if (m_held >= 0)
     {
-        m_slots[m_consume ^ 1].full = false; // the batch handed out by the previous call is released now
-        m_holding                   = false;
+        m_slots[m_held].state = slot_state::FREE; // the batch handed out by the previous call is released now
+        m_held                = -1;
         m_cv.notify_all();
     }
     slot& s = m_slots[m_consume];
-    m_cv.wait(lk, [&] { return s.full; });
-    m_consume ^= 1;
-    m_holding = true;
+    m_cv.wait(lk, [&] { return s.state == slot_state::SUBMITTED; });
+    m_held    = m_consume;
+    m_consume = (m_consume + 1) % k_slots;
+    s.state   = slot_state::HELD;
+    lk.unlock();
     if (s.error)
     {
         std::exception_ptr e = s.error;
         s.error              = nullptr;
         std::rethrow_exception(e);
     }
+    m_provider->wait_ticket(s.ticket); // the batch is complete (throws what went wrong with it)
     for (size_t i = 0; i < s.buffers.size(); ++i)
         buffers[i] = s.buffers[i];
     m_position++;

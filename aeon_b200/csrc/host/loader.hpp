@@ -3,8 +3,8 @@
 // (src/manifest_file.cpp:115-320), record loading (src/block_loader_file.cpp:45-117), the
 // endless block stream with epoch wrap-around (src/block_manager.cpp:61-106) and the
 // ONCE / INFINITE / COUNT position logic (src/loader.cpp:141-155,234-257).
-// A producer thread fills one of two output buffer sets while the consumer holds the other,
-// as aeon's async_manager stages do (src/async_manager.hpp:91-117).
+// A producer thread reads records and submits batches to the provider's pipeline, a few output buffer sets ahead
+// of the one the consumer holds, as aeon's async_manager stages do (src/async_manager.hpp:91-117).
 #pragma once
 
 #include <condition_variable>
@@ -82,12 +82,21 @@ struct aeonb_loader
     std::vector<std::string> axis_text;
 
 private:
+    enum class slot_state
+    {
+        FREE,      // the producer may fill it
+        SUBMITTED, // its batch is in the provider's pipeline (or failed before it got there: `error`)
+        HELD       // handed out to the consumer until the next call
+    };
     struct slot
     {
         std::vector<void*> buffers; // per output: pinned host or device memory for one batch
         std::exception_ptr error;
-        bool               full = false;
+        slot_state         state  = slot_state::FREE;
+        int64_t            ticket = 0;
+        std::vector<std::vector<std::vector<char>>> held; // the batch's records: they stay put until the batch is complete
     };
+    static constexpr int k_slots = 4;
     void producer();
     void start_producer();
     void stop_producer();
@@ -101,9 +110,9 @@ private:
     int             m_block_size = 5000;
     std::unique_ptr<aeonb::block_stream> m_stream; // the endless record stream (blocks, shuffle, CPIO cache)
 
-    slot                    m_slots[2];
-    int                     m_consume = 0;    // slot the consumer reads next
-    bool                    m_holding = false; // consumer currently holds m_slots[m_consume ^ 1]... released on the next call
+    slot                    m_slots[k_slots];
+    int                     m_consume = 0;  // slot the consumer reads next
+    int                     m_held    = -1; // slot the consumer holds (released on the next call), or -1
     std::thread             m_thread;
     std::mutex              m_mutex;
     std::condition_variable m_cv;

@@ -195,13 +195,14 @@ aeonb_provider::~aeonb_provider()
 
 void aeonb_provider::wait_ticket(int64_t t)
 {
-    if (t <= 0 || t > m_ticket)
-        throw std::invalid_argument("aeonb_provider_wait: no such batch");
-    if (m_ticket - t >= k_events)
-        return; // its event slot was recycled, which only happens after the batch completed
     {
-        // the driver thread has enqueued (or given up on) the batch
+        // may be called from another thread than the one that submits
         std::unique_lock<std::mutex> lk(m_job_mutex);
+        if (t <= 0 || t > m_ticket)
+            throw std::invalid_argument("aeonb_provider_wait: no such batch");
+        if (m_ticket - t >= k_events)
+            return; // its event slot was recycled, which only happens after the batch completed
+        // the driver thread has enqueued (or given up on) the batch
         m_done_cv.wait(lk, [&] { return m_processed >= t; });
         if (m_failed[t % k_events])
         {
