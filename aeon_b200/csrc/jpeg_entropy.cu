@@ -558,7 +558,7 @@ namespace aeonb
             uint32_t  blocks = 0;
             int       bad    = 0;
             const int bpm    = S.bpm;
-            int       mx = 0, my = 0, j = 0;
+            int       mx = 0, my = 0;
             int16_t*  out = nullptr;
             if (WRITE)
             {
@@ -571,6 +571,13 @@ namespace aeonb
                     out = block_home(S, mx, my, b);
             }
             uint32_t dc_look = S.dc_look[b], ac_look = S.ac_look[b];
+            // checkpoints: `slot` walks down this thread's column (state; the blocks so far NCHECK rows further on); `old_key` is
+            // the state an earlier run noted at the next checkpoint (no state has all bits set)
+            const uint32_t rows    = NCHECK * check_stride;
+            uint32_t*      slot    = chk;
+            uint32_t       old_key = !WRITE && compare ? chk[0] : 0xffffffffu;
+            if (WRITE)
+                check_at = 0xffffffffu;
             // The bits under p: `n` of them (33 to 64) at the top of `acc`; `next` is word `wp` of the copy, loaded a pass ahead.
             uint32_t wp   = (p >> 5) + 2;
             uint64_t acc  = ((uint64_t)words[wp - 2] << 32 | words[wp - 1]) << (p & 31);
@@ -637,25 +644,25 @@ namespace aeonb
                         out = block_home(S, mx, my, b);
                     }
                 }
-                if (!WRITE && p >= check_at && j < NCHECK)
+                if (!WRITE && p >= check_at)
                 {
-                    const uint32_t  key  = (p - check_at) << 10 | (uint32_t)b << 6 | (uint32_t)k; // p - check_at <= 30
-                    uint32_t* const slot = chk + (uint32_t)j * check_stride;                      // state; the blocks so far NCHECK rows on
-                    const uint32_t  rows = NCHECK * check_stride;
-                    if (compare && *slot == key)
+                    const uint32_t key = (p - check_at) << 10 | (uint32_t)b << 6 | (uint32_t)k; // p - check_at <= 30
+                    if (key == old_key)
                     {
                         // in step with the earlier run: its blocks from here on are this run's too
                         const uint32_t was = slot[rows];
-                        for (int jj = j; jj < NCHECK; ++jj)
-                            chk[(uint32_t)jj * check_stride + rows] += blocks - was;
+                        for (uint32_t* later = slot; later < chk + rows; later += check_stride)
+                            later[rows] += blocks - was;
                         blocks += old_blocks - was;
                         R.merged = true;
                         break;
                     }
                     slot[0]    = key;
                     slot[rows] = blocks;
-                    ++j;
-                    check_at += check_step;
+                    slot += check_stride;
+                    const bool more = slot < chk + rows;
+                    check_at        = more ? check_at + check_step : 0xffffffffu;     // past the last checkpoint: none left
+                    old_key         = more && compare ? slot[0] : 0xffffffffu;        // fetched now, wanted at the next checkpoint
                 }
             }
             R.p      = p;
@@ -862,13 +869,14 @@ namespace aeonb
             const uint32_t total_bit = clean_size * 8;
             const bool     mine      = (uint32_t)tid < nseg;
             const uint32_t pbeg = (uint32_t)tid * seg * 8, pend = min(total_bit, pbeg + seg * 8);
-            // checkpoints of this thread's segment: one every eighth of it (seg bits; a symbol is shorter, so it passes at most one)
+            // checkpoints of this thread's segment, evenly spaced (at least 64 bits apart; a symbol is shorter, so it passes at most one)
+            const uint32_t  step       = seg * 8 / (NCHECK + 1); // bits between checkpoints (seg is a multiple of 4 bytes)
             uint32_t* const chk        = chk_all + tid;
             uint32_t        run_blocks = 0; // blocks of this thread's latest run
             // first decoding pass: guessed entry states (segment 0: the true one)
             if (mine)
             {
-                const seg_result r = run_segment<false>(S, words, pbeg, 0, 0, pend, 0, nullptr, chk, T, pbeg + seg, seg, false, 0);
+                const seg_result r = run_segment<false>(S, words, pbeg, 0, 0, pend, 0, nullptr, chk, T, pbeg + step, step, false, 0);
                 S.ent_p[tid]  = pbeg;
                 S.ent_bk[tid] = 0;
                 S.ext_p[tid]  = r.p;
@@ -894,7 +902,7 @@ namespace aeonb
                 if (redo)
                 {
                     const seg_result r =
-                        run_segment<false>(S, words, cand_p, cand_bk >> 8, cand_bk & 255, pend, 0, nullptr, chk, T, pbeg + seg, seg, true, run_blocks);
+                        run_segment<false>(S, words, cand_p, cand_bk >> 8, cand_bk & 255, pend, 0, nullptr, chk, T, pbeg + step, step, true, run_blocks);
                     S.ent_p[tid]  = cand_p;
                     S.ent_bk[tid] = cand_bk;
                     S.cnt[tid]    = r.blocks;
@@ -927,7 +935,7 @@ namespace aeonb
             {
                 const uint32_t t = q / (NCHECK + 1), piece = q % (NCHECK + 1);
                 const uint32_t seg_beg = t * seg * 8, seg_end = min(total_bit, seg_beg + seg * 8);
-                const uint32_t at = seg_beg + piece * seg; // the checkpoint this piece starts from (a segment is 8 * seg bits long)
+                const uint32_t at = seg_beg + piece * step; // the checkpoint this piece starts from
                 if (at >= seg_end)
                     continue;
                 uint32_t p0 = S.ent_p[t], bk = S.ent_bk[t], before = 0;
@@ -938,7 +946,7 @@ namespace aeonb
                     bk                 = (key >> 6 & 15) << 8 | (key & 63);
                     before             = chk_all[(NCHECK + piece - 1) * T + t];
                 }
-                const seg_result r = run_segment<true>(S, words, p0, bk >> 8, bk & 255, min(seg_end, at + seg), S.ext_p[t] + before, dcdiff,
+                const seg_result r = run_segment<true>(S, words, p0, bk >> 8, bk & 255, min(seg_end, at + step), S.ext_p[t] + before, dcdiff,
                                                        nullptr, 0, 0, 0, false, 0);
                 if (r.bad)
                     S.bad = 1;
