@@ -1,3 +1,4 @@
+#include <cstdlib>
 #include "runtime.hpp"
 
 #include <algorithm>
@@ -28,6 +29,16 @@ namespace aeonb
         m_wake_rest.notify_all();
         for (auto& t : m_threads)
             t.join();
+    }
+
+    int worker_pool::light_threads()
+    {
+        static const int value = [] {
+            const char* e = std::getenv("AEONB_LIGHT_THREADS");
+            const int   v = e ? std::atoi(e) : 3;
+            return v < 1 ? 1 : v > 64 ? 64 : v;
+        }();
+        return value;
     }
 
     void worker_pool::start(int count, std::function<void(int)> fn, bool light)

@@ -27,7 +27,8 @@ namespace aeonb
         // returns at once; wait() blocks until all are done and rethrows the first exception.
         // `light` wakes only the first k_light threads: a few hundred small copies finish sooner on three threads than on
         // a whole pool whose wake-up competes with the calling thread for the cores.
-        static constexpr int k_light = 3;
+        static int light_threads(); // AEONB_LIGHT_THREADS or 3
+        const int k_light = light_threads();
         void start(int count, std::function<void(int)> fn, bool light = false);
         void wait();
         // The calling thread takes part in the job started last: runs fn(i) for indices it draws from the same counter until
