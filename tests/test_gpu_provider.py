@@ -611,3 +611,61 @@ def test_blob_stage_copies_bytes_next_to_an_image(ctx):
         make_provider(ctx, cfg).run_host([(recs[0][0], b"x" * 21)] + recs[1:])
     with pytest.raises(AeonError, match="received blob with size 0"):
         make_provider(ctx, cfg).run_host([(recs[0][0], b"")] + recs[1:])
+
+
+def test_seven_batches_in_flight_match_blocking_calls(ctx):
+    """The caller plans batch t+1 while the provider's driver thread stages and launches batch t: submitting seven batches
+    before waiting for any must give what seven blocking calls give (same draws in the same record order, no buffer of a
+    batch reused before its kernels and copies have finished)."""
+    import torch
+    cfg = {"batch_size": 16, "random_seed": 5, "decode_size": 32,
+           "etl": [{"type": "image", "height": 64, "width": 80, "output_type": "float", "bgr_to_rgb": True},
+                   {"type": "label", "binary": True}],
+           "augmentation": [AUG_C2]}
+    recs = image_records(61, 7 * 16)
+    blocking = make_provider(ctx, cfg)
+    want = [{k: v.copy() for k, v in blocking.run_host(recs[16 * b:16 * b + 16]).items()} for b in range(7)]
+    for to_device in (False, True):
+        prov = make_provider(ctx, cfg)
+        if to_device:
+            bufs = [{"image": torch.full((16, 3, 64, 80), -1.0, dtype=torch.float32, device="cuda:%d" % ctx.device),
+                     "label": torch.full((16, 1), -1, dtype=torch.int32, device="cuda:%d" % ctx.device)} for _ in range(7)]
+            tickets = [prov.submit_device(recs[16 * b:16 * b + 16], bufs[b]) for b in range(7)]
+        else:
+            bufs = [{"image": torch.full((16, 3, 64, 80), -1.0, dtype=torch.float32).pin_memory().numpy(),
+                     "label": np.full((16, 1), -1, np.int32)} for _ in range(7)]
+            tickets = [prov.submit_host(recs[16 * b:16 * b + 16], bufs[b]) for b in range(7)]
+        for b in (3, 0, 1, 2, 6, 5, 4):  # any order
+            prov.wait(tickets[b])
+        for b in range(7):
+            img = bufs[b]["image"].cpu().numpy() if to_device else bufs[b]["image"]
+            lbl = bufs[b]["label"].cpu().numpy() if to_device else bufs[b]["label"]
+            assert np.array_equal(img, want[b]["image"]) and np.array_equal(lbl, want[b]["label"]), (to_device, b)
+
+
+def test_errors_of_pipelined_batches(ctx):
+    """What the calling thread finds while planning (an empty record) fails the submission itself and uses up no ticket; what
+    the driver thread or the GPU finds (a scan that ends early) is reported when that batch is waited for; the batches
+    around it are delivered and the provider stays usable."""
+    import torch
+    from aeon_b200._lib import AeonError
+    cfg = {"batch_size": 2, "random_seed": 34, "etl": [{"type": "image", "height": 64, "width": 64, "output_type": "uint8_t"}],
+           "augmentation": [{"type": "image"}]}
+    good = image_records(62, 1)[0][0]
+    sos = good.index(b"\xff\xda")
+    broken = good[:sos + 14 + 100] + b"\xff\xd9"
+    prov = make_provider(ctx, cfg)
+    want = prov.run_host([(good,), (good,)])["image"].copy()
+    bufs = [{"image": torch.zeros((2, 3, 64, 64), dtype=torch.uint8).pin_memory().numpy()} for _ in range(3)]
+    t0 = prov.submit_host([(good,), (good,)], bufs[0])
+    with pytest.raises(AeonError, match="size 0"):
+        prov.submit_host([(good,), (b"",)], bufs[1])
+    t1 = prov.submit_host([(good,), (broken,)], bufs[1])
+    t2 = prov.submit_host([(good,), (good,)], bufs[2])
+    assert (t1, t2) == (t0 + 1, t0 + 2)
+    prov.wait(t0)
+    with pytest.raises(AeonError, match="Decoding image failed"):
+        prov.wait(t1)
+    prov.wait(t2)
+    assert np.array_equal(bufs[0]["image"], want) and np.array_equal(bufs[2]["image"], want)
+    assert np.array_equal(prov.run_host([(good,), (good,)])["image"], want)
