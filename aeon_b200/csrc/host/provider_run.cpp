@@ -1,4 +1,7 @@
 // aeonb_provider::run -- one batch through the host stages and the GPU kernels.
+#if defined(__SSE2__)
+#include <emmintrin.h>
+#endif
 #include <algorithm>
 #include <atomic>
 #include <chrono>
@@ -190,6 +193,36 @@ aeonb_provider::~aeonb_provider()
     {
         cudaStreamSynchronize(m_copy);
         cudaStreamDestroy(m_copy);
+    }
+}
+
+namespace
+{
+    // Copy into the pinned staging buffer with stores that bypass the cache: the CPU never reads these bytes again (the
+    // copy engine does), so they need not evict anything nor be read in before they are overwritten.  dst is 16-byte aligned.
+    inline void stream_copy(void* dst, const void* src, size_t n)
+    {
+#if defined(__SSE2__)
+        static const bool plain = std::getenv("AEONB_PLAIN_STAGING_COPY") != nullptr;
+        if (!plain && (reinterpret_cast<uintptr_t>(dst) & 15) == 0)
+        {
+            __m128i*       d = static_cast<__m128i*>(dst);
+            const __m128i* s = static_cast<const __m128i*>(src);
+            const size_t   v = n / 64;
+            for (size_t i = 0; i < v; ++i, d += 4, s += 4)
+            {
+                const __m128i a = _mm_loadu_si128(s), b = _mm_loadu_si128(s + 1), c = _mm_loadu_si128(s + 2), e = _mm_loadu_si128(s + 3);
+                _mm_stream_si128(d, a);
+                _mm_stream_si128(d + 1, b);
+                _mm_stream_si128(d + 2, c);
+                _mm_stream_si128(d + 3, e);
+            }
+            std::memcpy(d, s, n - v * 64);
+            _mm_sfence();
+            return;
+        }
+#endif
+        std::memcpy(dst, src, n);
     }
 }
 
@@ -928,7 +961,7 @@ void aeonb_provider::stage_inputs(batch_plan& B, int par)
                     if (job.on_device)
                     {
                         std::memcpy(hstage + job.tables_off, job.tables, sizeof job.tables);
-                        std::memcpy(hstage + job.scan_off, job.frame.scan, job.frame.scan_size);
+                        stream_copy(hstage + job.scan_off, job.frame.scan, job.frame.scan_size);
                         remaining[group_of(i)].fetch_sub(1, std::memory_order_release);
                         return;
                     }
