@@ -199,15 +199,19 @@ aeonb_provider::~aeonb_provider()
 namespace
 {
     // Copy into the pinned staging buffer with stores that bypass the cache: the CPU never reads these bytes again (the
-    // copy engine does), so they need not evict anything nor be read in before they are overwritten.  dst is 16-byte aligned.
+    // copy engine does), so they need not evict anything nor be read in before they are overwritten.
     inline void stream_copy(void* dst, const void* src, size_t n)
     {
 #if defined(__SSE2__)
         static const bool plain = std::getenv("AEONB_PLAIN_STAGING_COPY") != nullptr;
-        if (!plain && (reinterpret_cast<uintptr_t>(dst) & 15) == 0)
+        if (!plain && n >= 256)
         {
-            __m128i*       d = static_cast<__m128i*>(dst);
-            const __m128i* s = static_cast<const __m128i*>(src);
+            // up to the first 16-byte boundary of dst the ordinary way
+            const size_t head = (16 - (reinterpret_cast<uintptr_t>(dst) & 15)) & 15;
+            std::memcpy(dst, src, head);
+            n -= head;
+            __m128i*       d = reinterpret_cast<__m128i*>(static_cast<char*>(dst) + head);
+            const __m128i* s = reinterpret_cast<const __m128i*>(static_cast<const char*>(src) + head);
             const size_t   v = n / 64;
             for (size_t i = 0; i < v; ++i, d += 4, s += 4)
             {
@@ -973,7 +977,7 @@ void aeonb_provider::stage_inputs(batch_plan& B, int par)
                 else
                 {
                     const batch_plan::copy_job& c = B.copies[i - njobs];
-                    std::memcpy(hstage + c.stage_off, c.src, c.bytes);
+                    stream_copy(hstage + c.stage_off, c.src, c.bytes);
                 }
             }
             catch (...)
