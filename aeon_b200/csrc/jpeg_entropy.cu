@@ -389,7 +389,7 @@ namespace aeonb
         // positions are plain offsets), then cut into one segment per thread.  Every thread decodes its
         // segment starting from a guessed state (block 0 of an MCU, DC coefficient next) and records the
         // state in which it leaves the segment: the bit position of the first symbol that starts past the
-        // segment's end, the block's index inside the MCU and the zig-zag index.  At seven evenly spaced
+        // segment's end, the block's index inside the MCU and the zig-zag index.  At three evenly spaced
         // checkpoints inside the segment it also notes the state of the first symbol at or past the
         // checkpoint and the blocks completed so far.  Rounds follow in which every thread takes its left
         // neighbour's exit state as its entry state and, if that differs from the entry it used before,
@@ -491,8 +491,8 @@ namespace aeonb
             return pack_symbol(len, T.vals[((c16 >> (16 - len)) + T.valoff[len]) & 255], T.is_ac != 0);
         }
 
-        constexpr int PAR_THREADS = 1024; // most threads (= segments) a stream can have; the launch picks the actual number
-        constexpr int NCHECK      = 7;    // checkpoints inside a segment
+        constexpr int PAR_THREADS = 512;  // most threads (= segments) a stream can have; the launch picks the actual number
+        constexpr int NCHECK      = 3;    // checkpoints inside a segment (7 measured the same; 3 leaves room for a third kernel's CTA on the SM)
 
         struct par_state
         {
