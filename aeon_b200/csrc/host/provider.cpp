@@ -277,7 +277,7 @@ aeonb_provider::aeonb_provider(aeonb_ctx* c, const json& cfg) : ctx(c)
         }
         stages.push_back(std::move(st));
     }
-    for (int k = 0; k < 2; ++k)
+    for (int k = 0; k < k_sets; ++k)
     {
         out_dev[k].resize(outputs.size());
         out_dev_t[k].resize(outputs.size());

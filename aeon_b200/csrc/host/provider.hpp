@@ -175,19 +175,22 @@ struct aeonb_provider
     int                                  slot_cursor = 0;
     std::unique_ptr<aeonb::worker_pool>  pool;
 
-    // Staging: compressed scans + tables (or coefficients) / decoded PNG pictures / samples.  Two sets, taken in turn:
-    // the host fills set p for batch t while the upload stream still copies set 1-p of batch t-1 and the kernels of
-    // batch t-1 read its device copy.
-    aeonb::pinned_buffer                 staging[2];
-    aeonb::device_buffer                 staging_dev[2];
-    // device entropy decoding: status words, coefficient planes, work areas.  Two sets, taken in turn, so that the
-    // entropy kernel of batch t+1 (on a stream of its own) can run beside the back end and image kernel of batch t,
-    // and beside the last long streams of batch t's own entropy kernel
-    aeonb::device_buffer                 coef_dev[2];
-    aeonb_ctx*                           m_entropy_ctx[2] = {nullptr, nullptr}; // contexts whose streams carry the entropy kernels, in turn
-    cudaEvent_t                          m_entropy_done[2] = {nullptr, nullptr}; // planes of set p are complete
-    cudaEvent_t                          m_coef_free[2]    = {nullptr, nullptr}; // the back end has read set p (batch t-2)
-    bool                                 m_coef_free_valid[2] = {false, false};
+    // Every per-batch buffer exists k_sets times, taken in turn (batch t uses set t % k_sets): a batch takes about two
+    // kernel periods from its staging upload to its last kernel (upload -> entropy kernel -> back end -> image kernel), so
+    // with three sets the upload and entropy kernel of batches t+1 and t+2 run beside the back end and image kernel of batch t.
+    static constexpr int k_sets = 3;
+    // Staging: compressed scans + tables (or coefficients) / decoded PNG pictures / samples: the host fills set p for
+    // batch t while the upload stream still copies the set of batch t-1 and the kernels of batch t-1 read its device copy.
+    aeonb::pinned_buffer                 staging[k_sets];
+    aeonb::device_buffer                 staging_dev[k_sets];
+    // device entropy decoding: status words, coefficient planes, work areas: the entropy kernel of batch t+1 (on a stream
+    // of its own) runs beside the back end and image kernel of batch t, and beside the last long streams of batch t's own
+    // entropy kernel
+    aeonb::device_buffer                 coef_dev[k_sets];
+    aeonb_ctx*                           m_entropy_ctx[k_sets] = {}; // contexts whose streams carry the entropy kernels, in turn
+    cudaEvent_t                          m_entropy_done[k_sets] = {}; // planes of set p are complete
+    cudaEvent_t                          m_coef_free[k_sets]    = {}; // the back end has read set p (batch t - k_sets)
+    bool                                 m_coef_free_valid[k_sets] = {};
     aeonb::device_buffer                 pixels_dev;   // decoded pictures
     aeonb::device_buffer                 oriented_dev; // pictures after the EXIF orientation pass
     aeonb::device_buffer                 rotated_dev;  // pictures after the rotation pass
@@ -198,11 +201,11 @@ struct aeonb_provider
     std::vector<aeonb::device_buffer>    rcnn_anchor_dev, rcnn_result_dev;
     std::vector<aeonb::pinned_buffer>    rcnn_result_host;
     aeonb::random_engine_t               rcnn_engine;
-    // Device-side outputs of batches delivered to host memory, double buffered: the copy of batch t to the host
-    // (on the copy stream) overlaps the kernels of batch t+1, which write the other set.
-    std::vector<aeonb::device_buffer>    out_dev[2];   // per output, batch_size records
-    std::vector<aeonb::device_buffer>    out_dev_t[2]; // transposed copies (batch_major == false)
-    aeonb::pinned_buffer                 small_pinned[2]; // host-produced outputs on their way to device memory, two sets as above
+    // Device-side outputs of batches delivered to host memory: the copy of batch t to the host (on the copy stream)
+    // overlaps the kernels of the next batches, which write the other sets.
+    std::vector<aeonb::device_buffer>    out_dev[k_sets];   // per output, batch_size records
+    std::vector<aeonb::device_buffer>    out_dev_t[k_sets]; // transposed copies (batch_major == false)
+    aeonb::pinned_buffer                 small_pinned[k_sets]; // host-produced outputs on their way to device memory
 
     static constexpr int k_events = 8;
     cudaEvent_t m_done[k_events]    = {}; // batch t complete: m_done[t % k_events]
@@ -213,12 +216,12 @@ struct aeonb_provider
     cudaEvent_t m_trace[k_events][8] = {};
     int         m_trace_slot = 0; // slot of the batch being enqueued
     cudaStream_t m_upload           = nullptr; // host -> device copies of the staging sets: they run under the previous batch's kernels
-    cudaEvent_t m_staged[2]         = {nullptr, nullptr}; // staging set p has been copied to the device (upload stream)
-    bool        m_staged_valid[2]   = {false, false};
-    cudaEvent_t m_consumed[2]       = {nullptr, nullptr}; // the kernels that read the device copy of set p have finished
-    bool        m_consumed_valid[2] = {false, false};
-    cudaEvent_t m_uploaded[2]       = {nullptr, nullptr}; // small pinned set p has been copied
-    bool        m_uploaded_valid[2] = {false, false};
+    cudaEvent_t m_staged[k_sets]         = {}; // staging set p has been copied to the device (upload stream)
+    bool        m_staged_valid[k_sets]   = {};
+    cudaEvent_t m_consumed[k_sets]       = {}; // the kernels that read the device copy of set p have finished
+    bool        m_consumed_valid[k_sets] = {};
+    cudaEvent_t m_uploaded[k_sets]       = {}; // small pinned set p has been copied
+    bool        m_uploaded_valid[k_sets] = {};
     int64_t     m_ticket            = 0;       // number of batches submitted so far (calling thread)
     // A submitted batch is planned on the calling thread (headers, draws: the only phase that needs the records in
     // record order) and handed to the driver thread, which reserves memory, stages, launches and delivers one batch

@@ -173,11 +173,11 @@ aeonb_provider::~aeonb_provider()
         for (cudaEvent_t e : slot)
             if (e)
                 cudaEventDestroy(e);
-    for (int k = 0; k < 2; ++k)
+    for (int k = 0; k < k_sets; ++k)
         for (cudaEvent_t e : {m_uploaded[k], m_staged[k], m_consumed[k]})
             if (e)
                 cudaEventDestroy(e);
-    for (int k = 0; k < 2; ++k)
+    for (int k = 0; k < k_sets; ++k)
         for (cudaEvent_t e : {m_entropy_done[k], m_coef_free[k]})
             if (e)
                 cudaEventDestroy(e);
@@ -364,7 +364,7 @@ void aeonb_provider::process(batch_job& job)
     cudaStream_t st = ctx->stream;
     if (!m_upload)
     {
-        for (int k = 0; k < 2; ++k)
+        for (int k = 0; k < k_sets; ++k)
         {
             AEONB_CUDA(cudaEventCreateWithFlags(&m_uploaded[k], cudaEventDisableTiming));
             AEONB_CUDA(cudaEventCreateWithFlags(&m_staged[k], cudaEventDisableTiming));
@@ -376,7 +376,7 @@ void aeonb_provider::process(batch_job& job)
         for (cudaEvent_t& e : m_kernels)
             AEONB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         AEONB_CUDA(cudaStreamCreateWithFlags(&m_copy, cudaStreamNonBlocking));
-        for (int k = 0; k < 2; ++k)
+        for (int k = 0; k < k_sets; ++k)
         {
             AEONB_CUDA(cudaEventCreateWithFlags(&m_entropy_done[k], cudaEventDisableTiming));
             AEONB_CUDA(cudaEventCreateWithFlags(&m_coef_free[k], cudaEventDisableTiming));
@@ -385,12 +385,12 @@ void aeonb_provider::process(batch_job& job)
             if (aeonb_ctx_create(ctx->device, nullptr, &e) != AEONB_OK)
                 throw error(AEONB_ERR_CUDA, aeonb_last_error());
     }
-    // Batch T writes its device-side outputs into buffer set `par`, last used by batch T - 2, whose copy to the
+    // Batch T writes its device-side outputs into buffer set `par`, last used by batch T - k_sets, whose copy to the
     // host may still be running on the copy stream: kernels wait for it.
-    const int par = (int)(T & 1);
-    if (!on_device && T >= 3)
-        AEONB_CUDA(cudaStreamWaitEvent(st, m_done[(T - 2) % k_events], 0));
-    // The pinned staging set of this batch was last used two batches ago: its copy to the device must have finished.
+    const int par = (int)(T % k_sets);
+    if (!on_device && T > k_sets)
+        AEONB_CUDA(cudaStreamWaitEvent(st, m_done[(T - k_sets) % k_events], 0));
+    // The pinned staging set of this batch was last used k_sets batches ago: its copy to the device must have finished.
     if (m_staged_valid[par])
         AEONB_CUDA(cudaEventSynchronize(m_staged[par]));
     const int64_t launches_before = ctx->launches;
@@ -924,7 +924,7 @@ void aeonb_provider::stage_inputs(batch_plan& B, int par)
     // ---- 3. entropy decode on the pool, shipping finished slices while the rest decode
     char* const hstage = static_cast<char*>(staging[par].p);
     char* const dstage = static_cast<char*>(staging_dev[par].p);
-    // the device copy of this set was read by the kernels of two batches ago
+    // the device copy of this set was read by the kernels of k_sets batches ago
     if (m_consumed_valid[par])
         AEONB_CUDA(cudaStreamWaitEvent(m_upload, m_consumed[par], 0));
     const int   njobs  = (int)B.jobs.size();
@@ -1055,8 +1055,8 @@ void aeonb_provider::launch_kernels(batch_plan& B, int n, int par)
         if (B.n_device_jobs > 0)
         {
             // The entropy kernel runs on a stream of its own: it needs this batch's staged inputs and the coefficient set
-            // that the back end of two batches ago has read, nothing else -- so it runs beside the previous batch's back
-            // end and image kernel, and (two such streams, taken in turn) beside the last long streams of the previous
+            // that the back end of k_sets batches ago has read, nothing else -- so it runs beside the previous batch's back
+            // end and image kernel, and (k_sets such streams, taken in turn) beside the last long streams of the previous
             // batch's entropy kernel: a launch lasts as long as its longest stream, the SMs of the others fall idle.  (With the per-kernel
             // profile on, everything stays on one stream: a timed kernel then runs alone.)
             static const bool own_stream = [] {
@@ -1438,7 +1438,7 @@ void aeonb_provider::deliver(batch_plan& B, void* const* outs, int n, bool on_de
         if (outputs[o].host_produced && on_device)
             small_total += align_up(B.out_host[o].size(), 256);
     if (small_total > 0 && m_uploaded_valid[par])
-        AEONB_CUDA(cudaEventSynchronize(m_uploaded[par])); // the small pinned set is reused too (last used two batches ago)
+        AEONB_CUDA(cudaEventSynchronize(m_uploaded[par])); // the small pinned set is reused too (last used k_sets batches ago)
     small_pinned[par].reserve(small_total + 256);
     size_t small_off = 0;
     for (size_t o = 0; o < outputs.size(); ++o)
