@@ -394,10 +394,7 @@ void aeonb_provider::process(batch_job& job)
     if (m_staged_valid[par])
         AEONB_CUDA(cudaEventSynchronize(m_staged[par]));
     const int64_t launches_before = ctx->launches;
-    int64_t       h2d_before = h2d_bytes, d2h_before = d2h_bytes;
     h2d_bytes = d2h_bytes = 0;
-    (void)h2d_before;
-    (void)d2h_before;
     mark(0);
     const int trace_slot = (int)(T % k_events);
     if (trace)

@@ -578,15 +578,15 @@ def main():
         torch.cuda.synchronize()
 
     ts = ctx.torch_stream
-    # Steps are software-pipelined over two streams of the library (two contexts): the entropy kernel of step i+1 runs on
-    # the first while the back end and the image kernel of step i run on the second, which fills the tail of the entropy
+    # Steps are software-pipelined over streams of the library (one context each): the entropy kernel of step i+1 runs on
+    # one while the back end and the image kernel of step i run on another, which fills the tail of the entropy
     # kernel (few long streams left) with the other two kernels' blocks.  Every step still runs its three kernels in order
     # on its own buffers (the four batch sets rotate; a set is reused only after its image kernel has finished).
     two_streams = on_dev
     ctx2 = K.Context(local_rank) if two_streams else None
-    # ... and the entropy kernels of consecutive steps alternate between two streams, so that the next one's blocks take
-    # the SMs the current one's finished streams leave (a launch lasts as long as its longest stream)
-    ctx_e = [ctx, K.Context(local_rank)] if two_streams else [ctx]
+    # ... and the entropy kernels of consecutive steps take three streams in turn, as the provider's do, so that the next
+    # ones' blocks take the SMs the current one's finished streams leave (a launch lasts as long as its longest stream)
+    ctx_e = [ctx, K.Context(local_rank), K.Context(local_rank)] if two_streams else [ctx]
 
     def run_steps(count):
         """Enqueues `count` steps; returns the stream whose tail marks the end of the work."""
@@ -635,7 +635,8 @@ def main():
         ev[0].record(ts)
         if two_streams:
             ctx2.torch_stream.wait_event(ev[0])
-            ctx_e[1].torch_stream.wait_event(ev[0])
+            for ce in ctx_e[1:]:
+                ce.torch_stream.wait_event(ev[0])
         run_steps(args.steps).record_event(ev[1])
         barrier()
         t = torch.tensor([ev[0].elapsed_time(ev[1])], dtype=torch.float64, device=dev)
@@ -709,7 +710,7 @@ def main():
             "config": {"workload": W["describe"],
                        "l2": "four distinct batches (1024 records) cycle; their inputs total several hundred MB, larger than the 126 MB L2",
                        "records_per_gpu_per_step": BATCH, "decode": "crop regions only (MCUs the crop box can touch)",
-                       "entropy_decode": args.entropy, "kernel_streams": 3 if two_streams else 1,
+                       "entropy_decode": args.entropy, "kernel_streams": 1 + len(ctx_e) if two_streams else 1,
                        "resident_input": "compressed JPEG scans + tables" if on_dev else "coefficient planes (Huffman-decoded on the host, untimed)"},
             "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_kind": peak_kind, "frac_of_8tbs_nominal": achieved / 8000.0,
