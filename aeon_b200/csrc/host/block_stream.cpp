@@ -6,12 +6,14 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 #include <ctime>
 #include <fstream>
 #include <sstream>
 #include <stdexcept>
+#include <thread>
 
 using namespace std;
 
@@ -21,13 +23,6 @@ namespace aeonb
     {
         // ---- old binary cpio member header: thirteen 16-bit fields, name (with its NUL) and data each padded to even length
         void put16(ostream& o, uint16_t v) { o.write(reinterpret_cast<const char*>(&v), 2); }
-        uint16_t get16(istream& i)
-        {
-            uint16_t v = 0;
-            i.read(reinterpret_cast<char*>(&v), 2);
-            return v;
-        }
-
         void write_member_header(ostream& o, uint32_t size, const char* name)
         {
             const uint16_t namesize = (uint16_t)(strlen(name) + 1);
@@ -50,25 +45,6 @@ namespace aeonb
                 o.put(0);
         }
 
-        uint32_t read_member_header(istream& i, string& name)
-        {
-            if (get16(i) != 070707 || !i)
-                throw runtime_error("CPIO header magic incorrect");
-            for (int k = 0; k < 9; ++k) // dev, ino, mode, uid, gid, nlink, rdev, mtime
-                get16(i);
-            const uint16_t namesize = get16(i);
-            const uint32_t hi = get16(i), lo = get16(i);
-            name.assign(namesize, '\0');
-            i.read(&name[0], namesize);
-            if (!name.empty())
-                name.pop_back();
-            if (namesize % 2)
-                i.get();
-            if (!i)
-                throw runtime_error("cache system: cache file corrupted");
-            return hi << 16 | lo;
-        }
-
         void write_file_header(ostream& o, uint32_t record_count, uint32_t elements_field)
         {
             const uint32_t one = 1;
@@ -80,6 +56,52 @@ namespace aeonb
             o.write(reinterpret_cast<const char*>(&elements_field), 4);
             const char unused[36] = {};
             o.write(unused, sizeof unused);
+        }
+
+        // fn(i) for i in [0, n) on a few threads of this call's own (a block is thousands of records: file reads and copies of
+        // tens of kilobytes each); small jobs run on the calling thread.  The first exception is rethrown.
+        template <typename F>
+        void parallel_for(size_t n, size_t grain, F fn)
+        {
+            const size_t hw      = std::max(1u, thread::hardware_concurrency());
+            const size_t threads = std::min<size_t>(std::min<size_t>(8, std::max<size_t>(1, hw / 2)), n / std::max<size_t>(grain, 1));
+            if (threads <= 1)
+            {
+                for (size_t i = 0; i < n; ++i)
+                    fn(i);
+                return;
+            }
+            atomic<size_t>  next{0};
+            exception_ptr   failure;
+            mutex           failure_mutex;
+            auto body = [&] {
+                for (;;)
+                {
+                    const size_t first = next.fetch_add(grain);
+                    if (first >= n)
+                        return;
+                    try
+                    {
+                        for (size_t i = first; i < std::min(n, first + grain); ++i)
+                            fn(i);
+                    }
+                    catch (...)
+                    {
+                        lock_guard<mutex> lk(failure_mutex);
+                        if (!failure)
+                            failure = current_exception();
+                        next.store(n);
+                    }
+                }
+            };
+            vector<thread> team;
+            for (size_t t = 1; t < threads; ++t)
+                team.emplace_back(body);
+            body();
+            for (thread& t : team)
+                t.join();
+            if (failure)
+                rethrow_exception(failure);
         }
 
         bool exists(const string& path)
@@ -122,41 +144,79 @@ namespace aeonb
 
     vector<encoded_record> cpio_read_block(const string& path, size_t elements_per_record)
     {
-        ifstream i(path, ios::binary);
-        if (!i)
-            throw runtime_error("cache system: cache file missed");
-        string name;
-        const uint32_t header_size = read_member_header(i, name);
-        if (header_size != 64)
-            throw runtime_error("unexpected header size.  expected 64 found " + to_string(header_size));
-        char     magic[4];
-        uint32_t versions[2], record_count = 0, elements_field = 0;
-        char     skip[36];
-        i.read(magic, 4);
-        if (strncmp(magic, "MACR", 4) != 0)
-            throw runtime_error("Unrecognized format\n");
-        i.read(reinterpret_cast<char*>(versions), 8);
-        i.read(skip, 8);
-        i.read(reinterpret_cast<char*>(&record_count), 4);
-        i.read(reinterpret_cast<char*>(&elements_field), 4);
-        i.read(skip, 36);
-        if (!i || record_count == 0)
-            throw runtime_error("cache system: cache file corrupted");
-        vector<encoded_record> out(record_count);
-        for (encoded_record& rec : out)
+        // One walk over the member headers finds where every element lies; the elements are then read straight into their
+        // vectors by several threads (the page cache hands a block out at memcpy speed, one thread does not keep up with
+        // the GPU).
+        struct file
         {
-            rec.resize(elements_per_record);
-            for (vector<char>& e : rec)
+            int fd;
+            ~file()
             {
-                const uint32_t size = read_member_header(i, name);
-                e.resize(size);
-                i.read(e.data(), size);
-                if (size % 2)
-                    i.get();
-                if (!i)
-                    throw runtime_error("cache system: cache file corrupted");
+                if (fd >= 0)
+                    close(fd);
             }
-        }
+        } f{open(path.c_str(), O_RDONLY)};
+        if (f.fd < 0)
+            throw runtime_error("cache system: cache file missed");
+        struct stat st;
+        if (fstat(f.fd, &st) != 0)
+            throw runtime_error("cache system: cache file missed");
+        const size_t file_size = (size_t)st.st_size;
+        auto read_at = [&](void* dst, size_t size, size_t at) {
+            size_t done = 0;
+            while (done < size)
+            {
+                const ssize_t got = pread(f.fd, static_cast<char*>(dst) + done, size - done, (off_t)(at + done));
+                if (got <= 0)
+                    throw runtime_error("cache system: cache file corrupted");
+                done += (size_t)got;
+            }
+        };
+        // returns the data offset of the member that starts at `at`, its size in `size`, and moves `at` past it
+        auto member = [&](size_t& at, uint32_t& size) -> size_t {
+            uint16_t h[13];
+            read_at(h, sizeof h, at);
+            if (h[0] != 070707)
+                throw runtime_error("CPIO header magic incorrect");
+            const size_t namesize = h[10];
+            size                  = (uint32_t)h[11] << 16 | h[12];
+            const size_t data_at  = at + sizeof h + namesize + namesize % 2;
+            if (data_at + size > file_size)
+                throw runtime_error("cache system: cache file corrupted");
+            at                    = data_at + size + size % 2;
+            return data_at;
+        };
+        size_t       at   = 0;
+        uint32_t     size = 0;
+        const size_t header_at = member(at, size);
+        if (size != 64)
+            throw runtime_error("unexpected header size.  expected 64 found " + to_string(size));
+        char head[24];
+        read_at(head, sizeof head, header_at);
+        if (strncmp(head, "MACR", 4) != 0)
+            throw runtime_error("Unrecognized format\n");
+        uint32_t record_count = 0;
+        memcpy(&record_count, head + 20, 4);
+        if (record_count == 0)
+            throw runtime_error("cache system: cache file corrupted");
+        struct span
+        {
+            size_t   at;
+            uint32_t size;
+        };
+        vector<span> spans((size_t)record_count * elements_per_record);
+        for (span& sp : spans)
+            sp.at = member(at, sp.size);
+        vector<encoded_record> out(record_count);
+        parallel_for(record_count, 16, [&](size_t r) {
+            out[r].resize(elements_per_record);
+            for (size_t e = 0; e < elements_per_record; ++e)
+            {
+                const span& sp = spans[r * elements_per_record + e];
+                out[r][e].resize(sp.size);
+                read_at(out[r][e].data(), sp.size, sp.at);
+            }
+        });
         return out;
     }
 
@@ -255,10 +315,78 @@ namespace aeonb
             m_cache.reset(new block_cache(m.crc, m.blocks.size(), m.types.size(), cache_root, shuffle, seed));
     }
 
+    block_stream::~block_stream()
+    {
+        {
+            lock_guard<mutex> lk(m_mutex);
+            m_quit = true;
+        }
+        m_cv.notify_all();
+        if (m_worker.joinable())
+            m_worker.join();
+    }
+
+    // The worker loads one block ahead: asked for block k+1 at the moment block k is handed to the consumer (so the order
+    // of loads, cache writes and shuffles -- and with it every generator's state -- is the same as without it).
+    void block_stream::worker()
+    {
+        for (;;)
+        {
+            {
+                unique_lock<mutex> lk(m_mutex);
+                m_cv.wait(lk, [&] { return m_quit || m_state == ahead::wanted; });
+                if (m_quit)
+                    return;
+            }
+            vector<encoded_record> block;
+            exception_ptr          failure;
+            try
+            {
+                block = load_block();
+            }
+            catch (...)
+            {
+                failure = current_exception();
+            }
+            {
+                lock_guard<mutex> lk(m_mutex);
+                m_next       = std::move(block);
+                m_next_error = failure;
+                m_state      = ahead::ready;
+            }
+            m_cv.notify_all();
+        }
+    }
+
+    void block_stream::request_block()
+    {
+        {
+            lock_guard<mutex> lk(m_mutex);
+            if (!m_worker.joinable())
+                m_worker = thread([this] { worker(); });
+            m_state = ahead::wanted;
+        }
+        m_cv.notify_all();
+    }
+
+    // Waits for the block being loaded, if any; what it produced (or threw) stays in m_next / m_next_error.
+    void block_stream::settle()
+    {
+        unique_lock<mutex> lk(m_mutex);
+        m_cv.wait(lk, [&] { return m_state != ahead::wanted; });
+    }
+
     void block_stream::reset()
     {
         // every stage of aeon's chain starts over (src/async_manager.hpp:119-131): the manifest deals a new block order
-        // when it shuffles, the block manager and the cache go back to block 0
+        // when it shuffles, the block manager and the cache go back to block 0; the block loaded ahead is dropped
+        settle();
+        {
+            lock_guard<mutex> lk(m_mutex);
+            m_state = ahead::none;
+        }
+        m_next.clear();
+        m_next_error = nullptr;
         m_manifest.reset();
         m_manifest_at  = 0;
         m_block_number = 0;
@@ -268,22 +396,16 @@ namespace aeonb
         m_at = 0;
     }
 
-    // aeon block_manager::filler (src/block_manager.cpp:61-106)
-    void block_stream::next_block()
+    // aeon block_manager::filler (src/block_manager.cpp:61-106); the records of a block are read by a few threads at once
+    vector<encoded_record> block_stream::load_block()
     {
-        m_block.clear();
-        m_at = 0;
         if (m_cache && m_cache->is_complete())
-        {
-            m_block = m_cache->load_block();
-            return;
-        }
-        const auto range = m_manifest.blocks[m_manifest.block_sequence[m_manifest_at++]];
-        m_block.resize(range.second - range.first);
-        for (size_t i = range.first; i < range.second; ++i)
-            m_load(m_manifest.records[i], m_block[i - range.first]);
+            return m_cache->load_block();
+        const auto             range = m_manifest.blocks[m_manifest.block_sequence[m_manifest_at++]];
+        vector<encoded_record> block(range.second - range.first);
+        parallel_for(block.size(), 16, [&](size_t i) { m_load(m_manifest.records[range.first + i], block[i]); });
         if (m_cache && m_cache->is_ownership())
-            m_cache->store_block(m_block);
+            m_cache->store_block(block);
         if (++m_block_number == m_manifest.blocks.size())
         {
             // the record stream never ends: back to the start of the data set
@@ -294,7 +416,34 @@ namespace aeonb
                 m_cache->try_get_access();
         }
         if (m_shuffle)
-            std::shuffle(m_block.begin(), m_block.end(), m_random);
+            std::shuffle(block.begin(), block.end(), m_random);
+        return block;
+    }
+
+    void block_stream::next_block()
+    {
+        bool idle;
+        {
+            lock_guard<mutex> lk(m_mutex);
+            idle = m_state == ahead::none;
+        }
+        if (idle)
+            request_block(); // the very first block, or the first after a reset
+        settle();
+        {
+            lock_guard<mutex> lk(m_mutex);
+            m_state = ahead::none;
+        }
+        if (m_next_error)
+        {
+            exception_ptr e = m_next_error;
+            m_next_error    = nullptr;
+            rethrow_exception(e);
+        }
+        m_block = std::move(m_next);
+        m_next.clear();
+        m_at = 0;
+        request_block();
     }
 
     encoded_record block_stream::next()

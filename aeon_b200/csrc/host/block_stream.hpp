@@ -1,13 +1,19 @@
 // The endless stream of encoded records behind the loader: aeon's manifest blocks -> block_loader_file ->
 // block_manager chain (src/block_loader_file.cpp:45-117, src/block_manager.cpp:61-106) with the CPIO block cache
 // (src/cache_system.cpp:69-146, src/cpio.cpp), as one pull-style object: the loader's producer thread asks for the
-// next record and the stream loads, caches and shuffles whole blocks behind it.
+// next record and the stream loads, caches and shuffles whole blocks behind it, one block ahead of the consumer on a
+// thread of its own (aeon runs these stages as async_manager threads, src/async_manager.hpp:91-117).
 #pragma once
 
+#include <condition_variable>
 #include <cstdint>
+#include <exception>
 #include <functional>
+#include <memory>
+#include <mutex>
 #include <random>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "loader.hpp"
@@ -65,8 +71,20 @@ namespace aeonb
         void                  reset(); // aeon loader::reset: back to the first block; generators keep their state
         const block_cache*    cache() const { return m_cache.get(); }
 
+        ~block_stream();
+
     private:
-        void next_block();
+        enum class ahead
+        {
+            none,   // nothing asked for
+            wanted, // the worker is loading the next block
+            ready   // it is in m_next (or m_next_error says why not)
+        };
+        void                         next_block();
+        std::vector<encoded_record>  load_block(); // worker thread only
+        void                         worker();
+        void                         request_block();
+        void                         settle();
         manifest&                    m_manifest;
         std::function<void(const std::vector<std::string>&, encoded_record&)> m_load;
         bool                         m_shuffle;
@@ -74,7 +92,15 @@ namespace aeonb
         std::unique_ptr<block_cache> m_cache;
         size_t                       m_block_number = 0; // blocks read from the manifest in this pass
         size_t                       m_manifest_at  = 0; // position in the manifest's block sequence
-        std::vector<encoded_record>  m_block;
+        std::vector<encoded_record>  m_block;            // the block being handed out
         size_t                       m_at = 0;
+        // one block ahead, loaded by a thread of its own
+        std::thread                  m_worker;
+        std::mutex                   m_mutex;
+        std::condition_variable      m_cv;
+        ahead                        m_state = ahead::none;
+        bool                         m_quit  = false;
+        std::vector<encoded_record>  m_next;
+        std::exception_ptr           m_next_error;
     };
 }

@@ -1,3 +1,6 @@
+#include <fcntl.h>
+#include <sys/stat.h>
+#include <unistd.h>
 #include "loader.hpp"
 #include "block_stream.hpp"
 
@@ -40,15 +43,25 @@ namespace
 
     vector<char> read_file(const string& path)
     {
-        std::ifstream f(path, std::ios::binary);
-        if (!f)
+        const int fd = ::open(path.c_str(), O_RDONLY);
+        if (fd < 0)
             throw std::runtime_error("error opening file '" + path + "'");
-        f.seekg(0, std::ios::end);
-        std::streamoff n = f.tellg();
-        f.seekg(0);
-        vector<char> data((size_t)std::max<std::streamoff>(n, 0));
-        if (n > 0)
-            f.read(data.data(), n);
+        struct stat st;
+        vector<char> data;
+        if (::fstat(fd, &st) == 0 && st.st_size > 0)
+        {
+            data.resize((size_t)st.st_size);
+            size_t at = 0;
+            while (at < data.size())
+            {
+                const ssize_t got = ::read(fd, data.data() + at, data.size() - at);
+                if (got <= 0)
+                    break;
+                at += (size_t)got;
+            }
+            data.resize(at);
+        }
+        ::close(fd);
         return data;
     }
 }
