@@ -439,6 +439,40 @@ def host_link_ceiling(dev, world, d2h_bytes, h2d_bytes, barrier):
     return out
 
 
+def measure_loader(name, device_output, batches=60):
+    """Records/s through the drop-in loader (aeon_b200.DataLoader: manifest -> files -> blocks -> provider pipeline), the
+    records written as files under a temporary directory (shared memory when the box has it)."""
+    import base64
+    import shutil
+    import tempfile
+    from aeon_b200 import DataLoader
+    w = WORKLOADS[name]
+    recs = make_records(name, w["records"])
+    root = tempfile.mkdtemp(dir="/dev/shm" if os.path.isdir("/dev/shm") else None)
+    try:
+        lines = ["@FILE\tBINARY"]
+        for i, (blob, label) in enumerate(recs):
+            with open(os.path.join(root, "%05d.jpg" % i), "wb") as f:
+                f.write(blob)
+            lines.append("%05d.jpg\t%s" % (i, base64.b64encode(label).decode()))
+        with open(os.path.join(root, "manifest.tsv"), "w") as f:
+            f.write("\n".join(lines) + "\n")
+        cfg = provider_config(name, manifest_filename=os.path.join(root, "manifest.tsv"), manifest_root=root,
+                              iteration_mode="INFINITE", device_output=device_output)
+        it = iter(DataLoader(cfg))
+        for _ in range(8):
+            next(it)
+        t0 = time.perf_counter()
+        for _ in range(batches):
+            next(it)
+        dt = time.perf_counter() - t0
+        del it
+        return {"value": batches * w["batch"] / dt, "unit": "records/s", "ms_per_batch": 1e3 * dt / batches, "batches": batches,
+                "source": "%d files, manifest TSV, block size 5000, no cache directory" % len(recs)}
+    finally:
+        shutil.rmtree(root, ignore_errors=True)
+
+
 def measure_config(ctx, name, threads, peak, repeats, dev):
     """One of the other benchmark configurations through the provider: records/s with the batch left in device memory
     and copied to pinned host memory (pipelined calls, median of `repeats`), and the device time of each kernel with
@@ -688,6 +722,11 @@ def main():
     # one float32 batch device -> pinned host, one batch of compressed scans pinned host -> device (the ceiling of `e2e`)
     link = host_link_ceiling(dev, world, stats["e2e"]["d2h_bytes"], stats["e2e"]["h2d_bytes"], barrier)
 
+    # ---------------- the same configuration through the drop-in loader (one GPU, like the other configurations below)
+    loader_lines = None
+    if world == 1 and not args.headline_only:
+        loader_lines = {"device_output": measure_loader(HEADLINE, True), "host_output": measure_loader(HEADLINE, False)}
+
     # ---------------- the other configurations (one GPU: they are not part of the scaling runs)
     configs = {}
     if world == 1 and not args.headline_only:
@@ -728,6 +767,8 @@ def main():
                                   "d2h_bytes_per_step": stats["e2e_device_output"]["d2h_bytes"],
                                   "ms_per_step_repeats": results["e2e_device_output"]},
             "host_link": link,
+            # not part of the contract: aeon_b200.DataLoader (aeon's python iterator) from files on disk, same configuration
+            "loader": loader_lines,
             "configs": configs,
             "gpu_launches": (3 if on_dev else 2) * args.steps, "clocks": clocks,
         }
