@@ -515,7 +515,16 @@ int aeonb_jpeg_entropy_batch(aeonb_ctx* ctx, const aeonb_entropy_desc* descs, in
                     bytes += (int64_t)(r.roi[2] - r.roi[0]) * r.hs[c] * (r.roi[3] - r.roi[1]) * r.vs[c] * 128;
             }
         launch_timer timer(ctx, AEONB_KERNEL_ENTROPY, bytes);
-        cudaError_t  e = launch_jpeg_entropy(ddev, n, any_parallel, any_serial, jpeg_entropy_min_segment(), ctx->stream);
+        // A launch of short streams (video frames) takes smaller blocks: its streams have few segments, and more blocks fit an SM.
+        uint32_t longest = 0;
+        for (int i = 0; i < n; ++i)
+            if (descs[i].scratch && descs[i].restart_interval == 0)
+                longest = std::max(longest, descs[i].scan_size);
+        const int segments = (int)((longest + (uint32_t)jpeg_entropy_min_segment() - 1) / (uint32_t)jpeg_entropy_min_segment());
+        int       threads  = jpeg_entropy_threads();
+        while (threads > 128 && segments <= threads / 2)
+            threads /= 2;
+        cudaError_t  e = launch_jpeg_entropy(ddev, n, any_parallel, any_serial, jpeg_entropy_min_segment(), threads, ctx->stream);
         if (e != cudaSuccess)
             throw error(AEONB_ERR_CUDA, cuda_message("jpeg entropy kernel launch", e));
         ctx->launches += (any_parallel ? 1 : 0) + (any_serial ? 1 : 0);

@@ -122,9 +122,11 @@ namespace aeonb
     size_t      jpeg_backend_smem(const aeonb_jpeg_desc& d);
     int         jpeg_backend_strip(); // MCU rows one CTA of the back-end kernel handles
     // Entropy kernels: the block-parallel one takes the records that have a work area and no restart markers,
-    // the one-warp serial one the rest.  min_segment: smallest segment (bytes) a thread of the parallel kernel decodes.
+    // the one-warp serial one the rest.  min_segment: smallest segment (bytes) a thread of the parallel kernel decodes;
+    // threads: threads (= most segments) per stream of this launch, at most jpeg_entropy_threads().
     cudaError_t launch_jpeg_entropy(const aeonb_entropy_desc* descs_dev, int n, bool any_parallel, bool any_serial, int min_segment,
-                                    cudaStream_t stream);
+                                    int threads, cudaStream_t stream);
     int64_t     jpeg_entropy_scratch_bytes(const aeonb_entropy_desc& d);
     int         jpeg_entropy_min_segment(); // AEONB_ENTROPY_SEGMENT or the default
+    int         jpeg_entropy_threads();     // AEONB_ENTROPY_THREADS or the default: most threads per stream
 }

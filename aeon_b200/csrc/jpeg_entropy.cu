@@ -19,6 +19,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <algorithm>
 #include <cstdlib>
 
 #include "../../include/aeon_b200.h"
@@ -1039,17 +1040,18 @@ namespace aeonb
     }
 
     cudaError_t launch_jpeg_entropy(const aeonb_entropy_desc* descs_dev, int n, bool any_parallel, bool any_serial, int min_segment,
-                                    cudaStream_t stream)
+                                    int threads, cudaStream_t stream)
     {
         if (n <= 0)
             return cudaSuccess;
         if (any_parallel)
         {
-            const size_t smem = sizeof(par_state) + (size_t)2 * NCHECK * jpeg_entropy_threads() * sizeof(uint32_t);
+            threads           = std::min(std::max(threads, 64), jpeg_entropy_threads()) & ~31;
+            const size_t smem = sizeof(par_state) + (size_t)2 * NCHECK * threads * sizeof(uint32_t);
             cudaError_t  err  = cudaFuncSetAttribute(jpeg_entropy_parallel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (err != cudaSuccess)
                 return err;
-            jpeg_entropy_parallel_kernel<<<n, jpeg_entropy_threads(), smem, stream>>>(descs_dev, min_segment);
+            jpeg_entropy_parallel_kernel<<<n, threads, smem, stream>>>(descs_dev, min_segment);
             err = cudaGetLastError();
             if (err != cudaSuccess)
                 return err;
