@@ -484,11 +484,11 @@ def measure_config(ctx, name, threads, peak, repeats, dev):
     chunks = [recs[i:i + batch] for i in range(0, len(recs), batch)]
     prov = Provider(ctx, provider_config(name, decode_threads=threads))
     DEPTH = 5
-    steps = max(2 * len(chunks), DEPTH + 1)
+    steps = max(2 * len(chunks), DEPTH + 1, 40)   # at least 40 batches per timed region
     out = {"workload": w["describe"], "batch": batch, "batches_cycled": len(chunks)}
     for key, to_device in (("e2e_device_output", True), ("e2e", False)):
         bufs = provider_buffers(prov, DEPTH, to_device, dev)
-        pipelined(prov, chunks, bufs, DEPTH + 1, DEPTH, to_device)   # warm-up
+        pipelined(prov, chunks, bufs, max(DEPTH + 1, 2 * len(chunks)), DEPTH, to_device)   # warm-up: every batch twice, every buffer once
         secs = [pipelined(prov, chunks, bufs, steps, DEPTH, to_device) for _ in range(repeats)]
         s = summarize([1e3 * t / steps for t in secs])
         st = prov.stats()
