@@ -439,7 +439,7 @@ def host_link_ceiling(dev, world, d2h_bytes, h2d_bytes, barrier):
     return out
 
 
-def measure_loader(name, device_output, batches=60):
+def measure_loader(name, device_output, batches=60, repeats=5):
     """Records/s through the drop-in loader (aeon_b200.DataLoader: manifest -> files -> blocks -> provider pipeline), the
     records written as files under a temporary directory (shared memory when the box has it)."""
     import base64
@@ -462,12 +462,15 @@ def measure_loader(name, device_output, batches=60):
         it = iter(DataLoader(cfg))
         for _ in range(8):
             next(it)
-        t0 = time.perf_counter()
-        for _ in range(batches):
-            next(it)
-        dt = time.perf_counter() - t0
+        times = []
+        for _ in range(repeats):
+            t0 = time.perf_counter()
+            for _ in range(batches):
+                next(it)
+            times.append(1e3 * (time.perf_counter() - t0) / batches)
         del it
-        return {"value": batches * w["batch"] / dt, "unit": "records/s", "ms_per_batch": 1e3 * dt / batches, "batches": batches,
+        stat = summarize(times)
+        return {"value": w["batch"] / (stat["median"] * 1e-3), "unit": "records/s", "ms_per_batch": stat, "batches": batches,
                 "source": "%d files, manifest TSV, block size 5000, no cache directory" % len(recs)}
     finally:
         shutil.rmtree(root, ignore_errors=True)
