@@ -188,3 +188,30 @@ def test_shuffled_cache_reads_permute_blocks_and_records(tmp_path):
     assert sorted(e1) == list(range(30))
     assert all(len({v // 10 for v in e1[10 * k:10 * k + 10]}) == 1 for k in range(3))
     a.close()
+
+
+def test_large_blocks_are_read_by_several_threads_and_one_block_ahead(tmp_path):
+    """A block of a few hundred file records goes through the parallel readers (small blocks are read by the calling thread):
+    same records, same order; the cache written from it reads back the same; a file that disappears is reported by the call
+    that needs its block, with the reference's message, and the stream does not hang."""
+    n = 600
+    cache = tmp_path / "cache"
+    cache.mkdir()
+    cfg = {"manifest_filename": write_manifest(tmp_path, n, files=True), "manifest_root": str(tmp_path), "batch_size": 8,
+           "block_size": 250}
+    a = Stream(cfg)
+    first = a.take(2 * n)
+    assert ids(first) == list(range(n)) * 2 and first[417][0] == b"payload-417" + b"x" * (417 % 3)
+    a.close()
+    b = Stream(dict(cfg, cache_directory=str(cache)))
+    assert b.take(n) == first[:n]            # written to the cache on the way
+    assert b.state()[0] == 3
+    assert b.take(2 * n) == first            # read back from the CPIO blocks by the parallel reader
+    b.close()
+    os.remove(tmp_path / "f300.bin")          # second block of a stream without cache
+    c = Stream(cfg)
+    assert ids(c.take(200)) == list(range(200))
+    from aeon_b200._lib import AeonError
+    with pytest.raises(AeonError, match="error opening file"):
+        c.take(200)
+    c.close()
