@@ -174,6 +174,7 @@ struct aeonb_provider
     std::vector<aeonb::random_engine_t>  engines;
     int                                  slot_cursor = 0;
     std::unique_ptr<aeonb::worker_pool>  pool;
+    std::unique_ptr<aeonb::worker_pool>  plan_pool; // a few threads for the planning pass of the calling thread (SSD patch sampling)
 
     // Every per-batch buffer exists k_sets times, taken in turn (batch t uses set t % k_sets): a batch takes about two
     // kernel periods from its staging upload to its last kernel (upload -> entropy kernel -> back end -> image kernel), so

@@ -610,6 +610,50 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
         return d;
     };
 
+    // ---- 0. SSD records: the annotation and the seeded patch sampling (up to a few hundred trial boxes, each checked
+    // against every ground-truth box: about 20 us per record) are worked out ahead by a few threads.  Every record of a
+    // chunk of decode_size records draws from an engine of its own and this is the only draw of such a record, so the draws
+    // are what the sequential pass would have made.
+    struct ssd_ahead
+    {
+        vector<bbox>       boxes;
+        int                w = 0, h = 0;
+        image_params       params;
+        std::exception_ptr failure;
+    };
+    vector<ssd_ahead> ahead;
+    // (not with lighting: std::normal_distribution keeps half of every pair it draws for the next call, which couples a
+    // record's draws to the record before it)
+    if (nin > 0 && stages[0].kind == stage_kind::ssd && n >= 8 && factory.lighting.stddev() == 0)
+    {
+        if (!plan_pool)
+            plan_pool.reset(new worker_pool(3));
+        ahead.resize(n);
+        const stage& sg = stages[0];
+        for (int first = 0; first < n; first += decode_size)
+        {
+            const int count = std::min(decode_size, n - first);
+            plan_pool->start(count, [&, first](int i) {
+                const int  r = first + i;
+                ssd_ahead& a = ahead[r];
+                try
+                {
+                    if (sizes[(size_t)r * nin] == 0)
+                        return; // reported by the sequential pass, in record order
+                    parse_ssd_annotation(elems[(size_t)r * nin], sizes[(size_t)r * nin], sg.class_map, a.w, a.h, a.boxes);
+                    a.params = factory.make_ssd_params(engines[(slot_cursor + r) % decode_size], a.w, a.h, sg.ssd.width, sg.ssd.height,
+                                                       a.boxes);
+                }
+                catch (...)
+                {
+                    a.failure = std::current_exception();
+                }
+            });
+            plan_pool->help();
+            plan_pool->wait();
+        }
+    }
+
     // ---- 1. sequential planning pass (record order == RNG order)
     for (int r = 0; r < n; ++r)
     {
@@ -747,11 +791,22 @@ void aeonb_provider::plan_records(batch_plan& B, const void* const* elems, const
                     empty("localization_ssd data");
                 vector<bbox> boxes;
                 int          w = 0, h = 0;
-                parse_ssd_annotation(data, size, sg.class_map, w, h, boxes);
-                if (!have_params)
+                if (s == 0 && !ahead.empty())
                 {
-                    params      = factory.make_ssd_params(engine, w, h, sg.ssd.width, sg.ssd.height, boxes);
+                    if (ahead[r].failure)
+                        std::rethrow_exception(ahead[r].failure);
+                    boxes.swap(ahead[r].boxes);
+                    params      = ahead[r].params; // the first stage of the record: nothing has drawn parameters yet
                     have_params = true;
+                }
+                else
+                {
+                    parse_ssd_annotation(data, size, sg.class_map, w, h, boxes);
+                    if (!have_params)
+                    {
+                        params      = factory.make_ssd_params(engine, w, h, sg.ssd.width, sg.ssd.height, boxes);
+                        have_params = true;
+                    }
                 }
                 vector<bbox> gt = transform_boxes_for_ssd(boxes, params);
                 const int    o  = sg.first_output;
