@@ -282,7 +282,8 @@ void aeonb_provider::check_entropy_status(int slot)
     m_status_count[slot]  = 0;
     for (int i = 0; i < count; ++i)
         if (status[i] != 0)
-            throw error(AEONB_ERR_DECODE, "Decoding image failed due to invalid data in the image file. (entropy-coded data)");
+            throw error(AEONB_ERR_DECODE, "Decoding image failed due to invalid data in the image file. (entropy-coded data of picture " +
+                                              std::to_string(i) + " of the batch)");
 }
 
 void aeonb_provider::run(const void* const* elems, const size_t* sizes, int n, void* const* outs, bool on_device, bool wait)

@@ -577,7 +577,9 @@ namespace aeonb
             const uint32_t rows    = NCHECK * check_stride;
             uint32_t*      slot    = chk;
             uint32_t       old_key = !WRITE && compare ? chk[0] : 0xffffffffu;
-            if (WRITE)
+            // A checkpoint at or past the segment's end is never taken: a run can step over it with its last symbol or stop short
+            // of it, so what is noted there could be left from an older run than the one whose block count goes with it.
+            if (WRITE || check_at >= pend)
                 check_at = 0xffffffffu;
             // The bits under p: `n` of them (33 to 64) at the top of `acc`; `next` is word `wp` of the copy, loaded a pass ahead.
             uint32_t wp   = (p >> 5) + 2;
@@ -661,7 +663,7 @@ namespace aeonb
                     slot[0]    = key;
                     slot[rows] = blocks;
                     slot += check_stride;
-                    const bool more = slot < chk + rows;
+                    const bool more = slot < chk + rows && check_at + check_step < pend;
                     check_at        = more ? check_at + check_step : 0xffffffffu;     // past the last checkpoint: none left
                     old_key         = more && compare ? slot[0] : 0xffffffffu;        // fetched now, wanted at the next checkpoint
                 }

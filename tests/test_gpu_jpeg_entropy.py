@@ -136,3 +136,24 @@ def test_device_decoder_against_the_oracle_planes(ctx, golden_dir, parallel):
         for c in range(info.ncomp):
             mine = planes[c].cpu().numpy().reshape(info.blocks_h[c], info.blocks_w[c], 8, 8).transpose(0, 1, 3, 2)  # column-major blocks
             assert np.array_equal(mine, co.blocks[c]), (i, c)
+
+
+def test_streams_with_more_segments_than_the_smallest_segment_allows(ctx, golden_dir):
+    """Streams longer than threads x smallest segment get longer segments, and their last, short segment can end a few
+    bits before a checkpoint position.  The fixture is a 90 KB stream of the benchmark's generator (507 segments of 176
+    bytes) whose last segment ends 8 bits before its second checkpoint: a run that stepped over that position with its
+    last symbol once left a note there that a later run fell into step with, and the stream was reported as malformed
+    although every coefficient was right."""
+    blob = open(os.path.join(golden_dir, "entropy_stream_507_segments.jpg"), "rb").read()
+    check(ctx, [blob])
+    info = host_planes(blob)[0]
+    mcux, mcuy = info.blocks_w[0] // info.hs[0], info.blocks_h[0] // info.vs[0]
+    check(ctx, [blob] * 4, rois=[(0, 0, mcux, mcuy), (3, 5, mcux - 2, mcuy), (0, mcuy - 1, mcux, mcuy), (0, 0, mcux, mcuy - 1)])
+    rng = np.random.default_rng(77)
+    big = []
+    for k in range(24):   # 84-140 KB: segments of 164 to 280 bytes, last segments of every length
+        h, w = int(rng.integers(440, 513)), int(rng.integers(440, 513))
+        img = np.clip(gradient_image(rng, h, w).astype(np.int16) + rng.integers(-28 - k, 29 + k, (h, w, 3)), 0, 255).astype(np.uint8)
+        big.append(jpeg_bytes(img, 92))
+    assert min(len(b) for b in big) > 84000
+    check(ctx, big)
