@@ -294,17 +294,19 @@ def resident_batches(ctx, recs, batch, on_dev, out, keep):
     """Descriptor sets for the headline configuration with every input of the kernels resident in HBM: per batch the
     entropy descriptors (compressed scans + tables; `on_dev`) or host-decoded coefficient planes, the back-end descriptors
     and the image descriptors, built the way the provider builds them (region decoding, seeded draws).  Returns
-    (batches, check) where check = (device plane, host-decoded plane) of one component for a cross-check."""
+    (batches, check, statuses) where check = (device plane, host-decoded plane) of one component for a cross-check and
+    statuses = the entropy decoder's status words of every batch."""
     import torch
     from aeon_b200 import _lib as L, kernels as K
     lib, dev = ctx.lib, torch.device("cuda", ctx.device)
     aug = WORKLOADS[HEADLINE]["augmentation"][0]
     OUT = 224
-    batches, check = [], None
+    batches, check, statuses = [], None, []
     for b in range(len(recs) // batch):
         jd, idesc, ed = (L.JpegDesc * batch)(), (L.ImageDesc * batch)(), (L.EntropyDesc * batch)()
         status = torch.zeros(batch, dtype=torch.int32, device=dev)
         keep.append(status)
+        statuses.append(status)
         ent_bytes = 0
         infos = [K.jpeg_parse(recs[b * batch + i][0]) for i in range(batch)]
         ws, hs = (C.c_int32 * batch)(*[i.width for i in infos]), (C.c_int32 * batch)(*[i.height for i in infos])
@@ -369,7 +371,7 @@ def resident_batches(ctx, recs, batch, on_dev, out, keep):
                                                          light, float(p[i, 15])))
             e.dst = out.data_ptr() + i * 3 * OUT * OUT * 4
         batches.append((jd, idesc, ed))
-    return batches, check
+    return batches, check, statuses
 
 
 def summarize(times_ms):
@@ -590,7 +592,7 @@ def main():
     with torch.cuda.stream(ctx.torch_stream):
         out = torch.empty((BATCH, 3, OUT, OUT), dtype=torch.float32, device=dev)
     layout = K.make_layout(OUT, OUT, L.F32, True, True, MEAN, STD)
-    batches, check_plane = resident_batches(ctx, recs, BATCH, on_dev, out, keep)
+    batches, check_plane, statuses = resident_batches(ctx, recs, BATCH, on_dev, out, keep)
     torch.cuda.synchronize()
 
     def kernel_step(c, b):
@@ -605,7 +607,7 @@ def main():
         torch.cuda.synchronize()
         if not np.array_equal(check_plane[0].cpu().numpy(), check_plane[1]):
             raise SystemExit("device entropy decoder disagrees with the host decoder")
-        if keep[0].cpu().numpy().any():   # keep[0]: the first batch's status words
+        if statuses[0].cpu().numpy().any():
             raise SystemExit("device entropy decoder flagged a stream of the synthetic set")
 
     def barrier():
@@ -690,6 +692,8 @@ def main():
     prof = ctx.profile_read()
     ctx.profile(False)
     per_kernel = {k: (v["ms"] / v["launches"], v["algorithmic_bytes"] / v["launches"]) for k, v in prof.items() if v["launches"]}
+    if on_dev and any(bool(st.cpu().numpy().any()) for st in statuses):   # every stream of every batch of the timed steps
+        raise SystemExit("device entropy decoder flagged a stream of the synthetic set")
 
     if args.kernels_only:
         if rank == 0:
